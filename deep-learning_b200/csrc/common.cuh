@@ -1,0 +1,94 @@
+// Internal definitions shared by the kernels and the C ABI of libdlb200.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "dlb200.h"
+
+typedef struct ncclComm *ncclComm_t;
+
+struct dlb_ctx {
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  int *d_status = nullptr;      // sticky device status word
+  void *scratch = nullptr;      // arena for reduction partials / residual planes
+  size_t scratch_bytes = 0;
+  ncclComm_t comm = nullptr;
+  int rank = 0;
+  int world = 1;
+  bool use_tensor_core = true;
+  bool tensor_core_ok = false;  // device is sm_100
+  uint64_t launches = 0;
+};
+
+namespace dlb {
+
+void set_error(const char *fmt, ...);
+
+#define DLB_CUDA(call)                                                         \
+  do {                                                                         \
+    cudaError_t e__ = (call);                                                  \
+    if (e__ != cudaSuccess) {                                                  \
+      dlb::set_error("%s:%d %s: %s", __FILE__, __LINE__, #call,                \
+                     cudaGetErrorString(e__));                                 \
+      return DLB_ERR_CUDA;                                                     \
+    }                                                                          \
+  } while (0)
+
+#define DLB_REQUIRE(cond, what)                                                \
+  do {                                                                         \
+    if (!(cond)) {                                                             \
+      dlb::set_error("%s:%d invalid argument: %s", __FILE__, __LINE__, what);  \
+      return DLB_ERR_INVALID;                                                  \
+    }                                                                          \
+  } while (0)
+
+#define DLB_TRY(expr)                                                          \
+  do {                                                                         \
+    dlb_status s__ = (expr);                                                   \
+    if (s__ != DLB_OK) return s__;                                             \
+  } while (0)
+
+// After a kernel launch: count it and surface launch-configuration errors.
+#define DLB_LAUNCHED(ctx)                                                      \
+  do {                                                                         \
+    (ctx)->launches++;                                                         \
+    DLB_CUDA(cudaGetLastError());                                              \
+  } while (0)
+
+// Returns at least `bytes` of 256-byte aligned scratch, growing the arena if
+// needed (growth synchronises the stream; steady state never grows).
+dlb_status scratch(dlb_ctx *ctx, size_t bytes, void **out);
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// GEMM C[m,n] (+)= sum_k A(m,k) * B(n,k) with element strides; the three FC
+// products are three stride assignments of this one contract.
+struct GemmOperand {
+  const float *ptr;     // fp32 values (what the tensor core sees truncated)
+  const float *lo;      // TF32 residual plane or nullptr
+  long long stride_mn;  // elements between consecutive m (or n)
+  long long stride_k;   // elements between consecutive k
+};
+struct GemmEpilogue {
+  const float *bias = nullptr;   // per-n bias added to every row
+  float *colsum = nullptr;       // per-n sum over m of C (db), written/accumulated
+  int accumulate = 0;            // C += result
+};
+
+dlb_status gemm(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
+                long long ldc, int M, int N, int K, const GemmEpilogue &ep);
+dlb_status gemm_simt(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
+                     long long ldc, int M, int N, int K, const GemmEpilogue &ep);
+// Returns DLB_ERR_UNSUPPORTED (without touching C) when the shape or alignment
+// is outside what the TMA descriptors can express.
+dlb_status gemm_tcgen05(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
+                        long long ldc, int M, int N, int K, const GemmEpilogue &ep);
+bool gemm_tcgen05_supported(const GemmOperand &A, const GemmOperand &B, const float *C,
+                            long long ldc, int M, int N, int K);
+
+}  // namespace dlb

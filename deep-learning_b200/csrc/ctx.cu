@@ -1,0 +1,345 @@
+// Context, device memory helpers, the GEMM dispatcher behind the three FC entry
+// points, and the NCCL exchange of libdlb200.
+#include <dlfcn.h>
+#include <nccl.h>
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace dlb {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+dlb_status scratch(dlb_ctx *ctx, size_t bytes, void **out) {
+  if (bytes > ctx->scratch_bytes) {
+    // Growing invalidates earlier scratch pointers, so wait for their users.
+    DLB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->scratch) DLB_CUDA(cudaFree(ctx->scratch));
+    ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
+    const size_t want = align_up(bytes + bytes / 4, (size_t)1 << 20);
+    DLB_CUDA(cudaMalloc(&ctx->scratch, want));
+    ctx->scratch_bytes = want;
+  }
+  *out = ctx->scratch;
+  return DLB_OK;
+}
+
+bool gemm_tcgen05_supported(const GemmOperand &, const GemmOperand &, const float *, long long, int,
+                            int, int);
+dlb_status bias_gradient(dlb_ctx *ctx, const float *delta, int rows, int n, float *dbias,
+                         int accumulate);
+
+// Number of elements spanned by an operand stored densely in global memory.
+static size_t operand_elems(const GemmOperand &o, int mn, int k) {
+  if (o.stride_k == 1) return (size_t)(mn - 1) * o.stride_mn + k;
+  return (size_t)(k - 1) * o.stride_k + mn;
+}
+
+dlb_status gemm(dlb_ctx *ctx, const GemmOperand &A_in, const GemmOperand &B_in, float *C,
+                long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
+  GemmOperand A = A_in, B = B_in;
+  // The tensor-core tile is 128 x 256 x 16; below that the CUDA-core kernel
+  // is used, as it is for layouts TMA cannot address.
+  const bool big = (long long)M * N >= 128 * 64 && K >= 32;
+  if (ctx->use_tensor_core && ctx->tensor_core_ok && big &&
+      gemm_tcgen05_supported(A, B, C, ldc, M, N, K)) {
+    // Residual planes the caller did not keep are derived into scratch.
+    const size_t a_n = A.lo ? 0 : align_up(operand_elems(A, M, K), 64);
+    const size_t b_n = B.lo ? 0 : align_up(operand_elems(B, N, K), 64);
+    if (a_n + b_n) {
+      void *scr = nullptr;
+      DLB_TRY(scratch(ctx, (a_n + b_n) * sizeof(float), &scr));
+      float *s = static_cast<float *>(scr);
+      if (!A.lo) {
+        DLB_TRY(dlb_split_tf32(ctx, A.ptr, s, operand_elems(A, M, K)));
+        A.lo = s;
+      }
+      if (!B.lo) {
+        DLB_TRY(dlb_split_tf32(ctx, B.ptr, s + a_n, operand_elems(B, N, K)));
+        B.lo = s + a_n;
+      }
+    }
+    return gemm_tcgen05(ctx, A, B, C, ldc, M, N, K, ep);
+  }
+  return gemm_simt(ctx, A, B, C, ldc, M, N, K, ep);
+}
+
+// ---- NCCL through dlopen: the library is only needed by multi-GPU runs ------
+struct Nccl {
+  void *handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
+                            cudaStream_t) = nullptr;
+  const char *(*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+static Nccl *nccl() {
+  static Nccl n;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    n.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!n.handle) n.handle = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (n.handle) {
+      n.GetUniqueId = (decltype(n.GetUniqueId))dlsym(n.handle, "ncclGetUniqueId");
+      n.CommInitRank = (decltype(n.CommInitRank))dlsym(n.handle, "ncclCommInitRank");
+      n.CommDestroy = (decltype(n.CommDestroy))dlsym(n.handle, "ncclCommDestroy");
+      n.AllReduce = (decltype(n.AllReduce))dlsym(n.handle, "ncclAllReduce");
+      n.GetErrorString = (decltype(n.GetErrorString))dlsym(n.handle, "ncclGetErrorString");
+    }
+  }
+  if (!n.handle || !n.GetUniqueId || !n.CommInitRank || !n.AllReduce) return nullptr;
+  return &n;
+}
+
+#define DLB_NCCL(call)                                                              \
+  do {                                                                              \
+    ncclResult_t r__ = (call);                                                      \
+    if (r__ != ncclSuccess) {                                                       \
+      dlb::set_error("%s:%d %s: %s", __FILE__, __LINE__, #call,                     \
+                     nccl()->GetErrorString ? nccl()->GetErrorString(r__) : "nccl"); \
+      return DLB_ERR_COMM;                                                          \
+    }                                                                               \
+  } while (0)
+
+}  // namespace dlb
+
+using namespace dlb;
+
+extern "C" {
+
+const char *dlb_status_string(dlb_status s) {
+  switch (s) {
+    case DLB_OK: return "ok";
+    case DLB_ERR_INVALID: return "invalid argument";
+    case DLB_ERR_CUDA: return "CUDA error";
+    case DLB_ERR_UNSUPPORTED: return "outside the supported path";
+    case DLB_ERR_TIMEOUT: return "device-side wait timed out";
+    case DLB_ERR_COMM: return "NCCL error";
+    case DLB_ERR_NO_DEVICE: return "no sm_100 CUDA device (this library has no CPU path)";
+    default: return "unknown status";
+  }
+}
+
+const char *dlb_last_error(void) { return g_error; }
+
+int dlb_version(void) { return 100; }
+
+dlb_status dlb_ctx_create(dlb_ctx **out, int device) {
+  DLB_REQUIRE(out, "dlb_ctx_create: null");
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0 || device < 0 || device >= count) {
+    cudaGetLastError();
+    set_error("dlb_ctx_create: CUDA device %d is not available (%d devices); libdlb200 has no CPU path",
+              device, count);
+    return DLB_ERR_NO_DEVICE;
+  }
+  cudaDeviceProp prop;
+  DLB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    set_error("dlb_ctx_create: device %d is sm_%d%d; the kernels are built for sm_100a only", device,
+              prop.major, prop.minor);
+    return DLB_ERR_NO_DEVICE;
+  }
+  DLB_CUDA(cudaSetDevice(device));
+  dlb_ctx *ctx = new dlb_ctx;
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  ctx->tensor_core_ok = true;
+  if (const char *e = getenv("DLB_TENSOR_CORE")) ctx->use_tensor_core = atoi(e) != 0;
+  cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMalloc(&ctx->d_status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(int));
+  if (e != cudaSuccess) {
+    set_error("dlb_ctx_create: %s", cudaGetErrorString(e));
+    delete ctx;
+    return DLB_ERR_CUDA;
+  }
+  *out = ctx;
+  return DLB_OK;
+}
+
+dlb_status dlb_ctx_destroy(dlb_ctx *ctx) {
+  if (!ctx) return DLB_OK;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (ctx->comm && nccl() && nccl()->CommDestroy) nccl()->CommDestroy(ctx->comm);
+  if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return DLB_OK;
+}
+
+dlb_status dlb_ctx_sync(dlb_ctx *ctx, int *device_status) {
+  DLB_REQUIRE(ctx, "dlb_ctx_sync: null");
+  int st = 0;
+  DLB_CUDA(cudaMemcpyAsync(&st, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  DLB_CUDA(cudaStreamSynchronize(ctx->stream));
+  if (device_status) *device_status = st;
+  if (st != DLB_OK) {
+    set_error("a kernel reported device status %d (%s)", st, dlb_status_string(st));
+    return st;
+  }
+  return DLB_OK;
+}
+
+void *dlb_ctx_stream(dlb_ctx *ctx) { return ctx ? ctx->stream : nullptr; }
+
+dlb_status dlb_ctx_set_tensor_core(dlb_ctx *ctx, int enable) {
+  DLB_REQUIRE(ctx, "dlb_ctx_set_tensor_core: null");
+  ctx->use_tensor_core = enable != 0;
+  return DLB_OK;
+}
+
+uint64_t dlb_ctx_launch_count(dlb_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+dlb_status dlb_malloc(dlb_ctx *ctx, void **dev_ptr, size_t bytes) {
+  DLB_REQUIRE(ctx && dev_ptr, "dlb_malloc: null");
+  DLB_CUDA(cudaSetDevice(ctx->device));
+  DLB_CUDA(cudaMalloc(dev_ptr, bytes ? bytes : 16));
+  return DLB_OK;
+}
+
+dlb_status dlb_free(dlb_ctx *ctx, void *dev_ptr) {
+  DLB_REQUIRE(ctx, "dlb_free: null");
+  if (!dev_ptr) return DLB_OK;
+  DLB_CUDA(cudaStreamSynchronize(ctx->stream));
+  DLB_CUDA(cudaFree(dev_ptr));
+  return DLB_OK;
+}
+
+dlb_status dlb_memset(dlb_ctx *ctx, void *dev_ptr, int value, size_t bytes) {
+  DLB_REQUIRE(ctx && dev_ptr, "dlb_memset: null");
+  DLB_CUDA(cudaMemsetAsync(dev_ptr, value, bytes, ctx->stream));
+  return DLB_OK;
+}
+
+dlb_status dlb_memcpy_h2d(dlb_ctx *ctx, void *dev_dst, const void *host_src, size_t bytes) {
+  DLB_REQUIRE(ctx && dev_dst && host_src, "dlb_memcpy_h2d: null");
+  DLB_CUDA(cudaMemcpyAsync(dev_dst, host_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return DLB_OK;
+}
+
+dlb_status dlb_memcpy_d2h(dlb_ctx *ctx, void *host_dst, const void *dev_src, size_t bytes) {
+  DLB_REQUIRE(ctx && host_dst && dev_src, "dlb_memcpy_d2h: null");
+  DLB_CUDA(cudaMemcpyAsync(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  DLB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return DLB_OK;
+}
+
+dlb_status dlb_memcpy_d2d(dlb_ctx *ctx, void *dev_dst, const void *dev_src, size_t bytes) {
+  DLB_REQUIRE(ctx && dev_dst && dev_src, "dlb_memcpy_d2d: null");
+  DLB_CUDA(cudaMemcpyAsync(dev_dst, dev_src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  return DLB_OK;
+}
+
+dlb_status dlb_host_alloc(void **host_ptr, size_t bytes) {
+  DLB_REQUIRE(host_ptr, "dlb_host_alloc: null");
+  DLB_CUDA(cudaMallocHost(host_ptr, bytes ? bytes : 16));
+  return DLB_OK;
+}
+
+dlb_status dlb_host_free(void *host_ptr) {
+  if (host_ptr) DLB_CUDA(cudaFreeHost(host_ptr));
+  return DLB_OK;
+}
+
+// ---- FC products --------------------------------------------------------------
+
+dlb_status dlb_fc_forward(dlb_ctx *ctx, const float *X, const float *X_lo, const float *W,
+                          const float *W_lo, const float *bias, float *Z, int rows, int n_in,
+                          int n_out) {
+  DLB_REQUIRE(ctx && X && W && Z && rows > 0 && n_in > 0 && n_out > 0, "dlb_fc_forward");
+  GemmOperand A{X, X_lo, n_in, 1};   // (m=b, k=i)
+  GemmOperand B{W, W_lo, n_in, 1};   // (n=o, k=i)
+  GemmEpilogue ep;
+  ep.bias = bias;
+  return gemm(ctx, A, B, Z, n_out, rows, n_out, n_in, ep);
+}
+
+dlb_status dlb_fc_backward_input(dlb_ctx *ctx, const float *delta, const float *delta_lo,
+                                 const float *W, const float *W_lo, float *dX, int rows,
+                                 int n_in, int n_out) {
+  DLB_REQUIRE(ctx && delta && W && dX && rows > 0 && n_in > 0 && n_out > 0,
+              "dlb_fc_backward_input");
+  GemmOperand A{delta, delta_lo, n_out, 1};  // (m=b, k=o)
+  GemmOperand B{W, W_lo, 1, n_in};           // (n=i, k=o): W[o,i]
+  GemmEpilogue ep;
+  return gemm(ctx, A, B, dX, n_in, rows, n_in, n_out, ep);
+}
+
+dlb_status dlb_fc_weight_gradient(dlb_ctx *ctx, const float *delta, const float *delta_lo,
+                                  const float *X, const float *X_lo, float *dW, float *dbias,
+                                  int rows, int n_in, int n_out, int accumulate) {
+  DLB_REQUIRE(ctx && delta && X && dW && rows > 0 && n_in > 0 && n_out > 0,
+              "dlb_fc_weight_gradient");
+  GemmOperand A{delta, delta_lo, 1, n_out};  // (m=o, k=b): delta[b,o]
+  GemmOperand B{X, X_lo, 1, n_in};           // (n=i, k=b): X[b,i]
+  GemmEpilogue ep;
+  ep.accumulate = accumulate;
+  DLB_TRY(gemm(ctx, A, B, dW, n_in, n_out, n_in, rows, ep));
+  if (dbias) DLB_TRY(bias_gradient(ctx, delta, rows, n_out, dbias, accumulate));
+  return DLB_OK;
+}
+
+// ---- NCCL -----------------------------------------------------------------------
+
+dlb_status dlb_comm_unique_id(char out_id[128]) {
+  DLB_REQUIRE(out_id, "dlb_comm_unique_id: null");
+  if (!nccl()) {
+    set_error("dlb_comm_unique_id: libnccl.so.2 could not be loaded");
+    return DLB_ERR_COMM;
+  }
+  ncclUniqueId id;
+  static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is 128 bytes");
+  DLB_NCCL(nccl()->GetUniqueId(&id));
+  memcpy(out_id, &id, 128);
+  return DLB_OK;
+}
+
+dlb_status dlb_comm_init(dlb_ctx *ctx, const char id[128], int rank, int world) {
+  DLB_REQUIRE(ctx && id && world >= 1 && rank >= 0 && rank < world, "dlb_comm_init");
+  if (!nccl()) {
+    set_error("dlb_comm_init: libnccl.so.2 could not be loaded");
+    return DLB_ERR_COMM;
+  }
+  DLB_CUDA(cudaSetDevice(ctx->device));
+  ncclUniqueId uid;
+  memcpy(&uid, id, 128);
+  DLB_NCCL(nccl()->CommInitRank(&ctx->comm, world, uid, rank));
+  ctx->rank = rank;
+  ctx->world = world;
+  return DLB_OK;
+}
+
+int dlb_comm_world(dlb_ctx *ctx) { return ctx ? ctx->world : 1; }
+int dlb_comm_rank(dlb_ctx *ctx) { return ctx ? ctx->rank : 0; }
+
+dlb_status dlb_allreduce_f32(dlb_ctx *ctx, float *buf, size_t n) {
+  DLB_REQUIRE(ctx && (buf || n == 0), "dlb_allreduce_f32");
+  if (!ctx->comm || ctx->world == 1 || n == 0) return DLB_OK;
+  DLB_NCCL(nccl()->AllReduce(buf, buf, n, ncclFloat32, ncclSum, ctx->comm, ctx->stream));
+  return DLB_OK;
+}
+
+dlb_status dlb_allreduce_f64(dlb_ctx *ctx, double *buf, size_t n) {
+  DLB_REQUIRE(ctx && (buf || n == 0), "dlb_allreduce_f64");
+  if (!ctx->comm || ctx->world == 1 || n == 0) return DLB_OK;
+  DLB_NCCL(nccl()->AllReduce(buf, buf, n, ncclFloat64, ncclSum, ctx->comm, ctx->stream));
+  return DLB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,671 @@
+// HBM-bound kernels of the fully-connected step: batch-renormalization sums,
+// finalize, normalise + activation + dropout, their backward passes, softmax,
+// output error, and the TF32 residual split.  All are streaming kernels with
+// 128-bit accesses; per-unit (column) reductions go through partials in the
+// context scratch arena and are finished in double in a fixed order, so results
+// do not depend on block scheduling.
+#include "common.cuh"
+#include "math.cuh"
+
+namespace dlb {
+
+// ---------------------------------------------------------------------------
+// Column reductions over a row-major [rows, n] tensor.
+//
+// Grid (column blocks, row chunks).  A block of 256 threads covers 128 columns
+// (32 lanes x float4) and 8 row lanes; each thread walks its rows with stride
+// 8 accumulating NSUM float4 in registers, the 8 row lanes are folded through
+// shared memory in double, and the block writes NSUM x 128 doubles to
+// partials[chunk][s][col].  reduce_partials then sums the chunks in order.
+// ---------------------------------------------------------------------------
+constexpr int CR_LANES_X = 32;
+constexpr int CR_LANES_Y = 8;
+constexpr int CR_COLS = CR_LANES_X * 4;
+
+template <int NSUM, class Op>
+__global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
+    column_reduce_kernel(Op op, int rows, int n, int rows_per_chunk, double *partials) {
+  __shared__ double red[CR_LANES_Y][NSUM][CR_COLS + 1];
+  const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
+  const int col = blockIdx.x * CR_COLS + tx * 4;
+  const int r0 = blockIdx.y * rows_per_chunk;
+  const int r1 = min(rows, r0 + rows_per_chunk);
+  float acc[NSUM][4];
+#pragma unroll
+  for (int s = 0; s < NSUM; ++s)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[s][j] = 0.f;
+
+  if (col < n) {
+    if ((n & 3) == 0) {
+      typename Op::Cols4 c;
+      op.load_cols4(col, c);
+      for (int r = r0 + ty; r < r1; r += CR_LANES_Y) op.row4(r, col, c, acc);
+    } else {
+      for (int j = 0; j < 4 && col + j < n; ++j) {
+        typename Op::Cols1 c;
+        op.load_cols1(col + j, c);
+        float a1[NSUM];
+#pragma unroll
+        for (int s = 0; s < NSUM; ++s) a1[s] = 0.f;
+        for (int r = r0 + ty; r < r1; r += CR_LANES_Y) op.row1(r, col + j, c, a1);
+#pragma unroll
+        for (int s = 0; s < NSUM; ++s) acc[s][j] = a1[s];
+      }
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < NSUM; ++s)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) red[ty][s][tx * 4 + j] = (double)acc[s][j];
+  __syncthreads();
+  // 256 threads fold NSUM*128 columns.
+  for (int i = threadIdx.x; i < NSUM * CR_COLS; i += CR_LANES_X * CR_LANES_Y) {
+    const int s = i / CR_COLS, c = i % CR_COLS;
+    const int gc = blockIdx.x * CR_COLS + c;
+    if (gc < n) {
+      double t = 0.0;
+#pragma unroll
+      for (int y = 0; y < CR_LANES_Y; ++y) t += red[y][s][c];
+      partials[((size_t)blockIdx.y * NSUM + s) * n + gc] = t;
+    }
+  }
+}
+
+__global__ void reduce_partials_kernel(const double *partials, int chunks, int total, double *out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  double t = 0.0;
+  for (int c = 0; c < chunks; ++c) t += partials[(size_t)c * total + i];
+  out[i] = t;
+}
+
+// Chunking of the rows: a few waves of blocks over the SMs, chunks of at least
+// 64 rows.  Shared by the launcher and by callers that place their final sums
+// behind the partials in the same scratch request.
+static void column_reduce_plan(dlb_ctx *ctx, int rows, int n, int *chunks, int *rows_per_chunk) {
+  const int col_blocks = ceil_div(n, CR_COLS);
+  int c = ceil_div(ctx->sm_count * 4, col_blocks);
+  c = max(1, min(c, ceil_div(rows, 64)));
+  *rows_per_chunk = ceil_div(ceil_div(rows, c), CR_LANES_Y) * CR_LANES_Y;
+  *chunks = ceil_div(rows, *rows_per_chunk);
+}
+
+static size_t column_reduce_partial_bytes(dlb_ctx *ctx, int nsum, int rows, int n) {
+  int chunks, rpc;
+  column_reduce_plan(ctx, rows, n, &chunks, &rpc);
+  return align_up((size_t)chunks * nsum * n * sizeof(double), 256);
+}
+
+template <int NSUM, class Op>
+static dlb_status column_reduce(dlb_ctx *ctx, Op op, int rows, int n, double *out) {
+  const int col_blocks = ceil_div(n, CR_COLS);
+  int chunks, rows_per_chunk;
+  column_reduce_plan(ctx, rows, n, &chunks, &rows_per_chunk);
+  void *scr = nullptr;
+  DLB_TRY(scratch(ctx, column_reduce_partial_bytes(ctx, NSUM, rows, n), &scr));
+  double *partials = static_cast<double *>(scr);
+  column_reduce_kernel<NSUM, Op><<<dim3(col_blocks, chunks), CR_LANES_X * CR_LANES_Y, 0,
+                                   ctx->stream>>>(op, rows, n, rows_per_chunk, partials);
+  DLB_LAUNCHED(ctx);
+  const int total = NSUM * n;
+  reduce_partials_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(partials, chunks, total,
+                                                                        out);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+// --- sum(z), sum(z^2) --------------------------------------------------------
+struct SumSqOp {
+  const float *Z;
+  int n;
+  struct Cols4 {};
+  struct Cols1 {};
+  __device__ void load_cols4(int, Cols4 &) const {}
+  __device__ void load_cols1(int, Cols1 &) const {}
+  __device__ void row4(int r, int col, const Cols4 &, float (&acc)[2][4]) const {
+    const float4 z = __ldg(reinterpret_cast<const float4 *>(Z + (size_t)r * n + col));
+    acc[0][0] += z.x; acc[0][1] += z.y; acc[0][2] += z.z; acc[0][3] += z.w;
+    acc[1][0] += z.x * z.x; acc[1][1] += z.y * z.y; acc[1][2] += z.z * z.z; acc[1][3] += z.w * z.w;
+  }
+  __device__ void row1(int r, int col, const Cols1 &, float (&acc)[2]) const {
+    const float z = Z[(size_t)r * n + col];
+    acc[0] += z;
+    acc[1] += z * z;
+  }
+};
+
+// --- sum(x) only (bias gradient) ----------------------------------------------
+struct SumOp {
+  const float *X;
+  int n;
+  struct Cols4 {};
+  struct Cols1 {};
+  __device__ void load_cols4(int, Cols4 &) const {}
+  __device__ void load_cols1(int, Cols1 &) const {}
+  __device__ void row4(int r, int col, const Cols4 &, float (&acc)[1][4]) const {
+    const float4 z = __ldg(reinterpret_cast<const float4 *>(X + (size_t)r * n + col));
+    acc[0][0] += z.x; acc[0][1] += z.y; acc[0][2] += z.z; acc[0][3] += z.w;
+  }
+  __device__ void row1(int r, int col, const Cols1 &, float (&acc)[1]) const {
+    acc[0] += X[(size_t)r * n + col];
+  }
+};
+
+// Per-column constants of a batch-renormalised unit.
+struct BrnCol {
+  float mean, sigma, r, d, gamma, beta;
+};
+struct BrnPtrs {
+  const float *mean, *sigma, *r, *d, *gamma, *beta;
+  __device__ BrnCol at(int c) const {
+    return BrnCol{mean[c], sigma[c], r[c], d[c], gamma[c], beta[c]};
+  }
+};
+static BrnPtrs brn_ptrs(const dlb_brn_unit_arrays *u) {
+  return BrnPtrs{u->mean, u->sigma, u->r, u->d, u->gamma, u->beta};
+}
+
+// value_hat = (z - mean) / sigma * r + d      (fwp_mp.cpp L:4732)
+__device__ __forceinline__ float brn_hat(float z, const BrnCol &c) {
+  return (z - c.mean) / c.sigma * c.r + c.d;
+}
+// value_normalize = gamma * value_hat + beta  (fwp_mp.cpp L:4736)
+__device__ __forceinline__ float brn_norm(float xh, const BrnCol &c) {
+  return c.gamma * xh + c.beta;
+}
+
+// --- activation backward (+ BRN backward sums) --------------------------------
+template <bool NORM>
+struct ActBackwardOp {
+  float *dA;
+  const float *Z, *A;
+  BrnPtrs u;
+  int af, n;
+  struct Cols4 { BrnCol c[4]; };
+  struct Cols1 { BrnCol c; };
+  __device__ void load_cols4(int col, Cols4 &k) const {
+    if (NORM)
+      for (int j = 0; j < 4; ++j) k.c[j] = u.at(col + j);
+  }
+  __device__ void load_cols1(int col, Cols1 &k) const {
+    if (NORM) k.c = u.at(col);
+  }
+  __device__ __forceinline__ float one(float da, float z, float a, const BrnCol &c,
+                                       float *s0, float *s1, float *s2, float *s3) const {
+    float y = z, xh = 0.f;
+    if (NORM) {
+      xh = brn_hat(z, c);
+      y = brn_norm(xh, c);
+    }
+    const float e = da * af_derive(af, y, a);
+    if (NORM) {
+      // bwp_mp.cpp L:1559-1574
+      *s0 += e * xh;
+      *s1 += e;
+      const float eh = e * c.gamma;
+      const float neg_r = -c.r;
+      *s2 += eh * (neg_r / c.sigma);
+      *s3 += eh * (z - c.mean) * (neg_r / (c.sigma * c.sigma));
+    }
+    return e;
+  }
+  __device__ void row4(int r, int col, const Cols4 &k, float (&acc)[4][4]) const {
+    const size_t o = (size_t)r * n + col;
+    float4 da = *reinterpret_cast<const float4 *>(dA + o);
+    const float4 z = __ldg(reinterpret_cast<const float4 *>(Z + o));
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(A + o));
+    da.x = one(da.x, z.x, a.x, k.c[0], &acc[0][0], &acc[1][0], &acc[2][0], &acc[3][0]);
+    da.y = one(da.y, z.y, a.y, k.c[1], &acc[0][1], &acc[1][1], &acc[2][1], &acc[3][1]);
+    da.z = one(da.z, z.z, a.z, k.c[2], &acc[0][2], &acc[1][2], &acc[2][2], &acc[3][2]);
+    da.w = one(da.w, z.w, a.w, k.c[3], &acc[0][3], &acc[1][3], &acc[2][3], &acc[3][3]);
+    *reinterpret_cast<float4 *>(dA + o) = da;
+  }
+  __device__ void row1(int r, int col, const Cols1 &k, float (&acc)[4]) const {
+    const size_t o = (size_t)r * n + col;
+    dA[o] = one(dA[o], Z[o], A[o], k.c, &acc[0], &acc[1], &acc[2], &acc[3]);
+  }
+};
+
+// ---------------------------------------------------------------------------
+// Plain streaming kernels: grid-stride over float4 with a scalar tail path when
+// the row length is not a multiple of 4.
+// ---------------------------------------------------------------------------
+static inline int stream_grid(dlb_ctx *ctx, size_t work_items, int block) {
+  size_t blocks = (work_items + block - 1) / block;
+  size_t cap = (size_t)ctx->sm_count * 16;
+  return (int)max((size_t)1, min(blocks, cap));
+}
+
+__global__ void split_tf32_kernel(const float *__restrict__ x, float *__restrict__ lo, size_t n) {
+  const size_t n4 = n / 4;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i);
+    float4 o;
+    o.x = tf32_lo(v.x); o.y = tf32_lo(v.y); o.z = tf32_lo(v.z); o.w = tf32_lo(v.w);
+    reinterpret_cast<float4 *>(lo)[i] = o;
+  }
+  for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    lo[i] = tf32_lo(x[i]);
+}
+
+struct DropoutDev {
+  int type;
+  float scale;  // inverted Bernoulli: 1 / keep
+  const uint8_t *mask;
+  const float *noise;
+};
+
+__device__ __forceinline__ float apply_dropout(float a, const DropoutDev &dp, int col, size_t idx) {
+  switch (dp.type) {
+    case DLB_DROPOUT_BERNOULLI: return dp.mask[col] ? a : 0.f;                  // fwp_mp.cpp L:4842-4868
+    case DLB_DROPOUT_BERNOULLI_INVERTED: return dp.mask[col] ? a * dp.scale : 0.f;  // L:4809-4840
+    case DLB_DROPOUT_UOUT: return a + a * dp.noise[idx];                         // L:4959-4985
+    default: return a;
+  }
+}
+
+template <bool NORM, bool VEC4>
+__global__ void activation_forward_kernel(const float *__restrict__ Z, BrnPtrs u, int af,
+                                          DropoutDev dp, float *__restrict__ A,
+                                          float *__restrict__ A_lo, int rows, int n) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if (VEC4) {
+    const int n4 = n / 4;
+    const size_t total = (size_t)rows * n4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      const int col = (int)(i % n4) * 4;
+      const float4 z = __ldg(reinterpret_cast<const float4 *>(Z) + i);
+      float zz[4] = {z.x, z.y, z.z, z.w}, out[4], lo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float y = zz[j];
+        if (NORM) {
+          const BrnCol c = u.at(col + j);
+          y = brn_norm(brn_hat(y, c), c);
+        }
+        out[j] = apply_dropout(af_fire(af, y), dp, col + j, i * 4 + j);
+        lo[j] = tf32_lo(out[j]);
+      }
+      reinterpret_cast<float4 *>(A)[i] = make_float4(out[0], out[1], out[2], out[3]);
+      if (A_lo) reinterpret_cast<float4 *>(A_lo)[i] = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
+  } else {
+    const size_t total = (size_t)rows * n;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      const int col = (int)(i % n);
+      float y = Z[i];
+      if (NORM) {
+        const BrnCol c = u.at(col);
+        y = brn_norm(brn_hat(y, c), c);
+      }
+      const float a = apply_dropout(af_fire(af, y), dp, col, i);
+      A[i] = a;
+      if (A_lo) A_lo[i] = tf32_lo(a);
+    }
+  }
+}
+
+// One warp per row.  ref: fwp_mp.cpp L:4772-4807 (max, exp(x-max), * 1/sum).
+__global__ void softmax_forward_kernel(const float *__restrict__ Z, float *__restrict__ Q, int rows,
+                                       int n) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
+  if (warp >= rows) return;
+  const float *z = Z + (size_t)warp * n;
+  float *q = Q + (size_t)warp * n;
+  float mx = -3.402823466e+38f;
+  for (int i = lane; i < n; i += 32) mx = fmaxf(mx, z[i]);
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  for (int i = lane; i < n; i += 32) {
+    const float e = expf(z[i] - mx);
+    q[i] = e;
+    sum += e;
+  }
+  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.f / sum;
+  for (int i = lane; i < n; i += 32) q[i] *= inv;
+}
+
+template <bool VEC4>
+__global__ void brn_backward_apply_kernel(float *__restrict__ delta, float *__restrict__ delta_lo,
+                                          const float *__restrict__ Z, BrnPtrs u,
+                                          const double *__restrict__ sums, float inv_rows,
+                                          float rows_f, int rows, int n) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const double *d_mean = sums + 2 * (size_t)n, *d_sigma = sums + 3 * (size_t)n;
+  auto one = [&](float e, float z, int col) {
+    const BrnCol c = u.at(col);
+    // bwp_mp.cpp L:1565 (dX_h = dY * scale) then L:1608-1621.
+    float t = e * c.gamma;
+    t *= c.r / c.sigma;
+    t += (float)d_sigma[col] * ((z - c.mean) / (rows_f * c.sigma));
+    t += (float)d_mean[col] * inv_rows;
+    return t;
+  };
+  if (VEC4) {
+    const int n4 = n / 4;
+    const size_t total = (size_t)rows * n4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      const int col = (int)(i % n4) * 4;
+      float4 e = reinterpret_cast<const float4 *>(delta)[i];
+      const float4 z = __ldg(reinterpret_cast<const float4 *>(Z) + i);
+      e.x = one(e.x, z.x, col); e.y = one(e.y, z.y, col + 1);
+      e.z = one(e.z, z.z, col + 2); e.w = one(e.w, z.w, col + 3);
+      reinterpret_cast<float4 *>(delta)[i] = e;
+      if (delta_lo)
+        reinterpret_cast<float4 *>(delta_lo)[i] =
+            make_float4(tf32_lo(e.x), tf32_lo(e.y), tf32_lo(e.z), tf32_lo(e.w));
+    }
+  } else {
+    const size_t total = (size_t)rows * n;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      const float t = one(delta[i], Z[i], (int)(i % n));
+      delta[i] = t;
+      if (delta_lo) delta_lo[i] = tf32_lo(t);
+    }
+  }
+}
+
+template <bool VEC4>
+__global__ void activation_backward_plain_kernel(float *__restrict__ dA, const float *__restrict__ Z,
+                                                 const float *__restrict__ A, int af,
+                                                 size_t total) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if (VEC4) {
+    const size_t t4 = total / 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < t4; i += stride) {
+      float4 e = reinterpret_cast<const float4 *>(dA)[i];
+      const float4 z = __ldg(reinterpret_cast<const float4 *>(Z) + i);
+      const float4 a = __ldg(reinterpret_cast<const float4 *>(A) + i);
+      e.x *= af_derive(af, z.x, a.x); e.y *= af_derive(af, z.y, a.y);
+      e.z *= af_derive(af, z.z, a.z); e.w *= af_derive(af, z.w, a.w);
+      reinterpret_cast<float4 *>(dA)[i] = e;
+    }
+  } else {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
+      dA[i] *= af_derive(af, Z[i], A[i]);
+  }
+}
+
+__global__ void brn_finalize_kernel(const double *__restrict__ sums, int n, float batch_scale,
+                                    float momentum, float eps, float r_max, float d_max,
+                                    dlb_brn_unit_arrays u) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= n) return;
+  // fwp_mp.cpp L:4688-4717, in the reference's order: the running averages
+  // move first and r, d are taken from the moved averages.
+  const float mean = (float)sums[h] * batch_scale;
+  float mavg = u.mean_average[h];
+  mavg += momentum * (mean - mavg);
+  const float sigma = sqrtf((float)sums[n + h] * batch_scale - mean * mean + eps);
+  float savg = u.sigma_average[h];
+  savg += momentum * (sigma - savg);
+  u.mean[h] = mean;
+  u.sigma[h] = sigma;
+  u.mean_average[h] = mavg;
+  u.sigma_average[h] = savg;
+  u.r[h] = clipf(sigma / savg, 1.f / r_max, r_max);
+  u.d[h] = clipf((mean - mavg) / savg, -d_max, d_max);
+}
+
+__global__ void sums_to_grads_kernel(const double *__restrict__ sums, int n, float *d_gamma,
+                                     float *d_beta, int accumulate) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= n) return;
+  const float g = (float)sums[h], b = (float)sums[n + h];
+  if (accumulate) {
+    d_gamma[h] += g;
+    d_beta[h] += b;
+  } else {
+    d_gamma[h] = g;
+    d_beta[h] = b;
+  }
+}
+
+__global__ void sums_to_bias_grad_kernel(const double *__restrict__ sums, int n, float *dbias,
+                                         int accumulate) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= n) return;
+  if (accumulate) dbias[h] += (float)sums[h];
+  else dbias[h] = (float)sums[h];
+}
+
+// MSE (or any non-softmax output): delta = f'(x,q) * 2 (q - y) / (N * n_out).
+__global__ void loss_delta_mse_kernel(const float *__restrict__ pre, const float *__restrict__ q,
+                                      const float *__restrict__ y, float *__restrict__ delta,
+                                      float *__restrict__ delta_lo, int af, size_t total,
+                                      float denom, double *loss_sum) {
+  __shared__ double red[8];
+  double local = 0.0;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const float qq = q[i], yy = y[i];
+    const float diff = qq - yy;
+    local += (double)(diff * diff);  // loss_fn: pow(q - y, 2) in float, summed in double
+    float dl = 2.f * diff;
+    dl /= denom;
+    const float e = af_derive(af, pre[i], qq) * dl;
+    delta[i] = e;
+    if (delta_lo) delta_lo[i] = tf32_lo(e);
+  }
+  for (int o = 16; o; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < (int)(blockDim.x / 32); ++w) t += red[w];
+    atomicAdd(loss_sum, t);
+  }
+}
+
+// Softmax + cross-entropy, one warp per row.
+__global__ void loss_delta_softmax_ce_kernel(const float *__restrict__ q, const float *__restrict__ y,
+                                             float *__restrict__ delta, float *__restrict__ delta_lo,
+                                             int rows, int n, float rows_global, double *loss_sum) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
+  double local = 0.0;
+  if (warp < rows) {
+    const float *qr = q + (size_t)warp * n, *yr = y + (size_t)warp * n;
+    const float EPS = 1e-7f;
+    for (int j = lane; j < n; j += 32) {
+      const float qj = qr[j];
+      // delta_j = sum_k (q_j [j==k] - q_k q_j) * L'_k ; L'_k = 0 unless y_k == 1.
+      float e = 0.f;
+      for (int k = 0; k < n; ++k) {
+        if (yr[k] == 1.f) {
+          const float qk = qr[k];
+          float dl = -1.f / clipf(qk, EPS, 1.f - EPS);
+          dl /= rows_global;
+          e += (qj * (j == k ? 1.f : 0.f) - qk * qj) * dl;
+        }
+      }
+      delta[(size_t)warp * n + j] = e;
+      if (delta_lo) delta_lo[(size_t)warp * n + j] = tf32_lo(e);
+      if (yr[j] == 1.f) local += (double)(-(yr[j] * logf(clipf(qj, EPS, 1.f - EPS))));
+    }
+  }
+  for (int o = 16; o; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  if (lane == 0 && local != 0.0) atomicAdd(loss_sum, local);
+}
+
+}  // namespace dlb
+
+using namespace dlb;
+
+extern "C" {
+
+dlb_status dlb_split_tf32(dlb_ctx *ctx, const float *x, float *x_lo, size_t n) {
+  DLB_REQUIRE(ctx && x && x_lo, "dlb_split_tf32: null");
+  if (n == 0) return DLB_OK;
+  DLB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(x_lo) & 15) == 0,
+              "dlb_split_tf32: pointers must be 16-byte aligned");
+  split_tf32_kernel<<<stream_grid(ctx, n / 4 + 1, 256), 256, 0, ctx->stream>>>(x, x_lo, n);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_brn_forward_sums(dlb_ctx *ctx, const float *Z, int rows, int n_units,
+                                double *sums) {
+  DLB_REQUIRE(ctx && Z && sums && rows > 0 && n_units > 0, "dlb_brn_forward_sums");
+  DLB_REQUIRE((n_units & 3) || (reinterpret_cast<uintptr_t>(Z) & 15) == 0,
+              "dlb_brn_forward_sums: Z must be 16-byte aligned");
+  return column_reduce<2>(ctx, SumSqOp{Z, n_units}, rows, n_units, sums);
+}
+
+dlb_status dlb_brn_forward_finalize(dlb_ctx *ctx, const double *sums, int global_rows,
+                                    int n_units, float momentum, float epsilon, float r_max,
+                                    float d_max, const dlb_brn_unit_arrays *u) {
+  DLB_REQUIRE(ctx && sums && u && global_rows > 0 && n_units > 0, "dlb_brn_forward_finalize");
+  DLB_REQUIRE(u->mean && u->sigma && u->mean_average && u->sigma_average && u->r && u->d,
+              "dlb_brn_forward_finalize: null unit array");
+  brn_finalize_kernel<<<ceil_div(n_units, 256), 256, 0, ctx->stream>>>(
+      sums, n_units, 1.f / (float)global_rows, momentum, epsilon, r_max, d_max, *u);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_activation_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
+                                  int af, const dlb_dropout_desc *dropout, float *A,
+                                  float *A_lo, int rows, int n_units) {
+  DLB_REQUIRE(ctx && Z && A && rows > 0 && n_units > 0, "dlb_activation_forward");
+  DropoutDev dp{DLB_DROPOUT_NONE, 1.f, nullptr, nullptr};
+  if (dropout && dropout->type != DLB_DROPOUT_NONE) {
+    dp.type = dropout->type;
+    dp.mask = dropout->mask;
+    dp.noise = dropout->noise;
+    if (dp.type == DLB_DROPOUT_BERNOULLI || dp.type == DLB_DROPOUT_BERNOULLI_INVERTED) {
+      DLB_REQUIRE(dp.mask, "dlb_activation_forward: Bernoulli dropout needs a mask");
+      if (dp.type == DLB_DROPOUT_BERNOULLI_INVERTED) {
+        DLB_REQUIRE(dropout->value > 0.f, "dlb_activation_forward: keep probability");
+        dp.scale = 1.f / dropout->value;
+      }
+    } else if (dp.type == DLB_DROPOUT_UOUT) {
+      DLB_REQUIRE(dp.noise, "dlb_activation_forward: UOut needs noise");
+    } else {
+      set_error("dlb_activation_forward: dropout type %d is not applied here", dp.type);
+      return DLB_ERR_UNSUPPORTED;
+    }
+  }
+  BrnPtrs p{};
+  if (u) p = brn_ptrs(u);
+  const bool vec4 = (n_units % 4 == 0) && ((reinterpret_cast<uintptr_t>(Z) & 15) == 0) &&
+                    ((reinterpret_cast<uintptr_t>(A) & 15) == 0) &&
+                    (!A_lo || (reinterpret_cast<uintptr_t>(A_lo) & 15) == 0);
+  const size_t items = vec4 ? (size_t)rows * (n_units / 4) : (size_t)rows * n_units;
+  const int grid = stream_grid(ctx, items, 256);
+#define LAUNCH(NORM, V)                                                                  \
+  activation_forward_kernel<NORM, V><<<grid, 256, 0, ctx->stream>>>(Z, p, af, dp, A, A_lo, rows, \
+                                                                    n_units)
+  if (u) { if (vec4) LAUNCH(true, true); else LAUNCH(true, false); }
+  else   { if (vec4) LAUNCH(false, true); else LAUNCH(false, false); }
+#undef LAUNCH
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_softmax_forward(dlb_ctx *ctx, const float *Z, float *Q, int rows, int n_units) {
+  DLB_REQUIRE(ctx && Z && Q && rows > 0 && n_units > 0, "dlb_softmax_forward");
+  softmax_forward_kernel<<<ceil_div(rows, 8), 256, 0, ctx->stream>>>(Z, Q, rows, n_units);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_activation_backward(dlb_ctx *ctx, float *dA, const float *Z, const float *A,
+                                   const dlb_brn_unit_arrays *u, int af, int rows, int n_units,
+                                   double *sums) {
+  DLB_REQUIRE(ctx && dA && Z && A && rows > 0 && n_units > 0, "dlb_activation_backward");
+  if (u) {
+    DLB_REQUIRE(sums, "dlb_activation_backward: sums required with batch renormalization");
+    DLB_REQUIRE((n_units & 3) || ((reinterpret_cast<uintptr_t>(dA) | reinterpret_cast<uintptr_t>(Z) |
+                                   reinterpret_cast<uintptr_t>(A)) & 15) == 0,
+                "dlb_activation_backward: tensors must be 16-byte aligned");
+    return column_reduce<4>(ctx, ActBackwardOp<true>{dA, Z, A, brn_ptrs(u), af, n_units}, rows,
+                            n_units, sums);
+  }
+  const size_t total = (size_t)rows * n_units;
+  const bool vec4 = (total % 4 == 0) && ((reinterpret_cast<uintptr_t>(dA) & 15) == 0) &&
+                    ((reinterpret_cast<uintptr_t>(Z) & 15) == 0) &&
+                    ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+  const int grid = stream_grid(ctx, vec4 ? total / 4 : total, 256);
+  if (vec4)
+    activation_backward_plain_kernel<true><<<grid, 256, 0, ctx->stream>>>(dA, Z, A, af, total);
+  else
+    activation_backward_plain_kernel<false><<<grid, 256, 0, ctx->stream>>>(dA, Z, A, af, total);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_brn_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
+                                  const dlb_brn_unit_arrays *u, const double *sums,
+                                  int global_rows, int rows, int n_units) {
+  DLB_REQUIRE(ctx && delta && Z && u && sums && rows > 0 && n_units > 0 && global_rows > 0,
+              "dlb_brn_backward_apply");
+  const bool vec4 = (n_units % 4 == 0) && ((reinterpret_cast<uintptr_t>(Z) & 15) == 0) &&
+                    ((reinterpret_cast<uintptr_t>(delta) & 15) == 0) &&
+                    (!delta_lo || (reinterpret_cast<uintptr_t>(delta_lo) & 15) == 0);
+  const size_t items = vec4 ? (size_t)rows * (n_units / 4) : (size_t)rows * n_units;
+  const int grid = stream_grid(ctx, items, 256);
+  const float nf = (float)global_rows;
+  if (vec4)
+    brn_backward_apply_kernel<true><<<grid, 256, 0, ctx->stream>>>(
+        delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units);
+  else
+    brn_backward_apply_kernel<false><<<grid, 256, 0, ctx->stream>>>(
+        delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_brn_backward_param_grads(dlb_ctx *ctx, const double *sums, int n_units,
+                                        float *d_gamma, float *d_beta, int accumulate) {
+  DLB_REQUIRE(ctx && sums && d_gamma && d_beta && n_units > 0, "dlb_brn_backward_param_grads");
+  sums_to_grads_kernel<<<ceil_div(n_units, 256), 256, 0, ctx->stream>>>(sums, n_units, d_gamma,
+                                                                        d_beta, accumulate);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_loss_delta(dlb_ctx *ctx, int loss, int af, const float *pre, const float *q,
+                          const float *y, float *delta, float *delta_lo, int rows, int n_out,
+                          int global_rows, double *loss_sum) {
+  DLB_REQUIRE(ctx && q && y && delta && loss_sum && rows > 0 && n_out > 0 && global_rows > 0,
+              "dlb_loss_delta");
+  if (loss == DLB_LOSS_MSE && af != DLB_AF_SOFTMAX) {
+    DLB_REQUIRE(pre, "dlb_loss_delta: pre-activation values required");
+    const size_t total = (size_t)rows * n_out;
+    // loss_fn_derivative divides by static_cast<real>(bs * n_out).
+    const float denom = (float)((size_t)global_rows * (size_t)n_out);
+    loss_delta_mse_kernel<<<stream_grid(ctx, total, 256), 256, 0, ctx->stream>>>(
+        pre, q, y, delta, delta_lo, af, total, denom, loss_sum);
+    DLB_LAUNCHED(ctx);
+    return DLB_OK;
+  }
+  if (loss == DLB_LOSS_CROSS_ENTROPY && af == DLB_AF_SOFTMAX) {
+    loss_delta_softmax_ce_kernel<<<ceil_div(rows, 8), 256, 0, ctx->stream>>>(
+        q, y, delta, delta_lo, rows, n_out, (float)global_rows, loss_sum);
+    DLB_LAUNCHED(ctx);
+    return DLB_OK;
+  }
+  set_error("dlb_loss_delta: loss %d with activation %d is outside the supported path", loss, af);
+  return DLB_ERR_UNSUPPORTED;
+}
+
+}  // extern "C"
+
+namespace dlb {
+// Column sum of delta into the bias gradient (used by dlb_fc_weight_gradient).
+dlb_status bias_gradient(dlb_ctx *ctx, const float *delta, int rows, int n, float *dbias,
+                         int accumulate) {
+  void *scr = nullptr;
+  const size_t partial_bytes = column_reduce_partial_bytes(ctx, 1, rows, n);
+  DLB_TRY(scratch(ctx, partial_bytes + (size_t)n * sizeof(double), &scr));
+  double *out = reinterpret_cast<double *>(static_cast<char *>(scr) + partial_bytes);
+  DLB_TRY(column_reduce<1>(ctx, SumOp{delta, n}, rows, n, out));
+  sums_to_bias_grad_kernel<<<ceil_div(n, 256), 256, 0, ctx->stream>>>(out, n, dbias, accumulate);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+}  // namespace dlb

@@ -1,0 +1,510 @@
+// FC GEMM on Blackwell tensor cores (sm_100a): C[m,n] (+)= sum_k A(m,k) B(n,k).
+//
+// fp32-faithful product by TF32 splitting ("3xTF32"): every fp32 operand x is
+// used as hi(x) + lo(x), where hi(x) is what a kind::tf32 MMA reads of the raw
+// fp32 word (sign, exponent, top 10 mantissa bits) and lo(x) = x - hi(x) comes
+// from a residual plane in global memory.  Each 8-deep k step issues
+//     D += lo(A) hi(B);  D += hi(A) lo(B);  D += hi(A) hi(B)
+// into one fp32 accumulator in tensor memory.  The dropped lo*lo term is below
+// 2^-20 of the product.
+//
+// One CTA computes a 128 x BN tile.  Warp 0 (one lane) streams operand tiles
+// with TMA (cp.async.bulk.tensor, 128-byte or 64-byte swizzle, no multicast)
+// into a ring of shared-memory stages guarded by full/empty mbarriers; warp 1
+// (one lane) issues tcgen05.mma and commits each stage back to the producer;
+// warps 2-5 drain the accumulator with tcgen05.ld, add the bias, and write
+// rows to global memory through a per-warp shared-memory transpose so that each
+// store instruction covers 128 contiguous bytes.
+//
+// Operand majors.  "K-major": k is the contiguous direction in global memory
+// (X and W in the forward product).  "MN-major": m (or n) is contiguous (W in
+// the input-gradient product, delta and X in the weight-gradient product).  An
+// MN-major tile is fetched through a 3-d view {32 floats, k, mn/32} so that it
+// lands in the canonical layout of 32-float columns of 8-row groups.
+//
+// Every mbarrier wait is bounded by a clock budget; on expiry the kernel writes
+// DLB_ERR_TIMEOUT to the status word, waits (bounded) for its TMA loads in
+// flight, frees its tensor memory and returns.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+
+namespace dlb {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int NUM_THREADS = 192;
+constexpr long long WAIT_BUDGET_CLOCKS = 4000000000LL;  // ~2 s
+constexpr long long DRAIN_BUDGET_CLOCKS = 20000000LL;   // ~10 ms
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false if the budget ran out or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          int *status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > WAIT_BUDGET_CLOCKS) {
+        *abort_flag = 1;
+        atomicExch(status, DLB_ERR_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem], single-CTA, TF32 inputs, fp32 accumulate.
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// mbarrier arrives when all previously issued MMAs of this thread are done.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format, version 1).
+//   [0,14) start address >> 4   [16,30) leading byte offset >> 4
+//   [32,46) stride byte offset >> 4   [46,48) version   [61,64) swizzle mode
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes,
+                                                   uint32_t sbo_bytes, uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)layout_type << 61;
+  return d;
+}
+
+constexpr uint32_t LAYOUT_SW128 = 2, LAYOUT_SW64 = 4;
+
+template <int BN, int BK, int STAGES>
+struct SmemPlan {
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int EPI_BYTES = 4 * 32 * 33 * 4;  // per-warp 32x33 transpose
+  static constexpr int BAR_OFFSET = RING_BYTES + EPI_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // + alignment slack
+};
+
+template <int BN, int BK, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
+                       const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
+                       float *__restrict__ C, long long ldc, int M, int N, int K,
+                       const float *__restrict__ bias, int accumulate, int *status) {
+  using P = SmemPlan<BN, BK, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  // Swizzled tiles need 1024-byte alignment of each tile base.
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *smem = smem_raw + (base - raw);
+  float *epi = reinterpret_cast<float *>(smem + P::RING_BYTES);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P::BAR_OFFSET);
+  // bars[0..STAGES) full, [STAGES..2*STAGES) empty, [2*STAGES] accumulator ready
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * STAGES + 1);
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2);
+  int *issued_kb = reinterpret_cast<int *>(bars + 2 * STAGES + 3);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int num_kb = (K + BK - 1) / BK;
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES),
+                 acc_bar = smem_u32(bars + 2 * STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    *issued_kb = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    // Whole warp allocates BN columns of tensor memory (power of two >= 32).
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_holder)),
+                 "r"((uint32_t)BN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_acc = *tmem_holder;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, status)) break;
+        const uint32_t fb = full0 + 8 * s;
+        const uint32_t st = base + s * P::STAGE_BYTES;
+        mbar_expect_tx(fb, P::STAGE_BYTES);
+        const int k0 = kb * BK;
+        if (A_MN) {
+          tma_load_3d(st, &tm_a, fb, 0, k0, m0 / 32);
+          tma_load_3d(st + P::A_BYTES, &tm_a_lo, fb, 0, k0, m0 / 32);
+        } else {
+          tma_load_2d(st, &tm_a, fb, k0, m0);
+          tma_load_2d(st + P::A_BYTES, &tm_a_lo, fb, k0, m0);
+        }
+        if (B_MN) {
+          tma_load_3d(st + 2 * P::A_BYTES, &tm_b, fb, 0, k0, n0 / 32);
+          tma_load_3d(st + 2 * P::A_BYTES + P::B_BYTES, &tm_b_lo, fb, 0, k0, n0 / 32);
+        } else {
+          tma_load_2d(st + 2 * P::A_BYTES, &tm_b, fb, k0, n0);
+          tma_load_2d(st + 2 * P::A_BYTES + P::B_BYTES, &tm_b_lo, fb, k0, n0);
+        }
+        *issued_kb = kb + 1;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      // Instruction descriptor: fp32 accumulate, TF32 A and B, majors, N, M.
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
+                             ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(BM >> 4) << 24);
+      // K-major tiles: rows of BK*4 bytes, 8-row groups SBO apart, k step = 32 B
+      // inside the swizzled row.  MN-major tiles: 32-float columns LBO apart,
+      // each a stack of 8-row (1024 B) groups, k step = one group.
+      constexpr uint32_t K_ROW = BK * 4;
+      constexpr uint32_t K_LAYOUT = (BK == 32) ? LAYOUT_SW128 : LAYOUT_SW64;
+      constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, A_SBO = A_MN ? 1024 : 8 * K_ROW;
+      constexpr uint32_t B_LBO = B_MN ? BK * 128 : 16, B_SBO = B_MN ? 1024 : 8 * K_ROW;
+      constexpr uint32_t A_LAYOUT = A_MN ? LAYOUT_SW128 : K_LAYOUT;
+      constexpr uint32_t B_LAYOUT = B_MN ? LAYOUT_SW128 : K_LAYOUT;
+      constexpr uint32_t A_KSTEP = A_MN ? 1024 : 32, B_KSTEP = B_MN ? 1024 : 32;
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        ok = mbar_wait(full0 + 8 * s, ph, abort_flag, status);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t st = base + s * P::STAGE_BYTES;
+        const uint32_t a_hi = st, a_lo = st + P::A_BYTES, b_hi = st + 2 * P::A_BYTES,
+                       b_lo = st + 2 * P::A_BYTES + P::B_BYTES;
+#pragma unroll
+        for (int k8 = 0; k8 < BK / 8; ++k8) {
+          const uint64_t da_hi = make_smem_desc(a_hi + k8 * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+          const uint64_t da_lo = make_smem_desc(a_lo + k8 * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+          const uint64_t db_hi = make_smem_desc(b_hi + k8 * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+          const uint64_t db_lo = make_smem_desc(b_lo + k8 * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+          umma_tf32(tmem_acc, da_lo, db_hi, idesc, (kb | k8) != 0 ? 1u : 0u);
+          umma_tf32(tmem_acc, da_hi, db_lo, idesc, 1u);
+          umma_tf32(tmem_acc, da_hi, db_hi, idesc, 1u);
+        }
+        umma_commit(empty0 + 8 * s);  // stage reusable once these MMAs retire
+      }
+      if (ok) umma_commit(acc_bar);   // accumulator complete
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5 ----------------
+    const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
+    float *tile = epi + (warp - 2) * 32 * 33;
+    bool ok = true;
+    if (num_kb > 0) ok = mbar_wait(acc_bar, 0, abort_flag, status);
+    ok = __all_sync(0xffffffffu, ok);
+    tcgen05_fence_after();
+    if (ok) {
+      const int row_base = m0 + q * 32;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= N) break;
+        uint32_t v[32];
+        if (num_kb > 0) {
+          const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32);
+          asm volatile(
+              "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+              "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+              "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "
+              "[%32];"
+              : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]),
+                "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+                "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+                "=r"(v[31])
+              : "r"(taddr)
+              : "memory");
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0u;
+        }
+        // lane owns row (row_base + lane): park its 32 values, then each
+        // instruction below stores one row's 32 consecutive floats.
+#pragma unroll
+        for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = __uint_as_float(v[j]);
+        __syncwarp();
+        const int col = col0 + lane;
+        if (col < N) {
+          const float b = bias ? __ldg(bias + col) : 0.f;
+#pragma unroll 4
+          for (int r = 0; r < 32; ++r) {
+            const int row = row_base + r;
+            if (row < M) {
+              float *dst = C + (long long)row * ldc + col;
+              float val = tile[r * 33 + lane] + b;
+              if (accumulate) val += *dst;
+              *dst = val;
+            }
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // Let TMA loads that were already issued land before the CTA's shared
+    // memory is handed to another block.
+    const int issued = *issued_kb;
+    const long long t0 = clock64();
+    for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
+      const int s = kb % STAGES;
+      const uint32_t ph = (kb / STAGES) & 1;
+      while (!mbar_try_wait(full0 + 8 * s, ph)) {
+        if (clock64() - t0 > DRAIN_BUDGET_CLOCKS) break;
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc),
+                 "r"((uint32_t)BN)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// K-major operand: global [mn, k] with row pitch ld; box {BK, rows}.
+bool tmap_k_major(CUtensorMap *m, const float *ptr, uint64_t mn, uint64_t k, uint64_t ld,
+                  uint32_t box_k, uint32_t box_mn) {
+  const cuuint64_t dims[2] = {k, mn};
+  const cuuint64_t strides[1] = {ld * 4};
+  const cuuint32_t box[2] = {box_k, box_mn};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = box_k == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  return encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(ptr), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// MN-major operand: global [k, mn] with row pitch ld, viewed as
+// {32 floats, k, mn/32}; box {32, BK, cols/32} lands as 32-float columns.
+bool tmap_mn_major(CUtensorMap *m, const float *ptr, uint64_t mn, uint64_t k, uint64_t ld,
+                   uint32_t box_k, uint32_t box_mn) {
+  const cuuint64_t dims[3] = {32, k, mn / 32};
+  const cuuint64_t strides[2] = {ld * 4, 128};
+  const cuuint32_t box[3] = {32, box_k, box_mn / 32};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool operand_ok(const GemmOperand &o, int mn, int k) {
+  if (reinterpret_cast<uintptr_t>(o.ptr) & 15) return false;
+  if (o.lo && (reinterpret_cast<uintptr_t>(o.lo) & 15)) return false;
+  if (o.stride_k == 1) return o.stride_mn % 4 == 0 && o.stride_mn >= k;
+  if (o.stride_mn == 1) return o.stride_k % 4 == 0 && o.stride_k >= mn && mn % 32 == 0;
+  return false;
+}
+
+struct TileConfig {
+  int bn, bk, stages;
+};
+// Selected by DLB_GEMM_TILE=<bn>x<bk>x<stages> for experiments; default below.
+TileConfig tile_config() {
+  static TileConfig cfg = [] {
+    TileConfig c{256, 16, 4};
+    if (const char *e = getenv("DLB_GEMM_TILE")) {
+      int bn, bk, st;
+      if (sscanf(e, "%dx%dx%d", &bn, &bk, &st) == 3) c = TileConfig{bn, bk, st};
+    }
+    return c;
+  }();
+  return cfg;
+}
+
+template <int BN, int BK, int STAGES, bool A_MN, bool B_MN>
+dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
+                  long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
+  using P = SmemPlan<BN, BK, STAGES>;
+  CUtensorMap ta, tal, tb, tbl;
+  bool ok = true;
+  if (A_MN) {
+    ok &= tmap_mn_major(&ta, A.ptr, M, K, A.stride_k, BK, BM);
+    ok &= tmap_mn_major(&tal, A.lo, M, K, A.stride_k, BK, BM);
+  } else {
+    ok &= tmap_k_major(&ta, A.ptr, M, K, A.stride_mn, BK, BM);
+    ok &= tmap_k_major(&tal, A.lo, M, K, A.stride_mn, BK, BM);
+  }
+  if (B_MN) {
+    ok &= tmap_mn_major(&tb, B.ptr, N, K, B.stride_k, BK, BN);
+    ok &= tmap_mn_major(&tbl, B.lo, N, K, B.stride_k, BK, BN);
+  } else {
+    ok &= tmap_k_major(&tb, B.ptr, N, K, B.stride_mn, BK, BN);
+    ok &= tmap_k_major(&tbl, B.lo, N, K, B.stride_mn, BK, BN);
+  }
+  if (!ok) {
+    set_error("gemm_tcgen05: cuTensorMapEncodeTiled rejected an operand");
+    return DLB_ERR_CUDA;
+  }
+  auto kernel = gemm_tf32x3_kernel<BN, BK, STAGES, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    DLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::TOTAL));
+    attr_set = true;
+  }
+  dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
+  kernel<<<grid, NUM_THREADS, P::TOTAL, ctx->stream>>>(ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias,
+                                                      ep.accumulate, ctx->d_status);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+template <bool A_MN, bool B_MN>
+dlb_status launch_tile(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
+                       long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
+  const TileConfig t = tile_config();
+#define DLB_TILE(TBN, TBK, TST)                               \
+  if (t.bn == (TBN) && t.bk == (TBK) && t.stages == (TST))   \
+    return launch<TBN, TBK, TST, A_MN, B_MN>(ctx, A, B, C, ldc, M, N, K, ep);
+  DLB_TILE(256, 16, 4)
+  DLB_TILE(256, 32, 2)
+  DLB_TILE(128, 32, 3)
+  DLB_TILE(128, 16, 6)
+#undef DLB_TILE
+  set_error("gemm_tcgen05: tile %dx%dx%d is not compiled in", t.bn, t.bk, t.stages);
+  return DLB_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+bool gemm_tcgen05_supported(const GemmOperand &A, const GemmOperand &B, const float *C,
+                            long long ldc, int M, int N, int K) {
+  if (!encode_tiled()) return false;
+  if (M < 1 || N < 1 || K < 1) return false;
+  if (reinterpret_cast<uintptr_t>(C) & 3) return false;
+  if (ldc < N) return false;
+  // MN-major A with K-major B never occurs in the FC step.
+  if (A.stride_mn == 1 && A.stride_k != 1 && B.stride_k == 1 && B.stride_mn != 1) return false;
+  return operand_ok(A, M, K) && operand_ok(B, N, K);
+}
+
+dlb_status gemm_tcgen05(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
+                        long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
+  if (!gemm_tcgen05_supported(A, B, C, ldc, M, N, K) || !A.lo || !B.lo) {
+    set_error("gemm_tcgen05: operand layout outside the TMA path");
+    return DLB_ERR_UNSUPPORTED;
+  }
+  // A dimension of extent 1 along k makes stride_k ambiguous; treat k-contiguous first.
+  const bool a_mn = !(A.stride_k == 1);
+  const bool b_mn = !(B.stride_k == 1);
+  if (!a_mn && !b_mn) return launch_tile<false, false>(ctx, A, B, C, ldc, M, N, K, ep);
+  if (!a_mn && b_mn) return launch_tile<false, true>(ctx, A, B, C, ldc, M, N, K, ep);
+  if (a_mn && b_mn) return launch_tile<true, true>(ctx, A, B, C, ldc, M, N, K, ep);
+  set_error("gemm_tcgen05: MN-major A with K-major B is not instantiated");
+  return DLB_ERR_UNSUPPORTED;
+}
+
+}  // namespace dlb

@@ -1,0 +1,883 @@
+// Host-side Model: the reference's v1::Model construction, parameter layout and
+// step entry points (lib/deep-learning/v1/learner/model.hpp L:752-3384), with
+// every tensor resident in HBM and every numerical step dispatched to the
+// kernels of this library through its C ABI.  No arithmetic of the step runs on
+// the host.
+//
+// Device memory per model:
+//   params, grads, first/second(/hat) moments, and the TF32 residual plane of
+//   the weight block: flat [P] (the reference's ptr_array_parameters order);
+//   per layer and time step: Z (pre-normalisation sums), A (output, after
+//   dropout), A_lo, delta (error w.r.t. Z), delta_lo, all [rows, units];
+//   per normalised layer: mean, sigma, running averages, r, d [T, units];
+//   double sums for the statistics exchanges.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <string.h>
+
+#include <random>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+using namespace dlb;
+
+namespace {
+
+struct LayerRT {
+  int type = 0;
+  size_t units = 0;
+  int af = 0;            // 0 = not set / outside the supported set
+  int norm = DLB_NORM_NONE;
+  int dropout = DLB_DROPOUT_NONE;
+  float dropout_value = 0.f;
+  // Indices into the flat parameter vector.
+  size_t first_conn = 0, last_conn = 0, first_bias = 0, last_bias = 0, first_norm_unit = 0;
+  size_t fan_in = 0;
+  // Device buffers (allocated by ensure_batch).
+  float *Z = nullptr, *A = nullptr, *A_lo = nullptr, *delta = nullptr, *delta_lo = nullptr;
+  float *stats = nullptr;  // mean | sigma | mean_avg | sigma_avg | r | d, each [T*units]
+  uint8_t *mask = nullptr; // [T*units]
+  double *fwd_sums = nullptr, *bwd_sums = nullptr;
+};
+
+struct HParams {
+  float adam_learning_rate = 0.001f, adam_beta1 = 0.9f, adam_beta2 = 0.999f,
+        adam_previous_beta2 = 0.f, adam_epsilon = 1e-8f, adam_gamma = 0.1f,
+        learning_rate_final = 0.1f, learning_gamma = 1e-3f, weight_decay = 0.f,
+        optimizer_time_step = 0.f, epoch_time_step = 1.f;
+  bool use_adam_bias_correction = true;
+  // Model defaults, v1/learner/model.hpp L:3045-3048.
+  float normalization_momentum_average = 0.999f, normalization_epsilon = 1e-5f,
+        brn_r_max = 1.f, brn_d_max = 0.f;
+};
+
+}  // namespace
+
+struct dlb_model {
+  dlb_ctx *ctx = nullptr;
+  std::vector<LayerRT> layers;
+  size_t seq_w = 1, n_time_delay = 0;
+  int model_type = DLB_MODEL_FEEDFORWARD;
+  int loss = 0, optimizer = 0;
+  HParams hp;
+  size_t total_weights = 0, total_bias = 0, total_norm_units = 0, total_parameters = 0;
+  bool any_norm = false;
+  size_t max_batch = 0, alloc_rows = 0, global_rows = 0;
+  unsigned weight_seed = 5489u;
+  std::mt19937 weight_gen;
+  // Flat device vectors.
+  float *params = nullptr, *params_lo = nullptr, *grads = nullptr, *m1 = nullptr, *m2 = nullptr,
+        *m2hat = nullptr;
+  float *input = nullptr, *input_lo = nullptr, *target = nullptr;
+  float *stage_x = nullptr, *stage_y = nullptr;  // pinned
+  size_t stage_x_elems = 0, stage_y_elems = 0;
+  double *loss_sum = nullptr;
+  size_t loss_rows = 0;  // rows accumulated since reset_loss
+  bool params_lo_valid = false;
+};
+
+namespace {
+
+size_t n_in(const dlb_model *m) { return m->layers.front().units; }
+size_t n_out(const dlb_model *m) { return m->layers.back().units; }
+
+dlb_status dev_alloc(dlb_model *m, float **p, size_t elems, bool zero) {
+  if (*p) {
+    DLB_TRY(dlb_free(m->ctx, *p));
+    *p = nullptr;
+  }
+  DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(p), elems * sizeof(float)));
+  if (zero) DLB_TRY(dlb_memset(m->ctx, *p, 0, elems * sizeof(float)));
+  return DLB_OK;
+}
+
+// Parameter layout { W per layer | bias per layer | gamma per unit | beta per
+// unit }; gamma/beta exist for every unit of every layer as soon as one layer
+// is normalised (compile.cpp L:610-695, allocate.cpp L:1150-1176).
+dlb_status layout_parameters(dlb_model *m) {
+  size_t w = 0;
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    LayerRT &l = m->layers[i];
+    l.fan_in = m->layers[i - 1].units;
+    l.first_conn = w;
+    w += l.units * l.fan_in;
+    l.last_conn = w;
+  }
+  m->total_weights = w;
+  size_t b = w;
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    LayerRT &l = m->layers[i];
+    l.first_bias = b;
+    b += l.units;
+    l.last_bias = b;
+  }
+  m->total_bias = b - w;
+  m->any_norm = false;
+  for (auto &l : m->layers) m->any_norm |= l.norm != DLB_NORM_NONE;
+  size_t u = 0;
+  for (auto &l : m->layers) {
+    l.first_norm_unit = u;
+    u += l.units;
+  }
+  m->total_norm_units = m->any_norm ? u : 0;
+  m->total_parameters = m->total_weights + m->total_bias + 2 * m->total_norm_units;
+  return DLB_OK;
+}
+
+size_t gamma_index(const dlb_model *m, const LayerRT &l) {
+  return m->total_weights + m->total_bias + l.first_norm_unit;
+}
+size_t beta_index(const dlb_model *m, const LayerRT &l) {
+  return m->total_weights + m->total_bias + m->total_norm_units + l.first_norm_unit;
+}
+
+// (Re)allocates the flat vectors, keeping existing weights and biases when the
+// normalisation block is added later, as the reference's reallocation does.
+dlb_status allocate_parameters(dlb_model *m) {
+  const size_t old_wb = m->params ? m->total_weights + m->total_bias : 0;
+  std::vector<float> keep;
+  if (m->params && old_wb) {
+    keep.resize(old_wb);
+    DLB_TRY(dlb_memcpy_d2h(m->ctx, keep.data(), m->params, old_wb * sizeof(float)));
+  }
+  DLB_TRY(layout_parameters(m));
+  const size_t P = m->total_parameters;
+  std::vector<float> host(P, 0.f);
+  if (!keep.empty()) memcpy(host.data(), keep.data(), keep.size() * sizeof(float));
+  // gamma = 1, beta = 0 (allocate.cpp L:1485-1507).
+  for (size_t i = 0; i < m->total_norm_units; ++i)
+    host[m->total_weights + m->total_bias + i] = 1.f;
+  DLB_TRY(dev_alloc(m, &m->params, P, false));
+  DLB_TRY(dlb_memcpy_h2d(m->ctx, m->params, host.data(), P * sizeof(float)));
+  DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
+  DLB_TRY(dev_alloc(m, &m->params_lo, m->total_weights ? m->total_weights : 4, true));
+  DLB_TRY(dev_alloc(m, &m->grads, P, true));
+  DLB_TRY(dev_alloc(m, &m->m1, P, true));
+  DLB_TRY(dev_alloc(m, &m->m2, P, true));
+  DLB_TRY(dev_alloc(m, &m->m2hat, P, true));
+  m->params_lo_valid = false;
+  return DLB_OK;
+}
+
+dlb_status free_batch_buffers(dlb_model *m) {
+  for (auto &l : m->layers) {
+    float **bufs[] = {&l.Z, &l.A, &l.A_lo, &l.delta, &l.delta_lo};
+    for (float **b : bufs) {
+      if (*b) DLB_TRY(dlb_free(m->ctx, *b));
+      *b = nullptr;
+    }
+  }
+  float **bufs[] = {&m->input, &m->input_lo, &m->target};
+  for (float **b : bufs) {
+    if (*b) DLB_TRY(dlb_free(m->ctx, *b));
+    *b = nullptr;
+  }
+  m->alloc_rows = 0;
+  return DLB_OK;
+}
+
+dlb_status ensure_norm_state(dlb_model *m) {
+  const size_t T = m->seq_w;
+  for (auto &l : m->layers) {
+    if (l.norm == DLB_NORM_NONE || l.stats) continue;
+    const size_t n = T * l.units;
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.stats), 6 * n * sizeof(float)));
+    std::vector<float> h(6 * n, 0.f);
+    for (size_t i = 0; i < n; ++i) h[3 * n + i] = 1.f;  // running sigma = 1 (allocate.cpp L:1281-1284)
+    DLB_TRY(dlb_memcpy_h2d(m->ctx, l.stats, h.data(), h.size() * sizeof(float)));
+    DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.fwd_sums), 2 * l.units * sizeof(double)));
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.bwd_sums), 4 * l.units * sizeof(double)));
+  }
+  return DLB_OK;
+}
+
+dlb_status ensure_masks(dlb_model *m) {
+  for (auto &l : m->layers) {
+    const bool bern = l.dropout == DLB_DROPOUT_BERNOULLI || l.dropout == DLB_DROPOUT_BERNOULLI_INVERTED;
+    if (!bern || l.mask) continue;
+    const size_t n = m->seq_w * l.units;
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.mask), n));
+    DLB_TRY(dlb_memset(m->ctx, l.mask, 1, n));  // keep everything until a mask is set
+  }
+  return DLB_OK;
+}
+
+// Activation / error buffers for `rows` rows (the reference's
+// update_mem_batch_size, v1/learner/update_size.cpp L:169-205).
+dlb_status ensure_batch(dlb_model *m, size_t rows) {
+  if (!m->params) DLB_TRY(allocate_parameters(m));
+  DLB_TRY(ensure_norm_state(m));
+  DLB_TRY(ensure_masks(m));
+  if (rows <= m->alloc_rows) return DLB_OK;
+  DLB_TRY(free_batch_buffers(m));
+  const size_t T = m->seq_w;
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    LayerRT &l = m->layers[i];
+    const size_t n = T * rows * l.units;
+    DLB_TRY(dev_alloc(m, &l.Z, n, false));
+    DLB_TRY(dev_alloc(m, &l.A, n, false));
+    DLB_TRY(dev_alloc(m, &l.A_lo, n, false));
+    DLB_TRY(dev_alloc(m, &l.delta, n, false));
+    DLB_TRY(dev_alloc(m, &l.delta_lo, n, false));
+  }
+  DLB_TRY(dev_alloc(m, &m->input, T * rows * n_in(m), false));
+  DLB_TRY(dev_alloc(m, &m->input_lo, T * rows * n_in(m), false));
+  DLB_TRY(dev_alloc(m, &m->target, T * rows * n_out(m), false));
+  if (!m->loss_sum) {
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&m->loss_sum), sizeof(double)));
+    DLB_TRY(dlb_memset(m->ctx, m->loss_sum, 0, sizeof(double)));
+  }
+  m->alloc_rows = rows;
+  return DLB_OK;
+}
+
+dlb_brn_unit_arrays unit_arrays(dlb_model *m, LayerRT &l, size_t t) {
+  const size_t n = m->seq_w * l.units;
+  dlb_brn_unit_arrays u;
+  float *s = l.stats + t * l.units;
+  u.mean = s;
+  u.sigma = s + n;
+  u.mean_average = s + 2 * n;
+  u.sigma_average = s + 3 * n;
+  u.r = s + 4 * n;
+  u.d = s + 5 * n;
+  u.gamma = m->params + gamma_index(m, l);
+  u.beta = m->params + beta_index(m, l);
+  return u;
+}
+
+bool af_supported(int af) {
+  switch (af) {
+    case DLB_AF_ELU: case DLB_AF_ISRLU: case DLB_AF_LINEAR: case DLB_AF_LEAKY_RELU:
+    case DLB_AF_RELU: case DLB_AF_SELU: case DLB_AF_SOFTMAX: return true;
+    default: return false;
+  }
+}
+
+dlb_status check_supported(dlb_model *m) {
+  if (m->layers.size() < 2) {
+    set_error("model: compile() has not been called");
+    return DLB_ERR_INVALID;
+  }
+  if (m->seq_w != 1 || m->model_type != DLB_MODEL_FEEDFORWARD) {
+    set_error("model: recurrent models are outside the supported path of this build");
+    return DLB_ERR_UNSUPPORTED;
+  }
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    const LayerRT &l = m->layers[i];
+    if (l.type != DLB_LAYER_FULLY_CONNECTED) {
+      set_error("model: layer %zu has type %d; only fully connected layers are supported", i, l.type);
+      return DLB_ERR_UNSUPPORTED;
+    }
+    if (!af_supported(l.af)) {
+      set_error("model: layer %zu activation %d is outside the supported set "
+                "(the reference's default for a fully connected layer is SIGMOID; set one of "
+                "RELU/LEAKY_RELU/ELU/SELU/ISRLU/LINEAR/SOFTMAX)", i, l.af);
+      return DLB_ERR_UNSUPPORTED;
+    }
+    if (l.af == DLB_AF_SOFTMAX && i + 1 != m->layers.size()) {
+      set_error("model: softmax is only supported on the output layer");
+      return DLB_ERR_UNSUPPORTED;
+    }
+  }
+  return DLB_OK;
+}
+
+dlb_status refresh_weight_residuals(dlb_model *m) {
+  if (m->params_lo_valid || m->total_weights == 0) return DLB_OK;
+  DLB_TRY(dlb_split_tf32(m->ctx, m->params, m->params_lo, m->total_weights));
+  m->params_lo_valid = true;
+  return DLB_OK;
+}
+
+dlb_status forward_layers(dlb_model *m, size_t rows) {
+  DLB_TRY(refresh_weight_residuals(m));
+  const int B = (int)rows;
+  const int Bg = (int)(m->global_rows ? m->global_rows : rows);
+  const float *X = m->input, *X_lo = m->input_lo;
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    LayerRT &l = m->layers[i];
+    const int I = (int)l.fan_in, H = (int)l.units;
+    const bool norm = l.norm != DLB_NORM_NONE;
+    const bool last = i + 1 == m->layers.size();
+    // The bias enters only where there is no normalisation (model.hpp L:708).
+    const float *bias = norm ? nullptr : m->params + l.first_bias;
+    DLB_TRY(dlb_fc_forward(m->ctx, X, X_lo, m->params + l.first_conn, m->params_lo + l.first_conn,
+                           bias, l.Z, B, I, H));
+    dlb_brn_unit_arrays u;
+    if (norm) {
+      u = unit_arrays(m, l, 0);
+      DLB_TRY(dlb_brn_forward_sums(m->ctx, l.Z, B, H, l.fwd_sums));
+      DLB_TRY(dlb_allreduce_f64(m->ctx, l.fwd_sums, 2 * (size_t)H));
+      DLB_TRY(dlb_brn_forward_finalize(m->ctx, l.fwd_sums, Bg, H, m->hp.normalization_momentum_average,
+                                       m->hp.normalization_epsilon, m->hp.brn_r_max,
+                                       m->hp.brn_d_max, &u));
+    }
+    if (l.af == DLB_AF_SOFTMAX) {
+      DLB_TRY(dlb_softmax_forward(m->ctx, l.Z, l.A, B, H));
+    } else {
+      dlb_dropout_desc dp{l.dropout, l.dropout_value, l.mask, nullptr};
+      DLB_TRY(dlb_activation_forward(m->ctx, l.Z, norm ? &u : nullptr, l.af,
+                                     l.dropout != DLB_DROPOUT_NONE ? &dp : nullptr, l.A,
+                                     last ? nullptr : l.A_lo, B, H));
+    }
+    X = l.A;
+    X_lo = l.A_lo;
+  }
+  return DLB_OK;
+}
+
+dlb_status stage_rows(dlb_model *m, float **stage, size_t *stage_elems, size_t rows, size_t width,
+                      const float *const *row_ptrs, float *dev) {
+  const size_t need = rows * width;
+  if (need > *stage_elems) {
+    if (*stage) DLB_TRY(dlb_host_free(*stage));
+    *stage = nullptr;
+    DLB_TRY(dlb_host_alloc(reinterpret_cast<void **>(stage), need * sizeof(float)));
+    *stage_elems = need;
+  }
+  // The previous step's copy out of this staging buffer must have finished.
+  DLB_CUDA(cudaStreamSynchronize(m->ctx->stream));
+  for (size_t r = 0; r < rows; ++r) memcpy(*stage + r * width, row_ptrs[r], width * sizeof(float));
+  return dlb_memcpy_h2d(m->ctx, dev, *stage, need * sizeof(float));
+}
+
+dlb_status stage_block(dlb_model *m, float **stage, size_t *stage_elems, size_t elems,
+                       const float *host, float *dev) {
+  cudaPointerAttributes attr;
+  const bool pinned = cudaPointerGetAttributes(&attr, host) == cudaSuccess &&
+                      attr.type == cudaMemoryTypeHost;
+  cudaGetLastError();
+  if (pinned) return dlb_memcpy_h2d(m->ctx, dev, host, elems * sizeof(float));
+  if (elems > *stage_elems) {
+    if (*stage) DLB_TRY(dlb_host_free(*stage));
+    *stage = nullptr;
+    DLB_TRY(dlb_host_alloc(reinterpret_cast<void **>(stage), elems * sizeof(float)));
+    *stage_elems = elems;
+  }
+  DLB_CUDA(cudaStreamSynchronize(m->ctx->stream));
+  memcpy(*stage, host, elems * sizeof(float));
+  return dlb_memcpy_h2d(m->ctx, dev, *stage, elems * sizeof(float));
+}
+
+LayerRT *layer_at(dlb_model *m, size_t i) { return i < m->layers.size() ? &m->layers[i] : nullptr; }
+
+float *named_array(dlb_model *m, const std::string &n) {
+  if (n == "parameters") return m->params;
+  if (n == "derivatives") return m->grads;
+  if (n == "first_moment") return m->m1;
+  if (n == "second_moment") return m->m2;
+  if (n == "second_moment_hat") return m->m2hat;
+  return nullptr;
+}
+
+int norm_field(const std::string &n) {
+  if (n == "mean") return 0;
+  if (n == "variance") return 1;  // the reference's "variance" arrays hold sigma
+  if (n == "mean_average") return 2;
+  if (n == "variance_average") return 3;
+  if (n == "r_correction") return 4;
+  if (n == "d_correction") return 5;
+  return -1;
+}
+
+}  // namespace
+
+extern "C" {
+
+dlb_status dlb_model_create(dlb_model **out, dlb_ctx *ctx) {
+  DLB_REQUIRE(out && ctx, "dlb_model_create: null");
+  *out = new dlb_model;
+  (*out)->ctx = ctx;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_destroy(dlb_model *m) {
+  if (!m) return DLB_OK;
+  free_batch_buffers(m);
+  for (auto &l : m->layers) {
+    if (l.stats) dlb_free(m->ctx, l.stats);
+    if (l.mask) dlb_free(m->ctx, l.mask);
+    if (l.fwd_sums) dlb_free(m->ctx, l.fwd_sums);
+    if (l.bwd_sums) dlb_free(m->ctx, l.bwd_sums);
+  }
+  float *flat[] = {m->params, m->params_lo, m->grads, m->m1, m->m2, m->m2hat};
+  for (float *p : flat)
+    if (p) dlb_free(m->ctx, p);
+  if (m->loss_sum) dlb_free(m->ctx, m->loss_sum);
+  if (m->stage_x) dlb_host_free(m->stage_x);
+  if (m->stage_y) dlb_host_free(m->stage_y);
+  delete m;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_compile(dlb_model *m, size_t n_layers, size_t seq_w, int model_type,
+                             const int *layer_types, const size_t *layer_units) {
+  DLB_REQUIRE(m && layer_types && layer_units && n_layers >= 2 && seq_w >= 1, "dlb_model_compile");
+  DLB_REQUIRE(m->layers.empty(), "dlb_model_compile: already compiled");
+  m->layers.resize(n_layers);
+  for (size_t i = 0; i < n_layers; ++i) {
+    m->layers[i].type = layer_types[i];
+    m->layers[i].units = layer_units[i];
+    DLB_REQUIRE(layer_units[i] > 0, "dlb_model_compile: empty layer");
+  }
+  m->seq_w = seq_w;
+  m->model_type = model_type;
+  return layout_parameters(m);
+}
+
+dlb_status dlb_model_set_layer_activation_function(dlb_model *m, size_t layer, int af) {
+  DLB_REQUIRE(m && layer_at(m, layer) && layer > 0, "set_layer_activation_function: bad layer");
+  if (!af_supported(af)) {
+    set_error("set_layer_activation_function: activation %d is outside the supported set", af);
+    return DLB_ERR_UNSUPPORTED;
+  }
+  m->layers[layer].af = af;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_set_layer_normalization(dlb_model *m, size_t layer, int norm) {
+  DLB_REQUIRE(m && layer_at(m, layer), "Set__Layer_Normalization: bad layer");
+  // Not on the input or output layer (v1/learner/normalization.cpp L:419-422).
+  DLB_REQUIRE(layer > 0 && layer + 1 < m->layers.size(),
+              "Set__Layer_Normalization: not available on the input or output layer");
+  if (norm != DLB_NORM_NONE && norm != DLB_NORM_BATCH_RENORMALIZATION) {
+    set_error("Set__Layer_Normalization: only batch renormalization is supported (got %d)", norm);
+    return DLB_ERR_UNSUPPORTED;
+  }
+  m->layers[layer].norm = norm;
+  if (m->params) return allocate_parameters(m);
+  return layout_parameters(m);
+}
+
+dlb_status dlb_model_set_dropout(dlb_model *m, size_t layer, int type, float value0,
+                                 int scale_weights) {
+  DLB_REQUIRE(m && layer_at(m, layer), "set_dropout: bad layer");
+  // Not on the output layer (v1/learner/dropout.cpp L:57-60).
+  DLB_REQUIRE(layer + 1 < m->layers.size(), "set_dropout: not available on the output layer");
+  if (type != DLB_DROPOUT_NONE && type != DLB_DROPOUT_BERNOULLI &&
+      type != DLB_DROPOUT_BERNOULLI_INVERTED) {
+    set_error("set_dropout: dropout type %d is outside the supported set of this build", type);
+    return DLB_ERR_UNSUPPORTED;
+  }
+  if (type != DLB_DROPOUT_NONE) DLB_REQUIRE(value0 > 0.f && value0 <= 1.f, "set_dropout: keep probability");
+  if (scale_weights) {
+    set_error("set_dropout: scale_weights=true is not supported (on a fresh layer the reference "
+              "multiplies the layer's weights by 0/keep); pass false");
+    return DLB_ERR_UNSUPPORTED;
+  }
+  m->layers[layer].dropout = type;
+  m->layers[layer].dropout_value = value0;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_set_normalization_momentum_average(dlb_model *m, float v) {
+  DLB_REQUIRE(m, "null");
+  m->hp.normalization_momentum_average = v;
+  return DLB_OK;
+}
+dlb_status dlb_model_set_normalization_epsilon(dlb_model *m, float v) {
+  DLB_REQUIRE(m, "null");
+  m->hp.normalization_epsilon = v;
+  return DLB_OK;
+}
+dlb_status dlb_model_set_brn_r_correction_maximum(dlb_model *m, float v) {
+  DLB_REQUIRE(m, "null");
+  m->hp.brn_r_max = v;
+  return DLB_OK;
+}
+dlb_status dlb_model_set_brn_d_correction_maximum(dlb_model *m, float v) {
+  DLB_REQUIRE(m, "null");
+  m->hp.brn_d_max = v;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_set_loss_fn(dlb_model *m, int loss) {
+  DLB_REQUIRE(m, "null");
+  if (loss != DLB_LOSS_MSE && loss != DLB_LOSS_CROSS_ENTROPY) {
+    set_error("set_loss_fn: loss %d is outside the supported set (MSE, CROSS_ENTROPY)", loss);
+    return DLB_ERR_UNSUPPORTED;
+  }
+  m->loss = loss;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_set_optimizer(dlb_model *m, int optimizer) {
+  DLB_REQUIRE(m, "null");
+  switch (optimizer) {
+    case DLB_OPT_ADABOUND: case DLB_OPT_ADAM: case DLB_OPT_ADAMAX: case DLB_OPT_AMSBOUND:
+    case DLB_OPT_AMSGRAD: case DLB_OPT_NOSADAM:
+      m->optimizer = optimizer;
+      return DLB_OK;
+    default:
+      set_error("set_optimizer: optimizer %d is outside the supported set", optimizer);
+      return DLB_ERR_UNSUPPORTED;
+  }
+}
+
+#define DLB_HPARAMS(X)                                                                       \
+  X(adam_learning_rate) X(adam_beta1) X(adam_beta2) X(adam_previous_beta2) X(adam_epsilon)   \
+  X(adam_gamma) X(learning_rate_final) X(learning_gamma) X(weight_decay)                     \
+  X(optimizer_time_step) X(epoch_time_step)
+
+dlb_status dlb_model_set_hparam(dlb_model *m, const char *name, double value) {
+  DLB_REQUIRE(m && name, "set_hparam: null");
+  const std::string n(name);
+#define X(f) if (n == #f) { m->hp.f = (float)value; return DLB_OK; }
+  DLB_HPARAMS(X)
+#undef X
+  if (n == "use_adam_bias_correction") { m->hp.use_adam_bias_correction = value != 0.0; return DLB_OK; }
+  if (n == "pct_threads") return DLB_OK;  // CPU threading knob of the reference; nothing to set
+  set_error("set_hparam: unknown field %s", name);
+  return DLB_ERR_INVALID;
+}
+
+double dlb_model_get_hparam(dlb_model *m, const char *name) {
+  if (!m || !name) return -1.0;
+  const std::string n(name);
+#define X(f) if (n == #f) return (double)m->hp.f;
+  DLB_HPARAMS(X)
+#undef X
+  if (n == "use_adam_bias_correction") return m->hp.use_adam_bias_correction;
+  return -1.0;
+}
+
+dlb_status dlb_model_set_max_batch_size(dlb_model *m, size_t rows) {
+  DLB_REQUIRE(m && rows > 0, "set_max_batch_size");
+  m->max_batch = rows;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_set_seq_w(dlb_model *m, size_t time_delays) {
+  DLB_REQUIRE(m && time_delays < m->seq_w, "set_seq_w");
+  m->n_time_delay = time_delays;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_seed_weights(dlb_model *m, unsigned seed) {
+  DLB_REQUIRE(m, "null");
+  m->weight_seed = seed;
+  m->weight_gen.seed(seed);
+  return DLB_OK;
+}
+
+// Glorot-uniform draw in parameter order from std::mt19937 through
+// std::uniform_real_distribution<float>, bias 0.
+// ref: Model::initialize_weights_with_glorot_uniform (v1/ops/initializers/glorot.cpp
+// L:27-108, L:226-277).  fan_out is the width of the next layer, and for the
+// output layer fan_out := fan_in.
+dlb_status dlb_model_initialize_weights_with_glorot_uniform(dlb_model *m) {
+  DLB_REQUIRE(m && m->layers.size() >= 2, "glorot: compile first");
+  if (!m->params) DLB_TRY(allocate_parameters(m));
+  std::vector<float> w(m->total_weights + m->total_bias, 0.f);
+  std::uniform_real_distribution<float> dist;
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    const LayerRT &l = m->layers[i];
+    const size_t fan_in = l.fan_in;
+    const size_t fan_out = i + 1 < m->layers.size() ? m->layers[i + 1].units : fan_in;
+    float gain = 1.f, bound;
+    const bool rect = l.af == DLB_AF_RELU || l.af == DLB_AF_LEAKY_RELU || l.af == DLB_AF_SELU;
+    if (l.af == DLB_AF_RELU) gain = sqrtf(2.f);
+    if (l.af == DLB_AF_LEAKY_RELU) gain = sqrtf(2.f / (1.f + powf(0.01f, 2.f)));
+    if (rect) bound = sqrtf(6.f / (float)fan_in);
+    else bound = sqrtf(6.f / (float)(fan_in + fan_out));
+    bound *= gain;
+    dist.param(std::uniform_real_distribution<float>::param_type(-bound, bound));
+    for (size_t k = l.first_conn; k < l.last_conn; ++k) w[k] = dist(m->weight_gen);
+  }
+  DLB_TRY(dlb_memcpy_h2d(m->ctx, m->params, w.data(), w.size() * sizeof(float)));
+  DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
+  m->params_lo_valid = false;
+  return DLB_OK;
+}
+
+size_t dlb_model_get_size(dlb_model *m, const char *name) {
+  if (!m || !name) return (size_t)-1;
+  const std::string n(name);
+  if (n == "total_parameters") return m->total_parameters;
+  if (n == "total_weights") return m->total_weights;
+  if (n == "total_bias") return m->total_bias;
+  if (n == "total_layers") return m->layers.size();
+  if (n == "total_normalized_units") return m->total_norm_units;
+  if (n == "number_threads") return 1;
+  if (n == "batch_size") return m->alloc_rows ? m->alloc_rows : m->max_batch;
+  if (n == "seq_w") return m->seq_w;
+  if (n == "n_time_delay") return m->n_time_delay;
+  if (n == "n_inp") return m->layers.empty() ? 0 : n_in(m);
+  if (n == "n_out") return m->layers.empty() ? 0 : n_out(m);
+  return (size_t)-1;
+}
+
+dlb_status dlb_model_layer_info(dlb_model *m, size_t layer, size_t out[10]) {
+  DLB_REQUIRE(m && out && layer_at(m, layer), "layer_info");
+  const LayerRT &l = m->layers[layer];
+  out[0] = (size_t)l.type;
+  out[1] = l.units;
+  out[2] = l.first_conn;
+  out[3] = l.last_conn;
+  out[4] = l.first_bias;
+  out[5] = l.last_bias;
+  out[6] = (size_t)l.norm;
+  out[7] = (size_t)l.dropout;
+  out[8] = 0;
+  out[9] = m->any_norm ? l.first_norm_unit : 0;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_get_array(dlb_model *m, const char *name, float *host_out, size_t n) {
+  DLB_REQUIRE(m && name && host_out, "get_array: null");
+  if (!m->params) DLB_TRY(allocate_parameters(m));
+  float *p = named_array(m, name);
+  DLB_REQUIRE(p && n <= m->total_parameters, "get_array: unknown name or size");
+  return dlb_memcpy_d2h(m->ctx, host_out, p, n * sizeof(float));
+}
+
+dlb_status dlb_model_set_array(dlb_model *m, const char *name, const float *host_in, size_t n) {
+  DLB_REQUIRE(m && name && host_in, "set_array: null");
+  if (!m->params) DLB_TRY(allocate_parameters(m));
+  float *p = named_array(m, name);
+  DLB_REQUIRE(p && n <= m->total_parameters, "set_array: unknown name or size");
+  DLB_TRY(dlb_memcpy_h2d(m->ctx, p, host_in, n * sizeof(float)));
+  DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
+  if (p == m->params) m->params_lo_valid = false;
+  return DLB_OK;
+}
+
+static dlb_status layer_norm_io(dlb_model *m, size_t layer, const char *name, float *out,
+                                const float *in, size_t n) {
+  DLB_REQUIRE(m && name && layer_at(m, layer), "layer_norm: bad layer");
+  LayerRT &l = m->layers[layer];
+  DLB_REQUIRE(l.norm != DLB_NORM_NONE, "layer_norm: layer is not normalised");
+  if (!m->params) DLB_TRY(allocate_parameters(m));
+  DLB_TRY(ensure_norm_state(m));
+  const std::string nm(name);
+  float *dev = nullptr;
+  size_t count = 0;
+  if (nm == "scale") { dev = m->params + gamma_index(m, l); count = l.units; }
+  else if (nm == "shift") { dev = m->params + beta_index(m, l); count = l.units; }
+  else {
+    const int f = norm_field(nm);
+    DLB_REQUIRE(f >= 0, "layer_norm: unknown field");
+    count = m->seq_w * l.units;
+    dev = l.stats + (size_t)f * count;
+  }
+  DLB_REQUIRE(n == count, "layer_norm: size mismatch");
+  if (out) return dlb_memcpy_d2h(m->ctx, out, dev, n * sizeof(float));
+  DLB_TRY(dlb_memcpy_h2d(m->ctx, dev, in, n * sizeof(float)));
+  return dlb_ctx_sync(m->ctx, nullptr);
+}
+
+dlb_status dlb_model_get_layer_norm(dlb_model *m, size_t layer, const char *name, float *host_out,
+                                    size_t n) {
+  DLB_REQUIRE(host_out, "get_layer_norm: null");
+  return layer_norm_io(m, layer, name, host_out, nullptr, n);
+}
+dlb_status dlb_model_set_layer_norm(dlb_model *m, size_t layer, const char *name,
+                                    const float *host_in, size_t n) {
+  DLB_REQUIRE(host_in, "set_layer_norm: null");
+  return layer_norm_io(m, layer, name, nullptr, host_in, n);
+}
+
+dlb_status dlb_model_set_dropout_mask(dlb_model *m, size_t layer, const uint8_t *host_mask,
+                                      size_t n) {
+  DLB_REQUIRE(m && host_mask && layer_at(m, layer), "set_dropout_mask");
+  LayerRT &l = m->layers[layer];
+  DLB_REQUIRE(n == m->seq_w * l.units, "set_dropout_mask: size mismatch");
+  DLB_TRY(ensure_masks(m));
+  DLB_REQUIRE(l.mask, "set_dropout_mask: layer has no Bernoulli dropout");
+  std::vector<uint8_t> norm01(n);
+  for (size_t i = 0; i < n; ++i) norm01[i] = host_mask[i] ? 1 : 0;
+  DLB_TRY(dlb_memcpy_h2d(m->ctx, l.mask, norm01.data(), n));
+  return dlb_ctx_sync(m->ctx, nullptr);
+}
+
+dlb_status dlb_model_set_global_batch(dlb_model *m, size_t global_rows) {
+  DLB_REQUIRE(m, "null");
+  m->global_rows = global_rows;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_forward_pass_device(dlb_model *m, size_t rows, const float *X_dev) {
+  DLB_REQUIRE(m && X_dev && rows > 0, "forward_pass_device");
+  DLB_TRY(check_supported(m));
+  DLB_TRY(ensure_batch(m, rows));
+  const size_t n = rows * m->seq_w * n_in(m);
+  if (X_dev != m->input) DLB_TRY(dlb_memcpy_d2d(m->ctx, m->input, X_dev, n * sizeof(float)));
+  DLB_TRY(dlb_split_tf32(m->ctx, m->input, m->input_lo, n));
+  return forward_layers(m, rows);
+}
+
+dlb_status dlb_model_forward_pass(dlb_model *m, size_t rows, const float *const *Xm) {
+  DLB_REQUIRE(m && Xm && rows > 0, "forward_pass");
+  DLB_TRY(check_supported(m));
+  DLB_TRY(ensure_batch(m, rows));
+  DLB_TRY(stage_rows(m, &m->stage_x, &m->stage_x_elems, rows, m->seq_w * n_in(m), Xm, m->input));
+  return dlb_model_forward_pass_device(m, rows, m->input);
+}
+
+dlb_status dlb_model_compute_error_device(dlb_model *m, size_t rows, const float *Y_dev) {
+  DLB_REQUIRE(m && Y_dev && rows > 0 && rows <= m->alloc_rows, "compute_error_device");
+  LayerRT &o = m->layers.back();
+  const int Bg = (int)(m->global_rows ? m->global_rows : rows);
+  DLB_TRY(dlb_loss_delta(m->ctx, m->loss, o.af, o.Z, o.A, Y_dev, o.delta, o.delta_lo, (int)rows,
+                         (int)o.units, Bg, m->loss_sum));
+  m->loss_rows += rows;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_compute_error(dlb_model *m, size_t rows, const float *const *Ym) {
+  DLB_REQUIRE(m && Ym && rows > 0 && rows <= m->alloc_rows, "compute_error");
+  DLB_TRY(stage_rows(m, &m->stage_y, &m->stage_y_elems, rows, m->seq_w * n_out(m), Ym, m->target));
+  return dlb_model_compute_error_device(m, rows, m->target);
+}
+
+// ref: Model::FF__Backward_Pass_Batch__OpenMP (v1/learner/bwp_mp.cpp L:28-208):
+// from the output layer down to layer 2; the error into the input layer is
+// never formed.
+dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows) {
+  DLB_REQUIRE(m && rows > 0 && rows <= m->alloc_rows, "backward_pass");
+  const int B = (int)rows;
+  const int Bg = (int)(m->global_rows ? m->global_rows : rows);
+  for (size_t g = m->layers.size() - 1; g >= 2; --g) {
+    LayerRT &next = m->layers[g];
+    LayerRT &l = m->layers[g - 1];
+    const int H = (int)l.units;
+    DLB_TRY(dlb_fc_backward_input(m->ctx, next.delta, next.delta_lo, m->params + next.first_conn,
+                                  m->params_lo + next.first_conn, l.delta, B, H, (int)next.units));
+    if (l.norm != DLB_NORM_NONE) {
+      dlb_brn_unit_arrays u = unit_arrays(m, l, 0);
+      DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, &u, l.af, B, H, l.bwd_sums));
+      // d_gamma / d_beta travel with the gradient all-reduce; d_mean / d_sigma
+      // are needed now, summed over every rank's rows.
+      DLB_TRY(dlb_brn_backward_param_grads(m->ctx, l.bwd_sums, H, m->grads + gamma_index(m, l),
+                                           m->grads + beta_index(m, l), 1));
+      DLB_TRY(dlb_allreduce_f64(m->ctx, l.bwd_sums + 2 * (size_t)H, 2 * (size_t)H));
+      DLB_TRY(dlb_brn_backward_apply(m->ctx, l.delta, l.delta_lo, l.Z, &u, l.bwd_sums, Bg, B, H));
+    } else {
+      DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, nullptr, l.af, B, H, nullptr));
+      DLB_TRY(dlb_split_tf32(m->ctx, l.delta, l.delta_lo, (size_t)B * H));
+    }
+  }
+  return DLB_OK;
+}
+
+// ref: Model::update_derivatives (v1/learner/update_derivative_fwp_mp.cpp L:27-240).
+dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows) {
+  DLB_REQUIRE(m && rows > 0 && rows <= m->alloc_rows, "update_derivatives");
+  const float *X = m->input, *X_lo = m->input_lo;
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    LayerRT &l = m->layers[i];
+    float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
+    DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn,
+                                   dbias, (int)rows, (int)l.fan_in, (int)l.units, 1));
+    X = l.A;
+    X_lo = l.A_lo;
+  }
+  return DLB_OK;
+}
+
+dlb_status dlb_model_merge_derivatives(dlb_model *m) {
+  DLB_REQUIRE(m && m->grads, "merge_derivatives");
+  return dlb_allreduce_f32(m->ctx, m->grads, m->total_parameters);
+}
+
+// ref: Model::update_weights_mp (v1/learner/model.cpp L:4711-4796).
+dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_size) {
+  DLB_REQUIRE(m && m->params && rows > 0 && training_size > 0, "update_weights");
+  if (!m->optimizer) {
+    set_error("update_weights: no optimizer set");
+    return DLB_ERR_INVALID;
+  }
+  if (m->hp.weight_decay != 0.f) {
+    set_error("update_weights: weight decay is outside the supported path of this build");
+    return DLB_ERR_UNSUPPORTED;
+  }
+  const float hyper[8] = {m->hp.adam_learning_rate, m->hp.adam_beta1, m->hp.adam_beta2,
+                          m->hp.adam_epsilon, m->hp.adam_gamma, m->hp.learning_rate_final,
+                          m->hp.learning_gamma, m->hp.use_adam_bias_correction ? 1.f : 0.f};
+  dlb_optimizer_scalars k;
+  DLB_TRY(dlb_optimizer_prepare(m->optimizer, hyper, &m->hp.optimizer_time_step,
+                                &m->hp.adam_previous_beta2, &k));
+  DLB_TRY(dlb_optimizer_step(m->ctx, m->optimizer, &k, m->params, m->grads, m->m1, m->m2, m->m2hat,
+                             nullptr, m->total_parameters));
+  m->params_lo_valid = false;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_reset_loss(dlb_model *m) {
+  DLB_REQUIRE(m, "null");
+  m->loss_rows = 0;
+  if (m->loss_sum) DLB_TRY(dlb_memset(m->ctx, m->loss_sum, 0, sizeof(double)));
+  return DLB_OK;
+}
+
+// MSE: sum / (rows * n_out); cross-entropy: sum / rows (v1/learner/loss.cpp
+// L:158-221), over every rank's rows.
+dlb_status dlb_model_get_loss(dlb_model *m, double *loss) {
+  DLB_REQUIRE(m && loss && m->loss_sum, "get_loss");
+  void *scr = nullptr;
+  DLB_TRY(scratch(m->ctx, sizeof(double), &scr));
+  double *tmp = static_cast<double *>(scr);
+  DLB_TRY(dlb_memcpy_d2d(m->ctx, tmp, m->loss_sum, sizeof(double)));
+  DLB_TRY(dlb_allreduce_f64(m->ctx, tmp, 1));
+  double s = 0.0;
+  DLB_TRY(dlb_memcpy_d2h(m->ctx, &s, tmp, sizeof(double)));
+  const double rows = (double)m->loss_rows * (double)dlb_comm_world(m->ctx);
+  if (rows == 0) { *loss = 1.0; return DLB_OK; }
+  *loss = m->loss == DLB_LOSS_CROSS_ENTROPY ? s / rows : s / (rows * (double)n_out(m));
+  return DLB_OK;
+}
+
+dlb_status dlb_model_train_step_device(dlb_model *m, size_t rows, const float *X_dev,
+                                       const float *Y_dev) {
+  DLB_TRY(dlb_model_reset_loss(m));
+  DLB_TRY(dlb_model_forward_pass_device(m, rows, X_dev));
+  DLB_TRY(dlb_model_compute_error_device(m, rows, Y_dev));
+  DLB_TRY(dlb_model_backward_pass(m, rows));
+  DLB_TRY(dlb_model_update_derivatives(m, rows));
+  DLB_TRY(dlb_model_merge_derivatives(m));
+  const size_t g = m->global_rows ? m->global_rows : rows;
+  return dlb_model_update_weights(m, g, g);
+}
+
+dlb_status dlb_model_train_step(dlb_model *m, size_t rows, const float *X_host,
+                                const float *Y_host, double *loss) {
+  DLB_REQUIRE(m && X_host && Y_host && rows > 0, "train_step");
+  DLB_TRY(check_supported(m));
+  DLB_TRY(ensure_batch(m, rows));
+  DLB_TRY(stage_block(m, &m->stage_x, &m->stage_x_elems, rows * m->seq_w * n_in(m), X_host, m->input));
+  DLB_TRY(stage_block(m, &m->stage_y, &m->stage_y_elems, rows * m->seq_w * n_out(m), Y_host, m->target));
+  DLB_TRY(dlb_model_reset_loss(m));
+  DLB_TRY(dlb_model_forward_pass_device(m, rows, m->input));
+  DLB_TRY(dlb_model_compute_error_device(m, rows, m->target));
+  DLB_TRY(dlb_model_backward_pass(m, rows));
+  DLB_TRY(dlb_model_update_derivatives(m, rows));
+  DLB_TRY(dlb_model_merge_derivatives(m));
+  if (loss) DLB_TRY(dlb_model_get_loss(m, loss));
+  const size_t g = m->global_rows ? m->global_rows : rows;
+  return dlb_model_update_weights(m, g, g);
+}
+
+dlb_status dlb_model_get_layer_outputs(dlb_model *m, size_t layer, size_t rows, float *host_out) {
+  DLB_REQUIRE(m && host_out && layer_at(m, layer) && rows <= m->alloc_rows, "get_layer_outputs");
+  const LayerRT &l = m->layers[layer];
+  const float *src = layer == 0 ? m->input : l.A;
+  DLB_REQUIRE(src, "get_layer_outputs: no forward pass yet");
+  const size_t w = layer == 0 ? n_in(m) : l.units;
+  return dlb_memcpy_d2h(m->ctx, host_out, src, rows * w * m->seq_w * sizeof(float));
+}
+
+dlb_status dlb_model_get_layer_errors(dlb_model *m, size_t layer, size_t rows, int which,
+                                      float *host_out) {
+  DLB_REQUIRE(m && host_out && layer_at(m, layer) && layer > 0 && rows <= m->alloc_rows,
+              "get_layer_errors");
+  (void)which;
+  const LayerRT &l = m->layers[layer];
+  DLB_REQUIRE(l.delta, "get_layer_errors: no backward pass yet");
+  return dlb_memcpy_d2h(m->ctx, host_out, l.delta, rows * l.units * m->seq_w * sizeof(float));
+}
+
+}  // extern "C"

@@ -1,0 +1,187 @@
+// Adam-family update over flat parameter / gradient / moment vectors: one
+// streaming pass with 128-bit loads and stores, the rule chosen at compile time
+// so the inner loop carries no branch on it.  Algorithmic traffic per element:
+// read p, g, m, v and write p, m, v, g<-0 = 32 bytes (Adam, AdaBound, NosAdam,
+// AdaMax); +8 for the running maximum (AMSGrad, AMSBound); +4 for the
+// regularisation mask when weight decay is on.
+#include <math.h>
+
+#include "common.cuh"
+#include "math.cuh"
+
+namespace dlb {
+
+enum Rule { R_ADAM, R_AMSGRAD, R_ADABOUND, R_AMSBOUND, R_ADAMAX };
+
+struct OptState {
+  float p, g, m, v, vh;
+};
+
+// One element.  The arithmetic follows the reference loops term by term
+// (v1/optimizers/adam.cpp L:146-160, amsgrad.cpp, adabound.cpp, amsbound.cpp
+// L:100-120, nosadam.cpp L:86-99); NosAdam is Adam with beta2 replaced by the
+// time-dependent value, which the host passes in `beta2`.
+template <int RULE, bool WD>
+__device__ __forceinline__ void update_one(OptState &s, float mask, const dlb_optimizer_scalars &k) {
+  const float g = s.g;
+  s.m = k.beta1 * s.m + (1.f - k.beta1) * g;
+  if (RULE == R_ADAMAX) {
+    s.v = fmaxf(k.beta2 * s.v, fabsf(g));
+  } else {
+    s.v = k.beta2 * s.v + (1.f - k.beta2) * g * g;
+  }
+  float step;
+  if (RULE == R_ADAM) {
+    step = k.lr_t * s.m / (sqrtf(s.v) + k.epsilon);
+  } else if (RULE == R_AMSGRAD) {
+    s.vh = fmaxf(s.vh, s.v);
+    step = k.lr_t * s.m / (sqrtf(s.vh) + k.epsilon);
+  } else if (RULE == R_ADABOUND) {
+    step = clipf(k.lr_t / (sqrtf(s.v) + k.epsilon), k.lower_bound, k.upper_bound) * s.m;
+  } else if (RULE == R_AMSBOUND) {
+    s.vh = fmaxf(s.vh, s.v);
+    step = clipf(k.lr_t / (sqrtf(s.vh) + k.epsilon), k.lower_bound, k.upper_bound) * s.m;
+  } else {  // AdaMax: lr_t = lr / (1 - beta1^t)
+    step = k.lr_t * s.m / (s.v + k.epsilon);
+  }
+  if (WD) step += mask * k.weight_decay * s.p;
+  s.p -= step;
+  s.g = 0.f;
+}
+
+template <int RULE, bool WD>
+__global__ void __launch_bounds__(256)
+    optimizer_kernel(dlb_optimizer_scalars k, float *__restrict__ p, float *__restrict__ g,
+                     float *__restrict__ m, float *__restrict__ v, float *__restrict__ vh,
+                     const float *__restrict__ mask, size_t n) {
+  constexpr bool HAT = (RULE == R_AMSGRAD || RULE == R_AMSBOUND);
+  const size_t n4 = n / 4;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    float4 P = reinterpret_cast<float4 *>(p)[i];
+    const float4 G = reinterpret_cast<float4 *>(g)[i];
+    float4 M = reinterpret_cast<float4 *>(m)[i];
+    float4 V = reinterpret_cast<float4 *>(v)[i];
+    float4 H = make_float4(0.f, 0.f, 0.f, 0.f), K = H;
+    if (HAT) H = reinterpret_cast<float4 *>(vh)[i];
+    if (WD) K = __ldg(reinterpret_cast<const float4 *>(mask) + i);
+    OptState s0{P.x, G.x, M.x, V.x, H.x}, s1{P.y, G.y, M.y, V.y, H.y}, s2{P.z, G.z, M.z, V.z, H.z},
+        s3{P.w, G.w, M.w, V.w, H.w};
+    update_one<RULE, WD>(s0, K.x, k);
+    update_one<RULE, WD>(s1, K.y, k);
+    update_one<RULE, WD>(s2, K.z, k);
+    update_one<RULE, WD>(s3, K.w, k);
+    reinterpret_cast<float4 *>(p)[i] = make_float4(s0.p, s1.p, s2.p, s3.p);
+    reinterpret_cast<float4 *>(m)[i] = make_float4(s0.m, s1.m, s2.m, s3.m);
+    reinterpret_cast<float4 *>(v)[i] = make_float4(s0.v, s1.v, s2.v, s3.v);
+    if (HAT) reinterpret_cast<float4 *>(vh)[i] = make_float4(s0.vh, s1.vh, s2.vh, s3.vh);
+    reinterpret_cast<float4 *>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  // Tail (n not a multiple of 4).
+  for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    OptState s{p[i], g[i], m[i], v[i], HAT ? vh[i] : 0.f};
+    update_one<RULE, WD>(s, WD ? mask[i] : 0.f, k);
+    p[i] = s.p; m[i] = s.m; v[i] = s.v; g[i] = 0.f;
+    if (HAT) vh[i] = s.vh;
+  }
+}
+
+template <int RULE>
+static dlb_status launch_rule(dlb_ctx *ctx, const dlb_optimizer_scalars &k, float *p, float *g,
+                              float *m, float *v, float *vh, const float *mask, size_t n) {
+  // Enough blocks to keep every SM's memory pipeline full; each thread moves
+  // 8-10 float4 per iteration.
+  const size_t blocks_needed = (n / 4 + 255) / 256 + 1;
+  const int grid = (int)min(blocks_needed, (size_t)ctx->sm_count * 8);
+  if (k.weight_decay != 0.f)
+    optimizer_kernel<RULE, true><<<grid, 256, 0, ctx->stream>>>(k, p, g, m, v, vh, mask, n);
+  else
+    optimizer_kernel<RULE, false><<<grid, 256, 0, ctx->stream>>>(k, p, g, m, v, vh, mask, n);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+}  // namespace dlb
+
+using namespace dlb;
+
+extern "C" {
+
+dlb_status dlb_optimizer_step(dlb_ctx *ctx, int rule, const dlb_optimizer_scalars *s, float *p,
+                              float *g, float *first, float *second, float *second_hat,
+                              const float *wd_mask, size_t n) {
+  DLB_REQUIRE(ctx && s && p && g && first && second, "dlb_optimizer_step: null");
+  if (n == 0) return DLB_OK;
+  const bool hat = rule == DLB_OPT_AMSGRAD || rule == DLB_OPT_AMSBOUND;
+  DLB_REQUIRE(!hat || second_hat, "dlb_optimizer_step: second_hat required");
+  DLB_REQUIRE(s->weight_decay == 0.f || wd_mask, "dlb_optimizer_step: weight decay needs a mask");
+  const uintptr_t al = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
+                       reinterpret_cast<uintptr_t>(first) | reinterpret_cast<uintptr_t>(second) |
+                       (hat ? reinterpret_cast<uintptr_t>(second_hat) : 0) |
+                       (s->weight_decay != 0.f ? reinterpret_cast<uintptr_t>(wd_mask) : 0);
+  DLB_REQUIRE((al & 15) == 0, "dlb_optimizer_step: arrays must be 16-byte aligned");
+  switch (rule) {
+    case DLB_OPT_ADAM:
+    case DLB_OPT_NOSADAM:
+      return launch_rule<R_ADAM>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+    case DLB_OPT_AMSGRAD:
+      return launch_rule<R_AMSGRAD>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+    case DLB_OPT_ADABOUND:
+      return launch_rule<R_ADABOUND>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+    case DLB_OPT_AMSBOUND:
+      return launch_rule<R_AMSBOUND>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+    case DLB_OPT_ADAMAX:
+      return launch_rule<R_ADAMAX>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+    default:
+      set_error("dlb_optimizer_step: optimizer %d is outside the supported path", rule);
+      return DLB_ERR_UNSUPPORTED;
+  }
+}
+
+dlb_status dlb_optimizer_prepare(int rule, const float *hyper, float *time_step,
+                                 float *nos_previous, dlb_optimizer_scalars *out) {
+  DLB_REQUIRE(hyper && time_step && out, "dlb_optimizer_prepare: null");
+  const float lr = hyper[0], beta1 = hyper[1], beta2 = hyper[2], eps = hyper[3], gamma = hyper[4],
+              final_lr = hyper[5], bound_gamma = hyper[6];
+  const bool bias_correction = hyper[7] != 0.f;
+  *time_step += 1.f;  // the reference keeps the step count in a float
+  const float t = *time_step;
+  dlb_optimizer_scalars k{};
+  k.beta1 = beta1;
+  k.beta2 = beta2;
+  k.epsilon = eps;
+  k.weight_decay = 0.f;
+  k.lower_bound = 0.f;
+  k.upper_bound = 0.f;
+  // lr * sqrt(1 - beta2^t) / (1 - beta1^t), float pow as in adam.cpp L:113-118.
+  k.lr_t = bias_correction ? lr * sqrtf(1.f - powf(beta2, t)) / (1.f - powf(beta1, t)) : lr;
+  switch (rule) {
+    case DLB_OPT_ADAM:
+    case DLB_OPT_AMSGRAD:
+      break;
+    case DLB_OPT_ADABOUND:
+    case DLB_OPT_AMSBOUND:
+      // adabound.cpp L:52-60 / amsbound.cpp L:52-60
+      k.lower_bound = final_lr * (1.f - 1.f / (bound_gamma * t + 1.f));
+      k.upper_bound = final_lr * (1.f + 1.f / (bound_gamma * t));
+      break;
+    case DLB_OPT_NOSADAM: {
+      DLB_REQUIRE(nos_previous, "dlb_optimizer_prepare: NosAdam needs its running sum");
+      // nosadam.cpp L:50-53, L:70
+      const float b = powf(t, -gamma);
+      k.beta2 = *nos_previous / (*nos_previous + b);
+      *nos_previous += b;
+      break;
+    }
+    case DLB_OPT_ADAMAX:
+      k.lr_t = lr / (1.f - powf(beta1, t));
+      break;
+    default:
+      set_error("dlb_optimizer_prepare: optimizer %d is outside the supported path", rule);
+      return DLB_ERR_UNSUPPORTED;
+  }
+  *out = k;
+  return DLB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,450 @@
+"""ctypes binding of libdlb200.so (the C ABI declared in include/dlb200.h).
+
+``Model`` carries the method names of the reference library's ``DL::v1::Model``
+(lib/deep-learning/v1/learner/model.hpp L:752-3384): ``compile``,
+``set_layer_activation_function``, ``Set__Layer_Normalization``,
+``set_dropout``, ``set_optimizer``, ``forward_pass``, ``compute_error``,
+``backward_pass``, ``update_derivatives``, ``update_weights`` ...  Everything
+numerical runs in the CUDA library; there is no CPU path, and loading fails
+loudly when the library has not been built or no sm_100 GPU is present.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libdlb200.so")
+
+_vp, _sz, _i, _f, _d, _cp = C.c_void_p, C.c_size_t, C.c_int, C.c_float, C.c_double, C.c_char_p
+_u64 = C.c_uint64
+
+
+class BrnUnitArrays(C.Structure):
+    _fields_ = [(n, _vp) for n in ("mean", "sigma", "mean_average", "sigma_average", "r", "d", "gamma", "beta")]
+
+
+class DropoutDesc(C.Structure):
+    _fields_ = [("type", _i), ("value", _f), ("mask", _vp), ("noise", _vp)]
+
+
+class OptimizerScalars(C.Structure):
+    _fields_ = [(n, _f) for n in ("lr_t", "beta1", "beta2", "epsilon", "lower_bound", "upper_bound", "weight_decay")]
+
+
+# name -> (restype, argtypes); every symbol include/dlb200.h declares.
+SIGNATURES = {
+    "dlb_status_string": (_cp, [_i]),
+    "dlb_last_error": (_cp, []),
+    "dlb_version": (_i, []),
+    "dlb_ctx_create": (_i, [C.POINTER(_vp), _i]),
+    "dlb_ctx_destroy": (_i, [_vp]),
+    "dlb_ctx_sync": (_i, [_vp, C.POINTER(_i)]),
+    "dlb_ctx_stream": (_vp, [_vp]),
+    "dlb_ctx_set_tensor_core": (_i, [_vp, _i]),
+    "dlb_ctx_launch_count": (_u64, [_vp]),
+    "dlb_malloc": (_i, [_vp, C.POINTER(_vp), _sz]),
+    "dlb_free": (_i, [_vp, _vp]),
+    "dlb_memset": (_i, [_vp, _vp, _i, _sz]),
+    "dlb_memcpy_h2d": (_i, [_vp, _vp, _vp, _sz]),
+    "dlb_memcpy_d2h": (_i, [_vp, _vp, _vp, _sz]),
+    "dlb_memcpy_d2d": (_i, [_vp, _vp, _vp, _sz]),
+    "dlb_host_alloc": (_i, [C.POINTER(_vp), _sz]),
+    "dlb_host_free": (_i, [_vp]),
+    "dlb_split_tf32": (_i, [_vp, _vp, _vp, _sz]),
+    "dlb_fc_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
+    "dlb_fc_backward_input": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
+    "dlb_fc_weight_gradient": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
+    "dlb_brn_forward_sums": (_i, [_vp, _vp, _i, _i, _vp]),
+    "dlb_brn_forward_finalize": (_i, [_vp, _vp, _i, _i, _f, _f, _f, _f, C.POINTER(BrnUnitArrays)]),
+    "dlb_activation_forward": (_i, [_vp, _vp, C.POINTER(BrnUnitArrays), _i, C.POINTER(DropoutDesc), _vp, _vp, _i, _i]),
+    "dlb_softmax_forward": (_i, [_vp, _vp, _vp, _i, _i]),
+    "dlb_activation_backward": (_i, [_vp, _vp, _vp, _vp, C.POINTER(BrnUnitArrays), _i, _i, _i, _vp]),
+    "dlb_brn_backward_apply": (_i, [_vp, _vp, _vp, _vp, C.POINTER(BrnUnitArrays), _vp, _i, _i, _i]),
+    "dlb_brn_backward_param_grads": (_i, [_vp, _vp, _i, _vp, _vp, _i]),
+    "dlb_loss_delta": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "dlb_optimizer_step": (_i, [_vp, _i, C.POINTER(OptimizerScalars), _vp, _vp, _vp, _vp, _vp, _vp, _sz]),
+    "dlb_optimizer_prepare": (_i, [_i, C.POINTER(_f), C.POINTER(_f), C.POINTER(_f), C.POINTER(OptimizerScalars)]),
+    "dlb_comm_unique_id": (_i, [C.c_char * 128]),
+    "dlb_comm_init": (_i, [_vp, C.c_char * 128, _i, _i]),
+    "dlb_comm_world": (_i, [_vp]),
+    "dlb_comm_rank": (_i, [_vp]),
+    "dlb_allreduce_f32": (_i, [_vp, _vp, _sz]),
+    "dlb_allreduce_f64": (_i, [_vp, _vp, _sz]),
+    "dlb_model_create": (_i, [C.POINTER(_vp), _vp]),
+    "dlb_model_destroy": (_i, [_vp]),
+    "dlb_model_compile": (_i, [_vp, _sz, _sz, _i, _vp, _vp]),
+    "dlb_model_set_layer_activation_function": (_i, [_vp, _sz, _i]),
+    "dlb_model_set_layer_normalization": (_i, [_vp, _sz, _i]),
+    "dlb_model_set_dropout": (_i, [_vp, _sz, _i, _f, _i]),
+    "dlb_model_set_normalization_momentum_average": (_i, [_vp, _f]),
+    "dlb_model_set_normalization_epsilon": (_i, [_vp, _f]),
+    "dlb_model_set_brn_r_correction_maximum": (_i, [_vp, _f]),
+    "dlb_model_set_brn_d_correction_maximum": (_i, [_vp, _f]),
+    "dlb_model_set_loss_fn": (_i, [_vp, _i]),
+    "dlb_model_set_optimizer": (_i, [_vp, _i]),
+    "dlb_model_set_hparam": (_i, [_vp, _cp, _d]),
+    "dlb_model_get_hparam": (_d, [_vp, _cp]),
+    "dlb_model_set_max_batch_size": (_i, [_vp, _sz]),
+    "dlb_model_set_seq_w": (_i, [_vp, _sz]),
+    "dlb_model_seed_weights": (_i, [_vp, C.c_uint]),
+    "dlb_model_initialize_weights_with_glorot_uniform": (_i, [_vp]),
+    "dlb_model_get_size": (_sz, [_vp, _cp]),
+    "dlb_model_layer_info": (_i, [_vp, _sz, _vp]),
+    "dlb_model_get_array": (_i, [_vp, _cp, _vp, _sz]),
+    "dlb_model_set_array": (_i, [_vp, _cp, _vp, _sz]),
+    "dlb_model_get_layer_norm": (_i, [_vp, _sz, _cp, _vp, _sz]),
+    "dlb_model_set_layer_norm": (_i, [_vp, _sz, _cp, _vp, _sz]),
+    "dlb_model_set_dropout_mask": (_i, [_vp, _sz, _vp, _sz]),
+    "dlb_model_set_global_batch": (_i, [_vp, _sz]),
+    "dlb_model_forward_pass": (_i, [_vp, _sz, _vp]),
+    "dlb_model_compute_error": (_i, [_vp, _sz, _vp]),
+    "dlb_model_backward_pass": (_i, [_vp, _sz]),
+    "dlb_model_update_derivatives": (_i, [_vp, _sz]),
+    "dlb_model_merge_derivatives": (_i, [_vp]),
+    "dlb_model_update_weights": (_i, [_vp, _sz, _sz]),
+    "dlb_model_get_loss": (_i, [_vp, C.POINTER(_d)]),
+    "dlb_model_reset_loss": (_i, [_vp]),
+    "dlb_model_forward_pass_device": (_i, [_vp, _sz, _vp]),
+    "dlb_model_compute_error_device": (_i, [_vp, _sz, _vp]),
+    "dlb_model_train_step": (_i, [_vp, _sz, _vp, _vp, C.POINTER(_d)]),
+    "dlb_model_train_step_device": (_i, [_vp, _sz, _vp, _vp]),
+    "dlb_model_get_layer_outputs": (_i, [_vp, _sz, _sz, _vp]),
+    "dlb_model_get_layer_errors": (_i, [_vp, _sz, _sz, _i, _vp]),
+}
+
+_lib = None
+
+
+class DlbError(RuntimeError):
+    pass
+
+
+def lib():
+    """Loads libdlb200.so; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise DlbError(f"{LIB_PATH} is missing: run `make -C {_HERE}` (there is no CPU fallback)")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(status, what=""):
+    if status != 0:
+        L = lib()
+        raise DlbError(f"{what}: {L.dlb_status_string(status).decode()} [{L.dlb_last_error().decode()}]")
+
+
+def _ptr(a):
+    return a.ctypes.data_as(_vp)
+
+
+class Context:
+    """One GPU, one stream."""
+
+    def __init__(self, device=0):
+        self.L = lib()
+        h = _vp()
+        check(self.L.dlb_ctx_create(C.byref(h), device), "dlb_ctx_create")
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.dlb_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def sync(self):
+        st = _i(0)
+        check(self.L.dlb_ctx_sync(self.h, C.byref(st)), "dlb_ctx_sync")
+        return st.value
+
+    def set_tensor_core(self, on):
+        check(self.L.dlb_ctx_set_tensor_core(self.h, int(on)), "dlb_ctx_set_tensor_core")
+
+    def launch_count(self):
+        return int(self.L.dlb_ctx_launch_count(self.h))
+
+    @property
+    def stream(self):
+        return self.L.dlb_ctx_stream(self.h)
+
+    # --- device arrays --------------------------------------------------
+    def empty(self, shape, dtype=np.float32):
+        return DeviceArray(self, shape, dtype)
+
+    def zeros(self, shape, dtype=np.float32):
+        a = DeviceArray(self, shape, dtype)
+        check(self.L.dlb_memset(self.h, a.ptr, 0, a.nbytes), "dlb_memset")
+        return a
+
+    def array(self, host):
+        host = np.ascontiguousarray(host)
+        a = DeviceArray(self, host.shape, host.dtype)
+        a.set(host)
+        return a
+
+    # --- communicator ---------------------------------------------------
+    def unique_id(self):
+        buf = (C.c_char * 128)()
+        check(self.L.dlb_comm_unique_id(buf), "dlb_comm_unique_id")
+        return bytes(buf)
+
+    def comm_init(self, uid, rank, world):
+        buf = (C.c_char * 128).from_buffer_copy(uid)
+        check(self.L.dlb_comm_init(self.h, buf, rank, world), "dlb_comm_init")
+
+    @property
+    def world(self):
+        return self.L.dlb_comm_world(self.h)
+
+    @property
+    def rank(self):
+        return self.L.dlb_comm_rank(self.h)
+
+
+class DeviceArray:
+    def __init__(self, ctx, shape, dtype=np.float32):
+        self.ctx = ctx
+        self.shape = tuple(np.atleast_1d(shape).tolist()) if not isinstance(shape, tuple) else shape
+        self.dtype = np.dtype(dtype)
+        self.size = int(np.prod(self.shape)) if len(self.shape) else 1
+        self.nbytes = self.size * self.dtype.itemsize
+        p = _vp()
+        check(ctx.L.dlb_malloc(ctx.h, C.byref(p), max(self.nbytes, 16)), "dlb_malloc")
+        self.ptr = p
+
+    def set(self, host):
+        host = np.ascontiguousarray(host, dtype=self.dtype)
+        assert host.size == self.size
+        check(self.ctx.L.dlb_memcpy_h2d(self.ctx.h, self.ptr, _ptr(host), self.nbytes), "dlb_memcpy_h2d")
+        self.ctx.sync()
+
+    def get(self):
+        out = np.empty(self.shape, dtype=self.dtype)
+        check(self.ctx.L.dlb_memcpy_d2h(self.ctx.h, _ptr(out), self.ptr, self.nbytes), "dlb_memcpy_d2h")
+        return out
+
+    def offset(self, elems):
+        return _vp(self.ptr.value + elems * self.dtype.itemsize)
+
+    def free(self):
+        if self.ptr is not None and self.ctx.h:
+            self.ctx.L.dlb_free(self.ctx.h, self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def pinned_empty(shape, dtype=np.float32):
+    """numpy array over page-locked host memory (freed when dropped)."""
+    L = lib()
+    dtype = np.dtype(dtype)
+    n = int(np.prod(shape))
+    p = _vp()
+    check(L.dlb_host_alloc(C.byref(p), max(n * dtype.itemsize, 16)), "dlb_host_alloc")
+    buf = (C.c_char * (n * dtype.itemsize)).from_address(p.value)
+    arr = np.frombuffer(buf, dtype=dtype).reshape(shape)
+    _PINNED[id(buf)] = (buf, p)
+    return arr
+
+
+_PINNED = {}
+
+
+class Model:
+    backend = "cuda-sm100a"
+
+    def __init__(self, ctx=None, device=0):
+        self.L = lib()
+        self.ctx = ctx or Context(device)
+        h = _vp()
+        check(self.L.dlb_model_create(C.byref(h), self.ctx.h), "dlb_model_create")
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None) and self.ctx.h:
+            self.L.dlb_model_destroy(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # --- construction ---------------------------------------------------
+    def compile(self, layer_types, layer_units, seq_w=1, model_type=3, allowable_memory=None):
+        lt = np.ascontiguousarray(layer_types, dtype=np.int32)
+        lu = np.ascontiguousarray(layer_units, dtype=np.uint64)
+        check(self.L.dlb_model_compile(self.h, len(lt), seq_w, model_type, _ptr(lt), _ptr(lu)), "compile")
+
+    def set_layer_activation_function(self, layer, af):
+        check(self.L.dlb_model_set_layer_activation_function(self.h, layer, af), "set_layer_activation_function")
+
+    def Set__Layer_Normalization(self, layer, norm):
+        check(self.L.dlb_model_set_layer_normalization(self.h, layer, norm), "Set__Layer_Normalization")
+
+    def set_dropout(self, layer, kind, value, scale_weights=False):
+        check(self.L.dlb_model_set_dropout(self.h, layer, kind, value, int(scale_weights)), "set_dropout")
+
+    def Set__Normalization_Momentum_Average(self, v):
+        check(self.L.dlb_model_set_normalization_momentum_average(self.h, v), "momentum")
+
+    def Set__Normalization_Epsilon(self, v):
+        check(self.L.dlb_model_set_normalization_epsilon(self.h, v), "epsilon")
+
+    def Set__Batch_Renormalization_r_Correction_Maximum(self, v):
+        check(self.L.dlb_model_set_brn_r_correction_maximum(self.h, v), "r_max")
+
+    def Set__Batch_Renormalization_d_Correction_Maximum(self, v):
+        check(self.L.dlb_model_set_brn_d_correction_maximum(self.h, v), "d_max")
+
+    def set_loss_fn(self, loss):
+        check(self.L.dlb_model_set_loss_fn(self.h, loss), "set_loss_fn")
+
+    def set_optimizer(self, opt):
+        check(self.L.dlb_model_set_optimizer(self.h, opt), "set_optimizer")
+
+    def set_hparam(self, name, value):
+        check(self.L.dlb_model_set_hparam(self.h, name.encode(), float(value)), f"set_hparam {name}")
+
+    def get_hparam(self, name):
+        return self.L.dlb_model_get_hparam(self.h, name.encode())
+
+    def set_max_batch_size(self, b):
+        check(self.L.dlb_model_set_max_batch_size(self.h, b), "set_max_batch_size")
+
+    def set_mp(self, on):
+        pass  # OpenMP switch of the reference; the GPU path has nothing to switch
+
+    def set_seq_w(self, delays):
+        check(self.L.dlb_model_set_seq_w(self.h, delays), "set_seq_w")
+
+    def seed_weights(self, seed):
+        check(self.L.dlb_model_seed_weights(self.h, seed), "seed_weights")
+
+    def initialize_weights_with_glorot_uniform(self):
+        check(self.L.dlb_model_initialize_weights_with_glorot_uniform(self.h), "glorot")
+
+    def set_global_batch(self, rows):
+        check(self.L.dlb_model_set_global_batch(self.h, rows), "set_global_batch")
+
+    # --- state ----------------------------------------------------------
+    def size(self, name):
+        v = self.L.dlb_model_get_size(self.h, name.encode())
+        if v == 2**64 - 1:
+            raise KeyError(name)
+        return int(v)
+
+    def layer_info(self, layer):
+        out = np.zeros(10, dtype=np.uint64)
+        check(self.L.dlb_model_layer_info(self.h, layer, _ptr(out)), "layer_info")
+        keys = ("type", "n_out", "first_connection", "last_connection", "first_bias", "last_bias",
+                "norm", "dropout", "group", "first_norm_unit")
+        return {k: int(v) for k, v in zip(keys, out)}
+
+    def get_array(self, name, n=None):
+        n = self.size("total_parameters") if n is None else n
+        out = np.empty(n, dtype=np.float32)
+        check(self.L.dlb_model_get_array(self.h, name.encode(), _ptr(out), n), f"get_array {name}")
+        return out
+
+    def set_array(self, name, arr):
+        arr = np.ascontiguousarray(arr, dtype=np.float32)
+        check(self.L.dlb_model_set_array(self.h, name.encode(), _ptr(arr), arr.size), f"set_array {name}")
+
+    def get_layer_norm(self, layer, name, n):
+        out = np.empty(n, dtype=np.float32)
+        check(self.L.dlb_model_get_layer_norm(self.h, layer, name.encode(), _ptr(out), n), f"get_layer_norm {name}")
+        return out
+
+    def set_layer_norm(self, layer, name, arr):
+        arr = np.ascontiguousarray(arr, dtype=np.float32)
+        check(self.L.dlb_model_set_layer_norm(self.h, layer, name.encode(), _ptr(arr), arr.size), f"set_layer_norm {name}")
+
+    def set_dropout_mask(self, layer, mask):
+        mask = np.ascontiguousarray(mask, dtype=np.uint8)
+        check(self.L.dlb_model_set_dropout_mask(self.h, layer, _ptr(mask), mask.size), "set_dropout_mask")
+
+    # --- step -----------------------------------------------------------
+    def train_begin(self, batch):
+        pass
+
+    @staticmethod
+    def _row_pointers(a):
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        base = a.ctypes.data
+        stride = a.strides[0]
+        rows = (C.c_void_p * a.shape[0])(*[base + i * stride for i in range(a.shape[0])])
+        return a, rows
+
+    def forward_pass(self, batch, X):
+        self._x, rows = self._row_pointers(X)
+        check(self.L.dlb_model_forward_pass(self.h, batch, rows), "forward_pass")
+
+    def compute_error(self, batch, Y):
+        self._y, rows = self._row_pointers(Y)
+        check(self.L.dlb_model_compute_error(self.h, batch, rows), "compute_error")
+
+    def backward_pass(self, batch):
+        check(self.L.dlb_model_backward_pass(self.h, batch), "backward_pass")
+
+    def update_derivatives(self, batch):
+        check(self.L.dlb_model_update_derivatives(self.h, batch), "update_derivatives")
+
+    def merge_derivatives(self):
+        check(self.L.dlb_model_merge_derivatives(self.h), "merge_derivatives")
+
+    def reset_loss(self):
+        check(self.L.dlb_model_reset_loss(self.h), "reset_loss")
+
+    def get_loss(self):
+        v = _d(0.0)
+        check(self.L.dlb_model_get_loss(self.h, C.byref(v)), "get_loss")
+        return v.value
+
+    def update_weights(self, batch, training_size):
+        check(self.L.dlb_model_update_weights(self.h, batch, training_size), "update_weights")
+
+    def train_step(self, batch, X, Y, want_loss=True):
+        X = np.ascontiguousarray(X, dtype=np.float32) if not isinstance(X, np.ndarray) or not X.flags.c_contiguous else X
+        Y = np.ascontiguousarray(Y, dtype=np.float32) if not isinstance(Y, np.ndarray) or not Y.flags.c_contiguous else Y
+        loss = _d(0.0)
+        check(self.L.dlb_model_train_step(self.h, batch, _ptr(X), _ptr(Y), C.byref(loss) if want_loss else None),
+              "train_step")
+        return loss.value
+
+    def train_step_device(self, batch, X_dev, Y_dev):
+        check(self.L.dlb_model_train_step_device(self.h, batch, X_dev.ptr, Y_dev.ptr), "train_step_device")
+
+    def get_layer_outputs(self, layer, batch):
+        n_out = self.layer_info(layer)["n_out"]
+        T = self.size("seq_w")
+        out = np.empty((T, batch, n_out), dtype=np.float32)
+        check(self.L.dlb_model_get_layer_outputs(self.h, layer, batch, _ptr(out)), "get_layer_outputs")
+        return out
+
+    def get_layer_errors(self, layer, batch, which=0):
+        n_out = self.layer_info(layer)["n_out"]
+        T = self.size("seq_w")
+        out = np.empty((T, batch, n_out), dtype=np.float32)
+        check(self.L.dlb_model_get_layer_errors(self.h, layer, batch, which, _ptr(out)), "get_layer_errors")
+        return out

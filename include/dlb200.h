@@ -1,0 +1,322 @@
+/* dlb200 — B200 (sm_100a) kernels for the fully-connected training step of the
+ * SebastienKeroack/deep-learning library, behind a C ABI.
+ *
+ * Every entry point takes plain pointers and sizes.  Device pointers are
+ * ordinary CUDA device addresses owned by the caller (or obtained from
+ * dlb_malloc); all work is enqueued on the context's stream and nothing blocks
+ * the host except dlb_ctx_sync, dlb_memcpy_d2h and the functions documented as
+ * synchronous.  No function throws; each returns a dlb_status.
+ *
+ * Layouts are the reference's: activations are row-major [rows, units] per time
+ * step, weights of a layer are row-major [units_out, units_in], and the flat
+ * parameter vector is { all W | all bias | all gamma | all beta }
+ * (lib/deep-learning/v1/learner/compile.cpp L:610-695,
+ *  connections_prepare.cpp L:21-81, allocate.cpp L:1150-1233).
+ *
+ * Citations "ref:" name the reference function each entry point replaces, by
+ * path inside the reference project.
+ */
+#ifndef DLB200_H_
+#define DLB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int dlb_status;
+enum {
+  DLB_OK = 0,
+  DLB_ERR_INVALID = 1,      /* bad argument (null pointer, size, enum) */
+  DLB_ERR_CUDA = 2,         /* a CUDA runtime/driver call failed */
+  DLB_ERR_UNSUPPORTED = 3,  /* combination outside the supported path */
+  DLB_ERR_TIMEOUT = 4,      /* a bounded device-side wait gave up */
+  DLB_ERR_COMM = 5,         /* NCCL error */
+  DLB_ERR_NO_DEVICE = 6     /* no sm_100 device: there is no CPU fallback */
+};
+
+/* Numeric values of the reference's enums (v1/data/enum/*.hpp). */
+enum { DLB_AF_ELU = 3, DLB_AF_ISRLU = 10, DLB_AF_LINEAR = 11, DLB_AF_LEAKY_RELU = 14,
+       DLB_AF_RELU = 16, DLB_AF_SELU = 17, DLB_AF_SOFTMAX = 22 };
+enum { DLB_DROPOUT_NONE = 0, DLB_DROPOUT_BERNOULLI = 2, DLB_DROPOUT_BERNOULLI_INVERTED = 3,
+       DLB_DROPOUT_SHAKEDROP = 5, DLB_DROPOUT_UOUT = 6 };
+enum { DLB_OPT_ADABOUND = 1, DLB_OPT_ADAM = 2, DLB_OPT_ADAMAX = 3, DLB_OPT_AMSBOUND = 4,
+       DLB_OPT_AMSGRAD = 5, DLB_OPT_NOSADAM = 9 };
+enum { DLB_LOSS_CROSS_ENTROPY = 2, DLB_LOSS_MSE = 10 };
+enum { DLB_LAYER_FULLY_CONNECTED = 3, DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT = 4,
+       DLB_LAYER_RESIDUAL = 9 };
+enum { DLB_NORM_NONE = 0, DLB_NORM_BATCH_RENORMALIZATION = 2 };
+enum { DLB_MODEL_FEEDFORWARD = 3, DLB_MODEL_RECURRENT = 4 };
+
+const char *dlb_status_string(dlb_status s);
+/* Last error text recorded on the calling thread ("" if none). */
+const char *dlb_last_error(void);
+int dlb_version(void);
+
+/* ------------------------------------------------------------------------ */
+/* Context: one per GPU, single caller at a time (the reference's step
+ * functions are likewise entered by one OpenMP team, drivers/driver.cpp
+ * L:241-257).  Owns a stream, a scratch arena for reduction partials and
+ * TF32 residual planes, and optionally an NCCL communicator. */
+typedef struct dlb_ctx dlb_ctx;
+
+dlb_status dlb_ctx_create(dlb_ctx **out, int device);
+dlb_status dlb_ctx_destroy(dlb_ctx *ctx);
+/* Waits for the stream; *device_status receives the sticky device status word
+ * (DLB_OK, or DLB_ERR_TIMEOUT if a kernel's bounded wait expired). */
+dlb_status dlb_ctx_sync(dlb_ctx *ctx, int *device_status);
+void *dlb_ctx_stream(dlb_ctx *ctx); /* cudaStream_t */
+/* 0: always the CUDA-core GEMM; 1 (default): tcgen05 GEMM when shapes allow. */
+dlb_status dlb_ctx_set_tensor_core(dlb_ctx *ctx, int enable);
+/* Number of kernels this context has launched since creation. */
+uint64_t dlb_ctx_launch_count(dlb_ctx *ctx);
+
+/* Device memory for callers without their own CUDA binding. */
+dlb_status dlb_malloc(dlb_ctx *ctx, void **dev_ptr, size_t bytes);
+dlb_status dlb_free(dlb_ctx *ctx, void *dev_ptr);
+dlb_status dlb_memset(dlb_ctx *ctx, void *dev_ptr, int value, size_t bytes);
+dlb_status dlb_memcpy_h2d(dlb_ctx *ctx, void *dev_dst, const void *host_src, size_t bytes);
+/* Synchronous: returns after the bytes are in host memory. */
+dlb_status dlb_memcpy_d2h(dlb_ctx *ctx, void *host_dst, const void *dev_src, size_t bytes);
+dlb_status dlb_memcpy_d2d(dlb_ctx *ctx, void *dev_dst, const void *dev_src, size_t bytes);
+/* Pinned host memory for staging inputs. */
+dlb_status dlb_host_alloc(void **host_ptr, size_t bytes);
+dlb_status dlb_host_free(void *host_ptr);
+
+/* ------------------------------------------------------------------------ */
+/* TF32 residual plane.  The tensor-core GEMMs compute a*b as
+ * hi(a)*hi(b) + hi(a)*lo(b) + lo(a)*hi(b) ("3xTF32"), where hi(x) is what the
+ * tensor core sees of the fp32 word x (its top 19 bits) and lo(x) is the
+ * exactly representable remainder x - hi(x), rounded to TF32.  A `_lo`
+ * argument is a caller-kept plane of those remainders with the shape of its
+ * tensor; pass NULL and the library derives it into context scratch first. */
+dlb_status dlb_split_tf32(dlb_ctx *ctx, const float *x, float *x_lo, size_t n);
+
+/* ------------------------------------------------------------------------ */
+/* FC GEMMs. */
+
+/* Z[b,o] = sum_i X[b,i] * W[o,i]  (+ bias[o] when bias != NULL).
+ * ref: Model::Forward_Pass__FC__OpenMP (v1/learner/fwp_mp.cpp L:4419-4459) and
+ * Forward_Pass__Bias__OpenMP (L:4396-4417). */
+dlb_status dlb_fc_forward(dlb_ctx *ctx, const float *X, const float *X_lo, const float *W,
+                          const float *W_lo, const float *bias, float *Z, int rows, int n_in,
+                          int n_out);
+
+/* dX[b,i] = sum_o delta[b,o] * W[o,i].
+ * ref: Model::Backward_Pass__FC__OpenMP (v1/learner/bwp_mp.cpp L:968-1007). */
+dlb_status dlb_fc_backward_input(dlb_ctx *ctx, const float *delta, const float *delta_lo,
+                                 const float *W, const float *W_lo, float *dX, int rows,
+                                 int n_in, int n_out);
+
+/* dW[o,i] (+)= sum_b delta[b,o] * X[b,i];  dbias[o] (+)= sum_b delta[b,o] when
+ * dbias != NULL.  accumulate != 0 adds to dW/dbias, else overwrites.
+ * ref: Model::Update_Derivative_Weight__FC__OpenMP
+ * (v1/learner/update_derivative_fwp_mp.cpp L:175-213) and ...__Bias (L:215-240). */
+dlb_status dlb_fc_weight_gradient(dlb_ctx *ctx, const float *delta, const float *delta_lo,
+                                  const float *X, const float *X_lo, float *dW, float *dbias,
+                                  int rows, int n_in, int n_out, int accumulate);
+
+/* ------------------------------------------------------------------------ */
+/* Batch renormalization. */
+
+/* Per-unit statistics and corrections of one layer at one time step; every
+ * pointer addresses n_units floats. */
+typedef struct dlb_brn_unit_arrays {
+  float *mean;          /* batch mean                                   */
+  float *sigma;         /* batch standard deviation sqrt(E[x^2]-mu^2+eps) */
+  float *mean_average;  /* running mean                                 */
+  float *sigma_average; /* running standard deviation                   */
+  float *r;             /* r correction                                 */
+  float *d;             /* d correction                                 */
+  const float *gamma;   /* scale (inside the parameter vector)          */
+  const float *beta;    /* shift (inside the parameter vector)          */
+} dlb_brn_unit_arrays;
+
+/* sums[0..n) = sum_b Z[b,h], sums[n..2n) = sum_b Z[b,h]^2 over this rank's
+ * rows, in double.  ref: the "Summation" loop of
+ * Model::Forward_Pass__Batch_Renormalization__Training__OpenMP
+ * (v1/learner/fwp_mp.cpp L:4647-4663). */
+dlb_status dlb_brn_forward_sums(dlb_ctx *ctx, const float *Z, int rows, int n_units,
+                                double *sums);
+
+/* From (all-reduced) sums over global_rows rows: mean, sigma, running averages
+ * (updated first), then r and d from the updated averages.
+ * ref: the "Average" loop, fwp_mp.cpp L:4666-4718. */
+dlb_status dlb_brn_forward_finalize(dlb_ctx *ctx, const double *sums, int global_rows,
+                                    int n_units, float momentum, float epsilon, float r_max,
+                                    float d_max, const dlb_brn_unit_arrays *u);
+
+/* Dropout applied in place on the activation, as the reference does. */
+typedef struct dlb_dropout_desc {
+  int type;              /* DLB_DROPOUT_* */
+  float value;           /* Bernoulli: keep probability; UOut: unused */
+  const uint8_t *mask;   /* [n_units], one flag per unit shared by all rows */
+  const float *noise;    /* UOut: [rows, n_units] draws of U(-p, p) */
+} dlb_dropout_desc;
+
+/* x_hat = (Z-mean)/sigma*r + d; y = gamma*x_hat + beta (u != NULL), else y = Z;
+ * A = f(y); dropout in place.  A_lo (optional) receives the TF32 residual
+ * plane of A for the next GEMM.
+ * ref: the "Activation function" loop of the BRN forward (fwp_mp.cpp
+ * L:4721-4738), Forward_Pass__FC_AF__OpenMP (L:4741-4770, AF_FIRE in
+ * v1/ops/activations/functions.hpp L:124-219) and the dropout forwards
+ * (fwp_mp.cpp L:4809-4868, L:4959-4985). */
+dlb_status dlb_activation_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
+                                  int af, const dlb_dropout_desc *dropout, float *A,
+                                  float *A_lo, int rows, int n_units);
+
+/* Row softmax.  ref: Forward_Pass__FC_AF__Softmax__OpenMP (fwp_mp.cpp L:4772-4807). */
+dlb_status dlb_softmax_forward(dlb_ctx *ctx, const float *Z, float *Q, int rows, int n_units);
+
+/* delta_af = dA * f'(y, A) written over dA, with y recomputed from Z as in
+ * the forward pass.  With u != NULL also the four per-unit sums of the batch
+ * renormalization backward over this rank's rows, in double:
+ * sums[0..n) d_gamma, [n..2n) d_beta, [2n..3n) d_mean, [3n..4n) d_sigma.
+ * ref: Backward_Pass__FC__DF__OpenMP (v1/learner/bwp_mp.cpp L:1150-1186),
+ * Model::activation_fn_derivative (v1/learner/model.cpp L:2594-2650) and pass
+ * 1 of Backward_Pass__Batch_Renormalization__OpenMP (bwp_mp.cpp L:1543-1578). */
+dlb_status dlb_activation_backward(dlb_ctx *ctx, float *dA, const float *Z, const float *A,
+                                   const dlb_brn_unit_arrays *u, int af, int rows, int n_units,
+                                   double *sums);
+
+/* delta = delta_af*gamma*r/sigma + d_sigma*(Z-mean)/(N*sigma) + d_mean/N over
+ * delta (in place), N = global_rows; d_mean/d_sigma are sums[2n..4n) after the
+ * all-reduce.  delta_lo optional.  ref: pass 3, bwp_mp.cpp L:1600-1626. */
+dlb_status dlb_brn_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
+                                  const dlb_brn_unit_arrays *u, const double *sums,
+                                  int global_rows, int rows, int n_units);
+
+/* d_gamma (+)= sums[0..n), d_beta (+)= sums[n..2n) as floats into the gradient
+ * vector.  ref: the accumulation into ptr_array_derivatives_scales/shifts,
+ * bwp_mp.cpp L:1559-1565. */
+dlb_status dlb_brn_backward_param_grads(dlb_ctx *ctx, const double *sums, int n_units,
+                                        float *d_gamma, float *d_beta, int accumulate);
+
+/* ------------------------------------------------------------------------ */
+/* Output error and loss.
+ * MSE: delta = f'(pre, q) * 2 (q - y) / (global_rows * n_out); loss += (q-y)^2.
+ * Cross-entropy on a softmax layer: delta_j = sum_k (q_j [j==k] - q_k q_j) L'_k,
+ * L'_k = (y_k == 1 ? -1/clip(q_k, 1e-7, 1-1e-7) : 0) / global_rows;
+ * loss += (y==1 ? -log(clip(q)) : 0).  *loss_sum (device, double) accumulates.
+ * ref: Model::compute_error_fwp_mp (v1/learner/compute_error_mp.cpp L:28-141),
+ * loss_fn / loss_fn_derivative (v1/learner/compute_loss.cpp L:55-138). */
+dlb_status dlb_loss_delta(dlb_ctx *ctx, int loss, int af, const float *pre, const float *q,
+                          const float *y, float *delta, float *delta_lo, int rows, int n_out,
+                          int global_rows, double *loss_sum);
+
+/* ------------------------------------------------------------------------ */
+/* Optimizer: one pass over flat arrays of n elements; gradient zeroed after
+ * use as the reference does. */
+typedef struct dlb_optimizer_scalars {
+  float lr_t;        /* lr * sqrt(1-beta2^t)/(1-beta1^t) (or lr without bias correction) */
+  float beta1;
+  float beta2;       /* NosAdam: beta2 at time t                          */
+  float epsilon;
+  float lower_bound; /* AdaBound / AMSBound                               */
+  float upper_bound;
+  float weight_decay;/* 0: off; else p -= ... + mask*wd*p                 */
+} dlb_optimizer_scalars;
+
+/* ref: Model::Update_Parameters__{Adam,AMSGrad,AdaBound,AMSBound,NosAdam}__OpenMP
+ * (v1/optimizers/adam.cpp L:98-165, amsgrad.cpp L:34-109, adabound.cpp
+ * L:38-112, amsbound.cpp L:38-126, nosadam.cpp L:33-102).  AdaMax has no
+ * implementation in the reference (v1/learner/model.cpp L:4765-4767); the
+ * rule here is Kingma & Ba section 7 with second = the infinity norm u. */
+dlb_status dlb_optimizer_step(dlb_ctx *ctx, int rule, const dlb_optimizer_scalars *s, float *p,
+                              float *g, float *first, float *second, float *second_hat,
+                              const float *wd_mask, size_t n);
+
+/* Host-side scalars exactly as the reference derives them from its float time
+ * step (increments *time_step first).  hyper = {lr, beta1, beta2, epsilon,
+ * gamma(NosAdam), final_lr, bound_gamma, bias_correction(0/1)};
+ * *nos_previous is NosAdam's running B_{t-1}. */
+dlb_status dlb_optimizer_prepare(int rule, const float *hyper, float *time_step,
+                                 float *nos_previous, dlb_optimizer_scalars *out);
+
+/* ------------------------------------------------------------------------ */
+/* Data-parallel exchange (NCCL over NVLink): sums over all ranks, in place,
+ * on the context's stream.  With no communicator bound they are no-ops. */
+dlb_status dlb_comm_unique_id(char out_id[128]);
+dlb_status dlb_comm_init(dlb_ctx *ctx, const char id[128], int rank, int world);
+int dlb_comm_world(dlb_ctx *ctx);
+int dlb_comm_rank(dlb_ctx *ctx);
+dlb_status dlb_allreduce_f32(dlb_ctx *ctx, float *buf, size_t n);
+dlb_status dlb_allreduce_f64(dlb_ctx *ctx, double *buf, size_t n);
+
+/* ------------------------------------------------------------------------ */
+/* Model: the reference's v1::Model construction and step entry points
+ * (v1/learner/model.hpp L:752-3384) over the kernels above.  Same setter
+ * names, argument meaning and call order; errors are status codes where the
+ * reference returns false and logs. */
+typedef struct dlb_model dlb_model;
+
+dlb_status dlb_model_create(dlb_model **out, dlb_ctx *ctx);
+dlb_status dlb_model_destroy(dlb_model *m);
+/* ref: Model::compile (model.hpp L:2528). */
+dlb_status dlb_model_compile(dlb_model *m, size_t n_layers, size_t seq_w, int model_type,
+                             const int *layer_types, const size_t *layer_units);
+dlb_status dlb_model_set_layer_activation_function(dlb_model *m, size_t layer, int af);
+dlb_status dlb_model_set_layer_normalization(dlb_model *m, size_t layer, int norm);
+dlb_status dlb_model_set_dropout(dlb_model *m, size_t layer, int type, float value0,
+                                 int scale_weights);
+dlb_status dlb_model_set_normalization_momentum_average(dlb_model *m, float v);
+dlb_status dlb_model_set_normalization_epsilon(dlb_model *m, float v);
+dlb_status dlb_model_set_brn_r_correction_maximum(dlb_model *m, float v);
+dlb_status dlb_model_set_brn_d_correction_maximum(dlb_model *m, float v);
+dlb_status dlb_model_set_loss_fn(dlb_model *m, int loss);
+dlb_status dlb_model_set_optimizer(dlb_model *m, int optimizer);
+/* Public hyper-parameter fields of the reference's Model, by field name. */
+dlb_status dlb_model_set_hparam(dlb_model *m, const char *name, double value);
+double dlb_model_get_hparam(dlb_model *m, const char *name);
+dlb_status dlb_model_set_max_batch_size(dlb_model *m, size_t rows);
+dlb_status dlb_model_set_seq_w(dlb_model *m, size_t time_delays);
+dlb_status dlb_model_seed_weights(dlb_model *m, unsigned seed);
+dlb_status dlb_model_initialize_weights_with_glorot_uniform(dlb_model *m);
+size_t dlb_model_get_size(dlb_model *m, const char *name);
+dlb_status dlb_model_layer_info(dlb_model *m, size_t layer, size_t out[10]);
+/* name: parameters, derivatives, first_moment, second_moment,
+ * second_moment_hat.  Host <-> device copies of the flat vectors
+ * (the reference's Copy__Parameters__Device_To_Host, model.cpp L:2300-2351). */
+dlb_status dlb_model_get_array(dlb_model *m, const char *name, float *host_out, size_t n);
+dlb_status dlb_model_set_array(dlb_model *m, const char *name, const float *host_in, size_t n);
+dlb_status dlb_model_get_layer_norm(dlb_model *m, size_t layer, const char *name, float *host_out,
+                                    size_t n);
+dlb_status dlb_model_set_layer_norm(dlb_model *m, size_t layer, const char *name,
+                                    const float *host_in, size_t n);
+dlb_status dlb_model_set_dropout_mask(dlb_model *m, size_t layer, const uint8_t *host_mask,
+                                      size_t n);
+/* Data-parallel: rows given to forward_pass are this rank's shard of a batch
+ * of global_rows rows (default: equal to the call's rows). */
+dlb_status dlb_model_set_global_batch(dlb_model *m, size_t global_rows);
+
+/* Step entry points; X/Y are HOST arrays of row pointers exactly as the
+ * reference takes them (model.hpp L:2980, L:1054), each row seq_w*n values. */
+dlb_status dlb_model_forward_pass(dlb_model *m, size_t rows, const float *const *Xm);
+dlb_status dlb_model_compute_error(dlb_model *m, size_t rows, const float *const *Ym);
+dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows);
+dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows);
+/* Across GPUs this is the gradient all-reduce (the reference's thread merge,
+ * v1/learner/merge.cpp L:76-100). */
+dlb_status dlb_model_merge_derivatives(dlb_model *m);
+dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_size);
+dlb_status dlb_model_get_loss(dlb_model *m, double *loss);
+dlb_status dlb_model_reset_loss(dlb_model *m);
+/* Same step with inputs already on the device, contiguous [rows, seq_w*n]. */
+dlb_status dlb_model_forward_pass_device(dlb_model *m, size_t rows, const float *X_dev);
+dlb_status dlb_model_compute_error_device(dlb_model *m, size_t rows, const float *Y_dev);
+/* forward, error, backward, gradients, merge, update in one call.  X/Y are
+ * contiguous host arrays [rows, seq_w*n]; copied through pinned staging. */
+dlb_status dlb_model_train_step(dlb_model *m, size_t rows, const float *X_host,
+                                const float *Y_host, double *loss);
+dlb_status dlb_model_train_step_device(dlb_model *m, size_t rows, const float *X_dev,
+                                       const float *Y_dev);
+dlb_status dlb_model_get_layer_outputs(dlb_model *m, size_t layer, size_t rows, float *host_out);
+dlb_status dlb_model_get_layer_errors(dlb_model *m, size_t layer, size_t rows, int which,
+                                      float *host_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DLB200_H_ */
