@@ -5,22 +5,34 @@
 // fp32 word (sign, exponent, top 10 mantissa bits) and lo(x) = x - hi(x) comes
 // from a residual plane in global memory.  Each 8-deep k step issues
 //     D += lo(A) hi(B);  D += hi(A) lo(B);  D += hi(A) hi(B)
-// into one fp32 accumulator in tensor memory.  The dropped lo*lo term is below
+// into an fp32 accumulator in tensor memory.  The dropped lo*lo term is below
 // 2^-20 of the product.
 //
+// Accumulation.  The tensor core adds into its fp32 accumulator with
+// truncation, so a long k loop into one accumulator loses about half an ulp of
+// the running sum per MMA, always towards zero: the error grows like k^1.5 and
+// at k = 4096 is ten times that of an fp32 FMA loop.  The k loop is therefore
+// cut into chunks of CHUNK_KB k-blocks; each chunk starts a fresh accumulator
+// in one of two tensor-memory buffers, and while the tensor core works on the
+// next chunk the eight drain warps read the finished one (tcgen05.ld) and add
+// it into fp32 registers with round-to-nearest.  The truncation then acts on
+// short sums only.
+//
 // One CTA computes a 128 x BN tile.  Warp 0 (one lane) streams operand tiles
-// with TMA (cp.async.bulk.tensor, 128-byte or 64-byte swizzle, no multicast)
-// into a ring of shared-memory stages guarded by full/empty mbarriers; warp 1
-// (one lane) issues tcgen05.mma and commits each stage back to the producer;
-// warps 2-5 drain the accumulator with tcgen05.ld, add the bias, and write
-// rows to global memory through a per-warp shared-memory transpose so that each
-// store instruction covers 128 contiguous bytes.
+// with TMA (cp.async.bulk.tensor, swizzled, no multicast) into a ring of
+// shared-memory stages guarded by full/empty mbarriers; warp 1 (one lane)
+// issues tcgen05.mma and commits each stage back to the producer and each chunk
+// to the drain warps; warps 2-9 drain, and at the end add the bias and write
+// rows to global memory through a per-warp shared-memory transpose (in the
+// then idle ring) so that each store instruction covers 128 contiguous bytes.
 //
 // Operand majors.  "K-major": k is the contiguous direction in global memory
-// (X and W in the forward product).  "MN-major": m (or n) is contiguous (W in
-// the input-gradient product, delta and X in the weight-gradient product).  An
-// MN-major tile is fetched through a 3-d view {32 floats, k, mn/32} so that it
-// lands in the canonical layout of 32-float columns of 8-row groups.
+// (X and W in the forward product); tiles are rows of BK floats under the 64- or
+// 128-byte swizzle.  "MN-major": m (or n) is contiguous (W in the
+// input-gradient product, delta and X in the weight-gradient product).  An
+// MN-major tile is fetched through a 3-d view {32 floats, k, mn/32} under the
+// "128-byte swizzle of 32-byte atoms", the only shared-memory layout a TF32
+// MN-major operand may have: 32-float columns, each a stack of 4-row groups.
 //
 // Every mbarrier wait is bounded by a clock budget; on expiry the kernel writes
 // DLB_ERR_TIMEOUT to the status word, waits (bounded) for its TMA loads in
@@ -35,7 +47,6 @@ namespace dlb {
 namespace {
 
 constexpr int BM = 128;
-constexpr int NUM_THREADS = 192;
 constexpr long long WAIT_BUDGET_CLOCKS = 4000000000LL;  // ~2 s
 constexpr long long DRAIN_BUDGET_CLOCKS = 20000000LL;   // ~10 ms
 
@@ -136,7 +147,31 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
   return d;
 }
 
-constexpr uint32_t LAYOUT_SW128 = 2, LAYOUT_SW64 = 4;
+constexpr uint32_t LAYOUT_SW128_BASE32B = 1, LAYOUT_SW128 = 2, LAYOUT_SW64 = 4;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 consecutive accumulator columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "
+      "[%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+constexpr int NUM_DRAIN_WARPS = 8;
+constexpr int NUM_THREADS = 64 + NUM_DRAIN_WARPS * 32;
 
 template <int BN, int BK, int STAGES>
 struct SmemPlan {
@@ -144,51 +179,58 @@ struct SmemPlan {
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int EPI_BYTES = 4 * 32 * 33 * 4;  // per-warp 32x33 transpose
-  static constexpr int BAR_OFFSET = RING_BYTES + EPI_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // + alignment slack
+  static constexpr int EPI_BYTES = NUM_DRAIN_WARPS * 32 * 33 * 4;  // reuses the ring
+  static constexpr int BAR_OFFSET = RING_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
+  static_assert(EPI_BYTES <= RING_BYTES, "transpose buffers live in the idle ring");
 };
 
-template <int BN, int BK, int STAGES, bool A_MN, bool B_MN>
+// Barrier slots: [0,S) full, [S,2S) empty, 2S..2S+1 accumulator full,
+// 2S+2..2S+3 accumulator empty, then three 8-byte scalars.
+template <int BN, int BK, int STAGES, int CHUNK_KB, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                        const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
                        float *__restrict__ C, long long ldc, int M, int N, int K,
                        const float *__restrict__ bias, int accumulate, int *status) {
   using P = SmemPlan<BN, BK, STAGES>;
+  static_assert(BN == 256 || BN == 128, "two accumulators of BN columns must fit 512 columns");
+  constexpr int HALF = BN / 2;  // columns per drain warp
   extern __shared__ uint8_t smem_raw[];
   // Swizzled tiles need 1024-byte alignment of each tile base.
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t *smem = smem_raw + (base - raw);
-  float *epi = reinterpret_cast<float *>(smem + P::RING_BYTES);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P::BAR_OFFSET);
-  // bars[0..STAGES) full, [STAGES..2*STAGES) empty, [2*STAGES] accumulator ready
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * STAGES + 1);
-  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2);
-  int *issued_kb = reinterpret_cast<int *>(bars + 2 * STAGES + 3);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * STAGES + 4);
+  uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 5);
+  int *issued_kb = reinterpret_cast<int *>(bars + 2 * STAGES + 6);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   const int num_kb = (K + BK - 1) / BK;
+  const int num_chunks = (num_kb + CHUNK_KB - 1) / CHUNK_KB;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES),
-                 acc_bar = smem_u32(bars + 2 * STAGES);
+                 acc_full0 = smem_u32(bars + 2 * STAGES), acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_empty0 + 8 * b, NUM_DRAIN_WARPS);
+    }
     *abort_flag = 0;
     *issued_kb = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    // Whole warp allocates BN columns of tensor memory (power of two >= 32).
+    // Whole warp allocates two accumulators of BN columns (power of two).
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_holder)),
-                 "r"((uint32_t)BN)
+                 "r"((uint32_t)(2 * BN))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -234,93 +276,108 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                              ((uint32_t)(BM >> 4) << 24);
       // K-major tiles: rows of BK*4 bytes, 8-row groups SBO apart, k step = 32 B
       // inside the swizzled row.  MN-major tiles: 32-float columns LBO apart,
-      // each a stack of 8-row (1024 B) groups, k step = one group.
+      // each a stack of 4-row (512 B) groups SBO apart, k step = 8 rows.
       constexpr uint32_t K_ROW = BK * 4;
       constexpr uint32_t K_LAYOUT = (BK == 32) ? LAYOUT_SW128 : LAYOUT_SW64;
-      constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, A_SBO = A_MN ? 1024 : 8 * K_ROW;
-      constexpr uint32_t B_LBO = B_MN ? BK * 128 : 16, B_SBO = B_MN ? 1024 : 8 * K_ROW;
-      constexpr uint32_t A_LAYOUT = A_MN ? LAYOUT_SW128 : K_LAYOUT;
-      constexpr uint32_t B_LAYOUT = B_MN ? LAYOUT_SW128 : K_LAYOUT;
+      constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, A_SBO = A_MN ? 512 : 8 * K_ROW;
+      constexpr uint32_t B_LBO = B_MN ? BK * 128 : 16, B_SBO = B_MN ? 512 : 8 * K_ROW;
+      constexpr uint32_t A_LAYOUT = A_MN ? LAYOUT_SW128_BASE32B : K_LAYOUT;
+      constexpr uint32_t B_LAYOUT = B_MN ? LAYOUT_SW128_BASE32B : K_LAYOUT;
       constexpr uint32_t A_KSTEP = A_MN ? 1024 : 32, B_KSTEP = B_MN ? 1024 : 32;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        ok = mbar_wait(full0 + 8 * s, ph, abort_flag, status);
+      int kb = 0;
+      for (int c = 0; c < num_chunks && ok; ++c) {
+        const int buf = c & 1;
+        const uint32_t use = (uint32_t)(c >> 1);
+        // The drain warps must have emptied this buffer's previous chunk.
+        ok = mbar_wait(acc_empty0 + 8 * buf, (use & 1) ^ 1, abort_flag, status);
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t st = base + s * P::STAGE_BYTES;
-        const uint32_t a_hi = st, a_lo = st + P::A_BYTES, b_hi = st + 2 * P::A_BYTES,
-                       b_lo = st + 2 * P::A_BYTES + P::B_BYTES;
+        const uint32_t d_tmem = tmem_acc + (uint32_t)(buf * BN);
+        const int kb_end = min(num_kb, kb + CHUNK_KB);
+        bool first = true;
+        for (; kb < kb_end; ++kb) {
+          const int s = kb % STAGES;
+          const uint32_t ph = (kb / STAGES) & 1;
+          ok = mbar_wait(full0 + 8 * s, ph, abort_flag, status);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t st = base + s * P::STAGE_BYTES;
+          const uint32_t a_hi = st, a_lo = st + P::A_BYTES, b_hi = st + 2 * P::A_BYTES,
+                         b_lo = st + 2 * P::A_BYTES + P::B_BYTES;
 #pragma unroll
-        for (int k8 = 0; k8 < BK / 8; ++k8) {
-          const uint64_t da_hi = make_smem_desc(a_hi + k8 * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
-          const uint64_t da_lo = make_smem_desc(a_lo + k8 * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
-          const uint64_t db_hi = make_smem_desc(b_hi + k8 * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
-          const uint64_t db_lo = make_smem_desc(b_lo + k8 * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
-          umma_tf32(tmem_acc, da_lo, db_hi, idesc, (kb | k8) != 0 ? 1u : 0u);
-          umma_tf32(tmem_acc, da_hi, db_lo, idesc, 1u);
-          umma_tf32(tmem_acc, da_hi, db_hi, idesc, 1u);
+          for (int k8 = 0; k8 < BK / 8; ++k8) {
+            const uint64_t da_hi = make_smem_desc(a_hi + k8 * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+            const uint64_t da_lo = make_smem_desc(a_lo + k8 * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+            const uint64_t db_hi = make_smem_desc(b_hi + k8 * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+            const uint64_t db_lo = make_smem_desc(b_lo + k8 * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+            umma_tf32(d_tmem, da_lo, db_hi, idesc, first ? 0u : 1u);
+            umma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
+            umma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
+            first = false;
+          }
+          umma_commit(empty0 + 8 * s);  // stage reusable once these MMAs retire
         }
-        umma_commit(empty0 + 8 * s);  // stage reusable once these MMAs retire
+        if (ok) umma_commit(acc_full0 + 8 * buf);  // chunk complete
       }
-      if (ok) umma_commit(acc_bar);   // accumulator complete
     }
   } else {
-    // ---------------- epilogue: warps 2..5 ----------------
-    const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
-    float *tile = epi + (warp - 2) * 32 * 33;
+    // ---------------- drain + epilogue: warps 2..9 ----------------
+    const int q = warp & 3;          // tensor-memory lane quadrant this warp may read
+    const int h = (warp - 2) >> 2;   // which half of the BN columns
+    float acc[HALF];
+#pragma unroll
+    for (int j = 0; j < HALF; ++j) acc[j] = 0.f;
     bool ok = true;
-    if (num_kb > 0) ok = mbar_wait(acc_bar, 0, abort_flag, status);
-    ok = __all_sync(0xffffffffu, ok);
-    tcgen05_fence_after();
-    if (ok) {
-      const int row_base = m0 + q * 32;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= N) break;
+    for (int c = 0; c < num_chunks; ++c) {
+      const int buf = c & 1;
+      const uint32_t use = (uint32_t)(c >> 1);
+      ok = mbar_wait(acc_full0 + 8 * buf, use & 1, abort_flag, status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + h * HALF);
+#pragma unroll
+      for (int j = 0; j < HALF / 32; ++j) {
         uint32_t v[32];
-        if (num_kb > 0) {
-          const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32);
-          asm volatile(
-              "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-              "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-              "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "
-              "[%32];"
-              : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-                "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]),
-                "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
-                "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-                "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
-                "=r"(v[31])
-              : "r"(taddr)
-              : "memory");
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        } else {
+        tmem_ld32(taddr + j * 32, v);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0u;
-        }
-        // lane owns row (row_base + lane): park its 32 values, then each
-        // instruction below stores one row's 32 consecutive floats.
+        for (int i = 0; i < 32; ++i) acc[j * 32 + i] += __uint_as_float(v[i]);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+    }
+    if (ok) {
+      // All MMAs have retired (the last chunk was committed), so the operand
+      // ring is idle and serves as the transpose buffer.
+      float *tile = reinterpret_cast<float *>(smem) + (warp - 2) * 32 * 33;
+      const int row_base = m0 + q * 32;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = __uint_as_float(v[j]);
-        __syncwarp();
-        const int col = col0 + lane;
-        if (col < N) {
-          const float b = bias ? __ldg(bias + col) : 0.f;
+      for (int j = 0; j < HALF / 32; ++j) {
+        const int col0 = n0 + h * HALF + j * 32;
+        if (col0 < N) {
+          // lane owns row (row_base + lane): park its 32 values, then each
+          // instruction below stores one row's 32 consecutive floats.
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tile[lane * 33 + i] = acc[j * 32 + i];
+          __syncwarp();
+          const int col = col0 + lane;
+          if (col < N) {
+            const float b = bias ? __ldg(bias + col) : 0.f;
 #pragma unroll 4
-          for (int r = 0; r < 32; ++r) {
-            const int row = row_base + r;
-            if (row < M) {
-              float *dst = C + (long long)row * ldc + col;
-              float val = tile[r * 33 + lane] + b;
-              if (accumulate) val += *dst;
-              *dst = val;
+            for (int r = 0; r < 32; ++r) {
+              const int row = row_base + r;
+              if (row < M) {
+                float *dst = C + (long long)row * ldc + col;
+                float val = tile[r * 33 + lane] + b;
+                if (accumulate) val += *dst;
+                *dst = val;
+              }
             }
           }
+          __syncwarp();
         }
-        __syncwarp();
       }
     }
   }
@@ -345,7 +402,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   if (warp == 1) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc),
-                 "r"((uint32_t)BN)
+                 "r"((uint32_t)(2 * BN))
                  : "memory");
   }
 }
@@ -397,7 +454,7 @@ bool tmap_mn_major(CUtensorMap *m, const float *ptr, uint64_t mn, uint64_t k, ui
   const cuuint32_t estr[3] = {1, 1, 1};
   return encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims,
                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -410,22 +467,22 @@ bool operand_ok(const GemmOperand &o, int mn, int k) {
 }
 
 struct TileConfig {
-  int bn, bk, stages;
+  int bn, bk, stages, chunk;
 };
-// Selected by DLB_GEMM_TILE=<bn>x<bk>x<stages> for experiments; default below.
+// Selected by DLB_GEMM_TILE=<bn>x<bk>x<stages>x<chunk k-blocks> for experiments.
 TileConfig tile_config() {
   static TileConfig cfg = [] {
-    TileConfig c{256, 16, 4};
+    TileConfig c{256, 16, 4, 4};
     if (const char *e = getenv("DLB_GEMM_TILE")) {
-      int bn, bk, st;
-      if (sscanf(e, "%dx%dx%d", &bn, &bk, &st) == 3) c = TileConfig{bn, bk, st};
+      int bn, bk, st, ch;
+      if (sscanf(e, "%dx%dx%dx%d", &bn, &bk, &st, &ch) == 4) c = TileConfig{bn, bk, st, ch};
     }
     return c;
   }();
   return cfg;
 }
 
-template <int BN, int BK, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int BK, int STAGES, int CHUNK_KB, bool A_MN, bool B_MN>
 dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
                   long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
   using P = SmemPlan<BN, BK, STAGES>;
@@ -449,7 +506,7 @@ dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, floa
     set_error("gemm_tcgen05: cuTensorMapEncodeTiled rejected an operand");
     return DLB_ERR_CUDA;
   }
-  auto kernel = gemm_tf32x3_kernel<BN, BK, STAGES, A_MN, B_MN>;
+  auto kernel = gemm_tf32x3_kernel<BN, BK, STAGES, CHUNK_KB, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
     DLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::TOTAL));
@@ -466,15 +523,16 @@ template <bool A_MN, bool B_MN>
 dlb_status launch_tile(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
                        long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
   const TileConfig t = tile_config();
-#define DLB_TILE(TBN, TBK, TST)                               \
-  if (t.bn == (TBN) && t.bk == (TBK) && t.stages == (TST))   \
-    return launch<TBN, TBK, TST, A_MN, B_MN>(ctx, A, B, C, ldc, M, N, K, ep);
-  DLB_TILE(256, 16, 4)
-  DLB_TILE(256, 32, 2)
-  DLB_TILE(128, 32, 3)
-  DLB_TILE(128, 16, 6)
+#define DLB_TILE(TBN, TBK, TST, TCH)                                              \
+  if (t.bn == (TBN) && t.bk == (TBK) && t.stages == (TST) && t.chunk == (TCH))   \
+    return launch<TBN, TBK, TST, TCH, A_MN, B_MN>(ctx, A, B, C, ldc, M, N, K, ep);
+  DLB_TILE(256, 16, 4, 4)
+  DLB_TILE(256, 16, 4, 2)
+  DLB_TILE(256, 16, 4, 16)
+  DLB_TILE(256, 32, 2, 2)
+  DLB_TILE(128, 32, 3, 2)
 #undef DLB_TILE
-  set_error("gemm_tcgen05: tile %dx%dx%d is not compiled in", t.bn, t.bk, t.stages);
+  set_error("gemm_tcgen05: tile %dx%dx%dx%d is not compiled in", t.bn, t.bk, t.stages, t.chunk);
   return DLB_ERR_UNSUPPORTED;
 }
 
