@@ -94,7 +94,7 @@ def build_model(m, cfg, batch=None):
     if cfg.get("time_delays"):
         m.set_seq_w(cfg["time_delays"])
     m.set_max_batch_size(batch or cfg["batch"])
-    m.set_mp(True)
+    m.set_mp(cfg.get("mp", True))
     return m
 
 

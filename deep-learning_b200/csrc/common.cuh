@@ -5,6 +5,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <vector>
+
 #include "dlb200.h"
 
 typedef struct ncclComm *ncclComm_t;
@@ -22,6 +24,15 @@ struct dlb_ctx {
   bool use_tensor_core = true;
   bool tensor_core_ok = false;  // device is sm_100
   uint64_t launches = 0;
+  cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
+  // Optional per-launch record of the tensor-core GEMM.
+  struct GemmRecord {
+    cudaEvent_t start, stop;
+    double flops;
+  };
+  bool gemm_profile = false;
+  std::vector<GemmRecord> gemm_records;
+  std::vector<cudaEvent_t> event_pool;
 };
 
 namespace dlb {

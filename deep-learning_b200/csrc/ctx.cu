@@ -68,7 +68,23 @@ dlb_status gemm(dlb_ctx *ctx, const GemmOperand &A_in, const GemmOperand &B_in, 
         B.lo = s + a_n;
       }
     }
-    return gemm_tcgen05(ctx, A, B, C, ldc, M, N, K, ep);
+    if (!ctx->gemm_profile) return gemm_tcgen05(ctx, A, B, C, ldc, M, N, K, ep);
+    dlb_ctx::GemmRecord rec;
+    cudaEvent_t *ev[2] = {&rec.start, &rec.stop};
+    for (cudaEvent_t *e : ev) {
+      if (!ctx->event_pool.empty()) {
+        *e = ctx->event_pool.back();
+        ctx->event_pool.pop_back();
+      } else {
+        DLB_CUDA(cudaEventCreate(e));
+      }
+    }
+    rec.flops = 2.0 * M * N * K;
+    DLB_CUDA(cudaEventRecord(rec.start, ctx->stream));
+    const dlb_status st = gemm_tcgen05(ctx, A, B, C, ldc, M, N, K, ep);
+    DLB_CUDA(cudaEventRecord(rec.stop, ctx->stream));
+    ctx->gemm_records.push_back(rec);
+    return st;
   }
   return gemm_simt(ctx, A, B, C, ldc, M, N, K, ep);
 }
@@ -178,6 +194,13 @@ dlb_status dlb_ctx_destroy(dlb_ctx *ctx) {
   if (ctx->comm && nccl() && nccl()->CommDestroy) nccl()->CommDestroy(ctx->comm);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->timer_start) cudaEventDestroy(ctx->timer_start);
+  if (ctx->timer_stop) cudaEventDestroy(ctx->timer_stop);
+  for (auto &r : ctx->gemm_records) {
+    cudaEventDestroy(r.start);
+    cudaEventDestroy(r.stop);
+  }
+  for (cudaEvent_t e : ctx->event_pool) cudaEventDestroy(e);
   if (ctx->stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
   return DLB_OK;
@@ -205,6 +228,50 @@ dlb_status dlb_ctx_set_tensor_core(dlb_ctx *ctx, int enable) {
 }
 
 uint64_t dlb_ctx_launch_count(dlb_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+dlb_status dlb_ctx_timer_start(dlb_ctx *ctx) {
+  DLB_REQUIRE(ctx, "dlb_ctx_timer_start: null");
+  if (!ctx->timer_start) {
+    DLB_CUDA(cudaEventCreate(&ctx->timer_start));
+    DLB_CUDA(cudaEventCreate(&ctx->timer_stop));
+  }
+  DLB_CUDA(cudaEventRecord(ctx->timer_start, ctx->stream));
+  return DLB_OK;
+}
+
+dlb_status dlb_ctx_timer_stop(dlb_ctx *ctx, float *milliseconds) {
+  DLB_REQUIRE(ctx && milliseconds && ctx->timer_start, "dlb_ctx_timer_stop: no timer running");
+  DLB_CUDA(cudaEventRecord(ctx->timer_stop, ctx->stream));
+  DLB_CUDA(cudaEventSynchronize(ctx->timer_stop));
+  DLB_CUDA(cudaEventElapsedTime(milliseconds, ctx->timer_start, ctx->timer_stop));
+  return DLB_OK;
+}
+
+dlb_status dlb_ctx_gemm_profile(dlb_ctx *ctx, int enable) {
+  DLB_REQUIRE(ctx, "dlb_ctx_gemm_profile: null");
+  ctx->gemm_profile = enable != 0;
+  return DLB_OK;
+}
+
+dlb_status dlb_ctx_gemm_profile_read(dlb_ctx *ctx, uint64_t *launches, double *milliseconds,
+                                     double *flops) {
+  DLB_REQUIRE(ctx && launches && milliseconds && flops, "dlb_ctx_gemm_profile_read: null");
+  DLB_CUDA(cudaStreamSynchronize(ctx->stream));
+  *launches = 0;
+  *milliseconds = 0.0;
+  *flops = 0.0;
+  for (auto &r : ctx->gemm_records) {
+    float ms = 0.f;
+    DLB_CUDA(cudaEventElapsedTime(&ms, r.start, r.stop));
+    *milliseconds += ms;
+    *flops += r.flops;
+    *launches += 1;
+    ctx->event_pool.push_back(r.start);
+    ctx->event_pool.push_back(r.stop);
+  }
+  ctx->gemm_records.clear();
+  return DLB_OK;
+}
 
 dlb_status dlb_malloc(dlb_ctx *ctx, void **dev_ptr, size_t bytes) {
   DLB_REQUIRE(ctx && dev_ptr, "dlb_malloc: null");

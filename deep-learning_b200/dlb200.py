@@ -45,6 +45,10 @@ SIGNATURES = {
     "dlb_ctx_stream": (_vp, [_vp]),
     "dlb_ctx_set_tensor_core": (_i, [_vp, _i]),
     "dlb_ctx_launch_count": (_u64, [_vp]),
+    "dlb_ctx_timer_start": (_i, [_vp]),
+    "dlb_ctx_timer_stop": (_i, [_vp, C.POINTER(_f)]),
+    "dlb_ctx_gemm_profile": (_i, [_vp, _i]),
+    "dlb_ctx_gemm_profile_read": (_i, [_vp, C.POINTER(_u64), C.POINTER(_d), C.POINTER(_d)]),
     "dlb_malloc": (_i, [_vp, C.POINTER(_vp), _sz]),
     "dlb_free": (_i, [_vp, _vp]),
     "dlb_memset": (_i, [_vp, _vp, _i, _sz]),
@@ -177,6 +181,23 @@ class Context:
 
     def launch_count(self):
         return int(self.L.dlb_ctx_launch_count(self.h))
+
+    def timer_start(self):
+        check(self.L.dlb_ctx_timer_start(self.h), "dlb_ctx_timer_start")
+
+    def timer_stop(self):
+        ms = _f(0.0)
+        check(self.L.dlb_ctx_timer_stop(self.h, C.byref(ms)), "dlb_ctx_timer_stop")
+        return ms.value
+
+    def gemm_profile(self, on):
+        check(self.L.dlb_ctx_gemm_profile(self.h, int(on)), "dlb_ctx_gemm_profile")
+
+    def gemm_profile_read(self):
+        """(launches, total milliseconds, total algorithmic FLOPs) since the last read."""
+        n, ms, fl = _u64(0), _d(0.0), _d(0.0)
+        check(self.L.dlb_ctx_gemm_profile_read(self.h, C.byref(n), C.byref(ms), C.byref(fl)), "gemm_profile_read")
+        return int(n.value), ms.value, fl.value
 
     @property
     def stream(self):

@@ -72,6 +72,19 @@ void *dlb_ctx_stream(dlb_ctx *ctx); /* cudaStream_t */
 dlb_status dlb_ctx_set_tensor_core(dlb_ctx *ctx, int enable);
 /* Number of kernels this context has launched since creation. */
 uint64_t dlb_ctx_launch_count(dlb_ctx *ctx);
+/* Device-side timing on the context's stream (CUDA events): start records an
+ * event, stop records another, waits for it and returns the milliseconds
+ * between the two. */
+dlb_status dlb_ctx_timer_start(dlb_ctx *ctx);
+dlb_status dlb_ctx_timer_stop(dlb_ctx *ctx, float *milliseconds);
+/* Per-launch timing of the tensor-core GEMM: while enabled every launch is
+ * bracketed by a pair of events.  dlb_ctx_gemm_profile_read waits for the
+ * stream, returns the number of launches, their summed duration and their
+ * summed algorithmic FLOPs (2*M*N*K each, not multiplied by the three TF32
+ * passes), and clears the record. */
+dlb_status dlb_ctx_gemm_profile(dlb_ctx *ctx, int enable);
+dlb_status dlb_ctx_gemm_profile_read(dlb_ctx *ctx, uint64_t *launches, double *milliseconds,
+                                     double *flops);
 
 /* Device memory for callers without their own CUDA binding. */
 dlb_status dlb_malloc(dlb_ctx *ctx, void **dev_ptr, size_t bytes);

@@ -1,0 +1,64 @@
+"""Generates the committed golden fixtures of the fully-connected training step
+from the reference library's own code (oracle/_ref/libdlref.so, built by
+`make -C oracle` where the reference sources are present).
+
+    python tests/golden/make_golden.py
+
+Each fixture is a small .npz holding the seeded inputs, targets, dropout masks
+and initial parameters of one workload and what the reference produced from
+them: activations, errors and gradients of the first step, parameters after
+step 1 and after the last step, every step's loss and the running batch
+renormalization statistics.  The workloads are reduced shapes of the benchmark
+configurations so that the files stay a few hundred KB in total.
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+for sub in ("deep-learning_b200", "oracle", "tests"):
+    sys.path.insert(0, os.path.join(ROOT, sub))
+
+import configs  # noqa: E402
+import ref_binding  # noqa: E402
+import util  # noqa: E402
+from enums import ACTIVATION, LAYER_DROPOUT, OPTIMIZER  # noqa: E402
+
+
+def cases():
+    """name -> (config, steps).  Also imported by the tests."""
+    brn = configs.deep_brn_mlp
+    return {
+        "mlp_softmax_adam": (configs.mlp_softmax(n_in=36, hidden=24, n_out=10, batch=16), 12),
+        "brn_selu_bernoulli_amsbound": (brn(20, 32, 2, 12, 24), 12),
+        "brn_elu_inverted_adabound": (brn(20, 32, 2, 12, 24, af=ACTIVATION.ELU, optimizer=OPTIMIZER.ADABOUND,
+                                          dropout=LAYER_DROPOUT.BERNOULLI_INVERTED), 12),
+        "brn_isrlu_nosadam": (brn(20, 32, 2, 12, 24, af=ACTIVATION.ISRLU, optimizer=OPTIMIZER.NOSADAM), 12),
+        "brn_relu_amsgrad_nodrop": (brn(20, 32, 2, 12, 24, af=ACTIVATION.RELU, optimizer=OPTIMIZER.AMSGRAD,
+                                        dropout=None), 12),
+        "brn_lrelu_adam_ragged": (brn(19, 30, 2, 7, 13, af=ACTIVATION.LEAKY_RELU, optimizer=OPTIMIZER.ADAM), 12),
+    }
+
+
+def main():
+    if not ref_binding.available():
+        sys.exit("oracle/_ref/libdlref.so is missing: run `make -C oracle` where the reference sources are")
+    for name, (cfg, steps) in cases().items():
+        ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+        p0 = ref.get_array("parameters")
+        X, Y = configs.synthetic_batch(cfg)
+        masks = configs.dropout_masks(cfg)
+        out = util.trace(ref, cfg, steps=steps, X=X, Y=Y, masks=masks)
+        blob = {"in_X": X, "in_Y": Y, "in_params": p0, "steps": np.int64(steps)}
+        for li, mk in masks.items():
+            blob[f"in_mask{li}"] = mk
+        blob.update({f"out_{k}": v for k, v in out.items()})
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **blob)
+        print(f"{name}: {os.path.getsize(path)} bytes, loss {out['losses'][0]:.6f} -> {out['losses'][-1]:.6f}")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,120 @@
+"""Whole-step parity on the GPU through the Model entry points of the C ABI
+(forward_pass, compute_error, backward_pass, update_derivatives,
+update_weights): against the committed golden fixtures of the reference, the
+CPU restatement, and, where it has been built, the compiled reference."""
+import numpy as np
+import pytest
+
+import configs
+import dlb200
+import fc_step
+import golden_io
+import ref_binding
+import util
+from enums import ACTIVATION, LAYER_DROPOUT, OPTIMIZER
+
+pytestmark = pytest.mark.gpu
+
+# rel-err (L2) bars of the drop-in: activations, errors, gradients and updated
+# weights after one step; parameters after many steps.  The many-step bar is
+# widened to the reference's own serial-vs-threaded drift where that is larger.
+TOL_1 = 1e-5
+TOL_N = 1e-4
+# Element-wise worst case of the updated weights: an Adam-family first step is
+# lr * g / (|g| + eps), so weights whose gradient is of the order of eps move by
+# an amount that any change of summation order shifts.  The reference differs
+# from itself (one thread vs many) by this much.
+TOL_1_MAX = 2e-4
+
+
+def gpu_model(ctx, cfg, params):
+    return util.build(dlb200.Model(ctx), cfg, params=params)
+
+
+@pytest.mark.parametrize("name", sorted(golden_io.CASES))
+def test_model_matches_golden(gpu_ctx, name):
+    cfg, steps, X, Y, masks, p0, want = golden_io.load(name)
+    got = util.trace(gpu_model(gpu_ctx, cfg, p0), cfg, steps, X, Y, masks)
+    assert gpu_ctx.sync() == 0
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_1, f"{name}/{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+
+
+CASES = [
+    configs.mlp_softmax(),                                   # 784-256-10, batch 128
+    configs.deep_brn_mlp(256, 512, 4, 256, 512),             # reduced deep MLP, tensor-core tiles
+    configs.deep_brn_mlp(96, 160, 2, 40, 200, af=ACTIVATION.ELU, optimizer=OPTIMIZER.ADABOUND,
+                         dropout=LAYER_DROPOUT.BERNOULLI_INVERTED),
+    configs.deep_brn_mlp(130, 70, 3, 9, 33, af=ACTIVATION.ISRLU, optimizer=OPTIMIZER.NOSADAM),   # ragged
+]
+
+
+@pytest.mark.parametrize("cfg", CASES, ids=lambda c: c["name"])
+def test_model_one_step_vs_restatement(gpu_ctx, cfg):
+    ora = util.build(fc_step.OracleModel(), cfg)
+    rng = np.random.default_rng(0)
+    p0 = ora.get_array("parameters")
+    nw = ora.size("total_weights")
+    p0[:nw] = (rng.standard_normal(nw) / np.sqrt(cfg["layers"][1]["units"])).astype(np.float32)
+    ora.set_array("parameters", p0)
+    want = util.trace(ora, cfg, steps=3)
+    got = util.trace(gpu_model(gpu_ctx, cfg, p0), cfg, steps=3)
+    assert gpu_ctx.sync() == 0
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_1, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+    assert util.rel_max(got["params1"], want["params1"]) <= TOL_1_MAX
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("cfg", CASES[:2], ids=lambda c: c["name"])
+def test_model_100_steps_vs_compiled_reference(gpu_ctx, cfg):
+    serial = util.build(ref_binding.RefModel(), dict(cfg, mp=False), seed=0)
+    p0 = serial.get_array("parameters")
+    ws = util.trace(serial, dict(cfg, mp=False), steps=100)
+    want = util.trace(util.build(ref_binding.RefModel(), cfg, params=p0), cfg, steps=100)
+    got = util.trace(gpu_model(gpu_ctx, cfg, p0), cfg, steps=100)
+    assert gpu_ctx.sync() == 0
+    drift1 = util.rel_l2(ws["params1"], want["params1"])
+    drift100 = util.rel_l2(ws["params_last"], want["params_last"])
+    cmp = util.compare(got, want)
+    print({k: f"{v[0]:.2e}" for k, v in cmp.items()}, f"reference self-drift {drift1:.2e} / {drift100:.2e}")
+    for key in [k for k in cmp if k.startswith(("act", "delta", "grads"))]:
+        assert cmp[key][0] <= TOL_1, f"{key}: {cmp[key][0]:.2e}"
+    assert cmp["params1"][0] <= max(TOL_1, 3 * drift1)
+    assert cmp["params_last"][0] <= max(TOL_N, 3 * drift100)
+    assert util.rel_l2(got["losses"], want["losses"]) <= TOL_N
+
+
+def test_glorot_uniform_draw_matches_reference_generator(gpu_ctx):
+    """Same std::mt19937 stream and draw order as the reference: the fixture's
+    initial parameters were drawn by the reference from seed 0."""
+    cfg, _, _, _, _, p0, _ = golden_io.load("mlp_softmax_adam")
+    m = util.build(dlb200.Model(gpu_ctx), cfg, seed=0)
+    assert util.rel_max(m.get_array("parameters"), p0) <= 1e-6
+
+
+def test_row_pointer_inputs_and_device_inputs_agree(gpu_ctx):
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96)
+    X, Y = configs.synthetic_batch(cfg)
+    B = cfg["batch"]
+    a = util.build(dlb200.Model(gpu_ctx), cfg, seed=3)
+    b = util.build(dlb200.Model(gpu_ctx), cfg, seed=3)
+    a.forward_pass(B, X); a.compute_error(B, Y); a.backward_pass(B); a.update_derivatives(B)
+    a.merge_derivatives(); a.update_weights(B, B)
+    b.train_step_device(B, gpu_ctx.array(X), gpu_ctx.array(Y))
+    assert np.array_equal(a.get_array("parameters"), b.get_array("parameters"))
+
+
+def test_unsupported_configurations_are_refused(gpu_ctx):
+    m = dlb200.Model(gpu_ctx)
+    m.compile([3, 3, 3], [8, 8, 4])
+    with pytest.raises(dlb200.DlbError):
+        m.set_layer_activation_function(1, 18)       # SIGMOID: outside the path
+    with pytest.raises(dlb200.DlbError):
+        m.Set__Layer_Normalization(2, 2)             # not on the output layer
+    with pytest.raises(dlb200.DlbError):
+        m.set_dropout(2, 2, 0.5)                     # not on the output layer
+    with pytest.raises(dlb200.DlbError):
+        m.set_optimizer(6)                           # GD
+    with pytest.raises(dlb200.DlbError):
+        m.forward_pass(4, np.zeros((4, 8), np.float32))   # activations never set (reference default: sigmoid)

@@ -1,0 +1,284 @@
+"""Per-kernel parity on the GPU, through the C ABI, against the CPU restatement
+(oracle/fc_step.py) on seeded inputs; integer/flag work bit-exact, floating
+point within the tolerance written beside each check."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import dlb200
+import fc_step
+import util
+from dlb200 import check
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5     # rel-err bar for activations and gradients after one step
+GEMM_TOL = 2e-6    # rel_l2 of a 3xTF32 product against the float64 product
+
+
+def _fc(ctx, kind, A, Bm, rows, n_in, n_out, tensor_core, bias=None, accumulate=None):
+    L = ctx.L
+    ctx.set_tensor_core(tensor_core)
+    a, b = ctx.array(A), ctx.array(Bm)
+    if kind == "fwd":
+        out = ctx.zeros((rows, n_out))
+        bz = ctx.array(bias) if bias is not None else None
+        check(L.dlb_fc_forward(ctx.h, a.ptr, None, b.ptr, None, bz.ptr if bz else None, out.ptr, rows, n_in, n_out))
+    elif kind == "dx":
+        out = ctx.zeros((rows, n_in))
+        check(L.dlb_fc_backward_input(ctx.h, a.ptr, None, b.ptr, None, out.ptr, rows, n_in, n_out))
+    else:
+        out = ctx.array(accumulate) if accumulate is not None else ctx.zeros((n_out, n_in))
+        db = ctx.zeros(n_out) if bias is not None else None
+        check(L.dlb_fc_weight_gradient(ctx.h, a.ptr, None, b.ptr, None, out.ptr, db.ptr if db else None, rows,
+                                       n_in, n_out, 1 if accumulate is not None else 0))
+        assert ctx.sync() == 0
+        ctx.set_tensor_core(1)
+        return out.get(), (db.get() if db else None)
+    assert ctx.sync() == 0
+    ctx.set_tensor_core(1)
+    return out.get()
+
+
+def _operands(kind, rows, n_in, n_out, rng):
+    if kind == "fwd":
+        return rng.standard_normal((rows, n_in), dtype=np.float32), rng.standard_normal((n_out, n_in), dtype=np.float32)
+    if kind == "dx":
+        return rng.standard_normal((rows, n_out), dtype=np.float32), rng.standard_normal((n_out, n_in), dtype=np.float32)
+    return rng.standard_normal((rows, n_out), dtype=np.float32), rng.standard_normal((rows, n_in), dtype=np.float32)
+
+
+def _exact(kind, A, Bm):
+    A, Bm = A.astype(np.float64), Bm.astype(np.float64)
+    return A @ Bm.T if kind == "fwd" else (A @ Bm if kind == "dx" else A.T @ Bm)
+
+
+# rows, n_in, n_out: aligned tiles, k tails (784), partial m/n tiles, and
+# shapes only the CUDA-core kernel can take (row pitch not a multiple of 16 B).
+SHAPES = [(128, 64, 256), (256, 512, 512), (384, 784, 256), (200, 96, 160), (512, 1024, 1024), (128, 256, 10),
+          (37, 19, 7), (1, 4, 4)]
+
+
+@pytest.mark.parametrize("kind", ["fwd", "dx", "dw"])
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("tensor_core", [1, 0], ids=["tcgen05", "cuda-core"])
+def test_fc_products(gpu_ctx, kind, shape, tensor_core):
+    rows, n_in, n_out = shape
+    rng = np.random.default_rng(hash((kind, shape)) % 2**32)
+    A, Bm = _operands(kind, rows, n_in, n_out, rng)
+    want = _exact(kind, A, Bm)
+    got = _fc(gpu_ctx, kind, A, Bm, rows, n_in, n_out, tensor_core)
+    if kind == "dw":
+        got = got[0]
+    assert util.rel_l2(got, want) <= GEMM_TOL
+    assert util.rel_max(got, want) <= 5 * GEMM_TOL
+
+
+def test_fc_forward_bias_and_gradient_accumulate(gpu_ctx):
+    rng = np.random.default_rng(3)
+    rows, n_in, n_out = 256, 128, 384
+    X, W = _operands("fwd", rows, n_in, n_out, rng)
+    bias = rng.standard_normal(n_out, dtype=np.float32)
+    got = _fc(gpu_ctx, "fwd", X, W, rows, n_in, n_out, 1, bias=bias)
+    assert util.rel_l2(got, _exact("fwd", X, W) + bias) <= GEMM_TOL
+    delta = rng.standard_normal((rows, n_out), dtype=np.float32)
+    start = rng.standard_normal((n_out, n_in), dtype=np.float32)
+    dW, db = _fc(gpu_ctx, "dw", delta, X, rows, n_in, n_out, 1, bias=bias, accumulate=start)
+    assert util.rel_l2(dW, start + _exact("dw", delta, X)) <= GEMM_TOL
+    assert util.rel_l2(db, delta.astype(np.float64).sum(0)) <= GEMM_TOL
+
+
+def test_large_k_accumulation_stays_fp32_faithful(gpu_ctx):
+    """k = 4096: the chunked drain keeps the tensor core's truncating
+    accumulation from growing with k; the product is as close to the exact one
+    as an fp32 FMA loop."""
+    rng = np.random.default_rng(11)
+    X, W = _operands("fwd", 256, 4096, 256, rng)
+    want = _exact("fwd", X, W)
+    tc = util.rel_l2(_fc(gpu_ctx, "fwd", X, W, 256, 4096, 256, 1), want)
+    fma = util.rel_l2(_fc(gpu_ctx, "fwd", X, W, 256, 4096, 256, 0), want)
+    assert tc <= GEMM_TOL and tc <= 3 * fma + 1e-7
+
+
+def test_split_tf32_is_exact_residual(gpu_ctx):
+    rng = np.random.default_rng(1)
+    x = (rng.standard_normal(100_003) * 10.0 ** rng.integers(-6, 6, 100_003)).astype(np.float32)
+    xd, lo = gpu_ctx.array(x), gpu_ctx.empty(x.shape)
+    check(gpu_ctx.L.dlb_split_tf32(gpu_ctx.h, xd.ptr, lo.ptr, x.size))
+    got = lo.get()
+    hi = (x.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    resid = x - hi                                   # exact in fp32
+    assert (got.view(np.uint32) & np.uint32(0x1FFF)).max() == 0   # a TF32 value
+    assert np.all(np.abs(got - resid) <= np.abs(resid) * 2.0 ** -11 + 1e-45)
+
+
+def _brn_arrays(ctx, n, rng, gamma=None, beta=None):
+    host = dict(mean=np.zeros(n, np.float32), sigma=np.ones(n, np.float32),
+                mean_average=(0.1 * rng.standard_normal(n)).astype(np.float32),
+                sigma_average=(1 + 0.1 * rng.random(n)).astype(np.float32),
+                r=np.ones(n, np.float32), d=np.zeros(n, np.float32),
+                gamma=gamma if gamma is not None else (1 + 0.2 * rng.standard_normal(n)).astype(np.float32),
+                beta=beta if beta is not None else (0.1 * rng.standard_normal(n)).astype(np.float32))
+    dev = {k: ctx.array(v) for k, v in host.items()}
+    u = dlb200.BrnUnitArrays(**{k: dev[k].ptr for k in dev})
+    return host, dev, u
+
+
+@pytest.mark.parametrize("rows,n", [(512, 256), (300, 130), (64, 7), (4096, 1024)])
+def test_batch_renorm_forward(gpu_ctx, rows, n):
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rng = np.random.default_rng(rows * 131 + n)
+    Z = (rng.standard_normal((rows, n)) * 2 + 0.5).astype(np.float32)
+    host, dev, u = _brn_arrays(ctx, n, rng)
+    zd, sums = ctx.array(Z), ctx.zeros(2 * n, np.float64)
+    check(L.dlb_brn_forward_sums(ctx.h, zd.ptr, rows, n, sums.ptr))
+    check(L.dlb_brn_forward_finalize(ctx.h, sums.ptr, rows, n, 0.99, 1e-5, 3.0, 5.0, C.byref(u)))
+    s = sums.get()
+    np.testing.assert_allclose(s[:n], Z.astype(np.float64).sum(0), rtol=1e-6, atol=1e-4)
+    np.testing.assert_allclose(s[n:], (Z.astype(np.float64) ** 2).sum(0), rtol=1e-6)
+    state = dict(mean_average=host["mean_average"].copy(), variance_average=host["sigma_average"].copy(),
+                 gamma=host["gamma"], beta=host["beta"])
+    x_hat, y = fc_step.brn_forward(Z, state, dict(momentum=0.99, eps=1e-5, r_max=3.0, d_max=5.0))
+    for mine, theirs in (("mean", "mean"), ("sigma", "variance"), ("mean_average", "mean_average"),
+                         ("sigma_average", "variance_average"), ("r", "r"), ("d", "d")):
+        assert util.rel_max(dev[mine].get(), state[theirs]) <= F32_TOL, mine
+    # normalise + SELU + Bernoulli mask, and the residual plane of the result
+    mask = (rng.random(n) < 0.9).astype(np.uint8)
+    md, A, Alo = ctx.array(mask), ctx.empty((rows, n)), ctx.empty((rows, n))
+    dp = dlb200.DropoutDesc(fc_step.DROPOUT_BERNOULLI, 0.9, md.ptr, None)
+    check(L.dlb_activation_forward(ctx.h, zd.ptr, C.byref(u), fc_step.AF_SELU, C.byref(dp), A.ptr, Alo.ptr, rows, n))
+    want = fc_step.apply_dropout(fc_step.af_fire(fc_step.AF_SELU, y), fc_step.DROPOUT_BERNOULLI, 0.9, mask)
+    got = A.get()
+    assert util.rel_max(got, want) <= F32_TOL
+    assert np.array_equal(got[:, mask == 0], np.zeros_like(got[:, mask == 0]))   # dropped units: exact zeros
+    hi = (got.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    assert np.all(np.abs(Alo.get() - (got - hi)) <= np.abs(got - hi) * 2.0 ** -11 + 1e-45)
+
+
+@pytest.mark.parametrize("af", [fc_step.AF_RELU, fc_step.AF_LEAKY_RELU, fc_step.AF_ELU, fc_step.AF_SELU,
+                                fc_step.AF_ISRLU, fc_step.AF_LINEAR])
+@pytest.mark.parametrize("dropout", [fc_step.DROPOUT_NONE, fc_step.DROPOUT_BERNOULLI_INVERTED, fc_step.DROPOUT_UOUT])
+def test_activation_forward_without_norm(gpu_ctx, af, dropout):
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rng = np.random.default_rng(af * 10 + dropout)
+    rows, n = 129, 67
+    Z = (rng.standard_normal((rows, n)) * 2).astype(np.float32)
+    mask = (rng.random(n) < 0.8).astype(np.uint8)
+    noise = ((rng.random((rows, n)) * 2 - 1) * 0.1).astype(np.float32)
+    zd, md, nd, A = ctx.array(Z), ctx.array(mask), ctx.array(noise), ctx.empty((rows, n))
+    dp = dlb200.DropoutDesc(dropout, 0.8, md.ptr, nd.ptr)
+    check(L.dlb_activation_forward(ctx.h, zd.ptr, None, af, C.byref(dp) if dropout else None, A.ptr, None, rows, n))
+    want = fc_step.apply_dropout(fc_step.af_fire(af, Z), dropout, 0.8, mask, noise)
+    assert util.rel_max(A.get(), want) <= F32_TOL
+
+
+@pytest.mark.parametrize("af", [fc_step.AF_RELU, fc_step.AF_LEAKY_RELU, fc_step.AF_ELU, fc_step.AF_SELU,
+                                fc_step.AF_ISRLU])
+@pytest.mark.parametrize("rows,n", [(256, 128), (100, 37)])
+def test_batch_renorm_backward(gpu_ctx, af, rows, n):
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rng = np.random.default_rng(af * 1000 + rows + n)
+    Z = (rng.standard_normal((rows, n)) * 1.5 + 0.3).astype(np.float32)
+    host, dev, u = _brn_arrays(ctx, n, rng)
+    zd, sums = ctx.array(Z), ctx.zeros(2 * n, np.float64)
+    check(L.dlb_brn_forward_sums(ctx.h, zd.ptr, rows, n, sums.ptr))
+    check(L.dlb_brn_forward_finalize(ctx.h, sums.ptr, rows, n, 0.99, 1e-5, 3.0, 5.0, C.byref(u)))
+    mask = (rng.random(n) < 0.9).astype(np.uint8)
+    md, A = ctx.array(mask), ctx.empty((rows, n))
+    dp = dlb200.DropoutDesc(fc_step.DROPOUT_BERNOULLI, 0.9, md.ptr, None)
+    check(L.dlb_activation_forward(ctx.h, zd.ptr, C.byref(u), af, C.byref(dp), A.ptr, None, rows, n))
+    dA = rng.standard_normal((rows, n), dtype=np.float32)
+    dd, dlo, bs = ctx.array(dA), ctx.empty((rows, n)), ctx.zeros(4 * n, np.float64)
+    check(L.dlb_activation_backward(ctx.h, dd.ptr, zd.ptr, A.ptr, C.byref(u), af, rows, n, bs.ptr))
+    check(L.dlb_brn_backward_apply(ctx.h, dd.ptr, dlo.ptr, zd.ptr, C.byref(u), bs.ptr, rows, rows, n))
+    dg, db = ctx.zeros(n), ctx.zeros(n)
+    check(L.dlb_brn_backward_param_grads(ctx.h, bs.ptr, n, dg.ptr, db.ptr, 0))
+    # restatement
+    state = dict(mean_average=host["mean_average"].copy(), variance_average=host["sigma_average"].copy(),
+                 gamma=host["gamma"], beta=host["beta"])
+    x_hat, y = fc_step.brn_forward(Z, state, dict(momentum=0.99, eps=1e-5, r_max=3.0, d_max=5.0))
+    a = fc_step.apply_dropout(fc_step.af_fire(af, y), fc_step.DROPOUT_BERNOULLI, 0.9, mask)
+    e = (dA * fc_step.af_derive(af, y, a)).astype(np.float32)
+    dx, wg, wb = fc_step.brn_backward(e, Z, x_hat, state)
+    assert util.rel_l2(dd.get(), dx) <= F32_TOL
+    assert util.rel_l2(dg.get(), wg) <= F32_TOL and util.rel_l2(db.get(), wb) <= F32_TOL
+
+
+def test_softmax_and_cross_entropy_delta(gpu_ctx):
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rng = np.random.default_rng(2)
+    for rows, n in ((128, 10), (77, 1000), (5, 3)):
+        Z = (rng.standard_normal((rows, n)) * 3).astype(np.float32)
+        Y = np.zeros((rows, n), np.float32)
+        Y[np.arange(rows), rng.integers(0, n, rows)] = 1
+        zd, yd, Q, D = ctx.array(Z), ctx.array(Y), ctx.empty((rows, n)), ctx.empty((rows, n))
+        loss = ctx.zeros(1, np.float64)
+        check(L.dlb_softmax_forward(ctx.h, zd.ptr, Q.ptr, rows, n))
+        check(L.dlb_loss_delta(ctx.h, fc_step.LOSS_CROSS_ENTROPY, fc_step.AF_SOFTMAX, zd.ptr, Q.ptr, yd.ptr, D.ptr,
+                               None, rows, n, rows, loss.ptr))
+        q = fc_step.softmax(Z)
+        total, delta = fc_step.loss_and_delta(fc_step.LOSS_CROSS_ENTROPY, fc_step.AF_SOFTMAX, Z, q, Y)
+        assert util.rel_max(Q.get(), q) <= F32_TOL
+        assert util.rel_max(D.get(), delta) <= F32_TOL
+        np.testing.assert_allclose(loss.get()[0], total, rtol=1e-6)
+
+
+def test_mse_delta(gpu_ctx):
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rng = np.random.default_rng(4)
+    rows, n = 333, 41
+    pre = rng.standard_normal((rows, n), dtype=np.float32)
+    Y = rng.standard_normal((rows, n), dtype=np.float32)
+    pd, yd, D, loss = ctx.array(pre), ctx.array(Y), ctx.empty((rows, n)), ctx.zeros(1, np.float64)
+    check(L.dlb_loss_delta(ctx.h, fc_step.LOSS_MSE, fc_step.AF_LINEAR, pd.ptr, pd.ptr, yd.ptr, D.ptr, None, rows, n,
+                           2 * rows, loss.ptr))
+    total, delta = fc_step.loss_and_delta(fc_step.LOSS_MSE, fc_step.AF_LINEAR, pre, pre, Y, global_rows=2 * rows)
+    assert util.rel_max(D.get(), delta) <= 1e-6
+    np.testing.assert_allclose(loss.get()[0], total, rtol=1e-9)
+
+
+@pytest.mark.parametrize("rule", [fc_step.OPT_ADAM, fc_step.OPT_AMSGRAD, fc_step.OPT_ADABOUND,
+                                  fc_step.OPT_AMSBOUND, fc_step.OPT_NOSADAM, fc_step.OPT_ADAMAX])
+@pytest.mark.parametrize("n", [1_000_003, 4096, 5])
+def test_optimizer_sweep(gpu_ctx, rule, n):
+    """Flat-vector sweep: p ~ N(0, 0.02), g ~ N(0, 1e-3) refilled each step,
+    zero moments, 10 steps.  AdaMax has no reference implementation; its
+    expected values come from the published rule only."""
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rng = np.random.default_rng(rule * 7 + n % 97)
+    p = (0.02 * rng.standard_normal(n)).astype(np.float32)
+    g = (1e-3 * rng.standard_normal(n)).astype(np.float32)
+    hp = dict(adam_learning_rate=1e-3, adam_beta1=0.9, adam_beta2=0.999, adam_epsilon=1e-8, adam_gamma=0.1,
+              learning_rate_final=0.1, learning_gamma=1e-3)
+    pd, gd, m, v, vh = ctx.array(p), ctx.array(g), ctx.zeros(n), ctx.zeros(n), ctx.zeros(n)
+    hyper = (C.c_float * 8)(1e-3, 0.9, 0.999, 1e-8, 0.1, 0.1, 1e-3, 1.0)
+    t, prev = C.c_float(0), C.c_float(0)
+    po, mo, vo, vho, state = p.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.float32), {}
+    for step in range(10):
+        k = dlb200.OptimizerScalars()
+        check(L.dlb_optimizer_prepare(rule, hyper, C.byref(t), C.byref(prev), C.byref(k)))
+        if step:
+            gd.set(g)
+        check(L.dlb_optimizer_step(ctx.h, rule, C.byref(k), pd.ptr, gd.ptr, m.ptr, v.ptr, vh.ptr, None, n))
+        gg = g.copy()
+        fc_step.optimizer_update(rule, fc_step.optimizer_scalars(rule, hp, state), po, gg, mo, vo, vho)
+    assert ctx.sync() == 0
+    assert not gd.get().any()                       # gradient zeroed after use
+    assert util.rel_l2(pd.get() - p, po - p) <= F32_TOL
+    assert util.rel_l2(m.get(), mo) <= 1e-6 and util.rel_l2(v.get(), vo) <= 1e-6
+    if rule in (fc_step.OPT_AMSGRAD, fc_step.OPT_AMSBOUND):
+        assert util.rel_l2(vh.get(), vho) <= 1e-6
+
+
+def test_bad_arguments_are_refused(gpu_ctx):
+    ctx, L = gpu_ctx, gpu_ctx.L
+    x = ctx.zeros(16)
+    assert L.dlb_fc_forward(ctx.h, None, None, x.ptr, None, None, x.ptr, 1, 4, 4) == 1
+    assert L.dlb_fc_forward(ctx.h, x.ptr, None, x.ptr, None, None, x.ptr, 0, 4, 4) == 1
+    k = dlb200.OptimizerScalars()
+    assert L.dlb_optimizer_step(ctx.h, 6, C.byref(k), x.ptr, x.ptr, x.ptr, x.ptr, None, None, 16) == 3
+    assert L.dlb_optimizer_step(ctx.h, 5, C.byref(k), x.ptr, x.ptr, x.ptr, x.ptr, None, None, 16) == 1
+    assert L.dlb_loss_delta(ctx.h, 3, 11, x.ptr, x.ptr, x.ptr, x.ptr, None, 4, 4, 4, x.ptr) == 3
+    assert b"invalid" in L.dlb_status_string(1)
+    assert ctx.sync() == 0

@@ -1,0 +1,79 @@
+"""The CPU restatement (oracle/fc_step.py) against the reference: the committed
+golden fixtures the compiled reference produced, and, where oracle/_ref is
+built, the compiled reference itself on larger seeded workloads."""
+import numpy as np
+import pytest
+
+import configs
+import fc_step
+import golden_io
+import ref_binding
+import util
+from enums import ACTIVATION, LAYER_DROPOUT, OPTIMIZER
+
+# L2-relative bound for every compared tensor.  The restatement differs from the
+# reference only in summation order (blocked dot vs sequential loop).
+TOL_L2 = 2e-6
+
+
+@pytest.mark.parametrize("name", sorted(golden_io.CASES))
+def test_oracle_matches_golden(name):
+    cfg, steps, X, Y, masks, p0, want = golden_io.load(name)
+    got = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, steps, X, Y, masks)
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_L2, f"{name}/{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("cfg", [
+    configs.mlp_softmax(),
+    configs.deep_brn_mlp(64, 128, 3, 32, 64),
+    configs.deep_brn_mlp(64, 128, 3, 32, 64, af=ACTIVATION.ELU, optimizer=OPTIMIZER.ADABOUND),
+    configs.deep_brn_mlp(64, 128, 3, 32, 64, af=ACTIVATION.ISRLU, optimizer=OPTIMIZER.NOSADAM,
+                         dropout=LAYER_DROPOUT.BERNOULLI_INVERTED),
+    configs.deep_brn_mlp(64, 128, 3, 32, 64, af=ACTIVATION.RELU, optimizer=OPTIMIZER.AMSGRAD, dropout=None),
+], ids=lambda c: f"{c['name']}-opt{c['optimizer']}-af{c['layers'][1].get('af')}")
+def test_oracle_matches_compiled_reference(cfg):
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    p0 = ref.get_array("parameters")
+    want = util.trace(ref, cfg, steps=20)
+    got = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, steps=20)
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_L2, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("rule", [OPTIMIZER.ADAM, OPTIMIZER.AMSGRAD, OPTIMIZER.ADABOUND, OPTIMIZER.AMSBOUND,
+                                  OPTIMIZER.NOSADAM])
+def test_flat_optimizer_sweep(rule):
+    """Optimizer-only workload: flat vector, p ~ N(0, 0.02), g ~ N(0, 1e-3),
+    zero moments, 10 steps, against the reference's own update loops."""
+    rng = np.random.default_rng(5)
+    n = 100_003
+    p = (0.02 * rng.standard_normal(n)).astype(np.float32)
+    g = (1e-3 * rng.standard_normal(n)).astype(np.float32)
+    hp = dict(adam_learning_rate=1e-3, adam_beta1=0.9, adam_beta2=0.999, adam_epsilon=1e-8, adam_gamma=0.1,
+              learning_rate_final=0.1, learning_gamma=1e-3)
+    pr, m, v, vh = p.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    secs = ref_binding.optimizer_sweep(rule, pr, g, m, v, vh, 10, [1e-3, 0.9, 0.999, 1e-8, 0.1, 0.1, 1e-3])
+    assert secs >= 0
+    po, mo, vo, vho = p.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    state = {}
+    for _ in range(10):
+        gg = g.copy()
+        fc_step.optimizer_update(rule, fc_step.optimizer_scalars(rule, hp, state), po, gg, mo, vo, vho)
+    assert util.rel_l2(po - p, pr - p) <= 1e-5
+    assert util.rel_l2(mo, m) <= 1e-6 and util.rel_l2(vo, v) <= 1e-6
+
+
+def test_softmax_cross_entropy_known_answer():
+    """Closed form for one row: delta = (q - onehot) / rows when the softmax
+    Jacobian is contracted with the cross-entropy derivative (the identity the
+    reference's own gradient test exercises on a 3-weight network,
+    test/deep-learning/array_grad_adept_test.cpp L:149-237)."""
+    z = np.array([[0.4 + 0.5 * 1.3, 0.4 + 0.5 * -5.3, 0.4 + 0.5 * 4.3]], np.float32)
+    q = fc_step.softmax(z)
+    y = np.array([[0.0, 0.0, 1.0]], np.float32)
+    total, delta = fc_step.loss_and_delta(fc_step.LOSS_CROSS_ENTROPY, fc_step.AF_SOFTMAX, z, q, y)
+    np.testing.assert_allclose(delta, (q - y), rtol=2e-6, atol=1e-7)
+    np.testing.assert_allclose(total, -np.log(q[0, 2]), rtol=1e-6)

@@ -1,0 +1,80 @@
+"""Shared helpers of the parity tests: error measures and a step tracer that
+drives any backend exposing the reference's Model method names."""
+from __future__ import annotations
+
+import numpy as np
+
+import configs
+
+
+def rel_l2(a, b):
+    """||a - b||_2 / ||b||_2 in float64."""
+    a = np.asarray(a, np.float64).ravel()
+    b = np.asarray(b, np.float64).ravel()
+    den = np.linalg.norm(b)
+    return float(np.linalg.norm(a - b) / (den if den > 0 else 1.0))
+
+
+def rel_max(a, b):
+    """max|a - b| / max|b| in float64."""
+    a = np.asarray(a, np.float64)
+    b = np.asarray(b, np.float64)
+    den = np.abs(b).max()
+    return float(np.abs(a - b).max() / (den if den > 0 else 1.0))
+
+
+def build(model, cfg, params=None, seed=None):
+    configs.build_model(model, cfg)
+    if params is not None:
+        model.set_array("parameters", params)
+    elif seed is not None:
+        model.seed_weights(seed)
+        model.initialize_weights_with_glorot_uniform()
+    return model
+
+
+def trace(model, cfg, steps=1, X=None, Y=None, masks=None):
+    """Runs `steps` training steps on fixed inputs; returns the tensors the
+    parity bar names: activations, errors and gradients of step 1, parameters
+    after step 1 and after the last step, and the loss of every step."""
+    B = cfg["batch"]
+    if X is None:
+        X, Y = configs.synthetic_batch(cfg)
+    if masks is None:
+        masks = configs.dropout_masks(cfg)
+    model.train_begin(B)
+    for li, mk in masks.items():
+        model.set_dropout_mask(li, mk)
+    nl = len(cfg["layers"])
+    out = {}
+    if hasattr(model, "reset_loss"):
+        model.reset_loss()
+    model.forward_pass(B, X)
+    for li in range(1, nl):
+        out[f"act{li}"] = model.get_layer_outputs(li, B).reshape(B, -1)
+    model.compute_error(B, Y)
+    model.backward_pass(B)
+    for li in range(1, nl):
+        out[f"delta{li}"] = model.get_layer_errors(li, B).reshape(B, -1)
+    model.update_derivatives(B)
+    model.merge_derivatives()
+    losses = [model.get_loss()]
+    out["grads"] = model.get_array("derivatives")
+    model.update_weights(B, B)
+    out["params1"] = model.get_array("parameters")
+    for _ in range(1, steps):
+        losses.append(model.train_step(B, X, Y))
+    out["params_last"] = model.get_array("parameters")
+    out["losses"] = np.asarray(losses, np.float64)
+    for li, l in enumerate(cfg["layers"]):
+        if l.get("norm"):
+            n = l["units"]
+            out[f"mean_average{li}"] = model.get_layer_norm(li, "mean_average", n)
+            out[f"variance_average{li}"] = model.get_layer_norm(li, "variance_average", n)
+    return out
+
+
+def compare(got, want, keys=None):
+    """{key: (rel_l2, rel_max)} over the common keys."""
+    keys = keys or [k for k in want if k in got]
+    return {k: (rel_l2(got[k], want[k]), rel_max(got[k], want[k])) for k in keys}
