@@ -669,3 +669,77 @@ dlb_status bias_gradient(dlb_ctx *ctx, const float *delta, int rows, int n, floa
   return DLB_OK;
 }
 }  // namespace dlb
+
+// ---------------------------------------------------------------------------
+// Batch-renormalization sums without any allocation.
+//
+// The partial sums live in an array that is part of the library's device image
+// (every GPU that loads the library holds it until the process exits), so the
+// entry point below never calls cudaMalloc / cudaFree, directly or through the
+// context's scratch arena.  In host code the array's name is only a stand-in
+// for the symbol, not a device address: the address is looked up once per
+// device with cudaGetSymbolAddress and that pointer is what the kernels get.
+// ---------------------------------------------------------------------------
+namespace dlb {
+
+static __device__ __align__(256) double g_noalloc_partials[DLB_NOALLOC_SCRATCH_DOUBLES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+struct NoallocDevice {
+  double *partials = nullptr;  // device address of g_noalloc_partials on this device
+  int sm_count = 0;
+};
+static NoallocDevice g_noalloc_devices[NOALLOC_MAX_DEVICES];
+
+// Set-up for the current device: address of the array and SM count.  Neither
+// call allocates.  Done on the first call per device.
+static dlb_status noalloc_device(NoallocDevice **out) {
+  int dev = -1;
+  DLB_CUDA(cudaGetDevice(&dev));
+  DLB_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, "dlb_brn_forward_sums_noalloc: device index");
+  NoallocDevice &d = g_noalloc_devices[dev];
+  if (!d.partials) {
+    double *ptr = nullptr;
+    DLB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_noalloc_partials));
+    int sms = 0;
+    DLB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    DLB_REQUIRE(ptr && sms > 0, "dlb_brn_forward_sums_noalloc: device set-up");
+    d.sm_count = sms;
+    d.partials = ptr;
+  }
+  *out = &d;
+  return DLB_OK;
+}
+
+}  // namespace dlb
+
+extern "C" dlb_status dlb_brn_forward_sums_noalloc(const float *Z, int rows, int n_units,
+                                                   double *sums, void *stream) {
+  DLB_REQUIRE(Z && sums && rows > 0 && n_units > 0, "dlb_brn_forward_sums_noalloc");
+  DLB_REQUIRE((n_units & 3) || (reinterpret_cast<uintptr_t>(Z) & 15) == 0,
+              "dlb_brn_forward_sums_noalloc: Z must be 16-byte aligned");
+  NoallocDevice *dev = nullptr;
+  DLB_TRY(noalloc_device(&dev));
+  // Same chunking rule as the allocating entry point, so both give the same
+  // sums bit for bit.
+  const int col_blocks = ceil_div(n_units, CR_COLS);
+  int chunks = ceil_div(dev->sm_count * 4, col_blocks);
+  chunks = max(1, min(chunks, ceil_div(rows, 64)));
+  const int rows_per_chunk = ceil_div(ceil_div(rows, chunks), CR_LANES_Y) * CR_LANES_Y;
+  chunks = ceil_div(rows, rows_per_chunk);
+  const size_t need = (size_t)chunks * 2 * (size_t)n_units;
+  if (need > (size_t)DLB_NOALLOC_SCRATCH_DOUBLES) {
+    set_error("dlb_brn_forward_sums_noalloc: %d rows x %d units need %zu partial sums, the built-in "
+              "scratch holds %u; use dlb_brn_forward_sums or fewer units per call",
+              rows, n_units, need, (unsigned)DLB_NOALLOC_SCRATCH_DOUBLES);
+    return DLB_ERR_INVALID;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  column_reduce_kernel<2, SumSqOp><<<dim3(col_blocks, chunks), CR_LANES_X * CR_LANES_Y, 0, s>>>(
+      SumSqOp{Z, n_units}, rows, n_units, rows_per_chunk, dev->partials);
+  DLB_CUDA(cudaGetLastError());
+  const int total = 2 * n_units;
+  reduce_partials_kernel<<<ceil_div(total, 256), 256, 0, s>>>(dev->partials, chunks, total, sums);
+  DLB_CUDA(cudaGetLastError());
+  return DLB_OK;
+}

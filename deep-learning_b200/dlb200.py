@@ -62,7 +62,8 @@ SIGNATURES = {
     "dlb_fc_backward_input": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "dlb_fc_weight_gradient": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
     "dlb_brn_forward_sums": (_i, [_vp, _vp, _i, _i, _vp]),
-    "dlb_brn_forward_finalize": (_i, [_vp, _vp, _i, _i, _f, _f, _f, _f, C.POINTER(BrnUnitArrays)]),
+    "dlb_brn_forward_sums_noalloc": (_i, [_vp, _i, _i, _vp, _vp]),
+    "dlb_brn_forward_finalize":(_i, [_vp, _vp, _i, _i, _f, _f, _f, _f, C.POINTER(BrnUnitArrays)]),
     "dlb_activation_forward": (_i, [_vp, _vp, C.POINTER(BrnUnitArrays), _i, C.POINTER(DropoutDesc), _vp, _vp, _i, _i]),
     "dlb_softmax_forward": (_i, [_vp, _vp, _vp, _i, _i]),
     "dlb_activation_backward": (_i, [_vp, _vp, _vp, _vp, C.POINTER(BrnUnitArrays), _i, _i, _i, _vp]),

@@ -154,6 +154,34 @@ typedef struct dlb_brn_unit_arrays {
 dlb_status dlb_brn_forward_sums(dlb_ctx *ctx, const float *Z, int rows, int n_units,
                                 double *sums);
 
+/* Same sums as dlb_brn_forward_sums for callers that must not allocate device
+ * memory: code running between cudaStreamBeginCapture and EndCapture, inside a
+ * host callback or a latency-critical loop where cudaMalloc would serialise
+ * the device, or under a framework allocator that owns every byte of the GPU
+ * and treats foreign allocations as a bug.  dlb_brn_forward_sums may grow the
+ * context's scratch arena with cudaMalloc; this variant keeps its per-chunk
+ * partial sums in an array that is part of the library image on every GPU that
+ * loads it (DLB_NOALLOC_SCRATCH_DOUBLES doubles = 8 MiB, held until the process
+ * exits) and calls no cudaMalloc, cudaFree or allocating routine.  It needs no
+ * context: pass the stream to enqueue on (NULL = the default stream) with the
+ * target device current.  Has no counterpart in the reference.
+ *
+ * Limits and rules:
+ *  - the partial sums of one call must fit: row_chunks * 2 * n_units <=
+ *    DLB_NOALLOC_SCRATCH_DOUBLES, where row_chunks <= ceil(4 * SM count /
+ *    ceil(n_units / 128)) and <= ceil(rows / 64).  Larger requests return
+ *    DLB_ERR_INVALID with a message naming both numbers; nothing is launched.
+ *  - the first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress) and the SM count; make that first call outside any
+ *    stream capture.
+ *  - every call on a device shares the one array.  Nothing in it needs to
+ *    start at zero (each call overwrites every slot it later reads), but two
+ *    calls that overlap on the GPU (different streams) race on it: order them.
+ *  - Z must be 16-byte aligned when n_units is a multiple of 4. */
+#define DLB_NOALLOC_SCRATCH_DOUBLES (1u << 20)
+dlb_status dlb_brn_forward_sums_noalloc(const float *Z, int rows, int n_units, double *sums,
+                                        void *stream);
+
 /* From (all-reduced) sums over global_rows rows: mean, sigma, running averages
  * (updated first), then r and d from the updated averages.
  * ref: the "Average" loop, fwp_mp.cpp L:4666-4718. */
