@@ -21,6 +21,9 @@ struct dlb_ctx {
   ncclComm_t comm = nullptr;
   int rank = 0;
   int world = 1;
+  cudaStream_t comm_stream = nullptr;   // overlapped gradient all-reduces
+  cudaEvent_t ev_main = nullptr, ev_comm = nullptr;
+  bool comm_pending = false;
   bool use_tensor_core = true;
   bool tensor_core_ok = false;  // device is sm_100
   uint64_t launches = 0;

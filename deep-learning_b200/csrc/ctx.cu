@@ -191,7 +191,11 @@ dlb_status dlb_ctx_destroy(dlb_ctx *ctx) {
   if (!ctx) return DLB_OK;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  if (ctx->comm_stream) cudaStreamSynchronize(ctx->comm_stream);
   if (ctx->comm && nccl() && nccl()->CommDestroy) nccl()->CommDestroy(ctx->comm);
+  if (ctx->comm_stream) cudaStreamDestroy(ctx->comm_stream);
+  if (ctx->ev_main) cudaEventDestroy(ctx->ev_main);
+  if (ctx->ev_comm) cudaEventDestroy(ctx->ev_comm);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->timer_start) cudaEventDestroy(ctx->timer_start);
@@ -399,6 +403,30 @@ dlb_status dlb_allreduce_f32(dlb_ctx *ctx, float *buf, size_t n) {
   DLB_REQUIRE(ctx && (buf || n == 0), "dlb_allreduce_f32");
   if (!ctx->comm || ctx->world == 1 || n == 0) return DLB_OK;
   DLB_NCCL(nccl()->AllReduce(buf, buf, n, ncclFloat32, ncclSum, ctx->comm, ctx->stream));
+  return DLB_OK;
+}
+
+dlb_status dlb_allreduce_f32_overlapped(dlb_ctx *ctx, float *buf, size_t n) {
+  DLB_REQUIRE(ctx && (buf || n == 0), "dlb_allreduce_f32_overlapped");
+  if (!ctx->comm || ctx->world == 1 || n == 0) return DLB_OK;
+  if (!ctx->comm_stream) {
+    DLB_CUDA(cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking));
+    DLB_CUDA(cudaEventCreateWithFlags(&ctx->ev_main, cudaEventDisableTiming));
+    DLB_CUDA(cudaEventCreateWithFlags(&ctx->ev_comm, cudaEventDisableTiming));
+  }
+  DLB_CUDA(cudaEventRecord(ctx->ev_main, ctx->stream));
+  DLB_CUDA(cudaStreamWaitEvent(ctx->comm_stream, ctx->ev_main, 0));
+  DLB_NCCL(nccl()->AllReduce(buf, buf, n, ncclFloat32, ncclSum, ctx->comm, ctx->comm_stream));
+  ctx->comm_pending = true;
+  return DLB_OK;
+}
+
+dlb_status dlb_comm_join(dlb_ctx *ctx) {
+  DLB_REQUIRE(ctx, "dlb_comm_join");
+  if (!ctx->comm_pending) return DLB_OK;
+  DLB_CUDA(cudaEventRecord(ctx->ev_comm, ctx->comm_stream));
+  DLB_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_comm, 0));
+  ctx->comm_pending = false;
   return DLB_OK;
 }
 

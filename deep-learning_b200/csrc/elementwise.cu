@@ -182,31 +182,45 @@ struct ActBackwardOp {
   const float *Z, *A;
   BrnPtrs u;
   int af, n;
-  struct Cols4 { BrnCol c[4]; };
-  struct Cols1 { BrnCol c; };
+  // Per-unit constants plus the two quotients of bwp_mp.cpp L:1571-1574,
+  // -r / sigma and -r / (sigma * sigma), formed once per unit as the reference
+  // forms them once per element with the same operands.
+  struct Col {
+    BrnCol c;
+    float q_mean, q_sigma;
+  };
+  struct Cols4 { Col k[4]; };
+  struct Cols1 { Col k; };
+  __device__ Col make(int col) const {
+    Col k;
+    k.c = u.at(col);
+    const float neg_r = -k.c.r;
+    k.q_mean = neg_r / k.c.sigma;
+    k.q_sigma = neg_r / (k.c.sigma * k.c.sigma);
+    return k;
+  }
   __device__ void load_cols4(int col, Cols4 &k) const {
     if (NORM)
-      for (int j = 0; j < 4; ++j) k.c[j] = u.at(col + j);
+      for (int j = 0; j < 4; ++j) k.k[j] = make(col + j);
   }
   __device__ void load_cols1(int col, Cols1 &k) const {
-    if (NORM) k.c = u.at(col);
+    if (NORM) k.k = make(col);
   }
-  __device__ __forceinline__ float one(float da, float z, float a, const BrnCol &c,
-                                       float *s0, float *s1, float *s2, float *s3) const {
+  __device__ __forceinline__ float one(float da, float z, float a, const Col &k, float *s0,
+                                       float *s1, float *s2, float *s3) const {
     float y = z, xh = 0.f;
     if (NORM) {
-      xh = brn_hat(z, c);
-      y = brn_norm(xh, c);
+      xh = brn_hat(z, k.c);
+      y = brn_norm(xh, k.c);
     }
     const float e = da * af_derive(af, y, a);
     if (NORM) {
       // bwp_mp.cpp L:1559-1574
       *s0 += e * xh;
       *s1 += e;
-      const float eh = e * c.gamma;
-      const float neg_r = -c.r;
-      *s2 += eh * (neg_r / c.sigma);
-      *s3 += eh * (z - c.mean) * (neg_r / (c.sigma * c.sigma));
+      const float eh = e * k.c.gamma;
+      *s2 += eh * k.q_mean;
+      *s3 += eh * (z - k.c.mean) * k.q_sigma;
     }
     return e;
   }
@@ -215,15 +229,15 @@ struct ActBackwardOp {
     float4 da = *reinterpret_cast<const float4 *>(dA + o);
     const float4 z = __ldg(reinterpret_cast<const float4 *>(Z + o));
     const float4 a = __ldg(reinterpret_cast<const float4 *>(A + o));
-    da.x = one(da.x, z.x, a.x, k.c[0], &acc[0][0], &acc[1][0], &acc[2][0], &acc[3][0]);
-    da.y = one(da.y, z.y, a.y, k.c[1], &acc[0][1], &acc[1][1], &acc[2][1], &acc[3][1]);
-    da.z = one(da.z, z.z, a.z, k.c[2], &acc[0][2], &acc[1][2], &acc[2][2], &acc[3][2]);
-    da.w = one(da.w, z.w, a.w, k.c[3], &acc[0][3], &acc[1][3], &acc[2][3], &acc[3][3]);
+    da.x = one(da.x, z.x, a.x, k.k[0], &acc[0][0], &acc[1][0], &acc[2][0], &acc[3][0]);
+    da.y = one(da.y, z.y, a.y, k.k[1], &acc[0][1], &acc[1][1], &acc[2][1], &acc[3][1]);
+    da.z = one(da.z, z.z, a.z, k.k[2], &acc[0][2], &acc[1][2], &acc[2][2], &acc[3][2]);
+    da.w = one(da.w, z.w, a.w, k.k[3], &acc[0][3], &acc[1][3], &acc[2][3], &acc[3][3]);
     *reinterpret_cast<float4 *>(dA + o) = da;
   }
   __device__ void row1(int r, int col, const Cols1 &k, float (&acc)[4]) const {
     const size_t o = (size_t)r * n + col;
-    dA[o] = one(dA[o], Z[o], A[o], k.c, &acc[0], &acc[1], &acc[2], &acc[3]);
+    dA[o] = one(dA[o], Z[o], A[o], k.k, &acc[0], &acc[1], &acc[2], &acc[3]);
   }
 };
 
@@ -235,6 +249,16 @@ static inline int stream_grid(dlb_ctx *ctx, size_t work_items, int block) {
   size_t blocks = (work_items + block - 1) / block;
   size_t cap = (size_t)ctx->sm_count * 16;
   return (int)max((size_t)1, min(blocks, cap));
+}
+
+// Row chunking of the row-loop kernels: about 8 blocks of 256 threads per SM,
+// chunks a multiple of the 8 row lanes.
+static void rows_plan(dlb_ctx *ctx, int rows, int n, int *chunks, int *rows_per_chunk) {
+  const int col_blocks = ceil_div(n, CR_COLS);
+  int c = ceil_div(ctx->sm_count * 8, col_blocks);
+  c = max(1, min(c, ceil_div(rows, CR_LANES_Y)));
+  *rows_per_chunk = ceil_div(ceil_div(rows, c), CR_LANES_Y) * CR_LANES_Y;
+  *chunks = ceil_div(rows, *rows_per_chunk);
 }
 
 __global__ void split_tf32_kernel(const float *__restrict__ x, float *__restrict__ lo, size_t n) {
@@ -386,6 +410,83 @@ __global__ void activation_backward_plain_kernel(float *__restrict__ dA, const f
   } else {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
       dA[i] *= af_derive(af, Z[i], A[i]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Row-loop forms of the two normalised [rows, units] kernels (units % 4 == 0).
+// Grid (column blocks, row chunks) like the column reductions: a thread keeps
+// one float4 column group, loads its per-unit constants once and walks rows
+// with stride 8, so the inner loop is one 16-byte load per input tensor and
+// one 16-byte store per output tensor, each warp touching 512 contiguous bytes.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
+    activation_forward_rows_kernel(const float *__restrict__ Z, BrnPtrs u, int af, DropoutDev dp,
+                                   float *__restrict__ A, float *__restrict__ A_lo, int rows, int n,
+                                   int rows_per_chunk) {
+  const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
+  const int col = blockIdx.x * CR_COLS + tx * 4;
+  if (col >= n) return;
+  const int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+  BrnCol c[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) c[j] = u.at(col + j);
+  for (int r = r0 + ty; r < r1; r += CR_LANES_Y) {
+    const size_t o = (size_t)r * n + col;
+    const float4 z = __ldg(reinterpret_cast<const float4 *>(Z + o));
+    const float zz[4] = {z.x, z.y, z.z, z.w};
+    float out[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float y = brn_norm(brn_hat(zz[j], c[j]), c[j]);
+      out[j] = apply_dropout(af_fire(af, y), dp, col + j, o + j);
+      lo[j] = tf32_lo(out[j]);
+    }
+    *reinterpret_cast<float4 *>(A + o) = make_float4(out[0], out[1], out[2], out[3]);
+    if (A_lo) *reinterpret_cast<float4 *>(A_lo + o) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+  }
+}
+
+__global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
+    brn_backward_apply_rows_kernel(float *__restrict__ delta, float *__restrict__ delta_lo,
+                                   const float *__restrict__ Z, BrnPtrs u,
+                                   const double *__restrict__ sums, float inv_rows, float rows_f,
+                                   int rows, int n, int rows_per_chunk) {
+  const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
+  const int col = blockIdx.x * CR_COLS + tx * 4;
+  if (col >= n) return;
+  const int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+  // Per-unit factors in the reference's grouping (bwp_mp.cpp L:1608-1621):
+  // r / sigma, N * sigma, d_sigma, d_mean / N.
+  float gamma[4], mean[4], r_over_sigma[4], n_sigma[4], d_sigma[4], d_mean_n[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const BrnCol c = u.at(col + j);
+    gamma[j] = c.gamma;
+    mean[j] = c.mean;
+    r_over_sigma[j] = c.r / c.sigma;
+    n_sigma[j] = rows_f * c.sigma;
+    d_sigma[j] = (float)sums[3 * (size_t)n + col + j];
+    d_mean_n[j] = (float)sums[2 * (size_t)n + col + j] * inv_rows;
+  }
+  for (int r = r0 + ty; r < r1; r += CR_LANES_Y) {
+    const size_t o = (size_t)r * n + col;
+    const float4 e4 = *reinterpret_cast<const float4 *>(delta + o);
+    const float4 z4 = __ldg(reinterpret_cast<const float4 *>(Z + o));
+    const float e[4] = {e4.x, e4.y, e4.z, e4.w}, z[4] = {z4.x, z4.y, z4.z, z4.w};
+    float t[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float v = e[j] * gamma[j];
+      v *= r_over_sigma[j];
+      v += d_sigma[j] * ((z[j] - mean[j]) / n_sigma[j]);
+      v += d_mean_n[j];
+      t[j] = v;
+    }
+    *reinterpret_cast<float4 *>(delta + o) = make_float4(t[0], t[1], t[2], t[3]);
+    if (delta_lo)
+      *reinterpret_cast<float4 *>(delta_lo + o) =
+          make_float4(tf32_lo(t[0]), tf32_lo(t[1]), tf32_lo(t[2]), tf32_lo(t[3]));
   }
 }
 
@@ -554,9 +655,18 @@ dlb_status dlb_activation_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_un
   const bool vec4 = (n_units % 4 == 0) && ((reinterpret_cast<uintptr_t>(Z) & 15) == 0) &&
                     ((reinterpret_cast<uintptr_t>(A) & 15) == 0) &&
                     (!A_lo || (reinterpret_cast<uintptr_t>(A_lo) & 15) == 0);
+  if (u && vec4) {
+    int chunks, rpc;
+    rows_plan(ctx, rows, n_units, &chunks, &rpc);
+    activation_forward_rows_kernel<<<dim3(ceil_div(n_units, CR_COLS), chunks),
+                                     CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
+        Z, p, af, dp, A, A_lo, rows, n_units, rpc);
+    DLB_LAUNCHED(ctx);
+    return DLB_OK;
+  }
   const size_t items = vec4 ? (size_t)rows * (n_units / 4) : (size_t)rows * n_units;
   const int grid = stream_grid(ctx, items, 256);
-#define LAUNCH(NORM, V)                                                                  \
+#define LAUNCH(NORM, V)                                                                 \
   activation_forward_kernel<NORM, V><<<grid, 256, 0, ctx->stream>>>(Z, p, af, dp, A, A_lo, rows, \
                                                                     n_units)
   if (u) { if (vec4) LAUNCH(true, true); else LAUNCH(true, false); }
@@ -609,10 +719,13 @@ dlb_status dlb_brn_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, c
   const size_t items = vec4 ? (size_t)rows * (n_units / 4) : (size_t)rows * n_units;
   const int grid = stream_grid(ctx, items, 256);
   const float nf = (float)global_rows;
-  if (vec4)
-    brn_backward_apply_kernel<true><<<grid, 256, 0, ctx->stream>>>(
-        delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units);
-  else
+  if (vec4) {
+    int chunks, rpc;
+    rows_plan(ctx, rows, n_units, &chunks, &rpc);
+    brn_backward_apply_rows_kernel<<<dim3(ceil_div(n_units, CR_COLS), chunks),
+                                     CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
+        delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc);
+  } else
     brn_backward_apply_kernel<false><<<grid, 256, 0, ctx->stream>>>(
         delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units);
   DLB_LAUNCHED(ctx);

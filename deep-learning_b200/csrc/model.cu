@@ -76,6 +76,9 @@ struct dlb_model {
   double *loss_sum = nullptr;
   size_t loss_rows = 0;  // rows accumulated since reset_loss
   bool params_lo_valid = false;
+  // Inside train_step the step is known to be a single chunk, so each layer's
+  // weight gradient is all-reduced as soon as its GEMM has been enqueued.
+  bool overlap_grad_allreduce = false;
 };
 
 namespace {
@@ -773,6 +776,8 @@ dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows) {
     float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
     DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn,
                                    dbias, (int)rows, (int)l.fan_in, (int)l.units, 1));
+    if (m->overlap_grad_allreduce)
+      DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
     X = l.A;
     X_lo = l.A_lo;
   }
@@ -781,6 +786,12 @@ dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows) {
 
 dlb_status dlb_model_merge_derivatives(dlb_model *m) {
   DLB_REQUIRE(m && m->grads, "merge_derivatives");
+  if (m->overlap_grad_allreduce) {
+    // The weight blocks are already in flight; bias, gamma and beta follow.
+    DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + m->total_weights,
+                                         m->total_parameters - m->total_weights));
+    return dlb_comm_join(m->ctx);
+  }
   return dlb_allreduce_f32(m->ctx, m->grads, m->total_parameters);
 }
 
@@ -831,14 +842,21 @@ dlb_status dlb_model_get_loss(dlb_model *m, double *loss) {
   return DLB_OK;
 }
 
+static dlb_status update_and_merge_overlapped(dlb_model *m, size_t rows) {
+  m->overlap_grad_allreduce = dlb_comm_world(m->ctx) > 1;
+  dlb_status st = dlb_model_update_derivatives(m, rows);
+  if (st == DLB_OK) st = dlb_model_merge_derivatives(m);
+  m->overlap_grad_allreduce = false;
+  return st;
+}
+
 dlb_status dlb_model_train_step_device(dlb_model *m, size_t rows, const float *X_dev,
                                        const float *Y_dev) {
   DLB_TRY(dlb_model_reset_loss(m));
   DLB_TRY(dlb_model_forward_pass_device(m, rows, X_dev));
   DLB_TRY(dlb_model_compute_error_device(m, rows, Y_dev));
   DLB_TRY(dlb_model_backward_pass(m, rows));
-  DLB_TRY(dlb_model_update_derivatives(m, rows));
-  DLB_TRY(dlb_model_merge_derivatives(m));
+  DLB_TRY(update_and_merge_overlapped(m, rows));
   const size_t g = m->global_rows ? m->global_rows : rows;
   return dlb_model_update_weights(m, g, g);
 }
@@ -854,8 +872,7 @@ dlb_status dlb_model_train_step(dlb_model *m, size_t rows, const float *X_host,
   DLB_TRY(dlb_model_forward_pass_device(m, rows, m->input));
   DLB_TRY(dlb_model_compute_error_device(m, rows, m->target));
   DLB_TRY(dlb_model_backward_pass(m, rows));
-  DLB_TRY(dlb_model_update_derivatives(m, rows));
-  DLB_TRY(dlb_model_merge_derivatives(m));
+  DLB_TRY(update_and_merge_overlapped(m, rows));
   if (loss) DLB_TRY(dlb_model_get_loss(m, loss));
   const size_t g = m->global_rows ? m->global_rows : rows;
   return dlb_model_update_weights(m, g, g);

@@ -78,6 +78,8 @@ SIGNATURES = {
     "dlb_comm_rank": (_i, [_vp]),
     "dlb_allreduce_f32": (_i, [_vp, _vp, _sz]),
     "dlb_allreduce_f64": (_i, [_vp, _vp, _sz]),
+    "dlb_allreduce_f32_overlapped": (_i, [_vp, _vp, _sz]),
+    "dlb_comm_join": (_i, [_vp]),
     "dlb_model_create": (_i, [C.POINTER(_vp), _vp]),
     "dlb_model_destroy": (_i, [_vp]),
     "dlb_model_compile": (_i, [_vp, _sz, _sz, _i, _vp, _vp]),

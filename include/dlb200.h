@@ -285,6 +285,13 @@ int dlb_comm_world(dlb_ctx *ctx);
 int dlb_comm_rank(dlb_ctx *ctx);
 dlb_status dlb_allreduce_f32(dlb_ctx *ctx, float *buf, size_t n);
 dlb_status dlb_allreduce_f64(dlb_ctx *ctx, double *buf, size_t n);
+/* Same sum, enqueued on the context's second (communication) stream behind
+ * everything already on the main stream, so that it overlaps with the kernels
+ * the caller enqueues next (the gradient of one layer crosses NVLink while the
+ * weight-gradient GEMM of the next layer runs).  dlb_comm_join makes the main
+ * stream wait for all such transfers. */
+dlb_status dlb_allreduce_f32_overlapped(dlb_ctx *ctx, float *buf, size_t n);
+dlb_status dlb_comm_join(dlb_ctx *ctx);
 
 /* ------------------------------------------------------------------------ */
 /* Model: the reference's v1::Model construction and step entry points

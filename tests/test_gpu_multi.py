@@ -27,7 +27,7 @@ def _gpu_count():
 def _cfg():
     import configs
 
-    return configs.deep_brn_mlp(256, 512, 2, 128, 512)
+    return configs.deep_brn_mlp(256, 512, 2, 128, 256)
 
 
 def worker(rank, world, tmp):
@@ -74,7 +74,7 @@ def test_two_gpu_shards_equal_single_gpu_full_batch(gpu_ctx):
     cfg = _cfg()
     X, Y = configs.synthetic_batch(cfg)
     masks = configs.dropout_masks(cfg)
-    p0, _ = util.kink_free_parameters(cfg, fc_step.OracleModel, X, masks, scale=1.0 / 22)
+    p0, _ = util.kink_free_parameters(cfg, fc_step.OracleModel, X, masks, scale=1.0 / np.sqrt(512))
     want = util.trace(util.build(dlb200.Model(gpu_ctx), cfg, params=p0), cfg, 4, X, Y, masks)
     with tempfile.TemporaryDirectory() as tmp:
         np.save(os.path.join(tmp, "p0.npy"), p0)
