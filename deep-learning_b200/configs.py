@@ -56,6 +56,38 @@ def deep_brn_mlp(n_in=1024, hidden=4096, depth=4, n_out=1024, batch=4096,
     )
 
 
+def residual_mlp(width=8192, blocks=16, n_out=1000, batch=8192, p_last=0.5, optimizer=OPTIMIZER.ADAM):
+    """Residual MLP: `blocks` blocks of width `width`, each FC - batch renorm -
+    ELU - FC with a ShakeDrop skip, softmax cross-entropy over n_out classes,
+    Adam.  In the reference's layer list a block is a RESIDUAL layer of depth 2
+    followed by its two FC layers, the second carrying the normalization and
+    the activation (pre-activation order).  The paper's keep probability decays
+    linearly to p_last; the reference's ShakeDrop value is the probability that
+    a row IS perturbed, hence (l / blocks) * (1 - p_last) for block l."""
+    layers = [dict(type=LAYER.FULLY_CONNECTED, units=width)]
+    for b in range(1, blocks + 1):
+        layers.append(dict(type=LAYER.RESIDUAL, units=2,
+                           dropout=(LAYER_DROPOUT.SHAKEDROP, (b / blocks) * (1.0 - p_last))))
+        layers.append(dict(type=LAYER.FULLY_CONNECTED, units=width, af=ACTIVATION.ELU))
+        layers.append(dict(type=LAYER.FULLY_CONNECTED, units=width, af=ACTIVATION.ELU,
+                           norm=LAYER_NORM.BATCH_RENORMALIZATION))
+    layers.append(dict(type=LAYER.FULLY_CONNECTED, units=n_out, af=ACTIVATION.SOFTMAX))
+    return dict(
+        name=f"residual_mlp_{blocks}x{width}-{n_out}_b{batch}",
+        model_type=MODEL.FEEDFORWARD, seq_w=1, time_delays=0, layers=layers,
+        loss=LOSS_FN.CROSS_ENTROPY, optimizer=optimizer,
+        hparams=dict(adam_learning_rate=1e-3, adam_beta1=0.9, adam_beta2=0.999, adam_epsilon=1e-8),
+        brn=dict(r_max=3.0, d_max=5.0, momentum=0.99, eps=1e-5),
+        batch=batch, weight_seed=0, data_seed=0, shakedrop_seed=2, inputs="normal", targets="onehot", mp=False,
+    )
+
+
+def shakedrop_layers(cfg):
+    """[(layer index, probability)] of the residual layers that use ShakeDrop."""
+    return [(i, l["dropout"][1]) for i, l in enumerate(cfg["layers"])
+            if l["type"] == LAYER.RESIDUAL and l.get("dropout") and l["dropout"][0] == LAYER_DROPOUT.SHAKEDROP]
+
+
 def n_inputs(cfg):
     return cfg["layers"][0]["units"]
 

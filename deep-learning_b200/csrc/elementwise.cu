@@ -784,6 +784,97 @@ dlb_status bias_gradient(dlb_ctx *ctx, const float *delta, int rows, int n, floa
 }  // namespace dlb
 
 // ---------------------------------------------------------------------------
+// Residual block: ShakeDrop and the shortcut sum.
+// ---------------------------------------------------------------------------
+namespace dlb {
+
+// block[b,:] *= noise[b,:] on flagged rows (in place, as the reference perturbs
+// the block's output buffer), out = x + block, plus the residual plane of out.
+__global__ void residual_forward_kernel(const float *__restrict__ x, float *__restrict__ block,
+                                        const uint8_t *__restrict__ row_mask,
+                                        const float *__restrict__ noise, float *__restrict__ out,
+                                        float *__restrict__ out_lo, int rows, int width, int vec) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if (vec) {
+    const int w4 = width / 4;
+    const size_t total = (size_t)rows * w4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      const int r = (int)(i / w4);
+      float4 o = reinterpret_cast<float4 *>(block)[i];
+      if (row_mask && row_mask[r]) {
+        const float4 k = __ldg(reinterpret_cast<const float4 *>(noise) + i);
+        o.x *= k.x; o.y *= k.y; o.z *= k.z; o.w *= k.w;
+        reinterpret_cast<float4 *>(block)[i] = o;
+      }
+      const float4 s = __ldg(reinterpret_cast<const float4 *>(x) + i);
+      const float4 v = make_float4(s.x + o.x, s.y + o.y, s.z + o.z, s.w + o.w);
+      reinterpret_cast<float4 *>(out)[i] = v;
+      if (out_lo)
+        reinterpret_cast<float4 *>(out_lo)[i] =
+            make_float4(tf32_lo(v.x), tf32_lo(v.y), tf32_lo(v.z), tf32_lo(v.w));
+    }
+  } else {
+    const size_t total = (size_t)rows * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      const int r = (int)(i / width);
+      float o = block[i];
+      if (row_mask && row_mask[r]) {
+        o *= noise[i];
+        block[i] = o;
+      }
+      const float v = x[i] + o;
+      out[i] = v;
+      if (out_lo) out_lo[i] = tf32_lo(v);
+    }
+  }
+}
+
+// delta = d * noise on flagged rows, d elsewhere, plus its residual plane.
+__global__ void shakedrop_backward_kernel(const float *__restrict__ d,
+                                          const uint8_t *__restrict__ row_mask,
+                                          const float *__restrict__ noise, float *__restrict__ delta,
+                                          float *__restrict__ delta_lo, int rows, int width) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t total = (size_t)rows * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int r = (int)(i / width);
+    float v = d[i];
+    if (row_mask && row_mask[r]) v *= noise[i];
+    delta[i] = v;
+    if (delta_lo) delta_lo[i] = tf32_lo(v);
+  }
+}
+
+}  // namespace dlb
+
+extern "C" dlb_status dlb_residual_forward(dlb_ctx *ctx, const float *x, float *block,
+                                           const uint8_t *row_mask, const float *noise, float *out,
+                                           float *out_lo, int rows, int width) {
+  DLB_REQUIRE(ctx && x && block && out && rows > 0 && width > 0, "dlb_residual_forward");
+  DLB_REQUIRE(!row_mask || noise, "dlb_residual_forward: row flags need the noise draws");
+  const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(block) |
+                       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(out_lo) |
+                       reinterpret_cast<uintptr_t>(noise);
+  const int vec = (width % 4 == 0) && (al & 15) == 0;
+  const size_t items = vec ? (size_t)rows * (width / 4) : (size_t)rows * width;
+  residual_forward_kernel<<<stream_grid(ctx, items, 256), 256, 0, ctx->stream>>>(
+      x, block, row_mask, noise, out, out_lo, rows, width, vec);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+extern "C" dlb_status dlb_shakedrop_backward(dlb_ctx *ctx, const float *d, const uint8_t *row_mask,
+                                             const float *noise, float *delta, float *delta_lo,
+                                             int rows, int width) {
+  DLB_REQUIRE(ctx && d && delta && rows > 0 && width > 0, "dlb_shakedrop_backward");
+  DLB_REQUIRE(!row_mask || noise, "dlb_shakedrop_backward: row flags need the noise draws");
+  shakedrop_backward_kernel<<<stream_grid(ctx, (size_t)rows * width, 256), 256, 0, ctx->stream>>>(
+      d, row_mask, noise, delta, delta_lo, rows, width);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+// ---------------------------------------------------------------------------
 // Batch-renormalization sums without any allocation.
 //
 // The partial sums live in an array that is part of the library's device image

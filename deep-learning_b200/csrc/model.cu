@@ -35,11 +35,26 @@ struct LayerRT {
   // Indices into the flat parameter vector.
   size_t first_conn = 0, last_conn = 0, first_bias = 0, last_bias = 0, first_norm_unit = 0;
   size_t fan_in = 0;
-  // Device buffers (allocated by ensure_batch).
+  // Residual blocks (the reference's layer list: a RESIDUAL layer of depth d
+  // followed by its d block layers, v1/learner/compile.cpp).
+  int group = 0;            // 1 = layer inside a residual block
+  size_t depth = 0;         // RESIDUAL: number of block layers
+  bool block_input = false; // first layer of a block: no activation in front
+  size_t norm_units = 0;    // normalised units: width, or fan-in for a block layer
+  // Device buffers (allocated by ensure_batch).  Stand-alone FC layer: Z sums,
+  // A output after activation and dropout, delta error w.r.t. Z.  Block layer:
+  // IN its GEMM input (activation of the previous block layer's sums), A its
+  // sums, delta error w.r.t. the sums.  RESIDUAL layer: A = shortcut + block,
+  // delta = error of that output.
   float *Z = nullptr, *A = nullptr, *A_lo = nullptr, *delta = nullptr, *delta_lo = nullptr;
-  float *stats = nullptr;  // mean | sigma | mean_avg | sigma_avg | r | d, each [T*units]
+  float *IN = nullptr, *IN_lo = nullptr;
+  float *stats = nullptr;  // mean | sigma | mean_avg | sigma_avg | r | d, each [T*norm_units]
   uint8_t *mask = nullptr; // [T*units]
   double *fwd_sums = nullptr, *bwd_sums = nullptr;
+  // ShakeDrop of a RESIDUAL layer: row flags and the forward / backward draws.
+  uint8_t *sd_mask = nullptr;
+  float *sd_fwd = nullptr, *sd_bwd = nullptr;
+  size_t sd_rows = 0;
 };
 
 struct HParams {
@@ -100,10 +115,42 @@ dlb_status dev_alloc(dlb_model *m, float **p, size_t elems, bool zero) {
 // unit }; gamma/beta exist for every unit of every layer as soon as one layer
 // is normalised (compile.cpp L:610-695, allocate.cpp L:1150-1176).
 dlb_status layout_parameters(dlb_model *m) {
+  // Graph: fan-in of every FC layer, width of every RESIDUAL layer (that of the
+  // layer below it), and the number of normalised units (a block layer
+  // normalises its input, so it has fan-in many).
+  size_t width = m->layers[0].units;
+  m->layers[0].norm_units = width;
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    LayerRT &l = m->layers[i];
+    if (l.type == DLB_LAYER_RESIDUAL) {
+      DLB_REQUIRE(l.depth >= 1 && i + l.depth < m->layers.size(),
+                  "compile: a RESIDUAL layer needs its block layers and a layer after them");
+      l.units = width;
+      l.norm_units = width;
+      l.group = 0;
+      size_t fan = width;
+      for (size_t j = 1; j <= l.depth; ++j) {
+        LayerRT &b = m->layers[i + j];
+        DLB_REQUIRE(b.type == DLB_LAYER_FULLY_CONNECTED, "compile: block layers must be fully connected");
+        b.group = 1;
+        b.block_input = j == 1;
+        b.fan_in = fan;
+        b.norm_units = fan;
+        fan = b.units;
+      }
+      i += l.depth;
+    } else {
+      l.group = 0;
+      l.block_input = false;
+      l.fan_in = width;
+      l.norm_units = l.units;
+      width = l.units;
+    }
+  }
   size_t w = 0;
   for (size_t i = 1; i < m->layers.size(); ++i) {
     LayerRT &l = m->layers[i];
-    l.fan_in = m->layers[i - 1].units;
+    if (l.type == DLB_LAYER_RESIDUAL) continue;
     l.first_conn = w;
     w += l.units * l.fan_in;
     l.last_conn = w;
@@ -112,6 +159,7 @@ dlb_status layout_parameters(dlb_model *m) {
   size_t b = w;
   for (size_t i = 1; i < m->layers.size(); ++i) {
     LayerRT &l = m->layers[i];
+    if (l.type == DLB_LAYER_RESIDUAL) continue;
     l.first_bias = b;
     b += l.units;
     l.last_bias = b;
@@ -122,7 +170,7 @@ dlb_status layout_parameters(dlb_model *m) {
   size_t u = 0;
   for (auto &l : m->layers) {
     l.first_norm_unit = u;
-    u += l.units;
+    u += l.norm_units;
   }
   m->total_norm_units = m->any_norm ? u : 0;
   m->total_parameters = m->total_weights + m->total_bias + 2 * m->total_norm_units;
@@ -166,7 +214,7 @@ dlb_status allocate_parameters(dlb_model *m) {
 
 dlb_status free_batch_buffers(dlb_model *m) {
   for (auto &l : m->layers) {
-    float **bufs[] = {&l.Z, &l.A, &l.A_lo, &l.delta, &l.delta_lo};
+    float **bufs[] = {&l.Z, &l.A, &l.A_lo, &l.delta, &l.delta_lo, &l.IN, &l.IN_lo};
     for (float **b : bufs) {
       if (*b) DLB_TRY(dlb_free(m->ctx, *b));
       *b = nullptr;
@@ -185,14 +233,14 @@ dlb_status ensure_norm_state(dlb_model *m) {
   const size_t T = m->seq_w;
   for (auto &l : m->layers) {
     if (l.norm == DLB_NORM_NONE || l.stats) continue;
-    const size_t n = T * l.units;
+    const size_t n = T * l.norm_units;
     DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.stats), 6 * n * sizeof(float)));
     std::vector<float> h(6 * n, 0.f);
     for (size_t i = 0; i < n; ++i) h[3 * n + i] = 1.f;  // running sigma = 1 (allocate.cpp L:1281-1284)
     DLB_TRY(dlb_memcpy_h2d(m->ctx, l.stats, h.data(), h.size() * sizeof(float)));
     DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
-    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.fwd_sums), 2 * l.units * sizeof(double)));
-    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.bwd_sums), 4 * l.units * sizeof(double)));
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.fwd_sums), 2 * l.norm_units * sizeof(double)));
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.bwd_sums), 4 * l.norm_units * sizeof(double)));
   }
   return DLB_OK;
 }
@@ -220,11 +268,23 @@ dlb_status ensure_batch(dlb_model *m, size_t rows) {
   for (size_t i = 1; i < m->layers.size(); ++i) {
     LayerRT &l = m->layers[i];
     const size_t n = T * rows * l.units;
-    DLB_TRY(dev_alloc(m, &l.Z, n, false));
     DLB_TRY(dev_alloc(m, &l.A, n, false));
-    DLB_TRY(dev_alloc(m, &l.A_lo, n, false));
     DLB_TRY(dev_alloc(m, &l.delta, n, false));
+    if (l.type == DLB_LAYER_RESIDUAL) {
+      DLB_TRY(dev_alloc(m, &l.A_lo, n, false));
+      continue;
+    }
     DLB_TRY(dev_alloc(m, &l.delta_lo, n, false));
+    if (l.group == 1) {
+      // Block layer: A holds its sums; later layers also keep their GEMM input.
+      if (!l.block_input) {
+        DLB_TRY(dev_alloc(m, &l.IN, T * rows * l.fan_in, false));
+        DLB_TRY(dev_alloc(m, &l.IN_lo, T * rows * l.fan_in, false));
+      }
+    } else {
+      DLB_TRY(dev_alloc(m, &l.Z, n, false));
+      DLB_TRY(dev_alloc(m, &l.A_lo, n, false));
+    }
   }
   DLB_TRY(dev_alloc(m, &m->input, T * rows * n_in(m), false));
   DLB_TRY(dev_alloc(m, &m->input_lo, T * rows * n_in(m), false));
@@ -238,9 +298,9 @@ dlb_status ensure_batch(dlb_model *m, size_t rows) {
 }
 
 dlb_brn_unit_arrays unit_arrays(dlb_model *m, LayerRT &l, size_t t) {
-  const size_t n = m->seq_w * l.units;
+  const size_t n = m->seq_w * l.norm_units;
   dlb_brn_unit_arrays u;
-  float *s = l.stats + t * l.units;
+  float *s = l.stats + t * l.norm_units;
   u.mean = s;
   u.sigma = s + n;
   u.mean_average = s + 2 * n;
@@ -271,10 +331,26 @@ dlb_status check_supported(dlb_model *m) {
   }
   for (size_t i = 1; i < m->layers.size(); ++i) {
     const LayerRT &l = m->layers[i];
+    if (l.type == DLB_LAYER_RESIDUAL) {
+      const LayerRT &last = m->layers[i + l.depth];
+      if (last.units != l.units) {
+        set_error("model: residual block at layer %zu maps width %zu to %zu; the zero-padded shortcut "
+                  "for unequal widths is outside the supported path", i, l.units, last.units);
+        return DLB_ERR_UNSUPPORTED;
+      }
+      if (m->layers[i + 1].norm != DLB_NORM_NONE) {
+        set_error("model: normalization on the first layer of a residual block (layer %zu) is outside "
+                  "the supported path", i + 1);
+        return DLB_ERR_UNSUPPORTED;
+      }
+      continue;
+    }
     if (l.type != DLB_LAYER_FULLY_CONNECTED) {
-      set_error("model: layer %zu has type %d; only fully connected layers are supported", i, l.type);
+      set_error("model: layer %zu has type %d; only fully connected and residual layers are supported",
+                i, l.type);
       return DLB_ERR_UNSUPPORTED;
     }
+    if (l.block_input) continue;  // its activation is never applied (fwp_mp.cpp L:4003)
     if (!af_supported(l.af)) {
       set_error("model: layer %zu activation %d is outside the supported set "
                 "(the reference's default for a fully connected layer is SIGMOID; set one of "
@@ -296,13 +372,92 @@ dlb_status refresh_weight_residuals(dlb_model *m) {
   return DLB_OK;
 }
 
+// Batch-renormalization statistics of layer l over `in` [B, l.norm_units]:
+// sums, exchange across ranks, averages and corrections.
+dlb_status norm_statistics(dlb_model *m, LayerRT &l, const float *in, int B, dlb_brn_unit_arrays *u) {
+  const int Bg = (int)(m->global_rows ? m->global_rows : (size_t)B);
+  const int n = (int)l.norm_units;
+  *u = unit_arrays(m, l, 0);
+  DLB_TRY(dlb_brn_forward_sums(m->ctx, in, B, n, l.fwd_sums));
+  DLB_TRY(dlb_allreduce_f64(m->ctx, l.fwd_sums, 2 * (size_t)n));
+  return dlb_brn_forward_finalize(m->ctx, l.fwd_sums, Bg, n, m->hp.normalization_momentum_average,
+                                  m->hp.normalization_epsilon, m->hp.brn_r_max, m->hp.brn_d_max, u);
+}
+
+// Backward of the same: the four sums, d_gamma / d_beta into the gradient
+// vector, exchange of d_mean / d_sigma, and the apply pass.  `e` holds
+// delta_af on entry and the error w.r.t. the normalisation input on return.
+dlb_status norm_backward(dlb_model *m, LayerRT &l, float *e, float *e_lo, const float *in,
+                         const float *act, int af, int B) {
+  const int Bg = (int)(m->global_rows ? m->global_rows : (size_t)B);
+  const int n = (int)l.norm_units;
+  dlb_brn_unit_arrays u = unit_arrays(m, l, 0);
+  DLB_TRY(dlb_activation_backward(m->ctx, e, in, act, &u, af, B, n, l.bwd_sums));
+  DLB_TRY(dlb_brn_backward_param_grads(m->ctx, l.bwd_sums, n, m->grads + gamma_index(m, l),
+                                       m->grads + beta_index(m, l), 1));
+  DLB_TRY(dlb_allreduce_f64(m->ctx, l.bwd_sums + 2 * (size_t)n, 2 * (size_t)n));
+  return dlb_brn_backward_apply(m->ctx, e, e_lo, in, &u, l.bwd_sums, Bg, B, n);
+}
+
+// ref: Forward_Pass__Residual__OpenMP and Forward_Pass__Residual__FC__OpenMP
+// (v1/learner/fwp_mp.cpp L:3777-3911, L:3951-4192): pre-activation block layers,
+// then the residual layer's normalization, ShakeDrop and the shortcut sum.
+dlb_status forward_residual(dlb_model *m, size_t i, const float *X, const float *X_lo, int B) {
+  LayerRT &res = m->layers[i];
+  const float *in = X, *in_lo = X_lo;
+  const float *prev_sums = nullptr;
+  for (size_t j = 1; j <= res.depth; ++j) {
+    LayerRT &b = m->layers[i + j];
+    const bool norm = b.norm != DLB_NORM_NONE;
+    if (!b.block_input) {
+      dlb_brn_unit_arrays u;
+      if (norm) DLB_TRY(norm_statistics(m, b, prev_sums, B, &u));
+      dlb_dropout_desc dp{b.dropout, b.dropout_value, b.mask, nullptr};
+      DLB_TRY(dlb_activation_forward(m->ctx, prev_sums, norm ? &u : nullptr, b.af,
+                                     b.dropout != DLB_DROPOUT_NONE ? &dp : nullptr, b.IN, b.IN_lo, B,
+                                     (int)b.fan_in));
+      in = b.IN;
+      in_lo = b.IN_lo;
+    }
+    const float *bias = norm ? nullptr : m->params + b.first_bias;
+    DLB_TRY(dlb_fc_forward(m->ctx, in, in_lo, m->params + b.first_conn, m->params_lo + b.first_conn,
+                           bias, b.A, B, (int)b.fan_in, (int)b.units));
+    prev_sums = b.A;
+  }
+  LayerRT &last = m->layers[i + res.depth];
+  float *block = last.A;
+  if (res.norm != DLB_NORM_NONE) {
+    // The residual layer's own normalization writes to its error buffer's
+    // sibling: reuse last.delta as the normalised block output until backward.
+    dlb_brn_unit_arrays u;
+    DLB_TRY(norm_statistics(m, res, last.A, B, &u));
+    DLB_TRY(dlb_activation_forward(m->ctx, last.A, &u, DLB_AF_LINEAR, nullptr, last.delta, nullptr, B,
+                                   (int)res.units));
+    block = last.delta;
+  }
+  const bool shake = res.dropout == DLB_DROPOUT_SHAKEDROP;
+  if (shake && (!res.sd_mask || res.sd_rows < (size_t)B)) {
+    set_error("model: residual layer %zu uses ShakeDrop but no noise was set for %d rows "
+              "(dlb_model_set_shakedrop_noise)", i, B);
+    return DLB_ERR_INVALID;
+  }
+  return dlb_residual_forward(m->ctx, X, block, shake ? res.sd_mask : nullptr,
+                              shake ? res.sd_fwd : nullptr, res.A, res.A_lo, B, (int)res.units);
+}
+
 dlb_status forward_layers(dlb_model *m, size_t rows) {
   DLB_TRY(refresh_weight_residuals(m));
   const int B = (int)rows;
-  const int Bg = (int)(m->global_rows ? m->global_rows : rows);
   const float *X = m->input, *X_lo = m->input_lo;
   for (size_t i = 1; i < m->layers.size(); ++i) {
     LayerRT &l = m->layers[i];
+    if (l.type == DLB_LAYER_RESIDUAL) {
+      DLB_TRY(forward_residual(m, i, X, X_lo, B));
+      X = l.A;
+      X_lo = l.A_lo;
+      i += l.depth;
+      continue;
+    }
     const int I = (int)l.fan_in, H = (int)l.units;
     const bool norm = l.norm != DLB_NORM_NONE;
     const bool last = i + 1 == m->layers.size();
@@ -311,14 +466,7 @@ dlb_status forward_layers(dlb_model *m, size_t rows) {
     DLB_TRY(dlb_fc_forward(m->ctx, X, X_lo, m->params + l.first_conn, m->params_lo + l.first_conn,
                            bias, l.Z, B, I, H));
     dlb_brn_unit_arrays u;
-    if (norm) {
-      u = unit_arrays(m, l, 0);
-      DLB_TRY(dlb_brn_forward_sums(m->ctx, l.Z, B, H, l.fwd_sums));
-      DLB_TRY(dlb_allreduce_f64(m->ctx, l.fwd_sums, 2 * (size_t)H));
-      DLB_TRY(dlb_brn_forward_finalize(m->ctx, l.fwd_sums, Bg, H, m->hp.normalization_momentum_average,
-                                       m->hp.normalization_epsilon, m->hp.brn_r_max,
-                                       m->hp.brn_d_max, &u));
-    }
+    if (norm) DLB_TRY(norm_statistics(m, l, l.Z, B, &u));
     if (l.af == DLB_AF_SOFTMAX) {
       DLB_TRY(dlb_softmax_forward(m->ctx, l.Z, l.A, B, H));
     } else {
@@ -404,6 +552,9 @@ dlb_status dlb_model_destroy(dlb_model *m) {
   for (auto &l : m->layers) {
     if (l.stats) dlb_free(m->ctx, l.stats);
     if (l.mask) dlb_free(m->ctx, l.mask);
+    if (l.sd_mask) dlb_free(m->ctx, l.sd_mask);
+    if (l.sd_fwd) dlb_free(m->ctx, l.sd_fwd);
+    if (l.sd_bwd) dlb_free(m->ctx, l.sd_bwd);
     if (l.fwd_sums) dlb_free(m->ctx, l.fwd_sums);
     if (l.bwd_sums) dlb_free(m->ctx, l.bwd_sums);
   }
@@ -421,15 +572,23 @@ dlb_status dlb_model_compile(dlb_model *m, size_t n_layers, size_t seq_w, int mo
                              const int *layer_types, const size_t *layer_units) {
   DLB_REQUIRE(m && layer_types && layer_units && n_layers >= 2 && seq_w >= 1, "dlb_model_compile");
   DLB_REQUIRE(m->layers.empty(), "dlb_model_compile: already compiled");
+  DLB_REQUIRE(layer_types[0] == DLB_LAYER_FULLY_CONNECTED &&
+                  layer_types[n_layers - 1] == DLB_LAYER_FULLY_CONNECTED,
+              "dlb_model_compile: input and output layers are fully connected layers");
+  for (size_t i = 0; i < n_layers; ++i)
+    DLB_REQUIRE(layer_units[i] > 0, "dlb_model_compile: empty layer");
   m->layers.resize(n_layers);
   for (size_t i = 0; i < n_layers; ++i) {
     m->layers[i].type = layer_types[i];
-    m->layers[i].units = layer_units[i];
-    DLB_REQUIRE(layer_units[i] > 0, "dlb_model_compile: empty layer");
+    // For a RESIDUAL layer the parameter is the block depth (model.hpp L:78-82).
+    if (layer_types[i] == DLB_LAYER_RESIDUAL) m->layers[i].depth = layer_units[i];
+    else m->layers[i].units = layer_units[i];
   }
   m->seq_w = seq_w;
   m->model_type = model_type;
-  return layout_parameters(m);
+  const dlb_status st = layout_parameters(m);
+  if (st != DLB_OK) m->layers.clear();
+  return st;
 }
 
 dlb_status dlb_model_set_layer_activation_function(dlb_model *m, size_t layer, int af) {
@@ -451,6 +610,10 @@ dlb_status dlb_model_set_layer_normalization(dlb_model *m, size_t layer, int nor
     set_error("Set__Layer_Normalization: only batch renormalization is supported (got %d)", norm);
     return DLB_ERR_UNSUPPORTED;
   }
+  if (m->layers[layer].stats) {
+    set_error("Set__Layer_Normalization: cannot change after the first training step");
+    return DLB_ERR_UNSUPPORTED;
+  }
   m->layers[layer].norm = norm;
   if (m->params) return allocate_parameters(m);
   return layout_parameters(m);
@@ -461,12 +624,23 @@ dlb_status dlb_model_set_dropout(dlb_model *m, size_t layer, int type, float val
   DLB_REQUIRE(m && layer_at(m, layer), "set_dropout: bad layer");
   // Not on the output layer (v1/learner/dropout.cpp L:57-60).
   DLB_REQUIRE(layer + 1 < m->layers.size(), "set_dropout: not available on the output layer");
-  if (type != DLB_DROPOUT_NONE && type != DLB_DROPOUT_BERNOULLI &&
-      type != DLB_DROPOUT_BERNOULLI_INVERTED) {
-    set_error("set_dropout: dropout type %d is outside the supported set of this build", type);
-    return DLB_ERR_UNSUPPORTED;
+  const bool residual = m->layers[layer].type == DLB_LAYER_RESIDUAL;
+  if (residual) {
+    // A residual layer takes ShakeDrop only; value0 is the probability that a
+    // row IS perturbed (fwp_mp.cpp L:4942-4955).
+    if (type != DLB_DROPOUT_NONE && type != DLB_DROPOUT_SHAKEDROP) {
+      set_error("set_dropout: a residual layer supports ShakeDrop only (got %d)", type);
+      return DLB_ERR_UNSUPPORTED;
+    }
+    if (type != DLB_DROPOUT_NONE) DLB_REQUIRE(value0 >= 0.f && value0 <= 1.f, "set_dropout: probability");
+  } else {
+    if (type != DLB_DROPOUT_NONE && type != DLB_DROPOUT_BERNOULLI &&
+        type != DLB_DROPOUT_BERNOULLI_INVERTED) {
+      set_error("set_dropout: dropout type %d is outside the supported set of this build", type);
+      return DLB_ERR_UNSUPPORTED;
+    }
+    if (type != DLB_DROPOUT_NONE) DLB_REQUIRE(value0 > 0.f && value0 <= 1.f, "set_dropout: keep probability");
   }
-  if (type != DLB_DROPOUT_NONE) DLB_REQUIRE(value0 > 0.f && value0 <= 1.f, "set_dropout: keep probability");
   if (scale_weights) {
     set_error("set_dropout: scale_weights=true is not supported (on a fresh layer the reference "
               "multiplies the layer's weights by 0/keep); pass false");
@@ -579,6 +753,7 @@ dlb_status dlb_model_initialize_weights_with_glorot_uniform(dlb_model *m) {
   std::uniform_real_distribution<float> dist;
   for (size_t i = 1; i < m->layers.size(); ++i) {
     const LayerRT &l = m->layers[i];
+    if (l.type == DLB_LAYER_RESIDUAL) continue;  // no weights of its own
     const size_t fan_in = l.fan_in;
     const size_t fan_out = i + 1 < m->layers.size() ? m->layers[i + 1].units : fan_in;
     float gain = 1.f, bound;
@@ -625,7 +800,7 @@ dlb_status dlb_model_layer_info(dlb_model *m, size_t layer, size_t out[10]) {
   out[5] = l.last_bias;
   out[6] = (size_t)l.norm;
   out[7] = (size_t)l.dropout;
-  out[8] = 0;
+  out[8] = (size_t)l.group;
   out[9] = m->any_norm ? l.first_norm_unit : 0;
   return DLB_OK;
 }
@@ -659,12 +834,12 @@ static dlb_status layer_norm_io(dlb_model *m, size_t layer, const char *name, fl
   const std::string nm(name);
   float *dev = nullptr;
   size_t count = 0;
-  if (nm == "scale") { dev = m->params + gamma_index(m, l); count = l.units; }
-  else if (nm == "shift") { dev = m->params + beta_index(m, l); count = l.units; }
+  if (nm == "scale") { dev = m->params + gamma_index(m, l); count = l.norm_units; }
+  else if (nm == "shift") { dev = m->params + beta_index(m, l); count = l.norm_units; }
   else {
     const int f = norm_field(nm);
     DLB_REQUIRE(f >= 0, "layer_norm: unknown field");
-    count = m->seq_w * l.units;
+    count = m->seq_w * l.norm_units;
     dev = l.stats + (size_t)f * count;
   }
   DLB_REQUIRE(n == count, "layer_norm: size mismatch");
@@ -694,6 +869,35 @@ dlb_status dlb_model_set_dropout_mask(dlb_model *m, size_t layer, const uint8_t 
   std::vector<uint8_t> norm01(n);
   for (size_t i = 0; i < n; ++i) norm01[i] = host_mask[i] ? 1 : 0;
   DLB_TRY(dlb_memcpy_h2d(m->ctx, l.mask, norm01.data(), n));
+  return dlb_ctx_sync(m->ctx, nullptr);
+}
+
+dlb_status dlb_model_set_shakedrop_noise(dlb_model *m, size_t layer, const uint8_t *host_row_mask,
+                                         const float *host_forward, const float *host_backward,
+                                         size_t rows) {
+  DLB_REQUIRE(m && host_row_mask && host_forward && host_backward && layer_at(m, layer) && rows > 0,
+              "set_shakedrop_noise");
+  LayerRT &l = m->layers[layer];
+  DLB_REQUIRE(l.type == DLB_LAYER_RESIDUAL && l.dropout == DLB_DROPOUT_SHAKEDROP,
+              "set_shakedrop_noise: layer is not a residual layer with ShakeDrop");
+  const size_t n = rows * l.units;
+  if (rows > l.sd_rows) {
+    if (l.sd_mask) DLB_TRY(dlb_free(m->ctx, l.sd_mask));
+    if (l.sd_fwd) DLB_TRY(dlb_free(m->ctx, l.sd_fwd));
+    if (l.sd_bwd) DLB_TRY(dlb_free(m->ctx, l.sd_bwd));
+    l.sd_mask = nullptr;
+    l.sd_fwd = l.sd_bwd = nullptr;
+    l.sd_rows = 0;
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_mask), rows));
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_fwd), n * sizeof(float)));
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_bwd), n * sizeof(float)));
+    l.sd_rows = rows;
+  }
+  std::vector<uint8_t> flags(rows);
+  for (size_t i = 0; i < rows; ++i) flags[i] = host_row_mask[i] ? 1 : 0;
+  DLB_TRY(dlb_memcpy_h2d(m->ctx, l.sd_mask, flags.data(), rows));
+  DLB_TRY(dlb_memcpy_h2d(m->ctx, l.sd_fwd, host_forward, n * sizeof(float)));
+  DLB_TRY(dlb_memcpy_h2d(m->ctx, l.sd_bwd, host_backward, n * sizeof(float)));
   return dlb_ctx_sync(m->ctx, nullptr);
 }
 
@@ -737,32 +941,83 @@ dlb_status dlb_model_compute_error(dlb_model *m, size_t rows, const float *const
   return dlb_model_compute_error_device(m, rows, m->target);
 }
 
+static std::vector<size_t> top_level(const dlb_model *m) {
+  std::vector<size_t> t;
+  for (size_t i = 0; i < m->layers.size(); ++i)
+    if (m->layers[i].group == 0) t.push_back(i);
+  return t;
+}
+
+// ref: Backward_Pass__Residual__Block__OpenMP and
+// Backward_Pass__Gradient__Residual__FC__OpenMP (v1/learner/bwp_mp.cpp
+// L:310-406, L:658-874): the error of the residual output becomes the error of
+// the block output (ShakeDrop rows scaled by fresh U(0,1), then the residual
+// layer's normalization), then the block layers from last to first.
+static dlb_status backward_residual(dlb_model *m, size_t i, int B) {
+  LayerRT &res = m->layers[i];
+  LayerRT &last = m->layers[i + res.depth];
+  const bool shake = res.dropout == DLB_DROPOUT_SHAKEDROP;
+  const bool rnorm = res.norm != DLB_NORM_NONE;
+  DLB_TRY(dlb_shakedrop_backward(m->ctx, res.delta, shake ? res.sd_mask : nullptr,
+                                 shake ? res.sd_bwd : nullptr, last.delta,
+                                 rnorm ? nullptr : last.delta_lo, B, (int)res.units));
+  if (rnorm)
+    DLB_TRY(norm_backward(m, res, last.delta, last.delta_lo, last.A, last.A, DLB_AF_LINEAR, B));
+  for (size_t j = res.depth; j >= 2; --j) {
+    LayerRT &b = m->layers[i + j];
+    LayerRT &prev = m->layers[i + j - 1];
+    DLB_TRY(dlb_fc_backward_input(m->ctx, b.delta, b.delta_lo, m->params + b.first_conn,
+                                  m->params_lo + b.first_conn, prev.delta, B, (int)b.fan_in,
+                                  (int)b.units));
+    if (b.norm != DLB_NORM_NONE) {
+      DLB_TRY(norm_backward(m, b, prev.delta, prev.delta_lo, prev.A, b.IN, b.af, B));
+    } else {
+      DLB_TRY(dlb_activation_backward(m->ctx, prev.delta, prev.A, b.IN, nullptr, b.af, B,
+                                      (int)b.fan_in, nullptr));
+      DLB_TRY(dlb_split_tf32(m->ctx, prev.delta, prev.delta_lo, (size_t)B * b.fan_in));
+    }
+  }
+  return DLB_OK;
+}
+
 // ref: Model::FF__Backward_Pass_Batch__OpenMP (v1/learner/bwp_mp.cpp L:28-208):
-// from the output layer down to layer 2; the error into the input layer is
-// never formed.
+// from the output layer down; the error into the input layer is never formed.
 dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows) {
   DLB_REQUIRE(m && rows > 0 && rows <= m->alloc_rows, "backward_pass");
   const int B = (int)rows;
-  const int Bg = (int)(m->global_rows ? m->global_rows : rows);
-  for (size_t g = m->layers.size() - 1; g >= 2; --g) {
-    LayerRT &next = m->layers[g];
-    LayerRT &l = m->layers[g - 1];
-    const int H = (int)l.units;
-    DLB_TRY(dlb_fc_backward_input(m->ctx, next.delta, next.delta_lo, m->params + next.first_conn,
-                                  m->params_lo + next.first_conn, l.delta, B, H, (int)next.units));
-    if (l.norm != DLB_NORM_NONE) {
-      dlb_brn_unit_arrays u = unit_arrays(m, l, 0);
-      DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, &u, l.af, B, H, l.bwd_sums));
-      // d_gamma / d_beta travel with the gradient all-reduce; d_mean / d_sigma
-      // are needed now, summed over every rank's rows.
-      DLB_TRY(dlb_brn_backward_param_grads(m->ctx, l.bwd_sums, H, m->grads + gamma_index(m, l),
-                                           m->grads + beta_index(m, l), 1));
-      DLB_TRY(dlb_allreduce_f64(m->ctx, l.bwd_sums + 2 * (size_t)H, 2 * (size_t)H));
-      DLB_TRY(dlb_brn_backward_apply(m->ctx, l.delta, l.delta_lo, l.Z, &u, l.bwd_sums, Bg, B, H));
-    } else {
-      DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, nullptr, l.af, B, H, nullptr));
-      DLB_TRY(dlb_split_tf32(m->ctx, l.delta, l.delta_lo, (size_t)B * H));
+  const std::vector<size_t> tops = top_level(m);
+  for (size_t pos = tops.size() - 1; pos >= 1; --pos) {
+    const size_t i = tops[pos];
+    LayerRT &l = m->layers[i];
+    LayerRT *below = pos > 1 ? &m->layers[tops[pos - 1]] : nullptr;
+    if (l.type == DLB_LAYER_RESIDUAL) {
+      DLB_TRY(backward_residual(m, i, B));
+      if (below) {
+        // shortcut error + delta_1 W_1
+        LayerRT &first = m->layers[i + 1];
+        DLB_TRY(dlb_memcpy_d2d(m->ctx, below->delta, l.delta, (size_t)B * l.units * sizeof(float)));
+        GemmOperand A{first.delta, first.delta_lo, (long long)first.units, 1};
+        GemmOperand Bo{m->params + first.first_conn, m->params_lo + first.first_conn, 1,
+                       (long long)first.fan_in};
+        GemmEpilogue ep;
+        ep.accumulate = 1;
+        DLB_TRY(gemm(m->ctx, A, Bo, below->delta, (long long)first.fan_in, B, (int)first.fan_in,
+                     (int)first.units, ep));
+      }
+      continue;
     }
+    const int H = (int)l.units;
+    if (pos + 1 != tops.size()) {  // hidden layer: l.delta holds dA
+      if (l.norm != DLB_NORM_NONE) {
+        DLB_TRY(norm_backward(m, l, l.delta, l.delta_lo, l.Z, l.A, l.af, B));
+      } else {
+        DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, nullptr, l.af, B, H, nullptr));
+        DLB_TRY(dlb_split_tf32(m->ctx, l.delta, l.delta_lo, (size_t)B * H));
+      }
+    }
+    if (below)
+      DLB_TRY(dlb_fc_backward_input(m->ctx, l.delta, l.delta_lo, m->params + l.first_conn,
+                                    m->params_lo + l.first_conn, below->delta, B, (int)l.fan_in, H));
   }
   return DLB_OK;
 }
@@ -770,16 +1025,30 @@ dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows) {
 // ref: Model::update_derivatives (v1/learner/update_derivative_fwp_mp.cpp L:27-240).
 dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows) {
   DLB_REQUIRE(m && rows > 0 && rows <= m->alloc_rows, "update_derivatives");
-  const float *X = m->input, *X_lo = m->input_lo;
+  const float *top = m->input, *top_lo = m->input_lo;  // output of the top-level layer below
   for (size_t i = 1; i < m->layers.size(); ++i) {
     LayerRT &l = m->layers[i];
+    if (l.type == DLB_LAYER_RESIDUAL) continue;  // its block layers follow; its output is set after them
+    const float *X = top, *X_lo = top_lo;
+    if (l.group == 1 && !l.block_input) {
+      X = l.IN;
+      X_lo = l.IN_lo;
+    }
     float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
     DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn,
                                    dbias, (int)rows, (int)l.fan_in, (int)l.units, 1));
     if (m->overlap_grad_allreduce)
       DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
-    X = l.A;
-    X_lo = l.A_lo;
+    if (l.group == 0) {
+      top = l.A;
+      top_lo = l.A_lo;
+    } else if (i + 1 < m->layers.size() && m->layers[i + 1].group == 0) {
+      // last layer of a block: what follows reads the residual layer's output
+      size_t r = i;
+      while (m->layers[r].type != DLB_LAYER_RESIDUAL) --r;
+      top = m->layers[r].A;
+      top_lo = m->layers[r].A_lo;
+    }
   }
   return DLB_OK;
 }

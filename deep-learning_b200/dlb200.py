@@ -69,7 +69,10 @@ SIGNATURES = {
     "dlb_activation_backward": (_i, [_vp, _vp, _vp, _vp, C.POINTER(BrnUnitArrays), _i, _i, _i, _vp]),
     "dlb_brn_backward_apply": (_i, [_vp, _vp, _vp, _vp, C.POINTER(BrnUnitArrays), _vp, _i, _i, _i]),
     "dlb_brn_backward_param_grads": (_i, [_vp, _vp, _i, _vp, _vp, _i]),
-    "dlb_loss_delta": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "dlb_residual_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "dlb_shakedrop_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "dlb_model_set_shakedrop_noise": (_i, [_vp, _sz, _vp, _vp, _vp, _sz]),
+    "dlb_loss_delta":(_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "dlb_optimizer_step": (_i, [_vp, _i, C.POINTER(OptimizerScalars), _vp, _vp, _vp, _vp, _vp, _vp, _sz]),
     "dlb_optimizer_prepare": (_i, [_i, C.POINTER(_f), C.POINTER(_f), C.POINTER(_f), C.POINTER(OptimizerScalars)]),
     "dlb_comm_unique_id": (_i, [C.c_char * 128]),
@@ -407,6 +410,13 @@ class Model:
     def set_dropout_mask(self, layer, mask):
         mask = np.ascontiguousarray(mask, dtype=np.uint8)
         check(self.L.dlb_model_set_dropout_mask(self.h, layer, _ptr(mask), mask.size), "set_dropout_mask")
+
+    def set_shakedrop_noise(self, layer, mask, forward, backward):
+        mask = np.ascontiguousarray(mask, dtype=np.uint8)
+        forward = np.ascontiguousarray(forward, dtype=np.float32)
+        backward = np.ascontiguousarray(backward, dtype=np.float32)
+        check(self.L.dlb_model_set_shakedrop_noise(self.h, layer, _ptr(mask), _ptr(forward), _ptr(backward),
+                                                   mask.size), "set_shakedrop_noise")
 
     # --- step -----------------------------------------------------------
     def train_begin(self, batch):

@@ -236,6 +236,24 @@ dlb_status dlb_brn_backward_param_grads(dlb_ctx *ctx, const double *sums, int n_
                                         float *d_gamma, float *d_beta, int accumulate);
 
 /* ------------------------------------------------------------------------ */
+/* Residual block (shortcut and block of equal width).
+ * Forward: on rows with row_mask[b] != 0 every element of block[b,:] is
+ * multiplied by noise[b,:] (draws of U(-1,1)), in place as the reference
+ * perturbs the block's output buffer; out = x + block; out_lo optional.
+ * row_mask == NULL: plain shortcut sum.
+ * ref: Forward_Pass__Dropout__ShakeDrop__OpenMP (v1/learner/fwp_mp.cpp
+ * L:4922-4957) and Forward_Pass__Zero_Padded_Identity__OpenMP (L:5058-5123). */
+dlb_status dlb_residual_forward(dlb_ctx *ctx, const float *x, float *block,
+                                const uint8_t *row_mask, const float *noise, float *out,
+                                float *out_lo, int rows, int width);
+/* Backward: delta = d * noise (draws of U(0,1)) on the rows perturbed forward,
+ * d elsewhere; delta_lo optional.
+ * ref: Backward_Pass__Dropout__ShakeDrop__OpenMP (v1/learner/bwp_mp.cpp L:933-966). */
+dlb_status dlb_shakedrop_backward(dlb_ctx *ctx, const float *d, const uint8_t *row_mask,
+                                  const float *noise, float *delta, float *delta_lo, int rows,
+                                  int width);
+
+/* ------------------------------------------------------------------------ */
 /* Output error and loss.
  * MSE: delta = f'(pre, q) * 2 (q - y) / (global_rows * n_out); loss += (q-y)^2.
  * Cross-entropy on a softmax layer: delta_j = sum_k (q_j [j==k] - q_k q_j) L'_k,
@@ -335,6 +353,14 @@ dlb_status dlb_model_set_layer_norm(dlb_model *m, size_t layer, const char *name
                                     const float *host_in, size_t n);
 dlb_status dlb_model_set_dropout_mask(dlb_model *m, size_t layer, const uint8_t *host_mask,
                                       size_t n);
+/* ShakeDrop draws of one training step for a RESIDUAL layer: row flags [rows]
+ * and the forward U(-1,1) / backward U(0,1) draws [rows, width] (host arrays;
+ * only flagged rows are read).  The reference draws them from clock-seeded
+ * generators inside the step (fwp_mp.cpp L:4942-4955, bwp_mp.cpp L:959-963);
+ * here they are inputs so that a run can be reproduced. */
+dlb_status dlb_model_set_shakedrop_noise(dlb_model *m, size_t layer, const uint8_t *host_row_mask,
+                                         const float *host_forward, const float *host_backward,
+                                         size_t rows);
 /* Data-parallel: rows given to forward_pass are this rank's shard of a batch
  * of global_rows rows (default: equal to the call's rows). */
 dlb_status dlb_model_set_global_batch(dlb_model *m, size_t global_rows);

@@ -63,6 +63,7 @@ def lib():
         "ref_set_layer_norm": (i, [vp, sz, cp, _f32p, sz]),
         "ref_set_dropout_mask": (i, [vp, sz, _u8p, sz]),
         "ref_seed_shakedrop": (i, [vp, C.c_uint]),
+        "ref_shakedrop_draws": (i, [C.c_uint, sz, sz, sz, _f32p, _u8p, _f32p, _f32p]),
         "ref_train_begin": (i, [vp, sz]),
         "ref_forward_pass": (i, [vp, sz, _f32p]),
         "ref_compute_error": (i, [vp, sz, _f32p]),
@@ -70,6 +71,7 @@ def lib():
         "ref_update_derivatives": (i, [vp, sz]),
         "ref_merge_derivatives": (i, [vp]),
         "ref_get_loss": (d, [vp]),
+        "ref_reset_loss": (i, [vp]),
         "ref_update_weights": (i, [vp, sz, sz]),
         "ref_train_step": (i, [vp, sz, _f32p, _f32p, C.POINTER(d)]),
         "ref_get_layer_outputs": (i, [vp, sz, sz, _f32p]),
@@ -229,6 +231,9 @@ class RefModel:
     def get_loss(self):
         return self.L.ref_get_loss(self.h)
 
+    def reset_loss(self):
+        _ck(self.L.ref_reset_loss(self.h), "reset_loss")
+
     def update_weights(self, batch, training_size):
         _ck(self.L.ref_update_weights(self.h, batch, training_size), "update_weights")
 
@@ -252,6 +257,18 @@ class RefModel:
         out = np.empty((T, batch, n_out), dtype=np.float32)
         _ck(self.L.ref_get_layer_errors(self.h, layer, batch, which, out), "get_layer_errors")
         return out
+
+
+def shakedrop_draws(seed, probabilities, rows, width):
+    """(masks [n, rows], forward [n, rows, width], backward [n, rows, width]) that
+    a serial reference step draws after RefModel.seed_shakedrop(seed)."""
+    p = np.ascontiguousarray(probabilities, dtype=np.float32)
+    n = p.size
+    masks = np.zeros((n, rows), np.uint8)
+    fwd = np.ones((n, rows, width), np.float32)
+    bwd = np.ones((n, rows, width), np.float32)
+    _ck(lib().ref_shakedrop_draws(seed, n, rows, width, p, masks, fwd, bwd), "shakedrop_draws")
+    return masks, fwd, bwd
 
 
 def optimizer_sweep(optimizer, p, grad_fill, m, v, vhat, steps, hparams, use_mp=True):

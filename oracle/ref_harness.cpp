@@ -17,6 +17,7 @@
 #include <omp.h>
 
 #include <chrono>
+#include <iostream>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -37,7 +38,13 @@ struct Handle {
 void ensure_logger() {
   /* ERR()/ASSERT_MSG dereference the global logger. */
   static std::unique_ptr<Logger> lg;
-  if (!lg) lg = std::make_unique<Logger>(LOGLEVEL::FATAL);
+  if (!lg) {
+    lg = std::make_unique<Logger>(LOGLEVEL::FATAL);
+    /* Dist::Bernoulli::probability() logs a FATAL line on every call (its
+     * assertion is `p >= 0 && p < 0`, ops/distributions/bernoulli.cpp L:56);
+     * the logger writes to std::wcout, which is silenced here. */
+    std::wcout.setstate(std::ios_base::failbit);
+  }
 }
 
 inline Handle *H(ref_model m) { return static_cast<Handle *>(m); }
@@ -334,6 +341,35 @@ int ref_seed_shakedrop(ref_model m, unsigned seed) {
   return 0;
 }
 
+int ref_shakedrop_draws(unsigned seed, size_t n_blocks, size_t rows, size_t width,
+                        const float *probabilities, uint8_t *masks, float *forward,
+                        float *backward) {
+  ensure_logger();
+  /* Same seeds as ref_seed_shakedrop gives thread 0. */
+  Dist::Bernoulli bern;
+  Dist::Real real_gen;
+  bern.seed(seed);
+  real_gen.seed(seed + 1u);
+  for (size_t i = 0; i < n_blocks * rows * width; ++i) forward[i] = backward[i] = 1.0f;
+  for (size_t b = 0; b < n_blocks; ++b) {
+    bern.probability(probabilities[b]);
+    real_gen.range(-1_r, 1_r);
+    for (size_t r = 0; r < rows; ++r) {
+      bool const hit = bern();
+      masks[b * rows + r] = hit ? 1 : 0;
+      if (hit)
+        for (size_t k = 0; k < width; ++k) forward[(b * rows + r) * width + k] = real_gen();
+    }
+  }
+  for (size_t b = n_blocks; b-- > 0;) {
+    real_gen.range(0_r, 1_r);
+    for (size_t r = 0; r < rows; ++r)
+      if (masks[b * rows + r])
+        for (size_t k = 0; k < width; ++k) backward[(b * rows + r) * width + k] = real_gen();
+  }
+  return 0;
+}
+
 int ref_train_begin(ref_model m, size_t batch) {
   Handle *h = H(m);
   Model &M = h->model;
@@ -406,6 +442,11 @@ int ref_merge_derivatives(ref_model m) {
 }
 
 double ref_get_loss(ref_model m) { return H(m)->model.get_loss(ENV::NONE); }
+
+int ref_reset_loss(ref_model m) {
+  H(m)->model.reset_loss();
+  return 0;
+}
 
 int ref_update_weights(ref_model m, size_t batch, size_t training_size) {
   Model &M = H(m)->model;

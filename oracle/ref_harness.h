@@ -73,6 +73,16 @@ int ref_set_dropout_mask(ref_model m, size_t layer, const uint8_t *mask,
 /* Reseeds every ShakeDrop generator (Bernoulli and real, all threads). */
 int ref_seed_shakedrop(ref_model m, unsigned seed);
 
+/* The draws a serial (set_mp(0)) step makes from the ShakeDrop generators after
+ * ref_seed_shakedrop(m, seed), replayed with copies of the reference's own
+ * generator classes: forward, residual layers in order, per row one Bernoulli
+ * draw and, if set, `width` draws of U(-1,1); backward, residual layers in
+ * reverse, `width` draws of U(0,1) for every flagged row.  masks: [n_blocks,
+ * rows]; forward/backward: [n_blocks, rows, width] (rows not flagged hold 1). */
+int ref_shakedrop_draws(unsigned seed, size_t n_blocks, size_t rows, size_t width,
+                        const float *probabilities, uint8_t *masks, float *forward,
+                        float *backward);
+
 int ref_train_begin(ref_model m, size_t batch);
 /* X: [batch, seq_w * n_inp] row-major, Y: [batch, seq_w * n_out]. */
 int ref_forward_pass(ref_model m, size_t batch, const float *X);
@@ -81,6 +91,7 @@ int ref_backward_pass(ref_model m, size_t batch);
 int ref_update_derivatives(ref_model m, size_t batch);
 int ref_merge_derivatives(ref_model m);
 double ref_get_loss(ref_model m);
+int ref_reset_loss(ref_model m);
 int ref_update_weights(ref_model m, size_t batch, size_t training_size);
 /* forward, error, backward, gradient accumulation in one OpenMP region as
  * Driver::train_mp does (lib/deep-learning/drivers/driver.cpp L:227-266);

@@ -42,6 +42,30 @@ def cases():
     }
 
 
+def noisy_cases():
+    """Workloads whose steps consume ShakeDrop noise: name -> (config, steps)."""
+    return {
+        "residual_elu_shakedrop_adam": (configs.residual_mlp(width=24, blocks=3, n_out=7, batch=16), 6),
+    }
+
+
+def make_noisy(name, cfg, steps):
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    p0 = ref.get_array("parameters")
+    X, Y = configs.synthetic_batch(cfg)
+    draws = [util.shakedrop_step_draws(cfg, s) for s in range(steps)]
+    out = util.trace_noisy(ref, cfg, steps=steps, X=X, Y=Y, draws=draws)
+    blob = {"in_X": X, "in_Y": Y, "in_params": p0, "steps": np.int64(steps)}
+    for s, (seed, arrays) in enumerate(draws):
+        blob[f"in_sdseed{s}"] = np.int64(seed)
+        for li, (mk, fw, bw) in arrays.items():
+            blob[f"in_sd{s}_{li}_mask"], blob[f"in_sd{s}_{li}_fwd"], blob[f"in_sd{s}_{li}_bwd"] = mk, fw, bw
+    blob.update({f"out_{k}": v for k, v in out.items()})
+    path = os.path.join(HERE, name + ".npz")
+    np.savez_compressed(path, **blob)
+    print(f"{name}: {os.path.getsize(path)} bytes, loss {out['losses'][0]:.6f} -> {out['losses'][-1]:.6f}")
+
+
 def main():
     if not ref_binding.available():
         sys.exit("oracle/_ref/libdlref.so is missing: run `make -C oracle` where the reference sources are")
@@ -58,6 +82,8 @@ def main():
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, **blob)
         print(f"{name}: {os.path.getsize(path)} bytes, loss {out['losses'][0]:.6f} -> {out['losses'][-1]:.6f}")
+    for name, (cfg, steps) in noisy_cases().items():
+        make_noisy(name, cfg, steps)
 
 
 if __name__ == "__main__":

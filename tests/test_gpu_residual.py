@@ -1,0 +1,86 @@
+"""Residual blocks with ShakeDrop on the GPU, through the Model entry points of
+the C ABI: against the committed fixture of the compiled reference and against
+the CPU restatement on a shape whose products run on the tensor-core kernel."""
+import numpy as np
+import pytest
+
+import configs
+import dlb200
+import fc_residual
+import golden_io
+import ref_binding
+import util
+
+pytestmark = pytest.mark.gpu
+
+TOL_1 = 1e-5       # activations, errors, gradients after one step (rel_l2)
+TOL_PARAMS = 1e-4  # updated weights: Adam's first step magnifies gradients of the order of eps
+
+
+def _check(got, want, skip=()):
+    for key, (l2, mx) in util.compare(got, want).items():
+        if key in skip:
+            continue
+        tol = TOL_PARAMS if key.startswith("params") else TOL_1
+        assert l2 <= tol, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+
+
+@pytest.mark.parametrize("name", sorted(golden_io.NOISY_CASES))
+def test_residual_model_matches_golden(gpu_ctx, name):
+    cfg, steps, X, Y, draws, p0, want = golden_io.load_noisy(name)
+    model = util.build(dlb200.Model(gpu_ctx), cfg, params=p0)
+    got = util.trace_noisy(model, cfg, steps, X, Y, draws)
+    assert gpu_ctx.sync() == 0
+    _check(got, want)
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="ShakeDrop draws come from oracle/_ref")
+def test_residual_model_vs_restatement_tensor_core_shape(gpu_ctx):
+    cfg = configs.residual_mlp(width=256, blocks=2, n_out=10, batch=256)
+    X, Y = configs.synthetic_batch(cfg)
+    draws = [util.shakedrop_step_draws(cfg, s) for s in range(3)]
+
+    def prepare(model):
+        util.set_step_noise(model, cfg, 0, draws[0])
+
+    p0, seed = util.kink_free_parameters(cfg, fc_residual.ResidualOracleModel, X, {}, scale=1.0 / 16,
+                                         prepare=prepare)
+    want = util.trace_noisy(util.build(fc_residual.ResidualOracleModel(), cfg, params=p0), cfg, 3, X, Y, draws)
+    got = util.trace_noisy(util.build(dlb200.Model(gpu_ctx), cfg, params=p0), cfg, 3, X, Y, draws)
+    assert gpu_ctx.sync() == 0
+    _check(got, want, skip=("params_last",))
+
+
+def test_residual_kernels(gpu_ctx):
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rng = np.random.default_rng(9)
+    for rows, width in ((64, 128), (33, 10)):
+        x = rng.standard_normal((rows, width), dtype=np.float32)
+        block = rng.standard_normal((rows, width), dtype=np.float32)
+        mask = (rng.random(rows) < 0.5).astype(np.uint8)
+        noise = (rng.random((rows, width)) * 2 - 1).astype(np.float32)
+        xd, bd, md, nd = ctx.array(x), ctx.array(block), ctx.array(mask), ctx.array(noise)
+        out, lo = ctx.empty((rows, width)), ctx.empty((rows, width))
+        dlb200.check(L.dlb_residual_forward(ctx.h, xd.ptr, bd.ptr, md.ptr, nd.ptr, out.ptr, lo.ptr, rows, width))
+        pert = np.where(mask[:, None] != 0, block * noise, block)
+        assert np.array_equal(bd.get(), pert)            # perturbed in place
+        assert np.array_equal(out.get(), x + pert)
+        d = rng.standard_normal((rows, width), dtype=np.float32)
+        dd, delta = ctx.array(d), ctx.empty((rows, width))
+        dlb200.check(L.dlb_shakedrop_backward(ctx.h, dd.ptr, md.ptr, nd.ptr, delta.ptr, None, rows, width))
+        assert np.array_equal(delta.get(), np.where(mask[:, None] != 0, d * noise, d))
+        dlb200.check(L.dlb_shakedrop_backward(ctx.h, dd.ptr, None, None, delta.ptr, None, rows, width))
+        assert np.array_equal(delta.get(), d)
+    assert ctx.sync() == 0
+
+
+def test_unequal_block_width_is_refused(gpu_ctx):
+    m = dlb200.Model(gpu_ctx)
+    m.compile([3, 9, 3, 3, 3], [8, 2, 8, 12, 4])     # block maps 8 -> 12
+    for i in (2, 3):
+        m.set_layer_activation_function(i, 3)
+    m.set_layer_activation_function(4, 11)
+    m.set_loss_fn(10)
+    m.set_optimizer(2)
+    with pytest.raises(dlb200.DlbError):
+        m.forward_pass(4, np.zeros((4, 8), np.float32))

@@ -95,16 +95,19 @@ def near_kink(oracle_model, cfg, X, masks, band=1e-5):
     oracle_model.forward_pass(B, X)
     n = 0
     for li, l in enumerate(cfg["layers"][1:-1], start=1):
-        if l.get("af") in KINKED:
+        if l.get("af") in KINKED and "Y" in oracle_model.layers[li]:
             n += int((np.abs(oracle_model.layers[li]["Y"]) < band).sum())
     return n
 
 
-def kink_free_parameters(cfg, make_oracle, X, masks, scale, tries=64, band=1e-5):
+def kink_free_parameters(cfg, make_oracle, X, masks, scale, tries=64, band=1e-5, prepare=None):
     """Seeded random weights (first seed for which no pre-activation lies on a
-    derivative jump).  Returns (params, seed)."""
+    derivative jump).  Returns (params, seed).  `prepare(model)` runs before the
+    probing forward pass (e.g. to hand over ShakeDrop noise)."""
     for seed in range(tries):
         ora = build(make_oracle(), cfg)
+        if prepare:
+            prepare(ora)
         rng = np.random.default_rng(seed)
         p0 = ora.get_array("parameters")
         nw = ora.size("total_weights")
@@ -113,3 +116,69 @@ def kink_free_parameters(cfg, make_oracle, X, masks, scale, tries=64, band=1e-5)
         if near_kink(ora, cfg, X, masks, band) == 0:
             return p0, seed
     raise AssertionError("no kink-free seed found")
+
+
+def shakedrop_step_draws(cfg, step, rows=None):
+    """Draws of training step `step` for every ShakeDrop layer, taken from the
+    reference's own generator classes (oracle/_ref).  Seed of a step =
+    cfg['shakedrop_seed'] + 1000 * step."""
+    import ref_binding
+
+    layers = configs.shakedrop_layers(cfg)
+    width = cfg["layers"][0]["units"]
+    seed = cfg.get("shakedrop_seed", 2) + 1000 * step
+    masks, fwd, bwd = ref_binding.shakedrop_draws(seed, [p for _, p in layers], rows or cfg["batch"], width)
+    return seed, {li: (masks[k], fwd[k], bwd[k]) for k, (li, _) in enumerate(layers)}
+
+
+def set_step_noise(model, cfg, step, draws=None):
+    """Gives one training step its ShakeDrop noise: the reference is reseeded,
+    every other backend receives the arrays the reference will draw."""
+    if not configs.shakedrop_layers(cfg):
+        return
+    if draws is None:
+        seed, arrays = shakedrop_step_draws(cfg, step)
+    else:
+        seed, arrays = draws
+    if hasattr(model, "seed_shakedrop"):
+        model.seed_shakedrop(seed)
+    else:
+        for li, (mk, fw, bw) in arrays.items():
+            model.set_shakedrop_noise(li, mk, fw, bw)
+
+
+def trace_noisy(model, cfg, steps=1, X=None, Y=None, draws=None):
+    """`trace` for workloads whose steps consume ShakeDrop noise; `draws` maps a
+    step index to (seed, {layer: (mask, forward, backward)})."""
+    B = cfg["batch"]
+    if X is None:
+        X, Y = configs.synthetic_batch(cfg)
+    model.train_begin(B)
+    nl = len(cfg["layers"])
+    out = {}
+    losses = []
+    for step in range(steps):
+        set_step_noise(model, cfg, step, draws[step] if draws else None)
+        if hasattr(model, "reset_loss"):
+            model.reset_loss()
+        model.forward_pass(B, X)
+        if step == 0:
+            for li in range(1, nl):
+                out[f"act{li}"] = model.get_layer_outputs(li, B).reshape(B, -1)
+        model.compute_error(B, Y)
+        model.backward_pass(B)
+        if step == 0:
+            for li in range(1, nl):
+                if cfg["layers"][li]["type"] == 3:
+                    out[f"delta{li}"] = model.get_layer_errors(li, B).reshape(B, -1)
+        model.update_derivatives(B)
+        model.merge_derivatives()
+        losses.append(model.get_loss())
+        if step == 0:
+            out["grads"] = model.get_array("derivatives")
+        model.update_weights(B, B)
+        if step == 0:
+            out["params1"] = model.get_array("parameters")
+    out["params_last"] = model.get_array("parameters")
+    out["losses"] = np.asarray(losses, np.float64)
+    return out
