@@ -82,6 +82,56 @@ def residual_mlp(width=8192, blocks=16, n_out=1000, batch=8192, p_last=0.5, opti
     )
 
 
+def indrnn_stack(n_in=512, hidden=2048, depth=4, n_out=512, seq_w=256, batch=1024,
+                 af=ACTIVATION.RELU, optimizer=OPTIMIZER.ADABOUND, norm=True):
+    """IndRNN stack: `depth` independently recurrent layers of width `hidden`
+    with ReLU recurrence and batch renormalization (statistics per time step),
+    a linear output layer, MSE on the last time step only (time_delays =
+    seq_w - 1), AdaBound.  The recurrent weights are drawn from U(0, 1) by
+    `set_recurrent_uniform` after the Glorot initialisation."""
+    layers = [dict(type=LAYER.FULLY_CONNECTED, units=n_in)]
+    for _ in range(depth):
+        layers.append(dict(type=LAYER.FULLY_CONNECTED_INDEPENDENTLY_RECURRENT, units=hidden, af=af,
+                           norm=LAYER_NORM.BATCH_RENORMALIZATION if norm else None))
+    layers.append(dict(type=LAYER.FULLY_CONNECTED, units=n_out, af=ACTIVATION.LINEAR))
+    return dict(
+        name=f"indrnn_{n_in}-{depth}x{hidden}-{n_out}_T{seq_w}_b{batch}",
+        model_type=MODEL.RECURRENT, seq_w=seq_w, time_delays=seq_w - 1, layers=layers,
+        loss=LOSS_FN.MSE, optimizer=optimizer,
+        hparams=dict(adam_learning_rate=1e-3, adam_beta1=0.9, adam_beta2=0.999, adam_epsilon=1e-8,
+                     learning_rate_final=0.1, learning_gamma=1e-3, adam_gamma=0.1),
+        brn=dict(r_max=3.0, d_max=5.0, momentum=0.99, eps=1e-5),
+        batch=batch, weight_seed=0, data_seed=0, recurrent_seed=3, inputs="normal", targets="normal", mp=False,
+    )
+
+
+def recurrent_slices(cfg):
+    """[(layer index, slice of the flat parameter vector)] of the recurrent
+    weights: an IndRNN layer's u[units] follows its W[units, fan_in]
+    (v1/learner/connections_prepare.cpp L:46-81)."""
+    out, w = [], 0
+    layers = cfg["layers"]
+    for i in range(1, len(layers)):
+        w += layers[i]["units"] * layers[i - 1]["units"]
+        if layers[i]["type"] == LAYER.FULLY_CONNECTED_INDEPENDENTLY_RECURRENT:
+            out.append((i, slice(w, w + layers[i]["units"])))
+            w += layers[i]["units"]
+    return out
+
+
+def set_recurrent_uniform(m, cfg, low=0.0, high=1.0):
+    """Overwrites every IndRNN layer's recurrent weights with seeded draws of
+    U(low, high)."""
+    rs = recurrent_slices(cfg)
+    if not rs:
+        return
+    rng = np.random.default_rng(cfg.get("recurrent_seed", 3))
+    p = m.get_array("parameters")
+    for _, s in rs:
+        p[s] = rng.uniform(low, high, s.stop - s.start).astype(np.float32)
+    m.set_array("parameters", p)
+
+
 def shakedrop_layers(cfg):
     """[(layer index, probability)] of the residual layers that use ShakeDrop."""
     return [(i, l["dropout"][1]) for i, l in enumerate(cfg["layers"])

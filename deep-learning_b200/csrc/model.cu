@@ -35,6 +35,9 @@ struct LayerRT {
   // Indices into the flat parameter vector.
   size_t first_conn = 0, last_conn = 0, first_bias = 0, last_bias = 0, first_norm_unit = 0;
   size_t fan_in = 0;
+  // IndRNN layer: its recurrent weights u[units] follow its W inside
+  // [first_conn, last_conn) (v1/learner/connections_prepare.cpp L:46-81).
+  size_t first_recurrent = 0;
   // Residual blocks (the reference's layer list: a RESIDUAL layer of depth d
   // followed by its d block layers, v1/learner/compile.cpp).
   int group = 0;            // 1 = layer inside a residual block
@@ -86,6 +89,9 @@ struct dlb_model {
   float *params = nullptr, *params_lo = nullptr, *grads = nullptr, *m1 = nullptr, *m2 = nullptr,
         *m2hat = nullptr;
   float *input = nullptr, *input_lo = nullptr, *target = nullptr;
+  // Time-stepped models: the caller's rows [rows, T*n] as they arrive, before
+  // the reorder to [T, rows, n].
+  float *input_rows = nullptr, *target_rows = nullptr;
   float *stage_x = nullptr, *stage_y = nullptr;  // pinned
   size_t stage_x_elems = 0, stage_y_elems = 0;
   double *loss_sum = nullptr;
@@ -100,6 +106,17 @@ namespace {
 
 size_t n_in(const dlb_model *m) { return m->layers.front().units; }
 size_t n_out(const dlb_model *m) { return m->layers.back().units; }
+
+bool is_indrnn(const LayerRT &l) { return l.type == DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT; }
+
+// Models that run the [T, rows, n] path: more than one time step, or an IndRNN
+// layer (whose recurrence is then empty at T = 1).
+bool time_stepped(const dlb_model *m) {
+  if (m->seq_w > 1) return true;
+  for (const LayerRT &l : m->layers)
+    if (is_indrnn(l)) return true;
+  return false;
+}
 
 dlb_status dev_alloc(dlb_model *m, float **p, size_t elems, bool zero) {
   if (*p) {
@@ -153,6 +170,10 @@ dlb_status layout_parameters(dlb_model *m) {
     if (l.type == DLB_LAYER_RESIDUAL) continue;
     l.first_conn = w;
     w += l.units * l.fan_in;
+    if (l.type == DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT) {
+      l.first_recurrent = w;
+      w += l.units;
+    }
     l.last_conn = w;
   }
   m->total_weights = w;
@@ -197,9 +218,12 @@ dlb_status allocate_parameters(dlb_model *m) {
   const size_t P = m->total_parameters;
   std::vector<float> host(P, 0.f);
   if (!keep.empty()) memcpy(host.data(), keep.data(), keep.size() * sizeof(float));
-  // gamma = 1, beta = 0 (allocate.cpp L:1485-1507).
-  for (size_t i = 0; i < m->total_norm_units; ++i)
-    host[m->total_weights + m->total_bias + i] = 1.f;
+  // gamma = 1 (0.1 for an IndRNN layer), beta = 0 (allocate.cpp L:1485-1507).
+  if (m->total_norm_units)
+    for (const LayerRT &l : m->layers)
+      for (size_t i = 0; i < l.norm_units; ++i)
+        host[gamma_index(m, l) + i] =
+            l.type == DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT ? 0.1f : 1.f;
   DLB_TRY(dev_alloc(m, &m->params, P, false));
   DLB_TRY(dlb_memcpy_h2d(m->ctx, m->params, host.data(), P * sizeof(float)));
   DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
@@ -220,7 +244,7 @@ dlb_status free_batch_buffers(dlb_model *m) {
       *b = nullptr;
     }
   }
-  float **bufs[] = {&m->input, &m->input_lo, &m->target};
+  float **bufs[] = {&m->input, &m->input_lo, &m->target, &m->input_rows, &m->target_rows};
   for (float **b : bufs) {
     if (*b) DLB_TRY(dlb_free(m->ctx, *b));
     *b = nullptr;
@@ -239,8 +263,13 @@ dlb_status ensure_norm_state(dlb_model *m) {
     for (size_t i = 0; i < n; ++i) h[3 * n + i] = 1.f;  // running sigma = 1 (allocate.cpp L:1281-1284)
     DLB_TRY(dlb_memcpy_h2d(m->ctx, l.stats, h.data(), h.size() * sizeof(float)));
     DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
-    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.fwd_sums), 2 * l.norm_units * sizeof(double)));
-    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.bwd_sums), 4 * l.norm_units * sizeof(double)));
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.fwd_sums), 2 * n * sizeof(double)));
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.bwd_sums), 5 * n * sizeof(double)));
+  }
+  // An IndRNN layer without normalization still needs the per-step du sums.
+  for (auto &l : m->layers) {
+    if (l.type != DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT || l.bwd_sums) continue;
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.bwd_sums), T * l.units * sizeof(double)));
   }
   return DLB_OK;
 }
@@ -289,6 +318,10 @@ dlb_status ensure_batch(dlb_model *m, size_t rows) {
   DLB_TRY(dev_alloc(m, &m->input, T * rows * n_in(m), false));
   DLB_TRY(dev_alloc(m, &m->input_lo, T * rows * n_in(m), false));
   DLB_TRY(dev_alloc(m, &m->target, T * rows * n_out(m), false));
+  if (time_stepped(m)) {
+    DLB_TRY(dev_alloc(m, &m->input_rows, T * rows * n_in(m), false));
+    DLB_TRY(dev_alloc(m, &m->target_rows, T * rows * n_out(m), false));
+  }
   if (!m->loss_sum) {
     DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&m->loss_sum), sizeof(double)));
     DLB_TRY(dlb_memset(m->ctx, m->loss_sum, 0, sizeof(double)));
@@ -325,12 +358,37 @@ dlb_status check_supported(dlb_model *m) {
     set_error("model: compile() has not been called");
     return DLB_ERR_INVALID;
   }
-  if (m->seq_w != 1 || m->model_type != DLB_MODEL_FEEDFORWARD) {
-    set_error("model: recurrent models are outside the supported path of this build");
+  if (m->model_type != DLB_MODEL_FEEDFORWARD && m->model_type != DLB_MODEL_RECURRENT) {
+    set_error("model: model type %d is outside the supported path (FEEDFORWARD, RECURRENT)", m->model_type);
     return DLB_ERR_UNSUPPORTED;
   }
+  if (m->seq_w > 1 && m->model_type != DLB_MODEL_RECURRENT) {
+    set_error("model: seq_w %zu needs model type RECURRENT", m->seq_w);
+    return DLB_ERR_INVALID;
+  }
+  const bool stepped = time_stepped(m);
   for (size_t i = 1; i < m->layers.size(); ++i) {
     const LayerRT &l = m->layers[i];
+    if (stepped) {
+      // The time-stepped path covers stacks of IndRNN and fully connected
+      // layers with batch renormalization between them.
+      if (l.type == DLB_LAYER_RESIDUAL || l.dropout != DLB_DROPOUT_NONE) {
+        set_error("model: layer %zu: residual blocks and dropout are outside the supported path of "
+                  "time-stepped (recurrent) models", i);
+        return DLB_ERR_UNSUPPORTED;
+      }
+      if (is_indrnn(l) && (i + 1 == m->layers.size() || l.af == DLB_AF_SOFTMAX)) {
+        set_error("model: layer %zu: an IndRNN layer is a hidden layer with an element-wise activation", i);
+        return DLB_ERR_UNSUPPORTED;
+      }
+    }
+    if (is_indrnn(l)) {
+      if (!af_supported(l.af)) {
+        set_error("model: layer %zu activation %d is outside the supported set", i, l.af);
+        return DLB_ERR_UNSUPPORTED;
+      }
+      continue;
+    }
     if (l.type == DLB_LAYER_RESIDUAL) {
       const LayerRT &last = m->layers[i + l.depth];
       if (last.units != l.units) {
@@ -445,7 +503,52 @@ dlb_status forward_residual(dlb_model *m, size_t i, const float *X, const float 
                               shake ? res.sd_fwd : nullptr, res.A, res.A_lo, B, (int)res.units);
 }
 
+// Time-stepped forward, layer-major as the reference
+// (RNN__Forward_Pass_Batch__OpenMP, v1/learner/fwp_rec_mp.cpp L:29-110): one
+// GEMM over all T * rows rows of a layer, statistics for every time step in one
+// launch, then the walk over time.
+dlb_status forward_layers_time(dlb_model *m, size_t rows) {
+  DLB_TRY(refresh_weight_residuals(m));
+  const int B = (int)rows, T = (int)m->seq_w;
+  const int TB = T * B;
+  const int Bg = (int)(m->global_rows ? m->global_rows : rows);
+  const float *X = m->input, *X_lo = m->input_lo;
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    LayerRT &l = m->layers[i];
+    const int I = (int)l.fan_in, H = (int)l.units;
+    const bool norm = l.norm != DLB_NORM_NONE;
+    const bool last = i + 1 == m->layers.size();
+    const float *bias = norm ? nullptr : m->params + l.first_bias;
+    DLB_TRY(dlb_fc_forward(m->ctx, X, X_lo, m->params + l.first_conn, m->params_lo + l.first_conn,
+                           bias, l.Z, TB, I, H));
+    if (l.af == DLB_AF_SOFTMAX) {
+      DLB_TRY(dlb_softmax_forward(m->ctx, l.Z, l.A, TB, H));
+    } else if (norm || is_indrnn(l)) {
+      dlb_brn_unit_arrays u{};
+      if (norm) {
+        u = unit_arrays(m, l, 0);
+        DLB_TRY(dlb_brn_time_forward_sums(m->ctx, l.Z, T, B, H, l.fwd_sums));
+        DLB_TRY(dlb_allreduce_f64(m->ctx, l.fwd_sums, 2 * (size_t)T * H));
+        DLB_TRY(dlb_brn_time_forward_finalize(m->ctx, l.fwd_sums, Bg, T, H,
+                                              m->hp.normalization_momentum_average,
+                                              m->hp.normalization_epsilon, m->hp.brn_r_max,
+                                              m->hp.brn_d_max, &u));
+      }
+      DLB_TRY(dlb_indrnn_forward(m->ctx, l.Z, norm ? &u : nullptr,
+                                 is_indrnn(l) ? m->params + l.first_recurrent : nullptr, l.af, l.A,
+                                 last ? nullptr : l.A_lo, T, B, H));
+    } else {
+      DLB_TRY(dlb_activation_forward(m->ctx, l.Z, nullptr, l.af, nullptr, l.A, last ? nullptr : l.A_lo,
+                                     TB, H));
+    }
+    X = l.A;
+    X_lo = l.A_lo;
+  }
+  return DLB_OK;
+}
+
 dlb_status forward_layers(dlb_model *m, size_t rows) {
+  if (time_stepped(m)) return forward_layers_time(m, rows);
   DLB_TRY(refresh_weight_residuals(m));
   const int B = (int)rows;
   const float *X = m->input, *X_lo = m->input_lo;
@@ -765,6 +868,27 @@ dlb_status dlb_model_initialize_weights_with_glorot_uniform(dlb_model *m) {
     bound *= gain;
     dist.param(std::uniform_real_distribution<float>::param_type(-bound, bound));
     for (size_t k = l.first_conn; k < l.last_conn; ++k) w[k] = dist(m->weight_gen);
+    if (is_indrnn(l)) {
+      // The recurrent weights are drawn again from U(0, mag^(1/T)), mag = 2
+      // (Model::indrec_initialize_uniform, v1/learner/model.cpp L:5289-5333).
+      const float top = powf(2.f, 1.f / (float)m->seq_w);
+      dist.param(std::uniform_real_distribution<float>::param_type(-0.f, top));
+      for (size_t k = 0; k < l.units; ++k) w[l.first_recurrent + k] = dist(m->weight_gen);
+    }
+  }
+  // With the error on the last time step only, the top IndRNN layer's recurrent
+  // weights are drawn once more from U((1/mag)^(1/T), mag^(1/T)) to keep long-term
+  // memory (Model::indrec_initialize_uniform_ltm, model.cpp L:5335-5400).
+  if (m->seq_w > 1 && m->n_time_delay + 1 == m->seq_w) {
+    for (size_t i = m->layers.size() - 2; i >= 1; --i) {
+      const LayerRT &l = m->layers[i];
+      if (!is_indrnn(l)) continue;
+      const float T = (float)m->seq_w;
+      dist.param(std::uniform_real_distribution<float>::param_type(powf(1.f / 2.f, 1.f / T),
+                                                                   powf(2.f, 1.f / T)));
+      for (size_t k = 0; k < l.units; ++k) w[l.first_recurrent + k] = dist(m->weight_gen);
+      break;
+    }
   }
   DLB_TRY(dlb_memcpy_h2d(m->ctx, m->params, w.data(), w.size() * sizeof(float)));
   DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
@@ -912,6 +1036,13 @@ dlb_status dlb_model_forward_pass_device(dlb_model *m, size_t rows, const float 
   DLB_TRY(check_supported(m));
   DLB_TRY(ensure_batch(m, rows));
   const size_t n = rows * m->seq_w * n_in(m);
+  if (time_stepped(m)) {
+    // [rows, T * n_in] -> [T, rows, n_in] with the residual plane in the same pass.
+    DLB_REQUIRE(X_dev != m->input, "forward_pass_device: input aliases the model's own buffer");
+    DLB_REQUIRE(rows * m->seq_w < ((size_t)1 << 31), "forward_pass_device: rows * seq_w overflows int");
+    DLB_TRY(dlb_time_major(m->ctx, X_dev, m->input, m->input_lo, (int)rows, (int)m->seq_w, (int)n_in(m)));
+    return forward_layers(m, rows);
+  }
   if (X_dev != m->input) DLB_TRY(dlb_memcpy_d2d(m->ctx, m->input, X_dev, n * sizeof(float)));
   DLB_TRY(dlb_split_tf32(m->ctx, m->input, m->input_lo, n));
   return forward_layers(m, rows);
@@ -921,14 +1052,33 @@ dlb_status dlb_model_forward_pass(dlb_model *m, size_t rows, const float *const 
   DLB_REQUIRE(m && Xm && rows > 0, "forward_pass");
   DLB_TRY(check_supported(m));
   DLB_TRY(ensure_batch(m, rows));
-  DLB_TRY(stage_rows(m, &m->stage_x, &m->stage_x_elems, rows, m->seq_w * n_in(m), Xm, m->input));
-  return dlb_model_forward_pass_device(m, rows, m->input);
+  float *dst = time_stepped(m) ? m->input_rows : m->input;
+  DLB_TRY(stage_rows(m, &m->stage_x, &m->stage_x_elems, rows, m->seq_w * n_in(m), Xm, dst));
+  return dlb_model_forward_pass_device(m, rows, dst);
 }
 
 dlb_status dlb_model_compute_error_device(dlb_model *m, size_t rows, const float *Y_dev) {
   DLB_REQUIRE(m && Y_dev && rows > 0 && rows <= m->alloc_rows, "compute_error_device");
   LayerRT &o = m->layers.back();
   const int Bg = (int)(m->global_rows ? m->global_rows : rows);
+  if (time_stepped(m)) {
+    // The error exists for t >= n_time_delay only, each step with the divisor
+    // of one batch; earlier steps carry a zero error
+    // (compute_error_rec_mp, v1/learner/compute_error_mp.cpp L:143-265).
+    DLB_REQUIRE(Y_dev != m->target, "compute_error_device: target aliases the model's own buffer");
+    const size_t T = m->seq_w, d = m->n_time_delay, W = o.units;
+    DLB_TRY(dlb_time_major(m->ctx, Y_dev, m->target, nullptr, (int)rows, (int)T, (int)W));
+    const size_t skip = d * rows * W;
+    if (skip) {
+      DLB_TRY(dlb_memset(m->ctx, o.delta, 0, skip * sizeof(float)));
+      DLB_TRY(dlb_memset(m->ctx, o.delta_lo, 0, skip * sizeof(float)));
+    }
+    DLB_TRY(dlb_loss_delta(m->ctx, m->loss, o.af, o.Z + skip, o.A + skip, m->target + skip,
+                           o.delta + skip, o.delta_lo + skip, (int)((T - d) * rows), (int)W, Bg,
+                           m->loss_sum));
+    m->loss_rows += rows * (T - d);
+    return DLB_OK;
+  }
   DLB_TRY(dlb_loss_delta(m->ctx, m->loss, o.af, o.Z, o.A, Y_dev, o.delta, o.delta_lo, (int)rows,
                          (int)o.units, Bg, m->loss_sum));
   m->loss_rows += rows;
@@ -937,8 +1087,9 @@ dlb_status dlb_model_compute_error_device(dlb_model *m, size_t rows, const float
 
 dlb_status dlb_model_compute_error(dlb_model *m, size_t rows, const float *const *Ym) {
   DLB_REQUIRE(m && Ym && rows > 0 && rows <= m->alloc_rows, "compute_error");
-  DLB_TRY(stage_rows(m, &m->stage_y, &m->stage_y_elems, rows, m->seq_w * n_out(m), Ym, m->target));
-  return dlb_model_compute_error_device(m, rows, m->target);
+  float *dst = time_stepped(m) ? m->target_rows : m->target;
+  DLB_TRY(stage_rows(m, &m->stage_y, &m->stage_y_elems, rows, m->seq_w * n_out(m), Ym, dst));
+  return dlb_model_compute_error_device(m, rows, dst);
 }
 
 static std::vector<size_t> top_level(const dlb_model *m) {
@@ -980,10 +1131,63 @@ static dlb_status backward_residual(dlb_model *m, size_t i, int B) {
   return DLB_OK;
 }
 
+// ref: Model::RNN__Backward_Pass_Batch__OpenMP (v1/learner/bwp_rec_mp.cpp
+// L:29-110) with Backward_Pass__FC__DF_Ind_RNN__OpenMP (bwp_mp.cpp L:1188-1263)
+// and the recurrent-weight gradient of update_derivative_rec_mp.cpp L:460-487,
+// which is formed here because it shares its pass over dAF with the
+// batch-renormalization sums.
+static dlb_status backward_pass_time(dlb_model *m, size_t rows) {
+  const int B = (int)rows, T = (int)m->seq_w;
+  const int TB = T * B;
+  const int Bg = (int)(m->global_rows ? m->global_rows : rows);
+  for (size_t i = m->layers.size() - 1; i >= 1; --i) {
+    LayerRT &l = m->layers[i];
+    const int H = (int)l.units;
+    const bool norm = l.norm != DLB_NORM_NONE, rec = is_indrnn(l);
+    // Rows of this layer's error that can be non-zero.
+    size_t first_row = 0;
+    if (i + 1 == m->layers.size()) {
+      first_row = m->n_time_delay * rows;
+    } else if (norm || rec) {  // hidden layer: l.delta holds dA
+      const float *u_rec = rec ? m->params + l.first_recurrent : nullptr;
+      dlb_brn_unit_arrays u{};
+      if (norm) u = unit_arrays(m, l, 0);
+      DLB_TRY(dlb_indrnn_backward_walk(m->ctx, l.delta, l.Z, l.A, norm ? &u : nullptr, u_rec, l.af, T, B, H));
+      DLB_TRY(dlb_indrnn_backward_sums(m->ctx, l.delta, l.Z, l.A, norm ? &u : nullptr, rec ? 1 : 0, T, B,
+                                       H, l.bwd_sums));
+      const size_t plane = (size_t)T * H;
+      if (rec)
+        DLB_TRY(dlb_time_fold(m->ctx, l.bwd_sums + (norm ? 4 : 0) * plane, T, H,
+                              m->grads + l.first_recurrent));
+      if (norm) {
+        DLB_TRY(dlb_time_fold(m->ctx, l.bwd_sums, T, H, m->grads + gamma_index(m, l)));
+        DLB_TRY(dlb_time_fold(m->ctx, l.bwd_sums + plane, T, H, m->grads + beta_index(m, l)));
+        DLB_TRY(dlb_allreduce_f64(m->ctx, l.bwd_sums + 2 * plane, 2 * plane));
+        DLB_TRY(dlb_brn_time_backward_apply(m->ctx, l.delta, l.delta_lo, l.Z, &u, l.bwd_sums, Bg, T, B, H));
+      } else {
+        DLB_TRY(dlb_split_tf32(m->ctx, l.delta, l.delta_lo, (size_t)TB * H));
+      }
+    } else {
+      DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, nullptr, l.af, TB, H, nullptr));
+      DLB_TRY(dlb_split_tf32(m->ctx, l.delta, l.delta_lo, (size_t)TB * H));
+    }
+    if (i == 1) break;  // the error into the input layer is never formed
+    LayerRT &below = m->layers[i - 1];
+    const size_t I = l.fan_in;
+    if (first_row) DLB_TRY(dlb_memset(m->ctx, below.delta, 0, first_row * I * sizeof(float)));
+    if (first_row < (size_t)TB)
+      DLB_TRY(dlb_fc_backward_input(m->ctx, l.delta + first_row * H, l.delta_lo + first_row * H,
+                                    m->params + l.first_conn, m->params_lo + l.first_conn,
+                                    below.delta + first_row * I, TB - (int)first_row, (int)I, H));
+  }
+  return DLB_OK;
+}
+
 // ref: Model::FF__Backward_Pass_Batch__OpenMP (v1/learner/bwp_mp.cpp L:28-208):
 // from the output layer down; the error into the input layer is never formed.
 dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows) {
   DLB_REQUIRE(m && rows > 0 && rows <= m->alloc_rows, "backward_pass");
+  if (time_stepped(m)) return backward_pass_time(m, rows);
   const int B = (int)rows;
   const std::vector<size_t> tops = top_level(m);
   for (size_t pos = tops.size() - 1; pos >= 1; --pos) {
@@ -1022,9 +1226,33 @@ dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows) {
   return DLB_OK;
 }
 
+// ref: Model::RNN__Update_Derivative_Weight_Batch__OpenMP
+// (v1/learner/update_derivative_rec_mp.cpp L:27-167): the per-time-step rank-1
+// sums of a layer are one GEMM whose reduction runs over all T * rows rows.
+static dlb_status update_derivatives_time(dlb_model *m, size_t rows) {
+  const size_t TB = m->seq_w * rows;
+  const float *X = m->input, *X_lo = m->input_lo;
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    LayerRT &l = m->layers[i];
+    const size_t H = l.units, I = l.fan_in;
+    // The output layer's error is zero before the first step that has a target.
+    const size_t first_row = i + 1 == m->layers.size() ? m->n_time_delay * rows : 0;
+    float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
+    DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta + first_row * H, l.delta_lo + first_row * H,
+                                   X + first_row * I, X_lo + first_row * I, m->grads + l.first_conn,
+                                   dbias, (int)(TB - first_row), (int)I, (int)H, 1));
+    if (m->overlap_grad_allreduce)
+      DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
+    X = l.A;
+    X_lo = l.A_lo;
+  }
+  return DLB_OK;
+}
+
 // ref: Model::update_derivatives (v1/learner/update_derivative_fwp_mp.cpp L:27-240).
 dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows) {
   DLB_REQUIRE(m && rows > 0 && rows <= m->alloc_rows, "update_derivatives");
+  if (time_stepped(m)) return update_derivatives_time(m, rows);
   const float *top = m->input, *top_lo = m->input_lo;  // output of the top-level layer below
   for (size_t i = 1; i < m->layers.size(); ++i) {
     LayerRT &l = m->layers[i];
@@ -1083,6 +1311,14 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
                                 &m->hp.adam_previous_beta2, &k));
   DLB_TRY(dlb_optimizer_step(m->ctx, m->optimizer, &k, m->params, m->grads, m->m1, m->m2, m->m2hat,
                              nullptr, m->total_parameters));
+  // Recurrent weights of every IndRNN layer back into +-mag^(1/T), mag =
+  // clip(clip_gradient, 2, 10) = 2 with the reference's default clip_gradient of
+  // 1; every activation of the supported set is in a class that takes this
+  // bound (v1/ops/constraints/constraint.cpp L:64-95, L:245-289).
+  const float bound = powf(2.f, 1.f / (float)m->seq_w);
+  for (LayerRT &l : m->layers)
+    if (is_indrnn(l))
+      DLB_TRY(dlb_indrnn_clamp(m->ctx, m->params + l.first_recurrent, (int)l.units, -bound, bound));
   m->params_lo_valid = false;
   return DLB_OK;
 }
@@ -1135,11 +1371,13 @@ dlb_status dlb_model_train_step(dlb_model *m, size_t rows, const float *X_host,
   DLB_REQUIRE(m && X_host && Y_host && rows > 0, "train_step");
   DLB_TRY(check_supported(m));
   DLB_TRY(ensure_batch(m, rows));
-  DLB_TRY(stage_block(m, &m->stage_x, &m->stage_x_elems, rows * m->seq_w * n_in(m), X_host, m->input));
-  DLB_TRY(stage_block(m, &m->stage_y, &m->stage_y_elems, rows * m->seq_w * n_out(m), Y_host, m->target));
+  float *x_dev = time_stepped(m) ? m->input_rows : m->input;
+  float *y_dev = time_stepped(m) ? m->target_rows : m->target;
+  DLB_TRY(stage_block(m, &m->stage_x, &m->stage_x_elems, rows * m->seq_w * n_in(m), X_host, x_dev));
+  DLB_TRY(stage_block(m, &m->stage_y, &m->stage_y_elems, rows * m->seq_w * n_out(m), Y_host, y_dev));
   DLB_TRY(dlb_model_reset_loss(m));
-  DLB_TRY(dlb_model_forward_pass_device(m, rows, m->input));
-  DLB_TRY(dlb_model_compute_error_device(m, rows, m->target));
+  DLB_TRY(dlb_model_forward_pass_device(m, rows, x_dev));
+  DLB_TRY(dlb_model_compute_error_device(m, rows, y_dev));
   DLB_TRY(dlb_model_backward_pass(m, rows));
   DLB_TRY(update_and_merge_overlapped(m, rows));
   if (loss) DLB_TRY(dlb_model_get_loss(m, loss));

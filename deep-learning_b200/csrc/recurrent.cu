@@ -1,0 +1,529 @@
+// Time-batched kernels of the recurrent (IndRNN) step.  Tensors are
+// [T, rows, n] row-major: time step t, example b, unit h at ((t * rows) + b) * n
+// + h, the reference's own order (v1/learner/fwp_rec_mp.cpp L:774-775).  Batch
+// renormalization keeps statistics of its own per time step, stored [T, n]
+// (v1/learner/allocate.cpp L:1348-1356), so one launch covers all T steps
+// instead of T launches over [rows, n] slices.
+//
+//   time_major        [rows, T*n] (one example per row, as the caller holds it)
+//                     -> [T, rows, n] plus the TF32 residual plane
+//   time_reduce       per (t, unit) sums over the rows: statistics forward,
+//                     the four batch-renormalization sums and du backward
+//   time_forward      normalise, add u * h_{t-1}, activate: a thread owns
+//                     (b, 4 units) and walks t = 0..T-1 with h in registers
+//   time_backward     the reverse walk: dAF_t = dA_t f'_t + u f'_t dAF_{t+1}
+//   time_apply        batch-renormalization backward apply for all t
+//
+// All are HBM-bound streaming kernels with 128-bit accesses when n % 4 == 0.
+#include "common.cuh"
+#include "math.cuh"
+
+namespace dlb {
+
+namespace {
+
+constexpr int TR_LANES_X = 32;
+constexpr int TR_LANES_Y = 8;
+
+template <int W>
+struct Vec {
+  float v[W];
+};
+template <int W>
+__device__ __forceinline__ Vec<W> ldv(const float *p) {
+  Vec<W> r;
+  if constexpr (W == 4) {
+    const float4 q = *reinterpret_cast<const float4 *>(p);
+    r.v[0] = q.x; r.v[1] = q.y; r.v[2] = q.z; r.v[3] = q.w;
+  } else {
+    r.v[0] = *p;
+  }
+  return r;
+}
+template <int W>
+__device__ __forceinline__ void stv(float *p, const Vec<W> &x) {
+  if constexpr (W == 4) *reinterpret_cast<float4 *>(p) = make_float4(x.v[0], x.v[1], x.v[2], x.v[3]);
+  else *p = x.v[0];
+}
+
+// Per-(t, unit) constants of batch renormalization.
+struct TimeBrn {
+  const float *mean, *sigma, *r, *d;  // [T, n]
+  const float *gamma, *beta;          // [n]
+};
+static TimeBrn time_brn(const dlb_brn_unit_arrays *u) {
+  return TimeBrn{u->mean, u->sigma, u->r, u->d, u->gamma, u->beta};
+}
+
+// value_hat and value_normalize of v1/learner/fwp_mp.cpp L:4732-4736.
+__device__ __forceinline__ float hat(float z, float mean, float sigma, float r, float d) {
+  return (z - mean) / sigma * r + d;
+}
+
+// pre_t = y_t + u * h_{t-1}; the forward and the backward walk use this one
+// expression so that both see the same bits on either side of a derivative kink.
+__device__ __forceinline__ float recur(float y, float u, float h_prev) { return __fmaf_rn(u, h_prev, y); }
+
+// ---------------------------------------------------------------------------
+template <int W>
+__global__ void time_major_kernel(const float *__restrict__ x, float *__restrict__ out,
+                                  float *__restrict__ out_lo, int rows, int T, int n) {
+  const int nw = n / W;
+  const size_t total = (size_t)T * rows * nw;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int c = (int)(i % nw) * W;
+    const size_t tb = i / nw;
+    const int b = (int)(tb % rows), t = (int)(tb / rows);
+    const Vec<W> v = ldv<W>(x + ((size_t)b * T + t) * n + c);
+    stv<W>(out + i * W, v);
+    if (out_lo) {
+      Vec<W> lo;
+#pragma unroll
+      for (int j = 0; j < W; ++j) lo.v[j] = tf32_lo(v.v[j]);
+      stv<W>(out_lo + i * W, lo);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Reductions over the rows for every (t, unit).  Grid (column blocks, T); a
+// block of 32 x 8 threads covers 32*W units, each thread walks rows b = ty,
+// ty+8, ... in float, the 8 row lanes fold in double in a fixed order.
+// sums[(s * T + t) * n + h].
+// ---------------------------------------------------------------------------
+template <int NSUM, int W, class Op>
+__global__ void __launch_bounds__(TR_LANES_X *TR_LANES_Y)
+    time_reduce_kernel(Op op, int T, int rows, int n, double *__restrict__ sums) {
+  __shared__ double red[TR_LANES_Y][NSUM][TR_LANES_X * W + 1];
+  const int tx = threadIdx.x % TR_LANES_X, ty = threadIdx.x / TR_LANES_X;
+  const int col = (blockIdx.x * TR_LANES_X + tx) * W;
+  const int t = blockIdx.y;
+  float acc[NSUM][W];
+#pragma unroll
+  for (int s = 0; s < NSUM; ++s)
+#pragma unroll
+    for (int j = 0; j < W; ++j) acc[s][j] = 0.f;
+  if (col < n) {
+    typename Op::template Cols<W> k;
+    op.template load<W>(t, col, n, k);
+    for (int b = ty; b < rows; b += TR_LANES_Y)
+      op.template row<W>(t, ((size_t)t * rows + b) * n + col, (size_t)rows * n, k, acc);
+  }
+#pragma unroll
+  for (int s = 0; s < NSUM; ++s)
+#pragma unroll
+    for (int j = 0; j < W; ++j) red[ty][s][tx * W + j] = (double)acc[s][j];
+  __syncthreads();
+  for (int i = threadIdx.x; i < NSUM * TR_LANES_X * W; i += TR_LANES_X * TR_LANES_Y) {
+    const int s = i / (TR_LANES_X * W), c = i % (TR_LANES_X * W);
+    const int gc = blockIdx.x * TR_LANES_X * W + c;
+    if (gc < n) {
+      double v = 0.0;
+#pragma unroll
+      for (int y = 0; y < TR_LANES_Y; ++y) v += red[y][s][c];
+      sums[((size_t)s * T + t) * n + gc] = v;
+    }
+  }
+}
+
+struct TimeSumSqOp {
+  const float *Z;
+  template <int W> struct Cols {};
+  template <int W> __device__ void load(int, int, int, Cols<W> &) const {}
+  template <int W>
+  __device__ void row(int, size_t o, size_t, const Cols<W> &, float (&acc)[2][W]) const {
+    const Vec<W> z = ldv<W>(Z + o);
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      acc[0][j] += z.v[j];
+      acc[1][j] += z.v[j] * z.v[j];
+    }
+  }
+};
+
+// Backward sums over dAF (the error w.r.t. the normalised value):
+//   NORM: s0 = sum e x_hat, s1 = sum e, s2 = sum e gamma (-r / sigma),
+//         s3 = sum e gamma (z - mean) (-r / sigma^2)   (bwp_mp.cpp L:1559-1574)
+//   REC:  last sum = sum h_{t-1} e for t >= 1   (update_derivative_rec_mp.cpp L:460-487)
+template <bool NORM, bool REC>
+struct TimeBackwardOp {
+  const float *E, *Z, *A;
+  TimeBrn u;
+  static constexpr int NS = (NORM ? 4 : 0) + (REC ? 1 : 0);
+  template <int W>
+  struct Cols {
+    float mean[W], sigma[W], r[W], d[W], gamma[W], q_mean[W], q_sigma[W];
+  };
+  template <int W>
+  __device__ void load(int t, int col, int n, Cols<W> &k) const {
+    if constexpr (NORM) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      const size_t i = (size_t)t * n + col + j;
+      k.mean[j] = u.mean[i];
+      k.sigma[j] = u.sigma[i];
+      k.r[j] = u.r[i];
+      k.d[j] = u.d[i];
+      k.gamma[j] = u.gamma[col + j];
+      const float neg_r = -k.r[j];
+      k.q_mean[j] = neg_r / k.sigma[j];
+      k.q_sigma[j] = neg_r / (k.sigma[j] * k.sigma[j]);
+    }
+    }
+  }
+  template <int W>
+  __device__ void row(int t, size_t o, size_t step, const Cols<W> &k, float (&acc)[NS][W]) const {
+    const Vec<W> e = ldv<W>(E + o);
+    if (NORM) {
+      const Vec<W> z = ldv<W>(Z + o);
+#pragma unroll
+      for (int j = 0; j < W; ++j) {
+        const float xh = hat(z.v[j], k.mean[j], k.sigma[j], k.r[j], k.d[j]);
+        acc[0][j] += e.v[j] * xh;
+        acc[1][j] += e.v[j];
+        const float eh = e.v[j] * k.gamma[j];
+        acc[2][j] += eh * k.q_mean[j];
+        acc[3][j] += eh * (z.v[j] - k.mean[j]) * k.q_sigma[j];
+      }
+    }
+    if (REC && t > 0) {
+      const Vec<W> hp = ldv<W>(A + o - step);
+#pragma unroll
+      for (int j = 0; j < W; ++j) acc[NS - 1][j] += hp.v[j] * e.v[j];
+    }
+  }
+};
+
+// mean, sigma, running averages, r and d for every (t, unit), in the order of
+// v1/learner/fwp_mp.cpp L:4688-4717 (the averages move first).
+__global__ void time_finalize_kernel(const double *__restrict__ sums, int T, int n, float batch_scale,
+                                     float momentum, float eps, float r_max, float d_max,
+                                     dlb_brn_unit_arrays u) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t total = (size_t)T * n;
+  if (i >= total) return;
+  const float mean = (float)sums[i] * batch_scale;
+  float mavg = u.mean_average[i];
+  mavg += momentum * (mean - mavg);
+  const float sigma = sqrtf((float)sums[total + i] * batch_scale - mean * mean + eps);
+  float savg = u.sigma_average[i];
+  savg += momentum * (sigma - savg);
+  u.mean[i] = mean;
+  u.sigma[i] = sigma;
+  u.mean_average[i] = mavg;
+  u.sigma_average[i] = savg;
+  u.r[i] = clipf(sigma / savg, 1.f / r_max, r_max);
+  u.d[i] = clipf((mean - mavg) / savg, -d_max, d_max);
+}
+
+// out[h] (+)= sum over t (from T-1 down, the backward order) of sums[t, h].
+__global__ void time_fold_kernel(const double *__restrict__ sums, int T, int n, float *out) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= n) return;
+  double v = 0.0;
+  for (int t = T - 1; t >= 0; --t) v += sums[(size_t)t * n + h];
+  out[h] += (float)v;
+}
+
+// y_t = gamma * x_hat + beta for the units a thread owns, statistics of step t.
+template <int W>
+__device__ __forceinline__ Vec<W> normalised(const Vec<W> &z, const TimeBrn &u, size_t stat,
+                                             const float (&gamma)[W], const float (&beta)[W]) {
+  const Vec<W> mean = ldv<W>(u.mean + stat), sigma = ldv<W>(u.sigma + stat), r = ldv<W>(u.r + stat),
+               d = ldv<W>(u.d + stat);
+  Vec<W> y;
+#pragma unroll
+  for (int j = 0; j < W; ++j)
+    y.v[j] = __fmaf_rn(gamma[j], hat(z.v[j], mean.v[j], sigma.v[j], r.v[j], d.v[j]), beta[j]);
+  return y;
+}
+
+// Forward walk over time.  One thread per (example, W units); h stays in
+// registers from one step to the next, and the loads of step t + 1 do not
+// depend on step t, so the compiler can issue them ahead of the dependent math.
+// ref: Forward_Pass__FC_Ind_RNN__OpenMP (v1/learner/fwp_rec_mp.cpp L:762-800)
+// followed by the activation (L:335-348).
+template <int W, bool NORM, bool REC>
+__global__ void __launch_bounds__(256)
+    time_forward_kernel(const float *__restrict__ Z, TimeBrn u, const float *__restrict__ rec, int af,
+                        float *__restrict__ A, float *__restrict__ A_lo, int T, int rows, int n) {
+  const int nw = n / W;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * nw) return;
+  const int col = (int)(i % nw) * W;
+  const size_t step = (size_t)rows * n;
+  size_t o = (i / nw) * n + col;
+  float gamma[W], beta[W], w[W], h[W];
+#pragma unroll
+  for (int j = 0; j < W; ++j) {
+    gamma[j] = NORM ? u.gamma[col + j] : 1.f;
+    beta[j] = NORM ? u.beta[col + j] : 0.f;
+    w[j] = REC ? rec[col + j] : 0.f;
+    h[j] = 0.f;
+  }
+#pragma unroll 4
+  for (int t = 0; t < T; ++t, o += step) {
+    Vec<W> y = ldv<W>(Z + o);
+    if (NORM) y = normalised<W>(y, u, (size_t)t * n + col, gamma, beta);
+    Vec<W> out, lo;
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      const float pre = (REC && t > 0) ? recur(y.v[j], w[j], h[j]) : y.v[j];
+      h[j] = af_fire(af, pre);
+      out.v[j] = h[j];
+      lo.v[j] = tf32_lo(h[j]);
+    }
+    stv<W>(A + o, out);
+    if (A_lo) stv<W>(A_lo + o, lo);
+  }
+}
+
+// Reverse walk: E holds dA on entry and dAF on return.
+// ref: Backward_Pass__FC__DF_Ind_RNN__OpenMP (v1/learner/bwp_mp.cpp L:1188-1263).
+// pre_t is recomputed from Z, the statistics and h_{t-1} with the forward
+// walk's own expressions instead of being stored.
+template <int W, bool NORM, bool REC>
+__global__ void __launch_bounds__(256)
+    time_backward_kernel(float *__restrict__ E, const float *__restrict__ Z,
+                         const float *__restrict__ A, TimeBrn u, const float *__restrict__ rec, int af,
+                         int T, int rows, int n) {
+  const int nw = n / W;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * nw) return;
+  const int col = (int)(i % nw) * W;
+  const size_t step = (size_t)rows * n;
+  size_t o = (i / nw) * n + col + (size_t)(T - 1) * step;
+  float gamma[W], beta[W], w[W], next[W];
+#pragma unroll
+  for (int j = 0; j < W; ++j) {
+    gamma[j] = NORM ? u.gamma[col + j] : 1.f;
+    beta[j] = NORM ? u.beta[col + j] : 0.f;
+    w[j] = REC ? rec[col + j] : 0.f;
+    next[j] = 0.f;
+  }
+  Vec<W> h = ldv<W>(A + o);
+#pragma unroll 4
+  for (int t = T - 1; t >= 0; --t, o -= step) {
+    const Vec<W> da = ldv<W>(E + o);
+    Vec<W> y = ldv<W>(Z + o);
+    if (NORM) y = normalised<W>(y, u, (size_t)t * n + col, gamma, beta);
+    Vec<W> hp;
+    if (t > 0) hp = ldv<W>(A + o - step);
+    Vec<W> e;
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      const float pre = (REC && t > 0) ? recur(y.v[j], w[j], hp.v[j]) : y.v[j];
+      const float fp = af_derive(af, pre, h.v[j]);
+      const float d = da.v[j] * fp;
+      e.v[j] = (REC && t + 1 != T) ? d + w[j] * fp * next[j] : d;
+      next[j] = e.v[j];
+    }
+    stv<W>(E + o, e);
+    if (t > 0) h = hp;
+  }
+}
+
+// Batch-renormalization backward apply for every t (bwp_mp.cpp L:1608-1621).
+// Grid (column blocks, T), rows walked with stride 8.
+template <int W>
+__global__ void __launch_bounds__(TR_LANES_X *TR_LANES_Y)
+    time_apply_kernel(float *__restrict__ delta, float *__restrict__ delta_lo,
+                      const float *__restrict__ Z, TimeBrn u, const double *__restrict__ sums,
+                      float inv_rows, float rows_f, int T, int rows, int n) {
+  const int tx = threadIdx.x % TR_LANES_X, ty = threadIdx.x / TR_LANES_X;
+  const int col = (blockIdx.x * TR_LANES_X + tx) * W;
+  const int t = blockIdx.y;
+  if (col >= n) return;
+  float gamma[W], mean[W], r_over_sigma[W], n_sigma[W], d_sigma[W], d_mean_n[W];
+#pragma unroll
+  for (int j = 0; j < W; ++j) {
+    const size_t s = (size_t)t * n + col + j;
+    const float sigma = u.sigma[s];
+    gamma[j] = u.gamma[col + j];
+    mean[j] = u.mean[s];
+    r_over_sigma[j] = u.r[s] / sigma;
+    n_sigma[j] = rows_f * sigma;
+    d_mean_n[j] = (float)sums[((size_t)2 * T + t) * n + col + j] * inv_rows;
+    d_sigma[j] = (float)sums[((size_t)3 * T + t) * n + col + j];
+  }
+  for (int b = ty; b < rows; b += TR_LANES_Y) {
+    const size_t o = ((size_t)t * rows + b) * n + col;
+    const Vec<W> e = ldv<W>(delta + o), z = ldv<W>(Z + o);
+    Vec<W> out, lo;
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      float v = e.v[j] * gamma[j];
+      v *= r_over_sigma[j];
+      v += d_sigma[j] * ((z.v[j] - mean[j]) / n_sigma[j]);
+      v += d_mean_n[j];
+      out.v[j] = v;
+      lo.v[j] = tf32_lo(v);
+    }
+    stv<W>(delta + o, out);
+    if (delta_lo) stv<W>(delta_lo + o, lo);
+  }
+}
+
+__global__ void clamp_kernel(float *p, int n, float lo, float hi) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = clipf(p[i], lo, hi);
+}
+
+bool aligned16(std::initializer_list<const void *> ps) {
+  for (const void *p : ps)
+    if (reinterpret_cast<uintptr_t>(p) & 15) return false;
+  return true;
+}
+
+int walk_grid(size_t threads) { return (int)((threads + 255) / 256); }
+
+}  // namespace
+}  // namespace dlb
+
+using namespace dlb;
+
+extern "C" {
+
+dlb_status dlb_time_major(dlb_ctx *ctx, const float *x, float *out, float *out_lo, int rows,
+                          int seq_w, int n) {
+  DLB_REQUIRE(ctx && x && out && rows > 0 && seq_w > 0 && n > 0, "dlb_time_major");
+  const bool v4 = n % 4 == 0 && aligned16({x, out, out_lo});
+  const size_t items = (size_t)seq_w * rows * (v4 ? n / 4 : n);
+  const int grid = (int)min((items + 255) / 256, (size_t)ctx->sm_count * 16);
+  if (v4) time_major_kernel<4><<<grid, 256, 0, ctx->stream>>>(x, out, out_lo, rows, seq_w, n);
+  else time_major_kernel<1><<<grid, 256, 0, ctx->stream>>>(x, out, out_lo, rows, seq_w, n);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_brn_time_forward_sums(dlb_ctx *ctx, const float *Z, int seq_w, int rows, int n,
+                                     double *sums) {
+  DLB_REQUIRE(ctx && Z && sums && seq_w > 0 && rows > 0 && n > 0, "dlb_brn_time_forward_sums");
+  const bool v4 = n % 4 == 0 && aligned16({Z});
+  const dim3 grid(ceil_div(n, TR_LANES_X * (v4 ? 4 : 1)), seq_w);
+  if (v4)
+    time_reduce_kernel<2, 4, TimeSumSqOp><<<grid, TR_LANES_X * TR_LANES_Y, 0, ctx->stream>>>(
+        TimeSumSqOp{Z}, seq_w, rows, n, sums);
+  else
+    time_reduce_kernel<2, 1, TimeSumSqOp><<<grid, TR_LANES_X * TR_LANES_Y, 0, ctx->stream>>>(
+        TimeSumSqOp{Z}, seq_w, rows, n, sums);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_brn_time_forward_finalize(dlb_ctx *ctx, const double *sums, int global_rows,
+                                         int seq_w, int n, float momentum, float epsilon,
+                                         float r_max, float d_max, const dlb_brn_unit_arrays *u) {
+  DLB_REQUIRE(ctx && sums && u && global_rows > 0 && seq_w > 0 && n > 0, "dlb_brn_time_forward_finalize");
+  DLB_REQUIRE(u->mean && u->sigma && u->mean_average && u->sigma_average && u->r && u->d,
+              "dlb_brn_time_forward_finalize: null unit array");
+  const size_t total = (size_t)seq_w * n;
+  time_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
+      sums, seq_w, n, 1.f / (float)global_rows, momentum, epsilon, r_max, d_max, *u);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_indrnn_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
+                              const float *recurrent, int af, float *A, float *A_lo, int seq_w,
+                              int rows, int n) {
+  DLB_REQUIRE(ctx && Z && A && seq_w > 0 && rows > 0 && n > 0, "dlb_indrnn_forward");
+  TimeBrn p{};
+  if (u) p = time_brn(u);
+  const bool v4 = n % 4 == 0 && aligned16({Z, A, A_lo, p.mean, p.sigma, p.r, p.d});
+  const int grid = walk_grid((size_t)rows * (v4 ? n / 4 : n));
+#define LAUNCH(W, NORM, REC)                                                               \
+  time_forward_kernel<W, NORM, REC><<<grid, 256, 0, ctx->stream>>>(Z, p, recurrent, af, A, A_lo, \
+                                                                   seq_w, rows, n)
+#define PICK(W)                                                        \
+  do {                                                                 \
+    if (u && recurrent) LAUNCH(W, true, true);                         \
+    else if (u) LAUNCH(W, true, false);                                \
+    else if (recurrent) LAUNCH(W, false, true);                        \
+    else LAUNCH(W, false, false);                                      \
+  } while (0)
+  if (v4) PICK(4); else PICK(1);
+#undef LAUNCH
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_indrnn_backward_walk(dlb_ctx *ctx, float *E, const float *Z, const float *A,
+                                    const dlb_brn_unit_arrays *u, const float *recurrent, int af,
+                                    int seq_w, int rows, int n) {
+  DLB_REQUIRE(ctx && E && Z && A && seq_w > 0 && rows > 0 && n > 0, "dlb_indrnn_backward_walk");
+  TimeBrn p{};
+  if (u) p = time_brn(u);
+  const bool v4 = n % 4 == 0 && aligned16({E, Z, A, p.mean, p.sigma, p.r, p.d});
+  const int grid = walk_grid((size_t)rows * (v4 ? n / 4 : n));
+#define LAUNCH(W, NORM, REC)                                                                 \
+  time_backward_kernel<W, NORM, REC><<<grid, 256, 0, ctx->stream>>>(E, Z, A, p, recurrent, af, \
+                                                                    seq_w, rows, n)
+  if (v4) PICK(4); else PICK(1);
+#undef LAUNCH
+#undef PICK
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_indrnn_backward_sums(dlb_ctx *ctx, const float *E, const float *Z, const float *A,
+                                    const dlb_brn_unit_arrays *u, int recurrent, int seq_w,
+                                    int rows, int n, double *sums) {
+  DLB_REQUIRE(ctx && E && sums && seq_w > 0 && rows > 0 && n > 0 && (u || recurrent),
+              "dlb_indrnn_backward_sums");
+  DLB_REQUIRE((!u || Z) && (!recurrent || A), "dlb_indrnn_backward_sums: missing tensor");
+  TimeBrn p{};
+  if (u) p = time_brn(u);
+  const bool v4 = n % 4 == 0 && aligned16({E, Z, A});
+  const dim3 grid(ceil_div(n, TR_LANES_X * (v4 ? 4 : 1)), seq_w);
+  const int threads = TR_LANES_X * TR_LANES_Y;
+#define LAUNCH(W, NORM, REC)                                                                  \
+  time_reduce_kernel<TimeBackwardOp<NORM, REC>::NS, W, TimeBackwardOp<NORM, REC>>             \
+      <<<grid, threads, 0, ctx->stream>>>(TimeBackwardOp<NORM, REC>{E, Z, A, p}, seq_w, rows, n, sums)
+#define PICK(W)                                           \
+  do {                                                    \
+    if (u && recurrent) LAUNCH(W, true, true);            \
+    else if (u) LAUNCH(W, true, false);                   \
+    else LAUNCH(W, false, true);                          \
+  } while (0)
+  if (v4) PICK(4); else PICK(1);
+#undef LAUNCH
+#undef PICK
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_time_fold(dlb_ctx *ctx, const double *sums, int seq_w, int n, float *out) {
+  DLB_REQUIRE(ctx && sums && out && seq_w > 0 && n > 0, "dlb_time_fold");
+  time_fold_kernel<<<ceil_div(n, 256), 256, 0, ctx->stream>>>(sums, seq_w, n, out);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_brn_time_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
+                                       const dlb_brn_unit_arrays *u, const double *sums,
+                                       int global_rows, int seq_w, int rows, int n) {
+  DLB_REQUIRE(ctx && delta && Z && u && sums && global_rows > 0 && seq_w > 0 && rows > 0 && n > 0,
+              "dlb_brn_time_backward_apply");
+  const bool v4 = n % 4 == 0 && aligned16({delta, delta_lo, Z});
+  const dim3 grid(ceil_div(n, TR_LANES_X * (v4 ? 4 : 1)), seq_w);
+  const float nf = (float)global_rows;
+  if (v4)
+    time_apply_kernel<4><<<grid, TR_LANES_X * TR_LANES_Y, 0, ctx->stream>>>(
+        delta, delta_lo, Z, time_brn(u), sums, 1.f / nf, nf, seq_w, rows, n);
+  else
+    time_apply_kernel<1><<<grid, TR_LANES_X * TR_LANES_Y, 0, ctx->stream>>>(
+        delta, delta_lo, Z, time_brn(u), sums, 1.f / nf, nf, seq_w, rows, n);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+dlb_status dlb_indrnn_clamp(dlb_ctx *ctx, float *recurrent, int n, float lo, float hi) {
+  DLB_REQUIRE(ctx && recurrent && n > 0 && lo <= hi, "dlb_indrnn_clamp");
+  clamp_kernel<<<ceil_div(n, 256), 256, 0, ctx->stream>>>(recurrent, n, lo, hi);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+}  // extern "C"

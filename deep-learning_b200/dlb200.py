@@ -72,6 +72,15 @@ SIGNATURES = {
     "dlb_residual_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "dlb_shakedrop_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "dlb_model_set_shakedrop_noise": (_i, [_vp, _sz, _vp, _vp, _vp, _sz]),
+    "dlb_time_major": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
+    "dlb_brn_time_forward_sums": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "dlb_brn_time_forward_finalize": (_i, [_vp, _vp, _i, _i, _i, _f, _f, _f, _f, C.POINTER(BrnUnitArrays)]),
+    "dlb_indrnn_forward": (_i, [_vp, _vp, C.POINTER(BrnUnitArrays), _vp, _i, _vp, _vp, _i, _i, _i]),
+    "dlb_indrnn_backward_walk": (_i, [_vp, _vp, _vp, _vp, C.POINTER(BrnUnitArrays), _vp, _i, _i, _i, _i]),
+    "dlb_indrnn_backward_sums": (_i, [_vp, _vp, _vp, _vp, C.POINTER(BrnUnitArrays), _i, _i, _i, _i, _vp]),
+    "dlb_time_fold": (_i, [_vp, _vp, _i, _i, _vp]),
+    "dlb_brn_time_backward_apply": (_i, [_vp, _vp, _vp, _vp, C.POINTER(BrnUnitArrays), _vp, _i, _i, _i, _i]),
+    "dlb_indrnn_clamp": (_i, [_vp, _vp, _i, _f, _f]),
     "dlb_loss_delta":(_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "dlb_optimizer_step": (_i, [_vp, _i, C.POINTER(OptimizerScalars), _vp, _vp, _vp, _vp, _vp, _vp, _sz]),
     "dlb_optimizer_prepare": (_i, [_i, C.POINTER(_f), C.POINTER(_f), C.POINTER(_f), C.POINTER(OptimizerScalars)]),

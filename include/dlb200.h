@@ -254,6 +254,69 @@ dlb_status dlb_shakedrop_backward(dlb_ctx *ctx, const float *d, const uint8_t *r
                                   int width);
 
 /* ------------------------------------------------------------------------ */
+/* Recurrent (IndRNN) step.  Tensors are [seq_w, rows, n] row-major, the
+ * reference's order (time step, example, unit: v1/learner/fwp_rec_mp.cpp
+ * L:774-775).  With batch renormalization every time step has statistics of
+ * its own: the six arrays of dlb_brn_unit_arrays then address seq_w * n floats
+ * ([seq_w, n], v1/learner/allocate.cpp L:1348-1356), gamma and beta n floats.
+ * Per-(t, unit) sums are laid out sums[(s * seq_w + t) * n + h]. */
+
+/* [rows, seq_w * n] (one example per row, as the reference's callers hold
+ * their data) -> [seq_w, rows, n]; out_lo optional.  Replaces the per-example
+ * copy of Model::assign_inputs_rec_mp (v1/learner/assign_inputs.cpp L:199-225). */
+dlb_status dlb_time_major(dlb_ctx *ctx, const float *x, float *out, float *out_lo, int rows,
+                          int seq_w, int n);
+
+/* s = 0: sum_b Z, s = 1: sum_b Z^2 for every (t, unit), in double.
+ * ref: Forward_Pass__Batch_Renormalization__Training__OpenMP, reached once per
+ * time step from Recurrent__Forward_Pass__FC__OpenMP (v1/learner/fwp_rec_mp.cpp
+ * L:335-348; the sums loop is fwp_mp.cpp L:4647-4663). */
+dlb_status dlb_brn_time_forward_sums(dlb_ctx *ctx, const float *Z, int seq_w, int rows, int n,
+                                     double *sums);
+/* dlb_brn_forward_finalize for all time steps at once. */
+dlb_status dlb_brn_time_forward_finalize(dlb_ctx *ctx, const double *sums, int global_rows,
+                                         int seq_w, int n, float momentum, float epsilon,
+                                         float r_max, float d_max, const dlb_brn_unit_arrays *u);
+
+/* y_t = batch-renormalised Z_t (u != NULL) or Z_t; pre_t = y_t + recurrent *
+ * A_{t-1} (t = 0, or recurrent == NULL: pre_t = y_t); A_t = f(pre_t).
+ * ref: Forward_Pass__FC_Ind_RNN__OpenMP (v1/learner/fwp_rec_mp.cpp L:762-800)
+ * and the activation that follows it (L:335-348). */
+dlb_status dlb_indrnn_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
+                              const float *recurrent, int af, float *A, float *A_lo, int seq_w,
+                              int rows, int n);
+
+/* E holds dA on entry and dAF on return, t from seq_w-1 down to 0:
+ *   f'_t = f'(pre_t, A_t), dAF_t = dA_t f'_t + recurrent f'_t dAF_{t+1}.
+ * ref: Backward_Pass__FC__DF_Ind_RNN__OpenMP (v1/learner/bwp_mp.cpp L:1188-1263). */
+dlb_status dlb_indrnn_backward_walk(dlb_ctx *ctx, float *E, const float *Z, const float *A,
+                                    const dlb_brn_unit_arrays *u, const float *recurrent, int af,
+                                    int seq_w, int rows, int n);
+
+/* Per-(t, unit) sums over dAF.  With u != NULL, s = 0..3 are d_gamma, d_beta,
+ * d_mean, d_sigma of the batch renormalization backward (bwp_mp.cpp
+ * L:1543-1578); with recurrent != 0 the last s is sum_b A_{t-1} dAF_t (0 at
+ * t = 0), the recurrent-weight gradient of that time step
+ * (Update_Derivative_Weight__FC_Ind_RNN__OpenMP,
+ * v1/learner/update_derivative_rec_mp.cpp L:460-487). */
+dlb_status dlb_indrnn_backward_sums(dlb_ctx *ctx, const float *E, const float *Z, const float *A,
+                                    const dlb_brn_unit_arrays *u, int recurrent, int seq_w,
+                                    int rows, int n, double *sums);
+/* out[h] += sum_t sums[t * n + h], t from seq_w-1 down to 0. */
+dlb_status dlb_time_fold(dlb_ctx *ctx, const double *sums, int seq_w, int n, float *out);
+
+/* dlb_brn_backward_apply for all time steps at once; sums as written by
+ * dlb_indrnn_backward_sums (s = 2, 3 already summed over the ranks). */
+dlb_status dlb_brn_time_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
+                                       const dlb_brn_unit_arrays *u, const double *sums,
+                                       int global_rows, int seq_w, int rows, int n);
+
+/* recurrent[h] = clip(recurrent[h], lo, hi).
+ * ref: Model::Update_Weight_Regularization__Constraint_Recurrent_Weight
+ * (v1/ops/constraints/constraint.cpp L:245-289). */
+dlb_status dlb_indrnn_clamp(dlb_ctx *ctx, float *recurrent, int n, float lo, float hi);
+
+/* ------------------------------------------------------------------------ */
 /* Output error and loss.
  * MSE: delta = f'(pre, q) * 2 (q - y) / (global_rows * n_out); loss += (q-y)^2.
  * Cross-entropy on a softmax layer: delta_j = sum_k (q_j [j==k] - q_k q_j) L'_k,

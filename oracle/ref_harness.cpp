@@ -296,7 +296,9 @@ static int layer_norm_io(ref_model m, size_t layer, const char *name,
   bool const per_t = !(nm == "scale" || nm == "shift");
   size_t const T = per_t ? h->model.seq_w : 1;
   if (n != T * units) return -1;
-  size_t const stride = h->model.total_normalized_units_allocated;
+  /* A layer's statistics are [T][units of the layer], the unit's own pointer
+   * addressing t = 0 (v1/learner/allocate.cpp L:1348-1356). */
+  size_t const stride = units;
   for (size_t u = 0; u < units; ++u) {
     real *p = norm_field(l->ptr_array_normalized_units[u].normalized_batch_units,
                          nm);

@@ -2,7 +2,7 @@
 from the reference library's own code (oracle/_ref/libdlref.so, built by
 `make -C oracle` where the reference sources are present).
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [fixture names]
 
 Each fixture is a small .npz holding the seeded inputs, targets, dropout masks
 and initial parameters of one workload and what the reference produced from
@@ -49,6 +49,35 @@ def noisy_cases():
     }
 
 
+def recurrent_cases():
+    """Time-stepped (IndRNN) workloads: name -> (config, steps)."""
+    rnn = configs.indrnn_stack
+    all_steps = rnn(n_in=9, hidden=14, depth=2, n_out=5, seq_w=6, batch=7, af=ACTIVATION.LEAKY_RELU,
+                    optimizer=OPTIMIZER.ADAM, norm=False)
+    all_steps["time_delays"] = 0  # an error on every time step
+    all_steps["name"] += "_alltimes"
+    return {
+        "indrnn_relu_brn_adabound": (rnn(n_in=10, hidden=16, depth=2, n_out=6, seq_w=12, batch=8), 12),
+        "indrnn_lrelu_nonorm_adam_alltimes": (all_steps, 12),
+    }
+
+
+def make_plain(name, cfg, steps):
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    configs.set_recurrent_uniform(ref, cfg)
+    p0 = ref.get_array("parameters")
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    out = util.trace(ref, cfg, steps=steps, X=X, Y=Y, masks=masks)
+    blob = {"in_X": X, "in_Y": Y, "in_params": p0, "steps": np.int64(steps)}
+    for li, mk in masks.items():
+        blob[f"in_mask{li}"] = mk
+    blob.update({f"out_{k}": v for k, v in out.items()})
+    path = os.path.join(HERE, name + ".npz")
+    np.savez_compressed(path, **blob)
+    print(f"{name}: {os.path.getsize(path)} bytes, loss {out['losses'][0]:.6f} -> {out['losses'][-1]:.6f}")
+
+
 def make_noisy(name, cfg, steps):
     ref = util.build(ref_binding.RefModel(), cfg, seed=0)
     p0 = ref.get_array("parameters")
@@ -67,23 +96,16 @@ def make_noisy(name, cfg, steps):
 
 
 def main():
+    """With arguments, regenerates only the named fixtures."""
     if not ref_binding.available():
         sys.exit("oracle/_ref/libdlref.so is missing: run `make -C oracle` where the reference sources are")
-    for name, (cfg, steps) in cases().items():
-        ref = util.build(ref_binding.RefModel(), cfg, seed=0)
-        p0 = ref.get_array("parameters")
-        X, Y = configs.synthetic_batch(cfg)
-        masks = configs.dropout_masks(cfg)
-        out = util.trace(ref, cfg, steps=steps, X=X, Y=Y, masks=masks)
-        blob = {"in_X": X, "in_Y": Y, "in_params": p0, "steps": np.int64(steps)}
-        for li, mk in masks.items():
-            blob[f"in_mask{li}"] = mk
-        blob.update({f"out_{k}": v for k, v in out.items()})
-        path = os.path.join(HERE, name + ".npz")
-        np.savez_compressed(path, **blob)
-        print(f"{name}: {os.path.getsize(path)} bytes, loss {out['losses'][0]:.6f} -> {out['losses'][-1]:.6f}")
+    only = set(sys.argv[1:])
+    for name, (cfg, steps) in {**cases(), **recurrent_cases()}.items():
+        if not only or name in only:
+            make_plain(name, cfg, steps)
     for name, (cfg, steps) in noisy_cases().items():
-        make_noisy(name, cfg, steps)
+        if not only or name in only:
+            make_noisy(name, cfg, steps)
 
 
 if __name__ == "__main__":

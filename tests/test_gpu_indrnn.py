@@ -1,0 +1,193 @@
+"""IndRNN stacks on the GPU, through the Model entry points of the C ABI and
+through the time-batched kernels directly: against the committed fixtures of the
+compiled reference and against the CPU restatement on shapes whose products run
+on the tensor-core kernel."""
+import numpy as np
+import pytest
+
+import configs
+import dlb200
+import fc_indrnn
+import fc_step
+import golden_io
+import util
+from enums import ACTIVATION
+
+pytestmark = pytest.mark.gpu
+
+TOL_1 = 1e-5       # activations, errors, gradients after one step (rel_l2)
+TOL_PARAMS = 1e-4  # updated weights: the first Adam-family step magnifies gradients of the order of eps
+
+
+def _check(got, want, skip=()):
+    for key, (l2, mx) in util.compare(got, want).items():
+        if key in skip:
+            continue
+        tol = TOL_PARAMS if key.startswith("params") else TOL_1
+        assert l2 <= tol, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+
+
+@pytest.mark.parametrize("name", sorted(golden_io.RECURRENT_CASES))
+def test_indrnn_model_matches_golden(gpu_ctx, name):
+    cfg, steps, X, Y, masks, p0, want = golden_io.load(name)
+    got = util.trace(util.build(dlb200.Model(gpu_ctx), cfg, params=p0), cfg, steps, X, Y, masks)
+    assert gpu_ctx.sync() == 0
+    _check(got, want)
+
+
+def _kink_free(cfg, X, band=2e-6, tries=64):
+    """Seeded weights (recurrent weights from U(0, 1)) for which no hidden
+    pre-activation lies within `band` of a derivative jump."""
+    scale = 1.0 / np.sqrt(cfg["layers"][1]["units"])
+    for seed in range(tries):
+        ora = util.build(fc_indrnn.IndRnnOracleModel(), cfg)
+        rng = np.random.default_rng(seed)
+        p0 = ora.get_array("parameters")
+        nw = ora.size("total_weights")
+        p0[:nw] = (rng.standard_normal(nw) * scale).astype(np.float32)
+        for _, s in configs.recurrent_slices(cfg):
+            p0[s] = rng.uniform(0, 1, s.stop - s.start).astype(np.float32)
+        ora.set_array("parameters", p0)
+        if util.near_kink(ora, cfg, X, {}, band) == 0:
+            return p0
+    raise AssertionError("no kink-free seed found")
+
+
+@pytest.mark.parametrize("cfg", [
+    configs.indrnn_stack(n_in=64, hidden=128, depth=2, n_out=32, seq_w=8, batch=32),
+    configs.indrnn_stack(n_in=128, hidden=128, depth=2, n_out=64, seq_w=4, batch=64, af=ACTIVATION.SELU),
+    configs.indrnn_stack(n_in=64, hidden=128, depth=2, n_out=64, seq_w=6, batch=48, norm=False),
+], ids=lambda c: c["name"])
+def test_indrnn_model_vs_restatement_tensor_core_shape(gpu_ctx, cfg):
+    X, Y = configs.synthetic_batch(cfg)
+    p0 = _kink_free(cfg, X)
+    want = util.trace(util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0), cfg, 3, X, Y)
+    got = util.trace(util.build(dlb200.Model(gpu_ctx), cfg, params=p0), cfg, 3, X, Y)
+    assert gpu_ctx.sync() == 0
+    _check(got, want, skip=("params_last",))
+    assert util.rel_l2(got["losses"], want["losses"]) <= 1e-5
+
+
+def test_glorot_and_recurrent_initialisation_match_the_fixture_layout(gpu_ctx):
+    cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=2, n_out=5, seq_w=4, batch=3)
+    m = util.build(dlb200.Model(gpu_ctx), cfg, seed=0)
+    o = util.build(fc_indrnn.IndRnnOracleModel(), cfg)
+    for name in ("total_parameters", "total_weights", "total_bias", "total_normalized_units"):
+        assert m.size(name) == o.size(name)
+    p = m.get_array("parameters")
+    T = 4.0
+    lo, hi = 0.5 ** (1 / T), 2.0 ** (1 / T)
+    (l1, s1), (l2, s2) = configs.recurrent_slices(cfg)
+    assert (p[s1] >= 0).all() and (p[s1] <= hi).all()
+    assert (p[s2] >= lo * (1 - 1e-6)).all() and (p[s2] <= hi).all()   # top layer: long-term memory range
+    g0 = m.size("total_weights") + m.size("total_bias")
+    assert np.allclose(p[g0 + 6:g0 + 22], 0.1) and np.allclose(p[g0:g0 + 6], 1.0)
+
+
+def _brn_state(rng, T, n):
+    mean = rng.standard_normal((T, n)).astype(np.float32) * 0.1
+    sigma = (0.5 + rng.random((T, n))).astype(np.float32)
+    r = (0.8 + 0.4 * rng.random((T, n))).astype(np.float32)
+    d = (rng.standard_normal((T, n)) * 0.1).astype(np.float32)
+    gamma = (0.5 + rng.random(n)).astype(np.float32)
+    beta = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    return mean, sigma, r, d, gamma, beta
+
+
+@pytest.mark.parametrize("T,B,n", [(5, 16, 128), (7, 9, 10), (1, 8, 32)])
+@pytest.mark.parametrize("af", [ACTIVATION.RELU, ACTIVATION.ELU])
+def test_time_kernels(gpu_ctx, T, B, n, af):
+    """Forward walk, reverse walk, sums and apply against numpy on one layer."""
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rng = np.random.default_rng(T * 100 + n)
+    Z = rng.standard_normal((T, B, n)).astype(np.float32)
+    mean, sigma, r, d, gamma, beta = _brn_state(rng, T, n)
+    u_rec = rng.uniform(0, 1, n).astype(np.float32)
+    dev = {k: ctx.array(v) for k, v in dict(mean=mean, sigma=sigma, r=r, d=d, gamma=gamma, beta=beta).items()}
+    ma, sa = ctx.array(np.zeros((T, n), np.float32)), ctx.array(np.ones((T, n), np.float32))
+    ua = dlb200.BrnUnitArrays(dev["mean"].ptr, dev["sigma"].ptr, ma.ptr, sa.ptr, dev["r"].ptr, dev["d"].ptr,
+                              dev["gamma"].ptr, dev["beta"].ptr)
+    import ctypes as C
+    Zd, ud = ctx.array(Z), ctx.array(u_rec)
+    A, A_lo = ctx.empty((T, B, n)), ctx.empty((T, B, n))
+    dlb200.check(L.dlb_indrnn_forward(ctx.h, Zd.ptr, C.byref(ua), ud.ptr, af, A.ptr, A_lo.ptr, T, B, n))
+    # numpy
+    f32 = np.float32
+    xh = ((Z - mean[:, None]) / sigma[:, None] * r[:, None] + d[:, None]).astype(f32)
+    y = (gamma * xh + beta).astype(f32)
+    pre = np.empty_like(y)
+    h = np.empty_like(y)
+    for t in range(T):
+        pre[t] = y[t] if t == 0 else (y[t] + u_rec * h[t - 1]).astype(f32)
+        h[t] = fc_step.af_fire(af, pre[t])
+    got_h = A.get()
+    assert util.rel_l2(got_h, h) <= 1e-6
+    hi = got_h.view(np.uint32) & np.uint32(0xFFFFE000)
+    assert np.allclose(hi.view(np.float32) + A_lo.get(), got_h, rtol=0, atol=1e-6 * np.abs(got_h).max())
+    # reverse walk
+    dA = rng.standard_normal((T, B, n)).astype(np.float32)
+    E = ctx.array(dA)
+    dlb200.check(L.dlb_indrnn_backward_walk(ctx.h, E.ptr, Zd.ptr, A.ptr, C.byref(ua), ud.ptr, af, T, B, n))
+    daf = np.empty_like(dA)
+    for t in range(T - 1, -1, -1):
+        fp = fc_step.af_derive(af, pre[t], h[t])
+        dd = (dA[t] * fp).astype(f32)
+        daf[t] = dd if t == T - 1 else (dd + u_rec * fp * daf[t + 1]).astype(f32)
+    got_e = E.get()
+    kink = np.abs(pre) < 1e-6
+    assert util.rel_l2(np.where(kink, 0, got_e), np.where(kink, 0, daf)) <= 2e-6
+    # sums
+    sums = ctx.empty((5, T, n), dtype=np.float64)
+    dlb200.check(L.dlb_indrnn_backward_sums(ctx.h, E.ptr, Zd.ptr, A.ptr, C.byref(ua), 1, T, B, n, sums.ptr))
+    e = got_e.astype(np.float64)
+    want = np.zeros((5, T, n))
+    want[0] = (e * xh).sum(1)
+    want[1] = e.sum(1)
+    eh = e * gamma
+    want[2] = (eh * (-r / sigma)[:, None]).sum(1)
+    want[3] = (eh * (Z - mean[:, None]) * (-r / (sigma * sigma))[:, None]).sum(1)
+    want[4, 1:] = (got_h[:-1].astype(np.float64) * e[1:]).sum(1)
+    got_s = sums.get()
+    for s in range(5):
+        assert np.allclose(got_s[s], want[s], rtol=2e-5, atol=2e-5 * np.abs(want[s]).max() + 1e-12), s
+    # fold over time
+    out = ctx.array(np.ones(n, np.float32))
+    dlb200.check(L.dlb_time_fold(ctx.h, sums.offset(4 * T * n), T, n, out.ptr))
+    assert np.allclose(out.get(), 1 + got_s[4].sum(0), rtol=1e-6, atol=1e-6)
+    # apply
+    delta_lo = ctx.empty((T, B, n))
+    dlb200.check(L.dlb_brn_time_backward_apply(ctx.h, E.ptr, delta_lo.ptr, Zd.ptr, C.byref(ua), sums.ptr, B, T, B, n))
+    N = f32(B)
+    dx = (got_e * gamma * (r / sigma)[:, None]).astype(f32)
+    dx = dx + got_s[3].astype(f32)[:, None] * ((Z - mean[:, None]) / (N * sigma[:, None]))
+    dx = dx + got_s[2].astype(f32)[:, None] * (f32(1) / N)
+    assert util.rel_l2(E.get(), dx) <= 2e-6
+    assert ctx.sync() == 0
+
+
+@pytest.mark.parametrize("T,B,n", [(4, 8, 64), (3, 5, 7)])
+def test_time_major_sums_and_clamp(gpu_ctx, T, B, n):
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rng = np.random.default_rng(T + n)
+    x = rng.standard_normal((B, T * n)).astype(np.float32)
+    out, lo = ctx.empty((T, B, n)), ctx.empty((T, B, n))
+    dlb200.check(L.dlb_time_major(ctx.h, ctx.array(x).ptr, out.ptr, lo.ptr, B, T, n))
+    want = x.reshape(B, T, n).transpose(1, 0, 2)
+    assert np.array_equal(out.get(), want)
+    sums = ctx.empty((2, T, n), dtype=np.float64)
+    dlb200.check(L.dlb_brn_time_forward_sums(ctx.h, out.ptr, T, B, n, sums.ptr))
+    got = sums.get()
+    assert np.allclose(got[0], want.astype(np.float64).sum(1), rtol=1e-5, atol=1e-5)
+    assert np.allclose(got[1], (want.astype(np.float64) ** 2).sum(1), rtol=1e-5, atol=1e-5)
+    u = ctx.array(np.linspace(-2, 2, n).astype(np.float32))
+    dlb200.check(L.dlb_indrnn_clamp(ctx.h, u.ptr, n, -1.25, 1.25))
+    assert np.array_equal(u.get(), np.clip(np.linspace(-2, 2, n).astype(np.float32), -1.25, 1.25))
+    assert ctx.sync() == 0
+
+
+def test_dropout_in_a_time_stepped_model_is_refused(gpu_ctx):
+    cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=1, n_out=5, seq_w=4, batch=3)
+    m = util.build(dlb200.Model(gpu_ctx), cfg)
+    m.set_dropout(1, 2, 0.5, False)
+    with pytest.raises(dlb200.DlbError):
+        m.forward_pass(3, np.zeros((3, 24), np.float32))

@@ -68,7 +68,7 @@ def trace(model, cfg, steps=1, X=None, Y=None, masks=None):
     out["losses"] = np.asarray(losses, np.float64)
     for li, l in enumerate(cfg["layers"]):
         if l.get("norm"):
-            n = l["units"]
+            n = l["units"] * cfg.get("seq_w", 1)
             out[f"mean_average{li}"] = model.get_layer_norm(li, "mean_average", n)
             out[f"variance_average{li}"] = model.get_layer_norm(li, "variance_average", n)
     return out
@@ -96,7 +96,8 @@ def near_kink(oracle_model, cfg, X, masks, band=1e-5):
     n = 0
     for li, l in enumerate(cfg["layers"][1:-1], start=1):
         if l.get("af") in KINKED and "Y" in oracle_model.layers[li]:
-            n += int((np.abs(oracle_model.layers[li]["Y"]) < band).sum())
+            lay = oracle_model.layers[li]
+            n += int((np.abs(lay["PRE"] if "PRE" in lay else lay["Y"]) < band).sum())
     return n
 
 
