@@ -101,7 +101,7 @@ def indrnn_stack(n_in=512, hidden=2048, depth=4, n_out=512, seq_w=256, batch=102
         hparams=dict(adam_learning_rate=1e-3, adam_beta1=0.9, adam_beta2=0.999, adam_epsilon=1e-8,
                      learning_rate_final=0.1, learning_gamma=1e-3, adam_gamma=0.1),
         brn=dict(r_max=3.0, d_max=5.0, momentum=0.99, eps=1e-5),
-        batch=batch, weight_seed=0, data_seed=0, recurrent_seed=3, inputs="normal", targets="normal", mp=False,
+        batch=batch, weight_seed=0, data_seed=0, recurrent_seed=3, inputs="normal", targets="normal",
     )
 
 

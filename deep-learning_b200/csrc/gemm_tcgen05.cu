@@ -192,7 +192,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                        const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
                        float *__restrict__ C, long long ldc, int M, int N, int K,
-                       const float *__restrict__ bias, int accumulate, int *status) {
+                       const float *__restrict__ bias, int accumulate, int tiles_n, int whole_tiles,
+                       int *status) {
   using P = SmemPlan<BN, BK, STAGES>;
   static_assert(BN == 256 || BN == 128, "two accumulators of BN columns must fit 512 columns");
   constexpr int HALF = BN / 2;  // columns per drain warp
@@ -207,8 +208,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   int *issued_kb = reinterpret_cast<int *>(bars + 2 * STAGES + 6);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
-  const int num_kb = (K + BK - 1) / BK;
+  // Work of this CTA.  Output tiles are numbered row-major over (m block, n
+  // block); CTAs [0, whole_tiles) own one tile each over the full k range.
+  // The remaining tiles (the ones that would form a last, partly filled wave
+  // over the SMs) are each shared by two CTAs, one per half of the k range,
+  // which add their partial results into an output the host has zeroed: with
+  // exactly two addends the sum does not depend on which half arrives first.
+  const int lin = blockIdx.x;
+  const bool split = lin >= whole_tiles;
+  const int tile_id = split ? whole_tiles + ((lin - whole_tiles) >> 1) : lin;
+  const int k_half = split ? ((lin - whole_tiles) & 1) : 0;
+  const int n0 = (tile_id % tiles_n) * BN, m0 = (tile_id / tiles_n) * BM;
+  const int total_kb = (K + BK - 1) / BK;
+  const int mid_kb = min(total_kb, (total_kb / 2 + CHUNK_KB - 1) / CHUNK_KB * CHUNK_KB);
+  const int kb_begin = (split && k_half) ? mid_kb : 0;
+  const int num_kb = (split ? (k_half ? total_kb : mid_kb) : total_kb) - kb_begin;  // k blocks of this CTA
   const int num_chunks = (num_kb + CHUNK_KB - 1) / CHUNK_KB;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES),
                  acc_full0 = smem_u32(bars + 2 * STAGES), acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
@@ -249,7 +263,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const uint32_t fb = full0 + 8 * s;
         const uint32_t st = base + s * P::STAGE_BYTES;
         mbar_expect_tx(fb, P::STAGE_BYTES);
-        const int k0 = kb * BK;
+        const int k0 = (kb_begin + kb) * BK;
         if (A_MN) {
           tma_load_3d(st, &tm_a, fb, 0, k0, m0 / 32);
           tma_load_3d(st + P::A_BYTES, &tm_a_lo, fb, 0, k0, m0 / 32);
@@ -364,15 +378,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           __syncwarp();
           const int col = col0 + lane;
           if (col < N) {
-            const float b = bias ? __ldg(bias + col) : 0.f;
+            const float b = (bias && k_half == 0) ? __ldg(bias + col) : 0.f;
+            if (split) {
 #pragma unroll 4
-            for (int r = 0; r < 32; ++r) {
-              const int row = row_base + r;
-              if (row < M) {
-                float *dst = C + (long long)row * ldc + col;
-                float val = tile[r * 33 + lane] + b;
-                if (accumulate) val += *dst;
-                *dst = val;
+              for (int r = 0; r < 32; ++r) {
+                const int row = row_base + r;
+                if (row < M) atomicAdd(C + (long long)row * ldc + col, tile[r * 33 + lane] + b);
+              }
+            } else {
+#pragma unroll 4
+              for (int r = 0; r < 32; ++r) {
+                const int row = row_base + r;
+                if (row < M) {
+                  float *dst = C + (long long)row * ldc + col;
+                  float val = tile[r * 33 + lane] + b;
+                  if (accumulate) val += *dst;
+                  *dst = val;
+                }
               }
             }
           }
@@ -512,9 +534,30 @@ dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, floa
     DLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::TOTAL));
     attr_set = true;
   }
-  dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
-  kernel<<<grid, NUM_THREADS, P::TOTAL, ctx->stream>>>(ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias,
-                                                      ep.accumulate, ctx->d_status);
+  // One CTA per SM is resident, so the tiles run in waves of sm_count.  When
+  // the last wave would fill at most half of the SMs, its tiles are split in
+  // two along k: twice as many CTAs of half the length, and the wave takes half
+  // the time (4096^3: 512 tiles = 3 waves + 68 tiles -> 3 waves + 136 halves).
+  // Not with accumulate (three addends would depend on arrival order) and not
+  // for a short k loop.  DLB_GEMM_SPLIT=0 turns it off.
+  const int tiles_n = ceil_div(N, BN), tiles = tiles_n * ceil_div(M, BM);
+  static const bool split_enabled = [] {
+    const char *e = getenv("DLB_GEMM_SPLIT");
+    return !(e && e[0] == '0');
+  }();
+  int split_tiles = 0;
+  const int rest = tiles % ctx->sm_count;
+  if (split_enabled && !ep.accumulate && rest > 0 && 2 * rest <= ctx->sm_count &&
+      ceil_div(K, BK) >= 8 * CHUNK_KB)
+    split_tiles = rest;
+  const int whole_tiles = tiles - split_tiles;
+  if (split_tiles) {
+    const int first_row = (whole_tiles / tiles_n) * BM;
+    DLB_CUDA(cudaMemset2DAsync(C + (long long)first_row * ldc, (size_t)ldc * sizeof(float), 0,
+                               (size_t)N * sizeof(float), (size_t)(M - first_row), ctx->stream));
+  }
+  kernel<<<whole_tiles + 2 * split_tiles, NUM_THREADS, P::TOTAL, ctx->stream>>>(
+      ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, ctx->d_status);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }

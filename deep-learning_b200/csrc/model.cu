@@ -100,6 +100,9 @@ struct dlb_model {
   // Inside train_step the step is known to be a single chunk, so each layer's
   // weight gradient is all-reduced as soon as its GEMM has been enqueued.
   bool overlap_grad_allreduce = false;
+  // The gradient vector is all zero (fresh, or cleared by the last update), so
+  // the weight-gradient products may overwrite instead of accumulate.
+  bool grads_clean = false;
 };
 
 namespace {
@@ -232,6 +235,7 @@ dlb_status allocate_parameters(dlb_model *m) {
   DLB_TRY(dev_alloc(m, &m->m1, P, true));
   DLB_TRY(dev_alloc(m, &m->m2, P, true));
   DLB_TRY(dev_alloc(m, &m->m2hat, P, true));
+  m->grads_clean = true;
   m->params_lo_valid = false;
   return DLB_OK;
 }
@@ -945,6 +949,7 @@ dlb_status dlb_model_set_array(dlb_model *m, const char *name, const float *host
   DLB_TRY(dlb_memcpy_h2d(m->ctx, p, host_in, n * sizeof(float)));
   DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
   if (p == m->params) m->params_lo_valid = false;
+  if (p == m->grads) m->grads_clean = false;
   return DLB_OK;
 }
 
@@ -1240,12 +1245,13 @@ static dlb_status update_derivatives_time(dlb_model *m, size_t rows) {
     float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
     DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta + first_row * H, l.delta_lo + first_row * H,
                                    X + first_row * I, X_lo + first_row * I, m->grads + l.first_conn,
-                                   dbias, (int)(TB - first_row), (int)I, (int)H, 1));
+                                   dbias, (int)(TB - first_row), (int)I, (int)H, m->grads_clean ? 0 : 1));
     if (m->overlap_grad_allreduce)
       DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
     X = l.A;
     X_lo = l.A_lo;
   }
+  m->grads_clean = false;
   return DLB_OK;
 }
 
@@ -1264,7 +1270,7 @@ dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows) {
     }
     float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
     DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn,
-                                   dbias, (int)rows, (int)l.fan_in, (int)l.units, 1));
+                                   dbias, (int)rows, (int)l.fan_in, (int)l.units, m->grads_clean ? 0 : 1));
     if (m->overlap_grad_allreduce)
       DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
     if (l.group == 0) {
@@ -1278,6 +1284,7 @@ dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows) {
       top_lo = m->layers[r].A_lo;
     }
   }
+  m->grads_clean = false;
   return DLB_OK;
 }
 
@@ -1319,6 +1326,7 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
   for (LayerRT &l : m->layers)
     if (is_indrnn(l))
       DLB_TRY(dlb_indrnn_clamp(m->ctx, m->params + l.first_recurrent, (int)l.units, -bound, bound));
+  m->grads_clean = true;  // the update kernel clears every gradient it consumes
   m->params_lo_valid = false;
   return DLB_OK;
 }

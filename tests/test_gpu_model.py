@@ -51,8 +51,8 @@ CASES = [
 
 @pytest.mark.parametrize("cfg", CASES, ids=lambda c: c["name"])
 def test_model_one_step_vs_restatement(gpu_ctx, cfg):
-    """Activations, errors, gradients and updated weights after one step (and
-    parameters after three).  The weights are drawn from the first seed for
+    """Activations, errors, gradients, running statistics and updated weights
+    after one step.  The weights are drawn from the first seed for
     which no hidden pre-activation sits on a jump of the activation's
     derivative: there the branch x < 0 is decided by the last bits of a long
     sum and two correct implementations may differ (see util.near_kink)."""
@@ -60,13 +60,19 @@ def test_model_one_step_vs_restatement(gpu_ctx, cfg):
     masks = configs.dropout_masks(cfg)
     p0, seed = util.kink_free_parameters(cfg, fc_step.OracleModel, X, masks,
                                          scale=1.0 / np.sqrt(cfg["layers"][1]["units"]))
-    want = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, 3, X, Y, masks)
-    got = util.trace(gpu_model(gpu_ctx, cfg, p0), cfg, 3, X, Y, masks)
+    want = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, 1, X, Y, masks)
+    got = util.trace(gpu_model(gpu_ctx, cfg, p0), cfg, 1, X, Y, masks)
     assert gpu_ctx.sync() == 0
     for key, (l2, mx) in util.compare(got, want).items():
-        if key == "params_last":
-            continue   # later steps may meet a jump; covered against the reference's own drift below
         assert l2 <= TOL_1, f"{key} (weight seed {seed}): rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+    # Two more steps: a pre-activation may now meet a jump (the serial and the
+    # threaded reference then part by up to 4e-4 on the running means of this
+    # workload), so only the scale of the agreement is checked here; the
+    # 100-step test below measures it against the reference's own drift.
+    want3 = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, 3, X, Y, masks)
+    got3 = util.trace(gpu_model(gpu_ctx, cfg, p0), cfg, 3, X, Y, masks)
+    assert util.rel_l2(got3["params_last"], want3["params_last"]) <= 1e-3
+    assert util.rel_l2(got3["losses"], want3["losses"]) <= 1e-4
     assert util.rel_max(got["params1"], want["params1"]) <= TOL_1_MAX
 
 

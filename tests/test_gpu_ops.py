@@ -89,6 +89,43 @@ def test_fc_forward_bias_and_gradient_accumulate(gpu_ctx):
     assert util.rel_l2(db, delta.astype(np.float64).sum(0)) <= GEMM_TOL
 
 
+@pytest.mark.parametrize("kind", ["fwd", "dx", "dw"])
+def test_products_whose_last_wave_is_split_along_k(gpu_ctx, kind):
+    """160 output tiles on 148 SMs: the 12 tiles of the last wave are each
+    computed by two CTAs (one per half of k) that add into a zeroed output.  The
+    output buffer starts with garbage, the result must not depend on it, must
+    be the same bits on every run, and bias goes in exactly once."""
+    L = gpu_ctx.L
+    rng = np.random.default_rng(21)
+    if kind == "dw":
+        rows, n_in, n_out = 1024, 2560, 2048   # output [n_out, n_in]: 16 x 10 tiles
+    elif kind == "dx":
+        rows, n_in, n_out = 2048, 2560, 1024   # output [rows, n_in]
+    else:
+        rows, n_in, n_out = 2048, 1024, 2560   # output [rows, n_out]
+    A, Bm = _operands(kind, rows, n_in, n_out, rng)
+    want = _exact(kind, A, Bm)
+    bias = rng.standard_normal(n_out, dtype=np.float32) if kind == "fwd" else None
+    if bias is not None:
+        want = want + bias
+    a, b = gpu_ctx.array(A), gpu_ctx.array(Bm)
+    bz = gpu_ctx.array(bias) if bias is not None else None
+    runs = []
+    for fill in (7.5, -3.25):
+        out = gpu_ctx.array(np.full(want.shape, fill, np.float32))
+        if kind == "fwd":
+            check(L.dlb_fc_forward(gpu_ctx.h, a.ptr, None, b.ptr, None, bz.ptr, out.ptr, rows, n_in, n_out))
+        elif kind == "dx":
+            check(L.dlb_fc_backward_input(gpu_ctx.h, a.ptr, None, b.ptr, None, out.ptr, rows, n_in, n_out))
+        else:
+            check(L.dlb_fc_weight_gradient(gpu_ctx.h, a.ptr, None, b.ptr, None, out.ptr, None, rows, n_in, n_out, 0))
+        assert gpu_ctx.sync() == 0
+        runs.append(out.get())
+    assert np.array_equal(runs[0], runs[1])
+    assert util.rel_l2(runs[0], want) <= GEMM_TOL
+    assert util.rel_max(runs[0], want) <= 5 * GEMM_TOL
+
+
 def test_large_k_accumulation_stays_fp32_faithful(gpu_ctx):
     """k = 4096: the chunked drain keeps the tensor core's truncating
     accumulation from growing with k; the product is as close to the exact one

@@ -45,10 +45,16 @@ def test_residual_model_vs_restatement_tensor_core_shape(gpu_ctx):
 
     p0, seed = util.kink_free_parameters(cfg, fc_residual.ResidualOracleModel, X, {}, scale=1.0 / 16,
                                          prepare=prepare)
+    want = util.trace_noisy(util.build(fc_residual.ResidualOracleModel(), cfg, params=p0), cfg, 1, X, Y, draws)
+    got = util.trace_noisy(util.build(dlb200.Model(gpu_ctx), cfg, params=p0), cfg, 1, X, Y, draws)
+    assert gpu_ctx.sync() == 0
+    _check(got, want)
+    # Later steps may meet a derivative jump; only the scale of the agreement is checked.
     want = util.trace_noisy(util.build(fc_residual.ResidualOracleModel(), cfg, params=p0), cfg, 3, X, Y, draws)
     got = util.trace_noisy(util.build(dlb200.Model(gpu_ctx), cfg, params=p0), cfg, 3, X, Y, draws)
     assert gpu_ctx.sync() == 0
-    _check(got, want, skip=("params_last",))
+    assert util.rel_l2(got["params_last"], want["params_last"]) <= 1e-3
+    assert util.rel_l2(got["losses"], want["losses"]) <= 1e-4
 
 
 def test_residual_kernels(gpu_ctx):
