@@ -5,6 +5,7 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <map>
 #include <vector>
 
 #include "dlb200.h"
@@ -26,6 +27,20 @@ struct dlb_ctx {
   bool comm_pending = false;
   bool use_tensor_core = true;
   bool tensor_core_ok = false;  // device is sm_100
+  // Operand form of the tensor-core products: DLB_GEMM_TF32X3 or DLB_GEMM_F16X3.
+  int gemm_kind = DLB_GEMM_F16X3;
+  // fp16 plane buffers written by dlb_split_planes, keyed by the buffer's
+  // address: the tensor they were split from, its element count (the lo plane
+  // starts n halfs after the hi plane) and the device slot of its scale.
+  struct PlaneEntry {
+    const float *x;
+    size_t n;
+    float *scale;
+  };
+  std::map<uintptr_t, PlaneEntry> planes;
+  float *scale_pool = nullptr;   // SCALE_SLOTS slots of 4 floats: s, 1/s, |x|max bits, unused
+  std::vector<int> scale_free;
+  std::map<uintptr_t, size_t> allocs;  // dlb_malloc'd blocks, to retire plane entries on free
   uint64_t launches = 0;
   cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
   // Optional per-launch record of the tensor-core GEMM.
@@ -87,6 +102,12 @@ struct GemmOperand {
   const float *lo;      // TF32 residual plane or nullptr
   long long stride_mn;  // elements between consecutive m (or n)
   long long stride_k;   // elements between consecutive k
+  // fp16 planes of s * x (hi = fp16(s x), lo = fp16(s x - hi)) with the strides
+  // of the tensor, and the device scalar s (a power of two); when all three are
+  // set the product runs on kind::f16 instead of kind::tf32.
+  const uint16_t *h_hi = nullptr;
+  const uint16_t *h_lo = nullptr;
+  const float *scale = nullptr;
 };
 struct GemmEpilogue {
   const float *bias = nullptr;   // per-n bias added to every row
@@ -104,5 +125,15 @@ dlb_status gemm_tcgen05(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B
                         long long ldc, int M, int N, int K, const GemmEpilogue &ep);
 bool gemm_tcgen05_supported(const GemmOperand &A, const GemmOperand &B, const float *C,
                             long long ldc, int M, int N, int K);
+bool gemm_f16_supported(const GemmOperand &A, const GemmOperand &B, const float *C, long long ldc,
+                        int M, int N, int K);
+// Fills o.h_hi / h_lo / scale from the plane buffer registered for (o.ptr, aux),
+// if there is one and the planes are 16-byte aligned.
+bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o);
+// Drops the plane buffers registered at addresses in [base, base + bytes).
+void planes_forget(dlb_ctx *ctx, uintptr_t base, size_t bytes);
+// max |x| into slot[2] and the fp16 planes of s x, s = 2^(14 - floor(log2 max)).
+dlb_status split_f16(dlb_ctx *ctx, const float *x, size_t n, uint16_t *hi, uint16_t *lo, float *slot);
+constexpr int SCALE_SLOTS = 8192;
 
 }  // namespace dlb

@@ -44,15 +44,71 @@ static size_t operand_elems(const GemmOperand &o, int mn, int k) {
   return (size_t)(k - 1) * o.stride_k + mn;
 }
 
+// Runs the tensor-core kernel, bracketed by a pair of events when per-launch
+// profiling is on.
+static dlb_status gemm_tensor_core(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
+                                   long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
+  if (!ctx->gemm_profile) return gemm_tcgen05(ctx, A, B, C, ldc, M, N, K, ep);
+  dlb_ctx::GemmRecord rec;
+  cudaEvent_t *ev[2] = {&rec.start, &rec.stop};
+  for (cudaEvent_t *e : ev) {
+    if (!ctx->event_pool.empty()) {
+      *e = ctx->event_pool.back();
+      ctx->event_pool.pop_back();
+    } else {
+      DLB_CUDA(cudaEventCreate(e));
+    }
+  }
+  rec.flops = 2.0 * M * N * K;
+  DLB_CUDA(cudaEventRecord(rec.start, ctx->stream));
+  const dlb_status st = gemm_tcgen05(ctx, A, B, C, ldc, M, N, K, ep);
+  DLB_CUDA(cudaEventRecord(rec.stop, ctx->stream));
+  ctx->gemm_records.push_back(rec);
+  return st;
+}
+
 dlb_status gemm(dlb_ctx *ctx, const GemmOperand &A_in, const GemmOperand &B_in, float *C,
                 long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
   GemmOperand A = A_in, B = B_in;
-  // The tensor-core tile is 128 x 256 x 16; below that the CUDA-core kernel
-  // is used, as it is for layouts TMA cannot address.
+  // The tensor-core tile is 128 x 256; below that the CUDA-core kernel is
+  // used, as it is for layouts TMA cannot address.
   const bool big = (long long)M * N >= 128 * 64 && K >= 32;
-  if (ctx->use_tensor_core && ctx->tensor_core_ok && big &&
-      gemm_tcgen05_supported(A, B, C, ldc, M, N, K)) {
-    // Residual planes the caller did not keep are derived into scratch.
+  if (!(ctx->use_tensor_core && ctx->tensor_core_ok && big)) return gemm_simt(ctx, A, B, C, ldc, M, N, K, ep);
+
+  if (ctx->gemm_kind == DLB_GEMM_F16X3 && gemm_f16_supported(A, B, C, ldc, M, N, K)) {
+    // fp16 planes: the caller's registered plane buffers, or planes derived
+    // into scratch for this call.
+    const bool a_have = A.h_hi || planes_lookup(ctx, A.lo, &A);
+    const bool b_have = B.h_hi || planes_lookup(ctx, B.lo, &B);
+    const size_t a_n = a_have ? 0 : align_up(operand_elems(A, M, K), 64);
+    const size_t b_n = b_have ? 0 : align_up(operand_elems(B, N, K), 64);
+    if (a_n + b_n) {
+      void *scr = nullptr;
+      DLB_TRY(scratch(ctx, (a_n + b_n) * 2 * sizeof(uint16_t) + 64, &scr));
+      uint16_t *h = static_cast<uint16_t *>(scr);
+      float *slots = reinterpret_cast<float *>(h + 2 * (a_n + b_n));
+      if (!a_have) {
+        DLB_TRY(split_f16(ctx, A.ptr, operand_elems(A, M, K), h, h + a_n, slots));
+        A.h_hi = h;
+        A.h_lo = h + a_n;
+        A.scale = slots;
+      }
+      if (!b_have) {
+        uint16_t *hb = h + 2 * a_n;
+        DLB_TRY(split_f16(ctx, B.ptr, operand_elems(B, N, K), hb, hb + b_n, slots + 4));
+        B.h_hi = hb;
+        B.h_lo = hb + b_n;
+        B.scale = slots + 4;
+      }
+    }
+    return gemm_tensor_core(ctx, A, B, C, ldc, M, N, K, ep);
+  }
+
+  if (gemm_tcgen05_supported(A, B, C, ldc, M, N, K)) {
+    // TF32 residual planes the caller did not keep are derived into scratch.
+    // Under the fp16 form a caller's plane buffer does not hold them.
+    A.h_hi = A.h_lo = B.h_hi = B.h_lo = nullptr;
+    if (ctx->gemm_kind != DLB_GEMM_TF32X3) A.lo = B.lo = nullptr;
     const size_t a_n = A.lo ? 0 : align_up(operand_elems(A, M, K), 64);
     const size_t b_n = B.lo ? 0 : align_up(operand_elems(B, N, K), 64);
     if (a_n + b_n) {
@@ -68,23 +124,7 @@ dlb_status gemm(dlb_ctx *ctx, const GemmOperand &A_in, const GemmOperand &B_in, 
         B.lo = s + a_n;
       }
     }
-    if (!ctx->gemm_profile) return gemm_tcgen05(ctx, A, B, C, ldc, M, N, K, ep);
-    dlb_ctx::GemmRecord rec;
-    cudaEvent_t *ev[2] = {&rec.start, &rec.stop};
-    for (cudaEvent_t *e : ev) {
-      if (!ctx->event_pool.empty()) {
-        *e = ctx->event_pool.back();
-        ctx->event_pool.pop_back();
-      } else {
-        DLB_CUDA(cudaEventCreate(e));
-      }
-    }
-    rec.flops = 2.0 * M * N * K;
-    DLB_CUDA(cudaEventRecord(rec.start, ctx->stream));
-    const dlb_status st = gemm_tcgen05(ctx, A, B, C, ldc, M, N, K, ep);
-    DLB_CUDA(cudaEventRecord(rec.stop, ctx->stream));
-    ctx->gemm_records.push_back(rec);
-    return st;
+    return gemm_tensor_core(ctx, A, B, C, ldc, M, N, K, ep);
   }
   return gemm_simt(ctx, A, B, C, ldc, M, N, K, ep);
 }
@@ -175,6 +215,7 @@ dlb_status dlb_ctx_create(dlb_ctx **out, int device) {
   ctx->sm_count = prop.multiProcessorCount;
   ctx->tensor_core_ok = true;
   if (const char *e = getenv("DLB_TENSOR_CORE")) ctx->use_tensor_core = atoi(e) != 0;
+  if (const char *e = getenv("DLB_GEMM_KIND")) ctx->gemm_kind = e[0] == 't' ? DLB_GEMM_TF32X3 : DLB_GEMM_F16X3;
   cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaMalloc(&ctx->d_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(int));
@@ -198,6 +239,7 @@ dlb_status dlb_ctx_destroy(dlb_ctx *ctx) {
   if (ctx->ev_comm) cudaEventDestroy(ctx->ev_comm);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->scale_pool) cudaFree(ctx->scale_pool);
   if (ctx->timer_start) cudaEventDestroy(ctx->timer_start);
   if (ctx->timer_stop) cudaEventDestroy(ctx->timer_stop);
   for (auto &r : ctx->gemm_records) {
@@ -281,6 +323,7 @@ dlb_status dlb_malloc(dlb_ctx *ctx, void **dev_ptr, size_t bytes) {
   DLB_REQUIRE(ctx && dev_ptr, "dlb_malloc: null");
   DLB_CUDA(cudaSetDevice(ctx->device));
   DLB_CUDA(cudaMalloc(dev_ptr, bytes ? bytes : 16));
+  ctx->allocs[reinterpret_cast<uintptr_t>(*dev_ptr)] = bytes ? bytes : 16;
   return DLB_OK;
 }
 
@@ -288,6 +331,11 @@ dlb_status dlb_free(dlb_ctx *ctx, void *dev_ptr) {
   DLB_REQUIRE(ctx, "dlb_free: null");
   if (!dev_ptr) return DLB_OK;
   DLB_CUDA(cudaStreamSynchronize(ctx->stream));
+  auto it = ctx->allocs.find(reinterpret_cast<uintptr_t>(dev_ptr));
+  if (it != ctx->allocs.end()) {
+    planes_forget(ctx, it->first, it->second);
+    ctx->allocs.erase(it);
+  }
   DLB_CUDA(cudaFree(dev_ptr));
   return DLB_OK;
 }

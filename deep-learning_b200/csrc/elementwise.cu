@@ -628,7 +628,7 @@ dlb_status dlb_brn_forward_finalize(dlb_ctx *ctx, const double *sums, int global
   return DLB_OK;
 }
 
-dlb_status dlb_activation_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
+dlb_status activation_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
                                   int af, const dlb_dropout_desc *dropout, float *A,
                                   float *A_lo, int rows, int n_units) {
   DLB_REQUIRE(ctx && Z && A && rows > 0 && n_units > 0, "dlb_activation_forward");
@@ -708,7 +708,7 @@ dlb_status dlb_activation_backward(dlb_ctx *ctx, float *dA, const float *Z, cons
   return DLB_OK;
 }
 
-dlb_status dlb_brn_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
+dlb_status brn_backward_apply_impl(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
                                   const dlb_brn_unit_arrays *u, const double *sums,
                                   int global_rows, int rows, int n_units) {
   DLB_REQUIRE(ctx && delta && Z && u && sums && rows > 0 && n_units > 0 && global_rows > 0,
@@ -741,7 +741,7 @@ dlb_status dlb_brn_backward_param_grads(dlb_ctx *ctx, const double *sums, int n_
   return DLB_OK;
 }
 
-dlb_status dlb_loss_delta(dlb_ctx *ctx, int loss, int af, const float *pre, const float *q,
+dlb_status loss_delta_impl(dlb_ctx *ctx, int loss, int af, const float *pre, const float *q,
                           const float *y, float *delta, float *delta_lo, int rows, int n_out,
                           int global_rows, double *loss_sum) {
   DLB_REQUIRE(ctx && q && y && delta && loss_sum && rows > 0 && n_out > 0 && global_rows > 0,
@@ -847,7 +847,7 @@ __global__ void shakedrop_backward_kernel(const float *__restrict__ d,
 
 }  // namespace dlb
 
-extern "C" dlb_status dlb_residual_forward(dlb_ctx *ctx, const float *x, float *block,
+static dlb_status residual_forward_impl(dlb_ctx *ctx, const float *x, float *block,
                                            const uint8_t *row_mask, const float *noise, float *out,
                                            float *out_lo, int rows, int width) {
   DLB_REQUIRE(ctx && x && block && out && rows > 0 && width > 0, "dlb_residual_forward");
@@ -863,7 +863,7 @@ extern "C" dlb_status dlb_residual_forward(dlb_ctx *ctx, const float *x, float *
   return DLB_OK;
 }
 
-extern "C" dlb_status dlb_shakedrop_backward(dlb_ctx *ctx, const float *d, const uint8_t *row_mask,
+static dlb_status shakedrop_backward_impl(dlb_ctx *ctx, const float *d, const uint8_t *row_mask,
                                              const float *noise, float *delta, float *delta_lo,
                                              int rows, int width) {
   DLB_REQUIRE(ctx && d && delta && rows > 0 && width > 0, "dlb_shakedrop_backward");
@@ -947,3 +947,68 @@ extern "C" dlb_status dlb_brn_forward_sums_noalloc(const float *Z, int rows, int
   DLB_CUDA(cudaGetLastError());
   return DLB_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Entry points that produce a GEMM operand together with its plane buffer.
+// Under the TF32 form the kernel writes the residual plane itself; under the
+// fp16 form the planes need the tensor's maximum first, so the kernel runs
+// without the plane output and dlb_split_planes follows.
+// ---------------------------------------------------------------------------
+namespace {
+struct PlaneOutput {
+  float *kernel_arg;  // what the producing kernel receives
+  float *deferred;    // buffer to split into afterwards, or nullptr
+  PlaneOutput(dlb_ctx *ctx, float *planes) {
+    const bool defer = ctx && planes && ctx->gemm_kind == DLB_GEMM_F16X3;
+    kernel_arg = defer ? nullptr : planes;
+    deferred = defer ? planes : nullptr;
+  }
+  dlb_status finish(dlb_ctx *ctx, dlb_status st, const float *x, size_t n) const {
+    if (st != DLB_OK || !deferred) return st;
+    return dlb_split_planes(ctx, x, deferred, n);
+  }
+};
+}  // namespace
+
+extern "C" {
+
+dlb_status dlb_activation_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u, int af,
+                                  const dlb_dropout_desc *dropout, float *A, float *A_lo, int rows,
+                                  int n_units) {
+  const PlaneOutput p(ctx, A_lo);
+  return p.finish(ctx, activation_forward_impl(ctx, Z, u, af, dropout, A, p.kernel_arg, rows, n_units), A,
+                  (size_t)rows * n_units);
+}
+
+dlb_status dlb_brn_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
+                                  const dlb_brn_unit_arrays *u, const double *sums, int global_rows,
+                                  int rows, int n_units) {
+  const PlaneOutput p(ctx, delta_lo);
+  return p.finish(ctx, brn_backward_apply_impl(ctx, delta, p.kernel_arg, Z, u, sums, global_rows, rows, n_units),
+                  delta, (size_t)rows * n_units);
+}
+
+dlb_status dlb_loss_delta(dlb_ctx *ctx, int loss, int af, const float *pre, const float *q, const float *y,
+                          float *delta, float *delta_lo, int rows, int n_out, int global_rows,
+                          double *loss_sum) {
+  const PlaneOutput p(ctx, delta_lo);
+  return p.finish(ctx, loss_delta_impl(ctx, loss, af, pre, q, y, delta, p.kernel_arg, rows, n_out, global_rows,
+                                       loss_sum),
+                  delta, (size_t)rows * n_out);
+}
+
+dlb_status dlb_residual_forward(dlb_ctx *ctx, const float *x, float *block, const uint8_t *row_mask,
+                                const float *noise, float *out, float *out_lo, int rows, int width) {
+  const PlaneOutput p(ctx, out_lo);
+  return p.finish(ctx, residual_forward_impl(ctx, x, block, row_mask, noise, out, p.kernel_arg, rows, width), out,
+                  (size_t)rows * width);
+}
+
+dlb_status dlb_shakedrop_backward(dlb_ctx *ctx, const float *d, const uint8_t *row_mask, const float *noise,
+                                  float *delta, float *delta_lo, int rows, int width) {
+  const PlaneOutput p(ctx, delta_lo);
+  return p.finish(ctx, shakedrop_backward_impl(ctx, d, row_mask, noise, delta, p.kernel_arg, rows, width), delta,
+                  (size_t)rows * width);
+}
+
+}  // extern "C"

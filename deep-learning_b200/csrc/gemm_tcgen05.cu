@@ -126,6 +126,16 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with fp16 inputs (k = 16 per instruction).
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // mbarrier arrives when all previously issued MMAs of this thread are done.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile(
@@ -173,10 +183,10 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 constexpr int NUM_DRAIN_WARPS = 8;
 constexpr int NUM_THREADS = 64 + NUM_DRAIN_WARPS * 32;
 
-template <int BN, int BK, int STAGES>
+template <int BN, int BK, int STAGES, int ES>
 struct SmemPlan {
-  static constexpr int A_BYTES = BM * BK * 4;
-  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int A_BYTES = BM * BK * ES;
+  static constexpr int B_BYTES = BN * BK * ES;
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int EPI_BYTES = NUM_DRAIN_WARPS * 32 * 33 * 4;  // reuses the ring
@@ -187,14 +197,20 @@ struct SmemPlan {
 
 // Barrier slots: [0,S) full, [S,2S) empty, 2S..2S+1 accumulator full,
 // 2S+2..2S+3 accumulator empty, then three 8-byte scalars.
-template <int BN, int BK, int STAGES, int CHUNK_KB, bool A_MN, bool B_MN>
+// ES = 4: fp32 operands read as TF32 plus their TF32 residual planes.
+// ES = 2: fp16 planes hi = fp16(s x), lo = fp16(s x - hi) of every operand,
+// s a power of two per tensor; the result is scaled back by 1 / (s_a s_b).
+template <int BN, int BK, int STAGES, int CHUNK_KB, bool A_MN, bool B_MN, int ES>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-    gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
+    gemm_x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                        const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
                        float *__restrict__ C, long long ldc, int M, int N, int K,
                        const float *__restrict__ bias, int accumulate, int tiles_n, int whole_tiles,
+                       const float *__restrict__ scale_a, const float *__restrict__ scale_b,
                        int *status) {
-  using P = SmemPlan<BN, BK, STAGES>;
+  using P = SmemPlan<BN, BK, STAGES, ES>;
+  static_assert(ES == 4 || ES == 2, "fp32 (TF32) or fp16 operands");
+  constexpr int MN_W = 128 / ES;  // elements of one 128-byte column of an MN-major tile
   static_assert(BN == 256 || BN == 128, "two accumulators of BN columns must fit 512 columns");
   constexpr int HALF = BN / 2;  // columns per drain warp
   extern __shared__ uint8_t smem_raw[];
@@ -265,15 +281,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         mbar_expect_tx(fb, P::STAGE_BYTES);
         const int k0 = (kb_begin + kb) * BK;
         if (A_MN) {
-          tma_load_3d(st, &tm_a, fb, 0, k0, m0 / 32);
-          tma_load_3d(st + P::A_BYTES, &tm_a_lo, fb, 0, k0, m0 / 32);
+          tma_load_3d(st, &tm_a, fb, 0, k0, m0 / MN_W);
+          tma_load_3d(st + P::A_BYTES, &tm_a_lo, fb, 0, k0, m0 / MN_W);
         } else {
           tma_load_2d(st, &tm_a, fb, k0, m0);
           tma_load_2d(st + P::A_BYTES, &tm_a_lo, fb, k0, m0);
         }
         if (B_MN) {
-          tma_load_3d(st + 2 * P::A_BYTES, &tm_b, fb, 0, k0, n0 / 32);
-          tma_load_3d(st + 2 * P::A_BYTES + P::B_BYTES, &tm_b_lo, fb, 0, k0, n0 / 32);
+          tma_load_3d(st + 2 * P::A_BYTES, &tm_b, fb, 0, k0, n0 / MN_W);
+          tma_load_3d(st + 2 * P::A_BYTES + P::B_BYTES, &tm_b_lo, fb, 0, k0, n0 / MN_W);
         } else {
           tma_load_2d(st + 2 * P::A_BYTES, &tm_b, fb, k0, n0);
           tma_load_2d(st + 2 * P::A_BYTES + P::B_BYTES, &tm_b_lo, fb, k0, n0);
@@ -285,19 +301,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       // Instruction descriptor: fp32 accumulate, TF32 A and B, majors, N, M.
-      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) |
+      constexpr uint32_t FMT = ES == 4 ? 2u : 0u;  // operand format: TF32 / F16
+      const uint32_t idesc = (1u << 4) | (FMT << 7) | (FMT << 10) | ((A_MN ? 1u : 0u) << 15) |
                              ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
                              ((uint32_t)(BM >> 4) << 24);
-      // K-major tiles: rows of BK*4 bytes, 8-row groups SBO apart, k step = 32 B
-      // inside the swizzled row.  MN-major tiles: 32-float columns LBO apart,
-      // each a stack of 4-row (512 B) groups SBO apart, k step = 8 rows.
-      constexpr uint32_t K_ROW = BK * 4;
-      constexpr uint32_t K_LAYOUT = (BK == 32) ? LAYOUT_SW128 : LAYOUT_SW64;
-      constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, A_SBO = A_MN ? 512 : 8 * K_ROW;
-      constexpr uint32_t B_LBO = B_MN ? BK * 128 : 16, B_SBO = B_MN ? 512 : 8 * K_ROW;
-      constexpr uint32_t A_LAYOUT = A_MN ? LAYOUT_SW128_BASE32B : K_LAYOUT;
-      constexpr uint32_t B_LAYOUT = B_MN ? LAYOUT_SW128_BASE32B : K_LAYOUT;
-      constexpr uint32_t A_KSTEP = A_MN ? 1024 : 32, B_KSTEP = B_MN ? 1024 : 32;
+      // K-major tiles: rows of BK*ES bytes, 8-row groups SBO apart, k step = 32 B
+      // inside the swizzled row.  MN-major tiles: 128-byte columns (32 floats or
+      // 64 halfs) LBO apart, each a stack of k rows; fp32: 4-row (512 B) groups
+      // under the swizzle of 32-byte atoms, fp16: 8-row (1024 B) groups under the
+      // plain 128-byte swizzle; k step = the rows of one instruction.
+      constexpr int KI = 32 / ES;  // k per instruction: 8 (TF32), 16 (F16)
+      constexpr uint32_t K_ROW = BK * ES;
+      static_assert(K_ROW == 64 || K_ROW == 128, "k-major rows of 64 or 128 bytes");
+      constexpr uint32_t K_LAYOUT = (K_ROW == 128) ? LAYOUT_SW128 : LAYOUT_SW64;
+      constexpr uint32_t MN_SBO = ES == 4 ? 512 : 1024;
+      constexpr uint32_t MN_LAYOUT = ES == 4 ? LAYOUT_SW128_BASE32B : LAYOUT_SW128;
+      constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, A_SBO = A_MN ? MN_SBO : 8 * K_ROW;
+      constexpr uint32_t B_LBO = B_MN ? BK * 128 : 16, B_SBO = B_MN ? MN_SBO : 8 * K_ROW;
+      constexpr uint32_t A_LAYOUT = A_MN ? MN_LAYOUT : K_LAYOUT;
+      constexpr uint32_t B_LAYOUT = B_MN ? MN_LAYOUT : K_LAYOUT;
+      constexpr uint32_t A_KSTEP = A_MN ? KI * 128 : 32, B_KSTEP = B_MN ? KI * 128 : 32;
       bool ok = true;
       int kb = 0;
       for (int c = 0; c < num_chunks && ok; ++c) {
@@ -320,14 +343,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           const uint32_t a_hi = st, a_lo = st + P::A_BYTES, b_hi = st + 2 * P::A_BYTES,
                          b_lo = st + 2 * P::A_BYTES + P::B_BYTES;
 #pragma unroll
-          for (int k8 = 0; k8 < BK / 8; ++k8) {
+          for (int k8 = 0; k8 < BK / KI; ++k8) {
             const uint64_t da_hi = make_smem_desc(a_hi + k8 * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
             const uint64_t da_lo = make_smem_desc(a_lo + k8 * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
             const uint64_t db_hi = make_smem_desc(b_hi + k8 * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
             const uint64_t db_lo = make_smem_desc(b_lo + k8 * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
-            umma_tf32(d_tmem, da_lo, db_hi, idesc, first ? 0u : 1u);
-            umma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
-            umma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
+            if (ES == 4) {
+              umma_tf32(d_tmem, da_lo, db_hi, idesc, first ? 0u : 1u);
+              umma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
+              umma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
+            } else {
+              umma_f16(d_tmem, da_lo, db_hi, idesc, first ? 0u : 1u);
+              umma_f16(d_tmem, da_hi, db_lo, idesc, 1u);
+              umma_f16(d_tmem, da_hi, db_hi, idesc, 1u);
+            }
             first = false;
           }
           umma_commit(empty0 + 8 * s);  // stage reusable once these MMAs retire
@@ -367,6 +396,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       // ring is idle and serves as the transpose buffer.
       float *tile = reinterpret_cast<float *>(smem) + (warp - 2) * 32 * 33;
       const int row_base = m0 + q * 32;
+      // fp16 planes hold s x: both factors are powers of two, the scaling is exact.
+      const float out_a = ES == 2 ? 1.f / __ldg(scale_a) : 1.f, out_b = ES == 2 ? 1.f / __ldg(scale_b) : 1.f;
 #pragma unroll
       for (int j = 0; j < HALF / 32; ++j) {
         const int col0 = n0 + h * HALF + j * 32;
@@ -374,7 +405,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           // lane owns row (row_base + lane): park its 32 values, then each
           // instruction below stores one row's 32 consecutive floats.
 #pragma unroll
-          for (int i = 0; i < 32; ++i) tile[lane * 33 + i] = acc[j * 32 + i];
+          for (int i = 0; i < 32; ++i)
+            tile[lane * 33 + i] = ES == 2 ? acc[j * 32 + i] * out_a * out_b : acc[j * 32 + i];
           __syncwarp();
           const int col = col0 + lane;
           if (col < N) {
@@ -452,46 +484,53 @@ EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-// K-major operand: global [mn, k] with row pitch ld; box {BK, rows}.
-bool tmap_k_major(CUtensorMap *m, const float *ptr, uint64_t mn, uint64_t k, uint64_t ld,
+// K-major operand: global [mn, k] with row pitch ld (elements of `es` bytes);
+// box {BK, rows}.
+bool tmap_k_major(CUtensorMap *m, const void *ptr, int es, uint64_t mn, uint64_t k, uint64_t ld,
                   uint32_t box_k, uint32_t box_mn) {
   const cuuint64_t dims[2] = {k, mn};
-  const cuuint64_t strides[1] = {ld * 4};
+  const cuuint64_t strides[1] = {ld * es};
   const cuuint32_t box[2] = {box_k, box_mn};
   const cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapSwizzle sw = box_k == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-  return encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(ptr), dims,
-                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+  const CUtensorMapSwizzle sw = box_k * es == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  return encode_tiled()(m, es == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                        const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// MN-major operand: global [k, mn] with row pitch ld, viewed as {w, k, mn/w}
+// with w = 128 bytes of elements (32 floats, 64 halfs); box {w, BK, cols/w}
+// lands as 128-byte columns.  fp32 needs the swizzle of 32-byte atoms, fp16 the
+// plain 128-byte swizzle.
+bool tmap_mn_major(CUtensorMap *m, const void *ptr, int es, uint64_t mn, uint64_t k, uint64_t ld,
+                   uint32_t box_k, uint32_t box_mn) {
+  const uint32_t w = 128 / es;
+  const cuuint64_t dims[3] = {w, k, mn / w};
+  const cuuint64_t strides[2] = {ld * es, 128};
+  const cuuint32_t box[3] = {w, box_k, box_mn / w};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return encode_tiled()(m, es == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                        const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        es == 4 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// MN-major operand: global [k, mn] with row pitch ld, viewed as
-// {32 floats, k, mn/32}; box {32, BK, cols/32} lands as 32-float columns.
-bool tmap_mn_major(CUtensorMap *m, const float *ptr, uint64_t mn, uint64_t k, uint64_t ld,
-                   uint32_t box_k, uint32_t box_mn) {
-  const cuuint64_t dims[3] = {32, k, mn / 32};
-  const cuuint64_t strides[2] = {ld * 4, 128};
-  const cuuint32_t box[3] = {32, box_k, box_mn / 32};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  return encode_tiled()(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims,
-                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-bool operand_ok(const GemmOperand &o, int mn, int k) {
-  if (reinterpret_cast<uintptr_t>(o.ptr) & 15) return false;
-  if (o.lo && (reinterpret_cast<uintptr_t>(o.lo) & 15)) return false;
-  if (o.stride_k == 1) return o.stride_mn % 4 == 0 && o.stride_mn >= k;
-  if (o.stride_mn == 1) return o.stride_k % 4 == 0 && o.stride_k >= mn && mn % 32 == 0;
+// What TMA can address: 16-byte aligned base and row pitch; an MN-major extent
+// that is a whole number of 128-byte columns.
+bool operand_ok(const void *ptr, int es, long long stride_mn, long long stride_k, int mn, int k) {
+  const int per16 = 16 / es, w = 128 / es;
+  if (reinterpret_cast<uintptr_t>(ptr) & 15) return false;
+  if (stride_k == 1) return stride_mn % per16 == 0 && stride_mn >= k;
+  if (stride_mn == 1) return stride_k % per16 == 0 && stride_k >= mn && mn % w == 0;
   return false;
 }
 
 struct TileConfig {
   int bn, bk, stages, chunk;
 };
-// Selected by DLB_GEMM_TILE=<bn>x<bk>x<stages>x<chunk k-blocks> for experiments.
+// Selected by DLB_GEMM_TILE=<bn>x<bk bytes / 4>x<stages>x<chunk k-blocks> for experiments.
 TileConfig tile_config() {
   static TileConfig cfg = [] {
     TileConfig c{256, 16, 4, 4};
@@ -504,31 +543,38 @@ TileConfig tile_config() {
   return cfg;
 }
 
-template <int BN, int BK, int STAGES, int CHUNK_KB, bool A_MN, bool B_MN>
+// BKW = k-block in 4-byte words per row (16 -> 64-byte rows): BK = BKW floats or
+// 2 * BKW halfs.
+template <int BN, int BKW, int STAGES, int CHUNK_KB, bool A_MN, bool B_MN, int ES>
 dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
                   long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
-  using P = SmemPlan<BN, BK, STAGES>;
+  constexpr int BK = BKW * 4 / ES;
+  using P = SmemPlan<BN, BK, STAGES, ES>;
+  const void *a_hi = ES == 4 ? (const void *)A.ptr : (const void *)A.h_hi;
+  const void *a_lo = ES == 4 ? (const void *)A.lo : (const void *)A.h_lo;
+  const void *b_hi = ES == 4 ? (const void *)B.ptr : (const void *)B.h_hi;
+  const void *b_lo = ES == 4 ? (const void *)B.lo : (const void *)B.h_lo;
   CUtensorMap ta, tal, tb, tbl;
   bool ok = true;
   if (A_MN) {
-    ok &= tmap_mn_major(&ta, A.ptr, M, K, A.stride_k, BK, BM);
-    ok &= tmap_mn_major(&tal, A.lo, M, K, A.stride_k, BK, BM);
+    ok &= tmap_mn_major(&ta, a_hi, ES, M, K, A.stride_k, BK, BM);
+    ok &= tmap_mn_major(&tal, a_lo, ES, M, K, A.stride_k, BK, BM);
   } else {
-    ok &= tmap_k_major(&ta, A.ptr, M, K, A.stride_mn, BK, BM);
-    ok &= tmap_k_major(&tal, A.lo, M, K, A.stride_mn, BK, BM);
+    ok &= tmap_k_major(&ta, a_hi, ES, M, K, A.stride_mn, BK, BM);
+    ok &= tmap_k_major(&tal, a_lo, ES, M, K, A.stride_mn, BK, BM);
   }
   if (B_MN) {
-    ok &= tmap_mn_major(&tb, B.ptr, N, K, B.stride_k, BK, BN);
-    ok &= tmap_mn_major(&tbl, B.lo, N, K, B.stride_k, BK, BN);
+    ok &= tmap_mn_major(&tb, b_hi, ES, N, K, B.stride_k, BK, BN);
+    ok &= tmap_mn_major(&tbl, b_lo, ES, N, K, B.stride_k, BK, BN);
   } else {
-    ok &= tmap_k_major(&tb, B.ptr, N, K, B.stride_mn, BK, BN);
-    ok &= tmap_k_major(&tbl, B.lo, N, K, B.stride_mn, BK, BN);
+    ok &= tmap_k_major(&tb, b_hi, ES, N, K, B.stride_mn, BK, BN);
+    ok &= tmap_k_major(&tbl, b_lo, ES, N, K, B.stride_mn, BK, BN);
   }
   if (!ok) {
     set_error("gemm_tcgen05: cuTensorMapEncodeTiled rejected an operand");
     return DLB_ERR_CUDA;
   }
-  auto kernel = gemm_tf32x3_kernel<BN, BK, STAGES, CHUNK_KB, A_MN, B_MN>;
+  auto kernel = gemm_x3_kernel<BN, BK, STAGES, CHUNK_KB, A_MN, B_MN, ES>;
   static bool attr_set = false;
   if (!attr_set) {
     DLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::TOTAL));
@@ -557,55 +603,83 @@ dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, floa
                                (size_t)N * sizeof(float), (size_t)(M - first_row), ctx->stream));
   }
   kernel<<<whole_tiles + 2 * split_tiles, NUM_THREADS, P::TOTAL, ctx->stream>>>(
-      ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, ctx->d_status);
+      ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, A.scale, B.scale,
+      ctx->d_status);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int ES>
 dlb_status launch_tile(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
                        long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
   const TileConfig t = tile_config();
 #define DLB_TILE(TBN, TBK, TST, TCH)                                              \
   if (t.bn == (TBN) && t.bk == (TBK) && t.stages == (TST) && t.chunk == (TCH))   \
-    return launch<TBN, TBK, TST, TCH, A_MN, B_MN>(ctx, A, B, C, ldc, M, N, K, ep);
+    return launch<TBN, TBK, TST, TCH, A_MN, B_MN, ES>(ctx, A, B, C, ldc, M, N, K, ep);
   DLB_TILE(256, 16, 4, 4)
   DLB_TILE(256, 16, 4, 2)
   DLB_TILE(256, 16, 4, 16)
-  DLB_TILE(256, 32, 2, 2)
-  DLB_TILE(128, 32, 3, 2)
 #undef DLB_TILE
   set_error("gemm_tcgen05: tile %dx%dx%dx%d is not compiled in", t.bn, t.bk, t.stages, t.chunk);
   return DLB_ERR_UNSUPPORTED;
 }
 
-}  // namespace
+template <int ES>
+dlb_status launch_majors(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
+                         long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
+  // A dimension of extent 1 along k makes stride_k ambiguous; treat k-contiguous first.
+  const bool a_mn = !(A.stride_k == 1);
+  const bool b_mn = !(B.stride_k == 1);
+  if (!a_mn && !b_mn) return launch_tile<false, false, ES>(ctx, A, B, C, ldc, M, N, K, ep);
+  if (!a_mn && b_mn) return launch_tile<false, true, ES>(ctx, A, B, C, ldc, M, N, K, ep);
+  if (a_mn && b_mn) return launch_tile<true, true, ES>(ctx, A, B, C, ldc, M, N, K, ep);
+  set_error("gemm_tcgen05: MN-major A with K-major B is not instantiated");
+  return DLB_ERR_UNSUPPORTED;
+}
 
-bool gemm_tcgen05_supported(const GemmOperand &A, const GemmOperand &B, const float *C,
-                            long long ldc, int M, int N, int K) {
+bool shape_ok(const GemmOperand &A, const GemmOperand &B, const float *C, long long ldc, int M,
+              int N, int K) {
   if (!encode_tiled()) return false;
   if (M < 1 || N < 1 || K < 1) return false;
   if (reinterpret_cast<uintptr_t>(C) & 3) return false;
   if (ldc < N) return false;
   // MN-major A with K-major B never occurs in the FC step.
   if (A.stride_mn == 1 && A.stride_k != 1 && B.stride_k == 1 && B.stride_mn != 1) return false;
-  return operand_ok(A, M, K) && operand_ok(B, N, K);
+  return true;
+}
+
+}  // namespace
+
+bool gemm_tcgen05_supported(const GemmOperand &A, const GemmOperand &B, const float *C,
+                            long long ldc, int M, int N, int K) {
+  return shape_ok(A, B, C, ldc, M, N, K) && operand_ok(A.ptr, 4, A.stride_mn, A.stride_k, M, K) &&
+         operand_ok(B.ptr, 4, B.stride_mn, B.stride_k, N, K);
+}
+
+// The fp16-plane form: planes have the strides of their tensor, so the test is
+// on the strides alone (the planes' own base alignment is checked at launch).
+bool gemm_f16_supported(const GemmOperand &A, const GemmOperand &B, const float *C, long long ldc,
+                        int M, int N, int K) {
+  return shape_ok(A, B, C, ldc, M, N, K) && operand_ok(nullptr, 2, A.stride_mn, A.stride_k, M, K) &&
+         operand_ok(nullptr, 2, B.stride_mn, B.stride_k, N, K);
 }
 
 dlb_status gemm_tcgen05(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
                         long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
+  if (A.h_hi && A.h_lo && B.h_hi && B.h_lo) {
+    const uintptr_t al = reinterpret_cast<uintptr_t>(A.h_hi) | reinterpret_cast<uintptr_t>(A.h_lo) |
+                         reinterpret_cast<uintptr_t>(B.h_hi) | reinterpret_cast<uintptr_t>(B.h_lo);
+    if (!gemm_f16_supported(A, B, C, ldc, M, N, K) || (al & 15) || !A.scale || !B.scale) {
+      set_error("gemm_tcgen05: fp16 planes outside the TMA path");
+      return DLB_ERR_UNSUPPORTED;
+    }
+    return launch_majors<2>(ctx, A, B, C, ldc, M, N, K, ep);
+  }
   if (!gemm_tcgen05_supported(A, B, C, ldc, M, N, K) || !A.lo || !B.lo) {
     set_error("gemm_tcgen05: operand layout outside the TMA path");
     return DLB_ERR_UNSUPPORTED;
   }
-  // A dimension of extent 1 along k makes stride_k ambiguous; treat k-contiguous first.
-  const bool a_mn = !(A.stride_k == 1);
-  const bool b_mn = !(B.stride_k == 1);
-  if (!a_mn && !b_mn) return launch_tile<false, false>(ctx, A, B, C, ldc, M, N, K, ep);
-  if (!a_mn && b_mn) return launch_tile<false, true>(ctx, A, B, C, ldc, M, N, K, ep);
-  if (a_mn && b_mn) return launch_tile<true, true>(ctx, A, B, C, ldc, M, N, K, ep);
-  set_error("gemm_tcgen05: MN-major A with K-major B is not instantiated");
-  return DLB_ERR_UNSUPPORTED;
+  return launch_majors<4>(ctx, A, B, C, ldc, M, N, K, ep);
 }
 
 }  // namespace dlb

@@ -429,7 +429,13 @@ dlb_status check_supported(dlb_model *m) {
 
 dlb_status refresh_weight_residuals(dlb_model *m) {
   if (m->params_lo_valid || m->total_weights == 0) return DLB_OK;
-  DLB_TRY(dlb_split_tf32(m->ctx, m->params, m->params_lo, m->total_weights));
+  // One plane buffer per layer, so that every weight matrix gets a scale of its own.
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    const LayerRT &l = m->layers[i];
+    if (l.type == DLB_LAYER_RESIDUAL) continue;
+    DLB_TRY(dlb_split_planes(m->ctx, m->params + l.first_conn, m->params_lo + l.first_conn,
+                             l.units * l.fan_in));
+  }
   m->params_lo_valid = true;
   return DLB_OK;
 }
@@ -1049,7 +1055,7 @@ dlb_status dlb_model_forward_pass_device(dlb_model *m, size_t rows, const float 
     return forward_layers(m, rows);
   }
   if (X_dev != m->input) DLB_TRY(dlb_memcpy_d2d(m->ctx, m->input, X_dev, n * sizeof(float)));
-  DLB_TRY(dlb_split_tf32(m->ctx, m->input, m->input_lo, n));
+  DLB_TRY(dlb_split_planes(m->ctx, m->input, m->input_lo, n));
   return forward_layers(m, rows);
 }
 
@@ -1130,7 +1136,7 @@ static dlb_status backward_residual(dlb_model *m, size_t i, int B) {
     } else {
       DLB_TRY(dlb_activation_backward(m->ctx, prev.delta, prev.A, b.IN, nullptr, b.af, B,
                                       (int)b.fan_in, nullptr));
-      DLB_TRY(dlb_split_tf32(m->ctx, prev.delta, prev.delta_lo, (size_t)B * b.fan_in));
+      DLB_TRY(dlb_split_planes(m->ctx, prev.delta, prev.delta_lo, (size_t)B * b.fan_in));
     }
   }
   return DLB_OK;
@@ -1170,11 +1176,11 @@ static dlb_status backward_pass_time(dlb_model *m, size_t rows) {
         DLB_TRY(dlb_allreduce_f64(m->ctx, l.bwd_sums + 2 * plane, 2 * plane));
         DLB_TRY(dlb_brn_time_backward_apply(m->ctx, l.delta, l.delta_lo, l.Z, &u, l.bwd_sums, Bg, T, B, H));
       } else {
-        DLB_TRY(dlb_split_tf32(m->ctx, l.delta, l.delta_lo, (size_t)TB * H));
+        DLB_TRY(dlb_split_planes(m->ctx, l.delta, l.delta_lo, (size_t)TB * H));
       }
     } else {
       DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, nullptr, l.af, TB, H, nullptr));
-      DLB_TRY(dlb_split_tf32(m->ctx, l.delta, l.delta_lo, (size_t)TB * H));
+      DLB_TRY(dlb_split_planes(m->ctx, l.delta, l.delta_lo, (size_t)TB * H));
     }
     if (i == 1) break;  // the error into the input layer is never formed
     LayerRT &below = m->layers[i - 1];
@@ -1221,7 +1227,7 @@ dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows) {
         DLB_TRY(norm_backward(m, l, l.delta, l.delta_lo, l.Z, l.A, l.af, B));
       } else {
         DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, nullptr, l.af, B, H, nullptr));
-        DLB_TRY(dlb_split_tf32(m->ctx, l.delta, l.delta_lo, (size_t)B * H));
+        DLB_TRY(dlb_split_planes(m->ctx, l.delta, l.delta_lo, (size_t)B * H));
       }
     }
     if (below)

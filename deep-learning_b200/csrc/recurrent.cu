@@ -385,7 +385,7 @@ using namespace dlb;
 
 extern "C" {
 
-dlb_status dlb_time_major(dlb_ctx *ctx, const float *x, float *out, float *out_lo, int rows,
+dlb_status time_major_impl(dlb_ctx *ctx, const float *x, float *out, float *out_lo, int rows,
                           int seq_w, int n) {
   DLB_REQUIRE(ctx && x && out && rows > 0 && seq_w > 0 && n > 0, "dlb_time_major");
   const bool v4 = n % 4 == 0 && aligned16({x, out, out_lo});
@@ -425,7 +425,7 @@ dlb_status dlb_brn_time_forward_finalize(dlb_ctx *ctx, const double *sums, int g
   return DLB_OK;
 }
 
-dlb_status dlb_indrnn_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
+dlb_status indrnn_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
                               const float *recurrent, int af, float *A, float *A_lo, int seq_w,
                               int rows, int n) {
   DLB_REQUIRE(ctx && Z && A && seq_w > 0 && rows > 0 && n > 0, "dlb_indrnn_forward");
@@ -501,7 +501,7 @@ dlb_status dlb_time_fold(dlb_ctx *ctx, const double *sums, int seq_w, int n, flo
   return DLB_OK;
 }
 
-dlb_status dlb_brn_time_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
+dlb_status brn_time_backward_apply_impl(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
                                        const dlb_brn_unit_arrays *u, const double *sums,
                                        int global_rows, int seq_w, int rows, int n) {
   DLB_REQUIRE(ctx && delta && Z && u && sums && global_rows > 0 && seq_w > 0 && rows > 0 && n > 0,
@@ -524,6 +524,36 @@ dlb_status dlb_indrnn_clamp(dlb_ctx *ctx, float *recurrent, int n, float lo, flo
   clamp_kernel<<<ceil_div(n, 256), 256, 0, ctx->stream>>>(recurrent, n, lo, hi);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
+}
+
+}  // extern "C"
+
+// Producers of GEMM operands: under the fp16 operand form the plane buffer is
+// filled by dlb_split_planes after the kernel (it needs the tensor's maximum).
+extern "C" {
+
+dlb_status dlb_time_major(dlb_ctx *ctx, const float *x, float *out, float *out_lo, int rows, int seq_w,
+                          int n) {
+  const bool defer = ctx && out_lo && ctx->gemm_kind == DLB_GEMM_F16X3;
+  DLB_TRY(time_major_impl(ctx, x, out, defer ? nullptr : out_lo, rows, seq_w, n));
+  return defer ? dlb_split_planes(ctx, out, out_lo, (size_t)seq_w * rows * n) : DLB_OK;
+}
+
+dlb_status dlb_indrnn_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
+                              const float *recurrent, int af, float *A, float *A_lo, int seq_w, int rows,
+                              int n) {
+  const bool defer = ctx && A_lo && ctx->gemm_kind == DLB_GEMM_F16X3;
+  DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, A, defer ? nullptr : A_lo, seq_w, rows, n));
+  return defer ? dlb_split_planes(ctx, A, A_lo, (size_t)seq_w * rows * n) : DLB_OK;
+}
+
+dlb_status dlb_brn_time_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
+                                       const dlb_brn_unit_arrays *u, const double *sums, int global_rows,
+                                       int seq_w, int rows, int n) {
+  const bool defer = ctx && delta_lo && ctx->gemm_kind == DLB_GEMM_F16X3;
+  DLB_TRY(brn_time_backward_apply_impl(ctx, delta, defer ? nullptr : delta_lo, Z, u, sums, global_rows, seq_w,
+                                       rows, n));
+  return defer ? dlb_split_planes(ctx, delta, delta_lo, (size_t)seq_w * rows * n) : DLB_OK;
 }
 
 }  // extern "C"

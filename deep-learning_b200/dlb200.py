@@ -58,6 +58,9 @@ SIGNATURES = {
     "dlb_host_alloc": (_i, [C.POINTER(_vp), _sz]),
     "dlb_host_free": (_i, [_vp]),
     "dlb_split_tf32": (_i, [_vp, _vp, _vp, _sz]),
+    "dlb_split_planes": (_i, [_vp, _vp, _vp, _sz]),
+    "dlb_ctx_set_gemm_kind": (_i, [_vp, _i]),
+    "dlb_ctx_gemm_kind": (_i, [_vp]),
     "dlb_fc_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "dlb_fc_backward_input": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "dlb_fc_weight_gradient": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
@@ -193,6 +196,13 @@ class Context:
 
     def set_tensor_core(self, on):
         check(self.L.dlb_ctx_set_tensor_core(self.h, int(on)), "dlb_ctx_set_tensor_core")
+
+    def set_gemm_kind(self, kind):
+        """0: 3xTF32 operands, 1: 3xFP16 planes (the default)."""
+        check(self.L.dlb_ctx_set_gemm_kind(self.h, int(kind)), "dlb_ctx_set_gemm_kind")
+
+    def gemm_kind(self):
+        return self.L.dlb_ctx_gemm_kind(self.h)
 
     def launch_count(self):
         return int(self.L.dlb_ctx_launch_count(self.h))

@@ -107,6 +107,28 @@ dlb_status dlb_host_free(void *host_ptr);
  * tensor; pass NULL and the library derives it into context scratch first. */
 dlb_status dlb_split_tf32(dlb_ctx *ctx, const float *x, float *x_lo, size_t n);
 
+/* The same product on fp16 tensor-core inputs ("3xFP16", the default): every
+ * operand tensor x is scaled by a power of two s chosen from max |x| so that
+ * s*max lies in [2^14, 2^15), and used as hi = fp16(s x), lo = fp16(s x - hi):
+ * 22 bits of every element that is within 2^-17 of the tensor's largest, an
+ * absolute floor of 2^-39 max below that.  The three products hi*hi, hi*lo,
+ * lo*hi run at twice the TF32 rate and are exact in the fp32 accumulator; the
+ * result is scaled back by 1 / (s_a s_b), exactly.
+ *
+ * Under this form the `_lo` argument of an entry point is the tensor's plane
+ * buffer: storage of the tensor's own byte size (n floats) that dlb_split_planes
+ * fills with the two fp16 planes, remembering the tensor, its size and the
+ * device slot of s under the buffer's address.  Entry points that produce an
+ * operand tensor and take a `_lo` output (dlb_activation_forward,
+ * dlb_brn_backward_apply, dlb_loss_delta, ...) fill it in whichever form the
+ * context is in, so a caller's code is the same for both.  A `_lo` pointer that
+ * was not written that way is ignored and the planes are derived per call. */
+enum { DLB_GEMM_TF32X3 = 0, DLB_GEMM_F16X3 = 1 };
+dlb_status dlb_ctx_set_gemm_kind(dlb_ctx *ctx, int kind);
+int dlb_ctx_gemm_kind(dlb_ctx *ctx);
+/* Plane buffer of x in the context's current form (TF32: dlb_split_tf32). */
+dlb_status dlb_split_planes(dlb_ctx *ctx, const float *x, float *planes, size_t n);
+
 /* ------------------------------------------------------------------------ */
 /* FC GEMMs. */
 

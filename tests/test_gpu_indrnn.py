@@ -127,8 +127,14 @@ def test_time_kernels(gpu_ctx, T, B, n, af):
         h[t] = fc_step.af_fire(af, pre[t])
     got_h = A.get()
     assert util.rel_l2(got_h, h) <= 1e-6
-    hi = got_h.view(np.uint32) & np.uint32(0xFFFFE000)
-    assert np.allclose(hi.view(np.float32) + A_lo.get(), got_h, rtol=0, atol=1e-6 * np.abs(got_h).max())
+    if ctx.gemm_kind() == 0:   # TF32 residual plane
+        hi = got_h.view(np.uint32) & np.uint32(0xFFFFE000)
+        assert np.allclose(hi.view(np.float32) + A_lo.get(), got_h, rtol=0, atol=1e-6 * np.abs(got_h).max())
+    else:                      # fp16 planes of s * h, s = 2^(14 - floor(log2 max|h|))
+        planes = A_lo.get().ravel().view(np.float16).astype(np.float64)
+        s = 2.0 ** (14 - np.floor(np.log2(np.abs(got_h).max())))
+        both = (planes[:got_h.size] + planes[got_h.size:]) / s
+        assert np.allclose(both, got_h.ravel(), rtol=2.0 ** -21, atol=2.0 ** -38 * np.abs(got_h).max())
     # reverse walk
     dA = rng.standard_normal((T, B, n)).astype(np.float32)
     E = ctx.array(dA)

@@ -62,13 +62,17 @@ SHAPES = [(128, 64, 256), (256, 512, 512), (384, 784, 256), (200, 96, 160), (512
 
 @pytest.mark.parametrize("kind", ["fwd", "dx", "dw"])
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
-@pytest.mark.parametrize("tensor_core", [1, 0], ids=["tcgen05", "cuda-core"])
+@pytest.mark.parametrize("tensor_core", [1, 2, 0], ids=["tcgen05-f16x3", "tcgen05-tf32x3", "cuda-core"])
 def test_fc_products(gpu_ctx, kind, shape, tensor_core):
     rows, n_in, n_out = shape
     rng = np.random.default_rng(hash((kind, shape)) % 2**32)
     A, Bm = _operands(kind, rows, n_in, n_out, rng)
     want = _exact(kind, A, Bm)
-    got = _fc(gpu_ctx, kind, A, Bm, rows, n_in, n_out, tensor_core)
+    gpu_ctx.set_gemm_kind(0 if tensor_core == 2 else 1)
+    try:
+        got = _fc(gpu_ctx, kind, A, Bm, rows, n_in, n_out, min(tensor_core, 1))
+    finally:
+        gpu_ctx.set_gemm_kind(1)
     if kind == "dw":
         got = got[0]
     assert util.rel_l2(got, want) <= GEMM_TOL
@@ -124,6 +128,43 @@ def test_products_whose_last_wave_is_split_along_k(gpu_ctx, kind):
     assert np.array_equal(runs[0], runs[1])
     assert util.rel_l2(runs[0], want) <= GEMM_TOL
     assert util.rel_max(runs[0], want) <= 5 * GEMM_TOL
+
+
+@pytest.mark.parametrize("gemm_kind", [1, 0], ids=["f16x3", "tf32x3"])
+def test_products_with_caller_kept_plane_buffers(gpu_ctx, gemm_kind):
+    """Plane buffers written by dlb_split_planes (and by a producing entry
+    point) are what the products read; operands of very different magnitude
+    (errors ~1e-7, weights ~1e-2) keep fp32-faithful precision."""
+    L = gpu_ctx.L
+    rng = np.random.default_rng(5)
+    rows, n_in, n_out = 512, 384, 640
+    delta = (rng.standard_normal((rows, n_out)) * 1e-7).astype(np.float32)
+    W = (rng.standard_normal((n_out, n_in)) * 0.02).astype(np.float32)
+    X = rng.standard_normal((rows, n_in), dtype=np.float32)
+    gpu_ctx.set_gemm_kind(gemm_kind)
+    try:
+        d, w, x = gpu_ctx.array(delta), gpu_ctx.array(W), gpu_ctx.array(X)
+        dp, wp, xp = gpu_ctx.empty(delta.shape), gpu_ctx.empty(W.shape), gpu_ctx.empty(X.shape)
+        for t, p in ((d, dp), (w, wp), (x, xp)):
+            check(L.dlb_split_planes(gpu_ctx.h, t.ptr, p.ptr, t.size))
+        z = gpu_ctx.empty((rows, n_out))
+        check(L.dlb_fc_forward(gpu_ctx.h, x.ptr, xp.ptr, w.ptr, wp.ptr, None, z.ptr, rows, n_in, n_out))
+        dx = gpu_ctx.empty((rows, n_in))
+        check(L.dlb_fc_backward_input(gpu_ctx.h, d.ptr, dp.ptr, w.ptr, wp.ptr, dx.ptr, rows, n_in, n_out))
+        dw = gpu_ctx.empty((n_out, n_in))
+        check(L.dlb_fc_weight_gradient(gpu_ctx.h, d.ptr, dp.ptr, x.ptr, xp.ptr, dw.ptr, None, rows, n_in, n_out, 0))
+        # a sub-view of the rows, as the time-stepped model uses for the last steps
+        half = rows // 2
+        dx2 = gpu_ctx.empty((half, n_in))
+        check(L.dlb_fc_backward_input(gpu_ctx.h, d.offset(half * n_out), dp.offset(half * n_out), w.ptr, wp.ptr,
+                                      dx2.ptr, half, n_in, n_out))
+        assert gpu_ctx.sync() == 0
+        assert util.rel_l2(z.get(), _exact("fwd", X, W)) <= GEMM_TOL
+        assert util.rel_l2(dx.get(), _exact("dx", delta, W)) <= GEMM_TOL
+        assert util.rel_l2(dw.get(), _exact("dw", delta, X)) <= GEMM_TOL
+        assert util.rel_l2(dx2.get(), _exact("dx", delta[half:], W)) <= GEMM_TOL
+    finally:
+        gpu_ctx.set_gemm_kind(1)
 
 
 def test_large_k_accumulation_stays_fp32_faithful(gpu_ctx):
@@ -192,8 +233,15 @@ def test_batch_renorm_forward(gpu_ctx, rows, n):
     got = A.get()
     assert util.rel_max(got, want) <= F32_TOL
     assert np.array_equal(got[:, mask == 0], np.zeros_like(got[:, mask == 0]))   # dropped units: exact zeros
-    hi = (got.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
-    assert np.all(np.abs(Alo.get() - (got - hi)) <= np.abs(got - hi) * 2.0 ** -11 + 1e-45)
+    if ctx.gemm_kind() == 0:   # TF32 residual plane
+        hi = (got.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+        assert np.all(np.abs(Alo.get() - (got - hi)) <= np.abs(got - hi) * 2.0 ** -11 + 1e-45)
+    else:                      # fp16 planes of s * A, s = 2^(14 - floor(log2 max|A|))
+        planes = Alo.get().ravel().view(np.float16).astype(np.float64)
+        s = 2.0 ** (14 - np.floor(np.log2(np.abs(got).max())))
+        assert np.abs(planes[:got.size]).max() < 2.0 ** 15
+        both = (planes[:got.size] + planes[got.size:]) / s
+        assert np.allclose(both, got.ravel(), rtol=2.0 ** -21, atol=2.0 ** -38 * np.abs(got).max())
 
 
 @pytest.mark.parametrize("af", [fc_step.AF_RELU, fc_step.AF_LEAKY_RELU, fc_step.AF_ELU, fc_step.AF_SELU,
