@@ -336,6 +336,9 @@ def run_ours(args, rank, local_rank, world):
     value = rows * world * args.steps / (ms / 1e3)
     achieved = g_flops / (g_ms / 1e3) / 1e12 if g_ms > 0 else 0.0
     peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
+    f16 = ctx.gemm_kind() == 1
+    x3_sustained = peak / 3 if f16 else TF32_TFLOPS_SUSTAINED / 3
+    x3_burst = float(peaks.get("bf16_tflops", peak)) / 3 if f16 else TF32_TFLOPS_BURST / 3
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -346,15 +349,22 @@ def run_ours(args, rank, local_rank, world):
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {
-            "kernel": "gemm_tf32x3_kernel (tcgen05 3xTF32 FC products)", "bound": "tensor",
+            "kernel": "gemm_x3_kernel (tcgen05, all FC products; " +
+                      ("3xFP16 planes, kind::f16" if f16 else "3xTF32, kind::tf32") + ")",
+            "bound": "tensor",
             "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
             "peak_source": f"MEASURED_PEAKS.json bf16 dense, sustained ({peak_kind})",
             "traffic": gemm_traffic_per_launch(),
             "launches_timed": g_n, "avg_launch_ms": g_ms / g_n if g_n else None,
             "share_of_step": g_ms / ms if ms else None,
-            "tf32x3": {"peak": TF32_TFLOPS_SUSTAINED / 3, "frac": achieved / (TF32_TFLOPS_SUSTAINED / 3),
-                       "peak_burst": TF32_TFLOPS_BURST / 3,
-                       "note": "fp32-equivalent ceiling of a 3xTF32 product: cuBLAS TF32 dense on this pool / 3"},
+            # `achieved` counts 2*M*N*K per launch; the kernel issues three
+            # tensor-core products per such FLOP, so its ceiling is a third of
+            # the dense peak of its input type and `issued` is what the pipe ran.
+            "split3": {"issued_tflops": 3 * achieved, "ceiling": x3_sustained, "frac": achieved / x3_sustained,
+                       "ceiling_burst": x3_burst,
+                       "note": "fp32-equivalent ceiling of a three-product split: dense peak of the input type / 3 ("
+                               + ("bf16/fp16 from MEASURED_PEAKS.json" if f16 else
+                                  "TF32 measured on this pool with cuBLAS: 745 burst, 591 sustained") + ")"},
         },
     }
     sample_rows = WORKLOADS[args.workload][1]

@@ -189,25 +189,55 @@ struct SmemPlan {
   static constexpr int B_BYTES = BN * BK * ES;
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int EPI_BYTES = NUM_DRAIN_WARPS * 32 * 33 * 4;  // reuses the ring
-  static constexpr int BAR_OFFSET = RING_BYTES;
+  static constexpr int EPI_OFFSET = RING_BYTES;  // per-warp transpose buffers of the epilogue
+  static constexpr int EPI_BYTES = NUM_DRAIN_WARPS * 32 * 33 * 4;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + EPI_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
-  static_assert(EPI_BYTES <= RING_BYTES, "transpose buffers live in the idle ring");
+  static_assert(TOTAL <= 232448, "shared memory of one CTA");
 };
+
+// One unit of work: an output tile over a range of k blocks.  Output tiles are
+// numbered row-major over (m block, n block); items [0, whole_tiles) are whole
+// tiles.  The remaining tiles (those that would form a last, partly filled
+// wave over the SMs) are two items each, one per half of the k range, which
+// add their partial results into an output the host has zeroed: with exactly
+// two addends the sum does not depend on which half arrives first.
+struct WorkItem {
+  int m0, n0, kb_begin, num_kb, split, k_half;
+};
+template <int BN, int CHUNK_KB>
+__device__ __forceinline__ WorkItem work_item(int item, int tiles_n, int whole_tiles, int total_kb) {
+  WorkItem w;
+  w.split = item >= whole_tiles;
+  const int tile_id = w.split ? whole_tiles + ((item - whole_tiles) >> 1) : item;
+  w.k_half = w.split ? ((item - whole_tiles) & 1) : 0;
+  w.n0 = (tile_id % tiles_n) * BN;
+  w.m0 = (tile_id / tiles_n) * BM;
+  const int mid_kb = min(total_kb, (total_kb / 2 + CHUNK_KB - 1) / CHUNK_KB * CHUNK_KB);
+  w.kb_begin = (w.split && w.k_half) ? mid_kb : 0;
+  w.num_kb = (w.split ? (w.k_half ? total_kb : mid_kb) : total_kb) - w.kb_begin;
+  return w;
+}
 
 // Barrier slots: [0,S) full, [S,2S) empty, 2S..2S+1 accumulator full,
 // 2S+2..2S+3 accumulator empty, then three 8-byte scalars.
 // ES = 4: fp32 operands read as TF32 plus their TF32 residual planes.
 // ES = 2: fp16 planes hi = fp16(s x), lo = fp16(s x - hi) of every operand,
 // s a power of two per tensor; the result is scaled back by 1 / (s_a s_b).
+//
+// Persistent: the grid is one CTA per SM (or fewer), and CTA c works through
+// items c, c + gridDim.x, ...  The stage ring, the two accumulator buffers and
+// their barrier phases run on across items, so the producer prefetches the
+// next item's operands and the tensor core starts its first chunks while the
+// drain warps still write the previous tile.
 template <int BN, int BK, int STAGES, int CHUNK_KB, bool A_MN, bool B_MN, int ES>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
-                       const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
-                       float *__restrict__ C, long long ldc, int M, int N, int K,
-                       const float *__restrict__ bias, int accumulate, int tiles_n, int whole_tiles,
-                       const float *__restrict__ scale_a, const float *__restrict__ scale_b,
-                       int *status) {
+                   const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
+                   float *__restrict__ C, long long ldc, int M, int N, int K,
+                   const float *__restrict__ bias, int accumulate, int tiles_n, int whole_tiles,
+                   int total_items, const float *__restrict__ scale_a,
+                   const float *__restrict__ scale_b, int *status) {
   using P = SmemPlan<BN, BK, STAGES, ES>;
   static_assert(ES == 4 || ES == 2, "fp32 (TF32) or fp16 operands");
   constexpr int MN_W = 128 / ES;  // elements of one 128-byte column of an MN-major tile
@@ -221,25 +251,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P::BAR_OFFSET);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * STAGES + 4);
   uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 5);
-  int *issued_kb = reinterpret_cast<int *>(bars + 2 * STAGES + 6);
+  unsigned *issued_kb = reinterpret_cast<unsigned *>(bars + 2 * STAGES + 6);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  // Work of this CTA.  Output tiles are numbered row-major over (m block, n
-  // block); CTAs [0, whole_tiles) own one tile each over the full k range.
-  // The remaining tiles (the ones that would form a last, partly filled wave
-  // over the SMs) are each shared by two CTAs, one per half of the k range,
-  // which add their partial results into an output the host has zeroed: with
-  // exactly two addends the sum does not depend on which half arrives first.
-  const int lin = blockIdx.x;
-  const bool split = lin >= whole_tiles;
-  const int tile_id = split ? whole_tiles + ((lin - whole_tiles) >> 1) : lin;
-  const int k_half = split ? ((lin - whole_tiles) & 1) : 0;
-  const int n0 = (tile_id % tiles_n) * BN, m0 = (tile_id / tiles_n) * BM;
   const int total_kb = (K + BK - 1) / BK;
-  const int mid_kb = min(total_kb, (total_kb / 2 + CHUNK_KB - 1) / CHUNK_KB * CHUNK_KB);
-  const int kb_begin = (split && k_half) ? mid_kb : 0;
-  const int num_kb = (split ? (k_half ? total_kb : mid_kb) : total_kb) - kb_begin;  // k blocks of this CTA
-  const int num_chunks = (num_kb + CHUNK_KB - 1) / CHUNK_KB;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES),
                  acc_full0 = smem_u32(bars + 2 * STAGES), acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
 
@@ -272,35 +287,41 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, status)) break;
-        const uint32_t fb = full0 + 8 * s;
-        const uint32_t st = base + s * P::STAGE_BYTES;
-        mbar_expect_tx(fb, P::STAGE_BYTES);
-        const int k0 = (kb_begin + kb) * BK;
-        if (A_MN) {
-          tma_load_3d(st, &tm_a, fb, 0, k0, m0 / MN_W);
-          tma_load_3d(st + P::A_BYTES, &tm_a_lo, fb, 0, k0, m0 / MN_W);
-        } else {
-          tma_load_2d(st, &tm_a, fb, k0, m0);
-          tma_load_2d(st + P::A_BYTES, &tm_a_lo, fb, k0, m0);
+      unsigned it = 0;  // k blocks issued by this CTA so far, over all items
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const WorkItem w = work_item<BN, CHUNK_KB>(item, tiles_n, whole_tiles, total_kb);
+        for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
+          const unsigned s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, status);
+          if (!ok) break;
+          const uint32_t fb = full0 + 8 * s;
+          const uint32_t st = base + s * P::STAGE_BYTES;
+          mbar_expect_tx(fb, P::STAGE_BYTES);
+          const int k0 = (w.kb_begin + kb) * BK;
+          if (A_MN) {
+            tma_load_3d(st, &tm_a, fb, 0, k0, w.m0 / MN_W);
+            tma_load_3d(st + P::A_BYTES, &tm_a_lo, fb, 0, k0, w.m0 / MN_W);
+          } else {
+            tma_load_2d(st, &tm_a, fb, k0, w.m0);
+            tma_load_2d(st + P::A_BYTES, &tm_a_lo, fb, k0, w.m0);
+          }
+          if (B_MN) {
+            tma_load_3d(st + 2 * P::A_BYTES, &tm_b, fb, 0, k0, w.n0 / MN_W);
+            tma_load_3d(st + 2 * P::A_BYTES + P::B_BYTES, &tm_b_lo, fb, 0, k0, w.n0 / MN_W);
+          } else {
+            tma_load_2d(st + 2 * P::A_BYTES, &tm_b, fb, k0, w.n0);
+            tma_load_2d(st + 2 * P::A_BYTES + P::B_BYTES, &tm_b_lo, fb, k0, w.n0);
+          }
+          *issued_kb = it + 1;
         }
-        if (B_MN) {
-          tma_load_3d(st + 2 * P::A_BYTES, &tm_b, fb, 0, k0, n0 / MN_W);
-          tma_load_3d(st + 2 * P::A_BYTES + P::B_BYTES, &tm_b_lo, fb, 0, k0, n0 / MN_W);
-        } else {
-          tma_load_2d(st + 2 * P::A_BYTES, &tm_b, fb, k0, n0);
-          tma_load_2d(st + 2 * P::A_BYTES + P::B_BYTES, &tm_b_lo, fb, k0, n0);
-        }
-        *issued_kb = kb + 1;
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      // Instruction descriptor: fp32 accumulate, TF32 A and B, majors, N, M.
+      // Instruction descriptor: fp32 accumulate, operand format, majors, N, M.
       constexpr uint32_t FMT = ES == 4 ? 2u : 0u;  // operand format: TF32 / F16
       const uint32_t idesc = (1u << 4) | (FMT << 7) | (FMT << 10) | ((A_MN ? 1u : 0u) << 15) |
                              ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
@@ -322,85 +343,94 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       constexpr uint32_t B_LAYOUT = B_MN ? MN_LAYOUT : K_LAYOUT;
       constexpr uint32_t A_KSTEP = A_MN ? KI * 128 : 32, B_KSTEP = B_MN ? KI * 128 : 32;
       bool ok = true;
-      int kb = 0;
-      for (int c = 0; c < num_chunks && ok; ++c) {
-        const int buf = c & 1;
-        const uint32_t use = (uint32_t)(c >> 1);
-        // The drain warps must have emptied this buffer's previous chunk.
-        ok = mbar_wait(acc_empty0 + 8 * buf, (use & 1) ^ 1, abort_flag, status);
-        if (!ok) break;
-        tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_acc + (uint32_t)(buf * BN);
-        const int kb_end = min(num_kb, kb + CHUNK_KB);
-        bool first = true;
-        for (; kb < kb_end; ++kb) {
-          const int s = kb % STAGES;
-          const uint32_t ph = (kb / STAGES) & 1;
-          ok = mbar_wait(full0 + 8 * s, ph, abort_flag, status);
+      unsigned it = 0;  // k blocks consumed so far, over all items
+      unsigned cc = 0;  // chunks started so far, over all items
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const WorkItem w = work_item<BN, CHUNK_KB>(item, tiles_n, whole_tiles, total_kb);
+        int kb = 0;
+        while (kb < w.num_kb && ok) {
+          const unsigned buf = cc & 1, use = cc >> 1;
+          // The drain warps must have emptied this buffer's previous chunk.
+          ok = mbar_wait(acc_empty0 + 8 * buf, (use & 1) ^ 1, abort_flag, status);
           if (!ok) break;
           tcgen05_fence_after();
-          const uint32_t st = base + s * P::STAGE_BYTES;
-          const uint32_t a_hi = st, a_lo = st + P::A_BYTES, b_hi = st + 2 * P::A_BYTES,
-                         b_lo = st + 2 * P::A_BYTES + P::B_BYTES;
+          const uint32_t d_tmem = tmem_acc + (uint32_t)(buf * BN);
+          const int kb_end = min(w.num_kb, kb + CHUNK_KB);
+          bool first = true;
+          for (; kb < kb_end; ++kb, ++it) {
+            const unsigned s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            ok = mbar_wait(full0 + 8 * s, ph, abort_flag, status);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const uint32_t st = base + s * P::STAGE_BYTES;
+            const uint32_t a_hi = st, a_lo = st + P::A_BYTES, b_hi = st + 2 * P::A_BYTES,
+                           b_lo = st + 2 * P::A_BYTES + P::B_BYTES;
 #pragma unroll
-          for (int k8 = 0; k8 < BK / KI; ++k8) {
-            const uint64_t da_hi = make_smem_desc(a_hi + k8 * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
-            const uint64_t da_lo = make_smem_desc(a_lo + k8 * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
-            const uint64_t db_hi = make_smem_desc(b_hi + k8 * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
-            const uint64_t db_lo = make_smem_desc(b_lo + k8 * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
-            if (ES == 4) {
-              umma_tf32(d_tmem, da_lo, db_hi, idesc, first ? 0u : 1u);
-              umma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
-              umma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
-            } else {
-              umma_f16(d_tmem, da_lo, db_hi, idesc, first ? 0u : 1u);
-              umma_f16(d_tmem, da_hi, db_lo, idesc, 1u);
-              umma_f16(d_tmem, da_hi, db_hi, idesc, 1u);
+            for (int k8 = 0; k8 < BK / KI; ++k8) {
+              const uint64_t da_hi = make_smem_desc(a_hi + k8 * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+              const uint64_t da_lo = make_smem_desc(a_lo + k8 * A_KSTEP, A_LBO, A_SBO, A_LAYOUT);
+              const uint64_t db_hi = make_smem_desc(b_hi + k8 * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+              const uint64_t db_lo = make_smem_desc(b_lo + k8 * B_KSTEP, B_LBO, B_SBO, B_LAYOUT);
+              if (ES == 4) {
+                umma_tf32(d_tmem, da_lo, db_hi, idesc, first ? 0u : 1u);
+                umma_tf32(d_tmem, da_hi, db_lo, idesc, 1u);
+                umma_tf32(d_tmem, da_hi, db_hi, idesc, 1u);
+              } else {
+                umma_f16(d_tmem, da_lo, db_hi, idesc, first ? 0u : 1u);
+                umma_f16(d_tmem, da_hi, db_lo, idesc, 1u);
+                umma_f16(d_tmem, da_hi, db_hi, idesc, 1u);
+              }
+              first = false;
             }
-            first = false;
+            umma_commit(empty0 + 8 * s);  // stage reusable once these MMAs retire
           }
-          umma_commit(empty0 + 8 * s);  // stage reusable once these MMAs retire
+          if (ok) umma_commit(acc_full0 + 8 * buf);  // chunk complete
+          ++cc;
         }
-        if (ok) umma_commit(acc_full0 + 8 * buf);  // chunk complete
       }
     }
   } else {
     // ---------------- drain + epilogue: warps 2..9 ----------------
     const int q = warp & 3;          // tensor-memory lane quadrant this warp may read
     const int h = (warp - 2) >> 2;   // which half of the BN columns
+    float *tile = reinterpret_cast<float *>(smem + P::EPI_OFFSET) + (warp - 2) * 32 * 33;
+    // fp16 planes hold s x: both factors are powers of two, the scaling is exact.
+    const float out_a = ES == 2 ? 1.f / __ldg(scale_a) : 1.f, out_b = ES == 2 ? 1.f / __ldg(scale_b) : 1.f;
     float acc[HALF];
-#pragma unroll
-    for (int j = 0; j < HALF; ++j) acc[j] = 0.f;
     bool ok = true;
-    for (int c = 0; c < num_chunks; ++c) {
-      const int buf = c & 1;
-      const uint32_t use = (uint32_t)(c >> 1);
-      ok = mbar_wait(acc_full0 + 8 * buf, use & 1, abort_flag, status);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tcgen05_fence_after();
-      const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + h * HALF);
+    unsigned cc = 0;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const WorkItem w = work_item<BN, CHUNK_KB>(item, tiles_n, whole_tiles, total_kb);
+      const int num_chunks = (w.num_kb + CHUNK_KB - 1) / CHUNK_KB;
 #pragma unroll
-      for (int j = 0; j < HALF / 32; ++j) {
-        uint32_t v[32];
-        tmem_ld32(taddr + j * 32, v);
+      for (int j = 0; j < HALF; ++j) acc[j] = 0.f;
+      for (int c = 0; c < num_chunks; ++c, ++cc) {
+        const unsigned buf = cc & 1, use = cc >> 1;
+        ok = mbar_wait(acc_full0 + 8 * buf, use & 1, abort_flag, status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + h * HALF);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[j * 32 + i] += __uint_as_float(v[i]);
+        for (int j = 0; j < HALF / 32; ++j) {
+          uint32_t v[32];
+          tmem_ld32(taddr + j * 32, v);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[j * 32 + i] += __uint_as_float(v[i]);
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
-    }
-    if (ok) {
-      // All MMAs have retired (the last chunk was committed), so the operand
-      // ring is idle and serves as the transpose buffer.
-      float *tile = reinterpret_cast<float *>(smem) + (warp - 2) * 32 * 33;
-      const int row_base = m0 + q * 32;
-      // fp16 planes hold s x: both factors are powers of two, the scaling is exact.
-      const float out_a = ES == 2 ? 1.f / __ldg(scale_a) : 1.f, out_b = ES == 2 ? 1.f / __ldg(scale_b) : 1.f;
+      if (!ok) break;
+      // The tile is complete in registers; the tensor core is already on the
+      // next item.  Rows go out through the warp's transpose buffer so that
+      // each store instruction covers 128 contiguous bytes.
+      const int row_base = w.m0 + q * 32;
 #pragma unroll
       for (int j = 0; j < HALF / 32; ++j) {
-        const int col0 = n0 + h * HALF + j * 32;
+        const int col0 = w.n0 + h * HALF + j * 32;
         if (col0 < N) {
           // lane owns row (row_base + lane): park its 32 values, then each
           // instruction below stores one row's 32 consecutive floats.
@@ -410,8 +440,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           __syncwarp();
           const int col = col0 + lane;
           if (col < N) {
-            const float b = (bias && k_half == 0) ? __ldg(bias + col) : 0.f;
-            if (split) {
+            const float b = (bias && w.k_half == 0) ? __ldg(bias + col) : 0.f;
+            if (w.split) {
 #pragma unroll 4
               for (int r = 0; r < 32; ++r) {
                 const int row = row_base + r;
@@ -442,10 +472,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   if (*abort_flag && threadIdx.x == 0) {
     // Let TMA loads that were already issued land before the CTA's shared
     // memory is handed to another block.
-    const int issued = *issued_kb;
+    const unsigned issued = *issued_kb;
     const long long t0 = clock64();
-    for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
-      const int s = kb % STAGES;
+    for (unsigned kb = issued > (unsigned)STAGES ? issued - STAGES : 0; kb < issued; ++kb) {
+      const unsigned s = kb % STAGES;
       const uint32_t ph = (kb / STAGES) & 1;
       while (!mbar_try_wait(full0 + 8 * s, ph)) {
         if (clock64() - t0 > DRAIN_BUDGET_CLOCKS) break;
@@ -602,9 +632,10 @@ dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, floa
     DLB_CUDA(cudaMemset2DAsync(C + (long long)first_row * ldc, (size_t)ldc * sizeof(float), 0,
                                (size_t)N * sizeof(float), (size_t)(M - first_row), ctx->stream));
   }
-  kernel<<<whole_tiles + 2 * split_tiles, NUM_THREADS, P::TOTAL, ctx->stream>>>(
-      ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, A.scale, B.scale,
-      ctx->d_status);
+  const int items = whole_tiles + 2 * split_tiles;
+  kernel<<<min(items, ctx->sm_count), NUM_THREADS, P::TOTAL, ctx->stream>>>(
+      ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, items, A.scale,
+      B.scale, ctx->d_status);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
