@@ -293,8 +293,9 @@ __device__ __forceinline__ float apply_dropout(float a, const DropoutDev &dp, in
 template <bool NORM, bool VEC4>
 __global__ void activation_forward_kernel(const float *__restrict__ Z, BrnPtrs u, int af,
                                           DropoutDev dp, float *__restrict__ A,
-                                          float *__restrict__ A_lo, int rows, int n) {
+                                          float *__restrict__ A_lo, int rows, int n, unsigned *amax) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
+  unsigned mx = 0;
   if (VEC4) {
     const int n4 = n / 4;
     const size_t total = (size_t)rows * n4;
@@ -311,6 +312,7 @@ __global__ void activation_forward_kernel(const float *__restrict__ Z, BrnPtrs u
         }
         out[j] = apply_dropout(af_fire(af, y), dp, col + j, i * 4 + j);
         lo[j] = tf32_lo(out[j]);
+        mx = max(mx, abs_bits(out[j]));
       }
       reinterpret_cast<float4 *>(A)[i] = make_float4(out[0], out[1], out[2], out[3]);
       if (A_lo) reinterpret_cast<float4 *>(A_lo)[i] = make_float4(lo[0], lo[1], lo[2], lo[3]);
@@ -326,9 +328,11 @@ __global__ void activation_forward_kernel(const float *__restrict__ Z, BrnPtrs u
       }
       const float a = apply_dropout(af_fire(af, y), dp, col, i);
       A[i] = a;
+      mx = max(mx, abs_bits(a));
       if (A_lo) A_lo[i] = tf32_lo(a);
     }
   }
+  amax_commit(amax, mx);
 }
 
 // One warp per row.  ref: fwp_mp.cpp L:4772-4807 (max, exp(x-max), * 1/sum).
@@ -356,8 +360,9 @@ template <bool VEC4>
 __global__ void brn_backward_apply_kernel(float *__restrict__ delta, float *__restrict__ delta_lo,
                                           const float *__restrict__ Z, BrnPtrs u,
                                           const double *__restrict__ sums, float inv_rows,
-                                          float rows_f, int rows, int n) {
+                                          float rows_f, int rows, int n, unsigned *amax) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
+  unsigned mx = 0;
   const double *d_mean = sums + 2 * (size_t)n, *d_sigma = sums + 3 * (size_t)n;
   auto one = [&](float e, float z, int col) {
     const BrnCol c = u.at(col);
@@ -377,6 +382,7 @@ __global__ void brn_backward_apply_kernel(float *__restrict__ delta, float *__re
       const float4 z = __ldg(reinterpret_cast<const float4 *>(Z) + i);
       e.x = one(e.x, z.x, col); e.y = one(e.y, z.y, col + 1);
       e.z = one(e.z, z.z, col + 2); e.w = one(e.w, z.w, col + 3);
+      mx = max(max(mx, abs_bits(e.x)), max(abs_bits(e.y), max(abs_bits(e.z), abs_bits(e.w))));
       reinterpret_cast<float4 *>(delta)[i] = e;
       if (delta_lo)
         reinterpret_cast<float4 *>(delta_lo)[i] =
@@ -387,9 +393,11 @@ __global__ void brn_backward_apply_kernel(float *__restrict__ delta, float *__re
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
       const float t = one(delta[i], Z[i], (int)(i % n));
       delta[i] = t;
+      mx = max(mx, abs_bits(t));
       if (delta_lo) delta_lo[i] = tf32_lo(t);
     }
   }
+  amax_commit(amax, mx);
 }
 
 template <bool VEC4>
@@ -423,11 +431,12 @@ __global__ void activation_backward_plain_kernel(float *__restrict__ dA, const f
 __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
     activation_forward_rows_kernel(const float *__restrict__ Z, BrnPtrs u, int af, DropoutDev dp,
                                    float *__restrict__ A, float *__restrict__ A_lo, int rows, int n,
-                                   int rows_per_chunk) {
+                                   int rows_per_chunk, unsigned *amax) {
   const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
   const int col = blockIdx.x * CR_COLS + tx * 4;
   if (col >= n) return;
   const int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+  unsigned mx = 0;
   BrnCol c[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) c[j] = u.at(col + j);
@@ -441,21 +450,24 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
       const float y = brn_norm(brn_hat(zz[j], c[j]), c[j]);
       out[j] = apply_dropout(af_fire(af, y), dp, col + j, o + j);
       lo[j] = tf32_lo(out[j]);
+      mx = max(mx, abs_bits(out[j]));
     }
     *reinterpret_cast<float4 *>(A + o) = make_float4(out[0], out[1], out[2], out[3]);
     if (A_lo) *reinterpret_cast<float4 *>(A_lo + o) = make_float4(lo[0], lo[1], lo[2], lo[3]);
   }
+  amax_commit(amax, mx);
 }
 
 __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
     brn_backward_apply_rows_kernel(float *__restrict__ delta, float *__restrict__ delta_lo,
                                    const float *__restrict__ Z, BrnPtrs u,
                                    const double *__restrict__ sums, float inv_rows, float rows_f,
-                                   int rows, int n, int rows_per_chunk) {
+                                   int rows, int n, int rows_per_chunk, unsigned *amax) {
   const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
   const int col = blockIdx.x * CR_COLS + tx * 4;
   if (col >= n) return;
   const int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+  unsigned mx = 0;
   // Per-unit factors in the reference's grouping (bwp_mp.cpp L:1608-1621):
   // r / sigma, N * sigma, d_sigma, d_mean / N.
   float gamma[4], mean[4], r_over_sigma[4], n_sigma[4], d_sigma[4], d_mean_n[4];
@@ -482,12 +494,14 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
       v += d_sigma[j] * ((z[j] - mean[j]) / n_sigma[j]);
       v += d_mean_n[j];
       t[j] = v;
+      mx = max(mx, abs_bits(v));
     }
     *reinterpret_cast<float4 *>(delta + o) = make_float4(t[0], t[1], t[2], t[3]);
     if (delta_lo)
       *reinterpret_cast<float4 *>(delta_lo + o) =
           make_float4(tf32_lo(t[0]), tf32_lo(t[1]), tf32_lo(t[2]), tf32_lo(t[3]));
   }
+  amax_commit(amax, mx);
 }
 
 __global__ void brn_finalize_kernel(const double *__restrict__ sums, int n, float batch_scale,
@@ -537,9 +551,10 @@ __global__ void sums_to_bias_grad_kernel(const double *__restrict__ sums, int n,
 __global__ void loss_delta_mse_kernel(const float *__restrict__ pre, const float *__restrict__ q,
                                       const float *__restrict__ y, float *__restrict__ delta,
                                       float *__restrict__ delta_lo, int af, size_t total,
-                                      float denom, double *loss_sum) {
+                                      float denom, double *loss_sum, unsigned *amax) {
   __shared__ double red[8];
   double local = 0.0;
+  unsigned mx = 0;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const float qq = q[i], yy = y[i];
@@ -549,8 +564,10 @@ __global__ void loss_delta_mse_kernel(const float *__restrict__ pre, const float
     dl /= denom;
     const float e = af_derive(af, pre[i], qq) * dl;
     delta[i] = e;
+    mx = max(mx, abs_bits(e));
     if (delta_lo) delta_lo[i] = tf32_lo(e);
   }
+  amax_commit(amax, mx);
   for (int o = 16; o; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
   if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = local;
   __syncthreads();
@@ -564,9 +581,11 @@ __global__ void loss_delta_mse_kernel(const float *__restrict__ pre, const float
 // Softmax + cross-entropy, one warp per row.
 __global__ void loss_delta_softmax_ce_kernel(const float *__restrict__ q, const float *__restrict__ y,
                                              float *__restrict__ delta, float *__restrict__ delta_lo,
-                                             int rows, int n, float rows_global, double *loss_sum) {
+                                             int rows, int n, float rows_global, double *loss_sum,
+                                             unsigned *amax) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
   double local = 0.0;
+  unsigned mx = 0;
   if (warp < rows) {
     const float *qr = q + (size_t)warp * n, *yr = y + (size_t)warp * n;
     const float EPS = 1e-7f;
@@ -583,10 +602,12 @@ __global__ void loss_delta_softmax_ce_kernel(const float *__restrict__ q, const 
         }
       }
       delta[(size_t)warp * n + j] = e;
+      mx = max(mx, abs_bits(e));
       if (delta_lo) delta_lo[(size_t)warp * n + j] = tf32_lo(e);
       if (yr[j] == 1.f) local += (double)(-(yr[j] * logf(clipf(qj, EPS, 1.f - EPS))));
     }
   }
+  amax_commit(amax, mx);
   for (int o = 16; o; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
   if (lane == 0 && local != 0.0) atomicAdd(loss_sum, local);
 }
@@ -630,7 +651,7 @@ dlb_status dlb_brn_forward_finalize(dlb_ctx *ctx, const double *sums, int global
 
 dlb_status activation_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
                                   int af, const dlb_dropout_desc *dropout, float *A,
-                                  float *A_lo, int rows, int n_units) {
+                                  float *A_lo, int rows, int n_units, unsigned *amax) {
   DLB_REQUIRE(ctx && Z && A && rows > 0 && n_units > 0, "dlb_activation_forward");
   DropoutDev dp{DLB_DROPOUT_NONE, 1.f, nullptr, nullptr};
   if (dropout && dropout->type != DLB_DROPOUT_NONE) {
@@ -660,7 +681,7 @@ dlb_status activation_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_u
     rows_plan(ctx, rows, n_units, &chunks, &rpc);
     activation_forward_rows_kernel<<<dim3(ceil_div(n_units, CR_COLS), chunks),
                                      CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
-        Z, p, af, dp, A, A_lo, rows, n_units, rpc);
+        Z, p, af, dp, A, A_lo, rows, n_units, rpc, amax);
     DLB_LAUNCHED(ctx);
     return DLB_OK;
   }
@@ -668,7 +689,7 @@ dlb_status activation_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_u
   const int grid = stream_grid(ctx, items, 256);
 #define LAUNCH(NORM, V)                                                                 \
   activation_forward_kernel<NORM, V><<<grid, 256, 0, ctx->stream>>>(Z, p, af, dp, A, A_lo, rows, \
-                                                                    n_units)
+                                                                    n_units, amax)
   if (u) { if (vec4) LAUNCH(true, true); else LAUNCH(true, false); }
   else   { if (vec4) LAUNCH(false, true); else LAUNCH(false, false); }
 #undef LAUNCH
@@ -710,7 +731,7 @@ dlb_status dlb_activation_backward(dlb_ctx *ctx, float *dA, const float *Z, cons
 
 dlb_status brn_backward_apply_impl(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
                                   const dlb_brn_unit_arrays *u, const double *sums,
-                                  int global_rows, int rows, int n_units) {
+                                  int global_rows, int rows, int n_units, unsigned *amax) {
   DLB_REQUIRE(ctx && delta && Z && u && sums && rows > 0 && n_units > 0 && global_rows > 0,
               "dlb_brn_backward_apply");
   const bool vec4 = (n_units % 4 == 0) && ((reinterpret_cast<uintptr_t>(Z) & 15) == 0) &&
@@ -724,10 +745,10 @@ dlb_status brn_backward_apply_impl(dlb_ctx *ctx, float *delta, float *delta_lo, 
     rows_plan(ctx, rows, n_units, &chunks, &rpc);
     brn_backward_apply_rows_kernel<<<dim3(ceil_div(n_units, CR_COLS), chunks),
                                      CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
-        delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc);
+        delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc, amax);
   } else
     brn_backward_apply_kernel<false><<<grid, 256, 0, ctx->stream>>>(
-        delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units);
+        delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -743,7 +764,7 @@ dlb_status dlb_brn_backward_param_grads(dlb_ctx *ctx, const double *sums, int n_
 
 dlb_status loss_delta_impl(dlb_ctx *ctx, int loss, int af, const float *pre, const float *q,
                           const float *y, float *delta, float *delta_lo, int rows, int n_out,
-                          int global_rows, double *loss_sum) {
+                          int global_rows, double *loss_sum, unsigned *amax) {
   DLB_REQUIRE(ctx && q && y && delta && loss_sum && rows > 0 && n_out > 0 && global_rows > 0,
               "dlb_loss_delta");
   if (loss == DLB_LOSS_MSE && af != DLB_AF_SOFTMAX) {
@@ -752,13 +773,13 @@ dlb_status loss_delta_impl(dlb_ctx *ctx, int loss, int af, const float *pre, con
     // loss_fn_derivative divides by static_cast<real>(bs * n_out).
     const float denom = (float)((size_t)global_rows * (size_t)n_out);
     loss_delta_mse_kernel<<<stream_grid(ctx, total, 256), 256, 0, ctx->stream>>>(
-        pre, q, y, delta, delta_lo, af, total, denom, loss_sum);
+        pre, q, y, delta, delta_lo, af, total, denom, loss_sum, amax);
     DLB_LAUNCHED(ctx);
     return DLB_OK;
   }
   if (loss == DLB_LOSS_CROSS_ENTROPY && af == DLB_AF_SOFTMAX) {
     loss_delta_softmax_ce_kernel<<<ceil_div(rows, 8), 256, 0, ctx->stream>>>(
-        q, y, delta, delta_lo, rows, n_out, (float)global_rows, loss_sum);
+        q, y, delta, delta_lo, rows, n_out, (float)global_rows, loss_sum, amax);
     DLB_LAUNCHED(ctx);
     return DLB_OK;
   }
@@ -793,8 +814,10 @@ namespace dlb {
 __global__ void residual_forward_kernel(const float *__restrict__ x, float *__restrict__ block,
                                         const uint8_t *__restrict__ row_mask,
                                         const float *__restrict__ noise, float *__restrict__ out,
-                                        float *__restrict__ out_lo, int rows, int width, int vec) {
+                                        float *__restrict__ out_lo, int rows, int width, int vec,
+                                        unsigned *amax) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
+  unsigned mx = 0;
   if (vec) {
     const int w4 = width / 4;
     const size_t total = (size_t)rows * w4;
@@ -808,6 +831,7 @@ __global__ void residual_forward_kernel(const float *__restrict__ x, float *__re
       }
       const float4 s = __ldg(reinterpret_cast<const float4 *>(x) + i);
       const float4 v = make_float4(s.x + o.x, s.y + o.y, s.z + o.z, s.w + o.w);
+      mx = max(max(mx, abs_bits(v.x)), max(abs_bits(v.y), max(abs_bits(v.z), abs_bits(v.w))));
       reinterpret_cast<float4 *>(out)[i] = v;
       if (out_lo)
         reinterpret_cast<float4 *>(out_lo)[i] =
@@ -824,32 +848,38 @@ __global__ void residual_forward_kernel(const float *__restrict__ x, float *__re
       }
       const float v = x[i] + o;
       out[i] = v;
+      mx = max(mx, abs_bits(v));
       if (out_lo) out_lo[i] = tf32_lo(v);
     }
   }
+  amax_commit(amax, mx);
 }
 
 // delta = d * noise on flagged rows, d elsewhere, plus its residual plane.
 __global__ void shakedrop_backward_kernel(const float *__restrict__ d,
                                           const uint8_t *__restrict__ row_mask,
                                           const float *__restrict__ noise, float *__restrict__ delta,
-                                          float *__restrict__ delta_lo, int rows, int width) {
+                                          float *__restrict__ delta_lo, int rows, int width,
+                                          unsigned *amax) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t total = (size_t)rows * width;
+  unsigned mx = 0;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const int r = (int)(i / width);
     float v = d[i];
     if (row_mask && row_mask[r]) v *= noise[i];
     delta[i] = v;
+    mx = max(mx, abs_bits(v));
     if (delta_lo) delta_lo[i] = tf32_lo(v);
   }
+  amax_commit(amax, mx);
 }
 
 }  // namespace dlb
 
 static dlb_status residual_forward_impl(dlb_ctx *ctx, const float *x, float *block,
                                            const uint8_t *row_mask, const float *noise, float *out,
-                                           float *out_lo, int rows, int width) {
+                                           float *out_lo, int rows, int width, unsigned *amax) {
   DLB_REQUIRE(ctx && x && block && out && rows > 0 && width > 0, "dlb_residual_forward");
   DLB_REQUIRE(!row_mask || noise, "dlb_residual_forward: row flags need the noise draws");
   const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(block) |
@@ -858,18 +888,18 @@ static dlb_status residual_forward_impl(dlb_ctx *ctx, const float *x, float *blo
   const int vec = (width % 4 == 0) && (al & 15) == 0;
   const size_t items = vec ? (size_t)rows * (width / 4) : (size_t)rows * width;
   residual_forward_kernel<<<stream_grid(ctx, items, 256), 256, 0, ctx->stream>>>(
-      x, block, row_mask, noise, out, out_lo, rows, width, vec);
+      x, block, row_mask, noise, out, out_lo, rows, width, vec, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
 
 static dlb_status shakedrop_backward_impl(dlb_ctx *ctx, const float *d, const uint8_t *row_mask,
                                              const float *noise, float *delta, float *delta_lo,
-                                             int rows, int width) {
+                                             int rows, int width, unsigned *amax) {
   DLB_REQUIRE(ctx && d && delta && rows > 0 && width > 0, "dlb_shakedrop_backward");
   DLB_REQUIRE(!row_mask || noise, "dlb_shakedrop_backward: row flags need the noise draws");
   shakedrop_backward_kernel<<<stream_grid(ctx, (size_t)rows * width, 256), 256, 0, ctx->stream>>>(
-      d, row_mask, noise, delta, delta_lo, rows, width);
+      d, row_mask, noise, delta, delta_lo, rows, width, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -956,16 +986,24 @@ extern "C" dlb_status dlb_brn_forward_sums_noalloc(const float *Z, int rows, int
 // ---------------------------------------------------------------------------
 namespace {
 struct PlaneOutput {
-  float *kernel_arg;  // what the producing kernel receives
-  float *deferred;    // buffer to split into afterwards, or nullptr
-  PlaneOutput(dlb_ctx *ctx, float *planes) {
-    const bool defer = ctx && planes && ctx->gemm_kind == DLB_GEMM_F16X3;
-    kernel_arg = defer ? nullptr : planes;
-    deferred = defer ? planes : nullptr;
+  float *kernel_arg = nullptr;  // TF32 form: the residual plane the producing kernel writes
+  float *deferred = nullptr;    // fp16 form: buffer to split into afterwards
+  float *slot = nullptr;        // fp16 form: scale slot of the buffer
+  unsigned *amax = nullptr;     // where the producing kernel leaves max |x| (bits)
+  dlb_status begin(dlb_ctx *ctx, const float *x, float *planes, size_t n) {
+    if (!ctx || !planes) return DLB_OK;
+    if (ctx->gemm_kind != DLB_GEMM_F16X3) {
+      kernel_arg = planes;
+      return DLB_OK;
+    }
+    deferred = planes;
+    DLB_TRY(planes_begin(ctx, x, planes, n, &slot));
+    amax = reinterpret_cast<unsigned *>(slot) + 2;
+    return DLB_OK;
   }
   dlb_status finish(dlb_ctx *ctx, dlb_status st, const float *x, size_t n) const {
     if (st != DLB_OK || !deferred) return st;
-    return dlb_split_planes(ctx, x, deferred, n);
+    return planes_finish(ctx, x, deferred, n, slot);
   }
 };
 }  // namespace
@@ -975,40 +1013,46 @@ extern "C" {
 dlb_status dlb_activation_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u, int af,
                                   const dlb_dropout_desc *dropout, float *A, float *A_lo, int rows,
                                   int n_units) {
-  const PlaneOutput p(ctx, A_lo);
-  return p.finish(ctx, activation_forward_impl(ctx, Z, u, af, dropout, A, p.kernel_arg, rows, n_units), A,
-                  (size_t)rows * n_units);
+  PlaneOutput p;
+  DLB_TRY(p.begin(ctx, A, A_lo, (size_t)rows * n_units));
+  return p.finish(ctx, activation_forward_impl(ctx, Z, u, af, dropout, A, p.kernel_arg, rows, n_units, p.amax),
+                  A, (size_t)rows * n_units);
 }
 
 dlb_status dlb_brn_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
                                   const dlb_brn_unit_arrays *u, const double *sums, int global_rows,
                                   int rows, int n_units) {
-  const PlaneOutput p(ctx, delta_lo);
-  return p.finish(ctx, brn_backward_apply_impl(ctx, delta, p.kernel_arg, Z, u, sums, global_rows, rows, n_units),
+  PlaneOutput p;
+  DLB_TRY(p.begin(ctx, delta, delta_lo, (size_t)rows * n_units));
+  return p.finish(ctx, brn_backward_apply_impl(ctx, delta, p.kernel_arg, Z, u, sums, global_rows, rows, n_units,
+                                               p.amax),
                   delta, (size_t)rows * n_units);
 }
 
 dlb_status dlb_loss_delta(dlb_ctx *ctx, int loss, int af, const float *pre, const float *q, const float *y,
                           float *delta, float *delta_lo, int rows, int n_out, int global_rows,
                           double *loss_sum) {
-  const PlaneOutput p(ctx, delta_lo);
+  PlaneOutput p;
+  DLB_TRY(p.begin(ctx, delta, delta_lo, (size_t)rows * n_out));
   return p.finish(ctx, loss_delta_impl(ctx, loss, af, pre, q, y, delta, p.kernel_arg, rows, n_out, global_rows,
-                                       loss_sum),
+                                       loss_sum, p.amax),
                   delta, (size_t)rows * n_out);
 }
 
 dlb_status dlb_residual_forward(dlb_ctx *ctx, const float *x, float *block, const uint8_t *row_mask,
                                 const float *noise, float *out, float *out_lo, int rows, int width) {
-  const PlaneOutput p(ctx, out_lo);
-  return p.finish(ctx, residual_forward_impl(ctx, x, block, row_mask, noise, out, p.kernel_arg, rows, width), out,
-                  (size_t)rows * width);
+  PlaneOutput p;
+  DLB_TRY(p.begin(ctx, out, out_lo, (size_t)rows * width));
+  return p.finish(ctx, residual_forward_impl(ctx, x, block, row_mask, noise, out, p.kernel_arg, rows, width, p.amax),
+                  out, (size_t)rows * width);
 }
 
 dlb_status dlb_shakedrop_backward(dlb_ctx *ctx, const float *d, const uint8_t *row_mask, const float *noise,
                                   float *delta, float *delta_lo, int rows, int width) {
-  const PlaneOutput p(ctx, delta_lo);
-  return p.finish(ctx, shakedrop_backward_impl(ctx, d, row_mask, noise, delta, p.kernel_arg, rows, width), delta,
-                  (size_t)rows * width);
+  PlaneOutput p;
+  DLB_TRY(p.begin(ctx, delta, delta_lo, (size_t)rows * width));
+  return p.finish(ctx, shakedrop_backward_impl(ctx, d, row_mask, noise, delta, p.kernel_arg, rows, width, p.amax),
+                  delta, (size_t)rows * width);
 }
 
 }  // extern "C"

@@ -63,6 +63,19 @@ __device__ __forceinline__ float tf32_lo(float a) {
   return __uint_as_float(o);
 }
 
+// Largest |x| seen by a kernel, as raw bits (monotonic for non-negative
+// floats): each thread keeps a running maximum and the lanes still active at
+// the end fold theirs into the slot.  Kernels that produce a GEMM operand use
+// this so that the fp16 split that follows needs no pass of its own for the
+// tensor's maximum.
+__device__ __forceinline__ unsigned abs_bits(float v) { return __float_as_uint(v) & 0x7fffffffu; }
+__device__ __forceinline__ void amax_commit(unsigned *slot, unsigned m) {
+  if (!slot) return;
+  const unsigned mask = __activemask();
+  m = __reduce_max_sync(mask, m);
+  if ((threadIdx.x & 31u) == (unsigned)(__ffs(mask) - 1) && m) atomicMax(slot, m);
+}
+
 __device__ __forceinline__ float clipf(float v, float lo, float hi) {
   return v < lo ? lo : (v > hi ? hi : v);
 }

@@ -128,6 +128,40 @@ bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o) {
   return true;
 }
 
+// Registers `planes` as the plane buffer of x[0..n), clears the maximum of its
+// scale slot and returns the slot; the caller then lets max |x| (bits) arrive
+// in slot[2] and calls planes_finish.
+dlb_status planes_begin(dlb_ctx *ctx, const float *x, float *planes, size_t n, float **slot_out) {
+  DLB_REQUIRE(x && planes && n > 0 && n < ((size_t)1 << 40), "plane buffer: tensor, buffer and size");
+  const uintptr_t key = reinterpret_cast<uintptr_t>(planes);
+  // Buffers registered earlier that this one overwrites are stale: those that
+  // start inside it, and one that starts before and reaches into it.
+  planes_forget(ctx, key + 1, n * sizeof(float) - 1);
+  auto before = ctx->planes.lower_bound(key);
+  if (before != ctx->planes.begin()) {
+    --before;
+    if (before->first + before->second.n * sizeof(float) > key) planes_forget(ctx, before->first, 1);
+  }
+  auto it = ctx->planes.find(key);
+  if (it == ctx->planes.end()) {
+    float *slot = nullptr;
+    DLB_TRY(scale_slot(ctx, &slot));
+    it = ctx->planes.emplace(key, dlb_ctx::PlaneEntry{x, n, slot}).first;
+  }
+  it->second.x = x;
+  it->second.n = n;
+  DLB_CUDA(cudaMemsetAsync(it->second.scale + 2, 0, sizeof(float), ctx->stream));
+  *slot_out = it->second.scale;
+  return DLB_OK;
+}
+
+dlb_status planes_finish(dlb_ctx *ctx, const float *x, float *planes, size_t n, float *slot) {
+  __half *hi = reinterpret_cast<__half *>(planes);
+  split_f16_kernel<<<stream_blocks(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(x, n, hi, hi + n, slot);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
 // Drops the entries whose buffer starts inside [base, base + bytes).
 void planes_forget(dlb_ctx *ctx, uintptr_t base, size_t bytes) {
   auto it = ctx->planes.lower_bound(base);
@@ -155,25 +189,11 @@ dlb_status dlb_split_planes(dlb_ctx *ctx, const float *x, float *planes, size_t 
   DLB_REQUIRE(ctx && x && planes, "dlb_split_planes: null");
   if (n == 0) return DLB_OK;
   if (ctx->gemm_kind == DLB_GEMM_TF32X3) return dlb_split_tf32(ctx, x, planes, n);
-  const uintptr_t key = reinterpret_cast<uintptr_t>(planes);
-  // Buffers registered earlier that this one overwrites are stale: those that
-  // start inside it, and one that starts before and reaches into it.
-  planes_forget(ctx, key + 1, n * sizeof(float) - 1);
-  auto before = ctx->planes.lower_bound(key);
-  if (before != ctx->planes.begin()) {
-    --before;
-    if (before->first + before->second.n * sizeof(float) > key) planes_forget(ctx, before->first, 1);
-  }
-  auto it = ctx->planes.find(key);
-  if (it == ctx->planes.end()) {
-    float *slot = nullptr;
-    DLB_TRY(scale_slot(ctx, &slot));
-    it = ctx->planes.emplace(key, dlb_ctx::PlaneEntry{x, n, slot}).first;
-  }
-  it->second.x = x;
-  it->second.n = n;
-  uint16_t *hi = reinterpret_cast<uint16_t *>(planes);
-  return split_f16(ctx, x, n, hi, hi + n, it->second.scale);
+  float *slot = nullptr;
+  DLB_TRY(planes_begin(ctx, x, planes, n, &slot));
+  absmax_kernel<<<stream_blocks(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(x, n, reinterpret_cast<unsigned *>(slot) + 2);
+  DLB_LAUNCHED(ctx);
+  return planes_finish(ctx, x, planes, n, slot);
 }
 
 }  // extern "C"

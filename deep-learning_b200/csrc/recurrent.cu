@@ -67,16 +67,19 @@ __device__ __forceinline__ float recur(float y, float u, float h_prev) { return 
 // ---------------------------------------------------------------------------
 template <int W>
 __global__ void time_major_kernel(const float *__restrict__ x, float *__restrict__ out,
-                                  float *__restrict__ out_lo, int rows, int T, int n) {
+                                  float *__restrict__ out_lo, int rows, int T, int n, unsigned *amax) {
   const int nw = n / W;
   const size_t total = (size_t)T * rows * nw;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
+  unsigned mx = 0;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const int c = (int)(i % nw) * W;
     const size_t tb = i / nw;
     const int b = (int)(tb % rows), t = (int)(tb / rows);
     const Vec<W> v = ldv<W>(x + ((size_t)b * T + t) * n + c);
     stv<W>(out + i * W, v);
+#pragma unroll
+    for (int j = 0; j < W; ++j) mx = max(mx, abs_bits(v.v[j]));
     if (out_lo) {
       Vec<W> lo;
 #pragma unroll
@@ -84,6 +87,7 @@ __global__ void time_major_kernel(const float *__restrict__ x, float *__restrict
       stv<W>(out_lo + i * W, lo);
     }
   }
+  amax_commit(amax, mx);
 }
 
 // ---------------------------------------------------------------------------
@@ -247,10 +251,12 @@ __device__ __forceinline__ Vec<W> normalised(const Vec<W> &z, const TimeBrn &u, 
 template <int W, bool NORM, bool REC>
 __global__ void __launch_bounds__(256)
     time_forward_kernel(const float *__restrict__ Z, TimeBrn u, const float *__restrict__ rec, int af,
-                        float *__restrict__ A, float *__restrict__ A_lo, int T, int rows, int n) {
+                        float *__restrict__ A, float *__restrict__ A_lo, int T, int rows, int n,
+                        unsigned *amax) {
   const int nw = n / W;
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)rows * nw) return;
+  unsigned mx = 0;
   const int col = (int)(i % nw) * W;
   const size_t step = (size_t)rows * n;
   size_t o = (i / nw) * n + col;
@@ -273,10 +279,12 @@ __global__ void __launch_bounds__(256)
       h[j] = af_fire(af, pre);
       out.v[j] = h[j];
       lo.v[j] = tf32_lo(h[j]);
+      mx = max(mx, abs_bits(h[j]));
     }
     stv<W>(A + o, out);
     if (A_lo) stv<W>(A_lo + o, lo);
   }
+  amax_commit(amax, mx);
 }
 
 // Reverse walk: E holds dA on entry and dAF on return.
@@ -330,11 +338,12 @@ template <int W>
 __global__ void __launch_bounds__(TR_LANES_X *TR_LANES_Y)
     time_apply_kernel(float *__restrict__ delta, float *__restrict__ delta_lo,
                       const float *__restrict__ Z, TimeBrn u, const double *__restrict__ sums,
-                      float inv_rows, float rows_f, int T, int rows, int n) {
+                      float inv_rows, float rows_f, int T, int rows, int n, unsigned *amax) {
   const int tx = threadIdx.x % TR_LANES_X, ty = threadIdx.x / TR_LANES_X;
   const int col = (blockIdx.x * TR_LANES_X + tx) * W;
   const int t = blockIdx.y;
   if (col >= n) return;
+  unsigned mx = 0;
   float gamma[W], mean[W], r_over_sigma[W], n_sigma[W], d_sigma[W], d_mean_n[W];
 #pragma unroll
   for (int j = 0; j < W; ++j) {
@@ -359,10 +368,12 @@ __global__ void __launch_bounds__(TR_LANES_X *TR_LANES_Y)
       v += d_mean_n[j];
       out.v[j] = v;
       lo.v[j] = tf32_lo(v);
+      mx = max(mx, abs_bits(v));
     }
     stv<W>(delta + o, out);
     if (delta_lo) stv<W>(delta_lo + o, lo);
   }
+  amax_commit(amax, mx);
 }
 
 __global__ void clamp_kernel(float *p, int n, float lo, float hi) {
@@ -386,13 +397,13 @@ using namespace dlb;
 extern "C" {
 
 dlb_status time_major_impl(dlb_ctx *ctx, const float *x, float *out, float *out_lo, int rows,
-                          int seq_w, int n) {
+                          int seq_w, int n, unsigned *amax) {
   DLB_REQUIRE(ctx && x && out && rows > 0 && seq_w > 0 && n > 0, "dlb_time_major");
   const bool v4 = n % 4 == 0 && aligned16({x, out, out_lo});
   const size_t items = (size_t)seq_w * rows * (v4 ? n / 4 : n);
   const int grid = (int)min((items + 255) / 256, (size_t)ctx->sm_count * 16);
-  if (v4) time_major_kernel<4><<<grid, 256, 0, ctx->stream>>>(x, out, out_lo, rows, seq_w, n);
-  else time_major_kernel<1><<<grid, 256, 0, ctx->stream>>>(x, out, out_lo, rows, seq_w, n);
+  if (v4) time_major_kernel<4><<<grid, 256, 0, ctx->stream>>>(x, out, out_lo, rows, seq_w, n, amax);
+  else time_major_kernel<1><<<grid, 256, 0, ctx->stream>>>(x, out, out_lo, rows, seq_w, n, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -427,7 +438,7 @@ dlb_status dlb_brn_time_forward_finalize(dlb_ctx *ctx, const double *sums, int g
 
 dlb_status indrnn_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
                               const float *recurrent, int af, float *A, float *A_lo, int seq_w,
-                              int rows, int n) {
+                              int rows, int n, unsigned *amax) {
   DLB_REQUIRE(ctx && Z && A && seq_w > 0 && rows > 0 && n > 0, "dlb_indrnn_forward");
   TimeBrn p{};
   if (u) p = time_brn(u);
@@ -435,7 +446,7 @@ dlb_status indrnn_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_
   const int grid = walk_grid((size_t)rows * (v4 ? n / 4 : n));
 #define LAUNCH(W, NORM, REC)                                                               \
   time_forward_kernel<W, NORM, REC><<<grid, 256, 0, ctx->stream>>>(Z, p, recurrent, af, A, A_lo, \
-                                                                   seq_w, rows, n)
+                                                                   seq_w, rows, n, amax)
 #define PICK(W)                                                        \
   do {                                                                 \
     if (u && recurrent) LAUNCH(W, true, true);                         \
@@ -503,7 +514,7 @@ dlb_status dlb_time_fold(dlb_ctx *ctx, const double *sums, int seq_w, int n, flo
 
 dlb_status brn_time_backward_apply_impl(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
                                        const dlb_brn_unit_arrays *u, const double *sums,
-                                       int global_rows, int seq_w, int rows, int n) {
+                                       int global_rows, int seq_w, int rows, int n, unsigned *amax) {
   DLB_REQUIRE(ctx && delta && Z && u && sums && global_rows > 0 && seq_w > 0 && rows > 0 && n > 0,
               "dlb_brn_time_backward_apply");
   const bool v4 = n % 4 == 0 && aligned16({delta, delta_lo, Z});
@@ -511,10 +522,10 @@ dlb_status brn_time_backward_apply_impl(dlb_ctx *ctx, float *delta, float *delta
   const float nf = (float)global_rows;
   if (v4)
     time_apply_kernel<4><<<grid, TR_LANES_X * TR_LANES_Y, 0, ctx->stream>>>(
-        delta, delta_lo, Z, time_brn(u), sums, 1.f / nf, nf, seq_w, rows, n);
+        delta, delta_lo, Z, time_brn(u), sums, 1.f / nf, nf, seq_w, rows, n, amax);
   else
     time_apply_kernel<1><<<grid, TR_LANES_X * TR_LANES_Y, 0, ctx->stream>>>(
-        delta, delta_lo, Z, time_brn(u), sums, 1.f / nf, nf, seq_w, rows, n);
+        delta, delta_lo, Z, time_brn(u), sums, 1.f / nf, nf, seq_w, rows, n, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -528,32 +539,59 @@ dlb_status dlb_indrnn_clamp(dlb_ctx *ctx, float *recurrent, int n, float lo, flo
 
 }  // extern "C"
 
-// Producers of GEMM operands: under the fp16 operand form the plane buffer is
-// filled by dlb_split_planes after the kernel (it needs the tensor's maximum).
+// Producers of GEMM operands: under the fp16 operand form the producing kernel
+// leaves max |x| in the plane buffer's scale slot and the split follows.
+namespace {
+struct TimePlanes {
+  float *kernel_arg = nullptr, *deferred = nullptr, *slot = nullptr;
+  unsigned *amax = nullptr;
+  dlb_status begin(dlb_ctx *ctx, const float *x, float *planes, size_t n) {
+    if (!ctx || !planes) return DLB_OK;
+    if (ctx->gemm_kind != DLB_GEMM_F16X3) {
+      kernel_arg = planes;
+      return DLB_OK;
+    }
+    deferred = planes;
+    DLB_TRY(planes_begin(ctx, x, planes, n, &slot));
+    amax = reinterpret_cast<unsigned *>(slot) + 2;
+    return DLB_OK;
+  }
+  dlb_status finish(dlb_ctx *ctx, const float *x, size_t n) const {
+    return deferred ? planes_finish(ctx, x, deferred, n, slot) : DLB_OK;
+  }
+};
+}  // namespace
+
 extern "C" {
 
 dlb_status dlb_time_major(dlb_ctx *ctx, const float *x, float *out, float *out_lo, int rows, int seq_w,
                           int n) {
-  const bool defer = ctx && out_lo && ctx->gemm_kind == DLB_GEMM_F16X3;
-  DLB_TRY(time_major_impl(ctx, x, out, defer ? nullptr : out_lo, rows, seq_w, n));
-  return defer ? dlb_split_planes(ctx, out, out_lo, (size_t)seq_w * rows * n) : DLB_OK;
+  const size_t total = (size_t)(seq_w > 0 ? seq_w : 0) * (rows > 0 ? rows : 0) * (n > 0 ? n : 0);
+  TimePlanes p;
+  DLB_TRY(p.begin(ctx, out, out_lo, total));
+  DLB_TRY(time_major_impl(ctx, x, out, p.kernel_arg, rows, seq_w, n, p.amax));
+  return p.finish(ctx, out, total);
 }
 
 dlb_status dlb_indrnn_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
                               const float *recurrent, int af, float *A, float *A_lo, int seq_w, int rows,
                               int n) {
-  const bool defer = ctx && A_lo && ctx->gemm_kind == DLB_GEMM_F16X3;
-  DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, A, defer ? nullptr : A_lo, seq_w, rows, n));
-  return defer ? dlb_split_planes(ctx, A, A_lo, (size_t)seq_w * rows * n) : DLB_OK;
+  const size_t total = (size_t)(seq_w > 0 ? seq_w : 0) * (rows > 0 ? rows : 0) * (n > 0 ? n : 0);
+  TimePlanes p;
+  DLB_TRY(p.begin(ctx, A, A_lo, total));
+  DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, A, p.kernel_arg, seq_w, rows, n, p.amax));
+  return p.finish(ctx, A, total);
 }
 
 dlb_status dlb_brn_time_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
                                        const dlb_brn_unit_arrays *u, const double *sums, int global_rows,
                                        int seq_w, int rows, int n) {
-  const bool defer = ctx && delta_lo && ctx->gemm_kind == DLB_GEMM_F16X3;
-  DLB_TRY(brn_time_backward_apply_impl(ctx, delta, defer ? nullptr : delta_lo, Z, u, sums, global_rows, seq_w,
-                                       rows, n));
-  return defer ? dlb_split_planes(ctx, delta, delta_lo, (size_t)seq_w * rows * n) : DLB_OK;
+  const size_t total = (size_t)(seq_w > 0 ? seq_w : 0) * (rows > 0 ? rows : 0) * (n > 0 ? n : 0);
+  TimePlanes p;
+  DLB_TRY(p.begin(ctx, delta, delta_lo, total));
+  DLB_TRY(brn_time_backward_apply_impl(ctx, delta, p.kernel_arg, Z, u, sums, global_rows, seq_w, rows, n,
+                                       p.amax));
+  return p.finish(ctx, delta, total);
 }
 
 }  // extern "C"
