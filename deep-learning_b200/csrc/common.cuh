@@ -29,6 +29,9 @@ struct dlb_ctx {
   bool tensor_core_ok = false;  // device is sm_100
   // Operand form of the tensor-core products: DLB_GEMM_TF32X3 or DLB_GEMM_F16X3.
   int gemm_kind = DLB_GEMM_F16X3;
+  // SMs the persistent GEMM leaves free while a communicator is bound
+  // (DLB_GEMM_RESERVE_SMS), so that an overlapped all-reduce can run beside it.
+  int gemm_reserve_sms = 8;
   // fp16 plane buffers written by dlb_split_planes, keyed by the buffer's
   // address: the tensor they were split from, its element count (the lo plane
   // starts n halfs after the hi plane) and the device slot of its scale.

@@ -621,9 +621,14 @@ dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, floa
     const char *e = getenv("DLB_GEMM_SPLIT");
     return !(e && e[0] == '0');
   }();
+  // CTAs of this launch: one per SM, less the SMs left to a concurrent
+  // collective when the context is part of a multi-GPU job (the persistent
+  // CTAs would otherwise hold every SM until the product ends and the
+  // gradient all-reduce on the second stream could not start).
+  const int lanes = max(1, ctx->sm_count - (ctx->world > 1 ? ctx->gemm_reserve_sms : 0));
   int split_tiles = 0;
-  const int rest = tiles % ctx->sm_count;
-  if (split_enabled && !ep.accumulate && rest > 0 && 2 * rest <= ctx->sm_count &&
+  const int rest = tiles % lanes;
+  if (split_enabled && !ep.accumulate && rest > 0 && 2 * rest <= lanes &&
       ceil_div(K, BK) >= 8 * CHUNK_KB)
     split_tiles = rest;
   const int whole_tiles = tiles - split_tiles;
@@ -633,7 +638,7 @@ dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, floa
                                (size_t)N * sizeof(float), (size_t)(M - first_row), ctx->stream));
   }
   const int items = whole_tiles + 2 * split_tiles;
-  kernel<<<min(items, ctx->sm_count), NUM_THREADS, P::TOTAL, ctx->stream>>>(
+  kernel<<<min(items, lanes), NUM_THREADS, P::TOTAL, ctx->stream>>>(
       ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, items, A.scale,
       B.scale, ctx->d_status);
   DLB_LAUNCHED(ctx);
