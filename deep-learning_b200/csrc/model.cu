@@ -53,6 +53,8 @@ struct LayerRT {
   float *IN = nullptr, *IN_lo = nullptr;
   float *stats = nullptr;  // mean | sigma | mean_avg | sigma_avg | r | d, each [T*norm_units]
   uint8_t *mask = nullptr; // [T*units]
+  float *uout = nullptr;   // UOut draws of U(-beta, beta), [uout_rows, units (fan-in for a block layer)]
+  size_t uout_rows = 0;
   double *fwd_sums = nullptr, *bwd_sums = nullptr;
   // ShakeDrop of a RESIDUAL layer: row flags and the forward / backward draws.
   uint8_t *sd_mask = nullptr;
@@ -92,6 +94,7 @@ struct dlb_model {
   // Time-stepped models: the caller's rows [rows, T*n] as they arrive, before
   // the reorder to [T, rows, n].
   float *input_rows = nullptr, *target_rows = nullptr;
+  float *wd_mask = nullptr;  // [P]: 1 where weight decay applies
   float *stage_x = nullptr, *stage_y = nullptr;  // pinned
   size_t stage_x_elems = 0, stage_y_elems = 0;
   double *loss_sum = nullptr;
@@ -235,6 +238,10 @@ dlb_status allocate_parameters(dlb_model *m) {
   DLB_TRY(dev_alloc(m, &m->m1, P, true));
   DLB_TRY(dev_alloc(m, &m->m2, P, true));
   DLB_TRY(dev_alloc(m, &m->m2hat, P, true));
+  if (m->wd_mask) {
+    DLB_TRY(dlb_free(m->ctx, m->wd_mask));
+    m->wd_mask = nullptr;
+  }
   m->grads_clean = true;
   m->params_lo_valid = false;
   return DLB_OK;
@@ -467,6 +474,18 @@ dlb_status norm_backward(dlb_model *m, LayerRT &l, float *e, float *e_lo, const 
   return dlb_brn_backward_apply(m->ctx, e, e_lo, in, &u, l.bwd_sums, Bg, B, n);
 }
 
+// A layer with UOut needs this step's draws for at least B rows.
+dlb_status uout_ready(dlb_model *m, const LayerRT &l, size_t index, int B) {
+  (void)m;
+  if (l.dropout != DLB_DROPOUT_UOUT) return DLB_OK;
+  if (!l.uout || l.uout_rows < (size_t)B) {
+    set_error("model: layer %zu uses UOut but no noise was set for %d rows (dlb_model_set_uout_noise)",
+              index, B);
+    return DLB_ERR_INVALID;
+  }
+  return DLB_OK;
+}
+
 // ref: Forward_Pass__Residual__OpenMP and Forward_Pass__Residual__FC__OpenMP
 // (v1/learner/fwp_mp.cpp L:3777-3911, L:3951-4192): pre-activation block layers,
 // then the residual layer's normalization, ShakeDrop and the shortcut sum.
@@ -480,7 +499,8 @@ dlb_status forward_residual(dlb_model *m, size_t i, const float *X, const float 
     if (!b.block_input) {
       dlb_brn_unit_arrays u;
       if (norm) DLB_TRY(norm_statistics(m, b, prev_sums, B, &u));
-      dlb_dropout_desc dp{b.dropout, b.dropout_value, b.mask, nullptr};
+      DLB_TRY(uout_ready(m, b, i + j, B));
+      dlb_dropout_desc dp{b.dropout, b.dropout_value, b.mask, b.uout};
       DLB_TRY(dlb_activation_forward(m->ctx, prev_sums, norm ? &u : nullptr, b.af,
                                      b.dropout != DLB_DROPOUT_NONE ? &dp : nullptr, b.IN, b.IN_lo, B,
                                      (int)b.fan_in));
@@ -583,7 +603,8 @@ dlb_status forward_layers(dlb_model *m, size_t rows) {
     if (l.af == DLB_AF_SOFTMAX) {
       DLB_TRY(dlb_softmax_forward(m->ctx, l.Z, l.A, B, H));
     } else {
-      dlb_dropout_desc dp{l.dropout, l.dropout_value, l.mask, nullptr};
+      DLB_TRY(uout_ready(m, l, i, B));
+      dlb_dropout_desc dp{l.dropout, l.dropout_value, l.mask, l.uout};
       DLB_TRY(dlb_activation_forward(m->ctx, l.Z, norm ? &u : nullptr, l.af,
                                      l.dropout != DLB_DROPOUT_NONE ? &dp : nullptr, l.A,
                                      last ? nullptr : l.A_lo, B, H));
@@ -665,13 +686,14 @@ dlb_status dlb_model_destroy(dlb_model *m) {
   for (auto &l : m->layers) {
     if (l.stats) dlb_free(m->ctx, l.stats);
     if (l.mask) dlb_free(m->ctx, l.mask);
+    if (l.uout) dlb_free(m->ctx, l.uout);
     if (l.sd_mask) dlb_free(m->ctx, l.sd_mask);
     if (l.sd_fwd) dlb_free(m->ctx, l.sd_fwd);
     if (l.sd_bwd) dlb_free(m->ctx, l.sd_bwd);
     if (l.fwd_sums) dlb_free(m->ctx, l.fwd_sums);
     if (l.bwd_sums) dlb_free(m->ctx, l.bwd_sums);
   }
-  float *flat[] = {m->params, m->params_lo, m->grads, m->m1, m->m2, m->m2hat};
+  float *flat[] = {m->params, m->params_lo, m->grads, m->m1, m->m2, m->m2hat, m->wd_mask};
   for (float *p : flat)
     if (p) dlb_free(m->ctx, p);
   if (m->loss_sum) dlb_free(m->ctx, m->loss_sum);
@@ -748,11 +770,12 @@ dlb_status dlb_model_set_dropout(dlb_model *m, size_t layer, int type, float val
     if (type != DLB_DROPOUT_NONE) DLB_REQUIRE(value0 >= 0.f && value0 <= 1.f, "set_dropout: probability");
   } else {
     if (type != DLB_DROPOUT_NONE && type != DLB_DROPOUT_BERNOULLI &&
-        type != DLB_DROPOUT_BERNOULLI_INVERTED) {
+        type != DLB_DROPOUT_BERNOULLI_INVERTED && type != DLB_DROPOUT_UOUT) {
       set_error("set_dropout: dropout type %d is outside the supported set of this build", type);
       return DLB_ERR_UNSUPPORTED;
     }
-    if (type != DLB_DROPOUT_NONE) DLB_REQUIRE(value0 > 0.f && value0 <= 1.f, "set_dropout: keep probability");
+    // Bernoulli: keep probability; UOut: half-width beta of the noise U(-beta, beta).
+    if (type != DLB_DROPOUT_NONE) DLB_REQUIRE(value0 > 0.f && value0 <= 1.f, "set_dropout: value in (0, 1]");
   }
   if (scale_weights) {
     set_error("set_dropout: scale_weights=true is not supported (on a fresh layer the reference "
@@ -833,6 +856,13 @@ double dlb_model_get_hparam(dlb_model *m, const char *name) {
 #undef X
   if (n == "use_adam_bias_correction") return m->hp.use_adam_bias_correction;
   return -1.0;
+}
+
+// ref: Model::set_weight_decay (v1/ops/regularizers/weight_decay.cpp L:26-60).
+dlb_status dlb_model_set_weight_decay(dlb_model *m, float value) {
+  DLB_REQUIRE(m && value >= 0.f && value <= 1.f, "set_weight_decay: value in [0, 1]");
+  m->hp.weight_decay = value;
+  return DLB_OK;
 }
 
 dlb_status dlb_model_set_max_batch_size(dlb_model *m, size_t rows) {
@@ -1004,6 +1034,23 @@ dlb_status dlb_model_set_dropout_mask(dlb_model *m, size_t layer, const uint8_t 
   std::vector<uint8_t> norm01(n);
   for (size_t i = 0; i < n; ++i) norm01[i] = host_mask[i] ? 1 : 0;
   DLB_TRY(dlb_memcpy_h2d(m->ctx, l.mask, norm01.data(), n));
+  return dlb_ctx_sync(m->ctx, nullptr);
+}
+
+dlb_status dlb_model_set_uout_noise(dlb_model *m, size_t layer, const float *host_noise, size_t rows) {
+  DLB_REQUIRE(m && host_noise && layer_at(m, layer) && rows > 0, "set_uout_noise");
+  LayerRT &l = m->layers[layer];
+  DLB_REQUIRE(l.dropout == DLB_DROPOUT_UOUT, "set_uout_noise: layer does not use UOut");
+  // A block layer's dropout acts on its input (pre-activation order).
+  const size_t width = l.group == 1 ? l.fan_in : l.units;
+  if (rows > l.uout_rows) {
+    if (l.uout) DLB_TRY(dlb_free(m->ctx, l.uout));
+    l.uout = nullptr;
+    l.uout_rows = 0;
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.uout), rows * width * sizeof(float)));
+    l.uout_rows = rows;
+  }
+  DLB_TRY(dlb_memcpy_h2d(m->ctx, l.uout, host_noise, rows * width * sizeof(float)));
   return dlb_ctx_sync(m->ctx, nullptr);
 }
 
@@ -1312,9 +1359,21 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
     set_error("update_weights: no optimizer set");
     return DLB_ERR_INVALID;
   }
+  // Decoupled weight decay: step += mask * wd * p with the normalised wd of
+  // Model::normalized_wd (v1/learner/train.cpp L:278-283; the reference's default
+  // use_normalized_weight_decay = true) and the mask of
+  // Indexing_Regularization_Parameters (v1/learner/indexing.cpp L:58-81): 1 on
+  // the weights, 0 on biases, scales and shifts.
+  float wd = 0.f;
   if (m->hp.weight_decay != 0.f) {
-    set_error("update_weights: weight decay is outside the supported path of this build");
-    return DLB_ERR_UNSUPPORTED;
+    if (!m->wd_mask) {
+      std::vector<float> mask(m->total_parameters, 0.f);
+      for (size_t i = 0; i < m->total_weights; ++i) mask[i] = 1.f;
+      DLB_TRY(dev_alloc(m, &m->wd_mask, m->total_parameters, false));
+      DLB_TRY(dlb_memcpy_h2d(m->ctx, m->wd_mask, mask.data(), mask.size() * sizeof(float)));
+      DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
+    }
+    wd = m->hp.weight_decay * sqrtf((float)rows / ((float)training_size * m->hp.epoch_time_step));
   }
   const float hyper[8] = {m->hp.adam_learning_rate, m->hp.adam_beta1, m->hp.adam_beta2,
                           m->hp.adam_epsilon, m->hp.adam_gamma, m->hp.learning_rate_final,
@@ -1322,8 +1381,9 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
   dlb_optimizer_scalars k;
   DLB_TRY(dlb_optimizer_prepare(m->optimizer, hyper, &m->hp.optimizer_time_step,
                                 &m->hp.adam_previous_beta2, &k));
+  k.weight_decay = wd;
   DLB_TRY(dlb_optimizer_step(m->ctx, m->optimizer, &k, m->params, m->grads, m->m1, m->m2, m->m2hat,
-                             nullptr, m->total_parameters));
+                             wd != 0.f ? m->wd_mask : nullptr, m->total_parameters));
   // Recurrent weights of every IndRNN layer back into +-mag^(1/T), mag =
   // clip(clip_gradient, 2, 10) = 2 with the reference's default clip_gradient of
   // 1; every activation of the supported set is in a class that takes this

@@ -75,6 +75,7 @@ SIGNATURES = {
     "dlb_residual_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "dlb_shakedrop_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "dlb_model_set_shakedrop_noise": (_i, [_vp, _sz, _vp, _vp, _vp, _sz]),
+    "dlb_model_set_uout_noise": (_i, [_vp, _sz, _vp, _sz]),
     "dlb_time_major": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
     "dlb_brn_time_forward_sums": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "dlb_brn_time_forward_finalize": (_i, [_vp, _vp, _i, _i, _i, _f, _f, _f, _f, C.POINTER(BrnUnitArrays)]),
@@ -109,6 +110,7 @@ SIGNATURES = {
     "dlb_model_set_optimizer": (_i, [_vp, _i]),
     "dlb_model_set_hparam": (_i, [_vp, _cp, _d]),
     "dlb_model_get_hparam": (_d, [_vp, _cp]),
+    "dlb_model_set_weight_decay": (_i, [_vp, _f]),
     "dlb_model_set_max_batch_size": (_i, [_vp, _sz]),
     "dlb_model_set_seq_w": (_i, [_vp, _sz]),
     "dlb_model_seed_weights": (_i, [_vp, C.c_uint]),
@@ -384,6 +386,9 @@ class Model:
     def set_seq_w(self, delays):
         check(self.L.dlb_model_set_seq_w(self.h, delays), "set_seq_w")
 
+    def set_weight_decay(self, value):
+        check(self.L.dlb_model_set_weight_decay(self.h, float(value)), "set_weight_decay")
+
     def seed_weights(self, seed):
         check(self.L.dlb_model_seed_weights(self.h, seed), "seed_weights")
 
@@ -436,6 +441,10 @@ class Model:
         backward = np.ascontiguousarray(backward, dtype=np.float32)
         check(self.L.dlb_model_set_shakedrop_noise(self.h, layer, _ptr(mask), _ptr(forward), _ptr(backward),
                                                    mask.size), "set_shakedrop_noise")
+
+    def set_uout_noise(self, layer, noise):
+        noise = np.ascontiguousarray(noise, dtype=np.float32)
+        check(self.L.dlb_model_set_uout_noise(self.h, layer, _ptr(noise), noise.shape[0]), "set_uout_noise")
 
     # --- step -----------------------------------------------------------
     def train_begin(self, batch):

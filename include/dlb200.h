@@ -421,6 +421,11 @@ dlb_status dlb_model_set_optimizer(dlb_model *m, int optimizer);
 /* Public hyper-parameter fields of the reference's Model, by field name. */
 dlb_status dlb_model_set_hparam(dlb_model *m, const char *name, double value);
 double dlb_model_get_hparam(dlb_model *m, const char *name);
+/* Decoupled weight decay on the weights (not on biases, scales, shifts), with
+ * the reference's normalisation by sqrt(batch / (training_size * epoch)).
+ * ref: Model::set_weight_decay (v1/ops/regularizers/weight_decay.cpp L:26-60),
+ * Model::normalized_wd (v1/learner/train.cpp L:278-283). */
+dlb_status dlb_model_set_weight_decay(dlb_model *m, float value);
 dlb_status dlb_model_set_max_batch_size(dlb_model *m, size_t rows);
 dlb_status dlb_model_set_seq_w(dlb_model *m, size_t time_delays);
 dlb_status dlb_model_seed_weights(dlb_model *m, unsigned seed);
@@ -438,6 +443,12 @@ dlb_status dlb_model_set_layer_norm(dlb_model *m, size_t layer, const char *name
                                     const float *host_in, size_t n);
 dlb_status dlb_model_set_dropout_mask(dlb_model *m, size_t layer, const uint8_t *host_mask,
                                       size_t n);
+/* This step's UOut draws for a layer whose dropout is DLB_DROPOUT_UOUT:
+ * host_noise[rows, units] of U(-beta, beta); the forward pass computes
+ * A += A * noise.  The reference draws them on the host inside the forward
+ * pass (Forward_Pass__Dropout__Uout__OpenMP, v1/learner/fwp_mp.cpp
+ * L:4959-4985); here they are an input, like the dropout masks. */
+dlb_status dlb_model_set_uout_noise(dlb_model *m, size_t layer, const float *host_noise, size_t rows);
 /* ShakeDrop draws of one training step for a RESIDUAL layer: row flags [rows]
  * and the forward U(-1,1) / backward U(0,1) draws [rows, width] (host arrays;
  * only flagged rows are read).  The reference draws them from clock-seeded

@@ -210,7 +210,8 @@ class IndRnnOracleModel(OracleModel):
 
     def update_weights(self, batch, training_size):
         k = optimizer_scalars(self.optimizer, self.hp, self.opt_state)
-        optimizer_update(self.optimizer, k, self.params, self.grads, self.m1, self.m2, self.m2hat)
+        optimizer_update(self.optimizer, k, self.params, self.grads, self.m1, self.m2, self.m2hat,
+                         *self._decay(batch, training_size))
         bound = f32(np.power(f32(2), f32(1) / f32(self.T), dtype=f32))
         for l in self.layers[1:]:
             if l["type"] == LAYER_INDRNN:

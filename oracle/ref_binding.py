@@ -52,6 +52,9 @@ def lib():
         "ref_get_hparam": (d, [vp, cp]),
         "ref_set_max_batch_size": (i, [vp, sz]),
         "ref_set_mp": (i, [vp, i]),
+        "ref_set_weight_decay": (i, [vp, C.c_double]),
+        "ref_seed_uout": (i, [vp, C.c_uint]),
+        "ref_uout_draws": (i, [C.c_uint, sz, sz, _szp, _f32p, _f32p]),
         "ref_set_seq_w": (i, [vp, sz]),
         "ref_seed_weights": (i, [vp, C.c_uint]),
         "ref_initialize_weights_with_glorot_uniform": (i, [vp]),
@@ -159,6 +162,12 @@ class RefModel:
     def set_seq_w(self, delays):
         _ck(self.L.ref_set_seq_w(self.h, delays), "set_seq_w")
 
+    def seed_uout(self, seed):
+        _ck(self.L.ref_seed_uout(self.h, seed), "seed_uout")
+
+    def set_weight_decay(self, value):
+        _ck(self.L.ref_set_weight_decay(self.h, float(value)), "set_weight_decay")
+
     def seed_weights(self, seed):
         _ck(self.L.ref_seed_weights(self.h, seed), "seed")
 
@@ -257,6 +266,20 @@ class RefModel:
         out = np.empty((T, batch, n_out), dtype=np.float32)
         _ck(self.L.ref_get_layer_errors(self.h, layer, batch, which, out), "get_layer_errors")
         return out
+
+
+def uout_draws(seed, betas, rows, widths):
+    """[noise [rows, width] per layer] that a serial reference forward pass
+    draws after RefModel.seed_uout(seed)."""
+    w = np.ascontiguousarray(widths, dtype=np.uint64)
+    b = np.ascontiguousarray(betas, dtype=np.float32)
+    out = np.empty(int(rows * w.sum()), dtype=np.float32)
+    _ck(lib().ref_uout_draws(seed, len(w), rows, w, b, out), "uout_draws")
+    res, o = [], 0
+    for n in w:
+        res.append(out[o:o + rows * int(n)].reshape(rows, int(n)).copy())
+        o += rows * int(n)
+    return res
 
 
 def shakedrop_draws(seed, probabilities, rows, width):

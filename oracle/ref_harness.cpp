@@ -190,6 +190,9 @@ int ref_set_max_batch_size(ref_model m, size_t b) {
 int ref_set_mp(ref_model m, int use_mp) {
   return H(m)->model.set_mp(use_mp != 0) ? 0 : -1;
 }
+int ref_set_weight_decay(ref_model m, double value) {
+  return H(m)->model.set_weight_decay(static_cast<real>(value)) ? 0 : -1;
+}
 int ref_set_seq_w(ref_model m, size_t time_delays) {
   return H(m)->model.set_seq_w(time_delays) ? 0 : -1;
 }
@@ -368,6 +371,29 @@ int ref_shakedrop_draws(unsigned seed, size_t n_blocks, size_t rows, size_t widt
     for (size_t r = 0; r < rows; ++r)
       if (masks[b * rows + r])
         for (size_t k = 0; k < width; ++k) backward[(b * rows + r) * width + k] = real_gen();
+  }
+  return 0;
+}
+
+int ref_seed_uout(ref_model m, unsigned seed) {
+  Model &M = H(m)->model;
+  if (!M.ptr_array_Class_Generator_Real_Uout) return -1;
+  for (size_t t = 0; t < M.number_threads; ++t)
+    M.ptr_array_Class_Generator_Real_Uout[t].seed(seed + static_cast<unsigned>(t));
+  return 0;
+}
+
+int ref_uout_draws(unsigned seed, size_t n_layers, size_t rows, const size_t *widths,
+                   const float *betas, float *out) {
+  ensure_logger();
+  /* What a serial forward pass draws after ref_seed_uout(seed): layer by
+   * layer, rows * width values of U(-beta, beta) each. */
+  Dist::Real gen;
+  gen.seed(seed);
+  size_t o = 0;
+  for (size_t l = 0; l < n_layers; ++l) {
+    gen.range(-static_cast<real>(betas[l]), static_cast<real>(betas[l]));
+    for (size_t i = 0; i < rows * widths[l]; ++i) out[o++] = gen();
   }
   return 0;
 }

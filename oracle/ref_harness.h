@@ -45,6 +45,10 @@ int ref_set_hparam(ref_model m, const char *name, double value);
 double ref_get_hparam(ref_model m, const char *name);
 int ref_set_max_batch_size(ref_model m, size_t b);
 int ref_set_mp(ref_model m, int use_mp);
+int ref_set_weight_decay(ref_model m, double value);
+int ref_seed_uout(ref_model m, unsigned seed);
+int ref_uout_draws(unsigned seed, size_t n_layers, size_t rows, const size_t *widths,
+                   const float *betas, float *out);
 int ref_set_seq_w(ref_model m, size_t time_delays);
 int ref_seed_weights(ref_model m, unsigned seed);
 int ref_initialize_weights_with_glorot_uniform(ref_model m);

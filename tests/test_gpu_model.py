@@ -129,3 +129,58 @@ def test_unsupported_configurations_are_refused(gpu_ctx):
         m.set_optimizer(6)                           # GD
     with pytest.raises(dlb200.DlbError):
         m.forward_pass(4, np.zeros((4, 8), np.float32))   # activations never set (reference default: sigmoid)
+
+
+@pytest.mark.parametrize("optimizer", [OPTIMIZER.ADAM, OPTIMIZER.AMSBOUND], ids=["adam", "amsbound"])
+def test_weight_decay(gpu_ctx, optimizer):
+    """Decoupled, normalised weight decay on the weights only, against the CPU
+    restatement (itself pinned to the compiled reference)."""
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96, optimizer=optimizer)
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    p0, seed = util.kink_free_parameters(cfg, fc_step.OracleModel, X, masks, scale=1.0 / np.sqrt(128))
+    ora = util.build(fc_step.OracleModel(), cfg, params=p0)
+    ora.set_weight_decay(0.05)
+    want = util.trace(ora, cfg, 1, X, Y, masks)
+    mod = gpu_model(gpu_ctx, cfg, p0)
+    mod.set_weight_decay(0.05)
+    got = util.trace(mod, cfg, 1, X, Y, masks)
+    assert gpu_ctx.sync() == 0
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_1, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+    nw = mod.size("total_weights")
+    moved = np.abs(got["params1"][:nw] - p0[:nw]).mean()
+    plain = util.trace(gpu_model(gpu_ctx, cfg, p0), cfg, 1, X, Y, masks)
+    assert np.abs(plain["params1"][:nw] - got["params1"][:nw]).mean() > 0.01 * moved
+    with pytest.raises(dlb200.DlbError):
+        mod.set_weight_decay(1.5)
+
+
+def test_uout_dropout(gpu_ctx):
+    """UOut inside the Model: the draws are an input of the step."""
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96, dropout=LAYER_DROPOUT.UOUT, keep=0.25)
+    B = cfg["batch"]
+    X, Y = configs.synthetic_batch(cfg)
+    rng = np.random.default_rng(8)
+    noise = {li: rng.uniform(-0.25, 0.25, (B, 128)).astype(np.float32) for li in (1, 2)}
+
+    def prepare(model):
+        for li, nz in noise.items():
+            model.set_uout_noise(li, nz)
+
+    p0, seed = util.kink_free_parameters(cfg, fc_step.OracleModel, X, {}, scale=1.0 / np.sqrt(128), prepare=prepare)
+    ora = util.build(fc_step.OracleModel(), cfg, params=p0)
+    mod = gpu_model(gpu_ctx, cfg, p0)
+    with pytest.raises(dlb200.DlbError):
+        gpu_model(gpu_ctx, cfg, p0).forward_pass(B, X)   # no draws yet (on a model of its own: the
+                                                         # refused pass has already moved running averages)
+    prepare(ora)
+    prepare(mod)
+    want = util.trace(ora, cfg, 1, X, Y, {})
+    got = util.trace(mod, cfg, 1, X, Y, {})
+    assert gpu_ctx.sync() == 0
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_1, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+    plain = util.trace(gpu_model(gpu_ctx, dict(cfg, layers=[dict(l, dropout=None) for l in cfg["layers"]]), p0),
+                       cfg, 1, X, Y, {})
+    assert util.rel_l2(plain["act2"], got["act2"]) > 1e-2   # the noise is applied

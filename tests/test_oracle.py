@@ -77,3 +77,45 @@ def test_softmax_cross_entropy_known_answer():
     total, delta = fc_step.loss_and_delta(fc_step.LOSS_CROSS_ENTROPY, fc_step.AF_SOFTMAX, z, q, y)
     np.testing.assert_allclose(delta, (q - y), rtol=2e-6, atol=1e-7)
     np.testing.assert_allclose(total, -np.log(q[0, 2]), rtol=1e-6)
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("optimizer", [1, 2, 4, 5, 9], ids=["adabound", "adam", "amsbound", "amsgrad", "nosadam"])
+def test_weight_decay_matches_compiled_reference(optimizer):
+    """Decoupled, normalised weight decay on the weights only
+    (v1/optimizers/adam.cpp L:130-147, v1/learner/train.cpp L:278-283,
+    v1/learner/indexing.cpp L:58-81)."""
+    cfg = configs.deep_brn_mlp(20, 32, 2, 12, 24, optimizer=optimizer)
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    ref.set_weight_decay(0.01)
+    p0 = ref.get_array("parameters")
+    want = util.trace(ref, cfg, steps=4)
+    ora = util.build(fc_step.OracleModel(), cfg, params=p0)
+    ora.set_weight_decay(0.01)
+    got = util.trace(ora, cfg, steps=4)
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_L2, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+    plain = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, steps=4)
+    assert util.rel_l2(plain["params_last"], want["params_last"]) > 1e-4   # the decay is not a no-op
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+def test_uout_matches_compiled_reference():
+    """UOut, A += A * U(-beta, beta) per element (v1/learner/fwp_mp.cpp
+    L:4959-4985): the restatement receives the draws the serial reference makes
+    after its generator is reseeded, replayed through the reference's own
+    Dist::Real."""
+    cfg = dict(configs.deep_brn_mlp(20, 32, 2, 12, 24, dropout=LAYER_DROPOUT.UOUT, keep=0.3), mp=False)
+    B = cfg["batch"]
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    ora = util.build(fc_step.OracleModel(), cfg, params=ref.get_array("parameters"))
+    X, Y = configs.synthetic_batch(cfg)
+    ref.train_begin(B)
+    for step in range(4):
+        ref.seed_uout(100 + step)
+        noise = ref_binding.uout_draws(100 + step, [0.3, 0.3], B, [32, 32])
+        ora.set_uout_noise(1, noise[0])
+        ora.set_uout_noise(2, noise[1])
+        assert abs(ref.train_step(B, X, Y) - ora.train_step(B, X, Y)) <= 1e-6
+        assert util.rel_l2(ora.get_layer_outputs(2, B), ref.get_layer_outputs(2, B).reshape(B, -1)) <= TOL_L2
+        assert util.rel_l2(ora.get_array("parameters"), ref.get_array("parameters")) <= TOL_L2
