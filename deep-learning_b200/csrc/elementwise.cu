@@ -155,24 +155,29 @@ struct SumOp {
 // Per-column constants of a batch-renormalised unit.
 struct BrnCol {
   float mean, sigma, r, d, gamma, beta;
+  float r_over_sigma;  // formed once per unit; every kernel normalises through it
 };
 struct BrnPtrs {
   const float *mean, *sigma, *r, *d, *gamma, *beta;
   __device__ BrnCol at(int c) const {
-    return BrnCol{mean[c], sigma[c], r[c], d[c], gamma[c], beta[c]};
+    const float s = sigma[c], rr = r[c];
+    return BrnCol{mean[c], s, rr, d[c], gamma[c], beta[c], rr / s};
   }
 };
 static BrnPtrs brn_ptrs(const dlb_brn_unit_arrays *u) {
   return BrnPtrs{u->mean, u->sigma, u->r, u->d, u->gamma, u->beta};
 }
 
-// value_hat = (z - mean) / sigma * r + d      (fwp_mp.cpp L:4732)
+// value_hat = (z - mean) / sigma * r + d      (fwp_mp.cpp L:4732), with the
+// per-unit quotient r / sigma formed once instead of a division per element (a
+// difference of one rounding; forward and backward both come through here, so
+// they agree bit for bit on which side of a derivative jump a value lies).
 __device__ __forceinline__ float brn_hat(float z, const BrnCol &c) {
-  return (z - c.mean) / c.sigma * c.r + c.d;
+  return __fmaf_rn(z - c.mean, c.r_over_sigma, c.d);
 }
 // value_normalize = gamma * value_hat + beta  (fwp_mp.cpp L:4736)
 __device__ __forceinline__ float brn_norm(float xh, const BrnCol &c) {
-  return c.gamma * xh + c.beta;
+  return __fmaf_rn(c.gamma, xh, c.beta);
 }
 
 // --- activation backward (+ BRN backward sums) --------------------------------
@@ -438,22 +443,41 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
   const int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
   unsigned mx = 0;
   BrnCol c[4];
+  // Bernoulli dropout has one flag per unit: a factor per owned column.
+  float keep[4];
+  const bool bern = dp.type == DLB_DROPOUT_BERNOULLI || dp.type == DLB_DROPOUT_BERNOULLI_INVERTED;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) c[j] = u.at(col + j);
-  for (int r = r0 + ty; r < r1; r += CR_LANES_Y) {
-    const size_t o = (size_t)r * n + col;
-    const float4 z = __ldg(reinterpret_cast<const float4 *>(Z + o));
-    const float zz[4] = {z.x, z.y, z.z, z.w};
-    float out[4], lo[4];
+  for (int j = 0; j < 4; ++j) {
+    c[j] = u.at(col + j);
+    keep[j] = bern ? (dp.mask[col + j] ? (dp.type == DLB_DROPOUT_BERNOULLI_INVERTED ? dp.scale : 1.f) : 0.f) : 1.f;
+  }
+  // Two rows per iteration, loads first, so that each thread keeps two
+  // 16-byte requests in flight.
+  for (int r = r0 + ty; r < r1; r += 2 * CR_LANES_Y) {
+    const int rb = r + CR_LANES_Y;
+    const bool two = rb < r1;
+    const size_t o[2] = {(size_t)r * n + col, (size_t)rb * n + col};
+    float4 z[2];
+    z[0] = __ldg(reinterpret_cast<const float4 *>(Z + o[0]));
+    if (two) z[1] = __ldg(reinterpret_cast<const float4 *>(Z + o[1]));
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float y = brn_norm(brn_hat(zz[j], c[j]), c[j]);
-      out[j] = apply_dropout(af_fire(af, y), dp, col + j, o + j);
-      lo[j] = tf32_lo(out[j]);
-      mx = max(mx, abs_bits(out[j]));
+    for (int k = 0; k < 2; ++k) {
+      if (k == 1 && !two) break;
+      const float zz[4] = {z[k].x, z[k].y, z[k].z, z[k].w};
+      float out[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = af_fire(af, brn_norm(brn_hat(zz[j], c[j]), c[j]));
+        // Kept units pass unchanged under plain Bernoulli, as the reference leaves them.
+        if (bern) out[j] = keep[j] == 1.f ? a : (keep[j] == 0.f ? 0.f : a * keep[j]);
+        else out[j] = apply_dropout(a, dp, col + j, o[k] + j);
+        mx = max(mx, abs_bits(out[j]));
+      }
+      *reinterpret_cast<float4 *>(A + o[k]) = make_float4(out[0], out[1], out[2], out[3]);
+      if (A_lo)
+        *reinterpret_cast<float4 *>(A_lo + o[k]) =
+            make_float4(tf32_lo(out[0]), tf32_lo(out[1]), tf32_lo(out[2]), tf32_lo(out[3]));
     }
-    *reinterpret_cast<float4 *>(A + o) = make_float4(out[0], out[1], out[2], out[3]);
-    if (A_lo) *reinterpret_cast<float4 *>(A_lo + o) = make_float4(lo[0], lo[1], lo[2], lo[3]);
   }
   amax_commit(amax, mx);
 }

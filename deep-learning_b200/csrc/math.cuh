@@ -73,7 +73,10 @@ __device__ __forceinline__ void amax_commit(unsigned *slot, unsigned m) {
   if (!slot) return;
   const unsigned mask = __activemask();
   m = __reduce_max_sync(mask, m);
-  if ((threadIdx.x & 31u) == (unsigned)(__ffs(mask) - 1) && m) atomicMax(slot, m);
+  // Most warps find a larger value already there: read before the atomic so
+  // that thousands of warps do not queue on one address.
+  if ((threadIdx.x & 31u) == (unsigned)(__ffs(mask) - 1) && m > *reinterpret_cast<volatile unsigned *>(slot))
+    atomicMax(slot, m);
 }
 
 __device__ __forceinline__ float clipf(float v, float lo, float hi) {

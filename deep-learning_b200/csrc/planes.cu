@@ -22,6 +22,7 @@ __global__ void absmax_kernel(const float *__restrict__ x, size_t n, unsigned *s
   const size_t n4 = n / 4;
   const bool vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
   if (vec) {
+#pragma unroll 4
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
       const uint4 v = __ldg(reinterpret_cast<const uint4 *>(x) + i);
       m = max(max(m, v.x & 0x7fffffffu), max(v.y & 0x7fffffffu, max(v.z & 0x7fffffffu, v.w & 0x7fffffffu)));
@@ -33,7 +34,7 @@ __global__ void absmax_kernel(const float *__restrict__ x, size_t n, unsigned *s
       m = max(m, __float_as_uint(x[i]) & 0x7fffffffu);
   }
   for (int o = 16; o; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if (threadIdx.x % 32 == 0 && m) atomicMax(slot, m);
+  if (threadIdx.x % 32 == 0 && m > *reinterpret_cast<volatile unsigned *>(slot)) atomicMax(slot, m);
 }
 
 // s = 2^(14 - E) for max = 1.f * 2^E; 1 for a zero, infinite or NaN maximum.
