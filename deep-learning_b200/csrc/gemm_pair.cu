@@ -416,10 +416,11 @@ dlb_status launch_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B,
 
 }  // namespace
 
+// On unless DLB_GEMM_PAIR=0.
 bool gemm_pair_enabled() {
   static const bool on = [] {
     const char *e = getenv("DLB_GEMM_PAIR");
-    return e && e[0] == '1';
+    return !(e && e[0] == '0');
   }();
   return on;
 }
@@ -428,9 +429,20 @@ dlb_status gemm_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, f
                      int M, int N, int K, const GemmEpilogue &ep) {
   const bool a_mn = !(A.stride_k == 1);
   const bool b_mn = !(B.stride_k == 1);
-  if (!a_mn && !b_mn) return launch_pair<6, 4, false, false>(ctx, A, B, C, ldc, M, N, K, ep);
-  if (!a_mn && b_mn) return launch_pair<6, 4, false, true>(ctx, A, B, C, ldc, M, N, K, ep);
-  if (a_mn && b_mn) return launch_pair<6, 4, true, true>(ctx, A, B, C, ldc, M, N, K, ep);
+  static const int chunk = [] {
+    const char *e = getenv("DLB_GEMM_PAIR_CHUNK");
+    return e ? atoi(e) : 8;
+  }();
+#define DLB_PAIR(CH)                                                                                  \
+  if (chunk == (CH)) {                                                                                \
+    if (!a_mn && !b_mn) return launch_pair<6, CH, false, false>(ctx, A, B, C, ldc, M, N, K, ep);      \
+    if (!a_mn && b_mn) return launch_pair<6, CH, false, true>(ctx, A, B, C, ldc, M, N, K, ep);        \
+    if (a_mn && b_mn) return launch_pair<6, CH, true, true>(ctx, A, B, C, ldc, M, N, K, ep);          \
+  }
+  DLB_PAIR(4)
+  DLB_PAIR(8)
+  DLB_PAIR(16)
+#undef DLB_PAIR
   set_error("gemm_pair: MN-major A with K-major B is not instantiated");
   return DLB_ERR_UNSUPPORTED;
 }

@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   using P = SmemPlan<BN, BK, STAGES, ES>;
   static_assert(ES == 4 || ES == 2, "fp32 (TF32) or fp16 operands");
   constexpr int MN_W = 128 / ES;  // elements of one 128-byte column of an MN-major tile
-  static_assert(BN == 256 || BN == 128, "two accumulators of BN columns must fit 512 columns");
+  static_assert(BN == 256, "two accumulators of 256 columns; the drain reads 64 columns at a time");
   constexpr int HALF = BN / 2;  // columns per drain warp
   extern __shared__ uint8_t smem_raw[];
   // Swizzled tiles need 1024-byte alignment of each tile base.
@@ -519,6 +519,7 @@ dlb_status launch_tile(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B,
     return launch<TBN, TBK, TST, TCH, A_MN, B_MN, ES>(ctx, A, B, C, ldc, M, N, K, ep);
   DLB_TILE(256, 16, 4, 4)
   DLB_TILE(256, 16, 4, 2)
+  DLB_TILE(256, 16, 4, 8)
   DLB_TILE(256, 16, 4, 16)
 #undef DLB_TILE
   set_error("gemm_tcgen05: tile %dx%dx%dx%d is not compiled in", t.bn, t.bk, t.stages, t.chunk);
