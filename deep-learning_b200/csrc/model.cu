@@ -1421,6 +1421,63 @@ dlb_status dlb_model_get_loss(dlb_model *m, double *loss) {
   return DLB_OK;
 }
 
+static dlb_status update_and_merge_overlapped(dlb_model *m, size_t rows);
+
+// Plain stack of fully connected layers (no residual block, one time step).
+static bool plain_stack(const dlb_model *m) {
+  if (time_stepped(m)) return false;
+  for (const LayerRT &l : m->layers)
+    if (l.type != DLB_LAYER_FULLY_CONNECTED || l.group != 0) return false;
+  return true;
+}
+
+// Backward pass and weight gradients of a plain stack in one sweep, for
+// multi-GPU steps: a layer's weight gradient is formed as soon as its error is
+// final and its all-reduce starts on the second stream, so that the exchange
+// overlaps the rest of the backward pass instead of only the later weight-
+// gradient products.  Same kernels on the same operands as
+// dlb_model_backward_pass followed by dlb_model_update_derivatives: the
+// results are identical.
+static dlb_status backward_and_derivatives_overlapped(dlb_model *m, size_t rows) {
+  const int B = (int)rows;
+  const int accumulate = m->grads_clean ? 0 : 1;
+  for (size_t i = m->layers.size() - 1; i >= 1; --i) {
+    LayerRT &l = m->layers[i];
+    const int H = (int)l.units;
+    if (i + 1 != m->layers.size()) {  // hidden layer: l.delta holds dA
+      if (l.norm != DLB_NORM_NONE) {
+        DLB_TRY(norm_backward(m, l, l.delta, l.delta_lo, l.Z, l.A, l.af, B));
+      } else {
+        DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, nullptr, l.af, B, H, nullptr));
+        DLB_TRY(dlb_split_planes(m->ctx, l.delta, l.delta_lo, (size_t)B * H));
+      }
+    }
+    const float *X = i == 1 ? m->input : m->layers[i - 1].A;
+    const float *X_lo = i == 1 ? m->input_lo : m->layers[i - 1].A_lo;
+    float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
+    DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn, dbias,
+                                   B, (int)l.fan_in, H, accumulate));
+    DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
+    if (i > 1)
+      DLB_TRY(dlb_fc_backward_input(m->ctx, l.delta, l.delta_lo, m->params + l.first_conn,
+                                    m->params_lo + l.first_conn, m->layers[i - 1].delta, B, (int)l.fan_in, H));
+    if (i == 1) break;
+  }
+  m->grads_clean = false;
+  // Bias, gamma and beta gradients follow the weight blocks.
+  DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + m->total_weights,
+                                       m->total_parameters - m->total_weights));
+  return dlb_comm_join(m->ctx);
+}
+
+// Backward, weight gradients and their exchange inside a training step.
+static dlb_status backward_update_merge(dlb_model *m, size_t rows) {
+  DLB_REQUIRE(rows > 0 && rows <= m->alloc_rows, "train_step: rows");
+  if (dlb_comm_world(m->ctx) > 1 && plain_stack(m)) return backward_and_derivatives_overlapped(m, rows);
+  DLB_TRY(dlb_model_backward_pass(m, rows));
+  return update_and_merge_overlapped(m, rows);
+}
+
 static dlb_status update_and_merge_overlapped(dlb_model *m, size_t rows) {
   m->overlap_grad_allreduce = dlb_comm_world(m->ctx) > 1;
   dlb_status st = dlb_model_update_derivatives(m, rows);
@@ -1434,8 +1491,7 @@ dlb_status dlb_model_train_step_device(dlb_model *m, size_t rows, const float *X
   DLB_TRY(dlb_model_reset_loss(m));
   DLB_TRY(dlb_model_forward_pass_device(m, rows, X_dev));
   DLB_TRY(dlb_model_compute_error_device(m, rows, Y_dev));
-  DLB_TRY(dlb_model_backward_pass(m, rows));
-  DLB_TRY(update_and_merge_overlapped(m, rows));
+  DLB_TRY(backward_update_merge(m, rows));
   const size_t g = m->global_rows ? m->global_rows : rows;
   return dlb_model_update_weights(m, g, g);
 }
@@ -1452,8 +1508,7 @@ dlb_status dlb_model_train_step(dlb_model *m, size_t rows, const float *X_host,
   DLB_TRY(dlb_model_reset_loss(m));
   DLB_TRY(dlb_model_forward_pass_device(m, rows, x_dev));
   DLB_TRY(dlb_model_compute_error_device(m, rows, y_dev));
-  DLB_TRY(dlb_model_backward_pass(m, rows));
-  DLB_TRY(update_and_merge_overlapped(m, rows));
+  DLB_TRY(backward_update_merge(m, rows));
   if (loss) DLB_TRY(dlb_model_get_loss(m, loss));
   const size_t g = m->global_rows ? m->global_rows : rows;
   return dlb_model_update_weights(m, g, g);
