@@ -70,8 +70,8 @@ def gemm_traffic_per_launch():
     """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM
     kernel at M = N = K = 4096 (9 of the 14 launches of a step have that shape),
     from the ncu capture summarised in
-    profiles/gemm_tf32x3_kernel_4096x4096x4096.md: 682 MB + 61.6 MB."""
-    return 744.0e6
+    profiles/gemm_x3_pair_kernel_4096x4096x4096.md: 337 MB + 55.8 MB."""
+    return 393.0e6
 
 
 class ClockSampler:
@@ -349,8 +349,8 @@ def run_ours(args, rank, local_rank, world):
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {
-            "kernel": "gemm_x3_kernel (tcgen05, all FC products; " +
-                      ("3xFP16 planes, kind::f16" if f16 else "3xTF32, kind::tf32") + ")",
+            "kernel": ("gemm_x3_pair_kernel (tcgen05 cta_group::2, all FC products; 3xFP16 planes, kind::f16)"
+                       if f16 else "gemm_x3_kernel (tcgen05, all FC products; 3xTF32, kind::tf32)"),
             "bound": "tensor",
             "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
             "peak_source": f"MEASURED_PEAKS.json bf16 dense, sustained ({peak_kind})",
