@@ -19,8 +19,8 @@ all-reduced over NCCL so that every rank holds the full-batch result.
           host-to-device copy of inputs and targets and the device-to-host read
           of the loss are inside the timed region.
 `roofline` the tcgen05 GEMM kernel: algorithmic FLOPs (2*M*N*K per launch, not
-          multiplied by the three TF32 passes) over the summed event-timed launch
-          durations inside the timed region.
+          multiplied by the three tensor-core products per FLOP) over the summed
+          event-timed launch durations inside the timed region.
 `cpu_baseline` the reference's own OpenMP step (oracle/_ref, compiled from the
           reference's sources) on this host's cores, on a bounded sample.
 --impl reference times only that CPU implementation.

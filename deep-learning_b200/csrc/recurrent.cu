@@ -50,14 +50,24 @@ __device__ __forceinline__ void stv(float *p, const Vec<W> &x) {
 struct TimeBrn {
   const float *mean, *sigma, *r, *d;  // [T, n]
   const float *gamma, *beta;          // [n]
+  const float *rs;                    // [T, n]: r / sigma, formed once per (t, unit) for the walks
 };
 static TimeBrn time_brn(const dlb_brn_unit_arrays *u) {
-  return TimeBrn{u->mean, u->sigma, u->r, u->d, u->gamma, u->beta};
+  return TimeBrn{u->mean, u->sigma, u->r, u->d, u->gamma, u->beta, nullptr};
 }
 
-// value_hat and value_normalize of v1/learner/fwp_mp.cpp L:4732-4736.
-__device__ __forceinline__ float hat(float z, float mean, float sigma, float r, float d) {
-  return (z - mean) / sigma * r + d;
+// value_hat of v1/learner/fwp_mp.cpp L:4732, (z - mean) / sigma * r + d, through
+// the per-(t, unit) quotient r / sigma: every time kernel normalises through
+// this one expression, so all of them see the same bits on either side of a
+// derivative jump.
+__device__ __forceinline__ float hat(float z, float mean, float r_over_sigma, float d) {
+  return __fmaf_rn(z - mean, r_over_sigma, d);
+}
+
+__global__ void time_quotient_kernel(const float *__restrict__ r, const float *__restrict__ sigma,
+                                     float *__restrict__ rs, size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) rs[i] = r[i] / sigma[i];
 }
 
 // pre_t = y_t + u * h_{t-1}; the forward and the backward walk use this one
@@ -157,7 +167,7 @@ struct TimeBackwardOp {
   static constexpr int NS = (NORM ? 4 : 0) + (REC ? 1 : 0);
   template <int W>
   struct Cols {
-    float mean[W], sigma[W], r[W], d[W], gamma[W], q_mean[W], q_sigma[W];
+    float mean[W], sigma[W], r[W], rs[W], d[W], gamma[W], q_mean[W], q_sigma[W];
   };
   template <int W>
   __device__ void load(int t, int col, int n, Cols<W> &k) const {
@@ -168,6 +178,7 @@ struct TimeBackwardOp {
       k.mean[j] = u.mean[i];
       k.sigma[j] = u.sigma[i];
       k.r[j] = u.r[i];
+      k.rs[j] = k.r[j] / k.sigma[j];
       k.d[j] = u.d[i];
       k.gamma[j] = u.gamma[col + j];
       const float neg_r = -k.r[j];
@@ -183,7 +194,7 @@ struct TimeBackwardOp {
       const Vec<W> z = ldv<W>(Z + o);
 #pragma unroll
       for (int j = 0; j < W; ++j) {
-        const float xh = hat(z.v[j], k.mean[j], k.sigma[j], k.r[j], k.d[j]);
+        const float xh = hat(z.v[j], k.mean[j], k.rs[j], k.d[j]);
         acc[0][j] += e.v[j] * xh;
         acc[1][j] += e.v[j];
         const float eh = e.v[j] * k.gamma[j];
@@ -234,12 +245,10 @@ __global__ void time_fold_kernel(const double *__restrict__ sums, int T, int n, 
 template <int W>
 __device__ __forceinline__ Vec<W> normalised(const Vec<W> &z, const TimeBrn &u, size_t stat,
                                              const float (&gamma)[W], const float (&beta)[W]) {
-  const Vec<W> mean = ldv<W>(u.mean + stat), sigma = ldv<W>(u.sigma + stat), r = ldv<W>(u.r + stat),
-               d = ldv<W>(u.d + stat);
+  const Vec<W> mean = ldv<W>(u.mean + stat), rs = ldv<W>(u.rs + stat), d = ldv<W>(u.d + stat);
   Vec<W> y;
 #pragma unroll
-  for (int j = 0; j < W; ++j)
-    y.v[j] = __fmaf_rn(gamma[j], hat(z.v[j], mean.v[j], sigma.v[j], r.v[j], d.v[j]), beta[j]);
+  for (int j = 0; j < W; ++j) y.v[j] = __fmaf_rn(gamma[j], hat(z.v[j], mean.v[j], rs.v[j], d.v[j]), beta[j]);
   return y;
 }
 
@@ -389,6 +398,18 @@ bool aligned16(std::initializer_list<const void *> ps) {
 
 int walk_grid(size_t threads) { return (int)((threads + 255) / 256); }
 
+// r / sigma for every (t, unit) into context scratch, for the walk that follows.
+dlb_status time_quotients(dlb_ctx *ctx, TimeBrn *p, int T, int n) {
+  const size_t total = (size_t)T * n;
+  void *scr = nullptr;
+  DLB_TRY(scratch(ctx, total * sizeof(float), &scr));
+  float *rs = static_cast<float *>(scr);
+  time_quotient_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(p->r, p->sigma, rs, total);
+  DLB_LAUNCHED(ctx);
+  p->rs = rs;
+  return DLB_OK;
+}
+
 }  // namespace
 }  // namespace dlb
 
@@ -441,8 +462,11 @@ dlb_status indrnn_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_
                               int rows, int n, unsigned *amax) {
   DLB_REQUIRE(ctx && Z && A && seq_w > 0 && rows > 0 && n > 0, "dlb_indrnn_forward");
   TimeBrn p{};
-  if (u) p = time_brn(u);
-  const bool v4 = n % 4 == 0 && aligned16({Z, A, A_lo, p.mean, p.sigma, p.r, p.d});
+  if (u) {
+    p = time_brn(u);
+    DLB_TRY(time_quotients(ctx, &p, seq_w, n));
+  }
+  const bool v4 = n % 4 == 0 && aligned16({Z, A, A_lo, p.mean, p.rs, p.d});
   const int grid = walk_grid((size_t)rows * (v4 ? n / 4 : n));
 #define LAUNCH(W, NORM, REC)                                                               \
   time_forward_kernel<W, NORM, REC><<<grid, 256, 0, ctx->stream>>>(Z, p, recurrent, af, A, A_lo, \
@@ -465,8 +489,11 @@ dlb_status dlb_indrnn_backward_walk(dlb_ctx *ctx, float *E, const float *Z, cons
                                     int seq_w, int rows, int n) {
   DLB_REQUIRE(ctx && E && Z && A && seq_w > 0 && rows > 0 && n > 0, "dlb_indrnn_backward_walk");
   TimeBrn p{};
-  if (u) p = time_brn(u);
-  const bool v4 = n % 4 == 0 && aligned16({E, Z, A, p.mean, p.sigma, p.r, p.d});
+  if (u) {
+    p = time_brn(u);
+    DLB_TRY(time_quotients(ctx, &p, seq_w, n));
+  }
+  const bool v4 = n % 4 == 0 && aligned16({E, Z, A, p.mean, p.rs, p.d});
   const int grid = walk_grid((size_t)rows * (v4 ? n / 4 : n));
 #define LAUNCH(W, NORM, REC)                                                                 \
   time_backward_kernel<W, NORM, REC><<<grid, 256, 0, ctx->stream>>>(E, Z, A, p, recurrent, af, \
