@@ -95,6 +95,11 @@ void set_error(const char *fmt, ...);
 // needed (growth synchronises the stream; steady state never grows).
 dlb_status scratch(dlb_ctx *ctx, size_t bytes, void **out);
 
+// Internal dropout code of the inference pass (dlb_dropout_desc.type): every
+// activation times dlb_dropout_desc.value, the keep probability
+// (Forward_Pass__Dropout__Bernoulli__Inference__OpenMP, fwp_mp.cpp L:4870-4892).
+constexpr int DROPOUT_INFERENCE_SCALE = 100;
+
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 

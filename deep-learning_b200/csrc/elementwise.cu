@@ -291,6 +291,7 @@ __device__ __forceinline__ float apply_dropout(float a, const DropoutDev &dp, in
     case DLB_DROPOUT_BERNOULLI: return dp.mask[col] ? a : 0.f;                  // fwp_mp.cpp L:4842-4868
     case DLB_DROPOUT_BERNOULLI_INVERTED: return dp.mask[col] ? a * dp.scale : 0.f;  // L:4809-4840
     case DLB_DROPOUT_UOUT: return a + a * dp.noise[idx];                         // L:4959-4985
+    case DROPOUT_INFERENCE_SCALE: return a * dp.scale;                           // L:4870-4892
     default: return a;
   }
 }
@@ -688,6 +689,8 @@ dlb_status activation_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_u
         DLB_REQUIRE(dropout->value > 0.f, "dlb_activation_forward: keep probability");
         dp.scale = 1.f / dropout->value;
       }
+    } else if (dp.type == DROPOUT_INFERENCE_SCALE) {
+      dp.scale = dropout->value;
     } else if (dp.type == DLB_DROPOUT_UOUT) {
       DLB_REQUIRE(dp.noise, "dlb_activation_forward: UOut needs noise");
     } else {
@@ -1080,3 +1083,75 @@ dlb_status dlb_shakedrop_backward(dlb_ctx *ctx, const float *d, const uint8_t *r
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Evaluation: loss and accuracy counter of the outputs of a forward pass, no
+// error.  One warp per row.
+// ref: compute_loss_fwp_mp (v1/learner/compute_loss_mp.cpp L:28-113), loss_fn
+// (v1/learner/compute_loss.cpp L:55-99).
+// ---------------------------------------------------------------------------
+namespace dlb {
+__global__ void loss_eval_kernel(int loss, int accu_fn, float accu_var, const float *__restrict__ q,
+                                 const float *__restrict__ y, int rows, int n, double *loss_sum,
+                                 double *accu_sum) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
+  double local = 0.0, hits = 0.0;
+  if (warp < rows) {
+    const float *qr = q + (size_t)warp * n, *yr = y + (size_t)warp * n;
+    const float EPS = 1e-7f;
+    // Largest output (the last of equal maxima, as `q >= q_max` keeps it) and
+    // the last target flag, for the cross-entropy accuracy.
+    float best = -3.402823466e+38f;
+    int predict = 0, target = n;
+    for (int j = lane; j < n; j += 32) {
+      const float qj = qr[j], yj = yr[j];
+      if (loss == DLB_LOSS_CROSS_ENTROPY) {
+        if (yj == 1.f) local += (double)(-(yj * logf(clipf(qj, EPS, 1.f - EPS))));
+      } else {
+        const float d = qj - yj;
+        local += (double)(d * d);
+      }
+      if (accu_fn == DLB_ACCU_DISTANCE) {
+        if (fabsf(qj - yj) <= accu_var) hits += 1.0;
+      } else {
+        if (qj >= best) { best = qj; predict = j; }
+        if (yj == 1.f) target = j;
+      }
+    }
+    if (accu_fn == DLB_ACCU_CROSS_ENTROPY) {
+      for (int o = 16; o; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int op = __shfl_xor_sync(0xffffffffu, predict, o);
+        int ot = __shfl_xor_sync(0xffffffffu, target, o);
+        if (ob > best || (ob == best && op > predict)) { best = ob; predict = op; }
+        // the last flagged index wins; n means none
+        if (ot != n && (target == n || ot > target)) target = ot;
+      }
+      if (lane == 0 && predict == target) hits = 1.0;
+    }
+  }
+  for (int o = 16; o; o >>= 1) {
+    local += __shfl_xor_sync(0xffffffffu, local, o);
+    if (accu_fn == DLB_ACCU_DISTANCE) hits += __shfl_xor_sync(0xffffffffu, hits, o);
+  }
+  if (lane == 0) {
+    if (local != 0.0) atomicAdd(loss_sum, local);
+    if (hits != 0.0) atomicAdd(accu_sum, hits);
+  }
+}
+}  // namespace dlb
+
+extern "C" dlb_status dlb_loss_eval(dlb_ctx *ctx, int loss, int accu_fn, float accu_var, const float *q,
+                                    const float *y, int rows, int n_out, double *loss_sum,
+                                    double *accu_sum) {
+  DLB_REQUIRE(ctx && q && y && loss_sum && accu_sum && rows > 0 && n_out > 0, "dlb_loss_eval");
+  if ((loss != DLB_LOSS_MSE && loss != DLB_LOSS_CROSS_ENTROPY) ||
+      (accu_fn != DLB_ACCU_DISTANCE && accu_fn != DLB_ACCU_CROSS_ENTROPY)) {
+    set_error("dlb_loss_eval: loss %d / accuracy function %d outside the supported set", loss, accu_fn);
+    return DLB_ERR_UNSUPPORTED;
+  }
+  loss_eval_kernel<<<ceil_div(rows, 8), 256, 0, ctx->stream>>>(loss, accu_fn, accu_var, q, y, rows, n_out,
+                                                               loss_sum, accu_sum);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}

@@ -95,6 +95,14 @@ struct dlb_model {
   // the reorder to [T, rows, n].
   float *input_rows = nullptr, *target_rows = nullptr;
   float *wd_mask = nullptr;  // [P]: 1 where weight decay applies
+  // Evaluation (Driver::evalt): propagation state, accuracy function and its
+  // counter; r = 1 and d = 0 for the normalization by running averages.
+  int propagation = DLB_PROPAGATION_TRAINING;
+  int accu_fn = DLB_ACCU_DISTANCE;   // v1/learner/model.hpp L:157
+  float accu_var = 0.49f;            // L:3019
+  double *accu_sum = nullptr;
+  float *ones = nullptr, *zeros = nullptr;
+  size_t const_units = 0;
   float *stage_x = nullptr, *stage_y = nullptr;  // pinned
   size_t stage_x_elems = 0, stage_y_elems = 0;
   double *loss_sum = nullptr;
@@ -336,6 +344,8 @@ dlb_status ensure_batch(dlb_model *m, size_t rows) {
   if (!m->loss_sum) {
     DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&m->loss_sum), sizeof(double)));
     DLB_TRY(dlb_memset(m->ctx, m->loss_sum, 0, sizeof(double)));
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&m->accu_sum), sizeof(double)));
+    DLB_TRY(dlb_memset(m->ctx, m->accu_sum, 0, sizeof(double)));
   }
   m->alloc_rows = rows;
   return DLB_OK;
@@ -474,6 +484,22 @@ dlb_status norm_backward(dlb_model *m, LayerRT &l, float *e, float *e_lo, const 
   return dlb_brn_backward_apply(m->ctx, e, e_lo, in, &u, l.bwd_sums, Bg, B, n);
 }
 
+// Arrays of ones and zeros, the r and d of a normalization by running averages.
+dlb_status ensure_constants(dlb_model *m, size_t units) {
+  if (units <= m->const_units) return DLB_OK;
+  if (m->ones) DLB_TRY(dlb_free(m->ctx, m->ones));
+  if (m->zeros) DLB_TRY(dlb_free(m->ctx, m->zeros));
+  m->ones = m->zeros = nullptr;
+  std::vector<float> one(units, 1.f);
+  DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&m->ones), units * sizeof(float)));
+  DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&m->zeros), units * sizeof(float)));
+  DLB_TRY(dlb_memcpy_h2d(m->ctx, m->ones, one.data(), units * sizeof(float)));
+  DLB_TRY(dlb_memset(m->ctx, m->zeros, 0, units * sizeof(float)));
+  DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
+  m->const_units = units;
+  return DLB_OK;
+}
+
 // A layer with UOut needs this step's draws for at least B rows.
 dlb_status uout_ready(dlb_model *m, const LayerRT &l, size_t index, int B) {
   (void)m;
@@ -578,6 +604,15 @@ dlb_status forward_layers_time(dlb_model *m, size_t rows) {
 }
 
 dlb_status forward_layers(dlb_model *m, size_t rows) {
+  const bool inference = m->propagation == DLB_PROPAGATION_INFERENCE;
+  if (inference) {
+    for (const LayerRT &l : m->layers)
+      if (time_stepped(m) || l.type != DLB_LAYER_FULLY_CONNECTED || l.group != 0) {
+        set_error("model: the inference pass covers plain stacks of fully connected layers; residual "
+                  "blocks and time-stepped models are outside the supported path");
+        return DLB_ERR_UNSUPPORTED;
+      }
+  }
   if (time_stepped(m)) return forward_layers_time(m, rows);
   DLB_TRY(refresh_weight_residuals(m));
   const int B = (int)rows;
@@ -599,9 +634,27 @@ dlb_status forward_layers(dlb_model *m, size_t rows) {
     DLB_TRY(dlb_fc_forward(m->ctx, X, X_lo, m->params + l.first_conn, m->params_lo + l.first_conn,
                            bias, l.Z, B, I, H));
     dlb_brn_unit_arrays u;
-    if (norm) DLB_TRY(norm_statistics(m, l, l.Z, B, &u));
+    if (norm && inference) {
+      // Forward_Pass__Batch_Normalization__Inference__OpenMP (fwp_mp.cpp L:4461-4491),
+      // also for batch renormalization: gamma (z - running mean) / running sigma + beta.
+      DLB_TRY(ensure_constants(m, l.norm_units));
+      u = unit_arrays(m, l, 0);
+      u.mean = u.mean_average;
+      u.sigma = u.sigma_average;
+      u.r = m->ones;
+      u.d = m->zeros;
+    } else if (norm) {
+      DLB_TRY(norm_statistics(m, l, l.Z, B, &u));
+    }
     if (l.af == DLB_AF_SOFTMAX) {
       DLB_TRY(dlb_softmax_forward(m->ctx, l.Z, l.A, B, H));
+    } else if (inference) {
+      // Plain Bernoulli dropout scales by the keep probability at inference
+      // (fwp_mp.cpp L:4870-4892); the other kinds do nothing.
+      dlb_dropout_desc dp{DROPOUT_INFERENCE_SCALE, l.dropout_value, nullptr, nullptr};
+      DLB_TRY(dlb_activation_forward(m->ctx, l.Z, norm ? &u : nullptr, l.af,
+                                     l.dropout == DLB_DROPOUT_BERNOULLI ? &dp : nullptr, l.A,
+                                     last ? nullptr : l.A_lo, B, H));
     } else {
       DLB_TRY(uout_ready(m, l, i, B));
       dlb_dropout_desc dp{l.dropout, l.dropout_value, l.mask, l.uout};
@@ -697,6 +750,9 @@ dlb_status dlb_model_destroy(dlb_model *m) {
   for (float *p : flat)
     if (p) dlb_free(m->ctx, p);
   if (m->loss_sum) dlb_free(m->ctx, m->loss_sum);
+  if (m->accu_sum) dlb_free(m->ctx, m->accu_sum);
+  if (m->ones) dlb_free(m->ctx, m->ones);
+  if (m->zeros) dlb_free(m->ctx, m->zeros);
   if (m->stage_x) dlb_host_free(m->stage_x);
   if (m->stage_y) dlb_host_free(m->stage_y);
   delete m;
@@ -1401,6 +1457,68 @@ dlb_status dlb_model_reset_loss(dlb_model *m) {
   DLB_REQUIRE(m, "null");
   m->loss_rows = 0;
   if (m->loss_sum) DLB_TRY(dlb_memset(m->ctx, m->loss_sum, 0, sizeof(double)));
+  if (m->accu_sum) DLB_TRY(dlb_memset(m->ctx, m->accu_sum, 0, sizeof(double)));
+  return DLB_OK;
+}
+
+// ref: Model::type_state_propagation as Driver::evalt / Driver::train set it
+// (drivers/driver.cpp L:63, L:111).
+dlb_status dlb_model_set_propagation(dlb_model *m, int state) {
+  DLB_REQUIRE(m && (state == DLB_PROPAGATION_INFERENCE || state == DLB_PROPAGATION_TRAINING), "set_propagation");
+  m->propagation = state;
+  return DLB_OK;
+}
+
+// ref: Model::set_accu_fn (v1/learner/train.cpp L:63-75), Model::acc_var.
+dlb_status dlb_model_set_accu_fn(dlb_model *m, int fn) {
+  DLB_REQUIRE(m, "null");
+  if (fn != DLB_ACCU_CROSS_ENTROPY && fn != DLB_ACCU_DISTANCE) {
+    set_error("set_accu_fn: accuracy function %d is outside the supported set (CROSS_ENTROPY, DISTANCE)", fn);
+    return DLB_ERR_UNSUPPORTED;
+  }
+  m->accu_fn = fn;
+  return DLB_OK;
+}
+dlb_status dlb_model_set_accu_var(dlb_model *m, float v) {
+  DLB_REQUIRE(m && v >= 0.f, "set_accu_var");
+  m->accu_var = v;
+  return DLB_OK;
+}
+
+// ref: Model::compute_loss (v1/learner/compute_loss.cpp L:140-161).
+dlb_status dlb_model_compute_loss_device(dlb_model *m, size_t rows, const float *Y_dev) {
+  DLB_REQUIRE(m && Y_dev && rows > 0 && rows <= m->alloc_rows, "compute_loss_device");
+  if (time_stepped(m)) {
+    set_error("compute_loss: time-stepped models are outside the supported path of the evaluation pass");
+    return DLB_ERR_UNSUPPORTED;
+  }
+  LayerRT &o = m->layers.back();
+  DLB_TRY(dlb_loss_eval(m->ctx, m->loss, m->accu_fn, m->accu_var, o.A, Y_dev, (int)rows, (int)o.units,
+                        m->loss_sum, m->accu_sum));
+  m->loss_rows += rows;
+  return DLB_OK;
+}
+dlb_status dlb_model_compute_loss(dlb_model *m, size_t rows, const float *const *Ym) {
+  DLB_REQUIRE(m && Ym && rows > 0 && rows <= m->alloc_rows, "compute_loss");
+  DLB_TRY(stage_rows(m, &m->stage_y, &m->stage_y_elems, rows, m->seq_w * n_out(m), Ym, m->target));
+  return dlb_model_compute_loss_device(m, rows, m->target);
+}
+
+// Percent of trials since reset_loss, over every rank's rows
+// (Model::get_accu, v1/learner/metrics.cpp L:89-114; n_acc_trial as
+// Driver::evalt sets it, drivers/driver.cpp L:95-99).
+dlb_status dlb_model_get_accuracy(dlb_model *m, double *accuracy) {
+  DLB_REQUIRE(m && accuracy && m->accu_sum, "get_accuracy");
+  void *scr = nullptr;
+  DLB_TRY(scratch(m->ctx, sizeof(double), &scr));
+  double *tmp = static_cast<double *>(scr);
+  DLB_TRY(dlb_memcpy_d2d(m->ctx, tmp, m->accu_sum, sizeof(double)));
+  DLB_TRY(dlb_allreduce_f64(m->ctx, tmp, 1));
+  double s = 0.0;
+  DLB_TRY(dlb_memcpy_d2h(m->ctx, &s, tmp, sizeof(double)));
+  const double trials = (double)m->loss_rows * (double)dlb_comm_world(m->ctx) *
+                        (m->accu_fn == DLB_ACCU_CROSS_ENTROPY ? 1.0 : (double)n_out(m));
+  *accuracy = trials == 0.0 ? 0.0 : s / trials * 100.0;
   return DLB_OK;
 }
 

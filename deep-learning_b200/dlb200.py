@@ -130,6 +130,13 @@ SIGNATURES = {
     "dlb_model_merge_derivatives": (_i, [_vp]),
     "dlb_model_update_weights": (_i, [_vp, _sz, _sz]),
     "dlb_model_get_loss": (_i, [_vp, C.POINTER(_d)]),
+    "dlb_model_set_propagation": (_i, [_vp, _i]),
+    "dlb_model_set_accu_fn": (_i, [_vp, _i]),
+    "dlb_model_set_accu_var": (_i, [_vp, _f]),
+    "dlb_model_compute_loss": (_i, [_vp, _sz, _vp]),
+    "dlb_model_compute_loss_device": (_i, [_vp, _sz, _vp]),
+    "dlb_model_get_accuracy": (_i, [_vp, C.POINTER(_d)]),
+    "dlb_loss_eval": (_i, [_vp, _i, _i, _f, _vp, _vp, _i, _i, _vp, _vp]),
     "dlb_model_reset_loss": (_i, [_vp]),
     "dlb_model_forward_pass_device": (_i, [_vp, _sz, _vp]),
     "dlb_model_compute_error_device": (_i, [_vp, _sz, _vp]),
@@ -465,6 +472,24 @@ class Model:
     def compute_error(self, batch, Y):
         self._y, rows = self._row_pointers(Y)
         check(self.L.dlb_model_compute_error(self.h, batch, rows), "compute_error")
+
+    def set_propagation(self, state):
+        check(self.L.dlb_model_set_propagation(self.h, int(state)), "set_propagation")
+
+    def set_accu_fn(self, fn):
+        check(self.L.dlb_model_set_accu_fn(self.h, int(fn)), "set_accu_fn")
+
+    def set_accu_var(self, v):
+        check(self.L.dlb_model_set_accu_var(self.h, float(v)), "set_accu_var")
+
+    def compute_loss(self, batch, Y):
+        self._y, rows = self._row_pointers(Y)
+        check(self.L.dlb_model_compute_loss(self.h, batch, rows), "compute_loss")
+
+    def get_accu(self, rows_total=None):
+        v = _d(0.0)
+        check(self.L.dlb_model_get_accuracy(self.h, C.byref(v)), "get_accuracy")
+        return v.value
 
     def backward_pass(self, batch):
         check(self.L.dlb_model_backward_pass(self.h, batch), "backward_pass")

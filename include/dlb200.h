@@ -49,6 +49,8 @@ enum { DLB_LAYER_FULLY_CONNECTED = 3, DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RE
        DLB_LAYER_RESIDUAL = 9 };
 enum { DLB_NORM_NONE = 0, DLB_NORM_BATCH_RENORMALIZATION = 2 };
 enum { DLB_MODEL_FEEDFORWARD = 3, DLB_MODEL_RECURRENT = 4 };
+enum { DLB_PROPAGATION_INFERENCE = 0, DLB_PROPAGATION_TRAINING = 1 };
+enum { DLB_ACCU_CROSS_ENTROPY = 1, DLB_ACCU_DISTANCE = 3 };
 
 const char *dlb_status_string(dlb_status s);
 /* Last error text recorded on the calling thread ("" if none). */
@@ -350,6 +352,14 @@ dlb_status dlb_loss_delta(dlb_ctx *ctx, int loss, int af, const float *pre, cons
                           const float *y, float *delta, float *delta_lo, int rows, int n_out,
                           int global_rows, double *loss_sum);
 
+/* Evaluation: loss_sum += the loss of every output against its target (as
+ * dlb_loss_delta accumulates it) and accu_sum += the accuracy count: DISTANCE:
+ * elements with |q - y| <= accu_var; CROSS_ENTROPY: rows whose largest output
+ * (the last of equal maxima) sits where the target is 1.  No error is formed.
+ * ref: compute_loss_fwp_mp (v1/learner/compute_loss_mp.cpp L:28-113). */
+dlb_status dlb_loss_eval(dlb_ctx *ctx, int loss, int accu_fn, float accu_var, const float *q,
+                         const float *y, int rows, int n_out, double *loss_sum, double *accu_sum);
+
 /* ------------------------------------------------------------------------ */
 /* Optimizer: one pass over flat arrays of n elements; gradient zeroed after
  * use as the reference does. */
@@ -467,6 +477,19 @@ dlb_status dlb_model_forward_pass(dlb_model *m, size_t rows, const float *const 
 dlb_status dlb_model_compute_error(dlb_model *m, size_t rows, const float *const *Ym);
 dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows);
 dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows);
+/* Evaluation, as Driver::evalt (drivers/driver.cpp L:60-105): set the
+ * propagation state to INFERENCE, run forward passes (normalization by the
+ * running averages, fwp_mp.cpp L:4461-4491; plain Bernoulli dropout scales by
+ * its keep probability, L:4870-4892), and after each one dlb_model_compute_loss
+ * (Model::compute_loss, v1/learner/compute_loss.cpp L:140-161) accumulates the
+ * loss and the accuracy counter without forming an error.  dlb_model_get_loss
+ * and dlb_model_get_accuracy (percent, Model::get_accu) read them. */
+dlb_status dlb_model_set_propagation(dlb_model *m, int state);
+dlb_status dlb_model_set_accu_fn(dlb_model *m, int fn);
+dlb_status dlb_model_set_accu_var(dlb_model *m, float v);
+dlb_status dlb_model_compute_loss(dlb_model *m, size_t rows, const float *const *Ym);
+dlb_status dlb_model_compute_loss_device(dlb_model *m, size_t rows, const float *Y_dev);
+dlb_status dlb_model_get_accuracy(dlb_model *m, double *accuracy);
 /* Across GPUs this is the gradient all-reduce (the reference's thread merge,
  * v1/learner/merge.cpp L:76-100). */
 dlb_status dlb_model_merge_derivatives(dlb_model *m);

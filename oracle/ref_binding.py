@@ -53,6 +53,11 @@ def lib():
         "ref_set_max_batch_size": (i, [vp, sz]),
         "ref_set_mp": (i, [vp, i]),
         "ref_set_weight_decay": (i, [vp, C.c_double]),
+        "ref_set_propagation": (i, [vp, i]),
+        "ref_set_accu_fn": (i, [vp, i]),
+        "ref_set_accu_var": (i, [vp, C.c_double]),
+        "ref_compute_loss": (i, [vp, sz, _f32p]),
+        "ref_get_accu": (C.c_double, [vp, sz]),
         "ref_seed_uout": (i, [vp, C.c_uint]),
         "ref_uout_draws": (i, [C.c_uint, sz, sz, _szp, _f32p, _f32p]),
         "ref_set_seq_w": (i, [vp, sz]),
@@ -161,6 +166,23 @@ class RefModel:
 
     def set_seq_w(self, delays):
         _ck(self.L.ref_set_seq_w(self.h, delays), "set_seq_w")
+
+    def set_propagation(self, state):
+        """0: inference, 1: training (PROPAGATION, v1/data/enum/propagation.hpp)."""
+        _ck(self.L.ref_set_propagation(self.h, int(state)), "set_propagation")
+
+    def set_accu_fn(self, fn):
+        _ck(self.L.ref_set_accu_fn(self.h, int(fn)), "set_accu_fn")
+
+    def set_accu_var(self, v):
+        _ck(self.L.ref_set_accu_var(self.h, float(v)), "set_accu_var")
+
+    def compute_loss(self, batch, Y):
+        Y = np.ascontiguousarray(Y, dtype=np.float32)
+        _ck(self.L.ref_compute_loss(self.h, batch, Y), "compute_loss")
+
+    def get_accu(self, rows_total):
+        return float(self.L.ref_get_accu(self.h, rows_total))
 
     def seed_uout(self, seed):
         _ck(self.L.ref_seed_uout(self.h, seed), "seed_uout")

@@ -438,6 +438,41 @@ int ref_compute_error(ref_model m, size_t batch, const float *Y) {
   return 0;
 }
 
+/* Evaluation, as Driver::evalt (drivers/driver.cpp L:60-105, L:172-226): the
+ * propagation state, the loss-only pass over the outputs of a forward pass,
+ * the merge of the per-thread counters and the accuracy in percent. */
+int ref_set_propagation(ref_model m, int state) {
+  H(m)->model.type_state_propagation = static_cast<PROPAGATION::TYPE>(state);
+  return 0;
+}
+int ref_set_accu_fn(ref_model m, int fn) {
+  H(m)->model.set_accu_fn(static_cast<ACCU_FN::TYPE>(fn));
+  return 0;
+}
+int ref_set_accu_var(ref_model m, double v) {
+  H(m)->model.acc_var = static_cast<real>(v);
+  return 0;
+}
+int ref_compute_loss(ref_model m, size_t batch, const float *Y) {
+  Handle *h = H(m);
+  Model &M = h->model;
+  make_rows(h->rows_y, Y, batch, M.seq_w * M.n_out);
+  if (M.use_mp && M.is_mp_initialized) {
+#pragma omp parallel
+    M.compute_loss(batch, h->rows_y.data());
+  } else {
+    M.compute_loss(batch, h->rows_y.data());
+  }
+  M.merge_mp_accu_loss();
+  return 0;
+}
+double ref_get_accu(ref_model m, size_t rows_total) {
+  Model &M = H(m)->model;
+  M.n_acc_trial = rows_total * (M.seq_w - M.n_time_delay) *
+                  (ACCU_FN::CROSS_ENTROPY == M.type_accuracy_function ? 1_UZ : M.n_out);
+  return M.get_accu(ENV::NONE);
+}
+
 int ref_backward_pass(ref_model m, size_t batch) {
   Model &M = H(m)->model;
   if (M.use_mp && M.is_mp_initialized) {

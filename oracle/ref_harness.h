@@ -46,6 +46,11 @@ double ref_get_hparam(ref_model m, const char *name);
 int ref_set_max_batch_size(ref_model m, size_t b);
 int ref_set_mp(ref_model m, int use_mp);
 int ref_set_weight_decay(ref_model m, double value);
+int ref_set_propagation(ref_model m, int state);
+int ref_set_accu_fn(ref_model m, int fn);
+int ref_set_accu_var(ref_model m, double v);
+int ref_compute_loss(ref_model m, size_t batch, const float *Y);
+double ref_get_accu(ref_model m, size_t rows_total);
 int ref_seed_uout(ref_model m, unsigned seed);
 int ref_uout_draws(unsigned seed, size_t n_layers, size_t rows, const size_t *widths,
                    const float *betas, float *out);

@@ -184,3 +184,45 @@ def test_uout_dropout(gpu_ctx):
     plain = util.trace(gpu_model(gpu_ctx, dict(cfg, layers=[dict(l, dropout=None) for l in cfg["layers"]]), p0),
                        cfg, 1, X, Y, {})
     assert util.rel_l2(plain["act2"], got["act2"]) > 1e-2   # the noise is applied
+
+
+@pytest.mark.parametrize("case", ["brn_bernoulli_distance", "softmax_accuracy"])
+def test_evaluation_pass(gpu_ctx, case):
+    """Inference forward (running averages, dropout scaling) and the loss /
+    accuracy pass, against the CPU restatement (itself pinned to the compiled
+    reference's Driver::evalt sequence)."""
+    cfg, fn = {
+        "brn_bernoulli_distance": (configs.deep_brn_mlp(64, 128, 2, 32, 96), fc_step.ACCU_DISTANCE),
+        "softmax_accuracy": (configs.mlp_softmax(96, 128, 10, 128), fc_step.ACCU_CROSS_ENTROPY),
+    }[case]
+    B, last = cfg["batch"], len(cfg["layers"]) - 1
+    X, Y = configs.synthetic_batch(cfg)
+    Xe, Ye = configs.synthetic_batch(dict(cfg, data_seed=5))
+    masks = configs.dropout_masks(cfg)
+    p0, _ = util.kink_free_parameters(cfg, fc_step.OracleModel, X, masks, scale=1.0 / np.sqrt(128))
+    out = []
+    for m in (util.build(fc_step.OracleModel(), cfg, params=p0), gpu_model(gpu_ctx, cfg, p0)):
+        m.train_begin(B)
+        for li, mk in masks.items():
+            m.set_dropout_mask(li, mk)
+        m.train_step(B, X, Y)
+        m.set_propagation(0)
+        m.set_accu_fn(fn)
+        m.reset_loss()
+        m.forward_pass(B, Xe)
+        m.compute_loss(B, Ye)
+        out.append((m.get_loss(), m.get_accu(B), m.get_layer_outputs(last, B).reshape(B, -1)))
+        m.set_propagation(1)
+    (lo, ao, qo), (lg, ag, qg) = out
+    assert gpu_ctx.sync() == 0
+    assert util.rel_l2(qg, qo) <= TOL_1
+    assert abs(lg - lo) <= 1e-5 * abs(lo)
+    assert abs(ag - ao) <= 100.0 * 2 / (B * (1 if fn == fc_step.ACCU_CROSS_ENTROPY else qo.shape[1]))
+
+
+def test_inference_of_a_residual_model_is_refused(gpu_ctx):
+    cfg = configs.residual_mlp(width=32, blocks=1, n_out=5, batch=8)
+    m = util.build(dlb200.Model(gpu_ctx), cfg, seed=0)
+    m.set_propagation(0)
+    with pytest.raises(dlb200.DlbError):
+        m.forward_pass(8, np.zeros((8, 32), np.float32))

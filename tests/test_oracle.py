@@ -119,3 +119,39 @@ def test_uout_matches_compiled_reference():
         assert abs(ref.train_step(B, X, Y) - ora.train_step(B, X, Y)) <= 1e-6
         assert util.rel_l2(ora.get_layer_outputs(2, B), ref.get_layer_outputs(2, B).reshape(B, -1)) <= TOL_L2
         assert util.rel_l2(ora.get_array("parameters"), ref.get_array("parameters")) <= TOL_L2
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("mp", [False, True], ids=["serial", "openmp"])
+@pytest.mark.parametrize("case", ["brn_bernoulli_distance", "softmax_accuracy", "brn_inverted_distance"])
+def test_evaluation_pass_matches_compiled_reference(case, mp):
+    """Driver::evalt: forward pass in inference mode (running averages, dropout
+    scaling), loss and accuracy without an error (drivers/driver.cpp L:60-105)."""
+    cfg, fn = {
+        "brn_bernoulli_distance": (configs.deep_brn_mlp(20, 32, 2, 12, 24), fc_step.ACCU_DISTANCE),
+        "softmax_accuracy": (configs.mlp_softmax(36, 24, 10, 16), fc_step.ACCU_CROSS_ENTROPY),
+        "brn_inverted_distance": (configs.deep_brn_mlp(20, 32, 2, 12, 24, dropout=LAYER_DROPOUT.BERNOULLI_INVERTED),
+                                  fc_step.ACCU_DISTANCE),
+    }[case]
+    cfg = dict(cfg, mp=mp)
+    B, last = cfg["batch"], len(cfg["layers"]) - 1
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    ora = util.build(fc_step.OracleModel(), cfg, params=ref.get_array("parameters"))
+    X, Y = configs.synthetic_batch(cfg)
+    Xe, Ye = configs.synthetic_batch(dict(cfg, data_seed=5))
+    out = []
+    for m in (ref, ora):
+        m.train_begin(B)
+        for li, mk in configs.dropout_masks(cfg).items():
+            m.set_dropout_mask(li, mk)
+        for _ in range(3):
+            m.train_step(B, X, Y)   # move the running averages away from their start
+        m.set_propagation(0)
+        m.set_accu_fn(fn)
+        m.reset_loss()
+        m.forward_pass(B, Xe)
+        m.compute_loss(B, Ye)
+        out.append((m.get_loss(), m.get_accu(B), m.get_layer_outputs(last, B).reshape(B, -1)))
+    (lr, ar, qr), (lo, ao, qo) = out
+    assert abs(lr - lo) <= 1e-6 * abs(lr) and ar == ao
+    assert util.rel_l2(qo, qr) <= TOL_L2
