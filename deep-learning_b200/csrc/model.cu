@@ -105,6 +105,17 @@ struct dlb_model {
   size_t const_units = 0;
   float *stage_x = nullptr, *stage_y = nullptr;  // pinned
   size_t stage_x_elems = 0, stage_y_elems = 0;
+  // Batches copied ahead of the step that uses them: two device slots filled
+  // on a stream of their own, so that the copy of batch i+1 runs under the
+  // kernels of batch i.
+  struct Ahead {
+    float *x = nullptr, *y = nullptr;
+    size_t x_elems = 0, y_elems = 0, rows = 0;
+    cudaEvent_t ready = nullptr, consumed = nullptr;
+    bool in_use = false;  // `consumed` has been recorded at least once
+  } ahead[2];
+  cudaStream_t copy_stream = nullptr;
+  size_t ahead_head = 0, ahead_tail = 0;  // staged so far, consumed so far
   double *loss_sum = nullptr;
   size_t loss_rows = 0;  // rows accumulated since reset_loss
   bool params_lo_valid = false;
@@ -755,6 +766,16 @@ dlb_status dlb_model_destroy(dlb_model *m) {
   if (m->zeros) dlb_free(m->ctx, m->zeros);
   if (m->stage_x) dlb_host_free(m->stage_x);
   if (m->stage_y) dlb_host_free(m->stage_y);
+  if (m->copy_stream) {
+    cudaStreamSynchronize(m->copy_stream);
+    cudaStreamDestroy(m->copy_stream);
+  }
+  for (auto &a : m->ahead) {
+    if (a.x) dlb_free(m->ctx, a.x);
+    if (a.y) dlb_free(m->ctx, a.y);
+    if (a.ready) cudaEventDestroy(a.ready);
+    if (a.consumed) cudaEventDestroy(a.consumed);
+  }
   delete m;
   return DLB_OK;
 }
@@ -1627,6 +1648,67 @@ dlb_status dlb_model_train_step(dlb_model *m, size_t rows, const float *X_host,
   DLB_TRY(dlb_model_forward_pass_device(m, rows, x_dev));
   DLB_TRY(dlb_model_compute_error_device(m, rows, y_dev));
   DLB_TRY(backward_update_merge(m, rows));
+  if (loss) DLB_TRY(dlb_model_get_loss(m, loss));
+  const size_t g = m->global_rows ? m->global_rows : rows;
+  return dlb_model_update_weights(m, g, g);
+}
+
+// Input side of the mini-batch loop, MiniBatch::train_mp
+// (v1/data/dataset/minibatch.cpp L:286-323): the reference hands each batch
+// to the model as host rows; here the next batch crosses PCIe while the
+// current one trains.
+dlb_status dlb_model_stage_batch(dlb_model *m, size_t rows, const float *X_host, const float *Y_host) {
+  DLB_REQUIRE(m && X_host && Y_host && rows > 0, "stage_batch");
+  DLB_TRY(check_supported(m));
+  DLB_REQUIRE(m->ahead_head - m->ahead_tail < 2, "stage_batch: two batches are staged already");
+  DLB_CUDA(cudaSetDevice(m->ctx->device));
+  if (!m->copy_stream) DLB_CUDA(cudaStreamCreateWithFlags(&m->copy_stream, cudaStreamNonBlocking));
+  dlb_model::Ahead &a = m->ahead[m->ahead_head % 2];
+  if (!a.ready) {
+    DLB_CUDA(cudaEventCreateWithFlags(&a.ready, cudaEventDisableTiming));
+    DLB_CUDA(cudaEventCreateWithFlags(&a.consumed, cudaEventDisableTiming));
+  }
+  // The step that read this slot last must be past its reads.
+  if (a.in_use) DLB_CUDA(cudaStreamWaitEvent(m->copy_stream, a.consumed, 0));
+  const size_t nx = rows * m->seq_w * n_in(m), ny = rows * m->seq_w * n_out(m);
+  auto fit = [&](float **buf, size_t *have, size_t need) -> dlb_status {
+    if (need <= *have) return DLB_OK;
+    if (*buf) {
+      DLB_CUDA(cudaStreamSynchronize(m->copy_stream));
+      DLB_CUDA(cudaStreamSynchronize(m->ctx->stream));
+      DLB_TRY(dlb_free(m->ctx, *buf));
+    }
+    *buf = nullptr;
+    *have = 0;
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(buf), need * sizeof(float)));
+    *have = need;
+    return DLB_OK;
+  };
+  DLB_TRY(fit(&a.x, &a.x_elems, nx));
+  DLB_TRY(fit(&a.y, &a.y_elems, ny));
+  DLB_CUDA(cudaMemcpyAsync(a.x, X_host, nx * sizeof(float), cudaMemcpyHostToDevice, m->copy_stream));
+  DLB_CUDA(cudaMemcpyAsync(a.y, Y_host, ny * sizeof(float), cudaMemcpyHostToDevice, m->copy_stream));
+  DLB_CUDA(cudaEventRecord(a.ready, m->copy_stream));
+  a.rows = rows;
+  ++m->ahead_head;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_train_step_staged(dlb_model *m, double *loss) {
+  DLB_REQUIRE(m, "train_step_staged");
+  DLB_REQUIRE(m->ahead_head > m->ahead_tail, "train_step_staged: no batch has been staged");
+  dlb_model::Ahead &a = m->ahead[m->ahead_tail % 2];
+  ++m->ahead_tail;
+  const size_t rows = a.rows;
+  DLB_CUDA(cudaStreamWaitEvent(m->ctx->stream, a.ready, 0));
+  DLB_TRY(dlb_model_reset_loss(m));
+  DLB_TRY(dlb_model_forward_pass_device(m, rows, a.x));
+  DLB_TRY(dlb_model_compute_error_device(m, rows, a.y));
+  DLB_CUDA(cudaEventRecord(a.consumed, m->ctx->stream));
+  a.in_use = true;
+  DLB_TRY(backward_update_merge(m, rows));
+  // The loss is read before the update is enqueued, as train_step does: the
+  // update then runs while the host prepares the next call.
   if (loss) DLB_TRY(dlb_model_get_loss(m, loss));
   const size_t g = m->global_rows ? m->global_rows : rows;
   return dlb_model_update_weights(m, g, g);

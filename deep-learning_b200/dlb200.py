@@ -142,6 +142,8 @@ SIGNATURES = {
     "dlb_model_compute_error_device": (_i, [_vp, _sz, _vp]),
     "dlb_model_train_step": (_i, [_vp, _sz, _vp, _vp, C.POINTER(_d)]),
     "dlb_model_train_step_device": (_i, [_vp, _sz, _vp, _vp]),
+    "dlb_model_stage_batch": (_i, [_vp, _sz, _vp, _vp]),
+    "dlb_model_train_step_staged": (_i, [_vp, C.POINTER(_d)]),
     "dlb_model_get_layer_outputs": (_i, [_vp, _sz, _sz, _vp]),
     "dlb_model_get_layer_errors": (_i, [_vp, _sz, _sz, _i, _vp]),
 }
@@ -517,6 +519,21 @@ class Model:
         loss = _d(0.0)
         check(self.L.dlb_model_train_step(self.h, batch, _ptr(X), _ptr(Y), C.byref(loss) if want_loss else None),
               "train_step")
+        return loss.value
+
+    def stage_batch(self, batch, X, Y):
+        """Starts the host-to-device copy of one batch; X and Y are contiguous
+        float32 arrays (page-locked for an asynchronous copy) that stay
+        untouched until the step that uses them has been called."""
+        for a in (X, Y):
+            if not (isinstance(a, np.ndarray) and a.dtype == np.float32 and a.flags.c_contiguous):
+                raise ValueError("stage_batch: contiguous float32 arrays")
+        check(self.L.dlb_model_stage_batch(self.h, batch, _ptr(X), _ptr(Y)), "stage_batch")
+
+    def train_step_staged(self, want_loss=True):
+        loss = _d(0.0)
+        check(self.L.dlb_model_train_step_staged(self.h, C.byref(loss) if want_loss else None),
+              "train_step_staged")
         return loss.value
 
     def train_step_device(self, batch, X_dev, Y_dev):

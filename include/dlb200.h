@@ -505,6 +505,18 @@ dlb_status dlb_model_train_step(dlb_model *m, size_t rows, const float *X_host,
                                 const float *Y_host, double *loss);
 dlb_status dlb_model_train_step_device(dlb_model *m, size_t rows, const float *X_dev,
                                        const float *Y_dev);
+/* The same step with the input copy taken off the critical path.  stage_batch
+ * starts the host-to-device copy of one batch (contiguous [rows, seq_w*n]
+ * arrays, page-locked for the copy to be asynchronous; they must stay
+ * untouched until the step that uses them has been called) on a stream of its
+ * own and returns; up to two batches may be staged.  train_step_staged runs
+ * the step on the oldest staged batch.  Staging batch i+1 before stepping on
+ * batch i hides the copy under the kernels.  This is the mini-batch loop of
+ * MiniBatch::train_mp (v1/data/dataset/minibatch.cpp L:286-323): train on the
+ * batch, read its loss, update the weights, move to the next batch. */
+dlb_status dlb_model_stage_batch(dlb_model *m, size_t rows, const float *X_host,
+                                 const float *Y_host);
+dlb_status dlb_model_train_step_staged(dlb_model *m, double *loss);
 dlb_status dlb_model_get_layer_outputs(dlb_model *m, size_t layer, size_t rows, float *host_out);
 dlb_status dlb_model_get_layer_errors(dlb_model *m, size_t layer, size_t rows, int which,
                                       float *host_out);

@@ -116,6 +116,40 @@ def test_row_pointer_inputs_and_device_inputs_agree(gpu_ctx):
     assert np.array_equal(a.get_array("parameters"), b.get_array("parameters"))
 
 
+def test_staged_batches_train_like_train_step(gpu_ctx):
+    """Batches copied one step ahead on the copy stream give the same weights
+    and losses, bit for bit, as the same batches passed to train_step; the
+    third stage without a step in between is refused, and so is a step with
+    nothing staged."""
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96)
+    B = cfg["batch"]
+    batches = []
+    for step in range(5):
+        pair = []
+        for host in configs.synthetic_batch(cfg, step=step):
+            buf = dlb200.pinned_empty(host.shape)
+            buf[...] = host
+            pair.append(buf)
+        batches.append(tuple(pair))
+    a = util.build(dlb200.Model(gpu_ctx), cfg, seed=3)
+    b = util.build(dlb200.Model(gpu_ctx), cfg, seed=3)
+    want = [a.train_step(B, X, Y) for X, Y in batches]
+    with pytest.raises(dlb200.DlbError):
+        b.train_step_staged()
+    got = []
+    b.stage_batch(B, *batches[0])
+    for i in range(len(batches)):
+        if i + 1 < len(batches):
+            b.stage_batch(B, *batches[i + 1])
+            if i == 0:
+                with pytest.raises(dlb200.DlbError):
+                    b.stage_batch(B, *batches[2])
+        got.append(b.train_step_staged())
+    assert got == want
+    assert np.array_equal(a.get_array("parameters"), b.get_array("parameters"))
+    assert gpu_ctx.sync() == 0
+
+
 def test_unsupported_configurations_are_refused(gpu_ctx):
     m = dlb200.Model(gpu_ctx)
     m.compile([3, 3, 3], [8, 8, 4])
