@@ -44,6 +44,14 @@ struct dlb_ctx {
   float *scale_pool = nullptr;   // SCALE_SLOTS slots of 4 floats: s, 1/s, |x|max bits, unused
   std::vector<int> scale_free;
   std::map<uintptr_t, size_t> allocs;  // dlb_malloc'd blocks, to retire plane entries on free
+  // Exchange of small fp64 vectors through peer memory: every rank's buffer
+  // mapped by every rank of the node (peer.cu).
+  struct Peer {
+    bool ready = false;
+    void *local = nullptr;
+    void *mapped[8] = {};   // by rank; mapped[rank] == local
+    uint32_t seq = 0;       // exchanges so far, the same on every rank
+  } peer;
   uint64_t launches = 0;
   cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
   // Optional per-launch record of the tensor-core GEMM.
@@ -135,6 +143,19 @@ bool gemm_tcgen05_supported(const GemmOperand &A, const GemmOperand &B, const fl
                             long long ldc, int M, int N, int K);
 bool gemm_f16_supported(const GemmOperand &A, const GemmOperand &B, const float *C, long long ldc,
                         int M, int N, int K);
+// Peer-memory exchange (peer.cu) and the two communicator calls its set-up
+// needs (ctx.cu): every rank's `bytes` gathered into recv[world][bytes] on the
+// host, and the minimum of one int over the ranks.
+constexpr int PEER_MAX = 8;          // ranks of one node
+constexpr int PEER_CTAS = 32;        // blocks of one exchange
+constexpr size_t PEER_CAP = 32768;   // doubles per exchanged vector
+dlb_status peer_setup(dlb_ctx *ctx);
+void peer_teardown(dlb_ctx *ctx);
+bool peer_exchange_fits(dlb_ctx *ctx, size_t n);
+dlb_status peer_exchange_f64(dlb_ctx *ctx, double *buf, size_t n);
+dlb_status comm_allgather_host(dlb_ctx *ctx, const void *mine, void *all, size_t bytes);
+dlb_status comm_min_int(dlb_ctx *ctx, int *value);
+
 // Fills o.h_hi / h_lo / scale from the plane buffer registered for (o.ptr, aux),
 // if there is one and the planes are 16-byte aligned.
 bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o);

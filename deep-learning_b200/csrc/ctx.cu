@@ -135,6 +135,7 @@ struct Nccl {
   ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
                             cudaStream_t) = nullptr;
   const char *(*GetErrorString)(ncclResult_t) = nullptr;
@@ -152,6 +153,7 @@ static Nccl *nccl() {
       n.CommInitRank = (decltype(n.CommInitRank))dlsym(n.handle, "ncclCommInitRank");
       n.CommDestroy = (decltype(n.CommDestroy))dlsym(n.handle, "ncclCommDestroy");
       n.AllReduce = (decltype(n.AllReduce))dlsym(n.handle, "ncclAllReduce");
+      n.AllGather = (decltype(n.AllGather))dlsym(n.handle, "ncclAllGather");
       n.GetErrorString = (decltype(n.GetErrorString))dlsym(n.handle, "ncclGetErrorString");
     }
   }
@@ -168,6 +170,60 @@ static Nccl *nccl() {
       return DLB_ERR_COMM;                                                          \
     }                                                                               \
   } while (0)
+
+}  // namespace dlb
+
+namespace dlb {
+
+dlb_status comm_allgather_host(dlb_ctx *ctx, const void *mine, void *all, size_t bytes) {
+  if (!nccl()->AllGather) {
+    set_error("comm_allgather_host: the NCCL library has no ncclAllGather");
+    return DLB_ERR_COMM;
+  }
+  char *dev = nullptr;
+  DLB_CUDA(cudaMalloc(&dev, bytes * (size_t)(ctx->world + 1)));
+  dlb_status st = DLB_OK;
+  cudaError_t e = cudaMemcpyAsync(dev, mine, bytes, cudaMemcpyHostToDevice, ctx->stream);
+  if (e == cudaSuccess) {
+    ncclResult_t r = nccl()->AllGather(dev, dev + bytes, bytes, ncclChar, ctx->comm, ctx->stream);
+    if (r != ncclSuccess) {
+      set_error("comm_allgather_host: %s", nccl()->GetErrorString ? nccl()->GetErrorString(r) : "nccl");
+      st = DLB_ERR_COMM;
+    }
+  }
+  if (e == cudaSuccess && st == DLB_OK)
+    e = cudaMemcpyAsync(all, dev + bytes, bytes * (size_t)ctx->world, cudaMemcpyDeviceToHost, ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  cudaFree(dev);
+  if (e != cudaSuccess) {
+    set_error("comm_allgather_host: %s", cudaGetErrorString(e));
+    return DLB_ERR_CUDA;
+  }
+  return st;
+}
+
+dlb_status comm_min_int(dlb_ctx *ctx, int *value) {
+  int *dev = nullptr;
+  DLB_CUDA(cudaMalloc(&dev, sizeof(int)));
+  dlb_status st = DLB_OK;
+  cudaError_t e = cudaMemcpyAsync(dev, value, sizeof(int), cudaMemcpyHostToDevice, ctx->stream);
+  if (e == cudaSuccess) {
+    ncclResult_t r = nccl()->AllReduce(dev, dev, 1, ncclInt32, ncclMin, ctx->comm, ctx->stream);
+    if (r != ncclSuccess) {
+      set_error("comm_min_int: %s", nccl()->GetErrorString ? nccl()->GetErrorString(r) : "nccl");
+      st = DLB_ERR_COMM;
+    }
+  }
+  if (e == cudaSuccess && st == DLB_OK)
+    e = cudaMemcpyAsync(value, dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  cudaFree(dev);
+  if (e != cudaSuccess) {
+    set_error("comm_min_int: %s", cudaGetErrorString(e));
+    return DLB_ERR_CUDA;
+  }
+  return st;
+}
 
 }  // namespace dlb
 
@@ -234,6 +290,7 @@ dlb_status dlb_ctx_destroy(dlb_ctx *ctx) {
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   if (ctx->comm_stream) cudaStreamSynchronize(ctx->comm_stream);
+  peer_teardown(ctx);
   if (ctx->comm && nccl() && nccl()->CommDestroy) nccl()->CommDestroy(ctx->comm);
   if (ctx->comm_stream) cudaStreamDestroy(ctx->comm_stream);
   if (ctx->ev_main) cudaEventDestroy(ctx->ev_main);
@@ -417,6 +474,7 @@ dlb_status dlb_fc_weight_gradient(dlb_ctx *ctx, const float *delta, const float 
 
 // ---- NCCL -----------------------------------------------------------------------
 
+
 dlb_status dlb_comm_unique_id(char out_id[128]) {
   DLB_REQUIRE(out_id, "dlb_comm_unique_id: null");
   if (!nccl()) {
@@ -442,7 +500,7 @@ dlb_status dlb_comm_init(dlb_ctx *ctx, const char id[128], int rank, int world) 
   DLB_NCCL(nccl()->CommInitRank(&ctx->comm, world, uid, rank));
   ctx->rank = rank;
   ctx->world = world;
-  return DLB_OK;
+  return peer_setup(ctx);
 }
 
 int dlb_comm_world(dlb_ctx *ctx) { return ctx ? ctx->world : 1; }
@@ -482,6 +540,7 @@ dlb_status dlb_comm_join(dlb_ctx *ctx) {
 dlb_status dlb_allreduce_f64(dlb_ctx *ctx, double *buf, size_t n) {
   DLB_REQUIRE(ctx && (buf || n == 0), "dlb_allreduce_f64");
   if (!ctx->comm || ctx->world == 1 || n == 0) return DLB_OK;
+  if (peer_exchange_fits(ctx, n)) return peer_exchange_f64(ctx, buf, n);
   DLB_NCCL(nccl()->AllReduce(buf, buf, n, ncclFloat64, ncclSum, ctx->comm, ctx->stream));
   return DLB_OK;
 }

@@ -16,7 +16,7 @@
 //   empty[s]      one per CTA; the MMA lane's commit arrives on both
 //   acc_full[b]   one per CTA; the commit of a chunk arrives on both
 //   acc_empty[b]  lives in the even CTA; the drain warps of both CTAs arrive
-// Persistent over work items, last partial round split along k, chunked
+// Persistent over work items, last partial round cut along k, chunked
 // accumulation, bounded waits: as in gemm_x3_kernel.
 #include <stdlib.h>
 
@@ -101,20 +101,25 @@ struct PairPlan {
   static_assert(TOTAL <= 232448, "shared memory of one CTA");
 };
 
+// A work item: a whole tile, or one of the `parts` pieces along k of a tile of
+// the last partial round (pieces start on chunk boundaries).
 struct PairItem {
-  int m0, n0, kb_begin, num_kb, split, k_half;
+  int m0, n0, kb_begin, num_kb, split, piece;
 };
+__host__ __device__ __forceinline__ int piece_start(int piece, int parts, int total_kb, int chunk_kb) {
+  const int at = (int)(((long long)piece * total_kb / parts + chunk_kb - 1) / chunk_kb * chunk_kb);
+  return at < total_kb ? at : total_kb;
+}
 template <int CHUNK_KB>
-__device__ __forceinline__ PairItem pair_item(int item, int tiles_n, int whole_tiles, int total_kb) {
+__device__ __forceinline__ PairItem pair_item(int item, int tiles_n, int whole_tiles, int parts, int total_kb) {
   PairItem w;
   w.split = item >= whole_tiles;
-  const int tile_id = w.split ? whole_tiles + ((item - whole_tiles) >> 1) : item;
-  w.k_half = w.split ? ((item - whole_tiles) & 1) : 0;
+  const int tile_id = w.split ? whole_tiles + (item - whole_tiles) / parts : item;
+  w.piece = w.split ? (item - whole_tiles) % parts : 0;
   w.n0 = (tile_id % tiles_n) * PN;
   w.m0 = (tile_id / tiles_n) * PM;
-  const int mid_kb = min(total_kb, (total_kb / 2 + CHUNK_KB - 1) / CHUNK_KB * CHUNK_KB);
-  w.kb_begin = (w.split && w.k_half) ? mid_kb : 0;
-  w.num_kb = (w.split ? (w.k_half ? total_kb : mid_kb) : total_kb) - w.kb_begin;
+  w.kb_begin = w.split ? piece_start(w.piece, parts, total_kb, CHUNK_KB) : 0;
+  w.num_kb = (w.split ? piece_start(w.piece + 1, parts, total_kb, CHUNK_KB) : total_kb) - w.kb_begin;
   return w;
 }
 
@@ -124,7 +129,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
                         const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
                         float *__restrict__ C, long long ldc, int M, int N, int K,
                         const float *__restrict__ bias, int accumulate, int tiles_n, int whole_tiles,
-                        int total_items, const float *__restrict__ scale_a,
+                        int parts, int total_items, const float *__restrict__ scale_a,
                         const float *__restrict__ scale_b, int *status) {
   using P = PairPlan<STAGES>;
   constexpr int MN_W = 64;  // halfs of one 128-byte column of an MN-major tile
@@ -178,7 +183,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
       unsigned it = 0;
       bool ok = true;
       for (int item = pair; item < total_items && ok; item += pairs) {
-        const PairItem w = pair_item<CHUNK_KB>(item, tiles_n, whole_tiles, total_kb);
+        const PairItem w = pair_item<CHUNK_KB>(item, tiles_n, whole_tiles, parts, total_kb);
         const int am0 = w.m0 + (int)rank * BM, bn0 = w.n0 + (int)rank * HALF_N;
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           const unsigned s = it % STAGES;
@@ -223,7 +228,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
       bool ok = true;
       unsigned it = 0, cc = 0;
       for (int item = pair; item < total_items && ok; item += pairs) {
-        const PairItem w = pair_item<CHUNK_KB>(item, tiles_n, whole_tiles, total_kb);
+        const PairItem w = pair_item<CHUNK_KB>(item, tiles_n, whole_tiles, parts, total_kb);
         int kb = 0;
         while (kb < w.num_kb && ok) {
           const unsigned buf = cc & 1, use = cc >> 1;
@@ -272,7 +277,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     bool ok = true;
     unsigned cc = 0;
     for (int item = pair; item < total_items && ok; item += pairs) {
-      const PairItem w = pair_item<CHUNK_KB>(item, tiles_n, whole_tiles, total_kb);
+      const PairItem w = pair_item<CHUNK_KB>(item, tiles_n, whole_tiles, parts, total_kb);
       const int num_chunks = (w.num_kb + CHUNK_KB - 1) / CHUNK_KB;
 #pragma unroll
       for (int j = 0; j < HALF; ++j) acc[j] = 0.f;
@@ -305,7 +310,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
           __syncwarp();
           const int col = col0 + lane;
           if (col < N) {
-            const float b = (bias && w.k_half == 0) ? __ldg(bias + col) : 0.f;
+            const float b = (bias && w.piece == 0) ? __ldg(bias + col) : 0.f;
             if (w.split) {
 #pragma unroll 4
               for (int r = 0; r < 32; ++r) {
@@ -392,23 +397,44 @@ dlb_status launch_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B,
     DLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::TOTAL));
     attr_set = true;
   }
-  // Pairs of SMs work through the 256 x 256 tiles in rounds; the last partial
-  // round is split along k exactly as in the one-CTA kernel.
+  // Pairs of SMs work through the 256 x 256 tiles in rounds.  The tiles of the
+  // last partial round are cut along k into pieces that add into a zeroed
+  // output when that shortens the round: with `rest` tiles on `lanes` pairs it
+  // then lasts ceil(rest * parts / lanes) / parts of a full round.  Two pieces
+  // add in either order to the same bits.  Three pieces measured slower than
+  // no cut (the atomic adds of 46 tiles x 3 cost more than the third of a
+  // round they save) and would not be reproducible, so MAX_PARTS is 2.
+  // SMs are left free only while an all-reduce is in flight on the second
+  // stream.
   const int tiles_n = ceil_div(N, PN), tiles = tiles_n * ceil_div(M, PM);
-  const int sms = max(2, ctx->sm_count - (ctx->world > 1 ? ctx->gemm_reserve_sms : 0));
+  const int sms = max(2, ctx->sm_count - (ctx->comm_pending ? ctx->gemm_reserve_sms : 0));
   const int lanes = sms / 2;
-  int split_tiles = 0;
+  const int total_kb = ceil_div(K, PBK);
   const int rest = tiles % lanes;
-  if (!ep.accumulate && rest > 0 && 2 * rest <= lanes && ceil_div(K, PBK) >= 8 * CHUNK_KB) split_tiles = rest;
+  int parts = 1;
+  if (!ep.accumulate && rest > 0) {
+    // Twelfths of a round; a cut must save at least a twelfth per extra piece.
+    int best = 12;
+    constexpr int MAX_PARTS = 2;
+    for (int p = 2; p <= MAX_PARTS; ++p) {
+      if (total_kb < p * 4 * CHUNK_KB) break;  // a piece runs at least four chunks
+      const int cost = ceil_div(rest * p, lanes) * 12 / p + (p - 1);
+      if (cost < best) {
+        best = cost;
+        parts = p;
+      }
+    }
+  }
+  const int split_tiles = parts > 1 ? rest : 0;
   const int whole_tiles = tiles - split_tiles;
   if (split_tiles) {
     const int first_row = (whole_tiles / tiles_n) * PM;
     DLB_CUDA(cudaMemset2DAsync(C + (long long)first_row * ldc, (size_t)ldc * sizeof(float), 0,
                                (size_t)N * sizeof(float), (size_t)(M - first_row), ctx->stream));
   }
-  const int items = whole_tiles + 2 * split_tiles;
+  const int items = whole_tiles + parts * split_tiles;
   kernel<<<2 * min(items, lanes), NUM_THREADS, P::TOTAL, ctx->stream>>>(
-      ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, items, A.scale,
+      ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, parts, items, A.scale,
       B.scale, ctx->d_status);
   DLB_LAUNCHED(ctx);
   return DLB_OK;

@@ -96,6 +96,8 @@ SIGNATURES = {
     "dlb_allreduce_f64": (_i, [_vp, _vp, _sz]),
     "dlb_allreduce_f32_overlapped": (_i, [_vp, _vp, _sz]),
     "dlb_comm_join": (_i, [_vp]),
+    "dlb_comm_peer_exchange": (_i, [_vp]),
+    "dlb_peer_exchange_emulated": (_i, [_vp, _i, _sz, _i, _vp, _vp, _i, C.c_uint]),
     "dlb_model_create": (_i, [C.POINTER(_vp), _vp]),
     "dlb_model_destroy": (_i, [_vp]),
     "dlb_model_compile": (_i, [_vp, _sz, _sz, _i, _vp, _vp]),
@@ -263,6 +265,20 @@ class Context:
     def comm_init(self, uid, rank, world):
         buf = (C.c_char * 128).from_buffer_copy(uid)
         check(self.L.dlb_comm_init(self.h, buf, rank, world), "dlb_comm_init")
+
+    def peer_exchange(self):
+        """True when the small fp64 sums cross NVLink through peer memory."""
+        return bool(self.L.dlb_comm_peer_exchange(self.h))
+
+    def peer_exchange_emulated(self, vectors, rounds=1, absent=-1, wait_ms=20000):
+        """The peer-memory exchange with the rows of `vectors` [world, n] as
+        emulated ranks on this device; returns what every rank holds after
+        `rounds` exchanges (round k on the vectors times k + 1)."""
+        v = np.ascontiguousarray(vectors, dtype=np.float64)
+        out = np.empty_like(v)
+        check(self.L.dlb_peer_exchange_emulated(self.h, v.shape[0], v.shape[1], rounds, _ptr(v), _ptr(out),
+                                                absent, wait_ms), "dlb_peer_exchange_emulated")
+        return out
 
     @property
     def world(self):

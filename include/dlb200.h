@@ -405,6 +405,28 @@ dlb_status dlb_allreduce_f64(dlb_ctx *ctx, double *buf, size_t n);
  * stream wait for all such transfers. */
 dlb_status dlb_allreduce_f32_overlapped(dlb_ctx *ctx, float *buf, size_t n);
 dlb_status dlb_comm_join(dlb_ctx *ctx);
+/* dlb_allreduce_f64 of up to 32768 doubles (the batch-renormalization sums of
+ * a layer: Forward_Pass__Batch_Renormalization__Training__OpenMP,
+ * fwp_mp.cpp L:4647-4663, and the backward sums of bwp_mp.cpp L:1520-1621)
+ * does not go through NCCL when the ranks are processes of one host on GPUs of
+ * their own: dlb_comm_init maps a buffer of every rank into every rank (CUDA
+ * IPC) and one kernel per rank stores its vector, every 8-byte word tagged
+ * with the exchange's sequence number, into all of them over NVLink, waits
+ * (bounded; DLB_ERR_TIMEOUT in the device status after 20 s) for the other
+ * ranks' words and adds the vectors in rank order, so that all ranks hold the
+ * same bits.  1 if the context uses it
+ * (DLB_PEER_EXCHANGE=0 in the environment of any rank turns it off for all). */
+int dlb_comm_peer_exchange(dlb_ctx *ctx);
+/* The same protocol with `world` (<= 8) emulated ranks as the rows of one
+ * cooperative grid on this device, for checking it where there is one GPU.
+ * in/out: host arrays [world][n], n <= 32768; `rounds` exchanges run back to
+ * back on the same buffers, round k on the vectors times k + 1, and `out` is
+ * what each rank holds after the last.  absent >= 0 names a rank that never
+ * delivers: the others give up after wait_ms and the call returns
+ * DLB_ERR_TIMEOUT, the device status is cleared and the context stays usable. */
+dlb_status dlb_peer_exchange_emulated(dlb_ctx *ctx, int world, size_t n, int rounds,
+                                      const double *in, double *out, int absent,
+                                      unsigned wait_ms);
 
 /* ------------------------------------------------------------------------ */
 /* Model: the reference's v1::Model construction and step entry points

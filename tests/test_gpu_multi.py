@@ -49,6 +49,9 @@ def worker(rank, world, tmp):
             raise SystemExit("rank 0 never published the communicator id")
         time.sleep(0.05)
     ctx.comm_init(open(id_path, "rb").read(), rank, world)
+    # Two processes on two GPUs of one host: the statistics cross NVLink through
+    # the peer-memory exchange unless the environment turned it off.
+    assert ctx.peer_exchange() == (os.environ.get("DLB_PEER_EXCHANGE", "1") != "0")
     cfg = _cfg()
     B = cfg["batch"]
     X, Y = configs.synthetic_batch(cfg)

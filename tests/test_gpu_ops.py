@@ -370,3 +370,34 @@ def test_bad_arguments_are_refused(gpu_ctx):
     assert L.dlb_loss_delta(ctx.h, 3, 11, x.ptr, x.ptr, x.ptr, x.ptr, None, 4, 4, 4, x.ptr) == 3
     assert b"invalid" in L.dlb_status_string(1)
     assert ctx.sync() == 0
+
+
+# ---- peer-memory exchange of the batch-renormalization sums -----------------
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("n", [1, 7, 256, 8192, 32768])
+def test_peer_exchange_emulated_ranks(gpu_ctx, world, n):
+    """Every emulated rank ends with the sum of all ranks' vectors, added in
+    rank order (so bit-identical on all ranks and to the same loop on the
+    host), over three exchanges back to back on the same buffers (both inbox
+    halves and the flag sequence are reused)."""
+    rng = np.random.default_rng(world * 100003 + n)
+    v = rng.standard_normal((world, n)) * np.exp(rng.uniform(-20, 20, (world, n)))
+    out = gpu_ctx.peer_exchange_emulated(v, rounds=3)
+    want = np.zeros(n)
+    for r in range(world):
+        want = want + v[r] * 3.0
+    for r in range(world):
+        assert np.array_equal(out[r], want), r
+    assert gpu_ctx.sync() == 0
+
+
+def test_peer_exchange_gives_up_on_an_absent_rank(gpu_ctx):
+    """A rank that never delivers: the others' bounded waits run out, the call
+    reports the timeout, and the context works afterwards."""
+    v = np.arange(4 * 600, dtype=np.float64).reshape(4, 600)
+    with pytest.raises(dlb200.DlbError, match="gave up waiting"):
+        gpu_ctx.peer_exchange_emulated(v, absent=2, wait_ms=200)
+    assert gpu_ctx.sync() == 0
+    out = gpu_ctx.peer_exchange_emulated(v)
+    assert np.array_equal(out[3], v.sum(axis=0))
