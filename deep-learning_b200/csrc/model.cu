@@ -95,6 +95,9 @@ struct dlb_model {
   // the reorder to [T, rows, n].
   float *input_rows = nullptr, *target_rows = nullptr;
   float *wd_mask = nullptr;  // [P]: 1 where weight decay applies
+  // Model::use_clip_gradient / clip_gradient (model.hpp defaults: off, 1).
+  bool use_clip_gradient = false;
+  float clip_gradient = 1.f;
   // Evaluation (Driver::evalt): propagation state, accuracy function and its
   // counter; r = 1 and d = 0 for the normalization by running averages.
   int propagation = DLB_PROPAGATION_TRAINING;
@@ -131,6 +134,10 @@ namespace {
 
 size_t n_in(const dlb_model *m) { return m->layers.front().units; }
 size_t n_out(const dlb_model *m) { return m->layers.back().units; }
+
+// mag of the IndRNN bounds: clip(clip_gradient, 2, 10)
+// (v1/ops/constraints/constraint.cpp L:66, v1/learner/model.cpp L:5303, L:5336).
+float indrnn_magnitude(const dlb_model *m) { return fminf(fmaxf(m->clip_gradient, 2.f), 10.f); }
 
 bool is_indrnn(const LayerRT &l) { return l.type == DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT; }
 
@@ -986,9 +993,9 @@ dlb_status dlb_model_initialize_weights_with_glorot_uniform(dlb_model *m) {
     dist.param(std::uniform_real_distribution<float>::param_type(-bound, bound));
     for (size_t k = l.first_conn; k < l.last_conn; ++k) w[k] = dist(m->weight_gen);
     if (is_indrnn(l)) {
-      // The recurrent weights are drawn again from U(0, mag^(1/T)), mag = 2
+      // The recurrent weights are drawn again from U(0, mag^(1/T))
       // (Model::indrec_initialize_uniform, v1/learner/model.cpp L:5289-5333).
-      const float top = powf(2.f, 1.f / (float)m->seq_w);
+      const float top = powf(indrnn_magnitude(m), 1.f / (float)m->seq_w);
       dist.param(std::uniform_real_distribution<float>::param_type(-0.f, top));
       for (size_t k = 0; k < l.units; ++k) w[l.first_recurrent + k] = dist(m->weight_gen);
     }
@@ -1001,8 +1008,9 @@ dlb_status dlb_model_initialize_weights_with_glorot_uniform(dlb_model *m) {
       const LayerRT &l = m->layers[i];
       if (!is_indrnn(l)) continue;
       const float T = (float)m->seq_w;
-      dist.param(std::uniform_real_distribution<float>::param_type(powf(1.f / 2.f, 1.f / T),
-                                                                   powf(2.f, 1.f / T)));
+      const float mag = indrnn_magnitude(m);
+      dist.param(std::uniform_real_distribution<float>::param_type(powf(1.f / mag, 1.f / T),
+                                                                   powf(mag, 1.f / T)));
       for (size_t k = 0; k < l.units; ++k) w[l.first_recurrent + k] = dist(m->weight_gen);
       break;
     }
@@ -1455,6 +1463,8 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
   const float hyper[8] = {m->hp.adam_learning_rate, m->hp.adam_beta1, m->hp.adam_beta2,
                           m->hp.adam_epsilon, m->hp.adam_gamma, m->hp.learning_rate_final,
                           m->hp.learning_gamma, m->hp.use_adam_bias_correction ? 1.f : 0.f};
+  if (m->use_clip_gradient)
+    DLB_TRY(dlb_clip_gradient(m->ctx, m->grads, m->total_parameters, m->clip_gradient));
   dlb_optimizer_scalars k;
   DLB_TRY(dlb_optimizer_prepare(m->optimizer, hyper, &m->hp.optimizer_time_step,
                                 &m->hp.adam_previous_beta2, &k));
@@ -1465,12 +1475,20 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
   // clip(clip_gradient, 2, 10) = 2 with the reference's default clip_gradient of
   // 1; every activation of the supported set is in a class that takes this
   // bound (v1/ops/constraints/constraint.cpp L:64-95, L:245-289).
-  const float bound = powf(2.f, 1.f / (float)m->seq_w);
+  const float bound = powf(indrnn_magnitude(m), 1.f / (float)m->seq_w);
   for (LayerRT &l : m->layers)
     if (is_indrnn(l))
       DLB_TRY(dlb_indrnn_clamp(m->ctx, m->params + l.first_recurrent, (int)l.units, -bound, bound));
   m->grads_clean = true;  // the update kernel clears every gradient it consumes
   m->params_lo_valid = false;
+  return DLB_OK;
+}
+
+// ref: Model::set_clip_gradient (v1/ops/constraints/clip_gradient.cpp L:30-73).
+dlb_status dlb_model_set_clip_gradient(dlb_model *m, int use, float value) {
+  DLB_REQUIRE(m && value > 0.f, "set_clip_gradient: the norm must be positive");
+  m->use_clip_gradient = use != 0;
+  m->clip_gradient = value;
   return DLB_OK;
 }
 

@@ -101,6 +101,64 @@ static dlb_status launch_rule(dlb_ctx *ctx, const dlb_optimizer_scalars &k, floa
   return DLB_OK;
 }
 
+// ---- gradient clipping by the Euclidean norm -------------------------------
+// euclidean_norm_mp (v1/ops/constraints/euclidean.cpp L:48-71): the norm of the
+// whole vector, and g *= max / norm when norm >= max.  Three launches: block
+// partials of the sum of squares (fp64), one block that folds them in a fixed
+// order into the factor, and the scaling pass, which returns at once when the
+// factor is 1.
+
+constexpr int CLIP_BLOCKS = 1024;
+
+__global__ void __launch_bounds__(256) sumsq_partials_kernel(const float *__restrict__ g, size_t n, double *partials) {
+  double acc = 0.0;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t n4 = (reinterpret_cast<uintptr_t>(g) & 15) == 0 ? n / 4 : 0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 v = __ldg(reinterpret_cast<const float4 *>(g) + i);
+    acc += (double)v.x * v.x + (double)v.y * v.y + (double)v.z * v.z + (double)v.w * v.w;
+  }
+  for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) acc += (double)g[i] * g[i];
+  __shared__ double warp_sums[8];
+  for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (threadIdx.x % 32 == 0) warp_sums[threadIdx.x / 32] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double s = 0.0;
+    for (int w = 0; w < 8; ++w) s += warp_sums[w];
+    partials[blockIdx.x] = s;
+  }
+}
+
+__global__ void __launch_bounds__(256) clip_factor_kernel(const double *partials, int blocks, float max_norm, float *factor) {
+  __shared__ double part[256];
+  double s = 0.0;
+  for (int i = threadIdx.x; i < blocks; i += 256) s += partials[i];
+  part[threadIdx.x] = s;
+  __syncthreads();
+  for (int o = 128; o; o >>= 1) {
+    if ((int)threadIdx.x < o) part[threadIdx.x] += part[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const float norm = sqrtf((float)part[0]);
+    *factor = norm >= max_norm ? max_norm / norm : 1.f;
+  }
+}
+
+__global__ void __launch_bounds__(256) scale_by_factor_kernel(float *__restrict__ g, size_t n, const float *factor) {
+  const float f = *factor;
+  if (f == 1.f) return;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t n4 = (reinterpret_cast<uintptr_t>(g) & 15) == 0 ? n / 4 : 0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    float4 v = reinterpret_cast<float4 *>(g)[i];
+    v.x *= f, v.y *= f, v.z *= f, v.w *= f;
+    reinterpret_cast<float4 *>(g)[i] = v;
+  }
+  for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) g[i] *= f;
+}
+
 }  // namespace dlb
 
 using namespace dlb;
@@ -136,6 +194,23 @@ dlb_status dlb_optimizer_step(dlb_ctx *ctx, int rule, const dlb_optimizer_scalar
       set_error("dlb_optimizer_step: optimizer %d is outside the supported path", rule);
       return DLB_ERR_UNSUPPORTED;
   }
+}
+
+dlb_status dlb_clip_gradient(dlb_ctx *ctx, float *g, size_t n, float max_norm) {
+  DLB_REQUIRE(ctx && g && max_norm > 0.f, "dlb_clip_gradient");
+  if (n == 0) return DLB_OK;
+  void *scr = nullptr;
+  DLB_TRY(scratch(ctx, (CLIP_BLOCKS + 1) * sizeof(double), &scr));
+  double *partials = static_cast<double *>(scr);
+  float *factor = reinterpret_cast<float *>(partials + CLIP_BLOCKS);
+  const int blocks = (int)min((size_t)CLIP_BLOCKS, (n / 4 + 255) / 256 + 1);
+  sumsq_partials_kernel<<<blocks, 256, 0, ctx->stream>>>(g, n, partials);
+  DLB_LAUNCHED(ctx);
+  clip_factor_kernel<<<1, 256, 0, ctx->stream>>>(partials, blocks, max_norm, factor);
+  DLB_LAUNCHED(ctx);
+  scale_by_factor_kernel<<<blocks, 256, 0, ctx->stream>>>(g, n, factor);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
 }
 
 dlb_status dlb_optimizer_prepare(int rule, const float *hyper, float *time_step,

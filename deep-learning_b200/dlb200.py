@@ -87,6 +87,7 @@ SIGNATURES = {
     "dlb_indrnn_clamp": (_i, [_vp, _vp, _i, _f, _f]),
     "dlb_loss_delta":(_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "dlb_optimizer_step": (_i, [_vp, _i, C.POINTER(OptimizerScalars), _vp, _vp, _vp, _vp, _vp, _vp, _sz]),
+    "dlb_clip_gradient": (_i, [_vp, _vp, _sz, _f]),
     "dlb_optimizer_prepare": (_i, [_i, C.POINTER(_f), C.POINTER(_f), C.POINTER(_f), C.POINTER(OptimizerScalars)]),
     "dlb_comm_unique_id": (_i, [C.c_char * 128]),
     "dlb_comm_init": (_i, [_vp, C.c_char * 128, _i, _i]),
@@ -144,6 +145,7 @@ SIGNATURES = {
     "dlb_model_compute_error_device": (_i, [_vp, _sz, _vp]),
     "dlb_model_train_step": (_i, [_vp, _sz, _vp, _vp, C.POINTER(_d)]),
     "dlb_model_train_step_device": (_i, [_vp, _sz, _vp, _vp]),
+    "dlb_model_set_clip_gradient": (_i, [_vp, _i, _f]),
     "dlb_model_stage_batch": (_i, [_vp, _sz, _vp, _vp]),
     "dlb_model_train_step_staged": (_i, [_vp, C.POINTER(_d)]),
     "dlb_model_get_layer_outputs": (_i, [_vp, _sz, _sz, _vp]),
@@ -536,6 +538,9 @@ class Model:
         check(self.L.dlb_model_train_step(self.h, batch, _ptr(X), _ptr(Y), C.byref(loss) if want_loss else None),
               "train_step")
         return loss.value
+
+    def set_clip_gradient(self, use, value):
+        check(self.L.dlb_model_set_clip_gradient(self.h, int(bool(use)), float(value)), "set_clip_gradient")
 
     def stage_batch(self, batch, X, Y):
         """Starts the host-to-device copy of one batch; X and Y are contiguous

@@ -382,6 +382,13 @@ dlb_status dlb_optimizer_step(dlb_ctx *ctx, int rule, const dlb_optimizer_scalar
                               float *g, float *first, float *second, float *second_hat,
                               const float *wd_mask, size_t n);
 
+/* Gradient clipping by the Euclidean norm of g[0..n): g *= max_norm / |g| when
+ * |g| >= max_norm.  ref: euclidean_norm_mp (v1/ops/constraints/euclidean.cpp
+ * L:48-71) as Model::Clip_Gradient__OpenMP calls it between the merge and the
+ * optimizer (v1/learner/model.cpp L:4742-4743).  The sum of squares is formed
+ * in fp64 (the reference adds floats in thread order). */
+dlb_status dlb_clip_gradient(dlb_ctx *ctx, float *g, size_t n, float max_norm);
+
 /* Host-side scalars exactly as the reference derives them from its float time
  * step (increments *time_step first).  hyper = {lr, beta1, beta2, epsilon,
  * gamma(NosAdam), final_lr, bound_gamma, bias_correction(0/1)};
@@ -536,6 +543,11 @@ dlb_status dlb_model_train_step_device(dlb_model *m, size_t rows, const float *X
  * batch i hides the copy under the kernels.  This is the mini-batch loop of
  * MiniBatch::train_mp (v1/data/dataset/minibatch.cpp L:286-323): train on the
  * batch, read its loss, update the weights, move to the next batch. */
+/* Model::set_clip_gradient, both overloads (v1/ops/constraints/clip_gradient.cpp
+ * L:30-73): whether update_weights clips, and the norm; the norm also sets the
+ * default bound of IndRNN recurrent weights, clip(value, 2, 10)^(1/seq_w)
+ * (v1/ops/constraints/constraint.cpp L:64-95). */
+dlb_status dlb_model_set_clip_gradient(dlb_model *m, int use, float value);
 dlb_status dlb_model_stage_batch(dlb_model *m, size_t rows, const float *X_host,
                                  const float *Y_host);
 dlb_status dlb_model_train_step_staged(dlb_model *m, double *loss);

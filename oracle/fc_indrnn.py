@@ -209,10 +209,14 @@ class IndRnnOracleModel(OracleModel):
         return total / (rows * self.layers[-1]["units"])
 
     def update_weights(self, batch, training_size):
+        self._clip_gradient()
         k = optimizer_scalars(self.optimizer, self.hp, self.opt_state)
         optimizer_update(self.optimizer, k, self.params, self.grads, self.m1, self.m2, self.m2hat,
                          *self._decay(batch, training_size))
-        bound = f32(np.power(f32(2), f32(1) / f32(self.T), dtype=f32))
+        # mag = clip(clip_gradient, 2, 10): Compute__Regularization__Constraint_
+        # Recurrent_Weight__Default, v1/ops/constraints/constraint.cpp L:64-95.
+        mag = f32(min(max(self.hp.get("clip_gradient", 1.0), 2.0), 10.0))
+        bound = f32(np.power(mag, f32(1) / f32(self.T), dtype=f32))
         for l in self.layers[1:]:
             if l["type"] == LAYER_INDRNN:
                 s = slice(l["first_recurrent"], l["first_recurrent"] + l["units"])

@@ -53,6 +53,7 @@ def lib():
         "ref_set_max_batch_size": (i, [vp, sz]),
         "ref_set_mp": (i, [vp, i]),
         "ref_set_weight_decay": (i, [vp, C.c_double]),
+        "ref_set_clip_gradient": (i, [vp, i, C.c_double]),
         "ref_set_propagation": (i, [vp, i]),
         "ref_set_accu_fn": (i, [vp, i]),
         "ref_set_accu_var": (i, [vp, C.c_double]),
@@ -189,6 +190,9 @@ class RefModel:
 
     def set_weight_decay(self, value):
         _ck(self.L.ref_set_weight_decay(self.h, float(value)), "set_weight_decay")
+
+    def set_clip_gradient(self, use, value):
+        _ck(self.L.ref_set_clip_gradient(self.h, int(bool(use)), float(value)), "set_clip_gradient")
 
     def seed_weights(self, seed):
         _ck(self.L.ref_seed_weights(self.h, seed), "seed")

@@ -73,6 +73,29 @@ def test_indrnn_model_vs_restatement_tensor_core_shape(gpu_ctx, cfg):
     assert util.rel_l2(got["losses"], want["losses"]) <= 1e-4
 
 
+def test_clip_gradient_sets_the_recurrent_bound(gpu_ctx):
+    """Recurrent weights come back into +-clip(clip_gradient, 2, 10)^(1/T) after
+    the update, with clipping on (norm 5: the gradient is scaled as well) and
+    off (norm 5 only widens the bound)."""
+    cfg = configs.indrnn_stack(n_in=64, hidden=128, depth=2, n_out=32, seq_w=4, batch=32)
+    X, Y = configs.synthetic_batch(cfg)
+    p0 = _kink_free(cfg, X)
+    for _, s in configs.recurrent_slices(cfg):
+        p0[s] = np.linspace(-2.5, 2.5, s.stop - s.start, dtype=np.float32)
+    for use in (False, True):
+        ora = util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0)
+        ora.set_clip_gradient(use, 5.0)
+        want = util.trace(ora, cfg, 1, X, Y)
+        mod = util.build(dlb200.Model(gpu_ctx), cfg, params=p0)
+        mod.set_clip_gradient(use, 5.0)
+        got = util.trace(mod, cfg, 1, X, Y)
+        assert gpu_ctx.sync() == 0
+        bound = np.float32(5.0) ** np.float32(0.25)
+        for _, s in configs.recurrent_slices(cfg):
+            assert np.isclose(np.abs(got["params1"][s]).max(), bound, rtol=1e-6)
+        assert util.rel_l2(got["params1"], want["params1"]) <= 1e-5
+
+
 def test_glorot_and_recurrent_initialisation_match_the_fixture_layout(gpu_ctx):
     cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=2, n_out=5, seq_w=4, batch=3)
     m = util.build(dlb200.Model(gpu_ctx), cfg, seed=0)

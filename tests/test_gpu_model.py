@@ -190,6 +190,52 @@ def test_weight_decay(gpu_ctx, optimizer):
         mod.set_weight_decay(1.5)
 
 
+def test_gradient_clipping(gpu_ctx):
+    """Clipping by the norm of the whole gradient vector before the optimizer,
+    against the CPU restatement (itself pinned to the compiled reference); a
+    norm above the gradient's leaves the step bit for bit as it was."""
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96, optimizer=OPTIMIZER.ADAM)
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    p0, seed = util.kink_free_parameters(cfg, fc_step.OracleModel, X, masks, scale=1.0 / np.sqrt(128))
+    plain = util.trace(gpu_model(gpu_ctx, cfg, p0), cfg, 1, X, Y, masks)
+    norm = float(np.sqrt(np.sum(plain["grads"].astype(np.float64) ** 2)))
+    ora = util.build(fc_step.OracleModel(), cfg, params=p0)
+    ora.set_clip_gradient(True, norm / 50)
+    want = util.trace(ora, cfg, 2, X, Y, masks)
+    mod = gpu_model(gpu_ctx, cfg, p0)
+    mod.set_clip_gradient(True, norm / 50)
+    got = util.trace(mod, cfg, 2, X, Y, masks)
+    assert gpu_ctx.sync() == 0
+    assert util.rel_l2(got["params1"], want["params1"]) <= TOL_1
+    assert util.rel_l2(got["params_last"], want["params_last"]) <= TOL_N
+    loose = gpu_model(gpu_ctx, cfg, p0)
+    loose.set_clip_gradient(True, norm * 1e3)
+    assert np.array_equal(util.trace(loose, cfg, 1, X, Y, masks)["params1"], plain["params1"])
+    with pytest.raises(dlb200.DlbError):
+        mod.set_clip_gradient(True, 0.0)
+
+
+@pytest.mark.parametrize("n", [1, 5, 4096, 1000003])
+def test_clip_gradient_kernel(gpu_ctx, n):
+    """g *= max / |g| when |g| >= max, untouched otherwise; odd sizes and a
+    start that is not 16-byte aligned."""
+    rng = np.random.default_rng(n)
+    g = rng.standard_normal(n + 1).astype(np.float32)
+    norm = float(np.sqrt(np.sum(g[1:].astype(np.float64) ** 2)))
+    for limit, clipped in ((norm * 0.25, True), (norm * 4, False)):
+        d = gpu_ctx.array(g)
+        dlb200.check(gpu_ctx.L.dlb_clip_gradient(gpu_ctx.h, d.offset(1), n, limit), "clip")
+        out = d.get()
+        assert gpu_ctx.sync() == 0
+        assert out[0] == g[0]
+        if clipped:
+            f = np.float32(np.float32(limit) / np.float32(norm))
+            assert util.rel_l2(out[1:], g[1:] * f) <= 1e-6
+        else:
+            assert np.array_equal(out[1:], g[1:])
+
+
 def test_uout_dropout(gpu_ctx):
     """UOut inside the Model: the draws are an input of the step."""
     cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96, dropout=LAYER_DROPOUT.UOUT, keep=0.25)

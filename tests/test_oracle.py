@@ -100,6 +100,33 @@ def test_weight_decay_matches_compiled_reference(optimizer):
 
 
 @pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+def test_gradient_clipping_matches_compiled_reference():
+    """Clipping by the Euclidean norm of the whole gradient vector between the
+    merge and the optimizer (v1/ops/constraints/euclidean.cpp L:48-71,
+    v1/learner/model.cpp L:4742-4743).  Adam-family steps barely depend on
+    the gradient's scale, so the clipped gradient itself is compared as well:
+    the factor is max / norm of the gradients of the unclipped first step."""
+    cfg = configs.deep_brn_mlp(20, 32, 2, 12, 24)
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    p0 = ref.get_array("parameters")
+    plain = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, steps=4)
+    norm = float(np.sqrt(np.sum(plain["grads"].astype(np.float64) ** 2)))
+    limit = norm / 50.0
+    ref.set_clip_gradient(True, limit)
+    want = util.trace(ref, cfg, steps=4)
+    ora = util.build(fc_step.OracleModel(), cfg, params=p0)
+    ora.set_clip_gradient(True, limit)
+    got = util.trace(ora, cfg, steps=4)
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_L2, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+    assert util.rel_l2(plain["params_last"], want["params_last"]) > 1e-4   # the clipping is not a no-op
+    # A norm above the gradient's leaves the step as it was.
+    loose = util.build(fc_step.OracleModel(), cfg, params=p0)
+    loose.set_clip_gradient(True, norm * 1e3)
+    assert np.array_equal(util.trace(loose, cfg, steps=1)["params1"], plain["params1"])
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
 def test_uout_matches_compiled_reference():
     """UOut, A += A * U(-beta, beta) per element (v1/learner/fwp_mp.cpp
     L:4959-4985): the restatement receives the draws the serial reference makes

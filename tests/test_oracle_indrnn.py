@@ -72,6 +72,29 @@ def test_recurrent_weights_are_clamped_like_the_reference():
     _check(got, want)
 
 
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+def test_clip_gradient_widens_the_recurrent_bound_like_the_reference():
+    """The default bound is clip(clip_gradient, 2, 10)^(1/T)
+    (v1/ops/constraints/constraint.cpp L:64-95); setting the norm re-derives it
+    (v1/ops/constraints/clip_gradient.cpp L:34-73), also while clipping is off."""
+    cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=2, n_out=5, seq_w=4, batch=5)
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    ref.set_clip_gradient(False, 5.0)
+    p0 = ref.get_array("parameters")
+    for _, s in configs.recurrent_slices(cfg):
+        p0[s] = np.linspace(-2.5, 2.5, s.stop - s.start, dtype=np.float32)
+    ref.set_array("parameters", p0)
+    want = util.trace(ref, cfg, steps=2)
+    ora = util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0)
+    ora.set_clip_gradient(False, 5.0)
+    got = util.trace(ora, cfg, steps=2)
+    bound = np.float32(5.0) ** np.float32(0.25)
+    for _, s in configs.recurrent_slices(cfg):
+        assert np.isclose(np.abs(want["params1"][s]).max(), bound, rtol=1e-6)
+        assert np.isclose(np.abs(got["params1"][s]).max(), bound, rtol=1e-6)
+    _check(got, want)
+
+
 def test_parameter_layout():
     """An IndRNN layer's u follows its W; gamma starts at 0.1 for IndRNN layers."""
     cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=2, n_out=5, seq_w=4, batch=3)
