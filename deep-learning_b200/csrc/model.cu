@@ -475,9 +475,28 @@ dlb_status refresh_weight_residuals(dlb_model *m) {
   return DLB_OK;
 }
 
+dlb_status ensure_constants(dlb_model *m, size_t units);
+
+// Normalization by the running averages, the inference form of batch
+// normalization and renormalization alike
+// (Forward_Pass__Batch_Normalization__Inference__OpenMP, fwp_mp.cpp
+// L:4461-4491): gamma (z - running mean) / running sigma + beta, i.e. the
+// training formula with r = 1 and d = 0.  Covers all time steps of the layer.
+dlb_status inference_arrays(dlb_model *m, LayerRT &l, dlb_brn_unit_arrays *u) {
+  DLB_TRY(ensure_constants(m, m->seq_w * l.norm_units));
+  *u = unit_arrays(m, l, 0);
+  u->mean = u->mean_average;
+  u->sigma = u->sigma_average;
+  u->r = m->ones;
+  u->d = m->zeros;
+  return DLB_OK;
+}
+
 // Batch-renormalization statistics of layer l over `in` [B, l.norm_units]:
-// sums, exchange across ranks, averages and corrections.
+// sums, exchange across ranks, averages and corrections; the running averages
+// alone in an inference pass.
 dlb_status norm_statistics(dlb_model *m, LayerRT &l, const float *in, int B, dlb_brn_unit_arrays *u) {
+  if (m->propagation == DLB_PROPAGATION_INFERENCE) return inference_arrays(m, l, u);
   const int Bg = (int)(m->global_rows ? m->global_rows : (size_t)B);
   const int n = (int)l.norm_units;
   *u = unit_arrays(m, l, 0);
@@ -535,6 +554,7 @@ dlb_status uout_ready(dlb_model *m, const LayerRT &l, size_t index, int B) {
 // then the residual layer's normalization, ShakeDrop and the shortcut sum.
 dlb_status forward_residual(dlb_model *m, size_t i, const float *X, const float *X_lo, int B) {
   LayerRT &res = m->layers[i];
+  const bool inference = m->propagation == DLB_PROPAGATION_INFERENCE;
   const float *in = X, *in_lo = X_lo;
   const float *prev_sums = nullptr;
   for (size_t j = 1; j <= res.depth; ++j) {
@@ -543,11 +563,19 @@ dlb_status forward_residual(dlb_model *m, size_t i, const float *X, const float 
     if (!b.block_input) {
       dlb_brn_unit_arrays u;
       if (norm) DLB_TRY(norm_statistics(m, b, prev_sums, B, &u));
-      DLB_TRY(uout_ready(m, b, i + j, B));
-      dlb_dropout_desc dp{b.dropout, b.dropout_value, b.mask, b.uout};
-      DLB_TRY(dlb_activation_forward(m->ctx, prev_sums, norm ? &u : nullptr, b.af,
-                                     b.dropout != DLB_DROPOUT_NONE ? &dp : nullptr, b.IN, b.IN_lo, B,
-                                     (int)b.fan_in));
+      if (inference) {
+        // Plain Bernoulli dropout scales by the keep probability (fwp_mp.cpp L:4870-4892).
+        dlb_dropout_desc dp{DROPOUT_INFERENCE_SCALE, b.dropout_value, nullptr, nullptr};
+        DLB_TRY(dlb_activation_forward(m->ctx, prev_sums, norm ? &u : nullptr, b.af,
+                                       b.dropout == DLB_DROPOUT_BERNOULLI ? &dp : nullptr, b.IN, b.IN_lo, B,
+                                       (int)b.fan_in));
+      } else {
+        DLB_TRY(uout_ready(m, b, i + j, B));
+        dlb_dropout_desc dp{b.dropout, b.dropout_value, b.mask, b.uout};
+        DLB_TRY(dlb_activation_forward(m->ctx, prev_sums, norm ? &u : nullptr, b.af,
+                                       b.dropout != DLB_DROPOUT_NONE ? &dp : nullptr, b.IN, b.IN_lo, B,
+                                       (int)b.fan_in));
+      }
       in = b.IN;
       in_lo = b.IN_lo;
     }
@@ -558,16 +586,21 @@ dlb_status forward_residual(dlb_model *m, size_t i, const float *X, const float 
   }
   LayerRT &last = m->layers[i + res.depth];
   float *block = last.A;
-  if (res.norm != DLB_NORM_NONE) {
+  // At inference the block output of a ShakeDrop layer is scaled by 1 - p, p the
+  // layer's dropout value (fwp_mp.cpp L:3876-3897), in the same pass as the
+  // layer's own normalization where it has one.
+  dlb_dropout_desc keep{DROPOUT_INFERENCE_SCALE, 1.f - res.dropout_value, nullptr, nullptr};
+  const bool scale = inference && res.dropout == DLB_DROPOUT_SHAKEDROP;
+  if (res.norm != DLB_NORM_NONE || scale) {
     // The residual layer's own normalization writes to its error buffer's
     // sibling: reuse last.delta as the normalised block output until backward.
     dlb_brn_unit_arrays u;
-    DLB_TRY(norm_statistics(m, res, last.A, B, &u));
-    DLB_TRY(dlb_activation_forward(m->ctx, last.A, &u, DLB_AF_LINEAR, nullptr, last.delta, nullptr, B,
-                                   (int)res.units));
+    if (res.norm != DLB_NORM_NONE) DLB_TRY(norm_statistics(m, res, last.A, B, &u));
+    DLB_TRY(dlb_activation_forward(m->ctx, last.A, res.norm != DLB_NORM_NONE ? &u : nullptr, DLB_AF_LINEAR,
+                                   scale ? &keep : nullptr, last.delta, nullptr, B, (int)res.units));
     block = last.delta;
   }
-  const bool shake = res.dropout == DLB_DROPOUT_SHAKEDROP;
+  const bool shake = !inference && res.dropout == DLB_DROPOUT_SHAKEDROP;
   if (shake && (!res.sd_mask || res.sd_rows < (size_t)B)) {
     set_error("model: residual layer %zu uses ShakeDrop but no noise was set for %d rows "
               "(dlb_model_set_shakedrop_noise)", i, B);
@@ -599,7 +632,9 @@ dlb_status forward_layers_time(dlb_model *m, size_t rows) {
       DLB_TRY(dlb_softmax_forward(m->ctx, l.Z, l.A, TB, H));
     } else if (norm || is_indrnn(l)) {
       dlb_brn_unit_arrays u{};
-      if (norm) {
+      if (norm && m->propagation == DLB_PROPAGATION_INFERENCE) {
+        DLB_TRY(inference_arrays(m, l, &u));  // every time step has its own running averages
+      } else if (norm) {
         u = unit_arrays(m, l, 0);
         DLB_TRY(dlb_brn_time_forward_sums(m->ctx, l.Z, T, B, H, l.fwd_sums));
         DLB_TRY(dlb_allreduce_f64(m->ctx, l.fwd_sums, 2 * (size_t)T * H));
@@ -623,14 +658,6 @@ dlb_status forward_layers_time(dlb_model *m, size_t rows) {
 
 dlb_status forward_layers(dlb_model *m, size_t rows) {
   const bool inference = m->propagation == DLB_PROPAGATION_INFERENCE;
-  if (inference) {
-    for (const LayerRT &l : m->layers)
-      if (time_stepped(m) || l.type != DLB_LAYER_FULLY_CONNECTED || l.group != 0) {
-        set_error("model: the inference pass covers plain stacks of fully connected layers; residual "
-                  "blocks and time-stepped models are outside the supported path");
-        return DLB_ERR_UNSUPPORTED;
-      }
-  }
   if (time_stepped(m)) return forward_layers_time(m, rows);
   DLB_TRY(refresh_weight_residuals(m));
   const int B = (int)rows;
@@ -652,18 +679,7 @@ dlb_status forward_layers(dlb_model *m, size_t rows) {
     DLB_TRY(dlb_fc_forward(m->ctx, X, X_lo, m->params + l.first_conn, m->params_lo + l.first_conn,
                            bias, l.Z, B, I, H));
     dlb_brn_unit_arrays u;
-    if (norm && inference) {
-      // Forward_Pass__Batch_Normalization__Inference__OpenMP (fwp_mp.cpp L:4461-4491),
-      // also for batch renormalization: gamma (z - running mean) / running sigma + beta.
-      DLB_TRY(ensure_constants(m, l.norm_units));
-      u = unit_arrays(m, l, 0);
-      u.mean = u.mean_average;
-      u.sigma = u.sigma_average;
-      u.r = m->ones;
-      u.d = m->zeros;
-    } else if (norm) {
-      DLB_TRY(norm_statistics(m, l, l.Z, B, &u));
-    }
+    if (norm) DLB_TRY(norm_statistics(m, l, l.Z, B, &u));
     if (l.af == DLB_AF_SOFTMAX) {
       DLB_TRY(dlb_softmax_forward(m->ctx, l.Z, l.A, B, H));
     } else if (inference) {
@@ -1527,11 +1543,19 @@ dlb_status dlb_model_set_accu_var(dlb_model *m, float v) {
 // ref: Model::compute_loss (v1/learner/compute_loss.cpp L:140-161).
 dlb_status dlb_model_compute_loss_device(dlb_model *m, size_t rows, const float *Y_dev) {
   DLB_REQUIRE(m && Y_dev && rows > 0 && rows <= m->alloc_rows, "compute_loss_device");
-  if (time_stepped(m)) {
-    set_error("compute_loss: time-stepped models are outside the supported path of the evaluation pass");
-    return DLB_ERR_UNSUPPORTED;
-  }
   LayerRT &o = m->layers.back();
+  if (time_stepped(m)) {
+    // Time steps t >= n_time_delay of every row (compute_loss_rec_mp,
+    // v1/learner/compute_loss_mp.cpp L:115-205).
+    DLB_REQUIRE(Y_dev != m->target, "compute_loss_device: target aliases the model's own buffer");
+    const size_t T = m->seq_w, d = m->n_time_delay, W = o.units;
+    DLB_TRY(dlb_time_major(m->ctx, Y_dev, m->target, nullptr, (int)rows, (int)T, (int)W));
+    const size_t skip = d * rows * W;
+    DLB_TRY(dlb_loss_eval(m->ctx, m->loss, m->accu_fn, m->accu_var, o.A + skip, m->target + skip,
+                          (int)((T - d) * rows), (int)W, m->loss_sum, m->accu_sum));
+    m->loss_rows += rows * (T - d);
+    return DLB_OK;
+  }
   DLB_TRY(dlb_loss_eval(m->ctx, m->loss, m->accu_fn, m->accu_var, o.A, Y_dev, (int)rows, (int)o.units,
                         m->loss_sum, m->accu_sum));
   m->loss_rows += rows;
@@ -1539,8 +1563,9 @@ dlb_status dlb_model_compute_loss_device(dlb_model *m, size_t rows, const float 
 }
 dlb_status dlb_model_compute_loss(dlb_model *m, size_t rows, const float *const *Ym) {
   DLB_REQUIRE(m && Ym && rows > 0 && rows <= m->alloc_rows, "compute_loss");
-  DLB_TRY(stage_rows(m, &m->stage_y, &m->stage_y_elems, rows, m->seq_w * n_out(m), Ym, m->target));
-  return dlb_model_compute_loss_device(m, rows, m->target);
+  float *dst = time_stepped(m) ? m->target_rows : m->target;
+  DLB_TRY(stage_rows(m, &m->stage_y, &m->stage_y_elems, rows, m->seq_w * n_out(m), Ym, dst));
+  return dlb_model_compute_loss_device(m, rows, dst);
 }
 
 // Percent of trials since reset_loss, over every rank's rows

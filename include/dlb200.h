@@ -508,8 +508,10 @@ dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows);
 dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows);
 /* Evaluation, as Driver::evalt (drivers/driver.cpp L:60-105): set the
  * propagation state to INFERENCE, run forward passes (normalization by the
- * running averages, fwp_mp.cpp L:4461-4491; plain Bernoulli dropout scales by
- * its keep probability, L:4870-4892), and after each one dlb_model_compute_loss
+ * running averages, fwp_mp.cpp L:4461-4491, every time step by its own in a
+ * time-stepped model; plain Bernoulli dropout scales by its keep probability,
+ * L:4870-4892; the block output of a ShakeDrop layer by 1 - p, L:3876-3897),
+ * and after each one dlb_model_compute_loss
  * (Model::compute_loss, v1/learner/compute_loss.cpp L:140-161) accumulates the
  * loss and the accuracy counter without forming an error.  dlb_model_get_loss
  * and dlb_model_get_accuracy (percent, Model::get_accu) read them. */

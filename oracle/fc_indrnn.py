@@ -102,6 +102,12 @@ class IndRnnOracleModel(OracleModel):
         key = {"r_correction": "r", "d_correction": "d"}.get(name, name)
         return np.concatenate([st[key] for st in l["states"]])
 
+    def set_layer_norm(self, layer, name, arr):
+        l = self.layers[layer]
+        key = {"r_correction": "r", "d_correction": "d"}.get(name, name)
+        for st, part in zip(l["states"], np.asarray(arr, f32).reshape(self.T, -1)):
+            st[key] = part.copy()
+
     def _W(self, l):
         n = l["units"] * l["fan_in"]
         return self.params[l["first_connection"]:l["first_connection"] + n].reshape(l["units"], l["fan_in"])
@@ -129,6 +135,11 @@ class IndRnnOracleModel(OracleModel):
                 if l["norm"] == NORM_NONE:
                     z = (z + self.params[l["first_bias"]:l["last_bias"]]).astype(f32)
                     y = z
+                elif not self.training:
+                    # The running averages of this time step (fwp_mp.cpp L:4461-4491).
+                    st = l["states"][t]
+                    y = (self.params[self._gamma_slice(l)] * ((z - st["mean_average"]) / st["variance_average"])
+                         + self.params[self._beta_slice(l)]).astype(f32)
                 else:
                     st = l["states"][t]
                     st["gamma"] = self.params[self._gamma_slice(l)]
@@ -207,6 +218,21 @@ class IndRnnOracleModel(OracleModel):
         if self.loss == LOSS_CROSS_ENTROPY:
             return total / rows
         return total / (rows * self.layers[-1]["units"])
+
+    def compute_loss(self, batch, Y):
+        """compute_loss_rec_mp (v1/learner/compute_loss_mp.cpp L:115-205): every
+        row's time steps t >= n_time_delay as rows of the feed-forward form."""
+        T, d, W = self.T, self.time_delay, self.layers[-1]["units"]
+        y = np.asarray(Y[:batch], f32).reshape(batch, T, W).transpose(1, 0, 2)[d:].reshape(-1, W)
+        full = self.layers[-1]["A"]
+        try:
+            self.layers[-1]["A"] = full[d:, :batch].reshape(-1, W)
+            OracleModel.compute_loss(self, (T - d) * batch, y)
+        finally:
+            self.layers[-1]["A"] = full
+
+    def get_accu(self, rows_total):
+        return OracleModel.get_accu(self, rows_total * (self.T - self.time_delay))
 
     def update_weights(self, batch, training_size):
         self._clip_gradient()

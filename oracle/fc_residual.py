@@ -139,8 +139,12 @@ class ResidualOracleModel(OracleModel):
         return self.params[l["first_connection"]:l["last_connection"]].reshape(l["units"], l["fan_in"])
 
     def _norm_in(self, l, x):
-        """Batch renorm of a layer over `x`; remembers what backward needs."""
+        """Batch renorm of a layer over `x`; remembers what backward needs.  At
+        inference the running averages (fwp_mp.cpp L:4461-4491)."""
         st = l["state"]
+        if not self.training:
+            return (self.params[self._gamma_slice(l)] * ((x - st["mean_average"]) / st["variance_average"])
+                    + self.params[self._beta_slice(l)]).astype(f32)
         st["gamma"] = self.params[self._gamma_slice(l)]
         st["beta"] = self.params[self._beta_slice(l)]
         l["norm_in"] = x
@@ -171,14 +175,22 @@ class ResidualOracleModel(OracleModel):
                     else:
                         n = self._norm_in(b, h) if b["norm"] != NORM_NONE else h
                         b["Y"] = n
-                        b["IN"] = apply_dropout(af_fire(b["af"], n), b["dropout"][0], b["dropout"][1], b["mask"])
+                        if self.training:
+                            b["IN"] = apply_dropout(af_fire(b["af"], n), b["dropout"][0], b["dropout"][1], b["mask"])
+                        else:  # plain Bernoulli dropout scales by the keep probability, L:4870-4892
+                            b["IN"] = af_fire(b["af"], n)
+                            if b["dropout"][0] == fc_step.DROPOUT_BERNOULLI:
+                                b["IN"] = (b["IN"] * f32(b["dropout"][1])).astype(f32)
                     s = (b["IN"] @ self._W(b).T).astype(f32)
                     if b["norm"] == NORM_NONE:
                         s = (s + self.params[b["first_bias"]:b["last_bias"]]).astype(f32)
                     b["A"] = s
                     h = s
                 o = self._norm_in(l, h) if l["norm"] != NORM_NONE else h
-                if l["dropout"][0] == DROPOUT_SHAKEDROP:
+                if l["dropout"][0] == DROPOUT_SHAKEDROP and not self.training:
+                    # Inference: the block output times 1 - p (fwp_mp.cpp L:3876-3897).
+                    o = (o * (f32(1) - f32(l["dropout"][1]))).astype(f32)
+                elif l["dropout"][0] == DROPOUT_SHAKEDROP:
                     o = np.where(l["sd_mask"][:batch, None], o * l["sd_fwd"][:batch], o).astype(f32)
                 # The reference normalises / perturbs in place in the last block
                 # layer's output buffer, which is what a reader of that layer sees.
@@ -197,6 +209,10 @@ class ResidualOracleModel(OracleModel):
             l["Z"], l["Y"] = z, y
             if l["af"] == AF_SOFTMAX:
                 a = softmax(y)
+            elif not self.training:
+                a = af_fire(l["af"], y)
+                if l["dropout"][0] == fc_step.DROPOUT_BERNOULLI:
+                    a = (a * f32(l["dropout"][1])).astype(f32)
             else:
                 a = apply_dropout(af_fire(l["af"], y), l["dropout"][0], l["dropout"][1], l["mask"])
             l["A"] = a

@@ -96,6 +96,39 @@ def test_clip_gradient_sets_the_recurrent_bound(gpu_ctx):
         assert util.rel_l2(got["params1"], want["params1"]) <= 1e-5
 
 
+@pytest.mark.parametrize("delay", [7, 0], ids=["last_step", "all_steps"])
+def test_indrnn_evaluation_pass(gpu_ctx, delay):
+    """Inference through time (each time step's own running averages), loss and
+    accuracy over the steps t >= n_time_delay, against the CPU restatement from
+    the same trained state."""
+    cfg = dict(configs.indrnn_stack(n_in=64, hidden=128, depth=2, n_out=32, seq_w=8, batch=32), time_delays=delay)
+    B, last = cfg["batch"], len(cfg["layers"]) - 1
+    X, Y = configs.synthetic_batch(cfg)
+    Xe, Ye = configs.synthetic_batch(dict(cfg, data_seed=5))
+    p0 = _kink_free(cfg, X)
+    ora = util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0)
+    mod = util.build(dlb200.Model(gpu_ctx), cfg, params=p0)
+    util.trace(mod, cfg, 2, X, Y)
+    util.copy_trained_state(mod, ora, cfg)
+    out = []
+    for m in (ora, mod):
+        m.train_begin(B)
+        m.set_propagation(0)
+        m.set_accu_fn(3)   # DISTANCE
+        m.set_accu_var(0.6)
+        m.reset_loss()
+        m.forward_pass(B, Xe)
+        m.compute_loss(B, Ye)
+        out.append((m.get_loss(), m.get_accu(B), m.get_layer_outputs(last, B).reshape(-1)))
+        m.set_propagation(1)
+    (lo, ao, qo), (lg, ag, qg) = out
+    assert gpu_ctx.sync() == 0
+    assert util.rel_l2(qg, qo) <= 1e-5
+    assert abs(lg - lo) <= 1e-5 * abs(lo)
+    trials = B * (8 - delay) * 32
+    assert abs(ag - ao) <= 100.0 * 3 / trials
+
+
 def test_glorot_and_recurrent_initialisation_match_the_fixture_layout(gpu_ctx):
     cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=2, n_out=5, seq_w=4, batch=3)
     m = util.build(dlb200.Model(gpu_ctx), cfg, seed=0)

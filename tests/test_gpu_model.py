@@ -298,11 +298,3 @@ def test_evaluation_pass(gpu_ctx, case):
     assert util.rel_l2(qg, qo) <= TOL_1
     assert abs(lg - lo) <= 1e-5 * abs(lo)
     assert abs(ag - ao) <= 100.0 * 2 / (B * (1 if fn == fc_step.ACCU_CROSS_ENTROPY else qo.shape[1]))
-
-
-def test_inference_of_a_residual_model_is_refused(gpu_ctx):
-    cfg = configs.residual_mlp(width=32, blocks=1, n_out=5, batch=8)
-    m = util.build(dlb200.Model(gpu_ctx), cfg, seed=0)
-    m.set_propagation(0)
-    with pytest.raises(dlb200.DlbError):
-        m.forward_pass(8, np.zeros((8, 32), np.float32))

@@ -57,6 +57,40 @@ def test_residual_model_vs_restatement_tensor_core_shape(gpu_ctx):
     assert util.rel_l2(got["losses"], want["losses"]) <= 1e-4
 
 
+@pytest.mark.skipif(not ref_binding.available(), reason="ShakeDrop draws come from oracle/_ref")
+def test_residual_evaluation_pass(gpu_ctx):
+    """Inference through residual blocks (running averages, block output of a
+    ShakeDrop layer times 1 - p), loss and accuracy, against the CPU restatement
+    from the same trained state."""
+    cfg = configs.residual_mlp(width=256, blocks=2, n_out=10, batch=256)
+    B, last = cfg["batch"], len(cfg["layers"]) - 1
+    X, Y = configs.synthetic_batch(cfg)
+    Xe, Ye = configs.synthetic_batch(dict(cfg, data_seed=5))
+    draws = [util.shakedrop_step_draws(cfg, s) for s in range(2)]
+    mod = util.build(dlb200.Model(gpu_ctx), cfg, seed=4)   # Glorot draws of the library
+    ora = util.build(fc_residual.ResidualOracleModel(), cfg, params=mod.get_array("parameters"))
+    util.trace_noisy(mod, cfg, 2, X, Y, draws)
+    util.copy_trained_state(mod, ora, cfg)
+    out = []
+    for m in (ora, mod):
+        m.train_begin(B)
+        m.set_propagation(0)
+        m.set_accu_fn(1)   # CROSS_ENTROPY
+        m.reset_loss()
+        m.forward_pass(B, Xe)
+        m.compute_loss(B, Ye)
+        out.append((m.get_loss(), m.get_accu(B), m.get_layer_outputs(last, B).reshape(B, -1)))
+        m.set_propagation(1)
+    (lo, ao, qo), (lg, ag, qg) = out
+    assert gpu_ctx.sync() == 0
+    assert util.rel_l2(qg, qo) <= 1e-5
+    assert abs(lg - lo) <= 1e-5 * abs(lo)
+    assert abs(ag - ao) <= 100.0 * 2 / B
+    # Training goes on from the same state afterwards.
+    util.trace_noisy(mod, cfg, 1, X, Y, draws)
+    assert gpu_ctx.sync() == 0
+
+
 def test_residual_kernels(gpu_ctx):
     ctx, L = gpu_ctx, gpu_ctx.L
     rng = np.random.default_rng(9)

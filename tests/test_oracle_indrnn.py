@@ -106,3 +106,31 @@ def test_parameter_layout():
     g0 = m.size("total_weights") + m.size("total_bias")
     gamma = m.get_array("parameters")[g0:g0 + 27]
     assert np.allclose(gamma[:6], 1) and np.allclose(gamma[6:22], 0.1) and np.allclose(gamma[22:], 1)
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("delay", [3, 0], ids=["last_step", "all_steps"])
+def test_indrnn_evaluation_pass_matches_compiled_reference(delay):
+    """Inference through time: every time step normalised by its own running
+    averages, loss and accuracy over the steps t >= n_time_delay
+    (compute_loss_rec_mp, v1/learner/compute_loss_mp.cpp L:115-205)."""
+    cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=2, n_out=5, seq_w=4, batch=5)
+    cfg = dict(cfg, time_delays=delay)
+    B, last = cfg["batch"], len(cfg["layers"]) - 1
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    ora = util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=ref.get_array("parameters"))
+    Xe, Ye = configs.synthetic_batch(dict(cfg, data_seed=5))
+    out = []
+    util.trace(ref, cfg, steps=3)   # move the running averages away from their start
+    util.copy_trained_state(ref, ora, cfg)
+    for m in (ref, ora):
+        m.set_propagation(0)
+        m.set_accu_fn(3)   # DISTANCE
+        m.set_accu_var(0.6)
+        m.reset_loss()
+        m.forward_pass(B, Xe)
+        m.compute_loss(B, Ye)
+        out.append((m.get_loss(), m.get_accu(B), m.get_layer_outputs(last, B).reshape(-1)))
+    (lr, ar, qr), (lo, ao, qo) = out
+    assert abs(lr - lo) <= 1e-5 * abs(lr) and ar == ao
+    assert util.rel_l2(qo, qr) <= 5e-6

@@ -5,13 +5,14 @@ import pytest
 
 import configs
 import fc_residual
+import fc_step
 import golden_io
 import ref_binding
 import util
 
 TOL_L2 = 2e-6
 # Updated weights: the Adam first step lr*g/(|g|+eps) magnifies rounding of
-# gradients that are of the order of eps (parity).
+# gradients that are of the order of eps.
 TOL_PARAMS = 1e-4
 
 
@@ -37,3 +38,29 @@ def test_residual_restatement_matches_compiled_reference(cfg):
     want = util.trace_noisy(ref, cfg, steps=5)
     got = util.trace_noisy(util.build(fc_residual.ResidualOracleModel(), cfg, params=p0), cfg, steps=5)
     _check(got, want)
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+def test_residual_evaluation_pass_matches_compiled_reference():
+    """Inference through residual blocks: running averages in the blocks and in
+    the residual layer's own normalization where it has one, the block output of
+    a ShakeDrop layer times 1 - p (v1/learner/fwp_mp.cpp L:3876-3897), then the
+    loss and the accuracy without an error."""
+    cfg = configs.residual_mlp(40, 4, 5, 24)
+    B, last = cfg["batch"], len(cfg["layers"]) - 1
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    ora = util.build(fc_residual.ResidualOracleModel(), cfg, params=ref.get_array("parameters"))
+    Xe, Ye = configs.synthetic_batch(dict(cfg, data_seed=5))
+    out = []
+    util.trace_noisy(ref, cfg, steps=3)   # move the running averages away from their start
+    util.copy_trained_state(ref, ora, cfg)
+    for m in (ref, ora):
+        m.set_propagation(0)
+        m.set_accu_fn(fc_step.ACCU_CROSS_ENTROPY)
+        m.reset_loss()
+        m.forward_pass(B, Xe)
+        m.compute_loss(B, Ye)
+        out.append((m.get_loss(), m.get_accu(B), m.get_layer_outputs(last, B).reshape(B, -1)))
+    (lr, ar, qr), (lo, ao, qo) = out
+    assert abs(lr - lo) <= 1e-5 * abs(lr) and ar == ao
+    assert util.rel_l2(qo, qr) <= TOL_L2

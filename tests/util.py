@@ -74,6 +74,17 @@ def trace(model, cfg, steps=1, X=None, Y=None, masks=None):
     return out
 
 
+def copy_trained_state(src, dst, cfg):
+    """Parameters and running averages of `src` into `dst`, so that a pass of
+    both starts from the same bits."""
+    dst.set_array("parameters", src.get_array("parameters"))
+    for li, l in enumerate(cfg["layers"]):
+        if l.get("norm"):
+            n = l["units"] * cfg.get("seq_w", 1)
+            for name in ("mean_average", "variance_average"):
+                dst.set_layer_norm(li, name, src.get_layer_norm(li, name, n))
+
+
 def compare(got, want, keys=None):
     """{key: (rel_l2, rel_max)} over the common keys."""
     keys = keys or [k for k in want if k in got]
