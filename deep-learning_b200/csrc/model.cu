@@ -68,6 +68,9 @@ struct HParams {
         learning_rate_final = 0.1f, learning_gamma = 1e-3f, weight_decay = 0.f,
         optimizer_time_step = 0.f, epoch_time_step = 1.f;
   bool use_adam_bias_correction = true;
+  // Gradient descent (model.hpp L:3020-3022, L:2839).
+  float learning_rate = 0.01f, learning_momentum = 0.9f;
+  bool use_nesterov = false;
   // Model defaults, v1/learner/model.hpp L:3045-3048.
   float normalization_momentum_average = 0.999f, normalization_epsilon = 1e-5f,
         brn_r_max = 1.f, brn_d_max = 0.f;
@@ -134,6 +137,16 @@ namespace {
 
 size_t n_in(const dlb_model *m) { return m->layers.front().units; }
 size_t n_out(const dlb_model *m) { return m->layers.back().units; }
+
+// Plain batch normalization (Forward_Pass__Batch_Normalization__Training__OpenMP,
+// fwp_mp.cpp L:4493-4603, backward bwp_mp.cpp L:1265-1385) is batch
+// renormalization with r = 1 and d = 0, which the clips give with these bounds.
+float r_max_of(const dlb_model *m, const LayerRT &l) {
+  return l.norm == DLB_NORM_BATCH_NORMALIZATION ? 1.f : m->hp.brn_r_max;
+}
+float d_max_of(const dlb_model *m, const LayerRT &l) {
+  return l.norm == DLB_NORM_BATCH_NORMALIZATION ? 0.f : m->hp.brn_d_max;
+}
 
 // mag of the IndRNN bounds: clip(clip_gradient, 2, 10)
 // (v1/ops/constraints/constraint.cpp L:66, v1/learner/model.cpp L:5303, L:5336).
@@ -503,7 +516,7 @@ dlb_status norm_statistics(dlb_model *m, LayerRT &l, const float *in, int B, dlb
   DLB_TRY(dlb_brn_forward_sums(m->ctx, in, B, n, l.fwd_sums));
   DLB_TRY(dlb_allreduce_f64(m->ctx, l.fwd_sums, 2 * (size_t)n));
   return dlb_brn_forward_finalize(m->ctx, l.fwd_sums, Bg, n, m->hp.normalization_momentum_average,
-                                  m->hp.normalization_epsilon, m->hp.brn_r_max, m->hp.brn_d_max, u);
+                                  m->hp.normalization_epsilon, r_max_of(m, l), d_max_of(m, l), u);
 }
 
 // Backward of the same: the four sums, d_gamma / d_beta into the gradient
@@ -640,8 +653,8 @@ dlb_status forward_layers_time(dlb_model *m, size_t rows) {
         DLB_TRY(dlb_allreduce_f64(m->ctx, l.fwd_sums, 2 * (size_t)T * H));
         DLB_TRY(dlb_brn_time_forward_finalize(m->ctx, l.fwd_sums, Bg, T, H,
                                               m->hp.normalization_momentum_average,
-                                              m->hp.normalization_epsilon, m->hp.brn_r_max,
-                                              m->hp.brn_d_max, &u));
+                                              m->hp.normalization_epsilon, r_max_of(m, l),
+                                              d_max_of(m, l), &u));
       }
       DLB_TRY(dlb_indrnn_forward(m->ctx, l.Z, norm ? &u : nullptr,
                                  is_indrnn(l) ? m->params + l.first_recurrent : nullptr, l.af, l.A,
@@ -841,8 +854,8 @@ dlb_status dlb_model_set_layer_normalization(dlb_model *m, size_t layer, int nor
   // Not on the input or output layer (v1/learner/normalization.cpp L:419-422).
   DLB_REQUIRE(layer > 0 && layer + 1 < m->layers.size(),
               "Set__Layer_Normalization: not available on the input or output layer");
-  if (norm != DLB_NORM_NONE && norm != DLB_NORM_BATCH_RENORMALIZATION) {
-    set_error("Set__Layer_Normalization: only batch renormalization is supported (got %d)", norm);
+  if (norm != DLB_NORM_NONE && norm != DLB_NORM_BATCH_RENORMALIZATION && norm != DLB_NORM_BATCH_NORMALIZATION) {
+    set_error("Set__Layer_Normalization: batch normalization and renormalization are supported (got %d)", norm);
     return DLB_ERR_UNSUPPORTED;
   }
   if (m->layers[layer].stats) {
@@ -922,7 +935,7 @@ dlb_status dlb_model_set_optimizer(dlb_model *m, int optimizer) {
   DLB_REQUIRE(m, "null");
   switch (optimizer) {
     case DLB_OPT_ADABOUND: case DLB_OPT_ADAM: case DLB_OPT_ADAMAX: case DLB_OPT_AMSBOUND:
-    case DLB_OPT_AMSGRAD: case DLB_OPT_NOSADAM:
+    case DLB_OPT_AMSGRAD: case DLB_OPT_NOSADAM: case DLB_OPT_GD:
       m->optimizer = optimizer;
       return DLB_OK;
     default:
@@ -934,7 +947,7 @@ dlb_status dlb_model_set_optimizer(dlb_model *m, int optimizer) {
 #define DLB_HPARAMS(X)                                                                       \
   X(adam_learning_rate) X(adam_beta1) X(adam_beta2) X(adam_previous_beta2) X(adam_epsilon)   \
   X(adam_gamma) X(learning_rate_final) X(learning_gamma) X(weight_decay)                     \
-  X(optimizer_time_step) X(epoch_time_step)
+  X(optimizer_time_step) X(epoch_time_step) X(learning_rate) X(learning_momentum)
 
 dlb_status dlb_model_set_hparam(dlb_model *m, const char *name, double value) {
   DLB_REQUIRE(m && name, "set_hparam: null");
@@ -943,6 +956,7 @@ dlb_status dlb_model_set_hparam(dlb_model *m, const char *name, double value) {
   DLB_HPARAMS(X)
 #undef X
   if (n == "use_adam_bias_correction") { m->hp.use_adam_bias_correction = value != 0.0; return DLB_OK; }
+  if (n == "use_nesterov") { m->hp.use_nesterov = value != 0.0; return DLB_OK; }
   if (n == "pct_threads") return DLB_OK;  // CPU threading knob of the reference; nothing to set
   set_error("set_hparam: unknown field %s", name);
   return DLB_ERR_INVALID;
@@ -955,6 +969,7 @@ double dlb_model_get_hparam(dlb_model *m, const char *name) {
   DLB_HPARAMS(X)
 #undef X
   if (n == "use_adam_bias_correction") return m->hp.use_adam_bias_correction;
+  if (n == "use_nesterov") return m->hp.use_nesterov;
   return -1.0;
 }
 
@@ -1476,9 +1491,14 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
     }
     wd = m->hp.weight_decay * sqrtf((float)rows / ((float)training_size * m->hp.epoch_time_step));
   }
-  const float hyper[8] = {m->hp.adam_learning_rate, m->hp.adam_beta1, m->hp.adam_beta2,
-                          m->hp.adam_epsilon, m->hp.adam_gamma, m->hp.learning_rate_final,
-                          m->hp.learning_gamma, m->hp.use_adam_bias_correction ? 1.f : 0.f};
+  float hyper[8] = {m->hp.adam_learning_rate, m->hp.adam_beta1, m->hp.adam_beta2,
+                    m->hp.adam_epsilon, m->hp.adam_gamma, m->hp.learning_rate_final,
+                    m->hp.learning_gamma, m->hp.use_adam_bias_correction ? 1.f : 0.f};
+  if (m->optimizer == DLB_OPT_GD) {
+    hyper[0] = m->hp.learning_rate;
+    hyper[1] = m->hp.learning_momentum;
+    hyper[2] = m->hp.use_nesterov ? 1.f : 0.f;
+  }
   if (m->use_clip_gradient)
     DLB_TRY(dlb_clip_gradient(m->ctx, m->grads, m->total_parameters, m->clip_gradient));
   dlb_optimizer_scalars k;

@@ -1,9 +1,11 @@
-// Adam-family update over flat parameter / gradient / moment vectors: one
+// Adam-family and gradient-descent updates over flat parameter / gradient /
+// moment vectors: one
 // streaming pass with 128-bit loads and stores, the rule chosen at compile time
 // so the inner loop carries no branch on it.  Algorithmic traffic per element:
 // read p, g, m, v and write p, m, v, g<-0 = 32 bytes (Adam, AdaBound, NosAdam,
 // AdaMax); +8 for the running maximum (AMSGrad, AMSBound); +4 for the
-// regularisation mask when weight decay is on.
+// regularisation mask when weight decay is on.  Gradient descent reads p, g and
+// writes p, g<-0 (16 bytes), +8 for the previous delta with momentum.
 #include <math.h>
 
 #include "common.cuh"
@@ -11,7 +13,7 @@
 
 namespace dlb {
 
-enum Rule { R_ADAM, R_AMSGRAD, R_ADABOUND, R_AMSBOUND, R_ADAMAX };
+enum Rule { R_ADAM, R_AMSGRAD, R_ADABOUND, R_AMSBOUND, R_ADAMAX, R_GD, R_GD_MOMENTUM, R_GD_NESTEROV };
 
 struct OptState {
   float p, g, m, v, vh;
@@ -24,6 +26,20 @@ struct OptState {
 template <int RULE, bool WD>
 __device__ __forceinline__ void update_one(OptState &s, float mask, const dlb_optimizer_scalars &k) {
   const float g = s.g;
+  if (RULE == R_GD || RULE == R_GD_MOMENTUM || RULE == R_GD_NESTEROV) {
+    // v1/optimizers/gradient_descent.cpp L:57-130, gradient_descent_momentum.cpp
+    // L:66-107, nesterov_accelerated_gradient.cpp L:66-109: lr_t is the learning
+    // rate, beta1 the momentum, m the previous delta.
+    float step = k.lr_t * g;
+    if (RULE != R_GD) {
+      s.m = step + k.beta1 * s.m;
+      step = RULE == R_GD_NESTEROV ? k.beta1 * s.m - step : s.m;
+    }
+    if (WD) step += mask * k.weight_decay * s.p;
+    s.p -= step;
+    s.g = 0.f;
+    return;
+  }
   s.m = k.beta1 * s.m + (1.f - k.beta1) * g;
   if (RULE == R_ADAMAX) {
     s.v = fmaxf(k.beta2 * s.v, fabsf(g));
@@ -55,14 +71,16 @@ __global__ void __launch_bounds__(256)
                      float *__restrict__ m, float *__restrict__ v, float *__restrict__ vh,
                      const float *__restrict__ mask, size_t n) {
   constexpr bool HAT = (RULE == R_AMSGRAD || RULE == R_AMSBOUND);
+  constexpr bool FIRST = RULE != R_GD;                                              // m is read and written
+  constexpr bool SECOND = !(RULE == R_GD || RULE == R_GD_MOMENTUM || RULE == R_GD_NESTEROV);  // v likewise
   const size_t n4 = n / 4;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
     float4 P = reinterpret_cast<float4 *>(p)[i];
     const float4 G = reinterpret_cast<float4 *>(g)[i];
-    float4 M = reinterpret_cast<float4 *>(m)[i];
-    float4 V = reinterpret_cast<float4 *>(v)[i];
-    float4 H = make_float4(0.f, 0.f, 0.f, 0.f), K = H;
+    float4 H = make_float4(0.f, 0.f, 0.f, 0.f), K = H, M = H, V = H;
+    if (FIRST) M = reinterpret_cast<float4 *>(m)[i];
+    if (SECOND) V = reinterpret_cast<float4 *>(v)[i];
     if (HAT) H = reinterpret_cast<float4 *>(vh)[i];
     if (WD) K = __ldg(reinterpret_cast<const float4 *>(mask) + i);
     OptState s0{P.x, G.x, M.x, V.x, H.x}, s1{P.y, G.y, M.y, V.y, H.y}, s2{P.z, G.z, M.z, V.z, H.z},
@@ -72,16 +90,18 @@ __global__ void __launch_bounds__(256)
     update_one<RULE, WD>(s2, K.z, k);
     update_one<RULE, WD>(s3, K.w, k);
     reinterpret_cast<float4 *>(p)[i] = make_float4(s0.p, s1.p, s2.p, s3.p);
-    reinterpret_cast<float4 *>(m)[i] = make_float4(s0.m, s1.m, s2.m, s3.m);
-    reinterpret_cast<float4 *>(v)[i] = make_float4(s0.v, s1.v, s2.v, s3.v);
+    if (FIRST) reinterpret_cast<float4 *>(m)[i] = make_float4(s0.m, s1.m, s2.m, s3.m);
+    if (SECOND) reinterpret_cast<float4 *>(v)[i] = make_float4(s0.v, s1.v, s2.v, s3.v);
     if (HAT) reinterpret_cast<float4 *>(vh)[i] = make_float4(s0.vh, s1.vh, s2.vh, s3.vh);
     reinterpret_cast<float4 *>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   // Tail (n not a multiple of 4).
   for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    OptState s{p[i], g[i], m[i], v[i], HAT ? vh[i] : 0.f};
+    OptState s{p[i], g[i], FIRST ? m[i] : 0.f, SECOND ? v[i] : 0.f, HAT ? vh[i] : 0.f};
     update_one<RULE, WD>(s, WD ? mask[i] : 0.f, k);
-    p[i] = s.p; m[i] = s.m; v[i] = s.v; g[i] = 0.f;
+    p[i] = s.p; g[i] = 0.f;
+    if (FIRST) m[i] = s.m;
+    if (SECOND) v[i] = s.v;
     if (HAT) vh[i] = s.vh;
   }
 }
@@ -168,13 +188,17 @@ extern "C" {
 dlb_status dlb_optimizer_step(dlb_ctx *ctx, int rule, const dlb_optimizer_scalars *s, float *p,
                               float *g, float *first, float *second, float *second_hat,
                               const float *wd_mask, size_t n) {
-  DLB_REQUIRE(ctx && s && p && g && first && second, "dlb_optimizer_step: null");
+  DLB_REQUIRE(ctx && s && p && g, "dlb_optimizer_step: null");
   if (n == 0) return DLB_OK;
   const bool hat = rule == DLB_OPT_AMSGRAD || rule == DLB_OPT_AMSBOUND;
+  const bool descent = rule == DLB_OPT_GD;
+  DLB_REQUIRE(first || (descent && s->beta1 == 0.f), "dlb_optimizer_step: first required");
+  DLB_REQUIRE(second || descent, "dlb_optimizer_step: second required");
   DLB_REQUIRE(!hat || second_hat, "dlb_optimizer_step: second_hat required");
   DLB_REQUIRE(s->weight_decay == 0.f || wd_mask, "dlb_optimizer_step: weight decay needs a mask");
   const uintptr_t al = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
-                       reinterpret_cast<uintptr_t>(first) | reinterpret_cast<uintptr_t>(second) |
+                       (descent && s->beta1 == 0.f ? 0 : reinterpret_cast<uintptr_t>(first)) |
+                       (descent ? 0 : reinterpret_cast<uintptr_t>(second)) |
                        (hat ? reinterpret_cast<uintptr_t>(second_hat) : 0) |
                        (s->weight_decay != 0.f ? reinterpret_cast<uintptr_t>(wd_mask) : 0);
   DLB_REQUIRE((al & 15) == 0, "dlb_optimizer_step: arrays must be 16-byte aligned");
@@ -190,6 +214,13 @@ dlb_status dlb_optimizer_step(dlb_ctx *ctx, int rule, const dlb_optimizer_scalar
       return launch_rule<R_AMSBOUND>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
     case DLB_OPT_ADAMAX:
       return launch_rule<R_ADAMAX>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+    case DLB_OPT_GD:
+      // The three forms of Model::Update_Parameter__Gradient_Descent
+      // (v1/optimizers/gradient_descent.cpp L:24-55).
+      if (s->beta1 == 0.f) return launch_rule<R_GD>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+      if (s->beta2 != 0.f)
+        return launch_rule<R_GD_NESTEROV>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+      return launch_rule<R_GD_MOMENTUM>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
     default:
       set_error("dlb_optimizer_step: optimizer %d is outside the supported path", rule);
       return DLB_ERR_UNSUPPORTED;
@@ -221,6 +252,15 @@ dlb_status dlb_optimizer_prepare(int rule, const float *hyper, float *time_step,
   const bool bias_correction = hyper[7] != 0.f;
   *time_step += 1.f;  // the reference keeps the step count in a float
   const float t = *time_step;
+  if (rule == DLB_OPT_GD) {
+    // hyper = {learning_rate, learning_momentum, use_nesterov(0/1)}.
+    dlb_optimizer_scalars d{};
+    d.lr_t = hyper[0];
+    d.beta1 = hyper[1];
+    d.beta2 = hyper[2] != 0.f ? 1.f : 0.f;
+    *out = d;
+    return DLB_OK;
+  }
   dlb_optimizer_scalars k{};
   k.beta1 = beta1;
   k.beta2 = beta2;

@@ -26,6 +26,7 @@ class ACTIVATION:
 
 class LAYER_NORM:
     NONE = 0
+    BATCH_NORMALIZATION = 1
     BATCH_RENORMALIZATION = 2
 
 
@@ -43,6 +44,7 @@ class OPTIMIZER:
     ADAMAX = 3
     AMSBOUND = 4
     AMSGRAD = 5
+    GD = 6
     NOSADAM = 9
 
 

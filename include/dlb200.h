@@ -43,11 +43,11 @@ enum { DLB_AF_ELU = 3, DLB_AF_ISRLU = 10, DLB_AF_LINEAR = 11, DLB_AF_LEAKY_RELU 
 enum { DLB_DROPOUT_NONE = 0, DLB_DROPOUT_BERNOULLI = 2, DLB_DROPOUT_BERNOULLI_INVERTED = 3,
        DLB_DROPOUT_SHAKEDROP = 5, DLB_DROPOUT_UOUT = 6 };
 enum { DLB_OPT_ADABOUND = 1, DLB_OPT_ADAM = 2, DLB_OPT_ADAMAX = 3, DLB_OPT_AMSBOUND = 4,
-       DLB_OPT_AMSGRAD = 5, DLB_OPT_NOSADAM = 9 };
+       DLB_OPT_AMSGRAD = 5, DLB_OPT_GD = 6, DLB_OPT_NOSADAM = 9 };
 enum { DLB_LOSS_CROSS_ENTROPY = 2, DLB_LOSS_MSE = 10 };
 enum { DLB_LAYER_FULLY_CONNECTED = 3, DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT = 4,
        DLB_LAYER_RESIDUAL = 9 };
-enum { DLB_NORM_NONE = 0, DLB_NORM_BATCH_RENORMALIZATION = 2 };
+enum { DLB_NORM_NONE = 0, DLB_NORM_BATCH_NORMALIZATION = 1, DLB_NORM_BATCH_RENORMALIZATION = 2 };
 enum { DLB_MODEL_FEEDFORWARD = 3, DLB_MODEL_RECURRENT = 4 };
 enum { DLB_PROPAGATION_INFERENCE = 0, DLB_PROPAGATION_TRAINING = 1 };
 enum { DLB_ACCU_CROSS_ENTROPY = 1, DLB_ACCU_DISTANCE = 3 };
@@ -377,7 +377,12 @@ typedef struct dlb_optimizer_scalars {
  * (v1/optimizers/adam.cpp L:98-165, amsgrad.cpp L:34-109, adabound.cpp
  * L:38-112, amsbound.cpp L:38-126, nosadam.cpp L:33-102).  AdaMax has no
  * implementation in the reference (v1/learner/model.cpp L:4765-4767); the
- * rule here is Kingma & Ba section 7 with second = the infinity norm u. */
+ * rule here is Kingma & Ba section 7 with second = the infinity norm u.
+ * DLB_OPT_GD is Model::Update_Parameter__Gradient_Descent
+ * (v1/optimizers/gradient_descent.cpp L:24-130, gradient_descent_momentum.cpp
+ * L:66-107, nesterov_accelerated_gradient.cpp L:66-109): lr_t = learning rate,
+ * beta1 = momentum (0: plain descent, `first` unused), beta2 != 0 = the
+ * Nesterov form; `first` holds the previous delta, `second` is unused. */
 dlb_status dlb_optimizer_step(dlb_ctx *ctx, int rule, const dlb_optimizer_scalars *s, float *p,
                               float *g, float *first, float *second, float *second_hat,
                               const float *wd_mask, size_t n);
@@ -392,7 +397,8 @@ dlb_status dlb_clip_gradient(dlb_ctx *ctx, float *g, size_t n, float max_norm);
 /* Host-side scalars exactly as the reference derives them from its float time
  * step (increments *time_step first).  hyper = {lr, beta1, beta2, epsilon,
  * gamma(NosAdam), final_lr, bound_gamma, bias_correction(0/1)};
- * *nos_previous is NosAdam's running B_{t-1}. */
+ * *nos_previous is NosAdam's running B_{t-1}.  For DLB_OPT_GD hyper =
+ * {learning_rate, learning_momentum, use_nesterov(0/1)}. */
 dlb_status dlb_optimizer_prepare(int rule, const float *hyper, float *time_step,
                                  float *nos_previous, dlb_optimizer_scalars *out);
 

@@ -144,7 +144,7 @@ class IndRnnOracleModel(OracleModel):
                     st = l["states"][t]
                     st["gamma"] = self.params[self._gamma_slice(l)]
                     st["beta"] = self.params[self._beta_slice(l)]
-                    XH[t], y = brn_forward(z, st, self.brn, self.global_rows, self.allreduce)
+                    XH[t], y = brn_forward(z, st, self._brn_of(l), self.global_rows, self.allreduce)
                 Z[t], Y[t] = z, y
                 if l["type"] == LAYER_INDRNN:
                     PRE[t] = y if t == 0 else (y + self._u(l) * A[t - 1]).astype(f32)

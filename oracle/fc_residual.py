@@ -148,7 +148,7 @@ class ResidualOracleModel(OracleModel):
         st["gamma"] = self.params[self._gamma_slice(l)]
         st["beta"] = self.params[self._beta_slice(l)]
         l["norm_in"] = x
-        l["x_hat"], y = brn_forward(x, st, self.brn, self.global_rows, self.allreduce)
+        l["x_hat"], y = brn_forward(x, st, self._brn_of(l), self.global_rows, self.allreduce)
         return y
 
     def _norm_back(self, l, dy):

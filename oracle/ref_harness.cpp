@@ -150,6 +150,8 @@ int ref_set_optimizer(ref_model m, int optimizer) {
   X(adam_gamma)                   \
   X(adam_previous_beta2)          \
   X(learning_rate_final)          \
+  X(learning_rate)                \
+  X(learning_momentum)            \
   X(learning_gamma)               \
   X(weight_decay)                 \
   X(optimizer_time_step)          \
@@ -167,6 +169,10 @@ int ref_set_hparam(ref_model m, const char *name, double value) {
 #undef X
   if (n == "use_adam_bias_correction") {
     M.use_adam_bias_correction = value != 0.0;
+    return 0;
+  }
+  if (n == "use_nesterov") {
+    M.use_nesterov = value != 0.0;
     return 0;
   }
   if (n == "pct_threads") return M.Set__Maximum_Thread_Usage(value) ? 0 : -1;

@@ -64,7 +64,7 @@ def test_optimizer_prepare_is_host_only():
             np.testing.assert_allclose(k.lr_t, want["lr_t"], rtol=2e-6)
             np.testing.assert_allclose(k.beta2, want["beta2"], rtol=2e-6)
             np.testing.assert_allclose([k.lower_bound, k.upper_bound], [want["lo"], want["hi"]], rtol=2e-6)
-    assert L.dlb_optimizer_prepare(6, hyper, ctypes.byref(t), ctypes.byref(prev), ctypes.byref(k)) == 3
+    assert L.dlb_optimizer_prepare(7, hyper, ctypes.byref(t), ctypes.byref(prev), ctypes.byref(k)) == 3   # iRPROP-
 
 
 def test_no_cpu_fallback():

@@ -11,7 +11,7 @@ import fc_step
 import golden_io
 import ref_binding
 import util
-from enums import ACTIVATION, LAYER_DROPOUT, OPTIMIZER
+from enums import ACTIVATION, LAYER_DROPOUT, LAYER_NORM, OPTIMIZER
 
 pytestmark = pytest.mark.gpu
 
@@ -160,7 +160,7 @@ def test_unsupported_configurations_are_refused(gpu_ctx):
     with pytest.raises(dlb200.DlbError):
         m.set_dropout(2, 2, 0.5)                     # not on the output layer
     with pytest.raises(dlb200.DlbError):
-        m.set_optimizer(6)                           # GD
+        m.set_optimizer(7)                           # iRPROP-
     with pytest.raises(dlb200.DlbError):
         m.forward_pass(4, np.zeros((4, 8), np.float32))   # activations never set (reference default: sigmoid)
 
@@ -188,6 +188,48 @@ def test_weight_decay(gpu_ctx, optimizer):
     assert np.abs(plain["params1"][:nw] - got["params1"][:nw]).mean() > 0.01 * moved
     with pytest.raises(dlb200.DlbError):
         mod.set_weight_decay(1.5)
+
+
+def test_plain_batch_normalization(gpu_ctx):
+    """LAYER_NORM::BATCH_NORMALIZATION: r = 1, d = 0 whatever the model's maxima,
+    against the CPU restatement (itself pinned to the compiled reference)."""
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96)
+    layers = [dict(l, norm=LAYER_NORM.BATCH_NORMALIZATION) if l.get("norm") else l for l in cfg["layers"]]
+    cfg = dict(cfg, layers=layers)
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    p0, seed = util.kink_free_parameters(cfg, fc_step.OracleModel, X, masks, scale=1.0 / np.sqrt(128))
+    want = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, 1, X, Y, masks)
+    mod = gpu_model(gpu_ctx, cfg, p0)
+    got = util.trace(mod, cfg, 1, X, Y, masks)
+    assert gpu_ctx.sync() == 0
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_1, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+    assert np.all(mod.get_layer_norm(1, "r_correction", 128) == 1) and not mod.get_layer_norm(1, "d_correction", 128).any()
+
+
+@pytest.mark.parametrize("form", ["plain", "momentum", "nesterov"])
+def test_gradient_descent(gpu_ctx, form):
+    """Gradient descent, with momentum and in the Nesterov form, with weight
+    decay, against the CPU restatement (itself pinned to the compiled
+    reference)."""
+    extra = {"plain": dict(learning_momentum=0.0), "momentum": dict(learning_momentum=0.9),
+             "nesterov": dict(learning_momentum=0.9, use_nesterov=1)}[form]
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96, optimizer=OPTIMIZER.GD)
+    cfg = dict(cfg, hparams=dict(learning_rate=0.05, **extra))
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    p0, seed = util.kink_free_parameters(cfg, fc_step.OracleModel, X, masks, scale=1.0 / np.sqrt(128))
+    ora = util.build(fc_step.OracleModel(), cfg, params=p0)
+    ora.set_weight_decay(0.05)
+    want = util.trace(ora, cfg, 2, X, Y, masks)
+    mod = gpu_model(gpu_ctx, cfg, p0)
+    mod.set_weight_decay(0.05)
+    got = util.trace(mod, cfg, 2, X, Y, masks)
+    assert gpu_ctx.sync() == 0
+    assert util.rel_l2(got["params1"], want["params1"]) <= TOL_1
+    assert util.rel_l2(got["params_last"], want["params_last"]) <= TOL_N
+    assert util.rel_l2(got["params_last"] - p0, want["params_last"] - p0) <= 1e-3   # the movement itself
 
 
 def test_gradient_clipping(gpu_ctx):

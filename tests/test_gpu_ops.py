@@ -359,13 +359,46 @@ def test_optimizer_sweep(gpu_ctx, rule, n):
         assert util.rel_l2(vh.get(), vho) <= 1e-6
 
 
+@pytest.mark.parametrize("form", ["plain", "momentum", "nesterov"])
+@pytest.mark.parametrize("n", [1_000_003, 5])
+def test_gradient_descent_sweep(gpu_ctx, form, n):
+    """The three gradient-descent forms over a flat vector with weight decay,
+    10 steps; plain descent takes no moment arrays at all."""
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rng = np.random.default_rng(n % 89)
+    p = (0.02 * rng.standard_normal(n)).astype(np.float32)
+    g = (1e-3 * rng.standard_normal(n)).astype(np.float32)
+    mask = (rng.random(n) < 0.7).astype(np.float32)
+    mom, nag = {"plain": (0.0, 0), "momentum": (0.9, 0), "nesterov": (0.9, 1)}[form]
+    hp = dict(learning_rate=0.05, learning_momentum=mom, use_nesterov=nag)
+    pd, gd, m, md = ctx.array(p), ctx.array(g), ctx.zeros(n), ctx.array(mask)
+    hyper = (C.c_float * 8)(0.05, mom, nag, 0, 0, 0, 0, 0)
+    t, prev = C.c_float(0), C.c_float(0)
+    po, mo, state = p.copy(), np.zeros(n, np.float32), {}
+    for step in range(10):
+        k = dlb200.OptimizerScalars()
+        check(L.dlb_optimizer_prepare(6, hyper, C.byref(t), C.byref(prev), C.byref(k)))
+        k.weight_decay = 0.01
+        if step:
+            gd.set(g)
+        check(L.dlb_optimizer_step(ctx.h, 6, C.byref(k), pd.ptr, gd.ptr, m.ptr if mom else None, None, None,
+                                   md.ptr, n))
+        fc_step.optimizer_update(6, fc_step.optimizer_scalars(6, hp, state), po, g.copy(), mo, None, None,
+                                 wd=0.01, mask=mask)
+    assert ctx.sync() == 0 and t.value == 10
+    assert not gd.get().any()
+    assert util.rel_l2(pd.get() - p, po - p) <= F32_TOL
+    if mom:
+        assert util.rel_l2(m.get(), mo) <= 1e-6
+
+
 def test_bad_arguments_are_refused(gpu_ctx):
     ctx, L = gpu_ctx, gpu_ctx.L
     x = ctx.zeros(16)
     assert L.dlb_fc_forward(ctx.h, None, None, x.ptr, None, None, x.ptr, 1, 4, 4) == 1
     assert L.dlb_fc_forward(ctx.h, x.ptr, None, x.ptr, None, None, x.ptr, 0, 4, 4) == 1
     k = dlb200.OptimizerScalars()
-    assert L.dlb_optimizer_step(ctx.h, 6, C.byref(k), x.ptr, x.ptr, x.ptr, x.ptr, None, None, 16) == 3
+    assert L.dlb_optimizer_step(ctx.h, 7, C.byref(k), x.ptr, x.ptr, x.ptr, x.ptr, None, None, 16) == 3
     assert L.dlb_optimizer_step(ctx.h, 5, C.byref(k), x.ptr, x.ptr, x.ptr, x.ptr, None, None, 16) == 1
     assert L.dlb_loss_delta(ctx.h, 3, 11, x.ptr, x.ptr, x.ptr, x.ptr, None, 4, 4, 4, x.ptr) == 3
     assert b"invalid" in L.dlb_status_string(1)

@@ -9,7 +9,7 @@ import fc_step
 import golden_io
 import ref_binding
 import util
-from enums import ACTIVATION, LAYER_DROPOUT, OPTIMIZER
+from enums import ACTIVATION, LAYER_DROPOUT, LAYER_NORM, OPTIMIZER
 
 # L2-relative bound for every compared tensor.  The restatement differs from the
 # reference only in summation order (blocked dot vs sequential loop).
@@ -97,6 +97,51 @@ def test_weight_decay_matches_compiled_reference(optimizer):
         assert l2 <= TOL_L2, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
     plain = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, steps=4)
     assert util.rel_l2(plain["params_last"], want["params_last"]) > 1e-4   # the decay is not a no-op
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("mp", [True, False], ids=["openmp", "serial"])
+def test_plain_batch_normalization_matches_compiled_reference(mp):
+    """LAYER_NORM::BATCH_NORMALIZATION (fwp_mp.cpp L:4493-4603, bwp_mp.cpp
+    L:1265-1385): the renormalization path with r = 1 and d = 0, although the
+    model's r and d maxima are set to other values."""
+    cfg = configs.deep_brn_mlp(20, 32, 2, 12, 24)
+    layers = [dict(l, norm=LAYER_NORM.BATCH_NORMALIZATION) if l.get("norm") else l for l in cfg["layers"]]
+    cfg = dict(cfg, layers=layers, mp=mp)
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    p0 = ref.get_array("parameters")
+    want = util.trace(ref, cfg, steps=4)
+    got = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, steps=4)
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_L2, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+    brn_cfg = configs.deep_brn_mlp(20, 32, 2, 12, 24)
+    renorm = util.trace(util.build(fc_step.OracleModel(), brn_cfg, params=p0), brn_cfg, steps=4)
+    assert util.rel_l2(renorm["params_last"], want["params_last"]) > 1e-5   # not the same as renormalization
+
+
+GD_FORMS = {"plain": dict(learning_momentum=0.0), "momentum": dict(learning_momentum=0.9),
+            "nesterov": dict(learning_momentum=0.9, use_nesterov=1)}
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("form", sorted(GD_FORMS))
+@pytest.mark.parametrize("decay", [0.0, 0.01], ids=["no_decay", "decay"])
+def test_gradient_descent_matches_compiled_reference(form, decay):
+    """The three forms of Model::Update_Parameter__Gradient_Descent
+    (v1/optimizers/gradient_descent.cpp L:24-130, gradient_descent_momentum.cpp
+    L:66-107, nesterov_accelerated_gradient.cpp L:66-109), with and without
+    weight decay."""
+    cfg = configs.deep_brn_mlp(20, 32, 2, 12, 24, optimizer=OPTIMIZER.GD)
+    cfg = dict(cfg, hparams=dict(learning_rate=0.05, **GD_FORMS[form]))
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    ora = util.build(fc_step.OracleModel(), cfg, params=ref.get_array("parameters"))
+    if decay:
+        ref.set_weight_decay(decay)
+        ora.set_weight_decay(decay)
+    want = util.trace(ref, cfg, steps=4)
+    got = util.trace(ora, cfg, steps=4)
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_L2, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
 
 
 @pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
