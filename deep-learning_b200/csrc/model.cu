@@ -1153,21 +1153,85 @@ dlb_status dlb_model_set_dropout_mask(dlb_model *m, size_t layer, const uint8_t 
   return dlb_ctx_sync(m->ctx, nullptr);
 }
 
+// A block layer's dropout acts on its input (pre-activation order).
+static size_t uout_width(const LayerRT &l) { return l.group == 1 ? l.fan_in : l.units; }
+
+static dlb_status ensure_uout(dlb_model *m, LayerRT &l, size_t rows) {
+  if (rows <= l.uout_rows) return DLB_OK;
+  if (l.uout) DLB_TRY(dlb_free(m->ctx, l.uout));
+  l.uout = nullptr;
+  l.uout_rows = 0;
+  DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.uout), rows * uout_width(l) * sizeof(float)));
+  l.uout_rows = rows;
+  return DLB_OK;
+}
+
+static dlb_status ensure_shakedrop(dlb_model *m, LayerRT &l, size_t rows) {
+  if (rows <= l.sd_rows) return DLB_OK;
+  if (l.sd_mask) DLB_TRY(dlb_free(m->ctx, l.sd_mask));
+  if (l.sd_fwd) DLB_TRY(dlb_free(m->ctx, l.sd_fwd));
+  if (l.sd_bwd) DLB_TRY(dlb_free(m->ctx, l.sd_bwd));
+  l.sd_mask = nullptr;
+  l.sd_fwd = l.sd_bwd = nullptr;
+  l.sd_rows = 0;
+  DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_mask), rows));
+  DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_fwd), rows * l.units * sizeof(float)));
+  DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_bwd), rows * l.units * sizeof(float)));
+  l.sd_rows = rows;
+  return DLB_OK;
+}
+
 dlb_status dlb_model_set_uout_noise(dlb_model *m, size_t layer, const float *host_noise, size_t rows) {
   DLB_REQUIRE(m && host_noise && layer_at(m, layer) && rows > 0, "set_uout_noise");
   LayerRT &l = m->layers[layer];
   DLB_REQUIRE(l.dropout == DLB_DROPOUT_UOUT, "set_uout_noise: layer does not use UOut");
-  // A block layer's dropout acts on its input (pre-activation order).
-  const size_t width = l.group == 1 ? l.fan_in : l.units;
-  if (rows > l.uout_rows) {
-    if (l.uout) DLB_TRY(dlb_free(m->ctx, l.uout));
-    l.uout = nullptr;
-    l.uout_rows = 0;
-    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.uout), rows * width * sizeof(float)));
-    l.uout_rows = rows;
-  }
-  DLB_TRY(dlb_memcpy_h2d(m->ctx, l.uout, host_noise, rows * width * sizeof(float)));
+  DLB_TRY(ensure_uout(m, l, rows));
+  DLB_TRY(dlb_memcpy_h2d(m->ctx, l.uout, host_noise, rows * uout_width(l) * sizeof(float)));
   return dlb_ctx_sync(m->ctx, nullptr);
+}
+
+// The step's noise drawn on the device (csrc/noise.cu) instead of handed over:
+// per layer, stream 4 * layer + {0: Bernoulli flags, 1: forward draws, 2:
+// backward draws}.  Masks of Bernoulli dropout have one flag per unit (every
+// row shares it, Model::Dropout_Bernoulli); UOut and ShakeDrop arrays have one
+// row per example and are indexed by the example's row in the whole batch,
+// first_row + r, so that every sharding of the batch draws the same array.
+dlb_status dlb_model_draw_noise(dlb_model *m, size_t rows, uint64_t seed, uint32_t step, size_t first_row) {
+  DLB_REQUIRE(m && rows > 0, "draw_noise");
+  DLB_TRY(check_supported(m));
+  DLB_TRY(ensure_masks(m));
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    LayerRT &l = m->layers[i];
+    const uint32_t stream = 4u * (uint32_t)i;
+    switch (l.dropout) {
+      case DLB_DROPOUT_BERNOULLI:
+      case DLB_DROPOUT_BERNOULLI_INVERTED:
+        // dropout_value is the probability that a unit is kept.
+        DLB_TRY(dlb_noise_bernoulli(m->ctx, l.mask, m->seq_w * l.units, l.dropout_value, seed, stream, step, 0));
+        break;
+      case DLB_DROPOUT_UOUT: {
+        const size_t w = uout_width(l);
+        DLB_TRY(ensure_uout(m, l, rows));
+        DLB_TRY(dlb_noise_uniform(m->ctx, l.uout, rows * w, -l.dropout_value, l.dropout_value, seed, stream + 1,
+                                  step, first_row * w));
+        break;
+      }
+      case DLB_DROPOUT_SHAKEDROP:
+        // dropout_value is the probability that a row is perturbed; forward
+        // factors from U(-1, 1), backward factors from U(0, 1)
+        // (fwp_mp.cpp L:3881-3888, bwp_mp.cpp ShakeDrop backward).
+        DLB_TRY(ensure_shakedrop(m, l, rows));
+        DLB_TRY(dlb_noise_bernoulli(m->ctx, l.sd_mask, rows, l.dropout_value, seed, stream, step, first_row));
+        DLB_TRY(dlb_noise_uniform(m->ctx, l.sd_fwd, rows * l.units, -1.f, 1.f, seed, stream + 1, step,
+                                  first_row * l.units));
+        DLB_TRY(dlb_noise_uniform(m->ctx, l.sd_bwd, rows * l.units, 0.f, 1.f, seed, stream + 2, step,
+                                  first_row * l.units));
+        break;
+      default:
+        break;
+    }
+  }
+  return DLB_OK;
 }
 
 dlb_status dlb_model_set_shakedrop_noise(dlb_model *m, size_t layer, const uint8_t *host_row_mask,
@@ -1179,18 +1243,7 @@ dlb_status dlb_model_set_shakedrop_noise(dlb_model *m, size_t layer, const uint8
   DLB_REQUIRE(l.type == DLB_LAYER_RESIDUAL && l.dropout == DLB_DROPOUT_SHAKEDROP,
               "set_shakedrop_noise: layer is not a residual layer with ShakeDrop");
   const size_t n = rows * l.units;
-  if (rows > l.sd_rows) {
-    if (l.sd_mask) DLB_TRY(dlb_free(m->ctx, l.sd_mask));
-    if (l.sd_fwd) DLB_TRY(dlb_free(m->ctx, l.sd_fwd));
-    if (l.sd_bwd) DLB_TRY(dlb_free(m->ctx, l.sd_bwd));
-    l.sd_mask = nullptr;
-    l.sd_fwd = l.sd_bwd = nullptr;
-    l.sd_rows = 0;
-    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_mask), rows));
-    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_fwd), n * sizeof(float)));
-    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_bwd), n * sizeof(float)));
-    l.sd_rows = rows;
-  }
+  DLB_TRY(ensure_shakedrop(m, l, rows));
   std::vector<uint8_t> flags(rows);
   for (size_t i = 0; i < rows; ++i) flags[i] = host_row_mask[i] ? 1 : 0;
   DLB_TRY(dlb_memcpy_h2d(m->ctx, l.sd_mask, flags.data(), rows));

@@ -146,6 +146,9 @@ SIGNATURES = {
     "dlb_model_train_step": (_i, [_vp, _sz, _vp, _vp, C.POINTER(_d)]),
     "dlb_model_train_step_device": (_i, [_vp, _sz, _vp, _vp]),
     "dlb_model_set_clip_gradient": (_i, [_vp, _i, _f]),
+    "dlb_noise_uniform": (_i, [_vp, _vp, _sz, _f, _f, _u64, C.c_uint32, C.c_uint32, _u64]),
+    "dlb_noise_bernoulli": (_i, [_vp, _vp, _sz, _f, _u64, C.c_uint32, C.c_uint32, _u64]),
+    "dlb_model_draw_noise": (_i, [_vp, _sz, _u64, C.c_uint32, _sz]),
     "dlb_model_stage_batch": (_i, [_vp, _sz, _vp, _vp]),
     "dlb_model_train_step_staged": (_i, [_vp, C.POINTER(_d)]),
     "dlb_model_get_layer_outputs": (_i, [_vp, _sz, _sz, _vp]),
@@ -538,6 +541,10 @@ class Model:
         check(self.L.dlb_model_train_step(self.h, batch, _ptr(X), _ptr(Y), C.byref(loss) if want_loss else None),
               "train_step")
         return loss.value
+
+    def draw_noise(self, batch, seed, step, first_row=0):
+        """Draws the next step's dropout masks, UOut and ShakeDrop noise on the device."""
+        check(self.L.dlb_model_draw_noise(self.h, batch, seed, step, first_row), "draw_noise")
 
     def set_clip_gradient(self, use, value):
         check(self.L.dlb_model_set_clip_gradient(self.h, int(bool(use)), float(value)), "set_clip_gradient")

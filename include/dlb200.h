@@ -551,6 +551,24 @@ dlb_status dlb_model_train_step_device(dlb_model *m, size_t rows, const float *X
  * batch i hides the copy under the kernels.  This is the mini-batch loop of
  * MiniBatch::train_mp (v1/data/dataset/minibatch.cpp L:286-323): train on the
  * batch, read its loss, update the weights, move to the next batch. */
+/* Noise drawn on the device instead of handed over by the host: a counter-based
+ * generator (Philox4x32-10, Salmon et al., SC'11) in which element i of a draw
+ * is a function of (seed, stream, step, first + i) alone.  dlb_noise_uniform
+ * writes lo + (hi - lo) u with u = 24 random bits / 2^24; dlb_noise_bernoulli
+ * writes 1 where u < p.  dlb_model_draw_noise fills, for the next step of
+ * `rows` rows, every layer's Bernoulli mask (one flag per unit, kept with the
+ * layer's probability), UOut draws U(-beta, beta) and ShakeDrop flags and
+ * factors; rows are numbered from first_row, the rank's first row in the whole
+ * batch, so that the draws do not depend on the sharding.  The reference draws
+ * the same distributions from per-thread std::mt19937 streams during the step
+ * (Model::Dropout_Bernoulli; fwp_mp.cpp L:4959-4985, L:4922-4957); its streams
+ * depend on the thread count, the host-array setters reproduce them. */
+dlb_status dlb_noise_uniform(dlb_ctx *ctx, float *out, size_t n, float lo, float hi, uint64_t seed,
+                             uint32_t stream, uint32_t step, uint64_t first);
+dlb_status dlb_noise_bernoulli(dlb_ctx *ctx, uint8_t *out, size_t n, float p, uint64_t seed,
+                               uint32_t stream, uint32_t step, uint64_t first);
+dlb_status dlb_model_draw_noise(dlb_model *m, size_t rows, uint64_t seed, uint32_t step,
+                                size_t first_row);
 /* Model::set_clip_gradient, both overloads (v1/ops/constraints/clip_gradient.cpp
  * L:30-73): whether update_weights clips, and the norm; the norm also sets the
  * default bound of IndRNN recurrent weights, clip(value, 2, 10)^(1/seq_w)
