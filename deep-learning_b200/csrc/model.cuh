@@ -1,0 +1,118 @@
+// The host-side Model's state: layers, hyperparameters and device buffers.
+// Shared by model.cu (construction and the step) and checkpoint.cu (the
+// reference's text checkpoint format).
+#pragma once
+
+#include <random>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+
+struct LayerRT {
+  int type = 0;
+  size_t units = 0;
+  int af = 0;            // 0 = not set / outside the supported set
+  int norm = DLB_NORM_NONE;
+  int dropout = DLB_DROPOUT_NONE;
+  float dropout_value = 0.f;
+  // Indices into the flat parameter vector.
+  size_t first_conn = 0, last_conn = 0, first_bias = 0, last_bias = 0, first_norm_unit = 0;
+  size_t fan_in = 0;
+  // IndRNN layer: its recurrent weights u[units] follow its W inside
+  // [first_conn, last_conn) (v1/learner/connections_prepare.cpp L:46-81).
+  size_t first_recurrent = 0;
+  // Residual blocks (the reference's layer list: a RESIDUAL layer of depth d
+  // followed by its d block layers, v1/learner/compile.cpp).
+  int group = 0;            // 1 = layer inside a residual block
+  size_t depth = 0;         // RESIDUAL: number of block layers
+  bool block_input = false; // first layer of a block: no activation in front
+  size_t norm_units = 0;    // normalised units: width, or fan-in for a block layer
+  // Device buffers (allocated by ensure_batch).  Stand-alone FC layer: Z sums,
+  // A output after activation and dropout, delta error w.r.t. Z.  Block layer:
+  // IN its GEMM input (activation of the previous block layer's sums), A its
+  // sums, delta error w.r.t. the sums.  RESIDUAL layer: A = shortcut + block,
+  // delta = error of that output.
+  float *Z = nullptr, *A = nullptr, *A_lo = nullptr, *delta = nullptr, *delta_lo = nullptr;
+  float *IN = nullptr, *IN_lo = nullptr;
+  float *stats = nullptr;  // mean | sigma | mean_avg | sigma_avg | r | d, each [T*norm_units]
+  uint8_t *mask = nullptr; // [T*units]
+  float *uout = nullptr;   // UOut draws of U(-beta, beta), [uout_rows, units (fan-in for a block layer)]
+  size_t uout_rows = 0;
+  double *fwd_sums = nullptr, *bwd_sums = nullptr;
+  // ShakeDrop of a RESIDUAL layer: row flags and the forward / backward draws.
+  uint8_t *sd_mask = nullptr;
+  float *sd_fwd = nullptr, *sd_bwd = nullptr;
+  size_t sd_rows = 0;
+};
+
+struct HParams {
+  float adam_learning_rate = 0.001f, adam_beta1 = 0.9f, adam_beta2 = 0.999f,
+        adam_previous_beta2 = 0.f, adam_epsilon = 1e-8f, adam_gamma = 0.1f,
+        learning_rate_final = 0.1f, learning_gamma = 1e-3f, weight_decay = 0.f,
+        optimizer_time_step = 0.f, epoch_time_step = 1.f;
+  bool use_adam_bias_correction = true;
+  // Gradient descent (model.hpp L:3020-3022, L:2839).
+  float learning_rate = 0.01f, learning_momentum = 0.9f;
+  bool use_nesterov = false;
+  // Model defaults, v1/learner/model.hpp L:3045-3048.
+  float normalization_momentum_average = 0.999f, normalization_epsilon = 1e-5f,
+        brn_r_max = 1.f, brn_d_max = 0.f;
+};
+
+
+struct dlb_model {
+  dlb_ctx *ctx = nullptr;
+  std::vector<LayerRT> layers;
+  size_t seq_w = 1, n_time_delay = 0;
+  int model_type = DLB_MODEL_FEEDFORWARD;
+  int loss = 0, optimizer = 0;
+  HParams hp;
+  size_t total_weights = 0, total_bias = 0, total_norm_units = 0, total_parameters = 0;
+  bool any_norm = false;
+  size_t max_batch = 0, alloc_rows = 0, global_rows = 0;
+  unsigned weight_seed = 5489u;
+  std::mt19937 weight_gen;
+  // Flat device vectors.
+  float *params = nullptr, *params_lo = nullptr, *grads = nullptr, *m1 = nullptr, *m2 = nullptr,
+        *m2hat = nullptr;
+  float *input = nullptr, *input_lo = nullptr, *target = nullptr;
+  // Time-stepped models: the caller's rows [rows, T*n] as they arrive, before
+  // the reorder to [T, rows, n].
+  float *input_rows = nullptr, *target_rows = nullptr;
+  float *wd_mask = nullptr;  // [P]: 1 where weight decay applies
+  // Model::use_clip_gradient / clip_gradient (model.hpp defaults: off, 1).
+  bool use_clip_gradient = false;
+  float clip_gradient = 1.f;
+  // Evaluation (Driver::evalt): propagation state, accuracy function and its
+  // counter; r = 1 and d = 0 for the normalization by running averages.
+  int propagation = DLB_PROPAGATION_TRAINING;
+  int accu_fn = DLB_ACCU_DISTANCE;   // v1/learner/model.hpp L:157
+  float accu_var = 0.49f;            // L:3019
+  double *accu_sum = nullptr;
+  float *ones = nullptr, *zeros = nullptr;
+  size_t const_units = 0;
+  float *stage_x = nullptr, *stage_y = nullptr;  // pinned
+  size_t stage_x_elems = 0, stage_y_elems = 0;
+  // Batches copied ahead of the step that uses them: two device slots filled
+  // on a stream of their own, so that the copy of batch i+1 runs under the
+  // kernels of batch i.
+  struct Ahead {
+    float *x = nullptr, *y = nullptr;
+    size_t x_elems = 0, y_elems = 0, rows = 0;
+    cudaEvent_t ready = nullptr, consumed = nullptr;
+    bool in_use = false;  // `consumed` has been recorded at least once
+  } ahead[2];
+  cudaStream_t copy_stream = nullptr;
+  size_t ahead_head = 0, ahead_tail = 0;  // staged so far, consumed so far
+  double *loss_sum = nullptr;
+  size_t loss_rows = 0;  // rows accumulated since reset_loss
+  bool params_lo_valid = false;
+  // Inside train_step the step is known to be a single chunk, so each layer's
+  // weight gradient is all-reduced as soon as its GEMM has been enqueued.
+  bool overlap_grad_allreduce = false;
+  // The gradient vector is all zero (fresh, or cleared by the last update), so
+  // the weight-gradient products may overwrite instead of accumulate.
+  bool grads_clean = false;
+};

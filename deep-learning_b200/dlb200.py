@@ -146,6 +146,9 @@ SIGNATURES = {
     "dlb_model_train_step": (_i, [_vp, _sz, _vp, _vp, C.POINTER(_d)]),
     "dlb_model_train_step_device": (_i, [_vp, _sz, _vp, _vp]),
     "dlb_model_set_clip_gradient": (_i, [_vp, _i, _f]),
+    "dlb_model_save_params": (_i, [_vp, _cp]),
+    "dlb_model_save_spec_params": (_i, [_vp, _cp]),
+    "dlb_model_load": (_i, [_vp, _cp, _cp]),
     "dlb_noise_uniform": (_i, [_vp, _vp, _sz, _f, _f, _u64, C.c_uint32, C.c_uint32, _u64]),
     "dlb_noise_bernoulli": (_i, [_vp, _vp, _sz, _f, _u64, C.c_uint32, C.c_uint32, _u64]),
     "dlb_model_draw_noise": (_i, [_vp, _sz, _u64, C.c_uint32, _sz]),
@@ -545,6 +548,15 @@ class Model:
     def draw_noise(self, batch, seed, step, first_row=0):
         """Draws the next step's dropout masks, UOut and ShakeDrop noise on the device."""
         check(self.L.dlb_model_draw_noise(self.h, batch, seed, step, first_row), "draw_noise")
+
+    def save(self, path_params, path_spec):
+        """Model::save_params + Model::save_spec_params."""
+        check(self.L.dlb_model_save_params(self.h, path_params.encode()), "save_params")
+        check(self.L.dlb_model_save_spec_params(self.h, path_spec.encode()), "save_spec_params")
+
+    def load(self, path_params, path_spec):
+        """Model::load into a model that has not been compiled."""
+        check(self.L.dlb_model_load(self.h, path_params.encode(), path_spec.encode()), "load")
 
     def set_clip_gradient(self, use, value):
         check(self.L.dlb_model_set_clip_gradient(self.h, int(bool(use)), float(value)), "set_clip_gradient")

@@ -569,6 +569,19 @@ dlb_status dlb_noise_bernoulli(dlb_ctx *ctx, uint8_t *out, size_t n, float p, ui
                                uint32_t stream, uint32_t step, uint64_t first);
 dlb_status dlb_model_draw_noise(dlb_model *m, size_t rows, uint64_t seed, uint32_t step,
                                 size_t first_row);
+/* The reference's on-disk format.  dlb_model_save_params writes what
+ * Model::save_params writes (dimensions, layers, normalization state and every
+ * weight as text; v1/learner/save.cpp L:188-520) and dlb_model_save_spec_params
+ * what Model::save_spec_params writes (hyperparameters; L:34-186; values of
+ * options outside the supported path as the reference's defaults), so that the
+ * reference's Model::load reads a model trained here.  dlb_model_load reads the
+ * pair into a model that has not been compiled yet (Model::load,
+ * v1/learner/load.cpp L:1243-); a file that uses a layer type, regularizer or
+ * option outside the supported path is refused.  Optimizer moments are not
+ * part of the reference's format and are not written. */
+dlb_status dlb_model_save_params(dlb_model *m, const char *path);
+dlb_status dlb_model_save_spec_params(dlb_model *m, const char *path);
+dlb_status dlb_model_load(dlb_model *m, const char *path_params, const char *path_spec);
 /* Model::set_clip_gradient, both overloads (v1/ops/constraints/clip_gradient.cpp
  * L:30-73): whether update_weights clips, and the norm; the norm also sets the
  * default bound of IndRNN recurrent weights, clip(value, 2, 10)^(1/seq_w)

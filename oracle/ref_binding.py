@@ -54,6 +54,8 @@ def lib():
         "ref_set_mp": (i, [vp, i]),
         "ref_set_weight_decay": (i, [vp, C.c_double]),
         "ref_set_clip_gradient": (i, [vp, i, C.c_double]),
+        "ref_save": (i, [vp, cp, cp]),
+        "ref_load": (i, [vp, cp, cp]),
         "ref_set_propagation": (i, [vp, i]),
         "ref_set_accu_fn": (i, [vp, i]),
         "ref_set_accu_var": (i, [vp, C.c_double]),
@@ -190,6 +192,12 @@ class RefModel:
 
     def set_weight_decay(self, value):
         _ck(self.L.ref_set_weight_decay(self.h, float(value)), "set_weight_decay")
+
+    def save(self, path_params, path_spec):
+        _ck(self.L.ref_save(self.h, path_params.encode(), path_spec.encode()), "save")
+
+    def load(self, path_params, path_spec):
+        _ck(self.L.ref_load(self.h, path_params.encode(), path_spec.encode()), "load")
 
     def set_clip_gradient(self, use, value):
         _ck(self.L.ref_set_clip_gradient(self.h, int(bool(use)), float(value)), "set_clip_gradient")

@@ -203,6 +203,19 @@ int ref_set_clip_gradient(ref_model m, int use, double value) {
   H(m)->model.set_clip_gradient(use != 0);
   return H(m)->model.set_clip_gradient(static_cast<real>(value)) ? 0 : -1;
 }
+int ref_save(ref_model m, const char *path_params, const char *path_spec) {
+  std::string a(path_params), b(path_spec);
+  Model &M = H(m)->model;
+  if (!M.save_params(std::wstring(a.begin(), a.end()))) return -1;
+  return M.save_spec_params(std::wstring(b.begin(), b.end())) ? 0 : -2;
+}
+int ref_load(ref_model m, const char *path_params, const char *path_spec) {
+  std::string a(path_params), b(path_spec);
+  return H(m)->model.load(std::wstring(a.begin(), a.end()), std::wstring(b.begin(), b.end()),
+                          static_cast<size_t>(8) << 30)
+             ? 0
+             : -1;
+}
 int ref_set_seq_w(ref_model m, size_t time_delays) {
   return H(m)->model.set_seq_w(time_delays) ? 0 : -1;
 }

@@ -47,6 +47,9 @@ int ref_set_max_batch_size(ref_model m, size_t b);
 int ref_set_mp(ref_model m, int use_mp);
 int ref_set_weight_decay(ref_model m, double value);
 int ref_set_clip_gradient(ref_model m, int use, double value);
+/* Model::save_params + save_spec_params, Model::load (v1/learner/save.cpp, load.cpp). */
+int ref_save(ref_model m, const char *path_params, const char *path_spec);
+int ref_load(ref_model m, const char *path_params, const char *path_spec);
 int ref_set_propagation(ref_model m, int state);
 int ref_set_accu_fn(ref_model m, int fn);
 int ref_set_accu_var(ref_model m, double v);

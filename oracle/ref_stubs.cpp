@@ -22,10 +22,17 @@
 }
 
 namespace DL::File {
-bool create_temp_file(std::wstring const &) { off_path("File::create_temp_file"); }
-bool delete_temp_file(std::wstring const &) { off_path("File::delete_temp_file"); }
-bool recover_temp_file(std::wstring const &) { off_path("File::recover_temp_file"); }
-bool path_exist(std::wstring const &) { off_path("File::path_exist"); }
+bool create_temp_file(std::wstring const &) { return true; }
+bool delete_temp_file(std::wstring const &) { return true; }
+bool recover_temp_file(std::wstring const &) { return true; }
+bool path_exist(std::wstring const &path) {
+  std::string narrow(path.begin(), path.end());
+  if (FILE *f = std::fopen(narrow.c_str(), "rb")) {
+    std::fclose(f);
+    return true;
+  }
+  return false;
+}
 
 template <typename T>
 bool read_stream_block_n_parse(wchar_t *&, wchar_t *&, size_t &, size_t const,

@@ -1,0 +1,98 @@
+"""The reference's text checkpoint format: files written by the library are the
+bytes the compiled reference writes for the same state, the reference's loader
+reads them, and the library reads the reference's."""
+import os
+
+import numpy as np
+import pytest
+
+import configs
+import dlb200
+import ref_binding
+import util
+from enums import LOSS_FN
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")]
+
+CASES = {
+    "brn_mlp": lambda: configs.deep_brn_mlp(6, 8, 2, 4, 8),
+    "softmax_mlp": lambda: configs.mlp_softmax(7, 5, 3, 8),
+    "residual": lambda: configs.residual_mlp(6, 2, 4, 8),
+    "indrnn": lambda: configs.indrnn_stack(n_in=3, hidden=5, depth=2, n_out=2, seq_w=3, batch=6),
+}
+
+
+def _trained(gpu_ctx, cfg):
+    mod = util.build(dlb200.Model(gpu_ctx), cfg, seed=3)
+    if configs.shakedrop_layers(cfg):
+        util.trace_noisy(mod, cfg, steps=2)
+    else:
+        util.trace(mod, cfg, steps=2)
+    return mod
+
+
+@pytest.mark.parametrize("case", sorted(CASES))
+def test_files_are_the_reference_s_bytes_and_load_both_ways(gpu_ctx, case, tmp_path):
+    cfg = CASES[case]()
+    B, last = cfg["batch"], len(cfg["layers"]) - 1
+    mod = _trained(gpu_ctx, cfg)
+    # use_mp is the reference's threading switch; the library always writes 1.
+    ref = util.build(ref_binding.RefModel(), dict(cfg, mp=True), seed=0)
+    util.copy_trained_state(mod, ref, cfg)
+    for model in (mod, ref):
+        model.set_accu_fn(1 if cfg["loss"] == LOSS_FN.CROSS_ENTROPY else 3)
+    ours = (str(tmp_path / "ours.net"), str(tmp_path / "ours.nn"))
+    theirs = (str(tmp_path / "theirs.net"), str(tmp_path / "theirs.nn"))
+    mod.save(*ours)
+    ref.save(*theirs)
+    for a, b in zip(ours, theirs):
+        got, want = open(a, "rb").read(), open(b, "rb").read()
+        if got != want:
+            ga, wa = got.split(b"\r\n"), want.split(b"\r\n")
+            first = next((i for i, (x, y) in enumerate(zip(ga, wa)) if x != y), min(len(ga), len(wa)))
+            raise AssertionError(f"{os.path.basename(a)} line {first + 1}: {ga[first:first + 1]} != {wa[first:first + 1]}")
+
+    # The reference reads our files.
+    X, _ = configs.synthetic_batch(dict(cfg, data_seed=5))
+    back = ref_binding.RefModel()
+    back.load(*ours)
+    back.set_max_batch_size(B)
+    back.set_mp(True)
+    back.train_begin(B)
+    back.set_propagation(0)
+    back.forward_pass(B, X)
+    mod.set_propagation(0)
+    mod.forward_pass(B, X)
+    assert util.rel_l2(mod.get_layer_outputs(last, B).reshape(-1), back.get_layer_outputs(last, B).reshape(-1)) <= 1e-5
+    # Weights and biases come back bit for bit (16 significant digits carry a
+    # float); the scale / shift slots of layers without normalization are not in the file.
+    nw = mod.size("total_weights") + mod.size("total_bias")
+    assert np.array_equal(back.get_array("parameters")[:nw], mod.get_array("parameters")[:nw])
+
+    # We read the reference's files.
+    again = dlb200.Model(gpu_ctx)
+    again.load(*theirs)
+    assert np.array_equal(again.get_array("parameters"), mod.get_array("parameters"))
+    again.train_begin(B)
+    again.set_propagation(0)
+    again.forward_pass(B, X)
+    assert np.array_equal(again.get_layer_outputs(last, B), mod.get_layer_outputs(last, B))
+    rewritten = (str(tmp_path / "again.net"), str(tmp_path / "again.nn"))
+    again.save(*rewritten)
+    for a, b in zip(rewritten, theirs):
+        assert open(a, "rb").read() == open(b, "rb").read()
+    assert gpu_ctx.sync() == 0
+
+
+def test_a_file_outside_the_supported_path_is_refused(gpu_ctx, tmp_path):
+    cfg = CASES["brn_mlp"]()
+    mod = _trained(gpu_ctx, cfg)
+    files = (str(tmp_path / "a.net"), str(tmp_path / "a.nn"))
+    mod.save(*files)
+    text = open(files[0], "rb").read().replace(b"  Hidden layer 1:\r\n    type_layer 3", b"  Hidden layer 1:\r\n    type_layer 6")
+    open(files[0], "wb").write(text)
+    with pytest.raises(dlb200.DlbError, match="outside the supported path"):
+        dlb200.Model(gpu_ctx).load(*files)
+    with pytest.raises(dlb200.DlbError):
+        dlb200.Model(gpu_ctx).load(str(tmp_path / "missing.net"), files[1])
