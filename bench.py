@@ -77,7 +77,12 @@ def gemm_traffic_per_launch():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons while the timed region runs.  The
+    sampler is started before the warm-up steps (nvidia-smi takes a few hundred
+    milliseconds to deliver its first line, longer than a short timed region);
+    `mark()` notes where the timed region begins.  Samples from the mark on are
+    reported; with fewer than three of them, the warm-up steps' samples (the same
+    kernels under the same load) are included and `window` says so."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
@@ -86,12 +91,19 @@ class ClockSampler:
         self.device = device
         self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         self.proc = None
+        self.offset = 0
+
+    def mark(self):
+        try:
+            self.offset = os.path.getsize(self.file.name)
+        except OSError:
+            self.offset = 0
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+                 "-lms", "25"], stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
@@ -105,25 +117,35 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         self.file.flush()
-        self.file.seek(0)
-        sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.file:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 8:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[4:8]):
-                if val == "Active":
-                    reasons.add(name)
+
+        def parse(offset):
+            self.file.seek(offset)
+            sm, mx, reasons = [], [], set()
+            for line in self.file:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 8:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[4:8]):
+                    if val == "Active":
+                        reasons.add(name)
+            return sm, mx, reasons
+
+        sm, mx, reasons = parse(self.offset)
+        window = "timed region and end-to-end region"
+        if len(sm) < 3:
+            sm, mx, reasons = parse(0)
+            window = "warm-up steps, timed region and end-to-end region"
         self.file.close()
         os.unlink(self.file.name)
         if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm),
+                       window=window)
         return out
 
 
@@ -260,6 +282,9 @@ def run_ours(args, rank, local_rank, world):
         # path uses the library's own NCCL communicator.
         dist.init_process_group("gloo", rank=rank, world_size=world)
     ctx = dlb200.Context(local_rank)
+    sampler = ClockSampler(local_rank)   # started here: the model set-up below covers nvidia-smi's start-up
+    if rank == 0:
+        sampler.start()
     if world > 1:
         box = [ctx.unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
@@ -300,9 +325,8 @@ def run_ours(args, rank, local_rank, world):
     for _ in range(max(args.warmup, 3)):
         model.train_step_device(rows, Xd, Yd)
     barrier()
-    sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()
+        sampler.mark()
     ctx.gemm_profile(True)
     ctx.gemm_profile_read()
     launches0 = ctx.launch_count()

@@ -80,28 +80,42 @@ __global__ void reduce_partials_kernel(const double *partials, int chunks, int t
   out[i] = t;
 }
 
-// Chunking of the rows: a few waves of blocks over the SMs, chunks of at least
-// 64 rows.  Shared by the launcher and by callers that place their final sums
-// behind the partials in the same scratch request.
-static void column_reduce_plan(dlb_ctx *ctx, int rows, int n, int *chunks, int *rows_per_chunk) {
+// Chunking of the rows: one wave of blocks over the SMs, `per_sm` blocks on each
+// (what the kernel's registers allow, at most CR_MAX_PER_SM; a grid larger than
+// one wave leaves a partial second wave that costs a whole one), chunks of at
+// least 64 rows.
+constexpr int CR_MAX_PER_SM = 4;
+static void column_reduce_plan(dlb_ctx *ctx, int rows, int n, int per_sm, int *chunks, int *rows_per_chunk) {
   const int col_blocks = ceil_div(n, CR_COLS);
-  int c = ceil_div(ctx->sm_count * 4, col_blocks);
+  int c = per_sm == CR_MAX_PER_SM ? ceil_div(ctx->sm_count * per_sm, col_blocks)
+                                  : max(1, ctx->sm_count * per_sm / col_blocks);
   c = max(1, min(c, ceil_div(rows, 64)));
   *rows_per_chunk = ceil_div(ceil_div(rows, c), CR_LANES_Y) * CR_LANES_Y;
   *chunks = ceil_div(rows, *rows_per_chunk);
 }
 
+// Room for the partials of any kernel of the family (callers place their final
+// sums behind them in the same scratch request).
 static size_t column_reduce_partial_bytes(dlb_ctx *ctx, int nsum, int rows, int n) {
   int chunks, rpc;
-  column_reduce_plan(ctx, rows, n, &chunks, &rpc);
+  column_reduce_plan(ctx, rows, n, CR_MAX_PER_SM, &chunks, &rpc);
   return align_up((size_t)chunks * nsum * n * sizeof(double), 256);
 }
 
 template <int NSUM, class Op>
 static dlb_status column_reduce(dlb_ctx *ctx, Op op, int rows, int n, double *out) {
   const int col_blocks = ceil_div(n, CR_COLS);
+  static const int per_sm = [] {
+    int blocks = CR_MAX_PER_SM;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, column_reduce_kernel<NSUM, Op>,
+                                                      CR_LANES_X * CR_LANES_Y, 0) != cudaSuccess) {
+      cudaGetLastError();
+      blocks = CR_MAX_PER_SM;
+    }
+    return max(1, min(blocks, CR_MAX_PER_SM));
+  }();
   int chunks, rows_per_chunk;
-  column_reduce_plan(ctx, rows, n, &chunks, &rows_per_chunk);
+  column_reduce_plan(ctx, rows, n, per_sm, &chunks, &rows_per_chunk);
   void *scr = nullptr;
   DLB_TRY(scratch(ctx, column_reduce_partial_bytes(ctx, NSUM, rows, n), &scr));
   double *partials = static_cast<double *>(scr);
