@@ -21,6 +21,11 @@ namespace dlb {
 constexpr int CR_LANES_X = 32;
 constexpr int CR_LANES_Y = 8;
 constexpr int CR_COLS = CR_LANES_X * 4;
+// Most blocks per SM a plan counts on.  Capping the kernels' registers so that
+// every one of them reaches it was measured and is slower (the backward
+// reduction: 74 us at 64 registers with spills against 55 us at 71 registers
+// and three blocks per SM).
+constexpr int CR_MAX_PER_SM = 4;
 
 template <int NSUM, class Op>
 __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
@@ -84,7 +89,6 @@ __global__ void reduce_partials_kernel(const double *partials, int chunks, int t
 // (what the kernel's registers allow, at most CR_MAX_PER_SM; a grid larger than
 // one wave leaves a partial second wave that costs a whole one), chunks of at
 // least 64 rows.
-constexpr int CR_MAX_PER_SM = 4;
 static void column_reduce_plan(dlb_ctx *ctx, int rows, int n, int per_sm, int *chunks, int *rows_per_chunk) {
   const int col_blocks = ceil_div(n, CR_COLS);
   int c = per_sm == CR_MAX_PER_SM ? ceil_div(ctx->sm_count * per_sm, col_blocks)
