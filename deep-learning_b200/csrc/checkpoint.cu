@@ -526,7 +526,7 @@ dlb_status dlb_model_save_spec_params(dlb_model *m, const char *path) {
   kv("regularization__l2", "0");
   kv("regularization__srip", "0");
   kv("weight_decay", num(p.weight_decay));
-  kv("use_normalized_weight_decay", "1");
+  kv("use_normalized_weight_decay", num((int)p.use_normalized_weight_decay));
   end("REGULARIZATION PARAMETERS");
   section("NORMALIZATION PARAMETERS");
   kv("normalization_momentum_average", num(p.normalization_momentum_average));
@@ -734,11 +734,7 @@ dlb_status dlb_model_load(dlb_model *m, const char *path_params, const char *pat
   }
   DLB_TRY(s.real("weight_decay", &d));
   DLB_TRY(dlb_model_set_weight_decay(m, (float)d));
-  DLB_TRY(s.real("use_normalized_weight_decay", &d));
-  if (d == 0.0) {
-    set_error("load: weight decay without normalisation is outside the supported path");
-    return DLB_ERR_UNSUPPORTED;
-  }
+  DLB_TRY(hparam("use_normalized_weight_decay", "use_normalized_weight_decay"));
   DLB_TRY(s.expect("|END| REGULARIZATION PARAMETERS |END|"));
   DLB_TRY(s.expect("|===| NORMALIZATION PARAMETERS |===|"));
   DLB_TRY(s.real("normalization_momentum_average", &d));

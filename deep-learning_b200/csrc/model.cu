@@ -848,6 +848,7 @@ dlb_status dlb_model_set_hparam(dlb_model *m, const char *name, double value) {
 #undef X
   if (n == "use_adam_bias_correction") { m->hp.use_adam_bias_correction = value != 0.0; return DLB_OK; }
   if (n == "use_nesterov") { m->hp.use_nesterov = value != 0.0; return DLB_OK; }
+  if (n == "use_normalized_weight_decay") { m->hp.use_normalized_weight_decay = value != 0.0; return DLB_OK; }
   if (n == "pct_threads") return DLB_OK;  // CPU threading knob of the reference; nothing to set
   set_error("set_hparam: unknown field %s", name);
   return DLB_ERR_INVALID;
@@ -861,6 +862,7 @@ double dlb_model_get_hparam(dlb_model *m, const char *name) {
 #undef X
   if (n == "use_adam_bias_correction") return m->hp.use_adam_bias_correction;
   if (n == "use_nesterov") return m->hp.use_nesterov;
+  if (n == "use_normalized_weight_decay") return m->hp.use_normalized_weight_decay;
   return -1.0;
 }
 
@@ -1433,7 +1435,9 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
       DLB_TRY(dlb_memcpy_h2d(m->ctx, m->wd_mask, mask.data(), mask.size() * sizeof(float)));
       DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
     }
-    wd = m->hp.weight_decay * sqrtf((float)rows / ((float)training_size * m->hp.epoch_time_step));
+    wd = m->hp.use_normalized_weight_decay
+             ? m->hp.weight_decay * sqrtf((float)rows / ((float)training_size * m->hp.epoch_time_step))
+             : m->hp.weight_decay;
   }
   float hyper[8] = {m->hp.adam_learning_rate, m->hp.adam_beta1, m->hp.adam_beta2,
                     m->hp.adam_epsilon, m->hp.adam_gamma, m->hp.learning_rate_final,

@@ -53,6 +53,7 @@ struct HParams {
         learning_rate_final = 0.1f, learning_gamma = 1e-3f, weight_decay = 0.f,
         optimizer_time_step = 0.f, epoch_time_step = 1.f;
   bool use_adam_bias_correction = true;
+  bool use_normalized_weight_decay = true;  // model.hpp L:2840
   // Gradient descent (model.hpp L:3020-3022, L:2839).
   float learning_rate = 0.01f, learning_momentum = 0.9f;
   bool use_nesterov = false;

@@ -175,6 +175,10 @@ int ref_set_hparam(ref_model m, const char *name, double value) {
     M.use_nesterov = value != 0.0;
     return 0;
   }
+  if (n == "use_normalized_weight_decay") {
+    M.use_normalized_weight_decay = value != 0.0;
+    return 0;
+  }
   if (n == "pct_threads") return M.Set__Maximum_Thread_Usage(value) ? 0 : -1;
   return -1;
 }

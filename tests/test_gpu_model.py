@@ -191,6 +191,30 @@ def test_weight_decay(gpu_ctx, optimizer):
         mod.set_weight_decay(1.5)
 
 
+def test_weight_decay_without_normalisation(gpu_ctx):
+    """use_normalized_weight_decay = false: the decay enters as it is, whatever
+    the ratio of batch to training size."""
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96, optimizer=OPTIMIZER.ADAM)
+    cfg = dict(cfg, hparams=dict(cfg["hparams"], use_normalized_weight_decay=0))
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    B = cfg["batch"]
+    p0, seed = util.kink_free_parameters(cfg, fc_step.OracleModel, X, masks, scale=1.0 / np.sqrt(128))
+    out = []
+    for model in (util.build(fc_step.OracleModel(), cfg, params=p0), gpu_model(gpu_ctx, cfg, p0)):
+        model.set_weight_decay(0.05)
+        model.train_begin(B)
+        for li, mk in masks.items():
+            model.set_dropout_mask(li, mk)
+        model.reset_loss()
+        model.forward_pass(B, X); model.compute_error(B, Y); model.backward_pass(B)
+        model.update_derivatives(B); model.merge_derivatives(); model.update_weights(B, 16 * B)
+        out.append(model.get_array("parameters"))
+    assert gpu_ctx.sync() == 0
+    assert util.rel_l2(out[1], out[0]) <= TOL_1
+    assert util.rel_l2(out[1] - p0, out[0] - p0) <= 1e-3
+
+
 def test_plain_batch_normalization(gpu_ctx):
     """LAYER_NORM::BATCH_NORMALIZATION: r = 1, d = 0 whatever the model's maxima,
     against the CPU restatement (itself pinned to the compiled reference)."""

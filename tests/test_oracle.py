@@ -97,6 +97,24 @@ def test_weight_decay_matches_compiled_reference(optimizer):
         assert l2 <= TOL_L2, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
     plain = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, steps=4)
     assert util.rel_l2(plain["params_last"], want["params_last"]) > 1e-4   # the decay is not a no-op
+    # The un-normalised form, use_normalized_weight_decay = false.  training_size is
+    # 4 batches here so that the two forms differ.
+    raw = dict(cfg, hparams=dict(cfg["hparams"], use_normalized_weight_decay=0))
+    out = []
+    for model in (util.build(ref_binding.RefModel(), raw, params=p0), util.build(fc_step.OracleModel(), raw, params=p0),
+                  util.build(fc_step.OracleModel(), cfg, params=p0)):
+        model.set_weight_decay(0.01)
+        B = cfg["batch"]
+        X, Y = configs.synthetic_batch(cfg)
+        model.train_begin(B)
+        for li, mk in configs.dropout_masks(cfg).items():
+            model.set_dropout_mask(li, mk)
+        model.reset_loss()
+        model.forward_pass(B, X); model.compute_error(B, Y); model.backward_pass(B)
+        model.update_derivatives(B); model.merge_derivatives(); model.update_weights(B, 4 * B)
+        out.append(model.get_array("parameters"))
+    assert util.rel_l2(out[1], out[0]) <= TOL_L2
+    assert util.rel_l2(out[2] - p0, out[0] - p0) > 1e-3
 
 
 @pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
