@@ -163,6 +163,9 @@ bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o);
 void planes_forget(dlb_ctx *ctx, uintptr_t base, size_t bytes);
 // max |x| into slot[2] and the fp16 planes of s x, s = 2^(14 - floor(log2 max)).
 dlb_status split_f16(dlb_ctx *ctx, const float *x, size_t n, uint16_t *hi, uint16_t *lo, float *slot);
+dlb_status optimizer_step_amax(dlb_ctx *ctx, int rule, const dlb_optimizer_scalars *s, float *p, float *g,
+                               float *first, float *second, float *second_hat, const float *wd_mask, size_t n,
+                               unsigned *amax);
 dlb_status planes_begin(dlb_ctx *ctx, const float *x, float *planes, size_t n, float **slot_out);
 dlb_status planes_finish(dlb_ctx *ctx, const float *x, float *planes, size_t n, float *slot);
 constexpr int SCALE_SLOTS = 8192;

@@ -1453,8 +1453,39 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
   DLB_TRY(dlb_optimizer_prepare(m->optimizer, hyper, &m->hp.optimizer_time_step,
                                 &m->hp.adam_previous_beta2, &k));
   k.weight_decay = wd;
-  DLB_TRY(dlb_optimizer_step(m->ctx, m->optimizer, &k, m->params, m->grads, m->m1, m->m2, m->m2hat,
-                             wd != 0.f ? m->wd_mask : nullptr, m->total_parameters));
+  // One pass per weight matrix where the products run on fp16 planes: the pass
+  // leaves the matrix's largest |w| in the scale slot of its plane buffer and
+  // the split follows at once, while the matrix is still partly in L2; the
+  // next forward pass then finds the planes ready.  Everything between and
+  // after the matrices (recurrent weights, biases, scales, shifts) goes in
+  // passes of its own.
+  bool fused = m->ctx->gemm_kind == DLB_GEMM_F16X3 && m->params_lo != nullptr;
+  for (size_t i = 1; fused && i < m->layers.size(); ++i) {
+    const LayerRT &l = m->layers[i];
+    if (l.type != DLB_LAYER_RESIDUAL && ((l.first_conn | (l.units * l.fan_in) | l.last_conn) & 3)) fused = false;
+  }
+  auto segment = [&](size_t at, size_t n, unsigned *amax) -> dlb_status {
+    if (n == 0) return DLB_OK;
+    return optimizer_step_amax(m->ctx, m->optimizer, &k, m->params + at, m->grads + at, m->m1 + at, m->m2 + at,
+                               m->m2hat ? m->m2hat + at : nullptr, wd != 0.f ? m->wd_mask + at : nullptr, n, amax);
+  };
+  if (fused) {
+    size_t at = 0;
+    for (size_t i = 1; i < m->layers.size(); ++i) {
+      const LayerRT &l = m->layers[i];
+      if (l.type == DLB_LAYER_RESIDUAL) continue;
+      const size_t nw = l.units * l.fan_in;
+      DLB_TRY(segment(at, l.first_conn - at, nullptr));
+      float *slot = nullptr;
+      DLB_TRY(planes_begin(m->ctx, m->params + l.first_conn, m->params_lo + l.first_conn, nw, &slot));
+      DLB_TRY(segment(l.first_conn, nw, reinterpret_cast<unsigned *>(slot) + 2));
+      DLB_TRY(planes_finish(m->ctx, m->params + l.first_conn, m->params_lo + l.first_conn, nw, slot));
+      at = l.first_conn + nw;
+    }
+    DLB_TRY(segment(at, m->total_parameters - at, nullptr));
+  } else {
+    DLB_TRY(segment(0, m->total_parameters, nullptr));
+  }
   // Recurrent weights of every IndRNN layer back into +-mag^(1/T), mag =
   // clip(clip_gradient, 2, 10) = 2 with the reference's default clip_gradient of
   // 1; every activation of the supported set is in a class that takes this
@@ -1464,7 +1495,7 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
     if (is_indrnn(l))
       DLB_TRY(dlb_indrnn_clamp(m->ctx, m->params + l.first_recurrent, (int)l.units, -bound, bound));
   m->grads_clean = true;  // the update kernel clears every gradient it consumes
-  m->params_lo_valid = false;
+  m->params_lo_valid = fused;
   return DLB_OK;
 }
 

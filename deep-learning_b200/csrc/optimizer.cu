@@ -69,7 +69,8 @@ template <int RULE, bool WD>
 __global__ void __launch_bounds__(256)
     optimizer_kernel(dlb_optimizer_scalars k, float *__restrict__ p, float *__restrict__ g,
                      float *__restrict__ m, float *__restrict__ v, float *__restrict__ vh,
-                     const float *__restrict__ mask, size_t n) {
+                     const float *__restrict__ mask, size_t n, unsigned *amax) {
+  unsigned mx = 0;  // largest |p| written, for the fp16 split of a weight matrix
   constexpr bool HAT = (RULE == R_AMSGRAD || RULE == R_AMSBOUND);
   constexpr bool FIRST = RULE != R_GD;                                              // m is read and written
   constexpr bool SECOND = !(RULE == R_GD || RULE == R_GD_MOMENTUM || RULE == R_GD_NESTEROV);  // v likewise
@@ -90,6 +91,7 @@ __global__ void __launch_bounds__(256)
     update_one<RULE, WD>(s2, K.z, k);
     update_one<RULE, WD>(s3, K.w, k);
     reinterpret_cast<float4 *>(p)[i] = make_float4(s0.p, s1.p, s2.p, s3.p);
+    mx = max(max(mx, abs_bits(s0.p)), max(abs_bits(s1.p), max(abs_bits(s2.p), abs_bits(s3.p))));
     if (FIRST) reinterpret_cast<float4 *>(m)[i] = make_float4(s0.m, s1.m, s2.m, s3.m);
     if (SECOND) reinterpret_cast<float4 *>(v)[i] = make_float4(s0.v, s1.v, s2.v, s3.v);
     if (HAT) reinterpret_cast<float4 *>(vh)[i] = make_float4(s0.vh, s1.vh, s2.vh, s3.vh);
@@ -100,23 +102,26 @@ __global__ void __launch_bounds__(256)
     OptState s{p[i], g[i], FIRST ? m[i] : 0.f, SECOND ? v[i] : 0.f, HAT ? vh[i] : 0.f};
     update_one<RULE, WD>(s, WD ? mask[i] : 0.f, k);
     p[i] = s.p; g[i] = 0.f;
+    mx = max(mx, abs_bits(s.p));
     if (FIRST) m[i] = s.m;
     if (SECOND) v[i] = s.v;
     if (HAT) vh[i] = s.vh;
   }
+  amax_commit(amax, mx);
 }
 
 template <int RULE>
 static dlb_status launch_rule(dlb_ctx *ctx, const dlb_optimizer_scalars &k, float *p, float *g,
-                              float *m, float *v, float *vh, const float *mask, size_t n) {
+                              float *m, float *v, float *vh, const float *mask, size_t n,
+                              unsigned *amax) {
   // Enough blocks to keep every SM's memory pipeline full; each thread moves
   // 8-10 float4 per iteration.
   const size_t blocks_needed = (n / 4 + 255) / 256 + 1;
   const int grid = (int)min(blocks_needed, (size_t)ctx->sm_count * 8);
   if (k.weight_decay != 0.f)
-    optimizer_kernel<RULE, true><<<grid, 256, 0, ctx->stream>>>(k, p, g, m, v, vh, mask, n);
+    optimizer_kernel<RULE, true><<<grid, 256, 0, ctx->stream>>>(k, p, g, m, v, vh, mask, n, amax);
   else
-    optimizer_kernel<RULE, false><<<grid, 256, 0, ctx->stream>>>(k, p, g, m, v, vh, mask, n);
+    optimizer_kernel<RULE, false><<<grid, 256, 0, ctx->stream>>>(k, p, g, m, v, vh, mask, n, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -188,6 +193,16 @@ extern "C" {
 dlb_status dlb_optimizer_step(dlb_ctx *ctx, int rule, const dlb_optimizer_scalars *s, float *p,
                               float *g, float *first, float *second, float *second_hat,
                               const float *wd_mask, size_t n) {
+  return optimizer_step_amax(ctx, rule, s, p, g, first, second, second_hat, wd_mask, n, nullptr);
+}
+
+}  // extern "C"
+
+// The same pass that also leaves the largest |p| it wrote (raw bits) in *amax,
+// so that the fp16 split of a weight matrix needs no pass of its own for it.
+dlb_status dlb::optimizer_step_amax(dlb_ctx *ctx, int rule, const dlb_optimizer_scalars *s, float *p, float *g,
+                                    float *first, float *second, float *second_hat, const float *wd_mask,
+                                    size_t n, unsigned *amax) {
   DLB_REQUIRE(ctx && s && p && g, "dlb_optimizer_step: null");
   if (n == 0) return DLB_OK;
   const bool hat = rule == DLB_OPT_AMSGRAD || rule == DLB_OPT_AMSBOUND;
@@ -205,27 +220,29 @@ dlb_status dlb_optimizer_step(dlb_ctx *ctx, int rule, const dlb_optimizer_scalar
   switch (rule) {
     case DLB_OPT_ADAM:
     case DLB_OPT_NOSADAM:
-      return launch_rule<R_ADAM>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+      return launch_rule<R_ADAM>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
     case DLB_OPT_AMSGRAD:
-      return launch_rule<R_AMSGRAD>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+      return launch_rule<R_AMSGRAD>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
     case DLB_OPT_ADABOUND:
-      return launch_rule<R_ADABOUND>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+      return launch_rule<R_ADABOUND>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
     case DLB_OPT_AMSBOUND:
-      return launch_rule<R_AMSBOUND>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+      return launch_rule<R_AMSBOUND>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
     case DLB_OPT_ADAMAX:
-      return launch_rule<R_ADAMAX>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+      return launch_rule<R_ADAMAX>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
     case DLB_OPT_GD:
       // The three forms of Model::Update_Parameter__Gradient_Descent
       // (v1/optimizers/gradient_descent.cpp L:24-55).
-      if (s->beta1 == 0.f) return launch_rule<R_GD>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+      if (s->beta1 == 0.f) return launch_rule<R_GD>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
       if (s->beta2 != 0.f)
-        return launch_rule<R_GD_NESTEROV>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
-      return launch_rule<R_GD_MOMENTUM>(ctx, *s, p, g, first, second, second_hat, wd_mask, n);
+        return launch_rule<R_GD_NESTEROV>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
+      return launch_rule<R_GD_MOMENTUM>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
     default:
       set_error("dlb_optimizer_step: optimizer %d is outside the supported path", rule);
       return DLB_ERR_UNSUPPORTED;
   }
 }
+
+extern "C" {
 
 dlb_status dlb_clip_gradient(dlb_ctx *ctx, float *g, size_t n, float max_norm) {
   DLB_REQUIRE(ctx && g && max_norm > 0.f, "dlb_clip_gradient");
