@@ -24,13 +24,48 @@ def _gpu_count():
         return 0
 
 
-def _cfg():
+def _cfg(kind="brn_mlp"):
     import configs
 
+    if kind == "indrnn":
+        return configs.indrnn_stack(n_in=64, hidden=128, depth=2, n_out=32, seq_w=6, batch=64)
+    if kind == "residual":
+        return configs.residual_mlp(width=256, blocks=2, n_out=10, batch=128)
     return configs.deep_brn_mlp(256, 512, 2, 128, 256)
 
 
-def worker(rank, world, tmp):
+def _run(model, cfg, X, Y, masks, steps, first_row=0):
+    """`steps` training steps; ShakeDrop noise, where the model has any, is drawn
+    on the device by global row index, so that shards draw their rows of the
+    full batch's arrays."""
+    import configs
+    import util
+
+    if not configs.shakedrop_layers(cfg):
+        return util.trace(model, cfg, steps=steps, X=X, Y=Y, masks=masks)
+    B = cfg["batch"]
+    model.train_begin(B)
+    out, losses = {}, []
+    for step in range(steps):
+        model.draw_noise(B, 99, step, first_row)
+        model.reset_loss()
+        model.forward_pass(B, X)
+        model.compute_error(B, Y)
+        model.backward_pass(B)
+        model.update_derivatives(B)
+        model.merge_derivatives()
+        losses.append(model.get_loss())
+        if step == 0:
+            out["grads"] = model.get_array("derivatives")
+        model.update_weights(B, B)
+        if step == 0:
+            out["params1"] = model.get_array("parameters")
+    out["params_last"] = model.get_array("parameters")
+    out["losses"] = np.asarray(losses, np.float64)
+    return out
+
+
+def worker(rank, world, tmp, kind="brn_mlp"):
     for sub in ("deep-learning_b200", "oracle", "tests"):
         sys.path.insert(0, os.path.join(ROOT, sub))
     import configs
@@ -52,7 +87,7 @@ def worker(rank, world, tmp):
     # Two processes on two GPUs of one host: the statistics cross NVLink through
     # the peer-memory exchange unless the environment turned it off.
     assert ctx.peer_exchange() == (os.environ.get("DLB_PEER_EXCHANGE", "1") != "0")
-    cfg = _cfg()
+    cfg = _cfg(kind)
     B = cfg["batch"]
     X, Y = configs.synthetic_batch(cfg)
     masks = configs.dropout_masks(cfg)
@@ -61,7 +96,7 @@ def worker(rank, world, tmp):
     p0 = np.load(os.path.join(tmp, "p0.npy"))
     m = util.build(dlb200.Model(ctx), dict(cfg, batch=shard), params=p0)
     m.set_global_batch(B)
-    out = util.trace(m, dict(cfg, batch=shard), steps=4, X=X[lo:hi], Y=Y[lo:hi], masks=masks)
+    out = _run(m, dict(cfg, batch=shard), X[lo:hi], Y[lo:hi], masks, 4, first_row=lo)
     assert ctx.sync() == 0
     np.savez(os.path.join(tmp, f"rank{rank}.npz"), grads=out["grads"], params1=out["params1"],
              params_last=out["params_last"], losses=out["losses"])
@@ -97,5 +132,34 @@ def test_two_gpu_shards_equal_single_gpu_full_batch(gpu_ctx):
         assert np.array_equal(a["params_last"], b["params_last"])   # replicas stay bit-identical
 
 
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("kind", ["indrnn", "residual"])
+def test_two_gpu_shards_of_the_other_model_families(gpu_ctx, kind):
+    """The same for a time-stepped IndRNN stack (per-time-step statistics, 2 T H
+    doubles per exchange) and for residual blocks with ShakeDrop noise drawn on
+    the device by global row index."""
+    import dlb200
+    import util
+
+    cfg = _cfg(kind)
+    X, Y = __import__("configs").synthetic_batch(cfg)
+    seeded = util.build(dlb200.Model(gpu_ctx), cfg, seed=5)
+    p0 = seeded.get_array("parameters")
+    want = _run(util.build(dlb200.Model(gpu_ctx), cfg, params=p0), cfg, X, Y, {}, 4)
+    with tempfile.TemporaryDirectory() as tmp:
+        np.save(os.path.join(tmp, "p0.npy"), p0)
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+        procs = [subprocess.Popen([sys.executable, os.path.abspath(__file__), "--worker", str(r), "2", tmp, kind],
+                                  env=env) for r in range(2)]
+        for p in procs:
+            assert p.wait(timeout=600) == 0
+        a, b = np.load(os.path.join(tmp, "rank0.npz")), np.load(os.path.join(tmp, "rank1.npz"))
+        for key in ("grads", "params1", "losses"):
+            assert util.rel_l2(a[key], want[key]) <= 2e-5, key
+        # Later steps may meet a derivative jump; only the scale of the agreement is checked.
+        assert util.rel_l2(a["params_last"], want["params_last"]) <= 1e-3
+        assert np.array_equal(a["params_last"], b["params_last"])   # replicas stay bit-identical
+
+
 if __name__ == "__main__" and len(sys.argv) > 1 and sys.argv[1] == "--worker":
-    worker(int(sys.argv[2]), int(sys.argv[3]), sys.argv[4])
+    worker(int(sys.argv[2]), int(sys.argv[3]), sys.argv[4], sys.argv[5] if len(sys.argv) > 5 else "brn_mlp")
