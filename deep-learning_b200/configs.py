@@ -56,24 +56,29 @@ def deep_brn_mlp(n_in=1024, hidden=4096, depth=4, n_out=1024, batch=4096,
     )
 
 
-def residual_mlp(width=8192, blocks=16, n_out=1000, batch=8192, p_last=0.5, optimizer=OPTIMIZER.ADAM):
+def residual_mlp(width=8192, blocks=16, n_out=1000, batch=8192, p_last=0.5, optimizer=OPTIMIZER.ADAM,
+                 block_width=None):
     """Residual MLP: `blocks` blocks of width `width`, each FC - batch renorm -
     ELU - FC with a ShakeDrop skip, softmax cross-entropy over n_out classes,
     Adam.  In the reference's layer list a block is a RESIDUAL layer of depth 2
     followed by its two FC layers, the second carrying the normalization and
     the activation (pre-activation order).  The paper's keep probability decays
     linearly to p_last; the reference's ShakeDrop value is the probability that
-    a row IS perturbed, hence (l / blocks) * (1 - p_last) for block l."""
+    a row IS perturbed, hence (l / blocks) * (1 - p_last) for block l.
+    `block_width` (default: width) is the width of the layers inside the blocks;
+    where it differs from the shortcut's, the reference pads the narrower one
+    with zeros (the residual output is as wide as the wider one)."""
+    inner = block_width or width
     layers = [dict(type=LAYER.FULLY_CONNECTED, units=width)]
     for b in range(1, blocks + 1):
         layers.append(dict(type=LAYER.RESIDUAL, units=2,
                            dropout=(LAYER_DROPOUT.SHAKEDROP, (b / blocks) * (1.0 - p_last))))
-        layers.append(dict(type=LAYER.FULLY_CONNECTED, units=width, af=ACTIVATION.ELU))
-        layers.append(dict(type=LAYER.FULLY_CONNECTED, units=width, af=ACTIVATION.ELU,
+        layers.append(dict(type=LAYER.FULLY_CONNECTED, units=inner, af=ACTIVATION.ELU))
+        layers.append(dict(type=LAYER.FULLY_CONNECTED, units=inner, af=ACTIVATION.ELU,
                            norm=LAYER_NORM.BATCH_RENORMALIZATION))
     layers.append(dict(type=LAYER.FULLY_CONNECTED, units=n_out, af=ACTIVATION.SOFTMAX))
     return dict(
-        name=f"residual_mlp_{blocks}x{width}-{n_out}_b{batch}",
+        name=f"residual_mlp_{blocks}x{width}" + (f"({inner})" if inner != width else "") + f"-{n_out}_b{batch}",
         model_type=MODEL.FEEDFORWARD, seq_w=1, time_delays=0, layers=layers,
         loss=LOSS_FN.CROSS_ENTROPY, optimizer=optimizer,
         hparams=dict(adam_learning_rate=1e-3, adam_beta1=0.9, adam_beta2=0.999, adam_epsilon=1e-8),

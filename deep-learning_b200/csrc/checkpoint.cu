@@ -144,8 +144,10 @@ void normalization_lines(std::string &out, const dlb_model *m, size_t i, const H
   out += "    type_normalization " + num(l.norm) + CRLF;
   if (l.type != DLB_LAYER_RESIDUAL) out += std::string("      use_layer_normalization_before_activation 1") + CRLF;
   // Normalized units exist for every layer as soon as one layer is normalised,
-  // and for none otherwise.
-  const size_t n = m->any_norm ? l.units : 0;
+  // and for none otherwise: as many as the layer has units, a block layer as
+  // many as it has inputs (it normalises its input), a RESIDUAL layer as many
+  // as its block puts out.
+  const size_t n = m->any_norm ? l.norm_units : 0;
   out += "      number_normalized_units " + num(n) + CRLF;
   for (size_t k = 0; k < n; ++k) {
     out += "        NormU[" + num(k) + "]" + CRLF;
@@ -371,7 +373,7 @@ dlb_status dlb_model_save_params(dlb_model *m, const char *path) {
   const UnitBase base = unit_bases(m);
   size_t neurons = 0, basics = 0, afs = 0, inds = 0, all_units = 0;
   for (const LayerRT &l : m->layers) {
-    all_units += l.units;
+    all_units += l.norm_units;
     if (fc_like(l)) neurons += l.units;
     if (l.type == DLB_LAYER_RESIDUAL) basics += l.units;
     if (indrnn(l)) inds += l.units;
@@ -413,7 +415,7 @@ dlb_status dlb_model_save_params(dlb_model *m, const char *path) {
     out += std::string("    use_bidirectional 0") + CRLF;
     if (l.type == DLB_LAYER_RESIDUAL) {
       out += "    block_depth " + num(l.depth) + CRLF;
-      out += std::string("    padding 0") + CRLF;
+      out += "    padding " + num(l.pad) + CRLF;
       dropout_lines(out, l, true);
       normalization_lines(out, m, i, h);
       out += "    number_basic_units " + num(l.units) + CRLF;
@@ -773,7 +775,8 @@ dlb_status dlb_model_load(dlb_model *m, const char *path_params, const char *pat
     }
     if (L[i].norm == DLB_NORM_NONE) continue;
     const LayerRT &l = m->layers[i];
-    for (size_t k = 0; k < L[i].units; ++k) {
+    DLB_REQUIRE(L[i].scale.size() == l.norm_units, "load: a layer's normalized units do not match its shape");
+    for (size_t k = 0; k < L[i].scale.size(); ++k) {
       params[gamma_at(m, l) + k] = L[i].scale[k];
       params[beta_at(m, l) + k] = L[i].shift[k];
     }

@@ -901,7 +901,9 @@ __global__ void residual_forward_kernel(const float *__restrict__ x, float *__re
 }
 
 // delta = d * noise on flagged rows, d elsewhere, plus its residual plane.
-__global__ void shakedrop_backward_kernel(const float *__restrict__ d,
+// d has rows of ld_d floats of which `width` are read from column `first` on
+// (the block's window of the residual layer's error when the widths differ).
+__global__ void shakedrop_backward_kernel(const float *__restrict__ d, int ld_d, int first,
                                           const uint8_t *__restrict__ row_mask,
                                           const float *__restrict__ noise, float *__restrict__ delta,
                                           float *__restrict__ delta_lo, int rows, int width,
@@ -911,11 +913,46 @@ __global__ void shakedrop_backward_kernel(const float *__restrict__ d,
   unsigned mx = 0;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const int r = (int)(i / width);
-    float v = d[i];
+    float v = d[(size_t)r * ld_d + first + (i - (size_t)r * width)];
     if (row_mask && row_mask[r]) v *= noise[i];
     delta[i] = v;
     mx = max(mx, abs_bits(v));
     if (delta_lo) delta_lo[i] = tf32_lo(v);
+  }
+  amax_commit(amax, mx);
+}
+
+// The shortcut sum for unequal widths: the output is as wide as the wider of x
+// (width wx) and block (width wb); the narrower one enters from column `pad`
+// on (Forward_Pass__Zero_Padded_Identity__OpenMP, fwp_mp.cpp L:5058-5123).
+// ShakeDrop perturbs the block in place as in the equal-width kernel.
+__global__ void residual_forward_padded_kernel(const float *__restrict__ x, int wx, float *__restrict__ block,
+                                               int wb, int pad, const uint8_t *__restrict__ row_mask,
+                                               const float *__restrict__ noise, float *__restrict__ out,
+                                               float *__restrict__ out_lo, int rows, unsigned *amax) {
+  const int W = max(wx, wb);
+  const int off_x = wx < W ? pad : 0, off_b = wb < W ? pad : 0;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t total = (size_t)rows * W;
+  unsigned mx = 0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int r = (int)(i / W), c = (int)(i % W);
+    float v = 0.f;
+    const int cb = c - off_b;
+    if (cb >= 0 && cb < wb) {
+      const size_t j = (size_t)r * wb + cb;
+      float o = block[j];
+      if (row_mask && row_mask[r]) {
+        o *= noise[j];
+        block[j] = o;
+      }
+      v = o;
+    }
+    const int cx = c - off_x;
+    if (cx >= 0 && cx < wx) v += x[(size_t)r * wx + cx];
+    out[i] = v;
+    mx = max(mx, abs_bits(v));
+    if (out_lo) out_lo[i] = tf32_lo(v);
   }
   amax_commit(amax, mx);
 }
@@ -938,13 +975,27 @@ static dlb_status residual_forward_impl(dlb_ctx *ctx, const float *x, float *blo
   return DLB_OK;
 }
 
-static dlb_status shakedrop_backward_impl(dlb_ctx *ctx, const float *d, const uint8_t *row_mask,
-                                             const float *noise, float *delta, float *delta_lo,
-                                             int rows, int width, unsigned *amax) {
-  DLB_REQUIRE(ctx && d && delta && rows > 0 && width > 0, "dlb_shakedrop_backward");
+static dlb_status residual_forward_padded_impl(dlb_ctx *ctx, const float *x, int wx, float *block, int wb,
+                                               const uint8_t *row_mask, const float *noise, float *out,
+                                               float *out_lo, int rows, unsigned *amax) {
+  DLB_REQUIRE(ctx && x && block && out && rows > 0 && wx > 0 && wb > 0, "dlb_residual_forward_padded");
+  DLB_REQUIRE(!row_mask || noise, "dlb_residual_forward_padded: row flags need the noise draws");
+  const int W = wx > wb ? wx : wb;
+  const int pad = ((wx > wb ? wx - wb : wb - wx) + 1) / 2;  // v1/learner/compile.cpp L:344-352
+  residual_forward_padded_kernel<<<stream_grid(ctx, (size_t)rows * W, 256), 256, 0, ctx->stream>>>(
+      x, wx, block, wb, pad, row_mask, noise, out, out_lo, rows, amax);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
+
+static dlb_status shakedrop_backward_impl(dlb_ctx *ctx, const float *d, int ld_d, int first,
+                                          const uint8_t *row_mask, const float *noise, float *delta,
+                                          float *delta_lo, int rows, int width, unsigned *amax) {
+  DLB_REQUIRE(ctx && d && delta && rows > 0 && width > 0 && first >= 0 && first + width <= ld_d,
+              "dlb_shakedrop_backward");
   DLB_REQUIRE(!row_mask || noise, "dlb_shakedrop_backward: row flags need the noise draws");
   shakedrop_backward_kernel<<<stream_grid(ctx, (size_t)rows * width, 256), 256, 0, ctx->stream>>>(
-      d, row_mask, noise, delta, delta_lo, rows, width, amax);
+      d, ld_d, first, row_mask, noise, delta, delta_lo, rows, width, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -1096,8 +1147,27 @@ dlb_status dlb_shakedrop_backward(dlb_ctx *ctx, const float *d, const uint8_t *r
                                   float *delta, float *delta_lo, int rows, int width) {
   PlaneOutput p;
   DLB_TRY(p.begin(ctx, delta, delta_lo, (size_t)rows * width));
-  return p.finish(ctx, shakedrop_backward_impl(ctx, d, row_mask, noise, delta, p.kernel_arg, rows, width, p.amax),
+  return p.finish(ctx, shakedrop_backward_impl(ctx, d, width, 0, row_mask, noise, delta, p.kernel_arg, rows, width, p.amax),
                   delta, (size_t)rows * width);
+}
+
+dlb_status dlb_residual_forward_padded(dlb_ctx *ctx, const float *x, int width_x, float *block, int width_block,
+                                       const uint8_t *row_mask, const float *noise, float *out, float *out_lo,
+                                       int rows) {
+  const size_t n = (size_t)rows * (width_x > width_block ? width_x : width_block);
+  PlaneOutput p;
+  DLB_TRY(p.begin(ctx, out, out_lo, n));
+  return p.finish(ctx, residual_forward_padded_impl(ctx, x, width_x, block, width_block, row_mask, noise, out,
+                                                    p.kernel_arg, rows, p.amax), out, n);
+}
+
+dlb_status dlb_shakedrop_backward_window(dlb_ctx *ctx, const float *d, int width_d, int first,
+                                         const uint8_t *row_mask, const float *noise, float *delta,
+                                         float *delta_lo, int rows, int width) {
+  PlaneOutput p;
+  DLB_TRY(p.begin(ctx, delta, delta_lo, (size_t)rows * width));
+  return p.finish(ctx, shakedrop_backward_impl(ctx, d, width_d, first, row_mask, noise, delta, p.kernel_arg, rows,
+                                               width, p.amax), delta, (size_t)rows * width);
 }
 
 }  // extern "C"

@@ -78,8 +78,6 @@ dlb_status layout_parameters(dlb_model *m) {
     if (l.type == DLB_LAYER_RESIDUAL) {
       DLB_REQUIRE(l.depth >= 1 && i + l.depth < m->layers.size(),
                   "compile: a RESIDUAL layer needs its block layers and a layer after them");
-      l.units = width;
-      l.norm_units = width;
       l.group = 0;
       size_t fan = width;
       for (size_t j = 1; j <= l.depth; ++j) {
@@ -91,6 +89,14 @@ dlb_status layout_parameters(dlb_model *m) {
         b.norm_units = fan;
         fan = b.units;
       }
+      // As wide as the wider of shortcut and block; the narrower one enters
+      // from column pad on; the layer's own normalization acts on the block
+      // output (v1/learner/compile.cpp L:337-352).
+      l.units = std::max(width, fan);
+      l.pad = ((width > fan ? width - fan : fan - width) + 1) / 2;
+      l.norm_units = fan;
+      l.fan_in = width;  // width of the shortcut
+      width = l.units;
       i += l.depth;
     } else {
       l.group = 0;
@@ -333,12 +339,6 @@ dlb_status check_supported(dlb_model *m) {
       continue;
     }
     if (l.type == DLB_LAYER_RESIDUAL) {
-      const LayerRT &last = m->layers[i + l.depth];
-      if (last.units != l.units) {
-        set_error("model: residual block at layer %zu maps width %zu to %zu; the zero-padded shortcut "
-                  "for unequal widths is outside the supported path", i, l.units, last.units);
-        return DLB_ERR_UNSUPPORTED;
-      }
       if (m->layers[i + 1].norm != DLB_NORM_NONE) {
         set_error("model: normalization on the first layer of a residual block (layer %zu) is outside "
                   "the supported path", i + 1);
@@ -510,6 +510,10 @@ dlb_status forward_residual(dlb_model *m, size_t i, const float *X, const float 
               "(dlb_model_set_shakedrop_noise)", i, B);
     return DLB_ERR_INVALID;
   }
+  if (last.units != res.fan_in)
+    return dlb_residual_forward_padded(m->ctx, X, (int)res.fan_in, block, (int)last.units,
+                                       shake ? res.sd_mask : nullptr, shake ? res.sd_fwd : nullptr, res.A,
+                                       res.A_lo, B);
   return dlb_residual_forward(m->ctx, X, block, shake ? res.sd_mask : nullptr,
                               shake ? res.sd_fwd : nullptr, res.A, res.A_lo, B, (int)res.units);
 }
@@ -1068,8 +1072,8 @@ static dlb_status ensure_shakedrop(dlb_model *m, LayerRT &l, size_t rows) {
   l.sd_fwd = l.sd_bwd = nullptr;
   l.sd_rows = 0;
   DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_mask), rows));
-  DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_fwd), rows * l.units * sizeof(float)));
-  DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_bwd), rows * l.units * sizeof(float)));
+  DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_fwd), rows * l.norm_units * sizeof(float)));
+  DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&l.sd_bwd), rows * l.norm_units * sizeof(float)));
   l.sd_rows = rows;
   return DLB_OK;
 }
@@ -1115,10 +1119,11 @@ dlb_status dlb_model_draw_noise(dlb_model *m, size_t rows, uint64_t seed, uint32
         // (fwp_mp.cpp L:3881-3888, bwp_mp.cpp ShakeDrop backward).
         DLB_TRY(ensure_shakedrop(m, l, rows));
         DLB_TRY(dlb_noise_bernoulli(m->ctx, l.sd_mask, rows, l.dropout_value, seed, stream, step, first_row));
-        DLB_TRY(dlb_noise_uniform(m->ctx, l.sd_fwd, rows * l.units, -1.f, 1.f, seed, stream + 1, step,
-                                  first_row * l.units));
-        DLB_TRY(dlb_noise_uniform(m->ctx, l.sd_bwd, rows * l.units, 0.f, 1.f, seed, stream + 2, step,
-                                  first_row * l.units));
+        // (one factor per element of the block's output, norm_units wide)
+        DLB_TRY(dlb_noise_uniform(m->ctx, l.sd_fwd, rows * l.norm_units, -1.f, 1.f, seed, stream + 1, step,
+                                  first_row * l.norm_units));
+        DLB_TRY(dlb_noise_uniform(m->ctx, l.sd_bwd, rows * l.norm_units, 0.f, 1.f, seed, stream + 2, step,
+                                  first_row * l.norm_units));
         break;
       default:
         break;
@@ -1135,7 +1140,7 @@ dlb_status dlb_model_set_shakedrop_noise(dlb_model *m, size_t layer, const uint8
   LayerRT &l = m->layers[layer];
   DLB_REQUIRE(l.type == DLB_LAYER_RESIDUAL && l.dropout == DLB_DROPOUT_SHAKEDROP,
               "set_shakedrop_noise: layer is not a residual layer with ShakeDrop");
-  const size_t n = rows * l.units;
+  const size_t n = rows * l.norm_units;  // one factor per element of the block's output
   DLB_TRY(ensure_shakedrop(m, l, rows));
   std::vector<uint8_t> flags(rows);
   for (size_t i = 0; i < rows; ++i) flags[i] = host_row_mask[i] ? 1 : 0;
@@ -1229,9 +1234,11 @@ static dlb_status backward_residual(dlb_model *m, size_t i, int B) {
   LayerRT &last = m->layers[i + res.depth];
   const bool shake = res.dropout == DLB_DROPOUT_SHAKEDROP;
   const bool rnorm = res.norm != DLB_NORM_NONE;
-  DLB_TRY(dlb_shakedrop_backward(m->ctx, res.delta, shake ? res.sd_mask : nullptr,
-                                 shake ? res.sd_bwd : nullptr, last.delta,
-                                 rnorm ? nullptr : last.delta_lo, B, (int)res.units));
+  // The block reads its window of the residual layer's error.
+  const int first = last.units < res.units ? (int)res.pad : 0;
+  DLB_TRY(dlb_shakedrop_backward_window(m->ctx, res.delta, (int)res.units, first, shake ? res.sd_mask : nullptr,
+                                        shake ? res.sd_bwd : nullptr, last.delta,
+                                        rnorm ? nullptr : last.delta_lo, B, (int)last.units));
   if (rnorm)
     DLB_TRY(norm_backward(m, res, last.delta, last.delta_lo, last.A, last.A, DLB_AF_LINEAR, B));
   for (size_t j = res.depth; j >= 2; --j) {
@@ -1319,7 +1326,11 @@ dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows) {
       if (below) {
         // shortcut error + delta_1 W_1
         LayerRT &first = m->layers[i + 1];
-        DLB_TRY(dlb_memcpy_d2d(m->ctx, below->delta, l.delta, (size_t)B * l.units * sizeof(float)));
+        // (the shortcut's window of the residual layer's error)
+        const size_t first_col = l.fan_in < l.units ? l.pad : 0;
+        DLB_CUDA(cudaMemcpy2DAsync(below->delta, l.fan_in * sizeof(float), l.delta + first_col,
+                                   l.units * sizeof(float), l.fan_in * sizeof(float), (size_t)B,
+                                   cudaMemcpyDeviceToDevice, m->ctx->stream));
         GemmOperand A{first.delta, first.delta_lo, (long long)first.units, 1};
         GemmOperand Bo{m->params + first.first_conn, m->params_lo + first.first_conn, 1,
                        (long long)first.fan_in};

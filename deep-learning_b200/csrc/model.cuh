@@ -27,6 +27,7 @@ struct LayerRT {
   // followed by its d block layers, v1/learner/compile.cpp).
   int group = 0;            // 1 = layer inside a residual block
   size_t depth = 0;         // RESIDUAL: number of block layers
+  size_t pad = 0;           // RESIDUAL: first column of the narrower of shortcut and block in the output
   bool block_input = false; // first layer of a block: no activation in front
   size_t norm_units = 0;    // normalised units: width, or fan-in for a block layer
   // Device buffers (allocated by ensure_batch).  Stand-alone FC layer: Z sums,

@@ -74,6 +74,8 @@ SIGNATURES = {
     "dlb_brn_backward_param_grads": (_i, [_vp, _vp, _i, _vp, _vp, _i]),
     "dlb_residual_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "dlb_shakedrop_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "dlb_residual_forward_padded": (_i, [_vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i]),
+    "dlb_shakedrop_backward_window": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i]),
     "dlb_model_set_shakedrop_noise": (_i, [_vp, _sz, _vp, _vp, _vp, _sz]),
     "dlb_model_set_uout_noise": (_i, [_vp, _sz, _vp, _sz]),
     "dlb_time_major": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),

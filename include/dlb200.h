@@ -276,6 +276,19 @@ dlb_status dlb_residual_forward(dlb_ctx *ctx, const float *x, float *block,
 dlb_status dlb_shakedrop_backward(dlb_ctx *ctx, const float *d, const uint8_t *row_mask,
                                   const float *noise, float *delta, float *delta_lo, int rows,
                                   int width);
+/* The same pair where the block maps its input to another width.  The output is
+ * as wide as the wider of x and block, W = max(width_x, width_block); the
+ * narrower one enters from column pad = (|width_x - width_block| + 1) / 2 on
+ * (v1/learner/compile.cpp L:337-352, Forward_Pass__Zero_Padded_Identity__OpenMP,
+ * fwp_mp.cpp L:5058-5123).  Backward, each of the two reads its window of the
+ * error d [rows, width_d]: columns first .. first + width
+ * (Backward_Pass__Residual__OpenMP, bwp_mp.cpp L:1078-1140). */
+dlb_status dlb_residual_forward_padded(dlb_ctx *ctx, const float *x, int width_x, float *block,
+                                       int width_block, const uint8_t *row_mask,
+                                       const float *noise, float *out, float *out_lo, int rows);
+dlb_status dlb_shakedrop_backward_window(dlb_ctx *ctx, const float *d, int width_d, int first,
+                                         const uint8_t *row_mask, const float *noise,
+                                         float *delta, float *delta_lo, int rows, int width);
 
 /* ------------------------------------------------------------------------ */
 /* Recurrent (IndRNN) step.  Tensors are [seq_w, rows, n] row-major, the
@@ -495,7 +508,8 @@ dlb_status dlb_model_set_dropout_mask(dlb_model *m, size_t layer, const uint8_t 
  * L:4959-4985); here they are an input, like the dropout masks. */
 dlb_status dlb_model_set_uout_noise(dlb_model *m, size_t layer, const float *host_noise, size_t rows);
 /* ShakeDrop draws of one training step for a RESIDUAL layer: row flags [rows]
- * and the forward U(-1,1) / backward U(0,1) draws [rows, width] (host arrays;
+ * and the forward U(-1,1) / backward U(0,1) draws [rows, width of the block's
+ * last layer] (host arrays;
  * only flagged rows are read).  The reference draws them from clock-seeded
  * generators inside the step (fwp_mp.cpp L:4942-4955, bwp_mp.cpp L:959-963);
  * here they are inputs so that a run can be reproduced. */

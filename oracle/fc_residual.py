@@ -61,7 +61,15 @@ class ResidualOracleModel(OracleModel):
                                             dropout=(0, 0.0), mask=None, group=1, block_input=(j == 0),
                                             norm_units=fan))
                     fan = units[i]
-                assert fan == width, "block output width must equal its input width in this restatement"
+                # The residual output is as wide as the wider of shortcut and block;
+                # the narrower one is added from column `pad` on
+                # (v1/learner/compile.cpp L:337-352, Forward_Pass__Zero_Padded_Identity__OpenMP,
+                # fwp_mp.cpp L:5058-5123).
+                res["units"] = max(width, fan)
+                res["norm_units"] = fan   # the layer's own normalization acts on the block output
+                res["pad"] = (abs(width - fan) + 1) // 2
+                res["shortcut_width"], res["block_width"] = width, fan
+                width = res["units"]
             else:
                 self.layers.append(dict(type=LAYER_FC, units=units[i], fan_in=width, af=None, norm=NORM_NONE,
                                         dropout=(0, 0.0), mask=None, group=0, block_input=False,
@@ -195,7 +203,15 @@ class ResidualOracleModel(OracleModel):
                 # The reference normalises / perturbs in place in the last block
                 # layer's output buffer, which is what a reader of that layer sees.
                 self.layers[i + l["depth"]]["A"] = o
-                a = (x + o).astype(f32)
+                a = np.zeros((x.shape[0], l["units"]), f32)
+                sa = l["pad"] if x.shape[1] < l["units"] else 0
+                sb = l["pad"] if o.shape[1] < l["units"] else 0
+                if o.shape[1] >= x.shape[1]:   # the wider one is copied, the narrower one added
+                    a[:, sb:sb + o.shape[1]] = o
+                    a[:, sa:sa + x.shape[1]] += x
+                else:
+                    a[:, sa:sa + x.shape[1]] = x
+                    a[:, sb:sb + o.shape[1]] += o
                 l["A"] = a
                 i += l["depth"] + 1
                 continue
@@ -238,7 +254,12 @@ class ResidualOracleModel(OracleModel):
             l = self.layers[i]
             if l["type"] == LAYER_RESIDUAL:
                 d = dout[i]
-                do = d
+                # Backward_Pass__Residual__OpenMP (bwp_mp.cpp L:1078-1140): the
+                # narrower of shortcut and block reads its window of the error.
+                wa, wb = l["shortcut_width"], l["block_width"]
+                sa = l["pad"] if wa < l["units"] else 0
+                sb = l["pad"] if wb < l["units"] else 0
+                do = np.ascontiguousarray(d[:, sb:sb + wb])
                 if l["dropout"][0] == DROPOUT_SHAKEDROP:
                     do = np.where(l["sd_mask"][:batch, None], do * l["sd_bwd"][:batch], do).astype(f32)
                 if l["norm"] != NORM_NONE:
@@ -257,7 +278,7 @@ class ResidualOracleModel(OracleModel):
                 first = self.layers[i + 1]
                 l["delta"] = d
                 if pos > 1:   # no error into the input layer
-                    dout[tops[pos - 1]] = (d + (first["delta"] @ self._W(first)).astype(f32)).astype(f32)
+                    dout[tops[pos - 1]] = (d[:, sa:sa + wa] + (first["delta"] @ self._W(first)).astype(f32)).astype(f32)
             else:
                 if dout[i] is not None:   # hidden standalone layer
                     e = (dout[i] * af_derive(l["af"], l["Y"], l["A"])).astype(f32)

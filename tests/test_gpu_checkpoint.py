@@ -19,6 +19,7 @@ CASES = {
     "brn_mlp": lambda: configs.deep_brn_mlp(6, 8, 2, 4, 8),
     "softmax_mlp": lambda: configs.mlp_softmax(7, 5, 3, 8),
     "residual": lambda: configs.residual_mlp(6, 2, 4, 8),
+    "residual_wider_blocks": lambda: configs.residual_mlp(5, 2, 4, 8, block_width=8),
     "indrnn": lambda: configs.indrnn_stack(n_in=3, hidden=5, depth=2, n_out=2, seq_w=3, batch=6),
 }
 

@@ -114,13 +114,24 @@ def test_residual_kernels(gpu_ctx):
     assert ctx.sync() == 0
 
 
-def test_unequal_block_width_is_refused(gpu_ctx):
-    m = dlb200.Model(gpu_ctx)
-    m.compile([3, 9, 3, 3, 3], [8, 2, 8, 12, 4])     # block maps 8 -> 12
-    for i in (2, 3):
-        m.set_layer_activation_function(i, 3)
-    m.set_layer_activation_function(4, 11)
-    m.set_loss_fn(10)
-    m.set_optimizer(2)
-    with pytest.raises(dlb200.DlbError):
-        m.forward_pass(4, np.zeros((4, 8), np.float32))
+@pytest.mark.skipif(not ref_binding.available(), reason="ShakeDrop draws come from oracle/_ref")
+@pytest.mark.parametrize("width,block_width", [(128, 192), (192, 128), (130, 136)])
+def test_blocks_of_another_width_than_the_shortcut(gpu_ctx, width, block_width):
+    """The zero-padded shortcut: the residual output is as wide as the wider of
+    shortcut and block, the narrower one enters from column pad on, and each
+    reads its window of the error on the way back."""
+    cfg = configs.residual_mlp(width=width, blocks=2, n_out=10, batch=128, block_width=block_width)
+    X, Y = configs.synthetic_batch(cfg)
+    draws = [util.shakedrop_step_draws(cfg, s) for s in range(2)]
+
+    def prepare(model):
+        util.set_step_noise(model, cfg, 0, draws[0])
+
+    p0, seed = util.kink_free_parameters(cfg, fc_residual.ResidualOracleModel, X, {}, scale=1.0 / 12,
+                                         prepare=prepare)
+    want = util.trace_noisy(util.build(fc_residual.ResidualOracleModel(), cfg, params=p0), cfg, 1, X, Y, draws)
+    mod = util.build(dlb200.Model(gpu_ctx), cfg, params=p0)
+    got = util.trace_noisy(mod, cfg, 1, X, Y, draws)
+    assert gpu_ctx.sync() == 0
+    _check(got, want)
+    assert mod.layer_info(1)["n_out"] == max(width, block_width)

@@ -31,7 +31,12 @@ def test_residual_restatement_matches_golden(name):
 
 @pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
 @pytest.mark.parametrize("cfg", [configs.residual_mlp(32, 2, 10, 8, p_last=0.0),
-                                 configs.residual_mlp(40, 4, 5, 24)], ids=lambda c: c["name"])
+                                 configs.residual_mlp(40, 4, 5, 24),
+                                 # blocks wider / narrower than the shortcut, an odd difference:
+                                 # the zero-padded shortcut (fwp_mp.cpp L:5058-5123, bwp_mp.cpp L:1078-1140)
+                                 configs.residual_mlp(8, 2, 5, 12, block_width=12),
+                                 configs.residual_mlp(12, 2, 5, 12, block_width=8),
+                                 configs.residual_mlp(9, 2, 5, 12, block_width=12)], ids=lambda c: c["name"])
 def test_residual_restatement_matches_compiled_reference(cfg):
     ref = util.build(ref_binding.RefModel(), cfg, seed=0)
     p0 = ref.get_array("parameters")

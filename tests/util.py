@@ -137,7 +137,11 @@ def shakedrop_step_draws(cfg, step, rows=None):
     import ref_binding
 
     layers = configs.shakedrop_layers(cfg)
-    width = cfg["layers"][0]["units"]
+    # One factor per element of a block's output: the width of the block's last
+    # layer (the replay takes one width for all blocks).
+    widths = {cfg["layers"][li + cfg["layers"][li]["units"]]["units"] for li, _ in layers}
+    assert len(widths) == 1, "blocks of different widths need draws of their own"
+    width = widths.pop()
     seed = cfg.get("shakedrop_seed", 2) + 1000 * step
     masks, fwd, bwd = ref_binding.shakedrop_draws(seed, [p for _, p in layers], rows or cfg["batch"], width)
     return seed, {li: (masks[k], fwd[k], bwd[k]) for k, (li, _) in enumerate(layers)}
