@@ -88,7 +88,7 @@ def residual_mlp(width=8192, blocks=16, n_out=1000, batch=8192, p_last=0.5, opti
 
 
 def indrnn_stack(n_in=512, hidden=2048, depth=4, n_out=512, seq_w=256, batch=1024,
-                 af=ACTIVATION.RELU, optimizer=OPTIMIZER.ADABOUND, norm=True):
+                 af=ACTIVATION.RELU, optimizer=OPTIMIZER.ADABOUND, norm=True, dropout=None):
     """IndRNN stack: `depth` independently recurrent layers of width `hidden`
     with ReLU recurrence and batch renormalization (statistics per time step),
     a linear output layer, MSE on the last time step only (time_delays =
@@ -97,7 +97,7 @@ def indrnn_stack(n_in=512, hidden=2048, depth=4, n_out=512, seq_w=256, batch=102
     layers = [dict(type=LAYER.FULLY_CONNECTED, units=n_in)]
     for _ in range(depth):
         layers.append(dict(type=LAYER.FULLY_CONNECTED_INDEPENDENTLY_RECURRENT, units=hidden, af=af,
-                           norm=LAYER_NORM.BATCH_RENORMALIZATION if norm else None))
+                           norm=LAYER_NORM.BATCH_RENORMALIZATION if norm else None, dropout=dropout))
     layers.append(dict(type=LAYER.FULLY_CONNECTED, units=n_out, af=ACTIVATION.LINEAR))
     return dict(
         name=f"indrnn_{n_in}-{depth}x{hidden}-{n_out}_T{seq_w}_b{batch}",

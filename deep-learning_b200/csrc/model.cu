@@ -320,10 +320,12 @@ dlb_status check_supported(dlb_model *m) {
     const LayerRT &l = m->layers[i];
     if (stepped) {
       // The time-stepped path covers stacks of IndRNN and fully connected
-      // layers with batch renormalization between them.
-      if (l.type == DLB_LAYER_RESIDUAL || l.dropout != DLB_DROPOUT_NONE) {
-        set_error("model: layer %zu: residual blocks and dropout are outside the supported path of "
-                  "time-stepped (recurrent) models", i);
+      // layers with batch renormalization between them and Bernoulli dropout
+      // (plain or inverted) on their outputs.
+      const bool bern = l.dropout == DLB_DROPOUT_BERNOULLI || l.dropout == DLB_DROPOUT_BERNOULLI_INVERTED;
+      if (l.type == DLB_LAYER_RESIDUAL || (l.dropout != DLB_DROPOUT_NONE && !bern)) {
+        set_error("model: layer %zu: residual blocks and dropout other than Bernoulli are outside the "
+                  "supported path of time-stepped (recurrent) models", i);
         return DLB_ERR_UNSUPPORTED;
       }
       if (is_indrnn(l) && (i + 1 == m->layers.size() || l.af == DLB_AF_SOFTMAX)) {
@@ -538,7 +540,7 @@ dlb_status forward_layers_time(dlb_model *m, size_t rows) {
                            bias, l.Z, TB, I, H));
     if (l.af == DLB_AF_SOFTMAX) {
       DLB_TRY(dlb_softmax_forward(m->ctx, l.Z, l.A, TB, H));
-    } else if (norm || is_indrnn(l)) {
+    } else if (norm || is_indrnn(l) || l.dropout != DLB_DROPOUT_NONE) {
       dlb_brn_unit_arrays u{};
       if (norm && m->propagation == DLB_PROPAGATION_INFERENCE) {
         DLB_TRY(inference_arrays(m, l, &u));  // every time step has its own running averages
@@ -551,9 +553,23 @@ dlb_status forward_layers_time(dlb_model *m, size_t rows) {
                                               m->hp.normalization_epsilon, r_max_of(m, l),
                                               d_max_of(m, l), &u));
       }
-      DLB_TRY(dlb_indrnn_forward(m->ctx, l.Z, norm ? &u : nullptr,
-                                 is_indrnn(l) ? m->params + l.first_recurrent : nullptr, l.af, l.A,
-                                 last ? nullptr : l.A_lo, T, B, H));
+      // Dropout of time step t acts on the stored output, which the recurrence
+      // of step t + 1 reads; at inference the plain form scales by the keep
+      // probability and the inverted form does nothing.
+      const uint8_t *mask = nullptr;
+      float keep_scale = 1.f;
+      if (l.dropout != DLB_DROPOUT_NONE && !last) {
+        if (m->propagation == DLB_PROPAGATION_INFERENCE) {
+          if (l.dropout == DLB_DROPOUT_BERNOULLI) keep_scale = l.dropout_value;
+        } else {
+          mask = l.mask;
+          if (l.dropout == DLB_DROPOUT_BERNOULLI_INVERTED)
+            keep_scale = l.dropout_value == 0.f ? 0.f : 1.f / l.dropout_value;
+        }
+      }
+      DLB_TRY(dlb_indrnn_forward_dropout(m->ctx, l.Z, norm ? &u : nullptr,
+                                         is_indrnn(l) ? m->params + l.first_recurrent : nullptr, l.af, mask,
+                                         keep_scale, l.A, last ? nullptr : l.A_lo, T, B, H));
     } else {
       DLB_TRY(dlb_activation_forward(m->ctx, l.Z, nullptr, l.af, nullptr, l.A, last ? nullptr : l.A_lo,
                                      TB, H));

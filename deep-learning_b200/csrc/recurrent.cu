@@ -257,9 +257,15 @@ __device__ __forceinline__ Vec<W> normalised(const Vec<W> &z, const TimeBrn &u, 
 // depend on step t, so the compiler can issue them ahead of the dependent math.
 // ref: Forward_Pass__FC_Ind_RNN__OpenMP (v1/learner/fwp_rec_mp.cpp L:762-800)
 // followed by the activation (L:335-348).
-template <int W, bool NORM, bool REC>
+// DROP: Bernoulli dropout of time step t, flags mask[t * n + unit], applied to
+// the stored output, so that the recurrence of step t + 1 reads the masked
+// value (fwp_mp.cpp L:1228-1262, L:4842-4868); kept units are multiplied by
+// keep_scale (1, or 1 / p for the inverted form); without a mask every unit is
+// (the inference form, fwp_rec_mp.cpp L:299-312).
+template <int W, bool NORM, bool REC, bool DROP>
 __global__ void __launch_bounds__(256)
     time_forward_kernel(const float *__restrict__ Z, TimeBrn u, const float *__restrict__ rec, int af,
+                        const uint8_t *__restrict__ mask, float keep_scale,
                         float *__restrict__ A, float *__restrict__ A_lo, int T, int rows, int n,
                         unsigned *amax) {
   const int nw = n / W;
@@ -286,6 +292,10 @@ __global__ void __launch_bounds__(256)
     for (int j = 0; j < W; ++j) {
       const float pre = (REC && t > 0) ? recur(y.v[j], w[j], h[j]) : y.v[j];
       h[j] = af_fire(af, pre);
+      if (DROP) {
+        const float f = mask ? (mask[(size_t)t * n + col + j] ? keep_scale : 0.f) : keep_scale;
+        h[j] = f == 0.f ? 0.f : (f == 1.f ? h[j] : h[j] * f);
+      }
       out.v[j] = h[j];
       lo.v[j] = tf32_lo(h[j]);
       mx = max(mx, abs_bits(h[j]));
@@ -458,8 +468,8 @@ dlb_status dlb_brn_time_forward_finalize(dlb_ctx *ctx, const double *sums, int g
 }
 
 dlb_status indrnn_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
-                              const float *recurrent, int af, float *A, float *A_lo, int seq_w,
-                              int rows, int n, unsigned *amax) {
+                              const float *recurrent, int af, const uint8_t *mask, float keep_scale,
+                              float *A, float *A_lo, int seq_w, int rows, int n, unsigned *amax) {
   DLB_REQUIRE(ctx && Z && A && seq_w > 0 && rows > 0 && n > 0, "dlb_indrnn_forward");
   TimeBrn p{};
   if (u) {
@@ -468,9 +478,16 @@ dlb_status indrnn_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_
   }
   const bool v4 = n % 4 == 0 && aligned16({Z, A, A_lo, p.mean, p.rs, p.d});
   const int grid = walk_grid((size_t)rows * (v4 ? n / 4 : n));
-#define LAUNCH(W, NORM, REC)                                                               \
-  time_forward_kernel<W, NORM, REC><<<grid, 256, 0, ctx->stream>>>(Z, p, recurrent, af, A, A_lo, \
-                                                                   seq_w, rows, n, amax)
+  const bool drop = mask != nullptr || keep_scale != 1.f;
+#define LAUNCH(W, NORM, REC)                                                                          \
+  do {                                                                                                \
+    if (drop)                                                                                         \
+      time_forward_kernel<W, NORM, REC, true><<<grid, 256, 0, ctx->stream>>>(                         \
+          Z, p, recurrent, af, mask, keep_scale, A, A_lo, seq_w, rows, n, amax);                      \
+    else                                                                                              \
+      time_forward_kernel<W, NORM, REC, false><<<grid, 256, 0, ctx->stream>>>(                        \
+          Z, p, recurrent, af, nullptr, 1.f, A, A_lo, seq_w, rows, n, amax);                          \
+  } while (0)
 #define PICK(W)                                                        \
   do {                                                                 \
     if (u && recurrent) LAUNCH(W, true, true);                         \
@@ -606,7 +623,17 @@ dlb_status dlb_indrnn_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_a
   const size_t total = (size_t)(seq_w > 0 ? seq_w : 0) * (rows > 0 ? rows : 0) * (n > 0 ? n : 0);
   TimePlanes p;
   DLB_TRY(p.begin(ctx, A, A_lo, total));
-  DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, A, p.kernel_arg, seq_w, rows, n, p.amax));
+  DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, nullptr, 1.f, A, p.kernel_arg, seq_w, rows, n, p.amax));
+  return p.finish(ctx, A, total);
+}
+
+dlb_status dlb_indrnn_forward_dropout(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
+                                      const float *recurrent, int af, const uint8_t *mask, float keep_scale,
+                                      float *A, float *A_lo, int seq_w, int rows, int n) {
+  const size_t total = (size_t)(seq_w > 0 ? seq_w : 0) * (rows > 0 ? rows : 0) * (n > 0 ? n : 0);
+  TimePlanes p;
+  DLB_TRY(p.begin(ctx, A, A_lo, total));
+  DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, mask, keep_scale, A, p.kernel_arg, seq_w, rows, n, p.amax));
   return p.finish(ctx, A, total);
 }
 

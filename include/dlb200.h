@@ -322,6 +322,15 @@ dlb_status dlb_brn_time_forward_finalize(dlb_ctx *ctx, const double *sums, int g
 dlb_status dlb_indrnn_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
                               const float *recurrent, int af, float *A, float *A_lo, int seq_w,
                               int rows, int n);
+/* The same walk with Bernoulli dropout: the output of time step t is masked by
+ * mask[t * n + unit] (kept units times keep_scale: 1, or 1 / p for the inverted
+ * form) before it is stored, so the recurrence of step t + 1 reads the masked
+ * value (fwp_mp.cpp L:1228-1262, L:4842-4868).  mask == NULL scales every unit
+ * by keep_scale, the inference form (fwp_rec_mp.cpp L:299-312). */
+dlb_status dlb_indrnn_forward_dropout(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
+                                      const float *recurrent, int af, const uint8_t *mask,
+                                      float keep_scale, float *A, float *A_lo, int seq_w, int rows,
+                                      int n);
 
 /* E holds dA on entry and dAF on return, t from seq_w-1 down to 0:
  *   f'_t = f'(pre_t, A_t), dAF_t = dA_t f'_t + recurrent f'_t dAF_{t+1}.

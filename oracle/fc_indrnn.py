@@ -30,6 +30,7 @@ from __future__ import annotations
 
 import numpy as np
 
+import fc_step
 from fc_step import (LOSS_CROSS_ENTROPY, NORM_NONE, OracleModel, af_derive, af_fire, brn_backward, brn_forward,
                      f32, loss_and_delta, optimizer_scalars, optimizer_update)
 
@@ -152,6 +153,17 @@ class IndRnnOracleModel(OracleModel):
                 else:
                     PRE[t] = y
                     A[t] = af_fire(l["af"], y)
+                # Bernoulli dropout of time step t: flags mask[t * units + u], applied
+                # in place, so that the recurrence of step t + 1 reads the masked
+                # output (fwp_mp.cpp L:1228-1262, L:4842-4868); at inference the
+                # keep probability scales instead (fwp_rec_mp.cpp L:299-312).
+                kind, value = l["dropout"]
+                if kind in (fc_step.DROPOUT_BERNOULLI, fc_step.DROPOUT_BERNOULLI_INVERTED) and i + 1 < len(self.layers):
+                    if not self.training:
+                        if kind == fc_step.DROPOUT_BERNOULLI:
+                            A[t] = (A[t] * f32(value)).astype(f32)
+                    else:
+                        A[t] = fc_step.apply_dropout(A[t], kind, value, l["mask"][t * H:(t + 1) * H])
             l.update(Z=Z, Y=Y, XH=XH, A=A, PRE=PRE)
             a = A
 

@@ -11,7 +11,7 @@ import fc_indrnn
 import fc_step
 import golden_io
 import util
-from enums import ACTIVATION
+from enums import ACTIVATION, LAYER_DROPOUT
 
 pytestmark = pytest.mark.gpu
 
@@ -48,7 +48,7 @@ def _kink_free(cfg, X, band=2e-6, tries=64):
         for _, s in configs.recurrent_slices(cfg):
             p0[s] = rng.uniform(0, 1, s.stop - s.start).astype(np.float32)
         ora.set_array("parameters", p0)
-        if util.near_kink(ora, cfg, X, {}, band) == 0:
+        if util.near_kink(ora, cfg, X, configs.dropout_masks(cfg), band) == 0:
             return p0
     raise AssertionError("no kink-free seed found")
 
@@ -252,9 +252,37 @@ def test_time_major_sums_and_clamp(gpu_ctx, T, B, n):
     assert ctx.sync() == 0
 
 
-def test_dropout_in_a_time_stepped_model_is_refused(gpu_ctx):
+@pytest.mark.parametrize("kind", [LAYER_DROPOUT.BERNOULLI, LAYER_DROPOUT.BERNOULLI_INVERTED], ids=["plain", "inverted"])
+@pytest.mark.parametrize("norm", [True, False], ids=["brn", "no_norm"])
+def test_bernoulli_dropout_through_time(gpu_ctx, kind, norm):
+    """A mask per time step on the stored outputs (the recurrence reads the masked
+    value), training and inference, against the CPU restatement (itself pinned
+    to the compiled reference)."""
+    cfg = configs.indrnn_stack(n_in=64, hidden=128, depth=2, n_out=32, seq_w=6, batch=32, norm=norm,
+                               dropout=(kind, 0.7))
+    B, last = cfg["batch"], len(cfg["layers"]) - 1
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    p0 = _kink_free(cfg, X)
+    ora = util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0)
+    mod = util.build(dlb200.Model(gpu_ctx), cfg, params=p0)
+    want = util.trace(ora, cfg, 1, X, Y, masks)
+    got = util.trace(mod, cfg, 1, X, Y, masks)
+    assert gpu_ctx.sync() == 0
+    _check(got, want)
+    assert not got["act1"].reshape(6, B, 128)[:, :, masks[1].reshape(6, 128)[0] == 0][0].any()
+    util.copy_trained_state(mod, ora, cfg)
+    out = []
+    for m in (ora, mod):
+        m.set_propagation(0)
+        m.forward_pass(B, X)
+        out.append(m.get_layer_outputs(last, B).reshape(-1))
+    assert util.rel_l2(out[1], out[0]) <= 1e-5
+
+
+def test_other_dropout_in_a_time_stepped_model_is_refused(gpu_ctx):
     cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=1, n_out=5, seq_w=4, batch=3)
     m = util.build(dlb200.Model(gpu_ctx), cfg)
-    m.set_dropout(1, 2, 0.5, False)
+    m.set_dropout(1, LAYER_DROPOUT.UOUT, 0.5, False)
     with pytest.raises(dlb200.DlbError):
         m.forward_pass(3, np.zeros((3, 24), np.float32))

@@ -95,6 +95,32 @@ def test_clip_gradient_widens_the_recurrent_bound_like_the_reference():
     _check(got, want)
 
 
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("kind", [2, 3], ids=["plain", "inverted"])
+@pytest.mark.parametrize("norm", [True, False], ids=["brn", "no_norm"])
+def test_bernoulli_dropout_through_time_matches_compiled_reference(kind, norm):
+    """Bernoulli dropout in a time-stepped model: flags mask[t * units + u] on
+    the stored output of step t, which the recurrence of step t + 1 reads
+    (fwp_mp.cpp L:1228-1262, L:4842-4868); nothing in the backward pass."""
+    cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=2, n_out=5, seq_w=4, batch=5, norm=norm, dropout=(kind, 0.7))
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    p0 = ref.get_array("parameters")
+    want = util.trace(ref, cfg, steps=3)
+    got = util.trace(util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0), cfg, steps=3)
+    _check(got, want)
+    # Inference: the plain form scales by the keep probability, the inverted form does nothing.
+    ora = util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0)
+    util.copy_trained_state(ref, ora, cfg)
+    X, _ = configs.synthetic_batch(dict(cfg, data_seed=5))
+    out = []
+    for m in (ref, ora):
+        m.train_begin(5)
+        m.set_propagation(0)
+        m.forward_pass(5, X)
+        out.append(m.get_layer_outputs(3, 5).reshape(-1))
+    assert util.rel_l2(out[1], out[0]) <= TOL_L2
+
+
 def test_parameter_layout():
     """An IndRNN layer's u follows its W; gamma starts at 0.1 for IndRNN layers."""
     cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=2, n_out=5, seq_w=4, batch=3)
