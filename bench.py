@@ -68,12 +68,39 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
-def gemm_traffic_per_launch():
-    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM
-    kernel at M = N = K = 4096 (9 of the 14 launches of a step have that shape),
-    from the ncu capture summarised in
-    profiles/gemm_x3_pair_kernel_4096x4096x4096.md: 337 MB + 55.8 MB."""
-    return 393.0e6
+def gemm_traffic(f16):
+    """(bytes, where from): DRAM bytes one launch of the product kernel moved
+    under ncu (read + written), from the record kept beside the profile
+    summaries for the operand form that ran; the capture is of the 4096^3
+    product, 9 of the 14 launches of a step."""
+    path = os.path.join(ROOT, "profiles", "gemm_traffic.json")
+    try:
+        with open(path) as f:
+            e = json.load(f)["f16x3" if f16 else "tf32x3"]
+        shape = "x".join(str(v) for v in e["shape"])
+        return e["dram_bytes_read"] + e["dram_bytes_write"], f"ncu capture of {e['kernel']} at {shape} (profiles/{e['summary']})"
+    except (OSError, KeyError, ValueError):
+        return None, "no capture on record"
+
+
+def gemm_algorithmic_bytes(cfg, rows, f16=True):
+    """Operand and result bytes of the FC products of one step, each counted
+    once: per product (M, N, K) two operand planes of 2 bytes (or the fp32
+    tensor and its residual plane) per element read, M x N floats written.
+    Returns (total bytes, number of products)."""
+    per_elem = 4 if f16 else 8
+    widths = [l["units"] for l in cfg["layers"] if l["type"] != configs.LAYER.RESIDUAL]
+    T = cfg.get("seq_w", 1)
+    total, count = 0, 0
+    for i in range(1, len(widths)):
+        fan_in, fan_out, m = widths[i - 1], widths[i], rows * T
+        shapes = [(m, fan_out, fan_in), (fan_out, fan_in, m)]        # forward, weight gradient
+        if i > 1:
+            shapes.append((m, fan_in, fan_out))                         # input gradient
+        for (M, N, K) in shapes:
+            total += per_elem * (M * K + N * K) + 4 * M * N
+            count += 1
+    return total, count
 
 
 class ClockSampler:
@@ -169,6 +196,8 @@ WORKLOADS = {
 
 
 def workload(args):
+    if args.workload == "optimizer_sweep":
+        raise SystemExit("optimizer_sweep has no model")
     if args.workload not in WORKLOADS:
         raise SystemExit(f"unknown workload {args.workload}")
     rows = args.rows or WORKLOADS[args.workload][0]
@@ -187,6 +216,8 @@ def workload_config(args, cfg, world, extra=None):
     out = {
         "workload": WORKLOADS[args.workload][2].format(units=units, seq_w=cfg.get("seq_w", 1)),
         "rows_per_gpu": cfg["batch"], "global_batch": cfg["batch"] * world, "parallelism": f"dp{world}",
+        "noise": "Bernoulli masks (and ShakeDrop draws) are inputs set once before the steps: the reference draws "
+                 "its masks once per Driver::train call, not per step",
         "l2": "per-step working set (weights, residual planes, gradients, three moment vectors, activations: "
               "1.4 GB and up) is larger than the 126 MB L2; no explicit flush",
     }
@@ -249,9 +280,13 @@ def cpu_reference_rate(cfg_full, rows, steps, warmup):
 def run_reference(args, rank, world):
     if rank != 0:
         return
+    if args.workload == "optimizer_sweep":
+        return reference_optimizer_sweep(args)
     cfg = workload(args)
-    sample_rows = WORKLOADS[args.workload][1]
-    if sample_rows is None:
+    # --rows asks for that many rows per step (4096 = the library arm's batch, at
+    # about half a minute per step on 16 cores); the default is a bounded sample.
+    sample_rows = args.rows or WORKLOADS[args.workload][1]
+    if WORKLOADS[args.workload][1] is None:
         print(json.dumps({"impl": "reference", "unavailable": "the reference's OpenMP step keeps one gradient copy "
                           "per thread; at this workload's 8.6e9 parameters that does not fit this host"}), flush=True)
         return
@@ -372,6 +407,9 @@ def run_ours(args, rank, local_rank, world):
     achieved = g_flops / (g_ms / 1e3) / 1e12 if g_ms > 0 else 0.0
     peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops")))
     f16 = ctx.gemm_kind() == 1
+    traffic, traffic_source = gemm_traffic(f16)
+    plain_stack = args.workload in ("deep_brn_mlp", "deep_brn_mlp_small")
+    algo_bytes, algo_count = gemm_algorithmic_bytes(cfg, rows, f16) if plain_stack else (0, 1)
     x3_sustained = peak / 3 if f16 else TF32_TFLOPS_SUSTAINED / 3
     x3_burst = float(peaks.get("bf16_tflops", peak)) / 3 if f16 else TF32_TFLOPS_BURST / 3
     line = {
@@ -389,7 +427,8 @@ def run_ours(args, rank, local_rank, world):
             "bound": "tensor",
             "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
             "peak_source": f"MEASURED_PEAKS.json bf16 dense, sustained ({peak_kind})",
-            "traffic": gemm_traffic_per_launch(),
+            "traffic": traffic, "traffic_source": traffic_source,
+            "algorithmic_bytes_avg_launch": algo_bytes / algo_count if plain_stack else None,
             "launches_timed": g_n, "avg_launch_ms": g_ms / g_n if g_n else None,
             "share_of_step": g_ms / ms if ms else None,
             # `achieved` counts 2*M*N*K per launch; the kernel issues three
@@ -409,6 +448,212 @@ def run_ours(args, rank, local_rank, world):
     print(json.dumps(line), flush=True)
 
 
+# ----------------------------------------------------------------------------
+# Optimizer-only workload: a flat fp32 vector sharded by index range, no exchange.
+SWEEP_SIZES = (1_000_000, 100_000_000, 1_000_000_000)
+# name -> (rule code of the C ABI, algorithmic bytes per element: read p, g, m, v
+# and write p, m, v, g <- 0; + 8 for the running maximum of AMSGrad / AMSBound)
+SWEEP_RULES = {"adam": (2, 32), "amsgrad": (5, 40), "adamax": (3, 32), "nosadam": (9, 32), "amsbound": (4, 40)}
+SWEEP_HYPER = (1e-3, 0.9, 0.999, 1e-8, 0.1, 0.1, 1e-3)
+
+
+def sweep_config(world, extra=None):
+    out = {"workload": "optimizer-only sweep over a flat fp32 vector of 1e6 / 1e8 / 1e9 elements, p ~ N(0, 0.02), "
+                       "g ~ N(0, 1e-3) refilled before every step (outside the timed kernel), zero moments, 10 steps "
+                       "each of Adam, AMSGrad, AdaMax, NosAdam (gamma 0.1), AMSBound (final_lr 0.1, gamma 1e-3)",
+           "parallelism": f"index ranges over {world} GPU(s), no exchange",
+           "l2": "1e8 and 1e9 elements: arrays of 0.4 to 4 GB each, larger than the 126 MB L2; 1e6 elements: a 256 MB "
+                 "buffer is written between timed steps to flush L2"}
+    if extra:
+        out.update(extra)
+    return out
+
+
+def run_optimizer_sweep(args, rank, local_rank, world):
+    import ctypes as C
+
+    import dlb200
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    ctx = dlb200.Context(local_rank)
+    L = ctx.L
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    def max_over_ranks(v):
+        if not dist:
+            return v
+        import torch
+
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    rng = np.random.default_rng(100 + rank)
+    block = rng.standard_normal(1 << 22, dtype=np.float32)
+    flush = ctx.empty(64 << 20)   # 256 MB
+    steps, warmup = args.steps, max(args.warmup, 3)
+    table, launches = {}, 0
+    sizes = [int(s) for s in args.sizes.split(",")] if args.sizes else SWEEP_SIZES
+    for size in sizes:
+        n = size // world // 4 * 4
+        bufs = {k: ctx.empty(n) for k in ("p0", "g0", "p", "g", "m", "v", "vh")}
+
+        def fill(dst, scale):
+            # One seeded block of normal draws repeated over the vector.
+            head = min(n, block.size)
+            dlb200.check(L.dlb_memcpy_h2d(ctx.h, dst.ptr, dlb200._ptr(np.ascontiguousarray(block[:head] * np.float32(scale))),
+                                          head * 4))
+            ctx.sync()
+            have = head
+            while have < n:
+                step_n = min(have, n - have)
+                dlb200.check(L.dlb_memcpy_d2d(ctx.h, dst.offset(have), dst.ptr, step_n * 4))
+                have += step_n
+            ctx.sync()
+
+        fill(bufs["p0"], 0.02)
+        fill(bufs["g0"], 1e-3)
+        table[str(size)] = {}
+        for name, (rule, bytes_per) in SWEEP_RULES.items():
+            dlb200.check(L.dlb_memcpy_d2d(ctx.h, bufs["p"].ptr, bufs["p0"].ptr, n * 4))
+            for k in ("m", "v", "vh"):
+                dlb200.check(L.dlb_memset(ctx.h, bufs[k].ptr, 0, n * 4))
+            hyper = (C.c_float * 8)(*SWEEP_HYPER, 1.0)
+            t, prev = C.c_float(0), C.c_float(0)
+            total_ms = 0.0
+            for it in range(warmup + steps):
+                k = dlb200.OptimizerScalars()
+                dlb200.check(L.dlb_optimizer_prepare(rule, hyper, C.byref(t), C.byref(prev), C.byref(k)))
+                dlb200.check(L.dlb_memcpy_d2d(ctx.h, bufs["g"].ptr, bufs["g0"].ptr, n * 4))
+                if size < 50_000_000:
+                    dlb200.check(L.dlb_memset(ctx.h, flush.ptr, it & 0xff, flush.nbytes))
+                if it == warmup:
+                    ctx.sync()
+                    if dist:
+                        dist.barrier()
+                    if rank == 0 and size == sizes[-1] and name == "adam":
+                        sampler.mark()
+                ctx.timer_start()
+                dlb200.check(L.dlb_optimizer_step(ctx.h, rule, C.byref(k), bufs["p"].ptr, bufs["g"].ptr, bufs["m"].ptr,
+                                                  bufs["v"].ptr, bufs["vh"].ptr, None, n))
+                ms = ctx.timer_stop()
+                if it >= warmup:
+                    total_ms += ms
+                    launches += 1
+            total_ms = max_over_ranks(total_ms)
+            gbs = bytes_per * n * world * steps / (total_ms / 1e3) / 1e9
+            table[str(size)][name] = {"gb_per_s": gbs, "gb_per_s_per_gpu": gbs / world, "ms_per_step": total_ms / steps,
+                                      "bytes_per_element": bytes_per}
+        if ctx.sync() != 0:
+            raise SystemExit("device status after the sweep")
+        for b in bufs.values():
+            b.free()
+
+    # End to end at the middle size: the gradient arrives from pinned host memory
+    # every step and the first parameters are read back.
+    e2e = None
+    size = sizes[min(1, len(sizes) - 1)]
+    n = size // world // 4 * 4
+    gh = dlb200.pinned_empty(n)
+    gh[...] = np.resize(block * np.float32(1e-3), n)
+    bufs = {k: ctx.zeros(n) for k in ("p", "g", "m", "v", "vh")}
+    rule, bytes_per = SWEEP_RULES["amsbound"]
+    hyper = (C.c_float * 8)(*SWEEP_HYPER, 1.0)
+    t, prev = C.c_float(0), C.c_float(0)
+    back = np.zeros(2, np.float32)
+    for it in range(2 + steps):
+        if it == 2:
+            ctx.sync()
+            if dist:
+                dist.barrier()
+            t0 = time.perf_counter()
+        k = dlb200.OptimizerScalars()
+        dlb200.check(L.dlb_optimizer_prepare(rule, hyper, C.byref(t), C.byref(prev), C.byref(k)))
+        dlb200.check(L.dlb_memcpy_h2d(ctx.h, bufs["g"].ptr, dlb200._ptr(gh), n * 4))
+        dlb200.check(L.dlb_optimizer_step(ctx.h, rule, C.byref(k), bufs["p"].ptr, bufs["g"].ptr, bufs["m"].ptr,
+                                          bufs["v"].ptr, bufs["vh"].ptr, None, n))
+        dlb200.check(L.dlb_memcpy_d2h(ctx.h, dlb200._ptr(back), bufs["p"].ptr, 8))
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    e2e = {"value": bytes_per * n * world * steps / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(n * 4),
+           "d2h_bytes_per_step": 8, "ms_per_step": e2e_s / steps * 1e3,
+           "what": f"AMSBound over {size:.0e} elements with the gradient copied from pinned host memory each step"}
+    clocks = sampler.stop() if rank == 0 else None
+    if rank != 0:
+        return
+    peaks, peak_kind = measured_peaks()
+    peak = float(peaks["hbm_gbs"])
+    big = table[str(sizes[-1])]
+    total_bytes = sum(v["bytes_per_element"] for v in big.values())
+    total_ms = sum(v["ms_per_step"] for v in big.values())
+    n_big = sizes[-1] // world // 4 * 4
+    value = total_bytes * n_big * world / (total_ms / 1e3) / 1e9
+    for rules in table.values():
+        for v in rules.values():
+            v["frac_of_hbm_peak"] = v["gb_per_s_per_gpu"] / peak
+    line = {
+        "metric": "optimizer update HBM GB/s (flat fp32 vector)", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": total_ms / len(big), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": sweep_config(world, {"value_is": f"all GPUs together at {sizes[-1]:.0e} elements, the five rules "
+                                                   "weighted by their time"}),
+        "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+        "roofline": {"kernel": "optimizer_kernel<rule> (one streaming pass over p, g, m, v[, v_hat])", "bound": "hbm",
+                     "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
+                     "peak_source": f"MEASURED_PEAKS.json copy bandwidth ({peak_kind})", "traffic": None,
+                     "traffic_source": "no capture at this size; the in-step pass is in profiles/elementwise_kernels_deep_brn_mlp.md"},
+        "sweep": table,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_optimizer_sweep(min(100_000_000, sizes[-1]), 3)
+    print(json.dumps(line), flush=True)
+
+
+def cpu_optimizer_sweep(n, steps):
+    """GB/s of the reference's own update loops (Update_Parameters__*__OpenMP) on
+    this host: `steps` steps of each rule the reference implements (AdaMax has no
+    loop there) over n elements."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ref_binding
+
+    if not ref_binding.available():
+        return {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": "oracle/_ref is not built"}
+    rng = np.random.default_rng(0)
+    block = rng.standard_normal(1 << 22, dtype=np.float32)
+    p = np.resize(block * np.float32(0.02), n)
+    g = np.resize(block * np.float32(1e-3), n)
+    total_bytes, total_s, per_rule = 0.0, 0.0, {}
+    for name, (rule, bytes_per) in SWEEP_RULES.items():
+        if name == "adamax":
+            continue
+        m, v, vh = (np.full(n, 0, np.float32) for _ in range(3))   # touched, not lazily mapped
+        secs = ref_binding.optimizer_sweep(rule, p.copy(), g, m, v, vh, steps, list(SWEEP_HYPER))
+        per_rule[name] = bytes_per * n * steps / secs / 1e9
+        total_bytes += bytes_per * n * steps
+        total_s += secs
+    return {"value": total_bytes / total_s / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "reference",
+            "per_rule_gb_per_s": per_rule,
+            "sample": f"{steps} steps of Adam, AMSGrad, NosAdam, AMSBound over {n:.0e} elements (the reference has no "
+                      f"AdaMax loop); host has {os.cpu_count()} logical cores"}
+
+
+def reference_optimizer_sweep(args):
+    base = cpu_optimizer_sweep(100_000_000, max(1, args.steps))
+    line = {"impl": "reference", "metric": "optimizer update HBM GB/s (flat fp32 vector)", "value": base["value"],
+            "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": sweep_config(1, {"parallelism": f"openmp x{base['cores']}"}), "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -419,10 +664,13 @@ def main():
     ap.add_argument("--rows", type=int, default=0, help="rows per GPU (default: the workload's own)")
     ap.add_argument("--seq-w", type=int, default=256, help="sequence length of the indrnn workload")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sizes", default="", help="optimizer_sweep: comma-separated vector lengths (default 1e6,1e8,1e9)")
     args = ap.parse_args()
     rank, local_rank, world = env_int("RANK", 0), env_int("LOCAL_RANK", 0), env_int("WORLD_SIZE", 1)
     if args.impl == "reference":
         run_reference(args, rank, world)
+    elif args.workload == "optimizer_sweep":
+        run_optimizer_sweep(args, rank, local_rank, world)
     else:
         run_ours(args, rank, local_rank, world)
 

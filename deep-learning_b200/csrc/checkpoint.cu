@@ -657,7 +657,7 @@ dlb_status dlb_model_load(dlb_model *m, const char *path_params, const char *pat
   }
   for (size_t i = 1; i + 1 < n_layers; ++i)
     if (L[i].norm != DLB_NORM_NONE) DLB_TRY(dlb_model_set_layer_normalization(m, i, L[i].norm));
-  for (size_t i = 1; i + 1 < n_layers; ++i)
+  for (size_t i = 0; i + 1 < n_layers; ++i)
     if (L[i].dropout != DLB_DROPOUT_NONE)
       DLB_TRY(dlb_model_set_dropout(m, i, L[i].dropout, (float)L[i].dropout_value, 0));
   if (delay) DLB_TRY(dlb_model_set_seq_w(m, delay));

@@ -41,6 +41,32 @@ struct dlb_ctx {
     float *scale;
   };
   std::map<uintptr_t, PlaneEntry> planes;
+  // Bumped by dlb_ctx_set_gemm_kind, which also drops every registration above:
+  // a model compares it with the value it last split its weights under and
+  // splits them again in the new form.
+  uint64_t plane_generation = 0;
+  // TMA descriptors of the operands seen so far (the shapes of a model repeat
+  // every step), keyed by everything cuTensorMapEncodeTiled is given.
+  struct TmapKey {
+    uintptr_t ptr;
+    uint64_t mn, k, ld;
+    uint32_t box_k, box_mn;
+    int es, mn_major;
+    bool operator<(const TmapKey &o) const {
+      if (ptr != o.ptr) return ptr < o.ptr;
+      if (mn != o.mn) return mn < o.mn;
+      if (k != o.k) return k < o.k;
+      if (ld != o.ld) return ld < o.ld;
+      if (box_k != o.box_k) return box_k < o.box_k;
+      if (box_mn != o.box_mn) return box_mn < o.box_mn;
+      if (es != o.es) return es < o.es;
+      return mn_major < o.mn_major;
+    }
+  };
+  struct TmapBlob {
+    alignas(64) unsigned char bytes[128];
+  };
+  std::map<TmapKey, TmapBlob> tmaps;
   float *scale_pool = nullptr;   // SCALE_SLOTS slots of 4 floats: s, 1/s, |x|max bits, unused
   std::vector<int> scale_free;
   std::map<uintptr_t, size_t> allocs;  // dlb_malloc'd blocks, to retire plane entries on free
@@ -169,5 +195,6 @@ dlb_status optimizer_step_amax(dlb_ctx *ctx, int rule, const dlb_optimizer_scala
 dlb_status planes_begin(dlb_ctx *ctx, const float *x, float *planes, size_t n, float **slot_out);
 dlb_status planes_finish(dlb_ctx *ctx, const float *x, float *planes, size_t n, float *slot);
 constexpr int SCALE_SLOTS = 8192;
+constexpr int MAX_DEVICES = 64;  // device indices a process may hold contexts on
 
 }  // namespace dlb

@@ -423,6 +423,12 @@ dlb_status dlb_memcpy_d2d(dlb_ctx *ctx, void *dev_dst, const void *dev_src, size
   return DLB_OK;
 }
 
+dlb_status dlb_device_mem_info(size_t *free_bytes, size_t *total_bytes) {
+  DLB_REQUIRE(free_bytes && total_bytes, "dlb_device_mem_info: null");
+  DLB_CUDA(cudaMemGetInfo(free_bytes, total_bytes));
+  return DLB_OK;
+}
+
 dlb_status dlb_host_alloc(void **host_ptr, size_t bytes) {
   DLB_REQUIRE(host_ptr, "dlb_host_alloc: null");
   DLB_CUDA(cudaMallocHost(host_ptr, bytes ? bytes : 16));

@@ -4,6 +4,8 @@
 // 128-bit accesses; per-unit (column) reductions go through partials in the
 // context scratch arena and are finished in double in a fixed order, so results
 // do not depend on block scheduling.
+#include <mutex>
+
 #include "common.cuh"
 #include "math.cuh"
 
@@ -89,10 +91,10 @@ __global__ void reduce_partials_kernel(const double *partials, int chunks, int t
 // (what the kernel's registers allow, at most CR_MAX_PER_SM; a grid larger than
 // one wave leaves a partial second wave that costs a whole one), chunks of at
 // least 64 rows.
-static void column_reduce_plan(dlb_ctx *ctx, int rows, int n, int per_sm, int *chunks, int *rows_per_chunk) {
+static void column_reduce_plan(int sm_count, int rows, int n, int per_sm, int *chunks, int *rows_per_chunk) {
   const int col_blocks = ceil_div(n, CR_COLS);
-  int c = per_sm == CR_MAX_PER_SM ? ceil_div(ctx->sm_count * per_sm, col_blocks)
-                                  : max(1, ctx->sm_count * per_sm / col_blocks);
+  int c = per_sm == CR_MAX_PER_SM ? ceil_div(sm_count * per_sm, col_blocks)
+                                  : max(1, sm_count * per_sm / col_blocks);
   c = max(1, min(c, ceil_div(rows, 64)));
   *rows_per_chunk = ceil_div(ceil_div(rows, c), CR_LANES_Y) * CR_LANES_Y;
   *chunks = ceil_div(rows, *rows_per_chunk);
@@ -102,24 +104,31 @@ static void column_reduce_plan(dlb_ctx *ctx, int rows, int n, int per_sm, int *c
 // sums behind them in the same scratch request).
 static size_t column_reduce_partial_bytes(dlb_ctx *ctx, int nsum, int rows, int n) {
   int chunks, rpc;
-  column_reduce_plan(ctx, rows, n, CR_MAX_PER_SM, &chunks, &rpc);
+  column_reduce_plan(ctx->sm_count, rows, n, CR_MAX_PER_SM, &chunks, &rpc);
   return align_up((size_t)chunks * nsum * n * sizeof(double), 256);
+}
+
+// Blocks of one reduction kernel an SM of the current device holds, at most
+// CR_MAX_PER_SM.  The query allocates nothing.
+template <int NSUM, class Op>
+static int column_reduce_per_sm() {
+  int blocks = CR_MAX_PER_SM;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, column_reduce_kernel<NSUM, Op>,
+                                                    CR_LANES_X * CR_LANES_Y, 0) != cudaSuccess) {
+    cudaGetLastError();
+    blocks = CR_MAX_PER_SM;
+  }
+  return max(1, min(blocks, CR_MAX_PER_SM));
 }
 
 template <int NSUM, class Op>
 static dlb_status column_reduce(dlb_ctx *ctx, Op op, int rows, int n, double *out) {
   const int col_blocks = ceil_div(n, CR_COLS);
-  static const int per_sm = [] {
-    int blocks = CR_MAX_PER_SM;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, column_reduce_kernel<NSUM, Op>,
-                                                      CR_LANES_X * CR_LANES_Y, 0) != cudaSuccess) {
-      cudaGetLastError();
-      blocks = CR_MAX_PER_SM;
-    }
-    return max(1, min(blocks, CR_MAX_PER_SM));
-  }();
+  static int per_sm_of[MAX_DEVICES] = {};  // 0: not asked yet on that device
+  int &per_sm = per_sm_of[ctx->device];
+  if (per_sm == 0) per_sm = column_reduce_per_sm<NSUM, Op>();
   int chunks, rows_per_chunk;
-  column_reduce_plan(ctx, rows, n, per_sm, &chunks, &rows_per_chunk);
+  column_reduce_plan(ctx->sm_count, rows, n, per_sm, &chunks, &rows_per_chunk);
   void *scr = nullptr;
   DLB_TRY(scratch(ctx, column_reduce_partial_bytes(ctx, NSUM, rows, n), &scr));
   double *partials = static_cast<double *>(scr);
@@ -1023,29 +1032,37 @@ namespace dlb {
 
 static __device__ __align__(256) double g_noalloc_partials[DLB_NOALLOC_SCRATCH_DOUBLES];
 
-constexpr int NOALLOC_MAX_DEVICES = 64;
 struct NoallocDevice {
+  std::once_flag once;
+  dlb_status status = DLB_ERR_INVALID;
   double *partials = nullptr;  // device address of g_noalloc_partials on this device
   int sm_count = 0;
+  int per_sm = 0;              // resident blocks of the sums kernel per SM
 };
-static NoallocDevice g_noalloc_devices[NOALLOC_MAX_DEVICES];
+static NoallocDevice g_noalloc_devices[MAX_DEVICES];
 
-// Set-up for the current device: address of the array and SM count.  Neither
-// call allocates.  Done on the first call per device.
+static dlb_status noalloc_setup(NoallocDevice *d, int dev) {
+  double *ptr = nullptr;
+  DLB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_noalloc_partials));
+  int sms = 0;
+  DLB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  DLB_REQUIRE(ptr && sms > 0, "dlb_brn_forward_sums_noalloc: device set-up");
+  d->per_sm = column_reduce_per_sm<2, SumSqOp>();
+  d->sm_count = sms;
+  d->partials = ptr;
+  return DLB_OK;
+}
+
+// Set-up for the current device, once per device whichever host thread comes
+// first: address of the array, SM count, resident blocks per SM.  None of the
+// three calls allocates.
 static dlb_status noalloc_device(NoallocDevice **out) {
   int dev = -1;
   DLB_CUDA(cudaGetDevice(&dev));
-  DLB_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, "dlb_brn_forward_sums_noalloc: device index");
+  DLB_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "dlb_brn_forward_sums_noalloc: device index");
   NoallocDevice &d = g_noalloc_devices[dev];
-  if (!d.partials) {
-    double *ptr = nullptr;
-    DLB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_noalloc_partials));
-    int sms = 0;
-    DLB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    DLB_REQUIRE(ptr && sms > 0, "dlb_brn_forward_sums_noalloc: device set-up");
-    d.sm_count = sms;
-    d.partials = ptr;
-  }
+  std::call_once(d.once, [&] { d.status = noalloc_setup(&d, dev); });
+  DLB_REQUIRE(d.status == DLB_OK, "dlb_brn_forward_sums_noalloc: the set-up of this device failed");
   *out = &d;
   return DLB_OK;
 }
@@ -1059,13 +1076,18 @@ extern "C" dlb_status dlb_brn_forward_sums_noalloc(const float *Z, int rows, int
               "dlb_brn_forward_sums_noalloc: Z must be 16-byte aligned");
   NoallocDevice *dev = nullptr;
   DLB_TRY(noalloc_device(&dev));
-  // Same chunking rule as the allocating entry point, so both give the same
-  // sums bit for bit.
+  // Z and sums must be memory of the current device (the array used below is).
+  cudaPointerAttributes attr;
+  DLB_CUDA(cudaPointerGetAttributes(&attr, Z));
+  int cur = -1;
+  DLB_CUDA(cudaGetDevice(&cur));
+  DLB_REQUIRE(attr.type == cudaMemoryTypeDevice && attr.device == cur,
+              "dlb_brn_forward_sums_noalloc: Z is not memory of the current device");
+  // The chunking of the allocating entry point (same plan function, same
+  // occupancy figure), so both add the same partial sums in the same order.
   const int col_blocks = ceil_div(n_units, CR_COLS);
-  int chunks = ceil_div(dev->sm_count * 4, col_blocks);
-  chunks = max(1, min(chunks, ceil_div(rows, 64)));
-  const int rows_per_chunk = ceil_div(ceil_div(rows, chunks), CR_LANES_Y) * CR_LANES_Y;
-  chunks = ceil_div(rows, rows_per_chunk);
+  int chunks, rows_per_chunk;
+  column_reduce_plan(dev->sm_count, rows, n_units, dev->per_sm, &chunks, &rows_per_chunk);
   const size_t need = (size_t)chunks * 2 * (size_t)n_units;
   if (need > (size_t)DLB_NOALLOC_SCRATCH_DOUBLES) {
     set_error("dlb_brn_forward_sums_noalloc: %d rows x %d units need %zu partial sums, the built-in "

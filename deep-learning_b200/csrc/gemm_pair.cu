@@ -373,29 +373,19 @@ dlb_status launch_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B,
   using P = PairPlan<STAGES>;
   CUtensorMap ta, tal, tb, tbl;
   bool ok = true;
-  if (A_MN) {
-    ok &= tmap_mn_major(&ta, A.h_hi, 2, M, K, A.stride_k, PBK, BM);
-    ok &= tmap_mn_major(&tal, A.h_lo, 2, M, K, A.stride_k, PBK, BM);
-  } else {
-    ok &= tmap_k_major(&ta, A.h_hi, 2, M, K, A.stride_mn, PBK, BM);
-    ok &= tmap_k_major(&tal, A.h_lo, 2, M, K, A.stride_mn, PBK, BM);
-  }
-  if (B_MN) {
-    ok &= tmap_mn_major(&tb, B.h_hi, 2, N, K, B.stride_k, PBK, HALF_N);
-    ok &= tmap_mn_major(&tbl, B.h_lo, 2, N, K, B.stride_k, PBK, HALF_N);
-  } else {
-    ok &= tmap_k_major(&tb, B.h_hi, 2, N, K, B.stride_mn, PBK, HALF_N);
-    ok &= tmap_k_major(&tbl, B.h_lo, 2, N, K, B.stride_mn, PBK, HALF_N);
-  }
+  ok &= tmap_cached(ctx, &ta, A_MN, A.h_hi, 2, M, K, A_MN ? A.stride_k : A.stride_mn, PBK, BM);
+  ok &= tmap_cached(ctx, &tal, A_MN, A.h_lo, 2, M, K, A_MN ? A.stride_k : A.stride_mn, PBK, BM);
+  ok &= tmap_cached(ctx, &tb, B_MN, B.h_hi, 2, N, K, B_MN ? B.stride_k : B.stride_mn, PBK, HALF_N);
+  ok &= tmap_cached(ctx, &tbl, B_MN, B.h_lo, 2, N, K, B_MN ? B.stride_k : B.stride_mn, PBK, HALF_N);
   if (!ok) {
     set_error("gemm_pair: cuTensorMapEncodeTiled rejected an operand");
     return DLB_ERR_CUDA;
   }
   auto kernel = gemm_x3_pair_kernel<STAGES, CHUNK_KB, A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[MAX_DEVICES] = {};  // the attribute belongs to the (function, device) pair
+  if (!attr_set[ctx->device]) {
     DLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::TOTAL));
-    attr_set = true;
+    attr_set[ctx->device] = true;
   }
   // Pairs of SMs work through the 256 x 256 tiles in rounds.  The tiles of the
   // last partial round are cut along k into pieces that add into a zeroed

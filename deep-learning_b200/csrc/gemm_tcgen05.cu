@@ -39,6 +39,7 @@
 // flight, frees its tensor memory and returns.
 #include <cuda.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "tc_ptx.cuh"
@@ -410,6 +411,27 @@ bool tmap_mn_major(CUtensorMap *m, const void *ptr, int es, uint64_t mn, uint64_
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The descriptor of an operand, from the context's cache when the same
+// (address, shape, box) was encoded before: a descriptor depends on nothing else.
+bool tmap_cached(dlb_ctx *ctx, CUtensorMap *out, bool mn_major, const void *ptr, int es, uint64_t mn,
+                 uint64_t k, uint64_t ld, uint32_t box_k, uint32_t box_mn) {
+  static_assert(sizeof(CUtensorMap) == sizeof(dlb_ctx::TmapBlob), "descriptor size");
+  const dlb_ctx::TmapKey key{reinterpret_cast<uintptr_t>(ptr), mn, k, ld, box_k, box_mn, es, mn_major ? 1 : 0};
+  auto it = ctx->tmaps.find(key);
+  if (it != ctx->tmaps.end()) {
+    memcpy(out, it->second.bytes, sizeof(CUtensorMap));
+    return true;
+  }
+  const bool ok = mn_major ? tmap_mn_major(out, ptr, es, mn, k, ld, box_k, box_mn)
+                           : tmap_k_major(out, ptr, es, mn, k, ld, box_k, box_mn);
+  if (!ok) return false;
+  if (ctx->tmaps.size() >= 4096) ctx->tmaps.clear();
+  dlb_ctx::TmapBlob blob;
+  memcpy(blob.bytes, out, sizeof(CUtensorMap));
+  ctx->tmaps.emplace(key, blob);
+  return true;
+}
+
 namespace {
 
 // What TMA can address: 16-byte aligned base and row pitch; an MN-major extent
@@ -451,29 +473,20 @@ dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, floa
   const void *b_lo = ES == 4 ? (const void *)B.lo : (const void *)B.h_lo;
   CUtensorMap ta, tal, tb, tbl;
   bool ok = true;
-  if (A_MN) {
-    ok &= tmap_mn_major(&ta, a_hi, ES, M, K, A.stride_k, BK, BM);
-    ok &= tmap_mn_major(&tal, a_lo, ES, M, K, A.stride_k, BK, BM);
-  } else {
-    ok &= tmap_k_major(&ta, a_hi, ES, M, K, A.stride_mn, BK, BM);
-    ok &= tmap_k_major(&tal, a_lo, ES, M, K, A.stride_mn, BK, BM);
-  }
-  if (B_MN) {
-    ok &= tmap_mn_major(&tb, b_hi, ES, N, K, B.stride_k, BK, BN);
-    ok &= tmap_mn_major(&tbl, b_lo, ES, N, K, B.stride_k, BK, BN);
-  } else {
-    ok &= tmap_k_major(&tb, b_hi, ES, N, K, B.stride_mn, BK, BN);
-    ok &= tmap_k_major(&tbl, b_lo, ES, N, K, B.stride_mn, BK, BN);
-  }
+  ok &= tmap_cached(ctx, &ta, A_MN, a_hi, ES, M, K, A_MN ? A.stride_k : A.stride_mn, BK, BM);
+  ok &= tmap_cached(ctx, &tal, A_MN, a_lo, ES, M, K, A_MN ? A.stride_k : A.stride_mn, BK, BM);
+  ok &= tmap_cached(ctx, &tb, B_MN, b_hi, ES, N, K, B_MN ? B.stride_k : B.stride_mn, BK, BN);
+  ok &= tmap_cached(ctx, &tbl, B_MN, b_lo, ES, N, K, B_MN ? B.stride_k : B.stride_mn, BK, BN);
   if (!ok) {
     set_error("gemm_tcgen05: cuTensorMapEncodeTiled rejected an operand");
     return DLB_ERR_CUDA;
   }
   auto kernel = gemm_x3_kernel<BN, BK, STAGES, CHUNK_KB, A_MN, B_MN, ES>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // The attribute belongs to the (function, device) pair: once per device.
+  static bool attr_set[MAX_DEVICES] = {};
+  if (!attr_set[ctx->device]) {
     DLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::TOTAL));
-    attr_set = true;
+    attr_set[ctx->device] = true;
   }
   // One CTA per SM is resident, so the tiles run in waves of sm_count.  When
   // the last wave would fill at most half of the SMs, its tiles are split in
@@ -486,11 +499,11 @@ dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, floa
     const char *e = getenv("DLB_GEMM_SPLIT");
     return !(e && e[0] == '0');
   }();
-  // CTAs of this launch: one per SM, less the SMs left to a concurrent
-  // collective when the context is part of a multi-GPU job (the persistent
-  // CTAs would otherwise hold every SM until the product ends and the
-  // gradient all-reduce on the second stream could not start).
-  const int lanes = max(1, ctx->sm_count - (ctx->world > 1 ? ctx->gemm_reserve_sms : 0));
+  // CTAs of this launch: one per SM, less the SMs left to a collective while one
+  // is in flight on the second stream (the persistent CTAs would otherwise hold
+  // every SM until the product ends and the gradient all-reduce could not
+  // start).
+  const int lanes = max(1, ctx->sm_count - (ctx->comm_pending ? ctx->gemm_reserve_sms : 0));
   int split_tiles = 0;
   const int rest = tiles % lanes;
   if (split_enabled && !ep.accumulate && rest > 0 && 2 * rest <= lanes &&

@@ -316,6 +316,10 @@ dlb_status check_supported(dlb_model *m) {
     return DLB_ERR_INVALID;
   }
   const bool stepped = time_stepped(m);
+  if (stepped && m->layers[0].dropout != DLB_DROPOUT_NONE) {
+    set_error("model: dropout on the inputs of a time-stepped (recurrent) model is outside the supported path");
+    return DLB_ERR_UNSUPPORTED;
+  }
   for (size_t i = 1; i < m->layers.size(); ++i) {
     const LayerRT &l = m->layers[i];
     if (stepped) {
@@ -369,6 +373,12 @@ dlb_status check_supported(dlb_model *m) {
 }
 
 dlb_status refresh_weight_residuals(dlb_model *m) {
+  // A change of the context's operand form since the last split makes the
+  // weight planes stale.
+  if (m->plane_generation != m->ctx->plane_generation) {
+    m->plane_generation = m->ctx->plane_generation;
+    m->params_lo_valid = false;
+  }
   if (m->params_lo_valid || m->total_weights == 0) return DLB_OK;
   // One plane buffer per layer, so that every weight matrix gets a scale of its own.
   for (size_t i = 1; i < m->layers.size(); ++i) {
@@ -800,6 +810,12 @@ dlb_status dlb_model_set_dropout(dlb_model *m, size_t layer, int type, float val
     }
     // Bernoulli: keep probability; UOut: half-width beta of the noise U(-beta, beta).
     if (type != DLB_DROPOUT_NONE) DLB_REQUIRE(value0 > 0.f && value0 <= 1.f, "set_dropout: value in (0, 1]");
+    // The input layer's dropout acts on the batch as it is assigned
+    // (v1/learner/assign_inputs.cpp L:94-130); the Bernoulli kinds are built.
+    if (layer == 0 && type == DLB_DROPOUT_UOUT) {
+      set_error("set_dropout: UOut on the input layer is outside the supported path");
+      return DLB_ERR_UNSUPPORTED;
+    }
   }
   if (scale_weights) {
     set_error("set_dropout: scale_weights=true is not supported (on a fresh layer the reference "
@@ -1113,7 +1129,7 @@ dlb_status dlb_model_draw_noise(dlb_model *m, size_t rows, uint64_t seed, uint32
   DLB_REQUIRE(m && rows > 0, "draw_noise");
   DLB_TRY(check_supported(m));
   DLB_TRY(ensure_masks(m));
-  for (size_t i = 1; i < m->layers.size(); ++i) {
+  for (size_t i = 0; i < m->layers.size(); ++i) {
     LayerRT &l = m->layers[i];
     const uint32_t stream = 4u * (uint32_t)i;
     switch (l.dropout) {
@@ -1172,6 +1188,15 @@ dlb_status dlb_model_set_global_batch(dlb_model *m, size_t global_rows) {
   return DLB_OK;
 }
 
+// Number of examples of the training set, the `training_size` that the one-call
+// steps pass to update_weights (Model::normalized_wd divides the batch size by
+// it, v1/learner/train.cpp L:278-283).  0 (default): one batch is the whole set.
+dlb_status dlb_model_set_training_size(dlb_model *m, size_t training_size) {
+  DLB_REQUIRE(m, "null");
+  m->training_size = training_size;
+  return DLB_OK;
+}
+
 dlb_status dlb_model_forward_pass_device(dlb_model *m, size_t rows, const float *X_dev) {
   DLB_REQUIRE(m && X_dev && rows > 0, "forward_pass_device");
   DLB_TRY(check_supported(m));
@@ -1185,7 +1210,23 @@ dlb_status dlb_model_forward_pass_device(dlb_model *m, size_t rows, const float 
     return forward_layers(m, rows);
   }
   if (X_dev != m->input) DLB_TRY(dlb_memcpy_d2d(m->ctx, m->input, X_dev, n * sizeof(float)));
-  DLB_TRY(dlb_split_planes(m->ctx, m->input, m->input_lo, n));
+  // Dropout on the inputs acts on the model's copy of the batch, in place
+  // (Model::assign_inputs_fwp_mp, v1/learner/assign_inputs.cpp L:94-130): the
+  // Bernoulli kinds by the input layer's mask in training, the plain kind by its
+  // keep probability at inference.
+  const LayerRT &in = m->layers[0];
+  const bool bern = in.dropout == DLB_DROPOUT_BERNOULLI || in.dropout == DLB_DROPOUT_BERNOULLI_INVERTED;
+  if (bern && m->propagation == DLB_PROPAGATION_TRAINING) {
+    dlb_dropout_desc dp{in.dropout, in.dropout_value, in.mask, nullptr};
+    DLB_TRY(dlb_activation_forward(m->ctx, m->input, nullptr, DLB_AF_LINEAR, &dp, m->input, m->input_lo,
+                                   (int)rows, (int)n_in(m)));
+  } else if (in.dropout == DLB_DROPOUT_BERNOULLI) {
+    dlb_dropout_desc dp{DROPOUT_INFERENCE_SCALE, in.dropout_value, nullptr, nullptr};
+    DLB_TRY(dlb_activation_forward(m->ctx, m->input, nullptr, DLB_AF_LINEAR, &dp, m->input, m->input_lo,
+                                   (int)rows, (int)n_in(m)));
+  } else {
+    DLB_TRY(dlb_split_planes(m->ctx, m->input, m->input_lo, n));
+  }
   return forward_layers(m, rows);
 }
 
@@ -1701,7 +1742,7 @@ dlb_status dlb_model_train_step_device(dlb_model *m, size_t rows, const float *X
   DLB_TRY(dlb_model_compute_error_device(m, rows, Y_dev));
   DLB_TRY(backward_update_merge(m, rows));
   const size_t g = m->global_rows ? m->global_rows : rows;
-  return dlb_model_update_weights(m, g, g);
+  return dlb_model_update_weights(m, g, m->training_size ? m->training_size : g);
 }
 
 dlb_status dlb_model_train_step(dlb_model *m, size_t rows, const float *X_host,
@@ -1719,7 +1760,7 @@ dlb_status dlb_model_train_step(dlb_model *m, size_t rows, const float *X_host,
   DLB_TRY(backward_update_merge(m, rows));
   if (loss) DLB_TRY(dlb_model_get_loss(m, loss));
   const size_t g = m->global_rows ? m->global_rows : rows;
-  return dlb_model_update_weights(m, g, g);
+  return dlb_model_update_weights(m, g, m->training_size ? m->training_size : g);
 }
 
 // Input side of the mini-batch loop, MiniBatch::train_mp
@@ -1780,7 +1821,7 @@ dlb_status dlb_model_train_step_staged(dlb_model *m, double *loss) {
   // update then runs while the host prepares the next call.
   if (loss) DLB_TRY(dlb_model_get_loss(m, loss));
   const size_t g = m->global_rows ? m->global_rows : rows;
-  return dlb_model_update_weights(m, g, g);
+  return dlb_model_update_weights(m, g, m->training_size ? m->training_size : g);
 }
 
 dlb_status dlb_model_get_layer_outputs(dlb_model *m, size_t layer, size_t rows, float *host_out) {

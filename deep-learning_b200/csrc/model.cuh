@@ -74,6 +74,7 @@ struct dlb_model {
   size_t total_weights = 0, total_bias = 0, total_norm_units = 0, total_parameters = 0;
   bool any_norm = false;
   size_t max_batch = 0, alloc_rows = 0, global_rows = 0;
+  size_t training_size = 0;  // examples of the training set; 0: one batch is the whole set
   unsigned weight_seed = 5489u;
   std::mt19937 weight_gen;
   // Flat device vectors.
@@ -111,6 +112,7 @@ struct dlb_model {
   double *loss_sum = nullptr;
   size_t loss_rows = 0;  // rows accumulated since reset_loss
   bool params_lo_valid = false;
+  uint64_t plane_generation = 0;  // the context's value when the weights were last split
   // Inside train_step the step is known to be a single chunk, so each layer's
   // weight gradient is all-reduced as soon as its GEMM has been enqueued.
   bool overlap_grad_allreduce = false;

@@ -180,6 +180,13 @@ extern "C" {
 
 dlb_status dlb_ctx_set_gemm_kind(dlb_ctx *ctx, int kind) {
   DLB_REQUIRE(ctx && (kind == DLB_GEMM_TF32X3 || kind == DLB_GEMM_F16X3), "dlb_ctx_set_gemm_kind");
+  if (kind == ctx->gemm_kind) return DLB_OK;
+  // Plane buffers written under the other form do not hold what this form
+  // reads: drop every registration and let the models split their weights
+  // again (they compare plane_generation before each forward pass).
+  DLB_CUDA(cudaStreamSynchronize(ctx->stream));
+  planes_forget(ctx, 0, ~(size_t)0);
+  ctx->plane_generation++;
   ctx->gemm_kind = kind;
   return DLB_OK;
 }

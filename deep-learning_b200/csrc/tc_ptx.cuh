@@ -161,6 +161,8 @@ bool tmap_k_major(CUtensorMap *m, const void *ptr, int es, uint64_t mn, uint64_t
                   uint32_t box_k, uint32_t box_mn);
 bool tmap_mn_major(CUtensorMap *m, const void *ptr, int es, uint64_t mn, uint64_t k, uint64_t ld,
                    uint32_t box_k, uint32_t box_mn);
+bool tmap_cached(dlb_ctx *ctx, CUtensorMap *out, bool mn_major, const void *ptr, int es, uint64_t mn,
+                 uint64_t k, uint64_t ld, uint32_t box_k, uint32_t box_mn);
 // The 2-CTA form of the fp16-plane product (gemm_pair.cu).
 bool gemm_pair_enabled();
 dlb_status gemm_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C, long long ldc,

@@ -55,6 +55,7 @@ SIGNATURES = {
     "dlb_memcpy_h2d": (_i, [_vp, _vp, _vp, _sz]),
     "dlb_memcpy_d2h": (_i, [_vp, _vp, _vp, _sz]),
     "dlb_memcpy_d2d": (_i, [_vp, _vp, _vp, _sz]),
+    "dlb_device_mem_info": (_i, [C.POINTER(_sz), C.POINTER(_sz)]),
     "dlb_host_alloc": (_i, [C.POINTER(_vp), _sz]),
     "dlb_host_free": (_i, [_vp]),
     "dlb_split_tf32": (_i, [_vp, _vp, _vp, _sz]),
@@ -129,6 +130,7 @@ SIGNATURES = {
     "dlb_model_set_layer_norm": (_i, [_vp, _sz, _cp, _vp, _sz]),
     "dlb_model_set_dropout_mask": (_i, [_vp, _sz, _vp, _sz]),
     "dlb_model_set_global_batch": (_i, [_vp, _sz]),
+    "dlb_model_set_training_size": (_i, [_vp, _sz]),
     "dlb_model_forward_pass": (_i, [_vp, _sz, _vp]),
     "dlb_model_compute_error": (_i, [_vp, _sz, _vp]),
     "dlb_model_backward_pass": (_i, [_vp, _sz]),
@@ -337,6 +339,13 @@ class DeviceArray:
             pass
 
 
+def device_mem_info():
+    """(free, total) bytes of the current CUDA device."""
+    free, total = _sz(0), _sz(0)
+    check(lib().dlb_device_mem_info(C.byref(free), C.byref(total)), "dlb_device_mem_info")
+    return int(free.value), int(total.value)
+
+
 def pinned_empty(shape, dtype=np.float32):
     """numpy array over page-locked host memory (freed when dropped)."""
     L = lib()
@@ -433,6 +442,9 @@ class Model:
 
     def set_global_batch(self, rows):
         check(self.L.dlb_model_set_global_batch(self.h, rows), "set_global_batch")
+
+    def set_training_size(self, n):
+        check(self.L.dlb_model_set_training_size(self.h, n), "set_training_size")
 
     # --- state ----------------------------------------------------------
     def size(self, name):

@@ -82,8 +82,8 @@ dlb_status dlb_ctx_timer_stop(dlb_ctx *ctx, float *milliseconds);
 /* Per-launch timing of the tensor-core GEMM: while enabled every launch is
  * bracketed by a pair of events.  dlb_ctx_gemm_profile_read waits for the
  * stream, returns the number of launches, their summed duration and their
- * summed algorithmic FLOPs (2*M*N*K each, not multiplied by the three TF32
- * passes), and clears the record. */
+ * summed algorithmic FLOPs (2*M*N*K each, not multiplied by the three
+ * tensor-core products issued per FLOP), and clears the record. */
 dlb_status dlb_ctx_gemm_profile(dlb_ctx *ctx, int enable);
 dlb_status dlb_ctx_gemm_profile_read(dlb_ctx *ctx, uint64_t *launches, double *milliseconds,
                                      double *flops);
@@ -96,6 +96,9 @@ dlb_status dlb_memcpy_h2d(dlb_ctx *ctx, void *dev_dst, const void *host_src, siz
 /* Synchronous: returns after the bytes are in host memory. */
 dlb_status dlb_memcpy_d2h(dlb_ctx *ctx, void *host_dst, const void *dev_src, size_t bytes);
 dlb_status dlb_memcpy_d2d(dlb_ctx *ctx, void *dev_dst, const void *dev_src, size_t bytes);
+/* Free and total bytes of the current device (cudaMemGetInfo), for callers that
+ * watch what the library allocates. */
+dlb_status dlb_device_mem_info(size_t *free_bytes, size_t *total_bytes);
 /* Pinned host memory for staging inputs. */
 dlb_status dlb_host_alloc(void **host_ptr, size_t bytes);
 dlb_status dlb_host_free(void *host_ptr);
@@ -528,6 +531,11 @@ dlb_status dlb_model_set_shakedrop_noise(dlb_model *m, size_t layer, const uint8
 /* Data-parallel: rows given to forward_pass are this rank's shard of a batch
  * of global_rows rows (default: equal to the call's rows). */
 dlb_status dlb_model_set_global_batch(dlb_model *m, size_t global_rows);
+/* Examples in the training set: what dlb_model_train_step, _device and _staged
+ * pass as training_size to dlb_model_update_weights (the normalised weight decay
+ * is weight_decay * sqrt(batch / (training_size * epoch)), Model::normalized_wd,
+ * v1/learner/train.cpp L:278-283).  0 (default): the batch is the whole set. */
+dlb_status dlb_model_set_training_size(dlb_model *m, size_t training_size);
 
 /* Step entry points; X/Y are HOST arrays of row pointers exactly as the
  * reference takes them (model.hpp L:2980, L:1054), each row seq_w*n values. */
@@ -565,15 +573,6 @@ dlb_status dlb_model_train_step(dlb_model *m, size_t rows, const float *X_host,
                                 const float *Y_host, double *loss);
 dlb_status dlb_model_train_step_device(dlb_model *m, size_t rows, const float *X_dev,
                                        const float *Y_dev);
-/* The same step with the input copy taken off the critical path.  stage_batch
- * starts the host-to-device copy of one batch (contiguous [rows, seq_w*n]
- * arrays, page-locked for the copy to be asynchronous; they must stay
- * untouched until the step that uses them has been called) on a stream of its
- * own and returns; up to two batches may be staged.  train_step_staged runs
- * the step on the oldest staged batch.  Staging batch i+1 before stepping on
- * batch i hides the copy under the kernels.  This is the mini-batch loop of
- * MiniBatch::train_mp (v1/data/dataset/minibatch.cpp L:286-323): train on the
- * batch, read its loss, update the weights, move to the next batch. */
 /* Noise drawn on the device instead of handed over by the host: a counter-based
  * generator (Philox4x32-10, Salmon et al., SC'11) in which element i of a draw
  * is a function of (seed, stream, step, first + i) alone.  dlb_noise_uniform
@@ -610,6 +609,15 @@ dlb_status dlb_model_load(dlb_model *m, const char *path_params, const char *pat
  * default bound of IndRNN recurrent weights, clip(value, 2, 10)^(1/seq_w)
  * (v1/ops/constraints/constraint.cpp L:64-95). */
 dlb_status dlb_model_set_clip_gradient(dlb_model *m, int use, float value);
+/* The same step with the input copy taken off the critical path.  stage_batch
+ * starts the host-to-device copy of one batch (contiguous [rows, seq_w*n]
+ * arrays, page-locked for the copy to be asynchronous; they must stay
+ * untouched until the step that uses them has been called) on a stream of its
+ * own and returns; up to two batches may be staged.  train_step_staged runs
+ * the step on the oldest staged batch.  Staging batch i+1 before stepping on
+ * batch i hides the copy under the kernels.  This is the mini-batch loop of
+ * MiniBatch::train_mp (v1/data/dataset/minibatch.cpp L:286-323): train on the
+ * batch, read its loss, update the weights, move to the next batch. */
 dlb_status dlb_model_stage_batch(dlb_model *m, size_t rows, const float *X_host,
                                  const float *Y_host);
 dlb_status dlb_model_train_step_staged(dlb_model *m, double *loss);

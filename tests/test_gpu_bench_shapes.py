@@ -1,0 +1,239 @@
+"""Parity on the shapes the benchmark times, against the compiled reference
+(oracle/_ref, the reference's own OpenMP step): the deep batch-renorm MLP at its
+full layer widths 1024 - 4 x 4096 - 1024, the residual MLP at width 1024 and the
+IndRNN stack at hidden 512, so that every FC product of these steps runs on the
+2-CTA tcgen05 kernel with contraction lengths of 1024 and more, in both operand
+forms (3xFP16 planes, 3xTF32).
+
+Error measures: rel_l2 over a whole tensor (bar 1e-5 after one step) and the
+worst row-wise rel_l2 (`util.rowwise_rel_l2`), which a tensor-wide norm would
+hide.  Two facts about the reference set what can be asserted:
+
+* its sums depend on the OpenMP thread count, so the reference differs from
+  itself; each test runs it twice (all host threads, half of them) and widens a
+  bar to three times that drift where the drift exceeds it;
+* the derivative formulas of SELU / ELU / ReLU jump at 0 (and at every unit a
+  Bernoulli mask drops): a pre-activation within rounding of 0 takes either
+  branch, in the reference run with another thread count as well.  At these
+  sizes (millions of pre-activations) some always do, and one flipped branch
+  moves that row's error by percents.  Backward tensors of such steps are
+  therefore held against the reference's own drift; the strict backward
+  comparison runs on the same shapes with ISRLU and no dropout, whose
+  derivative is continuous.
+"""
+import time
+
+import numpy as np
+import pytest
+
+import configs
+import dlb200
+import ref_binding
+import util
+from enums import ACTIVATION
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")]
+
+TOL_1 = 1e-5     # rel_l2 after one step: activations, errors, gradients, updated weights
+TOL_ROW = 2e-5   # worst row of an activation or error tensor (a row of 1024-4096 sums of 1024-4096 products)
+KINDS = {"f16x3": 1, "tf32x3": 0}
+
+
+@pytest.fixture(params=sorted(KINDS))
+def kind_ctx(gpu_ctx, request):
+    """The session's context in one operand form; the default form afterwards."""
+    before = gpu_ctx.gemm_kind()
+    gpu_ctx.set_gemm_kind(KINDS[request.param])
+    yield gpu_ctx
+    gpu_ctx.set_gemm_kind(before)
+
+
+_CACHE = {}
+
+
+def _reference_twice(name, cfg, steps, X, Y, tracer=util.trace, prepare=None, **kw):
+    """The compiled reference with all host threads and with half of them, from
+    the same Glorot draw: (initial parameters, trace, trace at half the threads).
+    Kept per test name, so that both operand forms are held against one run."""
+    if name in _CACHE:
+        return _CACHE[name]
+    full = util.build(ref_binding.RefModel(), cfg, seed=0)
+    if prepare:
+        prepare(full)
+    p0 = full.get_array("parameters")
+    t0 = time.perf_counter()
+    want = tracer(full, cfg, steps, X, Y, **kw)
+    dt = time.perf_counter() - t0
+    half = util.build(ref_binding.RefModel(), cfg)
+    half.set_hparam("pct_threads", 50.0)
+    half.set_array("parameters", p0)
+    other = tracer(half, cfg, steps, X, Y, **kw)
+    print(f"reference: {full.size('number_threads')} and {half.size('number_threads')} threads, "
+          f"{dt:.1f} s for {steps} step(s)")
+    _CACHE[name] = (p0, want, other)
+    return _CACHE[name]
+
+
+def _report(got, want, other):
+    table = {}
+    print("tensor: GPU vs reference | reference at half the threads vs reference")
+    for key in want:
+        if key not in got or key == "losses":
+            continue
+        table[key] = (util.rel_l2(got[key], want[key]), util.rel_l2(other[key], want[key]))
+        print(f"  {key:>20s}  {table[key][0]:.2e} | {table[key][1]:.2e}")
+    return table
+
+
+def _check_rows(got, want, other, keys):
+    """rel_l2 of the tensor and of its worst row, the latter against the
+    reference's own worst row where that is larger than the bar."""
+    for key in keys:
+        l2 = util.rel_l2(got[key], want[key])
+        row = util.rowwise_rel_l2(got[key], want[key])
+        row_ref = util.rowwise_rel_l2(other[key], want[key])
+        print(f"  {key}: rel_l2 {l2:.2e}, worst row {row:.2e} (reference against itself: {row_ref:.2e})")
+        assert l2 <= TOL_1, f"{key}: rel_l2 {l2:.2e}"
+        assert row <= max(TOL_ROW, 3 * row_ref), f"{key}: worst row {row:.2e}, reference drift {row_ref:.2e}"
+
+
+def _check_rows_but_flipped(got, want, keys, max_share=0.05):
+    """Errors below layers whose derivative jumps at 0.  A pre-activation within
+    rounding of the jump takes the other branch and moves its whole row of the
+    errors below by percents; every other row must meet the row bar.  At most
+    `max_share` of the rows may be of the first kind."""
+    for key in keys:
+        g = np.asarray(got[key], np.float64)
+        w = np.asarray(want[key], np.float64)
+        den = np.linalg.norm(w, axis=1)
+        err = np.linalg.norm(g - w, axis=1) / np.where(den > 0, den, 1.0)
+        flipped = err > TOL_ROW
+        calm = ~flipped
+        l2 = np.linalg.norm((g - w)[calm]) / np.linalg.norm(w[calm])
+        print(f"  {key}: {int(flipped.sum())} of {len(err)} rows past a derivative jump "
+              f"(worst {err.max():.2e}); the others: rel_l2 {l2:.2e}, worst row {err[calm].max():.2e}")
+        assert flipped.mean() <= max_share, f"{key}: {int(flipped.sum())} rows above the row bar"
+        assert l2 <= TOL_1, f"{key}: rel_l2 {l2:.2e} over the rows without a flipped branch"
+
+
+def _drift_bar(table, key, bar):
+    return max(bar, 3 * table[key][1])
+
+
+def test_deep_brn_mlp_full_width_one_step(kind_ctx):
+    """BASELINE configuration 2 at its layer widths, 512 rows: every tensor of
+    one training step."""
+    cfg = configs.deep_brn_mlp(batch=512)
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    p0, want, other = _reference_twice("brn_selu", cfg, 1, X, Y, masks=masks)
+    got = util.trace(util.build(dlb200.Model(kind_ctx), cfg, params=p0), cfg, 1, X, Y, masks)
+    assert kind_ctx.sync() == 0
+    table = _report(got, want, other)
+    nl = len(cfg["layers"])
+    _check_rows(got, want, other, [f"act{i}" for i in range(1, nl)])
+    _check_rows(got, want, other, [f"delta{nl - 1}"])   # no derivative jump above the output error
+    _check_rows_but_flipped(got, want, [f"delta{i}" for i in range(1, nl - 1)])
+    # Gradients and weights carry the few flipped rows: their scale only.  The
+    # next test holds them to the bar on a step without jumps.
+    assert table["grads"][0] <= 5e-3 and table["params1"][0] <= 1e-4
+    for key in [k for k in want if k.startswith(("mean_average", "variance_average"))]:
+        assert table[key][0] <= _drift_bar(table, key, TOL_1), f"{key}: {table[key]}"
+    assert abs(got["losses"][0] - want["losses"][0]) <= 1e-6 * abs(want["losses"][0])
+
+
+def test_deep_brn_mlp_full_width_smooth_derivative(kind_ctx):
+    """The same widths with ISRLU and no dropout: no derivative jump, so errors,
+    gradients and updated weights are held to the bar itself, row by row."""
+    cfg = configs.deep_brn_mlp(batch=512, af=ACTIVATION.ISRLU, dropout=None)
+    X, Y = configs.synthetic_batch(cfg)
+    p0, want, other = _reference_twice("brn_isrlu", cfg, 1, X, Y, masks={})
+    got = util.trace(util.build(dlb200.Model(kind_ctx), cfg, params=p0), cfg, 1, X, Y, {})
+    assert kind_ctx.sync() == 0
+    table = _report(got, want, other)
+    nl = len(cfg["layers"])
+    _check_rows(got, want, other, [f"act{i}" for i in range(1, nl)] + [f"delta{i}" for i in range(1, nl)])
+    assert table["grads"][0] <= TOL_1, f"grads {table['grads'][0]:.2e}"
+    assert table["params1"][0] <= _drift_bar(table, "params1", TOL_1), f"params1 {table['params1']}"
+
+
+def test_deep_brn_mlp_full_size_steps(gpu_ctx):
+    """BASELINE configuration 2 at full size (4096 rows), two steps on the
+    default operand form: activations of the first step, losses and the weights
+    after the second."""
+    cfg = configs.deep_brn_mlp()
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    p0 = ref.get_array("parameters")
+    t0 = time.perf_counter()
+    want = util.trace(ref, cfg, 2, X, Y, masks)
+    print(f"reference: {ref.size('number_threads')} threads, {time.perf_counter() - t0:.1f} s for 2 steps of 4096 rows")
+    del ref
+    got = util.trace(util.build(dlb200.Model(gpu_ctx), cfg, params=p0), cfg, 2, X, Y, masks)
+    assert gpu_ctx.sync() == 0
+    nl = len(cfg["layers"])
+    for i in range(1, nl):
+        l2 = util.rel_l2(got[f"act{i}"], want[f"act{i}"])
+        row = util.rowwise_rel_l2(got[f"act{i}"], want[f"act{i}"])
+        print(f"  act{i}: rel_l2 {l2:.2e}, worst row {row:.2e}")
+        assert l2 <= TOL_1 and row <= TOL_ROW, f"act{i}: {l2:.2e} / {row:.2e}"
+    l2 = util.rel_l2(got[f"delta{nl - 1}"], want[f"delta{nl - 1}"])
+    assert l2 <= TOL_1, f"output error {l2:.2e}"
+    print("  losses", got["losses"], want["losses"], "params after 2 steps",
+          f"{util.rel_l2(got['params_last'], want['params_last']):.2e}")
+    assert util.rel_l2(got["losses"], want["losses"]) <= TOL_1
+    # Two AMSBound steps of about 1e-3 on weights of about 2e-2: a flipped
+    # derivative branch moves single weights, not the vector.
+    assert util.rel_l2(got["params_last"], want["params_last"]) <= 1e-4
+
+
+def test_residual_mlp_width_1024(kind_ctx):
+    """BASELINE configuration 3 reduced to 4 blocks of width 1024, 256 rows; the
+    reference runs serially so that its ShakeDrop draws can be replayed."""
+    cfg = configs.residual_mlp(width=1024, blocks=4, n_out=1000, batch=256)
+    X, Y = configs.synthetic_batch(cfg)
+    draws = [util.shakedrop_step_draws(cfg, 0)]
+    if "residual" not in _CACHE:
+        ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+        _CACHE["residual"] = (ref.get_array("parameters"), util.trace_noisy(ref, cfg, 1, X, Y, draws))
+    p0, want = _CACHE["residual"]
+    got = util.trace_noisy(util.build(dlb200.Model(kind_ctx), cfg, params=p0), cfg, 1, X, Y, draws)
+    assert kind_ctx.sync() == 0
+    cmp = util.compare(got, want)
+    print({k: f"{v[0]:.2e}" for k, v in cmp.items()})
+    for key, (l2, mx) in cmp.items():
+        if key.startswith("act"):
+            assert l2 <= TOL_1, f"{key}: {l2:.2e}"
+            assert util.rowwise_rel_l2(got[key], want[key]) <= TOL_ROW, key
+    last = len(cfg["layers"]) - 1
+    assert cmp[f"delta{last}"][0] <= TOL_1
+    # ELU's derivative jumps at 0: one flipped branch among 256 x 1024 x 4
+    # pre-activations moves a row of the errors below it by percents.
+    for key in [k for k in cmp if k.startswith("delta") or k == "grads"]:
+        assert cmp[key][0] <= 2e-3, f"{key}: {cmp[key][0]:.2e}"
+    assert abs(got["losses"][0] - want["losses"][0]) <= 1e-6 * abs(want["losses"][0])
+
+
+def test_indrnn_hidden_512(kind_ctx):
+    """BASELINE configuration 4 reduced to hidden 512, 32 time steps, 64
+    sequences."""
+    cfg = configs.indrnn_stack(n_in=512, hidden=512, depth=4, n_out=512, seq_w=32, batch=64)
+    X, Y = configs.synthetic_batch(cfg)
+
+    p0, want, other = _reference_twice("indrnn", cfg, 1, X, Y,
+                                       prepare=lambda m: configs.set_recurrent_uniform(m, cfg))
+    got = util.trace(util.build(dlb200.Model(kind_ctx), cfg, params=p0), cfg, 1, X, Y)
+    assert kind_ctx.sync() == 0
+    table = _report(got, want, other)
+    nl = len(cfg["layers"])
+    for i in range(1, nl):
+        assert table[f"act{i}"][0] <= TOL_1, f"act{i}: {table[f'act{i}'][0]:.2e}"
+    assert table[f"delta{nl - 1}"][0] <= TOL_1
+    # ReLU recurrence: the derivative jumps at 0 (module docstring); a flipped
+    # branch moves the errors of one sequence at the steps before it.
+    for i in range(1, nl - 1):
+        assert table[f"delta{i}"][0] <= _drift_bar(table, f"delta{i}", 2e-3), f"delta{i}: {table[f'delta{i}']}"
+    assert table["grads"][0] <= _drift_bar(table, "grads", 2e-3)
+    assert abs(got["losses"][0] - want["losses"][0]) <= 1e-6 * abs(want["losses"][0])

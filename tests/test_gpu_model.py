@@ -365,3 +365,96 @@ def test_evaluation_pass(gpu_ctx, case):
     assert util.rel_l2(qg, qo) <= TOL_1
     assert abs(lg - lo) <= 1e-5 * abs(lo)
     assert abs(ag - ao) <= 100.0 * 2 / (B * (1 if fn == fc_step.ACCU_CROSS_ENTROPY else qo.shape[1]))
+
+
+@pytest.mark.parametrize("kind", [LAYER_DROPOUT.BERNOULLI, LAYER_DROPOUT.BERNOULLI_INVERTED],
+                         ids=["bernoulli", "inverted"])
+def test_input_layer_dropout(gpu_ctx, kind):
+    """Dropout on the input layer (the reference applies it to the batch as it is
+    assigned, v1/learner/assign_inputs.cpp L:94-130) in training and at
+    inference, against the CPU restatement; it travels through a checkpoint."""
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96)
+    layers = [dict(l) for l in cfg["layers"]]
+    layers[0]["dropout"] = (kind, 0.8)
+    cfg = dict(cfg, layers=layers)
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    p0, seed = util.kink_free_parameters(cfg, fc_step.OracleModel, X, masks, scale=1.0 / np.sqrt(128))
+    ora = util.build(fc_step.OracleModel(), cfg, params=p0)
+    mod = gpu_model(gpu_ctx, cfg, p0)
+    want = util.trace(ora, cfg, 1, X, Y, masks)
+    got = util.trace(mod, cfg, 1, X, Y, masks)
+    assert gpu_ctx.sync() == 0
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_1, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+    unmasked = util.trace(gpu_model(gpu_ctx, cfg, p0), cfg, 1, X, Y, {k: v for k, v in masks.items() if k})
+    assert util.rel_l2(unmasked["act1"], got["act1"]) > 1e-2
+    B, last = cfg["batch"], len(cfg["layers"]) - 1
+    util.copy_trained_state(mod, ora, cfg)
+    outs = []
+    for m in (ora, mod):
+        m.set_propagation(0)
+        m.forward_pass(B, X)
+        outs.append(m.get_layer_outputs(last, B).reshape(B, -1))
+        m.set_propagation(1)
+    assert util.rel_l2(outs[1], outs[0]) <= TOL_1
+    assert mod.layer_info(0)["dropout"] == kind
+
+
+def test_operand_form_can_change_under_a_live_model(gpu_ctx):
+    """A model that has trained under one operand form keeps training correctly
+    after dlb_ctx_set_gemm_kind: its weight planes are split again in the new
+    form instead of being read as the other form's planes."""
+    cfg = configs.deep_brn_mlp(256, 512, 2, 256, 256)
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    B = cfg["batch"]
+    before = gpu_ctx.gemm_kind()
+    try:
+        for first, second in ((1, 0), (0, 1)):
+            gpu_ctx.set_gemm_kind(first)
+            live = util.build(dlb200.Model(gpu_ctx), cfg, seed=5)
+            for li, mk in masks.items():
+                live.set_dropout_mask(li, mk)
+            live.train_step(B, X, Y)
+            state = live.get_array("parameters")
+            gpu_ctx.set_gemm_kind(second)
+            fresh = util.build(dlb200.Model(gpu_ctx), cfg, params=state)
+            for li, mk in masks.items():
+                fresh.set_dropout_mask(li, mk)
+            util.copy_trained_state(live, fresh, cfg)
+            live.forward_pass(B, X)
+            fresh.forward_pass(B, X)
+            last = len(cfg["layers"]) - 1
+            a, b = live.get_layer_outputs(last, B), fresh.get_layer_outputs(last, B)
+            assert gpu_ctx.sync() == 0
+            assert np.array_equal(a, b), f"{first}->{second}: rel_l2 {util.rel_l2(a, b):.2e}"
+    finally:
+        gpu_ctx.set_gemm_kind(before)
+
+
+def test_training_size_enters_the_normalised_weight_decay(gpu_ctx):
+    """The one-call steps pass dlb_model_set_training_size to the update: with a
+    training set of 8 batches the decay is weight_decay * sqrt(1 / 8), as
+    update_weights(batch, 8 * batch) gives (v1/learner/train.cpp L:278-283)."""
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96, optimizer=OPTIMIZER.ADAM)
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    B = cfg["batch"]
+    models = []
+    for _ in range(3):
+        m = util.build(dlb200.Model(gpu_ctx), cfg, seed=11)
+        m.set_weight_decay(0.05)
+        for li, mk in masks.items():
+            m.set_dropout_mask(li, mk)
+        models.append(m)
+    one_call, by_hand, whole_set = models
+    one_call.set_training_size(8 * B)
+    one_call.train_step(B, X, Y)
+    by_hand.forward_pass(B, X); by_hand.compute_error(B, Y); by_hand.backward_pass(B)
+    by_hand.update_derivatives(B); by_hand.merge_derivatives(); by_hand.update_weights(B, 8 * B)
+    whole_set.train_step(B, X, Y)
+    assert gpu_ctx.sync() == 0
+    a, b, c = (m.get_array("parameters") for m in models)
+    assert np.array_equal(a, b)
+    assert not np.array_equal(a, c)

@@ -245,3 +245,42 @@ def test_evaluation_pass_matches_compiled_reference(case, mp):
     (lr, ar, qr), (lo, ao, qo) = out
     assert abs(lr - lo) <= 1e-6 * abs(lr) and ar == ao
     assert util.rel_l2(qo, qr) <= TOL_L2
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("kind", [2, 3], ids=["bernoulli", "inverted"])
+def test_input_layer_dropout_matches_compiled_reference(kind):
+    """Dropout on the input layer acts on the batch as it is assigned
+    (Model::assign_inputs_fwp_mp, v1/learner/assign_inputs.cpp L:94-130): masked
+    in training, the plain kind scaled by its keep probability at inference."""
+    cfg = configs.deep_brn_mlp(20, 32, 2, 12, 24)
+    layers = [dict(l) for l in cfg["layers"]]
+    layers[0]["dropout"] = (kind, 0.8)
+    cfg = dict(cfg, layers=layers)
+    masks = configs.dropout_masks(cfg)
+    assert 0 in masks and not masks[0].all()
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    p0 = ref.get_array("parameters")
+    want = util.trace(ref, cfg, 3, masks=masks)
+    ora = util.build(fc_step.OracleModel(), cfg, params=p0)
+    got = util.trace(ora, cfg, 3, masks=masks)
+    for key, (l2, mx) in util.compare(got, want).items():
+        # A running mean is a sum of values of both signs: its relative error is
+        # that of the batch means times their cancellation.
+        tol = 3 * TOL_L2 if key.startswith("mean_average") else TOL_L2
+        assert l2 <= tol, f"{key}: rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+    nomask = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, 1,
+                        masks={k: v for k, v in masks.items() if k != 0})
+    assert util.rel_l2(nomask["act1"], want["act1"]) > 1e-2   # the input mask is not a no-op
+    # Inference from the trained state.
+    B, last = cfg["batch"], len(cfg["layers"]) - 1
+    Xe, Ye = configs.synthetic_batch(dict(cfg, data_seed=5))
+    util.copy_trained_state(ref, ora, cfg)
+    outs = []
+    for m in (ref, ora):
+        m.set_propagation(0)
+        m.reset_loss()
+        m.forward_pass(B, Xe)
+        outs.append(m.get_layer_outputs(last, B).reshape(B, -1))
+        m.set_propagation(1)
+    assert util.rel_l2(outs[1], outs[0]) <= TOL_L2

@@ -45,6 +45,28 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point(gpu_ctx):
         # Same tolerance as the sums check of test_gpu_ops.test_batch_renorm_forward.
         np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-4)
         np.testing.assert_allclose(got, exact, rtol=1e-6, atol=1e-4)
+        # Both entry points cut the rows into the same chunks and add the
+        # chunks in the same order: the sums agree to the last bit.
+        assert np.array_equal(got, want)
+
+
+def test_calls_take_no_device_memory(gpu_ctx):
+    """After the first call on the device (which looks the array's address up),
+    further calls leave the free device memory where it was: nothing is
+    allocated, by the entry point or on its behalf."""
+    L = gpu_ctx.L
+    rng = np.random.default_rng(7)
+    Z = rng.standard_normal((512, 256)).astype(np.float32)
+    zd = gpu_ctx.array(Z)
+    out = gpu_ctx.zeros(2 * 256, np.float64)
+    check(L.dlb_brn_forward_sums_noalloc(zd.ptr, 512, 256, out.ptr, gpu_ctx.stream), "first call")
+    assert gpu_ctx.sync() == 0
+    free0, _ = dlb200.device_mem_info()
+    for rows in (512, 64, 300):
+        check(L.dlb_brn_forward_sums_noalloc(zd.ptr, rows, 256, out.ptr, gpu_ctx.stream), "later call")
+    assert gpu_ctx.sync() == 0
+    free1, _ = dlb200.device_mem_info()
+    assert free1 == free0
 
 
 def test_request_beyond_the_built_in_scratch_is_refused(gpu_ctx):

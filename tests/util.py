@@ -23,6 +23,20 @@ def rel_max(a, b):
     return float(np.abs(a - b).max() / (den if den > 0 else 1.0))
 
 
+def rowwise_rel_l2(a, b):
+    """Largest ||a[r] - b[r]||_2 / ||b[r]||_2 over the rows r of two [rows, n]
+    tensors, in float64: a tensor-wide norm hides a row whose values are far
+    below the rest, this does not.  Rows of b that are all zero are skipped."""
+    a = np.asarray(a, np.float64)
+    b = np.asarray(b, np.float64)
+    a = a.reshape(b.shape[0], -1)
+    b = b.reshape(b.shape[0], -1)
+    den = np.linalg.norm(b, axis=1)
+    num = np.linalg.norm(a - b, axis=1)
+    live = den > 0
+    return float((num[live] / den[live]).max()) if live.any() else 0.0
+
+
 def build(model, cfg, params=None, seed=None):
     configs.build_model(model, cfg)
     if params is not None:
