@@ -379,25 +379,64 @@ def run_ours(args, rank, local_rank, world):
     if status != 0:
         raise SystemExit(f"device status {status} after the timed region")
 
+    j_n, j_ms, x_n, x_ms = ctx.comm_profile_read()
+    comm = {"allreduce_exposed_ms": max_over_ranks(j_ms / args.steps), "stats_exchange_ms": max_over_ranks(x_ms / args.steps),
+            "stats_exchanges_per_step": x_n / args.steps, "gemm_avg_launch_ms": max_over_ranks(g_ms / g_n if g_n else 0.0),
+            "what": "per step, largest over the ranks, from CUDA events on the compute stream: time it stood still "
+                    "waiting for the overlapped gradient all-reduces; summed duration of the exchanges of "
+                    "batch-renormalization sums; average duration of an FC product (against the 1-GPU figure: "
+                    "the slowdown from sharing SMs and HBM with the transfers)"} if world > 1 else None
+
     # ---- end to end: host inputs in, loss out ----------------------------
     # Every step's batch crosses PCIe inside the timed region; the copy of batch
     # i+1 is started before the step on batch i so that it runs under its kernels.
-    for _ in range(2):  # warm-up: both staging slots get their device buffers
-        model.stage_batch(rows, Xp, Yp)
-    for _ in range(2):
-        model.train_step_staged()
-    ctx.sync()
-    barrier()
-    t0 = time.perf_counter()
-    loss = 0.0
-    model.stage_batch(rows, Xp, Yp)
-    for i in range(args.steps):
-        if i + 1 < args.steps:
+    # Every step reads a loss back (8 bytes): with a lag of one step it is the loss
+    # of the step before, so that the host never waits for the step it has just
+    # enqueued; the last step's loss is read before the clock stops.
+    def end_to_end(lag, steps):
+        model.set_loss_lag(lag)
+        for _ in range(2):  # warm-up: both staging slots get their device buffers
             model.stage_batch(rows, Xp, Yp)
-        loss = model.train_step_staged()
-    barrier()
-    e2e_s = max_over_ranks(time.perf_counter() - t0)
+        for _ in range(2):
+            model.train_step_staged()
+        ctx.sync()
+        barrier()
+        t0 = time.perf_counter()
+        model.stage_batch(rows, Xp, Yp)
+        for i in range(steps):
+            if i + 1 < steps:
+                model.stage_batch(rows, Xp, Yp)
+            last = model.train_step_staged()
+        if lag:
+            last = model.get_loss()
+        barrier()
+        return max_over_ranks(time.perf_counter() - t0), last
+
+    in_order_s, _ = end_to_end(0, args.steps)
+    e2e_s, loss = end_to_end(1, args.steps)
+    model.set_loss_lag(0)
+
+    # ---- strong scaling: the 4096-row batch itself sharded over the GPUs -----
+    strong = None
+    if world > 1 and args.workload == "deep_brn_mlp":
+        rows_s = rows // world
+        Xs, Ys = ctx.array(Xh[:rows_s]), ctx.array(Yh[:rows_s])
+        model.set_global_batch(rows_s * world)
+        for _ in range(3):
+            model.train_step_device(rows_s, Xs, Ys)
+        barrier()
+        ctx.timer_start()
+        for _ in range(args.steps):
+            model.train_step_device(rows_s, Xs, Ys)
+        ms_s = max_over_ranks(ctx.timer_stop())
+        barrier()
+        model.set_global_batch(rows * world)
+        strong = {"global_batch": rows_s * world, "rows_per_gpu": rows_s, "ms_per_step": ms_s / args.steps,
+                  "value": rows_s * world * args.steps / (ms_s / 1e3), "unit": UNIT,
+                  "what": "the same model with the 4096-row batch sharded over the GPUs (fixed total work), "
+                          "device-resident inputs, timed like `value`"}
     clocks = sampler.stop() if rank == 0 else None
+    guard = ctx.guard_counters()
     if rank != 0:
         return
 
@@ -418,9 +457,16 @@ def run_ours(args, rank, local_rank, world):
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args, cfg, world),
         "e2e": {"value": rows * world * args.steps / e2e_s, "unit": UNIT,
                 "h2d_bytes_per_step": int(Xp.nbytes + Yp.nbytes), "d2h_bytes_per_step": 8,
-                "ms_per_step": e2e_s / args.steps * 1e3, "last_loss": loss},
+                "ms_per_step": e2e_s / args.steps * 1e3, "last_loss": loss,
+                "loss_read": "every step reads the loss of the step before from page-locked memory (lag of one step), "
+                             "the last step's before the clock stops",
+                "in_order": {"value": rows * world * args.steps / in_order_s, "ms_per_step": in_order_s / args.steps * 1e3,
+                             "what": "each step waits for its own loss after enqueuing its update"}},
         "gpu_launches": launches,
+        "range_guard": {"operand_tensors_flagged": guard[0], "products_on_fp32_fallback": guard[1],
+                        "note": "3xFP16 form: products whose operand planes the range guard rejected (expected 0)"},
         "clocks": clocks,
+        "comm": comm, "strong": strong,
         "roofline": {
             "kernel": ("gemm_x3_pair_kernel (tcgen05 cta_group::2, all FC products; 3xFP16 planes, kind::f16)"
                        if f16 else "gemm_x3_kernel (tcgen05, all FC products; 3xTF32, kind::tf32)"),

@@ -32,13 +32,18 @@ struct dlb_ctx {
   // SMs the persistent GEMM leaves free while a communicator is bound
   // (DLB_GEMM_RESERVE_SMS), so that an overlapped all-reduce can run beside it.
   int gemm_reserve_sms = 8;
-  // fp16 plane buffers written by dlb_split_planes, keyed by the buffer's
-  // address: the tensor they were split from, its element count (the lo plane
-  // starts n halfs after the hi plane) and the device slot of its scale.
+  // fp16 plane buffers, keyed by the buffer's address: the tensor they were
+  // split from, its element count (the lo plane starts n halfs after the hi
+  // plane), its shape when the producer gave one, the device slot of its scale
+  // and flags, and the per-row / per-column maxima the producers leave for the
+  // range check (rows + cols words, zero between uses).
   struct PlaneEntry {
     const float *x;
     size_t n;
     float *scale;
+    int rows = 0, cols = 0;
+    unsigned *lines = nullptr;  // [rows] row maxima, then [cols] column maxima (raw bits of |x|)
+    bool seen = false;          // a split has completed: the slot holds a scale predicted for the next one
   };
   std::map<uintptr_t, PlaneEntry> planes;
   // Bumped by dlb_ctx_set_gemm_kind, which also drops every registration above:
@@ -67,7 +72,10 @@ struct dlb_ctx {
     alignas(64) unsigned char bytes[128];
   };
   std::map<TmapKey, TmapBlob> tmaps;
-  float *scale_pool = nullptr;   // SCALE_SLOTS slots of 4 floats: s, 1/s, |x|max bits, unused
+  float *scale_pool = nullptr;   // SCALE_SLOTS slots of SLOT_WORDS words (planes.cuh)
+  // Range guard of the fp16 operand form: [0] operand tensors found unsafe for it,
+  // [1] products that therefore ran on the fp32 CUDA-core kernel.
+  unsigned long long *d_guard = nullptr;
   std::vector<int> scale_free;
   std::map<uintptr_t, size_t> allocs;  // dlb_malloc'd blocks, to retire plane entries on free
   // Exchange of small fp64 vectors through peer memory: every rank's buffer
@@ -84,10 +92,14 @@ struct dlb_ctx {
   struct GemmRecord {
     cudaEvent_t start, stop;
     double flops;
+    int kind;  // 0: FC product, 1: wait of the main stream for the overlapped all-reduces, 2: exchange of sums
   };
   bool gemm_profile = false;
   std::vector<GemmRecord> gemm_records;
   std::vector<cudaEvent_t> event_pool;
+  // Totals of the last dlb_ctx_gemm_profile_read for kinds 1 and 2.
+  double join_wait_ms = 0.0, exchange_ms = 0.0;
+  uint64_t join_waits = 0, exchanges = 0;
 };
 
 namespace dlb {
@@ -150,6 +162,10 @@ struct GemmOperand {
   const uint16_t *h_hi = nullptr;
   const uint16_t *h_lo = nullptr;
   const float *scale = nullptr;
+  // Word that is non-zero when the planes cannot stand for the tensor (range
+  // guard, planes.cuh): the tensor-core kernel then computes the product from
+  // the fp32 tensors on the CUDA cores instead.
+  const unsigned *guard = nullptr;
 };
 struct GemmEpilogue {
   const float *bias = nullptr;   // per-n bias added to every row
@@ -182,19 +198,55 @@ dlb_status peer_exchange_f64(dlb_ctx *ctx, double *buf, size_t n);
 dlb_status comm_allgather_host(dlb_ctx *ctx, const void *mine, void *all, size_t bytes);
 dlb_status comm_min_int(dlb_ctx *ctx, int *value);
 
-// Fills o.h_hi / h_lo / scale from the plane buffer registered for (o.ptr, aux),
-// if there is one and the planes are 16-byte aligned.
+// Fills o.h_hi / h_lo / scale / guard from the plane buffer registered for
+// (o.ptr, aux), if there is one and the planes are 16-byte aligned.
 bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o);
 // Drops the plane buffers registered at addresses in [base, base + bytes).
 void planes_forget(dlb_ctx *ctx, uintptr_t base, size_t bytes);
-// max |x| into slot[2] and the fp16 planes of s x, s = 2^(14 - floor(log2 max)).
-dlb_status split_f16(dlb_ctx *ctx, const float *x, size_t n, uint16_t *hi, uint16_t *lo, float *slot);
+
+// What a kernel that produces a GEMM operand is handed to write the operand's
+// fp16 planes and range statistics in the same pass (device side: planes.cuh).
+struct PlaneSink {
+  uint16_t *hi = nullptr, *lo = nullptr;   // null: the kernel writes no planes
+  float *slot = nullptr;                   // scale slot; null: nothing to track
+  unsigned *rowmax = nullptr, *colmax = nullptr;   // rows, then cols words of one array
+  int n_lines = 0;                         // rows + cols (0: no line statistics)
+  int predicted = 0;                       // planes use the scale predicted from the previous split
+  unsigned long long *guard = nullptr;     // counter of tensors the range guard flagged
+};
+// One split of a tensor into its plane buffer.  planes_open registers the
+// buffer and decides the form: `fused` (the producing kernel writes planes and
+// statistics itself, with the scale predicted from the buffer's previous split)
+// when the kernel can and such a scale exists, else the kernel only tracks
+// max |x| (sink.slot) and planes_close runs the split pass.  planes_close then
+// launches the check that sets the slot's scale and guard flag for the
+// consumers and the prediction for the next split (the last block of the kernel
+// that wrote the planes does it: sink_complete in planes.cuh).
+struct PlaneJob {
+  PlaneSink sink;
+  const float *x = nullptr;
+  float *planes = nullptr;
+  size_t n = 0;
+  int rows = 0, cols = 0;
+  bool fused = false, active = false;
+};
+dlb_status planes_open(dlb_ctx *ctx, const float *x, float *planes, size_t n, int rows, int cols,
+                       bool kernel_can_fuse, PlaneJob *job);
+dlb_status planes_close(dlb_ctx *ctx, const PlaneJob &job);
+// max |x| of a tensor no kernel of the library produced (inputs, fresh weights).
+dlb_status planes_absmax(dlb_ctx *ctx, const float *x, size_t n, float *slot);
+// Split into caller storage outside the registry (scratch): planes, slot of
+// SLOT_WORDS words and rows + cols words of line maxima, all zeroed here.
+dlb_status planes_split_adhoc(dlb_ctx *ctx, const float *x, size_t n, int rows, int cols, uint16_t *hi,
+                              uint16_t *lo, float *slot, unsigned *lines);
 dlb_status optimizer_step_amax(dlb_ctx *ctx, int rule, const dlb_optimizer_scalars *s, float *p, float *g,
                                float *first, float *second, float *second_hat, const float *wd_mask, size_t n,
                                unsigned *amax);
-dlb_status planes_begin(dlb_ctx *ctx, const float *x, float *planes, size_t n, float **slot_out);
-dlb_status planes_finish(dlb_ctx *ctx, const float *x, float *planes, size_t n, float *slot);
+dlb_status optimizer_step_sink(dlb_ctx *ctx, int rule, const dlb_optimizer_scalars *s, float *p, float *g,
+                               float *first, float *second, float *second_hat, const float *wd_mask, int rows,
+                               int cols, const PlaneSink &sink);
 constexpr int SCALE_SLOTS = 8192;
+constexpr int SLOT_WORDS = 8;    // words of one scale slot (layout: planes.cuh)
 constexpr int MAX_DEVICES = 64;  // device indices a process may hold contexts on
 
 }  // namespace dlb

@@ -44,26 +44,45 @@ static size_t operand_elems(const GemmOperand &o, int mn, int k) {
   return (size_t)(k - 1) * o.stride_k + mn;
 }
 
+// A pair of events around one piece of work while per-launch profiling is on.
+struct ProfileSpan {
+  dlb_ctx *ctx;
+  dlb_ctx::GemmRecord rec;
+  bool on = false;
+  dlb_status begin(dlb_ctx *c, int kind, double flops) {
+    ctx = c;
+    if (!c->gemm_profile) return DLB_OK;
+    cudaEvent_t *ev[2] = {&rec.start, &rec.stop};
+    for (cudaEvent_t *e : ev) {
+      if (!c->event_pool.empty()) {
+        *e = c->event_pool.back();
+        c->event_pool.pop_back();
+      } else {
+        DLB_CUDA(cudaEventCreate(e));
+      }
+    }
+    rec.flops = flops;
+    rec.kind = kind;
+    DLB_CUDA(cudaEventRecord(rec.start, c->stream));
+    on = true;
+    return DLB_OK;
+  }
+  dlb_status end() {
+    if (!on) return DLB_OK;
+    DLB_CUDA(cudaEventRecord(rec.stop, ctx->stream));
+    ctx->gemm_records.push_back(rec);
+    return DLB_OK;
+  }
+};
+
 // Runs the tensor-core kernel, bracketed by a pair of events when per-launch
 // profiling is on.
 static dlb_status gemm_tensor_core(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
                                    long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
-  if (!ctx->gemm_profile) return gemm_tcgen05(ctx, A, B, C, ldc, M, N, K, ep);
-  dlb_ctx::GemmRecord rec;
-  cudaEvent_t *ev[2] = {&rec.start, &rec.stop};
-  for (cudaEvent_t *e : ev) {
-    if (!ctx->event_pool.empty()) {
-      *e = ctx->event_pool.back();
-      ctx->event_pool.pop_back();
-    } else {
-      DLB_CUDA(cudaEventCreate(e));
-    }
-  }
-  rec.flops = 2.0 * M * N * K;
-  DLB_CUDA(cudaEventRecord(rec.start, ctx->stream));
+  ProfileSpan span;
+  DLB_TRY(span.begin(ctx, 0, 2.0 * M * N * K));
   const dlb_status st = gemm_tcgen05(ctx, A, B, C, ldc, M, N, K, ep);
-  DLB_CUDA(cudaEventRecord(rec.stop, ctx->stream));
-  ctx->gemm_records.push_back(rec);
+  DLB_TRY(span.end());
   return st;
 }
 
@@ -83,24 +102,43 @@ dlb_status gemm(dlb_ctx *ctx, const GemmOperand &A_in, const GemmOperand &B_in, 
     const size_t a_n = a_have ? 0 : align_up(operand_elems(A, M, K), 64);
     const size_t b_n = b_have ? 0 : align_up(operand_elems(B, N, K), 64);
     if (a_n + b_n) {
+      // Behind the planes: two scale slots, then the line maxima of the dense
+      // operands ([M + K] and [N + K] words).
+      const size_t line_words = align_up((size_t)M + K, 4) + align_up((size_t)N + K, 4);
       void *scr = nullptr;
-      DLB_TRY(scratch(ctx, (a_n + b_n) * 2 * sizeof(uint16_t) + 64, &scr));
+      DLB_TRY(scratch(ctx, (a_n + b_n) * 2 * sizeof(uint16_t) + (2 * SLOT_WORDS + line_words) * 4 + 64, &scr));
       uint16_t *h = static_cast<uint16_t *>(scr);
       float *slots = reinterpret_cast<float *>(h + 2 * (a_n + b_n));
+      unsigned *lines = reinterpret_cast<unsigned *>(slots + 2 * SLOT_WORDS);
+      // A dense operand is a [mn, k] (k contiguous) or [k, mn] (mn contiguous) matrix.
+      auto shape = [](const GemmOperand &o, int mn, int k, int *rows, int *cols) {
+        *rows = *cols = 0;
+        if (o.stride_k == 1 && o.stride_mn == k) { *rows = mn; *cols = k; }
+        else if (o.stride_mn == 1 && o.stride_k == mn) { *rows = k; *cols = mn; }
+      };
       if (!a_have) {
-        DLB_TRY(split_f16(ctx, A.ptr, operand_elems(A, M, K), h, h + a_n, slots));
+        int r, c;
+        shape(A, M, K, &r, &c);
+        DLB_TRY(planes_split_adhoc(ctx, A.ptr, operand_elems(A, M, K), r, c, h, h + a_n, slots, lines));
         A.h_hi = h;
         A.h_lo = h + a_n;
         A.scale = slots;
+        A.guard = reinterpret_cast<const unsigned *>(slots) + 3;
       }
       if (!b_have) {
         uint16_t *hb = h + 2 * a_n;
-        DLB_TRY(split_f16(ctx, B.ptr, operand_elems(B, N, K), hb, hb + b_n, slots + 4));
+        int r, c;
+        shape(B, N, K, &r, &c);
+        DLB_TRY(planes_split_adhoc(ctx, B.ptr, operand_elems(B, N, K), r, c, hb, hb + b_n, slots + SLOT_WORDS,
+                                   lines + align_up((size_t)M + K, 4)));
         B.h_hi = hb;
         B.h_lo = hb + b_n;
-        B.scale = slots + 4;
+        B.scale = slots + SLOT_WORDS;
+        B.guard = reinterpret_cast<const unsigned *>(slots + SLOT_WORDS) + 3;
       }
     }
+    // A product with an operand the range guard flagged is computed by the
+    // same launch on the CUDA cores, from the fp32 tensors.
     return gemm_tensor_core(ctx, A, B, C, ldc, M, N, K, ep);
   }
 
@@ -297,7 +335,9 @@ dlb_status dlb_ctx_destroy(dlb_ctx *ctx) {
   if (ctx->ev_comm) cudaEventDestroy(ctx->ev_comm);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->d_status) cudaFree(ctx->d_status);
+  planes_forget(ctx, 0, ~(size_t)0);
   if (ctx->scale_pool) cudaFree(ctx->scale_pool);
+  if (ctx->d_guard) cudaFree(ctx->d_guard);
   if (ctx->timer_start) cudaEventDestroy(ctx->timer_start);
   if (ctx->timer_stop) cudaEventDestroy(ctx->timer_stop);
   for (auto &r : ctx->gemm_records) {
@@ -364,16 +404,36 @@ dlb_status dlb_ctx_gemm_profile_read(dlb_ctx *ctx, uint64_t *launches, double *m
   *launches = 0;
   *milliseconds = 0.0;
   *flops = 0.0;
+  ctx->join_wait_ms = ctx->exchange_ms = 0.0;
+  ctx->join_waits = ctx->exchanges = 0;
   for (auto &r : ctx->gemm_records) {
     float ms = 0.f;
     DLB_CUDA(cudaEventElapsedTime(&ms, r.start, r.stop));
-    *milliseconds += ms;
-    *flops += r.flops;
-    *launches += 1;
+    if (r.kind == 1) {
+      ctx->join_wait_ms += ms;
+      ctx->join_waits += 1;
+    } else if (r.kind == 2) {
+      ctx->exchange_ms += ms;
+      ctx->exchanges += 1;
+    } else {
+      *milliseconds += ms;
+      *flops += r.flops;
+      *launches += 1;
+    }
     ctx->event_pool.push_back(r.start);
     ctx->event_pool.push_back(r.stop);
   }
   ctx->gemm_records.clear();
+  return DLB_OK;
+}
+
+dlb_status dlb_ctx_comm_profile_read(dlb_ctx *ctx, uint64_t *join_waits, double *join_wait_ms,
+                                     uint64_t *exchanges, double *exchange_ms) {
+  DLB_REQUIRE(ctx && join_waits && join_wait_ms && exchanges && exchange_ms, "dlb_ctx_comm_profile_read: null");
+  *join_waits = ctx->join_waits;
+  *join_wait_ms = ctx->join_wait_ms;
+  *exchanges = ctx->exchanges;
+  *exchange_ms = ctx->exchange_ms;
   return DLB_OK;
 }
 
@@ -538,7 +598,10 @@ dlb_status dlb_comm_join(dlb_ctx *ctx) {
   DLB_REQUIRE(ctx, "dlb_comm_join");
   if (!ctx->comm_pending) return DLB_OK;
   DLB_CUDA(cudaEventRecord(ctx->ev_comm, ctx->comm_stream));
+  ProfileSpan span;  // how long the main stream stands still for the transfers
+  DLB_TRY(span.begin(ctx, 1, 0.0));
   DLB_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_comm, 0));
+  DLB_TRY(span.end());
   ctx->comm_pending = false;
   return DLB_OK;
 }
@@ -546,9 +609,14 @@ dlb_status dlb_comm_join(dlb_ctx *ctx) {
 dlb_status dlb_allreduce_f64(dlb_ctx *ctx, double *buf, size_t n) {
   DLB_REQUIRE(ctx && (buf || n == 0), "dlb_allreduce_f64");
   if (!ctx->comm || ctx->world == 1 || n == 0) return DLB_OK;
-  if (peer_exchange_fits(ctx, n)) return peer_exchange_f64(ctx, buf, n);
-  DLB_NCCL(nccl()->AllReduce(buf, buf, n, ncclFloat64, ncclSum, ctx->comm, ctx->stream));
-  return DLB_OK;
+  ProfileSpan span;
+  DLB_TRY(span.begin(ctx, 2, 0.0));
+  if (peer_exchange_fits(ctx, n)) {
+    DLB_TRY(peer_exchange_f64(ctx, buf, n));
+  } else {
+    DLB_NCCL(nccl()->AllReduce(buf, buf, n, ncclFloat64, ncclSum, ctx->comm, ctx->stream));
+  }
+  return span.end();
 }
 
 }  // extern "C"

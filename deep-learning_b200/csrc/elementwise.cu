@@ -8,6 +8,7 @@
 
 #include "common.cuh"
 #include "math.cuh"
+#include "planes.cuh"
 
 namespace dlb {
 
@@ -466,103 +467,141 @@ __global__ void activation_backward_plain_kernel(float *__restrict__ dA, const f
 // registers leave three blocks per SM instead of four).
 constexpr int AF_ROWS = 2;
 
+// PLANES: the kernel also writes the fp16 planes of A (with the scale predicted
+// from the buffer's previous split) and the row / column maxima of the range
+// guard; otherwise it leaves max |A| in the sink's slot for the split pass that
+// follows.
+template <bool PLANES>
 __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
     activation_forward_rows_kernel(const float *__restrict__ Z, BrnPtrs u, int af, DropoutDev dp,
                                    float *__restrict__ A, float *__restrict__ A_lo, int rows, int n,
-                                   int rows_per_chunk, unsigned *amax) {
+                                   int rows_per_chunk, PlaneSink sink) {
+  __shared__ unsigned line_shared[PLANES ? CR_LANES_Y * CR_COLS : 1];
   const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
   const int col = blockIdx.x * CR_COLS + tx * 4;
-  if (col >= n) return;
+  const bool live_col = col < n;
+  if (!PLANES && !live_col) return;
   const int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
-  unsigned mx = 0;
-  BrnCol c[4];
-  // Bernoulli dropout has one flag per unit: a factor per owned column.
-  float keep[4];
-  const bool bern = dp.type == DLB_DROPOUT_BERNOULLI || dp.type == DLB_DROPOUT_BERNOULLI_INVERTED;
+  LineTracker track;
+  const float plane_scale = PLANES ? sink_scale(sink) : 1.f;
+  if (live_col) {
+    BrnCol c[4];
+    // Bernoulli dropout has one flag per unit: a factor per owned column.
+    float keep[4];
+    const bool bern = dp.type == DLB_DROPOUT_BERNOULLI || dp.type == DLB_DROPOUT_BERNOULLI_INVERTED;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    c[j] = u.at(col + j);
-    keep[j] = bern ? (dp.mask[col + j] ? (dp.type == DLB_DROPOUT_BERNOULLI_INVERTED ? dp.scale : 1.f) : 0.f) : 1.f;
-  }
-  // AF_ROWS rows per iteration, loads first, so that each thread keeps that many
-  // 16-byte requests in flight.
-  for (int r = r0 + ty; r < r1; r += AF_ROWS * CR_LANES_Y) {
-    size_t o[AF_ROWS];
-    bool live[AF_ROWS];
-    float4 z[AF_ROWS];
-#pragma unroll
-    for (int k = 0; k < AF_ROWS; ++k) {
-      const int rk = r + k * CR_LANES_Y;
-      live[k] = rk < r1;
-      o[k] = (size_t)rk * n + col;
-      if (live[k]) z[k] = __ldg(reinterpret_cast<const float4 *>(Z + o[k]));
+    for (int j = 0; j < 4; ++j) {
+      c[j] = u.at(col + j);
+      keep[j] = bern ? (dp.mask[col + j] ? (dp.type == DLB_DROPOUT_BERNOULLI_INVERTED ? dp.scale : 1.f) : 0.f) : 1.f;
     }
+    // AF_ROWS rows per iteration, loads first, so that each thread keeps that many
+    // 16-byte requests in flight.
+    for (int r = r0 + ty; r < r1; r += AF_ROWS * CR_LANES_Y) {
+      size_t o[AF_ROWS];
+      bool live[AF_ROWS];
+      float4 z[AF_ROWS];
 #pragma unroll
-    for (int k = 0; k < AF_ROWS; ++k) {
-      if (!live[k]) break;
-      const float zz[4] = {z[k].x, z[k].y, z[k].z, z[k].w};
-      float out[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float a = af_fire(af, brn_norm(brn_hat(zz[j], c[j]), c[j]));
-        // Kept units pass unchanged under plain Bernoulli, as the reference leaves them.
-        if (bern) out[j] = keep[j] == 1.f ? a : (keep[j] == 0.f ? 0.f : a * keep[j]);
-        else out[j] = apply_dropout(a, dp, col + j, o[k] + j);
-        mx = max(mx, abs_bits(out[j]));
+      for (int k = 0; k < AF_ROWS; ++k) {
+        const int rk = r + k * CR_LANES_Y;
+        live[k] = rk < r1;
+        o[k] = (size_t)rk * n + col;
+        if (live[k]) z[k] = __ldg(reinterpret_cast<const float4 *>(Z + o[k]));
       }
-      *reinterpret_cast<float4 *>(A + o[k]) = make_float4(out[0], out[1], out[2], out[3]);
-      if (A_lo)
-        *reinterpret_cast<float4 *>(A_lo + o[k]) =
-            make_float4(tf32_lo(out[0]), tf32_lo(out[1]), tf32_lo(out[2]), tf32_lo(out[3]));
+#pragma unroll
+      for (int k = 0; k < AF_ROWS; ++k) {
+        if (!live[k]) break;
+        const float zz[4] = {z[k].x, z[k].y, z[k].z, z[k].w};
+        float out[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float a = af_fire(af, brn_norm(brn_hat(zz[j], c[j]), c[j]));
+          // Kept units pass unchanged under plain Bernoulli, as the reference leaves them.
+          if (bern) out[j] = keep[j] == 1.f ? a : (keep[j] == 0.f ? 0.f : a * keep[j]);
+          else out[j] = apply_dropout(a, dp, col + j, o[k] + j);
+        }
+        *reinterpret_cast<float4 *>(A + o[k]) = make_float4(out[0], out[1], out[2], out[3]);
+        if (PLANES) {
+          sink_store4(sink, o[k], out, plane_scale);
+          track.row(sink, r + k * CR_LANES_Y, out);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) track.all = max(track.all, abs_bits(out[j]));
+          if (A_lo)
+            *reinterpret_cast<float4 *>(A_lo + o[k]) =
+                make_float4(tf32_lo(out[0]), tf32_lo(out[1]), tf32_lo(out[2]), tf32_lo(out[3]));
+        }
+      }
     }
   }
-  amax_commit(amax, mx);
+  if (PLANES) {
+    track.finish(sink, line_shared, tx, ty, CR_LANES_Y, blockIdx.x * CR_COLS, n, live_col);
+    sink_complete(sink);
+  } else if (sink.slot) {
+    amax_commit(reinterpret_cast<unsigned *>(sink.slot) + SLOT_AMAX, track.all);
+  }
 }
 
+template <bool PLANES>
 __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
     brn_backward_apply_rows_kernel(float *__restrict__ delta, float *__restrict__ delta_lo,
                                    const float *__restrict__ Z, BrnPtrs u,
                                    const double *__restrict__ sums, float inv_rows, float rows_f,
-                                   int rows, int n, int rows_per_chunk, unsigned *amax) {
+                                   int rows, int n, int rows_per_chunk, PlaneSink sink) {
+  __shared__ unsigned line_shared[PLANES ? CR_LANES_Y * CR_COLS : 1];
   const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
   const int col = blockIdx.x * CR_COLS + tx * 4;
-  if (col >= n) return;
+  const bool live_col = col < n;
+  if (!PLANES && !live_col) return;
   const int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
-  unsigned mx = 0;
-  // Per-unit factors in the reference's grouping (bwp_mp.cpp L:1608-1621):
-  // r / sigma, N * sigma, d_sigma, d_mean / N.
-  float gamma[4], mean[4], r_over_sigma[4], n_sigma[4], d_sigma[4], d_mean_n[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const BrnCol c = u.at(col + j);
-    gamma[j] = c.gamma;
-    mean[j] = c.mean;
-    r_over_sigma[j] = c.r / c.sigma;
-    n_sigma[j] = rows_f * c.sigma;
-    d_sigma[j] = (float)sums[3 * (size_t)n + col + j];
-    d_mean_n[j] = (float)sums[2 * (size_t)n + col + j] * inv_rows;
-  }
-  for (int r = r0 + ty; r < r1; r += CR_LANES_Y) {
-    const size_t o = (size_t)r * n + col;
-    const float4 e4 = *reinterpret_cast<const float4 *>(delta + o);
-    const float4 z4 = __ldg(reinterpret_cast<const float4 *>(Z + o));
-    const float e[4] = {e4.x, e4.y, e4.z, e4.w}, z[4] = {z4.x, z4.y, z4.z, z4.w};
-    float t[4];
+  LineTracker track;
+  const float plane_scale = PLANES ? sink_scale(sink) : 1.f;
+  if (live_col) {
+    // Per-unit factors in the reference's grouping (bwp_mp.cpp L:1608-1621):
+    // r / sigma, N * sigma, d_sigma, d_mean / N.
+    float gamma[4], mean[4], r_over_sigma[4], n_sigma[4], d_sigma[4], d_mean_n[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float v = e[j] * gamma[j];
-      v *= r_over_sigma[j];
-      v += d_sigma[j] * ((z[j] - mean[j]) / n_sigma[j]);
-      v += d_mean_n[j];
-      t[j] = v;
-      mx = max(mx, abs_bits(v));
+      const BrnCol c = u.at(col + j);
+      gamma[j] = c.gamma;
+      mean[j] = c.mean;
+      r_over_sigma[j] = c.r / c.sigma;
+      n_sigma[j] = rows_f * c.sigma;
+      d_sigma[j] = (float)sums[3 * (size_t)n + col + j];
+      d_mean_n[j] = (float)sums[2 * (size_t)n + col + j] * inv_rows;
     }
-    *reinterpret_cast<float4 *>(delta + o) = make_float4(t[0], t[1], t[2], t[3]);
-    if (delta_lo)
-      *reinterpret_cast<float4 *>(delta_lo + o) =
-          make_float4(tf32_lo(t[0]), tf32_lo(t[1]), tf32_lo(t[2]), tf32_lo(t[3]));
+    for (int r = r0 + ty; r < r1; r += CR_LANES_Y) {
+      const size_t o = (size_t)r * n + col;
+      const float4 e4 = *reinterpret_cast<const float4 *>(delta + o);
+      const float4 z4 = __ldg(reinterpret_cast<const float4 *>(Z + o));
+      const float e[4] = {e4.x, e4.y, e4.z, e4.w}, z[4] = {z4.x, z4.y, z4.z, z4.w};
+      float t[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float v = e[j] * gamma[j];
+        v *= r_over_sigma[j];
+        v += d_sigma[j] * ((z[j] - mean[j]) / n_sigma[j]);
+        v += d_mean_n[j];
+        t[j] = v;
+      }
+      *reinterpret_cast<float4 *>(delta + o) = make_float4(t[0], t[1], t[2], t[3]);
+      if (PLANES) {
+        sink_store4(sink, o, t, plane_scale);
+        track.row(sink, r, t);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) track.all = max(track.all, abs_bits(t[j]));
+        if (delta_lo)
+          *reinterpret_cast<float4 *>(delta_lo + o) =
+              make_float4(tf32_lo(t[0]), tf32_lo(t[1]), tf32_lo(t[2]), tf32_lo(t[3]));
+      }
+    }
   }
-  amax_commit(amax, mx);
+  if (PLANES) {
+    track.finish(sink, line_shared, tx, ty, CR_LANES_Y, blockIdx.x * CR_COLS, n, live_col);
+    sink_complete(sink);
+  } else if (sink.slot) {
+    amax_commit(reinterpret_cast<unsigned *>(sink.slot) + SLOT_AMAX, track.all);
+  }
 }
 
 __global__ void brn_finalize_kernel(const double *__restrict__ sums, int n, float batch_scale,
@@ -710,9 +749,17 @@ dlb_status dlb_brn_forward_finalize(dlb_ctx *ctx, const double *sums, int global
   return DLB_OK;
 }
 
+// Shapes for which the row kernels run: they are the ones that can write the
+// fp16 planes themselves.
+static bool rows_kernel_applies(const void *a, const void *b, const void *c, int n_units) {
+  return (n_units % 4 == 0) &&
+         ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) == 0;
+}
+
 dlb_status activation_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
                                   int af, const dlb_dropout_desc *dropout, float *A,
-                                  float *A_lo, int rows, int n_units, unsigned *amax) {
+                                  float *A_lo, int rows, int n_units, const PlaneSink &sink) {
+  unsigned *amax = sink.slot ? reinterpret_cast<unsigned *>(sink.slot) + SLOT_AMAX : nullptr;
   DLB_REQUIRE(ctx && Z && A && rows > 0 && n_units > 0, "dlb_activation_forward");
   DropoutDev dp{DLB_DROPOUT_NONE, 1.f, nullptr, nullptr};
   if (dropout && dropout->type != DLB_DROPOUT_NONE) {
@@ -742,12 +789,17 @@ dlb_status activation_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_u
   if (u && vec4) {
     int chunks, rpc;
     rows_plan(ctx, rows, n_units, &chunks, &rpc);
-    activation_forward_rows_kernel<<<dim3(ceil_div(n_units, CR_COLS), chunks),
-                                     CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
-        Z, p, af, dp, A, A_lo, rows, n_units, rpc, amax);
+    const dim3 grid(ceil_div(n_units, CR_COLS), chunks);
+    if (sink.hi)
+      activation_forward_rows_kernel<true><<<grid, CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
+          Z, p, af, dp, A, A_lo, rows, n_units, rpc, sink);
+    else
+      activation_forward_rows_kernel<false><<<grid, CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
+          Z, p, af, dp, A, A_lo, rows, n_units, rpc, sink);
     DLB_LAUNCHED(ctx);
     return DLB_OK;
   }
+  DLB_REQUIRE(!sink.hi, "dlb_activation_forward: planes from a kernel that cannot write them");
   const size_t items = vec4 ? (size_t)rows * (n_units / 4) : (size_t)rows * n_units;
   const int grid = stream_grid(ctx, items, 256);
 #define LAUNCH(NORM, V)                                                                 \
@@ -794,7 +846,8 @@ dlb_status dlb_activation_backward(dlb_ctx *ctx, float *dA, const float *Z, cons
 
 dlb_status brn_backward_apply_impl(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
                                   const dlb_brn_unit_arrays *u, const double *sums,
-                                  int global_rows, int rows, int n_units, unsigned *amax) {
+                                  int global_rows, int rows, int n_units, const PlaneSink &sink) {
+  unsigned *amax = sink.slot ? reinterpret_cast<unsigned *>(sink.slot) + SLOT_AMAX : nullptr;
   DLB_REQUIRE(ctx && delta && Z && u && sums && rows > 0 && n_units > 0 && global_rows > 0,
               "dlb_brn_backward_apply");
   const bool vec4 = (n_units % 4 == 0) && ((reinterpret_cast<uintptr_t>(Z) & 15) == 0) &&
@@ -806,12 +859,18 @@ dlb_status brn_backward_apply_impl(dlb_ctx *ctx, float *delta, float *delta_lo, 
   if (vec4) {
     int chunks, rpc;
     rows_plan(ctx, rows, n_units, &chunks, &rpc);
-    brn_backward_apply_rows_kernel<<<dim3(ceil_div(n_units, CR_COLS), chunks),
-                                     CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
-        delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc, amax);
-  } else
+    const dim3 rgrid(ceil_div(n_units, CR_COLS), chunks);
+    if (sink.hi)
+      brn_backward_apply_rows_kernel<true><<<rgrid, CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
+          delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc, sink);
+    else
+      brn_backward_apply_rows_kernel<false><<<rgrid, CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
+          delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc, sink);
+  } else {
+    DLB_REQUIRE(!sink.hi, "dlb_brn_backward_apply: planes from a kernel that cannot write them");
     brn_backward_apply_kernel<false><<<grid, 256, 0, ctx->stream>>>(
         delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, amax);
+  }
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -1114,23 +1173,25 @@ extern "C" dlb_status dlb_brn_forward_sums_noalloc(const float *Z, int rows, int
 namespace {
 struct PlaneOutput {
   float *kernel_arg = nullptr;  // TF32 form: the residual plane the producing kernel writes
-  float *deferred = nullptr;    // fp16 form: buffer to split into afterwards
-  float *slot = nullptr;        // fp16 form: scale slot of the buffer
-  unsigned *amax = nullptr;     // where the producing kernel leaves max |x| (bits)
-  dlb_status begin(dlb_ctx *ctx, const float *x, float *planes, size_t n) {
+  PlaneJob job;                 // fp16 form
+  // can_fuse: the kernel that will run writes planes and range statistics itself
+  // when handed a full sink.
+  dlb_status begin(dlb_ctx *ctx, const float *x, float *planes, int rows, int cols, bool can_fuse) {
     if (!ctx || !planes) return DLB_OK;
     if (ctx->gemm_kind != DLB_GEMM_F16X3) {
       kernel_arg = planes;
       return DLB_OK;
     }
-    deferred = planes;
-    DLB_TRY(planes_begin(ctx, x, planes, n, &slot));
-    amax = reinterpret_cast<unsigned *>(slot) + 2;
-    return DLB_OK;
+    if (rows <= 0 || cols <= 0) return DLB_OK;  // the kernel's own argument check reports it
+    return planes_open(ctx, x, planes, (size_t)rows * cols, rows, cols, can_fuse, &job);
   }
-  dlb_status finish(dlb_ctx *ctx, dlb_status st, const float *x, size_t n) const {
-    if (st != DLB_OK || !deferred) return st;
-    return planes_finish(ctx, x, deferred, n, slot);
+  const PlaneSink &sink() const { return job.sink; }
+  unsigned *amax() const {
+    return job.sink.slot ? reinterpret_cast<unsigned *>(job.sink.slot) + SLOT_AMAX : nullptr;
+  }
+  dlb_status finish(dlb_ctx *ctx, dlb_status st) const {
+    if (st != DLB_OK) return st;
+    return planes_close(ctx, job);
   }
 };
 }  // namespace
@@ -1141,64 +1202,59 @@ dlb_status dlb_activation_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_un
                                   const dlb_dropout_desc *dropout, float *A, float *A_lo, int rows,
                                   int n_units) {
   PlaneOutput p;
-  DLB_TRY(p.begin(ctx, A, A_lo, (size_t)rows * n_units));
-  return p.finish(ctx, activation_forward_impl(ctx, Z, u, af, dropout, A, p.kernel_arg, rows, n_units, p.amax),
-                  A, (size_t)rows * n_units);
+  DLB_TRY(p.begin(ctx, A, A_lo, rows, n_units, u != nullptr && rows_kernel_applies(Z, A, nullptr, n_units)));
+  return p.finish(ctx, activation_forward_impl(ctx, Z, u, af, dropout, A, p.kernel_arg, rows, n_units, p.sink()));
 }
 
 dlb_status dlb_brn_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
                                   const dlb_brn_unit_arrays *u, const double *sums, int global_rows,
                                   int rows, int n_units) {
   PlaneOutput p;
-  DLB_TRY(p.begin(ctx, delta, delta_lo, (size_t)rows * n_units));
+  DLB_TRY(p.begin(ctx, delta, delta_lo, rows, n_units, rows_kernel_applies(Z, delta, nullptr, n_units)));
   return p.finish(ctx, brn_backward_apply_impl(ctx, delta, p.kernel_arg, Z, u, sums, global_rows, rows, n_units,
-                                               p.amax),
-                  delta, (size_t)rows * n_units);
+                                               p.sink()));
 }
 
 dlb_status dlb_loss_delta(dlb_ctx *ctx, int loss, int af, const float *pre, const float *q, const float *y,
                           float *delta, float *delta_lo, int rows, int n_out, int global_rows,
                           double *loss_sum) {
   PlaneOutput p;
-  DLB_TRY(p.begin(ctx, delta, delta_lo, (size_t)rows * n_out));
+  DLB_TRY(p.begin(ctx, delta, delta_lo, rows, n_out, false));
   return p.finish(ctx, loss_delta_impl(ctx, loss, af, pre, q, y, delta, p.kernel_arg, rows, n_out, global_rows,
-                                       loss_sum, p.amax),
-                  delta, (size_t)rows * n_out);
+                                       loss_sum, p.amax()));
 }
 
 dlb_status dlb_residual_forward(dlb_ctx *ctx, const float *x, float *block, const uint8_t *row_mask,
                                 const float *noise, float *out, float *out_lo, int rows, int width) {
   PlaneOutput p;
-  DLB_TRY(p.begin(ctx, out, out_lo, (size_t)rows * width));
-  return p.finish(ctx, residual_forward_impl(ctx, x, block, row_mask, noise, out, p.kernel_arg, rows, width, p.amax),
-                  out, (size_t)rows * width);
+  DLB_TRY(p.begin(ctx, out, out_lo, rows, width, false));
+  return p.finish(ctx, residual_forward_impl(ctx, x, block, row_mask, noise, out, p.kernel_arg, rows, width, p.amax()));
 }
 
 dlb_status dlb_shakedrop_backward(dlb_ctx *ctx, const float *d, const uint8_t *row_mask, const float *noise,
                                   float *delta, float *delta_lo, int rows, int width) {
   PlaneOutput p;
-  DLB_TRY(p.begin(ctx, delta, delta_lo, (size_t)rows * width));
-  return p.finish(ctx, shakedrop_backward_impl(ctx, d, width, 0, row_mask, noise, delta, p.kernel_arg, rows, width, p.amax),
-                  delta, (size_t)rows * width);
+  DLB_TRY(p.begin(ctx, delta, delta_lo, rows, width, false));
+  return p.finish(ctx, shakedrop_backward_impl(ctx, d, width, 0, row_mask, noise, delta, p.kernel_arg, rows, width,
+                                               p.amax()));
 }
 
 dlb_status dlb_residual_forward_padded(dlb_ctx *ctx, const float *x, int width_x, float *block, int width_block,
                                        const uint8_t *row_mask, const float *noise, float *out, float *out_lo,
                                        int rows) {
-  const size_t n = (size_t)rows * (width_x > width_block ? width_x : width_block);
   PlaneOutput p;
-  DLB_TRY(p.begin(ctx, out, out_lo, n));
+  DLB_TRY(p.begin(ctx, out, out_lo, rows, width_x > width_block ? width_x : width_block, false));
   return p.finish(ctx, residual_forward_padded_impl(ctx, x, width_x, block, width_block, row_mask, noise, out,
-                                                    p.kernel_arg, rows, p.amax), out, n);
+                                                    p.kernel_arg, rows, p.amax()));
 }
 
 dlb_status dlb_shakedrop_backward_window(dlb_ctx *ctx, const float *d, int width_d, int first,
                                          const uint8_t *row_mask, const float *noise, float *delta,
                                          float *delta_lo, int rows, int width) {
   PlaneOutput p;
-  DLB_TRY(p.begin(ctx, delta, delta_lo, (size_t)rows * width));
+  DLB_TRY(p.begin(ctx, delta, delta_lo, rows, width, false));
   return p.finish(ctx, shakedrop_backward_impl(ctx, d, width_d, first, row_mask, noise, delta, p.kernel_arg, rows,
-                                               width, p.amax), delta, (size_t)rows * width);
+                                               width, p.amax()));
 }
 
 }  // extern "C"

@@ -21,6 +21,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "gemm_simt.cuh"
 #include "tc_ptx.cuh"
 
 namespace dlb {
@@ -130,8 +131,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
                         float *__restrict__ C, long long ldc, int M, int N, int K,
                         const float *__restrict__ bias, int accumulate, int tiles_n, int whole_tiles,
                         int parts, int total_items, const float *__restrict__ scale_a,
-                        const float *__restrict__ scale_b, int *status) {
+                        const float *__restrict__ scale_b, int *status, const unsigned *guard_a,
+                        const unsigned *guard_b, SimtOperands fp32, unsigned long long *fallbacks) {
   using P = PairPlan<STAGES>;
+  // Range guard: the planes of a flagged operand do not stand for its tensor.
+  // The product is then formed from the fp32 tensors on the CUDA cores, every
+  // CTA taking its share of the 64 x 64 tiles (a rare and slow path that keeps
+  // the result right; the counter tells the host that it was taken).  Both
+  // CTAs of a pair read the same words and take the same branch.
+  if ((guard_a && *guard_a) || (guard_b && *guard_b)) {
+    extern __shared__ __align__(16) uint8_t guard_smem[];
+    if (fallbacks && blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(fallbacks, 1ull);
+    gemm_simt_guard_path(fp32, C, ldc, M, N, K, bias, accumulate, reinterpret_cast<float *>(guard_smem));
+    return;
+  }
   constexpr int MN_W = 64;  // halfs of one 128-byte column of an MN-major tile
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -425,7 +438,9 @@ dlb_status launch_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B,
   const int items = whole_tiles + parts * split_tiles;
   kernel<<<2 * min(items, lanes), NUM_THREADS, P::TOTAL, ctx->stream>>>(
       ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, parts, items, A.scale,
-      B.scale, ctx->d_status);
+      B.scale, ctx->d_status, A.guard, B.guard,
+      SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k},
+      ctx->d_guard ? ctx->d_guard + 1 : nullptr);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }

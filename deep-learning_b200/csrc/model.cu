@@ -384,8 +384,8 @@ dlb_status refresh_weight_residuals(dlb_model *m) {
   for (size_t i = 1; i < m->layers.size(); ++i) {
     const LayerRT &l = m->layers[i];
     if (l.type == DLB_LAYER_RESIDUAL) continue;
-    DLB_TRY(dlb_split_planes(m->ctx, m->params + l.first_conn, m->params_lo + l.first_conn,
-                             l.units * l.fan_in));
+    DLB_TRY(dlb_split_planes_2d(m->ctx, m->params + l.first_conn, m->params_lo + l.first_conn, (int)l.units,
+                                (int)l.fan_in));
   }
   m->params_lo_valid = true;
   return DLB_OK;
@@ -718,6 +718,10 @@ dlb_status dlb_model_destroy(dlb_model *m) {
   for (float *p : flat)
     if (p) dlb_free(m->ctx, p);
   if (m->loss_sum) dlb_free(m->ctx, m->loss_sum);
+  if (m->loss_tmp) dlb_free(m->ctx, m->loss_tmp);
+  if (m->loss_host) dlb_host_free(m->loss_host);
+  for (cudaEvent_t e : m->loss_ready)
+    if (e) cudaEventDestroy(e);
   if (m->accu_sum) dlb_free(m->ctx, m->accu_sum);
   if (m->ones) dlb_free(m->ctx, m->ones);
   if (m->zeros) dlb_free(m->ctx, m->zeros);
@@ -1225,7 +1229,7 @@ dlb_status dlb_model_forward_pass_device(dlb_model *m, size_t rows, const float 
     DLB_TRY(dlb_activation_forward(m->ctx, m->input, nullptr, DLB_AF_LINEAR, &dp, m->input, m->input_lo,
                                    (int)rows, (int)n_in(m)));
   } else {
-    DLB_TRY(dlb_split_planes(m->ctx, m->input, m->input_lo, n));
+    DLB_TRY(dlb_split_planes_2d(m->ctx, m->input, m->input_lo, (int)rows, (int)n_in(m)));
   }
   return forward_layers(m, rows);
 }
@@ -1309,7 +1313,7 @@ static dlb_status backward_residual(dlb_model *m, size_t i, int B) {
     } else {
       DLB_TRY(dlb_activation_backward(m->ctx, prev.delta, prev.A, b.IN, nullptr, b.af, B,
                                       (int)b.fan_in, nullptr));
-      DLB_TRY(dlb_split_planes(m->ctx, prev.delta, prev.delta_lo, (size_t)B * b.fan_in));
+      DLB_TRY(dlb_split_planes_2d(m->ctx, prev.delta, prev.delta_lo, B, (int)b.fan_in));
     }
   }
   return DLB_OK;
@@ -1349,11 +1353,11 @@ static dlb_status backward_pass_time(dlb_model *m, size_t rows) {
         DLB_TRY(dlb_allreduce_f64(m->ctx, l.bwd_sums + 2 * plane, 2 * plane));
         DLB_TRY(dlb_brn_time_backward_apply(m->ctx, l.delta, l.delta_lo, l.Z, &u, l.bwd_sums, Bg, T, B, H));
       } else {
-        DLB_TRY(dlb_split_planes(m->ctx, l.delta, l.delta_lo, (size_t)TB * H));
+        DLB_TRY(dlb_split_planes_2d(m->ctx, l.delta, l.delta_lo, TB, H));
       }
     } else {
       DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, nullptr, l.af, TB, H, nullptr));
-      DLB_TRY(dlb_split_planes(m->ctx, l.delta, l.delta_lo, (size_t)TB * H));
+      DLB_TRY(dlb_split_planes_2d(m->ctx, l.delta, l.delta_lo, TB, H));
     }
     if (i == 1) break;  // the error into the input layer is never formed
     LayerRT &below = m->layers[i - 1];
@@ -1404,7 +1408,7 @@ dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows) {
         DLB_TRY(norm_backward(m, l, l.delta, l.delta_lo, l.Z, l.A, l.af, B));
       } else {
         DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, nullptr, l.af, B, H, nullptr));
-        DLB_TRY(dlb_split_planes(m->ctx, l.delta, l.delta_lo, (size_t)B * H));
+        DLB_TRY(dlb_split_planes_2d(m->ctx, l.delta, l.delta_lo, B, H));
       }
     }
     if (below)
@@ -1544,10 +1548,18 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
       if (l.type == DLB_LAYER_RESIDUAL) continue;
       const size_t nw = l.units * l.fan_in;
       DLB_TRY(segment(at, l.first_conn - at, nullptr));
-      float *slot = nullptr;
-      DLB_TRY(planes_begin(m->ctx, m->params + l.first_conn, m->params_lo + l.first_conn, nw, &slot));
-      DLB_TRY(segment(l.first_conn, nw, reinterpret_cast<unsigned *>(slot) + 2));
-      DLB_TRY(planes_finish(m->ctx, m->params + l.first_conn, m->params_lo + l.first_conn, nw, slot));
+      PlaneJob job;
+      DLB_TRY(planes_open(m->ctx, m->params + l.first_conn, m->params_lo + l.first_conn, nw, (int)l.units,
+                          (int)l.fan_in, true, &job));
+      if (job.fused) {
+        const size_t o = l.first_conn;
+        DLB_TRY(optimizer_step_sink(m->ctx, m->optimizer, &k, m->params + o, m->grads + o, m->m1 + o, m->m2 + o,
+                                    m->m2hat ? m->m2hat + o : nullptr, wd != 0.f ? m->wd_mask + o : nullptr,
+                                    (int)l.units, (int)l.fan_in, job.sink));
+      } else {
+        DLB_TRY(segment(l.first_conn, nw, reinterpret_cast<unsigned *>(job.sink.slot) + 2));
+      }
+      DLB_TRY(planes_close(m->ctx, job));
       at = l.first_conn + nw;
     }
     DLB_TRY(segment(at, m->total_parameters - at, nullptr));
@@ -1672,6 +1684,39 @@ dlb_status dlb_model_get_loss(dlb_model *m, double *loss) {
 
 static dlb_status update_and_merge_overlapped(dlb_model *m, size_t rows);
 
+// Starts the trip of the current loss sum to the host (slot = step parity) and
+// returns without waiting.
+static dlb_status loss_capture(dlb_model *m, int slot) {
+  DLB_REQUIRE(m->loss_sum, "loss: no step has run");
+  if (!m->loss_tmp) {
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&m->loss_tmp), 2 * sizeof(double)));
+    DLB_TRY(dlb_host_alloc(reinterpret_cast<void **>(&m->loss_host), 2 * sizeof(double)));
+    for (cudaEvent_t &e : m->loss_ready) DLB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  }
+  DLB_TRY(dlb_memcpy_d2d(m->ctx, m->loss_tmp + slot, m->loss_sum, sizeof(double)));
+  DLB_TRY(dlb_allreduce_f64(m->ctx, m->loss_tmp + slot, 1));
+  DLB_CUDA(cudaMemcpyAsync(m->loss_host + slot, m->loss_tmp + slot, sizeof(double), cudaMemcpyDeviceToHost,
+                           m->ctx->stream));
+  DLB_CUDA(cudaEventRecord(m->loss_ready[slot], m->ctx->stream));
+  m->loss_rows_at[slot] = m->loss_rows;
+  m->loss_valid[slot] = true;
+  return DLB_OK;
+}
+
+// Waits for a captured loss and normalises it as dlb_model_get_loss does.
+static dlb_status loss_collect(dlb_model *m, int slot, double *loss) {
+  if (!m->loss_valid[slot]) {
+    *loss = nan("");  // a lagged read before the first step has finished
+    return DLB_OK;
+  }
+  DLB_CUDA(cudaEventSynchronize(m->loss_ready[slot]));
+  const double rows = (double)m->loss_rows_at[slot] * (double)dlb_comm_world(m->ctx);
+  const double s = m->loss_host[slot];
+  if (rows == 0) { *loss = 1.0; return DLB_OK; }
+  *loss = m->loss == DLB_LOSS_CROSS_ENTROPY ? s / rows : s / (rows * (double)n_out(m));
+  return DLB_OK;
+}
+
 // Plain stack of fully connected layers (no residual block, one time step).
 static bool plain_stack(const dlb_model *m) {
   if (time_stepped(m)) return false;
@@ -1698,7 +1743,7 @@ static dlb_status backward_and_derivatives_overlapped(dlb_model *m, size_t rows)
         DLB_TRY(norm_backward(m, l, l.delta, l.delta_lo, l.Z, l.A, l.af, B));
       } else {
         DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, nullptr, l.af, B, H, nullptr));
-        DLB_TRY(dlb_split_planes(m->ctx, l.delta, l.delta_lo, (size_t)B * H));
+        DLB_TRY(dlb_split_planes_2d(m->ctx, l.delta, l.delta_lo, B, H));
       }
     }
     const float *X = i == 1 ? m->input : m->layers[i - 1].A;
@@ -1758,9 +1803,14 @@ dlb_status dlb_model_train_step(dlb_model *m, size_t rows, const float *X_host,
   DLB_TRY(dlb_model_forward_pass_device(m, rows, x_dev));
   DLB_TRY(dlb_model_compute_error_device(m, rows, y_dev));
   DLB_TRY(backward_update_merge(m, rows));
-  if (loss) DLB_TRY(dlb_model_get_loss(m, loss));
+  // The loss starts its way to the host, the update is enqueued, and only then
+  // does the host wait for the loss: the update runs meanwhile.
+  const int slot = (int)(m->loss_steps++ & 1);
+  if (loss) DLB_TRY(loss_capture(m, slot));
   const size_t g = m->global_rows ? m->global_rows : rows;
-  return dlb_model_update_weights(m, g, m->training_size ? m->training_size : g);
+  DLB_TRY(dlb_model_update_weights(m, g, m->training_size ? m->training_size : g));
+  if (loss) DLB_TRY(loss_collect(m, slot, loss));
+  return DLB_OK;
 }
 
 // Input side of the mini-batch loop, MiniBatch::train_mp
@@ -1817,11 +1867,22 @@ dlb_status dlb_model_train_step_staged(dlb_model *m, double *loss) {
   DLB_CUDA(cudaEventRecord(a.consumed, m->ctx->stream));
   a.in_use = true;
   DLB_TRY(backward_update_merge(m, rows));
-  // The loss is read before the update is enqueued, as train_step does: the
-  // update then runs while the host prepares the next call.
-  if (loss) DLB_TRY(dlb_model_get_loss(m, loss));
+  // The loss starts its way to the host and the update is enqueued before the
+  // host waits for anything.  With a loss lag of one step the wait is for the
+  // loss of the step before, which has long arrived: the host then never waits
+  // for the step it has just enqueued and runs one step ahead of the device.
+  const int slot = (int)(m->loss_steps++ & 1);
+  if (loss) DLB_TRY(loss_capture(m, slot));
   const size_t g = m->global_rows ? m->global_rows : rows;
-  return dlb_model_update_weights(m, g, m->training_size ? m->training_size : g);
+  DLB_TRY(dlb_model_update_weights(m, g, m->training_size ? m->training_size : g));
+  if (loss) DLB_TRY(loss_collect(m, m->loss_lag ? slot ^ 1 : slot, loss));
+  return DLB_OK;
+}
+
+dlb_status dlb_model_set_loss_lag(dlb_model *m, int steps) {
+  DLB_REQUIRE(m && (steps == 0 || steps == 1), "set_loss_lag: 0 or 1");
+  m->loss_lag = steps;
+  return DLB_OK;
 }
 
 dlb_status dlb_model_get_layer_outputs(dlb_model *m, size_t layer, size_t rows, float *host_out) {

@@ -110,6 +110,17 @@ struct dlb_model {
   cudaStream_t copy_stream = nullptr;
   size_t ahead_head = 0, ahead_tail = 0;  // staged so far, consumed so far
   double *loss_sum = nullptr;
+  // The loss of a one-call step leaves the device asynchronously: a device copy of the
+  // sum, its exchange across ranks, a copy into page-locked host memory and an
+  // event, two slots used in turn, so that the update is enqueued before the
+  // host waits.  loss_lag = 1: a staged step returns the loss of the step before.
+  double *loss_tmp = nullptr;       // device [2]
+  double *loss_host = nullptr;      // page-locked [2]
+  cudaEvent_t loss_ready[2] = {nullptr, nullptr};
+  size_t loss_rows_at[2] = {0, 0};
+  bool loss_valid[2] = {false, false};
+  size_t loss_steps = 0;
+  int loss_lag = 0;
   size_t loss_rows = 0;  // rows accumulated since reset_loss
   bool params_lo_valid = false;
   uint64_t plane_generation = 0;  // the context's value when the weights were last split

@@ -8,8 +8,11 @@
 // writes p, g<-0 (16 bytes), +8 for the previous delta with momentum.
 #include <math.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "math.cuh"
+#include "planes.cuh"
 
 namespace dlb {
 
@@ -108,6 +111,100 @@ __global__ void __launch_bounds__(256)
     if (HAT) vh[i] = s.vh;
   }
   amax_commit(amax, mx);
+}
+
+// The same update over a weight matrix [rows, cols] (cols a multiple of 4) that
+// also writes the fp16 planes of the new weights, with the scale predicted from
+// the matrix's previous split, and the row / column maxima of the range guard:
+// the next forward pass finds the planes ready and no split pass reads the
+// matrix again.  Grid (column blocks of 128, row chunks); a thread owns four
+// columns and walks its rows eight apart.
+constexpr int OPT_LANES_Y = 8;
+template <int RULE, bool WD>
+__global__ void __launch_bounds__(32 * OPT_LANES_Y)
+    optimizer_rows_kernel(dlb_optimizer_scalars k, float *__restrict__ p, float *__restrict__ g,
+                          float *__restrict__ m, float *__restrict__ v, float *__restrict__ vh,
+                          const float *__restrict__ mask, int rows, int cols, int rows_per_chunk, PlaneSink sink) {
+  __shared__ unsigned line_shared[OPT_LANES_Y * 128];
+  constexpr bool HAT = (RULE == R_AMSGRAD || RULE == R_AMSBOUND);
+  constexpr bool FIRST = RULE != R_GD;
+  constexpr bool SECOND = !(RULE == R_GD || RULE == R_GD_MOMENTUM || RULE == R_GD_NESTEROV);
+  const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
+  const int col = blockIdx.x * 128 + tx * 4;
+  const bool live = col < cols;
+  const float plane_scale = sink_scale(sink);
+  LineTracker track;
+  if (live) {
+    const int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+    for (int r = r0 + ty; r < r1; r += OPT_LANES_Y) {
+      const size_t o = (size_t)r * cols + col;
+      float4 P = *reinterpret_cast<const float4 *>(p + o);
+      const float4 G = *reinterpret_cast<const float4 *>(g + o);
+      float4 H = make_float4(0.f, 0.f, 0.f, 0.f), K = H, M = H, V = H;
+      if (FIRST) M = *reinterpret_cast<const float4 *>(m + o);
+      if (SECOND) V = *reinterpret_cast<const float4 *>(v + o);
+      if (HAT) H = *reinterpret_cast<const float4 *>(vh + o);
+      if (WD) K = __ldg(reinterpret_cast<const float4 *>(mask + o));
+      OptState s0{P.x, G.x, M.x, V.x, H.x}, s1{P.y, G.y, M.y, V.y, H.y}, s2{P.z, G.z, M.z, V.z, H.z},
+          s3{P.w, G.w, M.w, V.w, H.w};
+      update_one<RULE, WD>(s0, K.x, k);
+      update_one<RULE, WD>(s1, K.y, k);
+      update_one<RULE, WD>(s2, K.z, k);
+      update_one<RULE, WD>(s3, K.w, k);
+      const float out[4] = {s0.p, s1.p, s2.p, s3.p};
+      *reinterpret_cast<float4 *>(p + o) = make_float4(s0.p, s1.p, s2.p, s3.p);
+      if (FIRST) *reinterpret_cast<float4 *>(m + o) = make_float4(s0.m, s1.m, s2.m, s3.m);
+      if (SECOND) *reinterpret_cast<float4 *>(v + o) = make_float4(s0.v, s1.v, s2.v, s3.v);
+      if (HAT) *reinterpret_cast<float4 *>(vh + o) = make_float4(s0.vh, s1.vh, s2.vh, s3.vh);
+      *reinterpret_cast<float4 *>(g + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+      sink_store4(sink, o, out, plane_scale);
+      track.row(sink, r, out);
+    }
+  }
+  track.finish(sink, line_shared, tx, ty, OPT_LANES_Y, blockIdx.x * 128, cols, live);
+  sink_complete(sink);
+}
+
+// Calls f(std::integral_constant<int, R>) with the kernel rule of an optimizer
+// code of the C ABI.
+template <class F>
+static dlb_status with_rule(int rule, const dlb_optimizer_scalars &s, F f) {
+  switch (rule) {
+    case DLB_OPT_ADAM:
+    case DLB_OPT_NOSADAM: return f(std::integral_constant<int, R_ADAM>{});
+    case DLB_OPT_AMSGRAD: return f(std::integral_constant<int, R_AMSGRAD>{});
+    case DLB_OPT_ADABOUND: return f(std::integral_constant<int, R_ADABOUND>{});
+    case DLB_OPT_AMSBOUND: return f(std::integral_constant<int, R_AMSBOUND>{});
+    case DLB_OPT_ADAMAX: return f(std::integral_constant<int, R_ADAMAX>{});
+    case DLB_OPT_GD:
+      // The three forms of Model::Update_Parameter__Gradient_Descent
+      // (v1/optimizers/gradient_descent.cpp L:24-55).
+      if (s.beta1 == 0.f) return f(std::integral_constant<int, R_GD>{});
+      if (s.beta2 != 0.f) return f(std::integral_constant<int, R_GD_NESTEROV>{});
+      return f(std::integral_constant<int, R_GD_MOMENTUM>{});
+    default:
+      set_error("dlb_optimizer_step: optimizer %d is outside the supported path", rule);
+      return DLB_ERR_UNSUPPORTED;
+  }
+}
+
+template <int RULE>
+static dlb_status launch_rule_rows(dlb_ctx *ctx, const dlb_optimizer_scalars &k, float *p, float *g, float *m,
+                                   float *v, float *vh, const float *mask, int rows, int cols,
+                                   const PlaneSink &sink) {
+  const int col_blocks = ceil_div(cols, 128);
+  int chunks = max(1, min(ceil_div(ctx->sm_count * 8, col_blocks), ceil_div(rows, OPT_LANES_Y)));
+  const int rpc = ceil_div(ceil_div(rows, chunks), OPT_LANES_Y) * OPT_LANES_Y;
+  chunks = ceil_div(rows, rpc);
+  const dim3 grid(col_blocks, chunks);
+  if (k.weight_decay != 0.f)
+    optimizer_rows_kernel<RULE, true><<<grid, 32 * OPT_LANES_Y, 0, ctx->stream>>>(k, p, g, m, v, vh, mask, rows, cols,
+                                                                                  rpc, sink);
+  else
+    optimizer_rows_kernel<RULE, false><<<grid, 32 * OPT_LANES_Y, 0, ctx->stream>>>(k, p, g, m, v, vh, mask, rows,
+                                                                                   cols, rpc, sink);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
 }
 
 template <int RULE>
@@ -217,29 +314,21 @@ dlb_status dlb::optimizer_step_amax(dlb_ctx *ctx, int rule, const dlb_optimizer_
                        (hat ? reinterpret_cast<uintptr_t>(second_hat) : 0) |
                        (s->weight_decay != 0.f ? reinterpret_cast<uintptr_t>(wd_mask) : 0);
   DLB_REQUIRE((al & 15) == 0, "dlb_optimizer_step: arrays must be 16-byte aligned");
-  switch (rule) {
-    case DLB_OPT_ADAM:
-    case DLB_OPT_NOSADAM:
-      return launch_rule<R_ADAM>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
-    case DLB_OPT_AMSGRAD:
-      return launch_rule<R_AMSGRAD>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
-    case DLB_OPT_ADABOUND:
-      return launch_rule<R_ADABOUND>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
-    case DLB_OPT_AMSBOUND:
-      return launch_rule<R_AMSBOUND>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
-    case DLB_OPT_ADAMAX:
-      return launch_rule<R_ADAMAX>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
-    case DLB_OPT_GD:
-      // The three forms of Model::Update_Parameter__Gradient_Descent
-      // (v1/optimizers/gradient_descent.cpp L:24-55).
-      if (s->beta1 == 0.f) return launch_rule<R_GD>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
-      if (s->beta2 != 0.f)
-        return launch_rule<R_GD_NESTEROV>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
-      return launch_rule<R_GD_MOMENTUM>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
-    default:
-      set_error("dlb_optimizer_step: optimizer %d is outside the supported path", rule);
-      return DLB_ERR_UNSUPPORTED;
-  }
+  return with_rule(rule, *s, [&](auto R) {
+    return launch_rule<decltype(R)::value>(ctx, *s, p, g, first, second, second_hat, wd_mask, n, amax);
+  });
+}
+
+// The pass over one weight matrix [rows, cols] that also writes the matrix's
+// fp16 planes and range statistics through `sink` (optimizer_rows_kernel).
+dlb_status dlb::optimizer_step_sink(dlb_ctx *ctx, int rule, const dlb_optimizer_scalars *s, float *p, float *g,
+                                    float *first, float *second, float *second_hat, const float *wd_mask,
+                                    int rows, int cols, const PlaneSink &sink) {
+  DLB_REQUIRE(ctx && s && p && g && rows > 0 && cols > 0 && (cols & 3) == 0 && sink.hi && sink.slot,
+              "optimizer_step_sink");
+  return with_rule(rule, *s, [&](auto R) {
+    return launch_rule_rows<decltype(R)::value>(ctx, *s, p, g, first, second, second_hat, wd_mask, rows, cols, sink);
+  });
 }
 
 extern "C" {

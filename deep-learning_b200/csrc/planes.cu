@@ -8,8 +8,10 @@
 // into it, its element count and the device slot of s; the FC entry points
 // look their `_lo` arguments up there.
 #include <cuda_fp16.h>
+#include <string.h>
 
 #include "common.cuh"
+#include "planes.cuh"
 
 namespace dlb {
 
@@ -37,44 +39,59 @@ __global__ void absmax_kernel(const float *__restrict__ x, size_t n, unsigned *s
   if (threadIdx.x % 32 == 0 && m > *reinterpret_cast<volatile unsigned *>(slot)) atomicMax(slot, m);
 }
 
-// s = 2^(14 - E) for max = 1.f * 2^E; 1 for a zero, infinite or NaN maximum.
-__device__ __forceinline__ float scale_from_bits(unsigned bits) {
-  const int be = (int)(bits >> 23);  // biased exponent of the maximum
-  if (bits == 0 || be == 255) return 1.f;
-  int se = 14 - (be - 127) + 127;    // biased exponent of s
-  se = min(max(se, 1), 254);
-  return __uint_as_float((unsigned)se << 23);
-}
-
-__global__ void split_f16_kernel(const float *__restrict__ x, size_t n, __half *__restrict__ hi,
-                                 __half *__restrict__ lo, float *slot) {
-  const float s = scale_from_bits(reinterpret_cast<const unsigned *>(slot)[2]);
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    slot[0] = s;
-    slot[1] = 1.f / s;
-  }
+// Flat split of a tensor without a shape (or one whose rows are not a whole
+// number of float4): planes only, no line statistics.
+__global__ void split_flat_kernel(const float *__restrict__ x, size_t n, PlaneSink k) {
+  const float s = sink_scale(k);
+  __half *hi = reinterpret_cast<__half *>(k.hi), *lo = reinterpret_cast<__half *>(k.lo);
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const bool vec = ((reinterpret_cast<uintptr_t>(x) & 15) | (reinterpret_cast<uintptr_t>(hi) & 7) |
                     (reinterpret_cast<uintptr_t>(lo) & 7)) == 0;
-  auto one = [s](float v, __half *h, __half *l) {
-    const float t = v * s;
-    const __half a = __float2half_rn(t);
-    *h = a;
-    *l = __float2half_rn(t - __half2float(a));
-  };
   const size_t n4 = vec ? n / 4 : 0;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
     const float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i);
-    __half h[4], l[4];
-    one(v.x, h, l);
-    one(v.y, h + 1, l + 1);
-    one(v.z, h + 2, l + 2);
-    one(v.w, h + 3, l + 3);
-    reinterpret_cast<uint2 *>(hi)[i] = *reinterpret_cast<uint2 *>(h);
-    reinterpret_cast<uint2 *>(lo)[i] = *reinterpret_cast<uint2 *>(l);
+    const float a[4] = {v.x, v.y, v.z, v.w};
+    sink_store4(k, i * 4, a, s);
   }
   for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
-    one(x[i], hi + i, lo + i);
+    plane_halves(x[i], s, hi + i, lo + i);
+  sink_complete(k);
+}
+
+// Split of a [rows, cols] tensor (cols a multiple of 4) with the row and column
+// maxima: grid (column blocks of 128, row chunks), a thread owns four columns
+// and walks its rows eight apart, as the other row kernels of the step do.
+constexpr int SPLIT_LANES_Y = 8;
+__global__ void __launch_bounds__(32 * SPLIT_LANES_Y)
+    split_rows_kernel(const float *__restrict__ x, int rows, int cols, int rows_per_chunk, PlaneSink k) {
+  __shared__ unsigned shared[SPLIT_LANES_Y * 128];
+  const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
+  const int col = blockIdx.x * 128 + tx * 4;
+  const bool live = col < cols;
+  const float s = sink_scale(k);
+  LineTracker track;
+  if (live) {
+    const int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+    for (int r = r0 + ty; r < r1; r += 2 * SPLIT_LANES_Y) {
+      const int r2 = r + SPLIT_LANES_Y;
+      const size_t o = (size_t)r * cols + col, o2 = (size_t)r2 * cols + col;
+      const float4 v = __ldg(reinterpret_cast<const float4 *>(x + o));
+      float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r2 < r1) w = __ldg(reinterpret_cast<const float4 *>(x + o2));
+      const float a[4] = {v.x, v.y, v.z, v.w};
+      sink_store4(k, o, a, s);
+      track.row(k, r, a);
+      if (r2 < r1) {
+        const float b[4] = {w.x, w.y, w.z, w.w};
+        sink_store4(k, o2, b, s);
+        track.row(k, r2, b);
+      }
+    }
+  }
+  // Under a predicted scale the tensor's maximum is found here as well; where it
+  // was known before (it gave s) the atomic maximum changes nothing.
+  track.finish(k, shared, tx, ty, SPLIT_LANES_Y, blockIdx.x * 128, cols, live);
+  sink_complete(k);
 }
 
 int stream_blocks(dlb_ctx *ctx, size_t items) {
@@ -84,7 +101,7 @@ int stream_blocks(dlb_ctx *ctx, size_t items) {
 
 dlb_status scale_slot(dlb_ctx *ctx, float **out) {
   if (!ctx->scale_pool) {
-    DLB_CUDA(cudaMalloc(&ctx->scale_pool, (size_t)SCALE_SLOTS * 4 * sizeof(float)));
+    DLB_CUDA(cudaMalloc(&ctx->scale_pool, (size_t)SCALE_SLOTS * SLOT_WORDS * sizeof(float)));
     ctx->scale_free.reserve(SCALE_SLOTS);
     for (int i = SCALE_SLOTS - 1; i >= 0; --i) ctx->scale_free.push_back(i);
   }
@@ -92,23 +109,50 @@ dlb_status scale_slot(dlb_ctx *ctx, float **out) {
     set_error("dlb_split_planes: more than %d plane buffers are registered", SCALE_SLOTS);
     return DLB_ERR_INVALID;
   }
-  *out = ctx->scale_pool + 4 * (size_t)ctx->scale_free.back();
+  *out = ctx->scale_pool + (size_t)SLOT_WORDS * ctx->scale_free.back();
   ctx->scale_free.pop_back();
   return DLB_OK;
 }
 
-}  // namespace
+dlb_status guard_counters(dlb_ctx *ctx) {
+  if (ctx->d_guard) return DLB_OK;
+  DLB_CUDA(cudaMalloc(&ctx->d_guard, 4 * sizeof(unsigned long long)));
+  DLB_CUDA(cudaMemsetAsync(ctx->d_guard, 0, 4 * sizeof(unsigned long long), ctx->stream));
+  return DLB_OK;
+}
 
-dlb_status split_f16(dlb_ctx *ctx, const float *x, size_t n, uint16_t *hi, uint16_t *lo, float *slot) {
-  DLB_CUDA(cudaMemsetAsync(slot + 2, 0, sizeof(float), ctx->stream));
-  const int grid = stream_blocks(ctx, n / 4 + 1);
-  absmax_kernel<<<grid, 256, 0, ctx->stream>>>(x, n, reinterpret_cast<unsigned *>(slot) + 2);
-  DLB_LAUNCHED(ctx);
-  split_f16_kernel<<<grid, 256, 0, ctx->stream>>>(x, n, reinterpret_cast<__half *>(hi),
-                                                  reinterpret_cast<__half *>(lo), slot);
+void release_entry(dlb_ctx *ctx, dlb_ctx::PlaneEntry &e) {
+  ctx->scale_free.push_back((int)((e.scale - ctx->scale_pool) / SLOT_WORDS));
+  if (e.lines) {
+    cudaStreamSynchronize(ctx->stream);  // a check kernel may still read the array
+    cudaFree(e.lines);
+    e.lines = nullptr;
+  }
+}
+
+// The split pass of a tensor whose maximum is in its slot (or whose predicted
+// scale is to be used): by rows with statistics where the shape allows.
+dlb_status launch_split(dlb_ctx *ctx, const float *x, size_t n, int rows, int cols, const PlaneSink &k) {
+  const bool by_rows = rows > 0 && cols > 0 && (cols & 3) == 0 && (size_t)rows * cols == n &&
+                       ((reinterpret_cast<uintptr_t>(x) & 15) | (reinterpret_cast<uintptr_t>(k.hi) & 7) |
+                        (reinterpret_cast<uintptr_t>(k.lo) & 7)) == 0;
+  if (by_rows) {
+    const int col_blocks = ceil_div(cols, 128);
+    int chunks = max(1, min(ceil_div(ctx->sm_count * 8, col_blocks), ceil_div(rows, 2 * SPLIT_LANES_Y)));
+    const int rpc = ceil_div(ceil_div(rows, chunks), 2 * SPLIT_LANES_Y) * 2 * SPLIT_LANES_Y;
+    chunks = ceil_div(rows, rpc);
+    split_rows_kernel<<<dim3(col_blocks, chunks), 32 * SPLIT_LANES_Y, 0, ctx->stream>>>(x, rows, cols, rpc, k);
+  } else {
+    PlaneSink flat = k;
+    flat.rowmax = flat.colmax = nullptr;
+    flat.n_lines = 0;
+    split_flat_kernel<<<stream_blocks(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(x, n, flat);
+  }
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
+
+}  // namespace
 
 bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o) {
   if (!aux || ctx->planes.empty()) return false;
@@ -126,17 +170,19 @@ bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o) {
   o->h_hi = hi;
   o->h_lo = lo;
   o->scale = e.scale;
+  o->guard = reinterpret_cast<const unsigned *>(e.scale) + SLOT_FLAGS;
   return true;
 }
 
-// Registers `planes` as the plane buffer of x[0..n), clears the maximum of its
-// scale slot and returns the slot; the caller then lets max |x| (bits) arrive
-// in slot[2] and calls planes_finish.
-dlb_status planes_begin(dlb_ctx *ctx, const float *x, float *planes, size_t n, float **slot_out) {
+// Registers `planes` as the plane buffer of x[0..n) with the given shape (0, 0:
+// none) and fills the job.  A registration of the same tensor, size and shape
+// is kept, with its predicted scale; anything else this buffer overlaps is
+// stale and dropped.
+dlb_status planes_open(dlb_ctx *ctx, const float *x, float *planes, size_t n, int rows, int cols,
+                       bool kernel_can_fuse, PlaneJob *job) {
   DLB_REQUIRE(x && planes && n > 0 && n < ((size_t)1 << 40), "plane buffer: tensor, buffer and size");
+  if ((size_t)rows * (size_t)cols != n) rows = cols = 0;
   const uintptr_t key = reinterpret_cast<uintptr_t>(planes);
-  // Buffers registered earlier that this one overwrites are stale: those that
-  // start inside it, and one that starts before and reaches into it.
   planes_forget(ctx, key + 1, n * sizeof(float) - 1);
   auto before = ctx->planes.lower_bound(key);
   if (before != ctx->planes.begin()) {
@@ -144,30 +190,104 @@ dlb_status planes_begin(dlb_ctx *ctx, const float *x, float *planes, size_t n, f
     if (before->first + before->second.n * sizeof(float) > key) planes_forget(ctx, before->first, 1);
   }
   auto it = ctx->planes.find(key);
-  if (it == ctx->planes.end()) {
-    float *slot = nullptr;
-    DLB_TRY(scale_slot(ctx, &slot));
-    it = ctx->planes.emplace(key, dlb_ctx::PlaneEntry{x, n, slot}).first;
+  if (it != ctx->planes.end() &&
+      (it->second.x != x || it->second.n != n || it->second.rows != rows || it->second.cols != cols)) {
+    planes_forget(ctx, key, 1);
+    it = ctx->planes.end();
   }
-  it->second.x = x;
-  it->second.n = n;
-  DLB_CUDA(cudaMemsetAsync(it->second.scale + 2, 0, sizeof(float), ctx->stream));
-  *slot_out = it->second.scale;
+  if (it == ctx->planes.end()) {
+    dlb_ctx::PlaneEntry e;
+    e.x = x;
+    e.n = n;
+    e.rows = rows;
+    e.cols = cols;
+    DLB_TRY(scale_slot(ctx, &e.scale));
+    DLB_CUDA(cudaMemsetAsync(e.scale, 0, SLOT_WORDS * sizeof(float), ctx->stream));
+    if (rows > 0) {
+      DLB_CUDA(cudaMalloc(&e.lines, (size_t)(rows + cols) * sizeof(unsigned)));
+      DLB_CUDA(cudaMemsetAsync(e.lines, 0, (size_t)(rows + cols) * sizeof(unsigned), ctx->stream));
+    }
+    it = ctx->planes.emplace(key, e).first;
+  }
+  dlb_ctx::PlaneEntry &e = it->second;
+  static const bool fuse_enabled = [] {
+    const char *v = getenv("DLB_PLANES_FUSED");
+    return !(v && v[0] == '0');
+  }();
+  job->x = x;
+  job->planes = planes;
+  job->n = n;
+  job->rows = rows;
+  job->cols = cols;
+  job->active = true;
+  job->fused = kernel_can_fuse && e.seen && fuse_enabled && rows > 0 && (cols & 3) == 0 &&
+               (reinterpret_cast<uintptr_t>(planes) & 7) == 0 && ((n * 2) & 7) == 0;
+  DLB_TRY(guard_counters(ctx));
+  job->sink = PlaneSink{};
+  job->sink.slot = e.scale;
+  job->sink.guard = ctx->d_guard;
+  if (job->fused) {
+    job->sink.n_lines = rows + cols;
+    job->sink.hi = reinterpret_cast<uint16_t *>(planes);
+    job->sink.lo = job->sink.hi + n;
+    job->sink.rowmax = e.lines;
+    job->sink.colmax = e.lines + rows;
+    job->sink.predicted = 1;
+  }
   return DLB_OK;
 }
 
-dlb_status planes_finish(dlb_ctx *ctx, const float *x, float *planes, size_t n, float *slot) {
-  __half *hi = reinterpret_cast<__half *>(planes);
-  split_f16_kernel<<<stream_blocks(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(x, n, hi, hi + n, slot);
+dlb_status planes_close(dlb_ctx *ctx, const PlaneJob &job) {
+  if (!job.active) return DLB_OK;
+  auto it = ctx->planes.find(reinterpret_cast<uintptr_t>(job.planes));
+  DLB_REQUIRE(it != ctx->planes.end(), "plane buffer: closed without a registration");
+  dlb_ctx::PlaneEntry &e = it->second;
+  if (!job.fused) {
+    // The producing kernel left the tensor's maximum in the slot: the split pass.
+    PlaneSink k;
+    k.hi = reinterpret_cast<uint16_t *>(job.planes);
+    k.lo = k.hi + job.n;
+    k.slot = e.scale;
+    k.rowmax = e.lines;
+    k.colmax = e.lines ? e.lines + e.rows : nullptr;
+    k.n_lines = e.lines ? e.rows + e.cols : 0;
+    k.predicted = 0;
+    k.guard = ctx->d_guard;
+    DLB_TRY(launch_split(ctx, job.x, job.n, e.rows, e.cols, k));
+  }
+  e.seen = true;
+  return DLB_OK;
+}
+
+dlb_status planes_absmax(dlb_ctx *ctx, const float *x, size_t n, float *slot) {
+  absmax_kernel<<<stream_blocks(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(x, n, reinterpret_cast<unsigned *>(slot) + SLOT_AMAX);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
+}
+
+dlb_status planes_split_adhoc(dlb_ctx *ctx, const float *x, size_t n, int rows, int cols, uint16_t *hi,
+                              uint16_t *lo, float *slot, unsigned *lines) {
+  if ((size_t)rows * (size_t)cols != n) rows = cols = 0;
+  DLB_CUDA(cudaMemsetAsync(slot, 0, SLOT_WORDS * sizeof(float), ctx->stream));
+  if (rows > 0 && lines) DLB_CUDA(cudaMemsetAsync(lines, 0, (size_t)(rows + cols) * sizeof(unsigned), ctx->stream));
+  DLB_TRY(planes_absmax(ctx, x, n, slot));
+  DLB_TRY(guard_counters(ctx));
+  PlaneSink k;
+  k.hi = hi;
+  k.lo = lo;
+  k.slot = slot;
+  k.rowmax = rows > 0 ? lines : nullptr;
+  k.colmax = rows > 0 && lines ? lines + rows : nullptr;
+  k.n_lines = k.rowmax ? rows + cols : 0;
+  k.guard = ctx->d_guard;
+  return launch_split(ctx, x, n, rows, cols, k);
 }
 
 // Drops the entries whose buffer starts inside [base, base + bytes).
 void planes_forget(dlb_ctx *ctx, uintptr_t base, size_t bytes) {
   auto it = ctx->planes.lower_bound(base);
   while (it != ctx->planes.end() && it->first < base + bytes) {
-    ctx->scale_free.push_back((int)((it->second.scale - ctx->scale_pool) / 4));
+    release_entry(ctx, it->second);
     it = ctx->planes.erase(it);
   }
 }
@@ -193,15 +313,40 @@ dlb_status dlb_ctx_set_gemm_kind(dlb_ctx *ctx, int kind) {
 
 int dlb_ctx_gemm_kind(dlb_ctx *ctx) { return ctx ? ctx->gemm_kind : -1; }
 
+dlb_status dlb_split_planes_2d(dlb_ctx *ctx, const float *x, float *planes, int rows, int cols) {
+  DLB_REQUIRE(ctx && x && planes && rows >= 0 && cols >= 0, "dlb_split_planes_2d");
+  const size_t n = (size_t)rows * (size_t)cols;
+  if (n == 0) return DLB_OK;
+  if (ctx->gemm_kind == DLB_GEMM_TF32X3) return dlb_split_tf32(ctx, x, planes, n);
+  PlaneJob job;
+  DLB_TRY(planes_open(ctx, x, planes, n, rows, cols, true, &job));
+  // With a scale predicted from this buffer's previous split one pass does; the
+  // first split takes the tensor's maximum first.
+  if (job.fused) DLB_TRY(launch_split(ctx, x, n, rows, cols, job.sink));
+  else DLB_TRY(planes_absmax(ctx, x, n, job.sink.slot));
+  return planes_close(ctx, job);
+}
+
 dlb_status dlb_split_planes(dlb_ctx *ctx, const float *x, float *planes, size_t n) {
   DLB_REQUIRE(ctx && x && planes, "dlb_split_planes: null");
   if (n == 0) return DLB_OK;
   if (ctx->gemm_kind == DLB_GEMM_TF32X3) return dlb_split_tf32(ctx, x, planes, n);
-  float *slot = nullptr;
-  DLB_TRY(planes_begin(ctx, x, planes, n, &slot));
-  absmax_kernel<<<stream_blocks(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(x, n, reinterpret_cast<unsigned *>(slot) + 2);
-  DLB_LAUNCHED(ctx);
-  return planes_finish(ctx, x, planes, n, slot);
+  PlaneJob job;
+  DLB_TRY(planes_open(ctx, x, planes, n, 0, 0, false, &job));
+  DLB_TRY(planes_absmax(ctx, x, n, job.sink.slot));
+  return planes_close(ctx, job);
+}
+
+dlb_status dlb_ctx_guard_counters(dlb_ctx *ctx, uint64_t *tensors_flagged, uint64_t *products_on_fallback) {
+  DLB_REQUIRE(ctx && tensors_flagged && products_on_fallback, "dlb_ctx_guard_counters: null");
+  unsigned long long host[2] = {0, 0};
+  if (ctx->d_guard) {
+    DLB_CUDA(cudaMemcpyAsync(host, ctx->d_guard, sizeof(host), cudaMemcpyDeviceToHost, ctx->stream));
+    DLB_CUDA(cudaStreamSynchronize(ctx->stream));
+  }
+  *tensors_flagged = host[0];
+  *products_on_fallback = host[1];
+  return DLB_OK;
 }
 
 }  // extern "C"

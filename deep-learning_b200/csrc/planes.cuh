@@ -1,0 +1,173 @@
+// Device side of the fp16 operand planes: the scale slot, the split of a value
+// into its two halves, and the statistics a producing kernel leaves for the
+// range guard.
+//
+// Scale slot of a plane buffer (SLOT_WORDS 4-byte words):
+//   [SLOT_S]     s, the power of two the planes in the buffer were scaled by
+//   [SLOT_INV]   1 / s
+//   [SLOT_AMAX]  raw bits of max |x| of the split in progress; zero between splits
+//   [SLOT_FLAGS] non-zero: the planes cannot stand for the tensor (see below)
+//   [SLOT_NEXT]  the scale predicted for the next split of this buffer
+//   [SLOT_TICKET] blocks of the writing kernel that have finished; zero between splits
+//
+// A split with the tensor's own maximum known (two passes over the tensor) puts
+// s max|x| in [2^14, 2^15).  A producing kernel that writes the planes itself
+// cannot know its maximum beforehand and uses the scale predicted from the
+// buffer's previous split, which aims at [2^12, 2^13): the tensor may grow
+// eightfold from one step to the next before a value leaves the fp16 range.
+//
+// Range guard.  hi = fp16(s x), lo = fp16(s x - hi) carry 22 bits of x while
+// s |x| >= 2^-3; below that lo falls into the fp16 subnormals and a bit is lost
+// per factor of two.  That is harmless for small elements among large ones (the
+// error is 2^-39 of the tensor's maximum), but not when every element of a row
+// or a column is small: the outputs that row or column feeds are then wrong by
+// more than fp32 rounding relative to their own size.  Producers therefore
+// leave max |x| per row and per column, and the last block of the kernel that
+// wrote the planes (sink_complete) flags the tensor when a non-zero row or
+// column maximum is below PLANE_TINY / s (18 bits left) or when the tensor's
+// maximum overflowed the predicted scale.  The
+// tensor-core kernels compute a product with a flagged operand on the CUDA
+// cores from the fp32 tensors instead.
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "math.cuh"
+
+namespace dlb {
+
+constexpr int SLOT_S = 0, SLOT_INV = 1, SLOT_AMAX = 2, SLOT_FLAGS = 3, SLOT_NEXT = 4, SLOT_TICKET = 5;
+constexpr int PLANE_EXP_OWN = 14;        // s max in [2^14, 2^15): the scale from the tensor's own maximum
+constexpr int PLANE_EXP_PREDICTED = 12;  // s max in [2^12, 2^13): the scale predicted for the next split
+constexpr float PLANE_TINY = 0.0078125f; // 2^-7: a line whose largest s |x| is below this has under 18 bits
+constexpr float PLANE_HALF_MAX = 65504.f;
+
+// s = 2^(target - E) for max = 1.f * 2^E; 1 for a zero, infinite or NaN maximum.
+__host__ __device__ __forceinline__ float plane_scale_from_bits(unsigned bits, int target) {
+  const int be = (int)(bits >> 23);  // biased exponent of the maximum
+  if (bits == 0 || be == 255) return 1.f;
+  int se = target - (be - 127) + 127;  // biased exponent of s
+  se = se < 1 ? 1 : (se > 254 ? 254 : se);
+  const unsigned u = (unsigned)se << 23;
+#ifdef __CUDA_ARCH__
+  return __uint_as_float(u);
+#else
+  float f;
+  memcpy(&f, &u, sizeof(f));
+  return f;
+#endif
+}
+
+// The scale a kernel writing through `k` uses for this split.
+__device__ __forceinline__ float sink_scale(const PlaneSink &k) {
+  if (!k.hi) return 1.f;
+  return k.predicted ? k.slot[SLOT_NEXT]
+                     : plane_scale_from_bits(reinterpret_cast<const unsigned *>(k.slot)[SLOT_AMAX], PLANE_EXP_OWN);
+}
+
+__device__ __forceinline__ void plane_halves(float v, float s, __half *h, __half *l) {
+  const float t = v * s;
+  const __half a = __float2half_rn(t);
+  *h = a;
+  *l = __float2half_rn(t - __half2float(a));
+}
+
+// Four consecutive elements starting at element `off` (a multiple of 4): one
+// 8-byte store into each plane.
+__device__ __forceinline__ void sink_store4(const PlaneSink &k, size_t off, const float (&v)[4], float s) {
+  __half h[4], l[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) plane_halves(v[j], s, h + j, l + j);
+  *reinterpret_cast<uint2 *>(k.hi + off) = *reinterpret_cast<uint2 *>(h);
+  *reinterpret_cast<uint2 *>(k.lo + off) = *reinterpret_cast<uint2 *>(l);
+}
+
+// Statistics of a thread that owns four columns and visits whole rows together
+// with the other lanes of its warp (every lane of the warp is on the same row
+// in the same call): the row's maximum goes out with one atomic per warp and
+// row, the column maxima stay in registers until `finish`.
+struct LineTracker {
+  unsigned cm[4] = {0u, 0u, 0u, 0u};
+  unsigned all = 0u;
+  __device__ __forceinline__ void row(const PlaneSink &k, int r, const float (&v)[4]) {
+    unsigned m = 0u;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const unsigned b = abs_bits(v[j]);
+      cm[j] = max(cm[j], b);
+      m = max(m, b);
+    }
+    all = max(all, m);
+    if (k.rowmax) {
+      const unsigned mask = __activemask();
+      const unsigned w = __reduce_max_sync(mask, m);
+      if ((threadIdx.x & 31u) == (unsigned)(__ffs(mask) - 1) && w) atomicMax(k.rowmax + r, w);
+    }
+  }
+  // Called by every thread of the block (threads past the last column with
+  // live = false).  `shared` holds lanes_y * 128 words; tx in [0, 32), ty in
+  // [0, lanes_y), col0 the block's first column, n the number of columns.
+  __device__ __forceinline__ void finish(const PlaneSink &k, unsigned *shared, int tx, int ty, int lanes_y,
+                                         int col0, int n, bool live) {
+    if (k.slot) amax_commit(reinterpret_cast<unsigned *>(k.slot) + SLOT_AMAX, live ? all : 0u);
+    if (!k.colmax) return;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) shared[ty * 128 + tx * 4 + j] = live ? cm[j] : 0u;
+    __syncthreads();
+    const int t = ty * 32 + tx;
+    if (t < 128 && col0 + t < n) {
+      unsigned m = 0u;
+      for (int y = 0; y < lanes_y; ++y) m = max(m, shared[y * 128 + t]);
+      if (m) atomicMax(k.colmax + col0 + t, m);
+    }
+  }
+};
+
+// Last step of a kernel that wrote planes through `k`, called by every thread of
+// every block once the block's stores and statistics are out.  The block that
+// finishes last turns the statistics into what the consumers read: the scale
+// and its inverse, the guard flag, the scale predicted for the next split; and
+// it clears what the next split accumulates into (maximum, line maxima, ticket).
+__device__ __forceinline__ void sink_complete(const PlaneSink &k) {
+  if (!k.slot) return;
+  __shared__ int is_last;
+  unsigned *uslot = reinterpret_cast<unsigned *>(k.slot);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned blocks = gridDim.x * gridDim.y * gridDim.z;
+    is_last = atomicAdd(uslot + SLOT_TICKET, 1u) == blocks - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const unsigned amax = __ldcg(uslot + SLOT_AMAX);
+  const float s = k.predicted ? __ldcg(k.slot + SLOT_NEXT) : plane_scale_from_bits(amax, PLANE_EXP_OWN);
+  int tiny = 0;
+  unsigned *lines = k.rowmax;
+  for (int i = threadIdx.x; i < (lines ? k.n_lines : 0); i += blockDim.x) {
+    const unsigned v = __ldcg(lines + i);
+    if (v) {
+      if (__uint_as_float(v) * s < PLANE_TINY) tiny = 1;
+      lines[i] = 0u;
+    }
+  }
+  tiny = __syncthreads_or(tiny);
+  if (threadIdx.x == 0) {
+    // NaN or infinity in the tensor, or growth past the predicted scale.
+    const bool overflow = !(__uint_as_float(amax) * s < PLANE_HALF_MAX);
+    const unsigned unsafe = (tiny || overflow) ? 1u : 0u;
+    k.slot[SLOT_S] = s;
+    k.slot[SLOT_INV] = 1.f / s;
+    uslot[SLOT_FLAGS] = unsafe;
+    // The next split is predicted from this one's maximum; an empty or
+    // non-finite tensor leaves the prediction where it was.
+    k.slot[SLOT_NEXT] = (amax == 0u || (amax >> 23) == 255u) ? s : plane_scale_from_bits(amax, PLANE_EXP_PREDICTED);
+    uslot[SLOT_AMAX] = 0u;
+    uslot[SLOT_TICKET] = 0u;
+    if (unsafe && k.guard) atomicAdd(k.guard, 1ull);
+  }
+}
+
+}  // namespace dlb

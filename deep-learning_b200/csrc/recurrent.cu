@@ -587,22 +587,23 @@ dlb_status dlb_indrnn_clamp(dlb_ctx *ctx, float *recurrent, int n, float lo, flo
 // leaves max |x| in the plane buffer's scale slot and the split follows.
 namespace {
 struct TimePlanes {
-  float *kernel_arg = nullptr, *deferred = nullptr, *slot = nullptr;
+  float *kernel_arg = nullptr;
+  PlaneJob job;
   unsigned *amax = nullptr;
-  dlb_status begin(dlb_ctx *ctx, const float *x, float *planes, size_t n) {
+  // The tensor is [seq_w * rows, n]: its range statistics are per row of that
+  // matrix and per unit.
+  dlb_status begin(dlb_ctx *ctx, const float *x, float *planes, size_t rows, int n) {
     if (!ctx || !planes) return DLB_OK;
     if (ctx->gemm_kind != DLB_GEMM_F16X3) {
       kernel_arg = planes;
       return DLB_OK;
     }
-    deferred = planes;
-    DLB_TRY(planes_begin(ctx, x, planes, n, &slot));
-    amax = reinterpret_cast<unsigned *>(slot) + 2;
+    if (rows == 0 || n <= 0 || rows > 0x7fffffffu) return DLB_OK;
+    DLB_TRY(planes_open(ctx, x, planes, rows * (size_t)n, (int)rows, n, false, &job));
+    amax = reinterpret_cast<unsigned *>(job.sink.slot) + 2;
     return DLB_OK;
   }
-  dlb_status finish(dlb_ctx *ctx, const float *x, size_t n) const {
-    return deferred ? planes_finish(ctx, x, deferred, n, slot) : DLB_OK;
-  }
+  dlb_status finish(dlb_ctx *ctx) const { return planes_close(ctx, job); }
 };
 }  // namespace
 
@@ -612,9 +613,9 @@ dlb_status dlb_time_major(dlb_ctx *ctx, const float *x, float *out, float *out_l
                           int n) {
   const size_t total = (size_t)(seq_w > 0 ? seq_w : 0) * (rows > 0 ? rows : 0) * (n > 0 ? n : 0);
   TimePlanes p;
-  DLB_TRY(p.begin(ctx, out, out_lo, total));
+  DLB_TRY(p.begin(ctx, out, out_lo, total / (size_t)(n > 0 ? n : 1), n));
   DLB_TRY(time_major_impl(ctx, x, out, p.kernel_arg, rows, seq_w, n, p.amax));
-  return p.finish(ctx, out, total);
+  return p.finish(ctx);
 }
 
 dlb_status dlb_indrnn_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
@@ -622,9 +623,9 @@ dlb_status dlb_indrnn_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_a
                               int n) {
   const size_t total = (size_t)(seq_w > 0 ? seq_w : 0) * (rows > 0 ? rows : 0) * (n > 0 ? n : 0);
   TimePlanes p;
-  DLB_TRY(p.begin(ctx, A, A_lo, total));
+  DLB_TRY(p.begin(ctx, A, A_lo, total / (size_t)(n > 0 ? n : 1), n));
   DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, nullptr, 1.f, A, p.kernel_arg, seq_w, rows, n, p.amax));
-  return p.finish(ctx, A, total);
+  return p.finish(ctx);
 }
 
 dlb_status dlb_indrnn_forward_dropout(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
@@ -632,9 +633,9 @@ dlb_status dlb_indrnn_forward_dropout(dlb_ctx *ctx, const float *Z, const dlb_br
                                       float *A, float *A_lo, int seq_w, int rows, int n) {
   const size_t total = (size_t)(seq_w > 0 ? seq_w : 0) * (rows > 0 ? rows : 0) * (n > 0 ? n : 0);
   TimePlanes p;
-  DLB_TRY(p.begin(ctx, A, A_lo, total));
+  DLB_TRY(p.begin(ctx, A, A_lo, total / (size_t)(n > 0 ? n : 1), n));
   DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, mask, keep_scale, A, p.kernel_arg, seq_w, rows, n, p.amax));
-  return p.finish(ctx, A, total);
+  return p.finish(ctx);
 }
 
 dlb_status dlb_brn_time_backward_apply(dlb_ctx *ctx, float *delta, float *delta_lo, const float *Z,
@@ -642,10 +643,10 @@ dlb_status dlb_brn_time_backward_apply(dlb_ctx *ctx, float *delta, float *delta_
                                        int seq_w, int rows, int n) {
   const size_t total = (size_t)(seq_w > 0 ? seq_w : 0) * (rows > 0 ? rows : 0) * (n > 0 ? n : 0);
   TimePlanes p;
-  DLB_TRY(p.begin(ctx, delta, delta_lo, total));
+  DLB_TRY(p.begin(ctx, delta, delta_lo, total / (size_t)(n > 0 ? n : 1), n));
   DLB_TRY(brn_time_backward_apply_impl(ctx, delta, p.kernel_arg, Z, u, sums, global_rows, seq_w, rows, n,
                                        p.amax));
-  return p.finish(ctx, delta, total);
+  return p.finish(ctx);
 }
 
 }  // extern "C"

@@ -49,6 +49,7 @@ SIGNATURES = {
     "dlb_ctx_timer_stop": (_i, [_vp, C.POINTER(_f)]),
     "dlb_ctx_gemm_profile": (_i, [_vp, _i]),
     "dlb_ctx_gemm_profile_read": (_i, [_vp, C.POINTER(_u64), C.POINTER(_d), C.POINTER(_d)]),
+    "dlb_ctx_comm_profile_read": (_i, [_vp, C.POINTER(_u64), C.POINTER(_d), C.POINTER(_u64), C.POINTER(_d)]),
     "dlb_malloc": (_i, [_vp, C.POINTER(_vp), _sz]),
     "dlb_free": (_i, [_vp, _vp]),
     "dlb_memset": (_i, [_vp, _vp, _i, _sz]),
@@ -60,6 +61,8 @@ SIGNATURES = {
     "dlb_host_free": (_i, [_vp]),
     "dlb_split_tf32": (_i, [_vp, _vp, _vp, _sz]),
     "dlb_split_planes": (_i, [_vp, _vp, _vp, _sz]),
+    "dlb_split_planes_2d": (_i, [_vp, _vp, _vp, _i, _i]),
+    "dlb_ctx_guard_counters": (_i, [_vp, C.POINTER(_u64), C.POINTER(_u64)]),
     "dlb_ctx_set_gemm_kind": (_i, [_vp, _i]),
     "dlb_ctx_gemm_kind": (_i, [_vp]),
     "dlb_fc_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
@@ -159,6 +162,7 @@ SIGNATURES = {
     "dlb_model_draw_noise": (_i, [_vp, _sz, _u64, C.c_uint32, _sz]),
     "dlb_model_stage_batch": (_i, [_vp, _sz, _vp, _vp]),
     "dlb_model_train_step_staged": (_i, [_vp, C.POINTER(_d)]),
+    "dlb_model_set_loss_lag": (_i, [_vp, _i]),
     "dlb_model_get_layer_outputs": (_i, [_vp, _sz, _sz, _vp]),
     "dlb_model_get_layer_errors": (_i, [_vp, _sz, _sz, _i, _vp]),
 }
@@ -230,6 +234,12 @@ class Context:
     def gemm_kind(self):
         return self.L.dlb_ctx_gemm_kind(self.h)
 
+    def guard_counters(self):
+        """(operand tensors the range guard flagged, products that ran on the fp32 kernel instead)."""
+        a, b = _u64(0), _u64(0)
+        check(self.L.dlb_ctx_guard_counters(self.h, C.byref(a), C.byref(b)), "dlb_ctx_guard_counters")
+        return int(a.value), int(b.value)
+
     def launch_count(self):
         return int(self.L.dlb_ctx_launch_count(self.h))
 
@@ -249,6 +259,14 @@ class Context:
         n, ms, fl = _u64(0), _d(0.0), _d(0.0)
         check(self.L.dlb_ctx_gemm_profile_read(self.h, C.byref(n), C.byref(ms), C.byref(fl)), "gemm_profile_read")
         return int(n.value), ms.value, fl.value
+
+    def comm_profile_read(self):
+        """(waits for the overlapped all-reduces, their ms, exchanges of sums, their ms) of the
+        records the last gemm_profile_read consumed."""
+        a, b, c, d = _u64(0), _d(0.0), _u64(0), _d(0.0)
+        check(self.L.dlb_ctx_comm_profile_read(self.h, C.byref(a), C.byref(b), C.byref(c), C.byref(d)),
+              "comm_profile_read")
+        return int(a.value), b.value, int(c.value), d.value
 
     @property
     def stream(self):
@@ -590,6 +608,10 @@ class Model:
         check(self.L.dlb_model_train_step_staged(self.h, C.byref(loss) if want_loss else None),
               "train_step_staged")
         return loss.value
+
+    def set_loss_lag(self, steps):
+        """1: train_step_staged returns the loss of the step before (NaN at first)."""
+        check(self.L.dlb_model_set_loss_lag(self.h, int(steps)), "set_loss_lag")
 
     def train_step_device(self, batch, X_dev, Y_dev):
         check(self.L.dlb_model_train_step_device(self.h, batch, X_dev.ptr, Y_dev.ptr), "train_step_device")

@@ -87,6 +87,14 @@ dlb_status dlb_ctx_timer_stop(dlb_ctx *ctx, float *milliseconds);
 dlb_status dlb_ctx_gemm_profile(dlb_ctx *ctx, int enable);
 dlb_status dlb_ctx_gemm_profile_read(dlb_ctx *ctx, uint64_t *launches, double *milliseconds,
                                      double *flops);
+/* While the same profiling is on, two more things are bracketed by events on the
+ * context's stream: every wait of the stream for the overlapped gradient
+ * all-reduces (dlb_comm_join: the part of the transfers that the kernels did
+ * not hide) and every exchange of batch-renormalization sums
+ * (dlb_allreduce_f64).  Their counts and summed durations over the records that
+ * the last dlb_ctx_gemm_profile_read consumed: */
+dlb_status dlb_ctx_comm_profile_read(dlb_ctx *ctx, uint64_t *join_waits, double *join_wait_ms,
+                                     uint64_t *exchanges, double *exchange_ms);
 
 /* Device memory for callers without their own CUDA binding. */
 dlb_status dlb_malloc(dlb_ctx *ctx, void **dev_ptr, size_t bytes);
@@ -133,6 +141,23 @@ dlb_status dlb_ctx_set_gemm_kind(dlb_ctx *ctx, int kind);
 int dlb_ctx_gemm_kind(dlb_ctx *ctx);
 /* Plane buffer of x in the context's current form (TF32: dlb_split_tf32). */
 dlb_status dlb_split_planes(dlb_ctx *ctx, const float *x, float *planes, size_t n);
+/* The same for a row-major [rows, cols] tensor.  Knowing the shape, the split
+ * also records the largest |x| of every row and every column for the range
+ * guard of the fp16 form: the planes carry 22 bits of an element only while
+ * it is within 2^-17 of the tensor's largest, so a row or column whose every
+ * element is far smaller than the rest of the tensor would come out of a
+ * product with less than fp32 accuracy relative to its own size.  Such a tensor
+ * (a non-zero row or column maximum below 2^-21 of the tensor's, or a value
+ * that overflows the scale) is flagged, the tensor-core kernel skips every
+ * product that reads it and an fp32 CUDA-core kernel computes those products
+ * instead.  dlb_ctx_guard_counters reads how often that happened: operand
+ * tensors flagged, products that took the fp32 kernel.  Entry points that
+ * produce an operand tensor together with its plane buffer record the same
+ * statistics.  The check sees each operand alone: a column that is small in one
+ * operand and made up for by a huge column in the other is not detected; the
+ * TF32 form has fp32 range throughout. */
+dlb_status dlb_split_planes_2d(dlb_ctx *ctx, const float *x, float *planes, int rows, int cols);
+dlb_status dlb_ctx_guard_counters(dlb_ctx *ctx, uint64_t *tensors_flagged, uint64_t *products_on_fallback);
 
 /* ------------------------------------------------------------------------ */
 /* FC GEMMs. */
@@ -621,6 +646,13 @@ dlb_status dlb_model_set_clip_gradient(dlb_model *m, int use, float value);
 dlb_status dlb_model_stage_batch(dlb_model *m, size_t rows, const float *X_host,
                                  const float *Y_host);
 dlb_status dlb_model_train_step_staged(dlb_model *m, double *loss);
+/* steps = 1: dlb_model_train_step_staged returns the loss of the step before the
+ * one it has just enqueued (NaN on the first call), so that the host never
+ * waits for the device inside the loop and runs one step ahead of it;
+ * dlb_model_get_loss after the loop reads the last step's.  steps = 0
+ * (default): the loss of the step itself, for which the host waits after it
+ * has enqueued the update. */
+dlb_status dlb_model_set_loss_lag(dlb_model *m, int steps);
 dlb_status dlb_model_get_layer_outputs(dlb_model *m, size_t layer, size_t rows, float *host_out);
 dlb_status dlb_model_get_layer_errors(dlb_model *m, size_t layer, size_t rows, int which,
                                       float *host_out);

@@ -238,7 +238,8 @@ def test_time_major_sums_and_clamp(gpu_ctx, T, B, n):
     rng = np.random.default_rng(T + n)
     x = rng.standard_normal((B, T * n)).astype(np.float32)
     out, lo = ctx.empty((T, B, n)), ctx.empty((T, B, n))
-    dlb200.check(L.dlb_time_major(ctx.h, ctx.array(x).ptr, out.ptr, lo.ptr, B, T, n))
+    xd = ctx.array(x)   # kept alive: a temporary would be freed before the kernel reads it
+    dlb200.check(L.dlb_time_major(ctx.h, xd.ptr, out.ptr, lo.ptr, B, T, n))
     want = x.reshape(B, T, n).transpose(1, 0, 2)
     assert np.array_equal(out.get(), want)
     sums = ctx.empty((2, T, n), dtype=np.float64)

@@ -458,3 +458,34 @@ def test_training_size_enters_the_normalised_weight_decay(gpu_ctx):
     a, b, c = (m.get_array("parameters") for m in models)
     assert np.array_equal(a, b)
     assert not np.array_equal(a, c)
+
+
+def test_staged_steps_with_a_lagged_loss(gpu_ctx):
+    """With a loss lag of one step a staged step returns the loss of the step
+    before (NaN at first) and the host never waits for the step it has just
+    enqueued; weights and losses are those of the in-order loop."""
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96)
+    B = cfg["batch"]
+    batches = []
+    for step in range(4):
+        pair = []
+        for host in configs.synthetic_batch(cfg, step=step):
+            buf = dlb200.pinned_empty(host.shape)
+            buf[...] = host
+            pair.append(buf)
+        batches.append(tuple(pair))
+    a = util.build(dlb200.Model(gpu_ctx), cfg, seed=3)
+    b = util.build(dlb200.Model(gpu_ctx), cfg, seed=3)
+    want = [a.train_step(B, X, Y) for X, Y in batches]
+    b.set_loss_lag(1)
+    got = []
+    for X, Y in batches:
+        b.stage_batch(B, X, Y)
+        got.append(b.train_step_staged())
+    got.append(b.get_loss())
+    assert np.isnan(got[0])
+    np.testing.assert_allclose(got[1:], want, rtol=1e-12)
+    assert np.array_equal(a.get_array("parameters"), b.get_array("parameters"))
+    with pytest.raises(dlb200.DlbError):
+        b.set_loss_lag(2)
+    assert gpu_ctx.sync() == 0
