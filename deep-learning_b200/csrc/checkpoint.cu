@@ -525,7 +525,7 @@ dlb_status dlb_model_save_spec_params(dlb_model *m, const char *path) {
   section("REGULARIZATION PARAMETERS");
   kv("regularization__max_norm_constraints", "0");
   kv("regularization__l1", "0");
-  kv("regularization__l2", "0");
+  kv("regularization__l2", num(m->hp.regularization_l2));
   kv("regularization__srip", "0");
   kv("weight_decay", num(p.weight_decay));
   kv("use_normalized_weight_decay", num((int)p.use_normalized_weight_decay));
@@ -729,6 +729,10 @@ dlb_status dlb_model_load(dlb_model *m, const char *path_params, const char *pat
   for (const char *k : {"regularization__max_norm_constraints", "regularization__l1", "regularization__l2",
                         "regularization__srip"}) {
     DLB_TRY(s.real(k, &d));
+    if (std::string(k) == "regularization__l2") {
+      DLB_TRY(dlb_model_set_l2(m, (float)d));
+      continue;
+    }
     if (d != 0.0) {
       set_error("load: %s = %g is outside the supported path", k, d);
       return DLB_ERR_UNSUPPORTED;

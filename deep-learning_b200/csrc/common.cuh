@@ -87,6 +87,8 @@ struct dlb_ctx {
     uint32_t seq = 0;       // exchanges so far, the same on every rank
   } peer;
   uint64_t launches = 0;
+  // Programmatic dependent launch for the library's kernels (DLB_PDL=0 turns it off).
+  bool use_pdl = true;
   cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
   // Optional per-launch record of the tensor-core GEMM.
   struct GemmRecord {
@@ -129,6 +131,42 @@ void set_error(const char *fmt, ...);
     dlb_status s__ = (expr);                                                   \
     if (s__ != DLB_OK) return s__;                                             \
   } while (0)
+
+// Every kernel of the library begins with pdl_enter(): it waits until the kernels
+// before it in the stream have completed and their writes are visible
+// (griddepcontrol.wait; nothing to wait for under an ordinary launch), then lets
+// the kernel behind it be scheduled (griddepcontrol.launch_dependents).  Launched
+// with programmatic stream serialization (DLB_LAUNCH_KERNEL), the blocks of the
+// next kernel take the places the last blocks of this one leave, run up to their
+// own wait and start the moment this kernel is complete: the launch latency and
+// the ramp of the block scheduler, a few microseconds per kernel boundary,
+// disappear from a step of sixty kernels.  The hardware dispatches all blocks of
+// a grid before any block of the next, so a waiting block never takes a place a
+// working block needs.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <class... P, class... A>
+inline cudaError_t launch_kernel(dlb_ctx *ctx, void (*kernel)(P...), dim3 grid, dim3 block, size_t smem,
+                                 A &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->use_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+#define DLB_LAUNCH_KERNEL(ctx, kernel, grid, block, smem, ...) \
+  dlb::launch_kernel((ctx), (kernel), dim3(grid), dim3(block), (size_t)(smem), __VA_ARGS__)
+#endif
 
 // After a kernel launch: count it and surface launch-configuration errors.
 #define DLB_LAUNCHED(ctx)                                                      \
@@ -220,8 +258,7 @@ struct PlaneSink {
 // when the kernel can and such a scale exists, else the kernel only tracks
 // max |x| (sink.slot) and planes_close runs the split pass.  planes_close then
 // launches the check that sets the slot's scale and guard flag for the
-// consumers and the prediction for the next split (the last block of the kernel
-// that wrote the planes does it: sink_complete in planes.cuh).
+// consumers and the prediction for the next split (planes_finalize_kernel).
 struct PlaneJob {
   PlaneSink sink;
   const float *x = nullptr;

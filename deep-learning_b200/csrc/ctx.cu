@@ -310,6 +310,7 @@ dlb_status dlb_ctx_create(dlb_ctx **out, int device) {
   ctx->tensor_core_ok = true;
   if (const char *e = getenv("DLB_TENSOR_CORE")) ctx->use_tensor_core = atoi(e) != 0;
   if (const char *e = getenv("DLB_GEMM_RESERVE_SMS")) ctx->gemm_reserve_sms = max(0, min(atoi(e), prop.multiProcessorCount - 1));
+  if (const char *e = getenv("DLB_PDL")) ctx->use_pdl = atoi(e) != 0;
   if (const char *e = getenv("DLB_GEMM_KIND")) ctx->gemm_kind = e[0] == 't' ? DLB_GEMM_TF32X3 : DLB_GEMM_F16X3;
   cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaMalloc(&ctx->d_status, sizeof(int));

@@ -33,6 +33,7 @@ constexpr int CR_MAX_PER_SM = 4;
 template <int NSUM, class Op>
 __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
     column_reduce_kernel(Op op, int rows, int n, int rows_per_chunk, double *partials) {
+  pdl_enter();
   __shared__ double red[CR_LANES_Y][NSUM][CR_COLS + 1];
   const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
   const int col = blockIdx.x * CR_COLS + tx * 4;
@@ -48,7 +49,19 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
     if ((n & 3) == 0) {
       typename Op::Cols4 c;
       op.load_cols4(col, c);
-      for (int r = r0 + ty; r < r1; r += CR_LANES_Y) op.row4(r, col, c, acc);
+      // Op::IN_FLIGHT rows per iteration, their loads first: each thread keeps
+      // that many 16-byte requests per input tensor in flight.  The sums take
+      // the rows in ascending order either way.
+      constexpr int U = Op::IN_FLIGHT;
+      for (int r = r0 + ty; r < r1; r += U * CR_LANES_Y) {
+        typename Op::Row4 x[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k)
+          if (r + k * CR_LANES_Y < r1) op.load4(r + k * CR_LANES_Y, col, x[k]);
+#pragma unroll
+        for (int k = 0; k < U; ++k)
+          if (r + k * CR_LANES_Y < r1) op.use4(r + k * CR_LANES_Y, col, c, x[k], acc);
+      }
     } else {
       for (int j = 0; j < 4 && col + j < n; ++j) {
         typename Op::Cols1 c;
@@ -81,6 +94,7 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
 }
 
 __global__ void reduce_partials_kernel(const double *partials, int chunks, int total, double *out) {
+  pdl_enter();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   double t = 0.0;
@@ -133,12 +147,10 @@ static dlb_status column_reduce(dlb_ctx *ctx, Op op, int rows, int n, double *ou
   void *scr = nullptr;
   DLB_TRY(scratch(ctx, column_reduce_partial_bytes(ctx, NSUM, rows, n), &scr));
   double *partials = static_cast<double *>(scr);
-  column_reduce_kernel<NSUM, Op><<<dim3(col_blocks, chunks), CR_LANES_X * CR_LANES_Y, 0,
-                                   ctx->stream>>>(op, rows, n, rows_per_chunk, partials);
+  DLB_LAUNCH_KERNEL(ctx, (column_reduce_kernel<NSUM, Op>), dim3(col_blocks, chunks), CR_LANES_X * CR_LANES_Y, 0, op, rows, n, rows_per_chunk, partials);
   DLB_LAUNCHED(ctx);
   const int total = NSUM * n;
-  reduce_partials_kernel<<<ceil_div(total, 256), 256, 0, ctx->stream>>>(partials, chunks, total,
-                                                                        out);
+  DLB_LAUNCH_KERNEL(ctx, reduce_partials_kernel, ceil_div(total, 256), 256, 0, partials, chunks, total, out);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -151,8 +163,13 @@ struct SumSqOp {
   struct Cols1 {};
   __device__ void load_cols4(int, Cols4 &) const {}
   __device__ void load_cols1(int, Cols1 &) const {}
-  __device__ void row4(int r, int col, const Cols4 &, float (&acc)[2][4]) const {
-    const float4 z = __ldg(reinterpret_cast<const float4 *>(Z + (size_t)r * n + col));
+  static constexpr int IN_FLIGHT = 4;
+  struct Row4 { float4 z; };
+  __device__ void load4(int r, int col, Row4 &x) const {
+    x.z = __ldg(reinterpret_cast<const float4 *>(Z + (size_t)r * n + col));
+  }
+  __device__ void use4(int, int, const Cols4 &, const Row4 &x, float (&acc)[2][4]) const {
+    const float4 z = x.z;
     acc[0][0] += z.x; acc[0][1] += z.y; acc[0][2] += z.z; acc[0][3] += z.w;
     acc[1][0] += z.x * z.x; acc[1][1] += z.y * z.y; acc[1][2] += z.z * z.z; acc[1][3] += z.w * z.w;
   }
@@ -171,8 +188,13 @@ struct SumOp {
   struct Cols1 {};
   __device__ void load_cols4(int, Cols4 &) const {}
   __device__ void load_cols1(int, Cols1 &) const {}
-  __device__ void row4(int r, int col, const Cols4 &, float (&acc)[1][4]) const {
-    const float4 z = __ldg(reinterpret_cast<const float4 *>(X + (size_t)r * n + col));
+  static constexpr int IN_FLIGHT = 4;
+  struct Row4 { float4 z; };
+  __device__ void load4(int r, int col, Row4 &x) const {
+    x.z = __ldg(reinterpret_cast<const float4 *>(X + (size_t)r * n + col));
+  }
+  __device__ void use4(int, int, const Cols4 &, const Row4 &x, float (&acc)[1][4]) const {
+    const float4 z = x.z;
     acc[0][0] += z.x; acc[0][1] += z.y; acc[0][2] += z.z; acc[0][3] += z.w;
   }
   __device__ void row1(int r, int col, const Cols1 &, float (&acc)[1]) const {
@@ -257,11 +279,18 @@ struct ActBackwardOp {
     }
     return e;
   }
-  __device__ void row4(int r, int col, const Cols4 &k, float (&acc)[4][4]) const {
+  static constexpr int IN_FLIGHT = 2;
+  struct Row4 { float4 da, z, a; };
+  __device__ void load4(int r, int col, Row4 &x) const {
     const size_t o = (size_t)r * n + col;
-    float4 da = *reinterpret_cast<const float4 *>(dA + o);
-    const float4 z = __ldg(reinterpret_cast<const float4 *>(Z + o));
-    const float4 a = __ldg(reinterpret_cast<const float4 *>(A + o));
+    x.da = *reinterpret_cast<const float4 *>(dA + o);
+    x.z = __ldg(reinterpret_cast<const float4 *>(Z + o));
+    x.a = __ldg(reinterpret_cast<const float4 *>(A + o));
+  }
+  __device__ void use4(int r, int col, const Cols4 &k, const Row4 &x, float (&acc)[4][4]) const {
+    const size_t o = (size_t)r * n + col;
+    float4 da = x.da;
+    const float4 z = x.z, a = x.a;
     da.x = one(da.x, z.x, a.x, k.k[0], &acc[0][0], &acc[1][0], &acc[2][0], &acc[3][0]);
     da.y = one(da.y, z.y, a.y, k.k[1], &acc[0][1], &acc[1][1], &acc[2][1], &acc[3][1]);
     da.z = one(da.z, z.z, a.z, k.k[2], &acc[0][2], &acc[1][2], &acc[2][2], &acc[3][2]);
@@ -295,6 +324,7 @@ static void rows_plan(dlb_ctx *ctx, int rows, int n, int *chunks, int *rows_per_
 }
 
 __global__ void split_tf32_kernel(const float *__restrict__ x, float *__restrict__ lo, size_t n) {
+  pdl_enter();
   const size_t n4 = n / 4;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
@@ -328,6 +358,7 @@ template <bool NORM, bool VEC4>
 __global__ void activation_forward_kernel(const float *__restrict__ Z, BrnPtrs u, int af,
                                           DropoutDev dp, float *__restrict__ A,
                                           float *__restrict__ A_lo, int rows, int n, unsigned *amax) {
+  pdl_enter();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   unsigned mx = 0;
   if (VEC4) {
@@ -372,6 +403,7 @@ __global__ void activation_forward_kernel(const float *__restrict__ Z, BrnPtrs u
 // One warp per row.  ref: fwp_mp.cpp L:4772-4807 (max, exp(x-max), * 1/sum).
 __global__ void softmax_forward_kernel(const float *__restrict__ Z, float *__restrict__ Q, int rows,
                                        int n) {
+  pdl_enter();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
   if (warp >= rows) return;
   const float *z = Z + (size_t)warp * n;
@@ -395,6 +427,7 @@ __global__ void brn_backward_apply_kernel(float *__restrict__ delta, float *__re
                                           const float *__restrict__ Z, BrnPtrs u,
                                           const double *__restrict__ sums, float inv_rows,
                                           float rows_f, int rows, int n, unsigned *amax) {
+  pdl_enter();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   unsigned mx = 0;
   const double *d_mean = sums + 2 * (size_t)n, *d_sigma = sums + 3 * (size_t)n;
@@ -438,6 +471,7 @@ template <bool VEC4>
 __global__ void activation_backward_plain_kernel(float *__restrict__ dA, const float *__restrict__ Z,
                                                  const float *__restrict__ A, int af,
                                                  size_t total) {
+  pdl_enter();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   if (VEC4) {
     const size_t t4 = total / 4;
@@ -462,20 +496,22 @@ __global__ void activation_backward_plain_kernel(float *__restrict__ dA, const f
 // with stride 8, so the inner loop is one 16-byte load per input tensor and
 // one 16-byte store per output tensor, each warp touching 512 contiguous bytes.
 // ---------------------------------------------------------------------------
-// Rows a thread of activation_forward_rows_kernel has in flight.  Four were
-// measured slower than two (36.7 us against 31.9 us on 4096 x 4096: 76
-// registers leave three blocks per SM instead of four).
-constexpr int AF_ROWS = 2;
+// Rows a thread of activation_forward_rows_kernel has in flight (template
+// parameter AF_ROWS: 4, or 2 with DLB_AF_ROWS=2 for measurements).  Four at 76
+// registers, three blocks per SM, measured slower than two (36.7 us against
+// 31.9 us on 4096 x 4096); held to 64 registers, four blocks per SM, four rows
+// are the faster (a few bytes of spills).
 
 // PLANES: the kernel also writes the fp16 planes of A (with the scale predicted
 // from the buffer's previous split) and the row / column maxima of the range
 // guard; otherwise it leaves max |A| in the sink's slot for the split pass that
 // follows.
-template <bool PLANES>
-__global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
+template <bool PLANES, int AF_ROWS>
+__global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y, 4)
     activation_forward_rows_kernel(const float *__restrict__ Z, BrnPtrs u, int af, DropoutDev dp,
                                    float *__restrict__ A, float *__restrict__ A_lo, int rows, int n,
                                    int rows_per_chunk, PlaneSink sink) {
+  pdl_enter();
   __shared__ unsigned line_shared[PLANES ? CR_LANES_Y * CR_COLS : 1];
   const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
   const int col = blockIdx.x * CR_COLS + tx * 4;
@@ -535,7 +571,6 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
   }
   if (PLANES) {
     track.finish(sink, line_shared, tx, ty, CR_LANES_Y, blockIdx.x * CR_COLS, n, live_col);
-    sink_complete(sink);
   } else if (sink.slot) {
     amax_commit(reinterpret_cast<unsigned *>(sink.slot) + SLOT_AMAX, track.all);
   }
@@ -547,6 +582,7 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
                                    const float *__restrict__ Z, BrnPtrs u,
                                    const double *__restrict__ sums, float inv_rows, float rows_f,
                                    int rows, int n, int rows_per_chunk, PlaneSink sink) {
+  pdl_enter();
   __shared__ unsigned line_shared[PLANES ? CR_LANES_Y * CR_COLS : 1];
   const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
   const int col = blockIdx.x * CR_COLS + tx * 4;
@@ -569,36 +605,50 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
       d_sigma[j] = (float)sums[3 * (size_t)n + col + j];
       d_mean_n[j] = (float)sums[2 * (size_t)n + col + j] * inv_rows;
     }
-    for (int r = r0 + ty; r < r1; r += CR_LANES_Y) {
-      const size_t o = (size_t)r * n + col;
-      const float4 e4 = *reinterpret_cast<const float4 *>(delta + o);
-      const float4 z4 = __ldg(reinterpret_cast<const float4 *>(Z + o));
-      const float e[4] = {e4.x, e4.y, e4.z, e4.w}, z[4] = {z4.x, z4.y, z4.z, z4.w};
-      float t[4];
+    // APPLY_ROWS rows per iteration, the loads of all of them first.
+    constexpr int APPLY_ROWS = 2;
+    for (int r = r0 + ty; r < r1; r += APPLY_ROWS * CR_LANES_Y) {
+      float4 e4[APPLY_ROWS], z4[APPLY_ROWS];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float v = e[j] * gamma[j];
-        v *= r_over_sigma[j];
-        v += d_sigma[j] * ((z[j] - mean[j]) / n_sigma[j]);
-        v += d_mean_n[j];
-        t[j] = v;
+      for (int k = 0; k < APPLY_ROWS; ++k) {
+        const int rk = r + k * CR_LANES_Y;
+        if (rk < r1) {
+          const size_t o = (size_t)rk * n + col;
+          e4[k] = *reinterpret_cast<const float4 *>(delta + o);
+          z4[k] = __ldg(reinterpret_cast<const float4 *>(Z + o));
+        }
       }
-      *reinterpret_cast<float4 *>(delta + o) = make_float4(t[0], t[1], t[2], t[3]);
-      if (PLANES) {
-        sink_store4(sink, o, t, plane_scale);
-        track.row(sink, r, t);
-      } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) track.all = max(track.all, abs_bits(t[j]));
-        if (delta_lo)
-          *reinterpret_cast<float4 *>(delta_lo + o) =
-              make_float4(tf32_lo(t[0]), tf32_lo(t[1]), tf32_lo(t[2]), tf32_lo(t[3]));
+      for (int k = 0; k < APPLY_ROWS; ++k) {
+        const int rk = r + k * CR_LANES_Y;
+        if (rk >= r1) break;
+        const size_t o = (size_t)rk * n + col;
+        const float e[4] = {e4[k].x, e4[k].y, e4[k].z, e4[k].w}, z[4] = {z4[k].x, z4[k].y, z4[k].z, z4[k].w};
+        float t[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float v = e[j] * gamma[j];
+          v *= r_over_sigma[j];
+          v += d_sigma[j] * ((z[j] - mean[j]) / n_sigma[j]);
+          v += d_mean_n[j];
+          t[j] = v;
+        }
+        *reinterpret_cast<float4 *>(delta + o) = make_float4(t[0], t[1], t[2], t[3]);
+        if (PLANES) {
+          sink_store4(sink, o, t, plane_scale);
+          track.row(sink, rk, t);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) track.all = max(track.all, abs_bits(t[j]));
+          if (delta_lo)
+            *reinterpret_cast<float4 *>(delta_lo + o) =
+                make_float4(tf32_lo(t[0]), tf32_lo(t[1]), tf32_lo(t[2]), tf32_lo(t[3]));
+        }
       }
     }
   }
   if (PLANES) {
     track.finish(sink, line_shared, tx, ty, CR_LANES_Y, blockIdx.x * CR_COLS, n, live_col);
-    sink_complete(sink);
   } else if (sink.slot) {
     amax_commit(reinterpret_cast<unsigned *>(sink.slot) + SLOT_AMAX, track.all);
   }
@@ -607,6 +657,7 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
 __global__ void brn_finalize_kernel(const double *__restrict__ sums, int n, float batch_scale,
                                     float momentum, float eps, float r_max, float d_max,
                                     dlb_brn_unit_arrays u) {
+  pdl_enter();
   const int h = blockIdx.x * blockDim.x + threadIdx.x;
   if (h >= n) return;
   // fwp_mp.cpp L:4688-4717, in the reference's order: the running averages
@@ -627,6 +678,7 @@ __global__ void brn_finalize_kernel(const double *__restrict__ sums, int n, floa
 
 __global__ void sums_to_grads_kernel(const double *__restrict__ sums, int n, float *d_gamma,
                                      float *d_beta, int accumulate) {
+  pdl_enter();
   const int h = blockIdx.x * blockDim.x + threadIdx.x;
   if (h >= n) return;
   const float g = (float)sums[h], b = (float)sums[n + h];
@@ -641,6 +693,7 @@ __global__ void sums_to_grads_kernel(const double *__restrict__ sums, int n, flo
 
 __global__ void sums_to_bias_grad_kernel(const double *__restrict__ sums, int n, float *dbias,
                                          int accumulate) {
+  pdl_enter();
   const int h = blockIdx.x * blockDim.x + threadIdx.x;
   if (h >= n) return;
   if (accumulate) dbias[h] += (float)sums[h];
@@ -652,6 +705,7 @@ __global__ void loss_delta_mse_kernel(const float *__restrict__ pre, const float
                                       const float *__restrict__ y, float *__restrict__ delta,
                                       float *__restrict__ delta_lo, int af, size_t total,
                                       float denom, double *loss_sum, unsigned *amax) {
+  pdl_enter();
   __shared__ double red[8];
   double local = 0.0;
   unsigned mx = 0;
@@ -683,6 +737,7 @@ __global__ void loss_delta_softmax_ce_kernel(const float *__restrict__ q, const 
                                              float *__restrict__ delta, float *__restrict__ delta_lo,
                                              int rows, int n, float rows_global, double *loss_sum,
                                              unsigned *amax) {
+  pdl_enter();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
   double local = 0.0;
   unsigned mx = 0;
@@ -724,7 +779,7 @@ dlb_status dlb_split_tf32(dlb_ctx *ctx, const float *x, float *x_lo, size_t n) {
   DLB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                   (reinterpret_cast<uintptr_t>(x_lo) & 15) == 0,
               "dlb_split_tf32: pointers must be 16-byte aligned");
-  split_tf32_kernel<<<stream_grid(ctx, n / 4 + 1, 256), 256, 0, ctx->stream>>>(x, x_lo, n);
+  DLB_LAUNCH_KERNEL(ctx, split_tf32_kernel, stream_grid(ctx, n / 4 + 1, 256), 256, 0, x, x_lo, n);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -743,8 +798,7 @@ dlb_status dlb_brn_forward_finalize(dlb_ctx *ctx, const double *sums, int global
   DLB_REQUIRE(ctx && sums && u && global_rows > 0 && n_units > 0, "dlb_brn_forward_finalize");
   DLB_REQUIRE(u->mean && u->sigma && u->mean_average && u->sigma_average && u->r && u->d,
               "dlb_brn_forward_finalize: null unit array");
-  brn_finalize_kernel<<<ceil_div(n_units, 256), 256, 0, ctx->stream>>>(
-      sums, n_units, 1.f / (float)global_rows, momentum, epsilon, r_max, d_max, *u);
+  DLB_LAUNCH_KERNEL(ctx, brn_finalize_kernel, ceil_div(n_units, 256), 256, 0, sums, n_units, 1.f / (float)global_rows, momentum, epsilon, r_max, d_max, *u);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -790,12 +844,15 @@ dlb_status activation_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_u
     int chunks, rpc;
     rows_plan(ctx, rows, n_units, &chunks, &rpc);
     const dim3 grid(ceil_div(n_units, CR_COLS), chunks);
-    if (sink.hi)
-      activation_forward_rows_kernel<true><<<grid, CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
-          Z, p, af, dp, A, A_lo, rows, n_units, rpc, sink);
-    else
-      activation_forward_rows_kernel<false><<<grid, CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
-          Z, p, af, dp, A, A_lo, rows, n_units, rpc, sink);
+    static const int in_flight = [] {
+      const char *e = getenv("DLB_AF_ROWS");
+      return e && atoi(e) == 2 ? 2 : 4;
+    }();
+#define DLB_AF_LAUNCH(PL, R)                                                                        \
+  DLB_LAUNCH_KERNEL(ctx, (activation_forward_rows_kernel<PL, R>), grid, CR_LANES_X * CR_LANES_Y, 0, Z, p, af, dp, A, A_lo, rows, n_units, rpc, sink)
+    if (sink.hi) { if (in_flight == 4) DLB_AF_LAUNCH(true, 4); else DLB_AF_LAUNCH(true, 2); }
+    else         { if (in_flight == 4) DLB_AF_LAUNCH(false, 4); else DLB_AF_LAUNCH(false, 2); }
+#undef DLB_AF_LAUNCH
     DLB_LAUNCHED(ctx);
     return DLB_OK;
   }
@@ -803,8 +860,7 @@ dlb_status activation_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_u
   const size_t items = vec4 ? (size_t)rows * (n_units / 4) : (size_t)rows * n_units;
   const int grid = stream_grid(ctx, items, 256);
 #define LAUNCH(NORM, V)                                                                 \
-  activation_forward_kernel<NORM, V><<<grid, 256, 0, ctx->stream>>>(Z, p, af, dp, A, A_lo, rows, \
-                                                                    n_units, amax)
+  DLB_LAUNCH_KERNEL(ctx, (activation_forward_kernel<NORM, V>), grid, 256, 0, Z, p, af, dp, A, A_lo, rows, n_units, amax)
   if (u) { if (vec4) LAUNCH(true, true); else LAUNCH(true, false); }
   else   { if (vec4) LAUNCH(false, true); else LAUNCH(false, false); }
 #undef LAUNCH
@@ -814,7 +870,7 @@ dlb_status activation_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_u
 
 dlb_status dlb_softmax_forward(dlb_ctx *ctx, const float *Z, float *Q, int rows, int n_units) {
   DLB_REQUIRE(ctx && Z && Q && rows > 0 && n_units > 0, "dlb_softmax_forward");
-  softmax_forward_kernel<<<ceil_div(rows, 8), 256, 0, ctx->stream>>>(Z, Q, rows, n_units);
+  DLB_LAUNCH_KERNEL(ctx, softmax_forward_kernel, ceil_div(rows, 8), 256, 0, Z, Q, rows, n_units);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -837,9 +893,9 @@ dlb_status dlb_activation_backward(dlb_ctx *ctx, float *dA, const float *Z, cons
                     ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
   const int grid = stream_grid(ctx, vec4 ? total / 4 : total, 256);
   if (vec4)
-    activation_backward_plain_kernel<true><<<grid, 256, 0, ctx->stream>>>(dA, Z, A, af, total);
+    DLB_LAUNCH_KERNEL(ctx, activation_backward_plain_kernel<true>, grid, 256, 0, dA, Z, A, af, total);
   else
-    activation_backward_plain_kernel<false><<<grid, 256, 0, ctx->stream>>>(dA, Z, A, af, total);
+    DLB_LAUNCH_KERNEL(ctx, activation_backward_plain_kernel<false>, grid, 256, 0, dA, Z, A, af, total);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -861,15 +917,12 @@ dlb_status brn_backward_apply_impl(dlb_ctx *ctx, float *delta, float *delta_lo, 
     rows_plan(ctx, rows, n_units, &chunks, &rpc);
     const dim3 rgrid(ceil_div(n_units, CR_COLS), chunks);
     if (sink.hi)
-      brn_backward_apply_rows_kernel<true><<<rgrid, CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
-          delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc, sink);
+      DLB_LAUNCH_KERNEL(ctx, brn_backward_apply_rows_kernel<true>, rgrid, CR_LANES_X * CR_LANES_Y, 0, delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc, sink);
     else
-      brn_backward_apply_rows_kernel<false><<<rgrid, CR_LANES_X * CR_LANES_Y, 0, ctx->stream>>>(
-          delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc, sink);
+      DLB_LAUNCH_KERNEL(ctx, brn_backward_apply_rows_kernel<false>, rgrid, CR_LANES_X * CR_LANES_Y, 0, delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc, sink);
   } else {
     DLB_REQUIRE(!sink.hi, "dlb_brn_backward_apply: planes from a kernel that cannot write them");
-    brn_backward_apply_kernel<false><<<grid, 256, 0, ctx->stream>>>(
-        delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, amax);
+    DLB_LAUNCH_KERNEL(ctx, brn_backward_apply_kernel<false>, grid, 256, 0, delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, amax);
   }
   DLB_LAUNCHED(ctx);
   return DLB_OK;
@@ -878,8 +931,7 @@ dlb_status brn_backward_apply_impl(dlb_ctx *ctx, float *delta, float *delta_lo, 
 dlb_status dlb_brn_backward_param_grads(dlb_ctx *ctx, const double *sums, int n_units,
                                         float *d_gamma, float *d_beta, int accumulate) {
   DLB_REQUIRE(ctx && sums && d_gamma && d_beta && n_units > 0, "dlb_brn_backward_param_grads");
-  sums_to_grads_kernel<<<ceil_div(n_units, 256), 256, 0, ctx->stream>>>(sums, n_units, d_gamma,
-                                                                        d_beta, accumulate);
+  DLB_LAUNCH_KERNEL(ctx, sums_to_grads_kernel, ceil_div(n_units, 256), 256, 0, sums, n_units, d_gamma, d_beta, accumulate);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -894,14 +946,12 @@ dlb_status loss_delta_impl(dlb_ctx *ctx, int loss, int af, const float *pre, con
     const size_t total = (size_t)rows * n_out;
     // loss_fn_derivative divides by static_cast<real>(bs * n_out).
     const float denom = (float)((size_t)global_rows * (size_t)n_out);
-    loss_delta_mse_kernel<<<stream_grid(ctx, total, 256), 256, 0, ctx->stream>>>(
-        pre, q, y, delta, delta_lo, af, total, denom, loss_sum, amax);
+    DLB_LAUNCH_KERNEL(ctx, loss_delta_mse_kernel, stream_grid(ctx, total, 256), 256, 0, pre, q, y, delta, delta_lo, af, total, denom, loss_sum, amax);
     DLB_LAUNCHED(ctx);
     return DLB_OK;
   }
   if (loss == DLB_LOSS_CROSS_ENTROPY && af == DLB_AF_SOFTMAX) {
-    loss_delta_softmax_ce_kernel<<<ceil_div(rows, 8), 256, 0, ctx->stream>>>(
-        q, y, delta, delta_lo, rows, n_out, (float)global_rows, loss_sum, amax);
+    DLB_LAUNCH_KERNEL(ctx, loss_delta_softmax_ce_kernel, ceil_div(rows, 8), 256, 0, q, y, delta, delta_lo, rows, n_out, (float)global_rows, loss_sum, amax);
     DLB_LAUNCHED(ctx);
     return DLB_OK;
   }
@@ -920,7 +970,7 @@ dlb_status bias_gradient(dlb_ctx *ctx, const float *delta, int rows, int n, floa
   DLB_TRY(scratch(ctx, partial_bytes + (size_t)n * sizeof(double), &scr));
   double *out = reinterpret_cast<double *>(static_cast<char *>(scr) + partial_bytes);
   DLB_TRY(column_reduce<1>(ctx, SumOp{delta, n}, rows, n, out));
-  sums_to_bias_grad_kernel<<<ceil_div(n, 256), 256, 0, ctx->stream>>>(out, n, dbias, accumulate);
+  DLB_LAUNCH_KERNEL(ctx, sums_to_bias_grad_kernel, ceil_div(n, 256), 256, 0, out, n, dbias, accumulate);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -938,6 +988,7 @@ __global__ void residual_forward_kernel(const float *__restrict__ x, float *__re
                                         const float *__restrict__ noise, float *__restrict__ out,
                                         float *__restrict__ out_lo, int rows, int width, int vec,
                                         unsigned *amax) {
+  pdl_enter();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   unsigned mx = 0;
   if (vec) {
@@ -985,6 +1036,7 @@ __global__ void shakedrop_backward_kernel(const float *__restrict__ d, int ld_d,
                                           const float *__restrict__ noise, float *__restrict__ delta,
                                           float *__restrict__ delta_lo, int rows, int width,
                                           unsigned *amax) {
+  pdl_enter();
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t total = (size_t)rows * width;
   unsigned mx = 0;
@@ -1007,6 +1059,7 @@ __global__ void residual_forward_padded_kernel(const float *__restrict__ x, int 
                                                int wb, int pad, const uint8_t *__restrict__ row_mask,
                                                const float *__restrict__ noise, float *__restrict__ out,
                                                float *__restrict__ out_lo, int rows, unsigned *amax) {
+  pdl_enter();
   const int W = max(wx, wb);
   const int off_x = wx < W ? pad : 0, off_b = wb < W ? pad : 0;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -1046,8 +1099,7 @@ static dlb_status residual_forward_impl(dlb_ctx *ctx, const float *x, float *blo
                        reinterpret_cast<uintptr_t>(noise);
   const int vec = (width % 4 == 0) && (al & 15) == 0;
   const size_t items = vec ? (size_t)rows * (width / 4) : (size_t)rows * width;
-  residual_forward_kernel<<<stream_grid(ctx, items, 256), 256, 0, ctx->stream>>>(
-      x, block, row_mask, noise, out, out_lo, rows, width, vec, amax);
+  DLB_LAUNCH_KERNEL(ctx, residual_forward_kernel, stream_grid(ctx, items, 256), 256, 0, x, block, row_mask, noise, out, out_lo, rows, width, vec, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -1059,8 +1111,7 @@ static dlb_status residual_forward_padded_impl(dlb_ctx *ctx, const float *x, int
   DLB_REQUIRE(!row_mask || noise, "dlb_residual_forward_padded: row flags need the noise draws");
   const int W = wx > wb ? wx : wb;
   const int pad = ((wx > wb ? wx - wb : wb - wx) + 1) / 2;  // v1/learner/compile.cpp L:344-352
-  residual_forward_padded_kernel<<<stream_grid(ctx, (size_t)rows * W, 256), 256, 0, ctx->stream>>>(
-      x, wx, block, wb, pad, row_mask, noise, out, out_lo, rows, amax);
+  DLB_LAUNCH_KERNEL(ctx, residual_forward_padded_kernel, stream_grid(ctx, (size_t)rows * W, 256), 256, 0, x, wx, block, wb, pad, row_mask, noise, out, out_lo, rows, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -1071,8 +1122,7 @@ static dlb_status shakedrop_backward_impl(dlb_ctx *ctx, const float *d, int ld_d
   DLB_REQUIRE(ctx && d && delta && rows > 0 && width > 0 && first >= 0 && first + width <= ld_d,
               "dlb_shakedrop_backward");
   DLB_REQUIRE(!row_mask || noise, "dlb_shakedrop_backward: row flags need the noise draws");
-  shakedrop_backward_kernel<<<stream_grid(ctx, (size_t)rows * width, 256), 256, 0, ctx->stream>>>(
-      d, ld_d, first, row_mask, noise, delta, delta_lo, rows, width, amax);
+  DLB_LAUNCH_KERNEL(ctx, shakedrop_backward_kernel, stream_grid(ctx, (size_t)rows * width, 256), 256, 0, d, ld_d, first, row_mask, noise, delta, delta_lo, rows, width, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -1269,6 +1319,7 @@ namespace dlb {
 __global__ void loss_eval_kernel(int loss, int accu_fn, float accu_var, const float *__restrict__ q,
                                  const float *__restrict__ y, int rows, int n, double *loss_sum,
                                  double *accu_sum) {
+  pdl_enter();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
   double local = 0.0, hits = 0.0;
   if (warp < rows) {
@@ -1325,8 +1376,7 @@ extern "C" dlb_status dlb_loss_eval(dlb_ctx *ctx, int loss, int accu_fn, float a
     set_error("dlb_loss_eval: loss %d / accuracy function %d outside the supported set", loss, accu_fn);
     return DLB_ERR_UNSUPPORTED;
   }
-  loss_eval_kernel<<<ceil_div(rows, 8), 256, 0, ctx->stream>>>(loss, accu_fn, accu_var, q, y, rows, n_out,
-                                                               loss_sum, accu_sum);
+  DLB_LAUNCH_KERNEL(ctx, loss_eval_kernel, ceil_div(rows, 8), 256, 0, loss, accu_fn, accu_var, q, y, rows, n_out, loss_sum, accu_sum);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }

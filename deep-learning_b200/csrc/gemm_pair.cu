@@ -133,6 +133,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
                         int parts, int total_items, const float *__restrict__ scale_a,
                         const float *__restrict__ scale_b, int *status, const unsigned *guard_a,
                         const unsigned *guard_b, SimtOperands fp32, unsigned long long *fallbacks) {
+  pdl_enter();
   using P = PairPlan<STAGES>;
   // Range guard: the planes of a flagged operand do not stand for its tensor.
   // The product is then formed from the fp32 tensors on the CUDA cores, every
@@ -436,11 +437,7 @@ dlb_status launch_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B,
                                (size_t)N * sizeof(float), (size_t)(M - first_row), ctx->stream));
   }
   const int items = whole_tiles + parts * split_tiles;
-  kernel<<<2 * min(items, lanes), NUM_THREADS, P::TOTAL, ctx->stream>>>(
-      ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, parts, items, A.scale,
-      B.scale, ctx->d_status, A.guard, B.guard,
-      SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k},
-      ctx->d_guard ? ctx->d_guard + 1 : nullptr);
+  DLB_LAUNCH_KERNEL(ctx, kernel, 2 * min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, parts, items, A.scale, B.scale, ctx->d_status, A.guard, B.guard, SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }

@@ -10,6 +10,7 @@ namespace dlb {
 __global__ void __launch_bounds__(256)
     gemm_simt_kernel(SimtOperands o, float *__restrict__ C, long long ldc, int M, int N, int K,
                      const float *__restrict__ bias, int accumulate) {
+  pdl_enter();
   __shared__ float shared[SIMT_SMEM_FLOATS];
   gemm_simt_body(o, C, ldc, M, N, K, bias, accumulate, shared, blockIdx.x, gridDim.x);
 }
@@ -17,9 +18,7 @@ __global__ void __launch_bounds__(256)
 dlb_status gemm_simt(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
                      long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
   const int grid = ceil_div(N, ST_N) * ceil_div(M, ST_M);
-  gemm_simt_kernel<<<grid, 256, 0, ctx->stream>>>(
-      SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k}, C, ldc, M, N, K, ep.bias,
-      ep.accumulate);
+  DLB_LAUNCH_KERNEL(ctx, gemm_simt_kernel, grid, 256, 0, SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k}, C, ldc, M, N, K, ep.bias, ep.accumulate);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }

@@ -913,6 +913,17 @@ dlb_status dlb_model_set_weight_decay(dlb_model *m, float value) {
   return DLB_OK;
 }
 
+// ref: Model::set_l2 (v1/ops/regularizers/l2.cpp L:31-66).  The value is kept (it
+// is part of the hyperparameter file) and, as in the reference, never reaches the
+// gradient: update_weights_mp calls the L2 routine with (batch_size, 0,
+// total_weights) where it takes (start, end, batch_size) (v1/learner/model.cpp
+// L:4717-4719, l2.cpp L:92-104), so its loop covers no element.
+dlb_status dlb_model_set_l2(dlb_model *m, float value) {
+  DLB_REQUIRE(m && value >= 0.f && value <= 1.f, "set_l2: value in [0, 1]");
+  m->hp.regularization_l2 = value;
+  return DLB_OK;
+}
+
 dlb_status dlb_model_set_max_batch_size(dlb_model *m, size_t rows) {
   DLB_REQUIRE(m && rows > 0, "set_max_batch_size");
   m->max_batch = rows;

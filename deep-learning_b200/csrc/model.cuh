@@ -58,6 +58,7 @@ struct HParams {
   // Gradient descent (model.hpp L:3020-3022, L:2839).
   float learning_rate = 0.01f, learning_momentum = 0.9f;
   bool use_nesterov = false;
+  float regularization_l2 = 0.f;  // kept and saved; without effect on the step, as in the reference
   // Model defaults, v1/learner/model.hpp L:3045-3048.
   float normalization_momentum_average = 0.999f, normalization_epsilon = 1e-5f,
         brn_r_max = 1.f, brn_d_max = 0.f;

@@ -68,12 +68,14 @@ __device__ __forceinline__ void for_each_word(const NoiseKey &k, size_t n, Emit 
 }
 
 __global__ void __launch_bounds__(256) uniform_kernel(float *__restrict__ out, size_t n, float lo, float width, NoiseKey k) {
+  pdl_enter();
   // Two roundings (no fused multiply-add), so that a host restatement in fp32
   // gives the same bits.
   for_each_word(k, n, [=](size_t i, uint32_t x) { out[i] = __fadd_rn(__fmul_rn(unit_float(x), width), lo); });
 }
 
 __global__ void __launch_bounds__(256) bernoulli_kernel(uint8_t *__restrict__ out, size_t n, float p, NoiseKey k) {
+  pdl_enter();
   for_each_word(k, n, [=](size_t i, uint32_t x) { out[i] = unit_float(x) < p ? 1 : 0; });
 }
 
@@ -102,7 +104,7 @@ dlb_status dlb_noise_uniform(dlb_ctx *ctx, float *out, size_t n, float lo, float
                              uint32_t stream, uint32_t step, uint64_t first) {
   DLB_REQUIRE(ctx && (out || n == 0) && hi >= lo, "dlb_noise_uniform");
   if (n == 0) return DLB_OK;
-  uniform_kernel<<<noise_blocks(ctx, n), 256, 0, ctx->stream>>>(out, n, lo, hi - lo, make_key(seed, stream, step, first));
+  DLB_LAUNCH_KERNEL(ctx, uniform_kernel, noise_blocks(ctx, n), 256, 0, out, n, lo, hi - lo, make_key(seed, stream, step, first));
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -111,7 +113,7 @@ dlb_status dlb_noise_bernoulli(dlb_ctx *ctx, uint8_t *out, size_t n, float p, ui
                                uint32_t step, uint64_t first) {
   DLB_REQUIRE(ctx && (out || n == 0) && p >= 0.f && p <= 1.f, "dlb_noise_bernoulli");
   if (n == 0) return DLB_OK;
-  bernoulli_kernel<<<noise_blocks(ctx, n), 256, 0, ctx->stream>>>(out, n, p, make_key(seed, stream, step, first));
+  DLB_LAUNCH_KERNEL(ctx, bernoulli_kernel, noise_blocks(ctx, n), 256, 0, out, n, p, make_key(seed, stream, step, first));
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }

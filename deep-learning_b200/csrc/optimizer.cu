@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(256)
     optimizer_kernel(dlb_optimizer_scalars k, float *__restrict__ p, float *__restrict__ g,
                      float *__restrict__ m, float *__restrict__ v, float *__restrict__ vh,
                      const float *__restrict__ mask, size_t n, unsigned *amax) {
+  pdl_enter();
   unsigned mx = 0;  // largest |p| written, for the fp16 split of a weight matrix
   constexpr bool HAT = (RULE == R_AMSGRAD || RULE == R_AMSBOUND);
   constexpr bool FIRST = RULE != R_GD;                                              // m is read and written
@@ -125,6 +126,7 @@ __global__ void __launch_bounds__(32 * OPT_LANES_Y)
     optimizer_rows_kernel(dlb_optimizer_scalars k, float *__restrict__ p, float *__restrict__ g,
                           float *__restrict__ m, float *__restrict__ v, float *__restrict__ vh,
                           const float *__restrict__ mask, int rows, int cols, int rows_per_chunk, PlaneSink sink) {
+  pdl_enter();
   __shared__ unsigned line_shared[OPT_LANES_Y * 128];
   constexpr bool HAT = (RULE == R_AMSGRAD || RULE == R_AMSBOUND);
   constexpr bool FIRST = RULE != R_GD;
@@ -162,7 +164,6 @@ __global__ void __launch_bounds__(32 * OPT_LANES_Y)
     }
   }
   track.finish(sink, line_shared, tx, ty, OPT_LANES_Y, blockIdx.x * 128, cols, live);
-  sink_complete(sink);
 }
 
 // Calls f(std::integral_constant<int, R>) with the kernel rule of an optimizer
@@ -198,11 +199,9 @@ static dlb_status launch_rule_rows(dlb_ctx *ctx, const dlb_optimizer_scalars &k,
   chunks = ceil_div(rows, rpc);
   const dim3 grid(col_blocks, chunks);
   if (k.weight_decay != 0.f)
-    optimizer_rows_kernel<RULE, true><<<grid, 32 * OPT_LANES_Y, 0, ctx->stream>>>(k, p, g, m, v, vh, mask, rows, cols,
-                                                                                  rpc, sink);
+    DLB_LAUNCH_KERNEL(ctx, (optimizer_rows_kernel<RULE, true>), grid, 32 * OPT_LANES_Y, 0, k, p, g, m, v, vh, mask, rows, cols, rpc, sink);
   else
-    optimizer_rows_kernel<RULE, false><<<grid, 32 * OPT_LANES_Y, 0, ctx->stream>>>(k, p, g, m, v, vh, mask, rows,
-                                                                                   cols, rpc, sink);
+    DLB_LAUNCH_KERNEL(ctx, (optimizer_rows_kernel<RULE, false>), grid, 32 * OPT_LANES_Y, 0, k, p, g, m, v, vh, mask, rows, cols, rpc, sink);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -216,9 +215,9 @@ static dlb_status launch_rule(dlb_ctx *ctx, const dlb_optimizer_scalars &k, floa
   const size_t blocks_needed = (n / 4 + 255) / 256 + 1;
   const int grid = (int)min(blocks_needed, (size_t)ctx->sm_count * 8);
   if (k.weight_decay != 0.f)
-    optimizer_kernel<RULE, true><<<grid, 256, 0, ctx->stream>>>(k, p, g, m, v, vh, mask, n, amax);
+    DLB_LAUNCH_KERNEL(ctx, (optimizer_kernel<RULE, true>), grid, 256, 0, k, p, g, m, v, vh, mask, n, amax);
   else
-    optimizer_kernel<RULE, false><<<grid, 256, 0, ctx->stream>>>(k, p, g, m, v, vh, mask, n, amax);
+    DLB_LAUNCH_KERNEL(ctx, (optimizer_kernel<RULE, false>), grid, 256, 0, k, p, g, m, v, vh, mask, n, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -233,6 +232,7 @@ static dlb_status launch_rule(dlb_ctx *ctx, const dlb_optimizer_scalars &k, floa
 constexpr int CLIP_BLOCKS = 1024;
 
 __global__ void __launch_bounds__(256) sumsq_partials_kernel(const float *__restrict__ g, size_t n, double *partials) {
+  pdl_enter();
   double acc = 0.0;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t n4 = (reinterpret_cast<uintptr_t>(g) & 15) == 0 ? n / 4 : 0;
@@ -253,6 +253,7 @@ __global__ void __launch_bounds__(256) sumsq_partials_kernel(const float *__rest
 }
 
 __global__ void __launch_bounds__(256) clip_factor_kernel(const double *partials, int blocks, float max_norm, float *factor) {
+  pdl_enter();
   __shared__ double part[256];
   double s = 0.0;
   for (int i = threadIdx.x; i < blocks; i += 256) s += partials[i];
@@ -269,6 +270,7 @@ __global__ void __launch_bounds__(256) clip_factor_kernel(const double *partials
 }
 
 __global__ void __launch_bounds__(256) scale_by_factor_kernel(float *__restrict__ g, size_t n, const float *factor) {
+  pdl_enter();
   const float f = *factor;
   if (f == 1.f) return;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -341,11 +343,11 @@ dlb_status dlb_clip_gradient(dlb_ctx *ctx, float *g, size_t n, float max_norm) {
   double *partials = static_cast<double *>(scr);
   float *factor = reinterpret_cast<float *>(partials + CLIP_BLOCKS);
   const int blocks = (int)min((size_t)CLIP_BLOCKS, (n / 4 + 255) / 256 + 1);
-  sumsq_partials_kernel<<<blocks, 256, 0, ctx->stream>>>(g, n, partials);
+  DLB_LAUNCH_KERNEL(ctx, sumsq_partials_kernel, blocks, 256, 0, g, n, partials);
   DLB_LAUNCHED(ctx);
-  clip_factor_kernel<<<1, 256, 0, ctx->stream>>>(partials, blocks, max_norm, factor);
+  DLB_LAUNCH_KERNEL(ctx, clip_factor_kernel, 1, 256, 0, partials, blocks, max_norm, factor);
   DLB_LAUNCHED(ctx);
-  scale_by_factor_kernel<<<blocks, 256, 0, ctx->stream>>>(g, n, factor);
+  DLB_LAUNCH_KERNEL(ctx, scale_by_factor_kernel, blocks, 256, 0, g, n, factor);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }

@@ -19,6 +19,7 @@ namespace {
 
 // Largest |x| as raw bits (monotonic for non-negative floats).
 __global__ void absmax_kernel(const float *__restrict__ x, size_t n, unsigned *slot) {
+  pdl_enter();
   unsigned m = 0;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t n4 = n / 4;
@@ -42,6 +43,7 @@ __global__ void absmax_kernel(const float *__restrict__ x, size_t n, unsigned *s
 // Flat split of a tensor without a shape (or one whose rows are not a whole
 // number of float4): planes only, no line statistics.
 __global__ void split_flat_kernel(const float *__restrict__ x, size_t n, PlaneSink k) {
+  pdl_enter();
   const float s = sink_scale(k);
   __half *hi = reinterpret_cast<__half *>(k.hi), *lo = reinterpret_cast<__half *>(k.lo);
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -55,7 +57,6 @@ __global__ void split_flat_kernel(const float *__restrict__ x, size_t n, PlaneSi
   }
   for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
     plane_halves(x[i], s, hi + i, lo + i);
-  sink_complete(k);
 }
 
 // Split of a [rows, cols] tensor (cols a multiple of 4) with the row and column
@@ -64,6 +65,7 @@ __global__ void split_flat_kernel(const float *__restrict__ x, size_t n, PlaneSi
 constexpr int SPLIT_LANES_Y = 8;
 __global__ void __launch_bounds__(32 * SPLIT_LANES_Y)
     split_rows_kernel(const float *__restrict__ x, int rows, int cols, int rows_per_chunk, PlaneSink k) {
+  pdl_enter();
   __shared__ unsigned shared[SPLIT_LANES_Y * 128];
   const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
   const int col = blockIdx.x * 128 + tx * 4;
@@ -91,8 +93,10 @@ __global__ void __launch_bounds__(32 * SPLIT_LANES_Y)
   // Under a predicted scale the tensor's maximum is found here as well; where it
   // was known before (it gave s) the atomic maximum changes nothing.
   track.finish(k, shared, tx, ty, SPLIT_LANES_Y, blockIdx.x * 128, cols, live);
-  sink_complete(k);
 }
+
+__global__ void __launch_bounds__(1024) planes_finalize_kernel(PlaneSink k) {
+  pdl_enter(); sink_finalize(k); }
 
 int stream_blocks(dlb_ctx *ctx, size_t items) {
   const size_t blocks = (items + 255) / 256;
@@ -141,12 +145,12 @@ dlb_status launch_split(dlb_ctx *ctx, const float *x, size_t n, int rows, int co
     int chunks = max(1, min(ceil_div(ctx->sm_count * 8, col_blocks), ceil_div(rows, 2 * SPLIT_LANES_Y)));
     const int rpc = ceil_div(ceil_div(rows, chunks), 2 * SPLIT_LANES_Y) * 2 * SPLIT_LANES_Y;
     chunks = ceil_div(rows, rpc);
-    split_rows_kernel<<<dim3(col_blocks, chunks), 32 * SPLIT_LANES_Y, 0, ctx->stream>>>(x, rows, cols, rpc, k);
+    DLB_LAUNCH_KERNEL(ctx, split_rows_kernel, dim3(col_blocks, chunks), 32 * SPLIT_LANES_Y, 0, x, rows, cols, rpc, k);
   } else {
     PlaneSink flat = k;
     flat.rowmax = flat.colmax = nullptr;
     flat.n_lines = 0;
-    split_flat_kernel<<<stream_blocks(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(x, n, flat);
+    DLB_LAUNCH_KERNEL(ctx, split_flat_kernel, stream_blocks(ctx, n / 4 + 1), 256, 0, x, n, flat);
   }
   DLB_LAUNCHED(ctx);
   return DLB_OK;
@@ -255,12 +259,19 @@ dlb_status planes_close(dlb_ctx *ctx, const PlaneJob &job) {
     k.guard = ctx->d_guard;
     DLB_TRY(launch_split(ctx, job.x, job.n, e.rows, e.cols, k));
   }
+  PlaneSink k = job.sink;
+  k.rowmax = e.lines;
+  k.colmax = e.lines ? e.lines + e.rows : nullptr;
+  k.n_lines = e.lines ? e.rows + e.cols : 0;
+  k.predicted = job.fused ? 1 : 0;
+  DLB_LAUNCH_KERNEL(ctx, planes_finalize_kernel, 1, 1024, 0, k);
+  DLB_LAUNCHED(ctx);
   e.seen = true;
   return DLB_OK;
 }
 
 dlb_status planes_absmax(dlb_ctx *ctx, const float *x, size_t n, float *slot) {
-  absmax_kernel<<<stream_blocks(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(x, n, reinterpret_cast<unsigned *>(slot) + SLOT_AMAX);
+  DLB_LAUNCH_KERNEL(ctx, absmax_kernel, stream_blocks(ctx, n / 4 + 1), 256, 0, x, n, reinterpret_cast<unsigned *>(slot) + SLOT_AMAX);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -280,7 +291,10 @@ dlb_status planes_split_adhoc(dlb_ctx *ctx, const float *x, size_t n, int rows, 
   k.colmax = rows > 0 && lines ? lines + rows : nullptr;
   k.n_lines = k.rowmax ? rows + cols : 0;
   k.guard = ctx->d_guard;
-  return launch_split(ctx, x, n, rows, cols, k);
+  DLB_TRY(launch_split(ctx, x, n, rows, cols, k));
+  DLB_LAUNCH_KERNEL(ctx, planes_finalize_kernel, 1, 1024, 0, k);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
 }
 
 // Drops the entries whose buffer starts inside [base, base + bytes).

@@ -8,7 +8,6 @@
 //   [SLOT_AMAX]  raw bits of max |x| of the split in progress; zero between splits
 //   [SLOT_FLAGS] non-zero: the planes cannot stand for the tensor (see below)
 //   [SLOT_NEXT]  the scale predicted for the next split of this buffer
-//   [SLOT_TICKET] blocks of the writing kernel that have finished; zero between splits
 //
 // A split with the tensor's own maximum known (two passes over the tensor) puts
 // s max|x| in [2^14, 2^15).  A producing kernel that writes the planes itself
@@ -22,10 +21,10 @@
 // error is 2^-39 of the tensor's maximum), but not when every element of a row
 // or a column is small: the outputs that row or column feeds are then wrong by
 // more than fp32 rounding relative to their own size.  Producers therefore
-// leave max |x| per row and per column, and the last block of the kernel that
-// wrote the planes (sink_complete) flags the tensor when a non-zero row or
-// column maximum is below PLANE_TINY / s (18 bits left) or when the tensor's
-// maximum overflowed the predicted scale.  The
+// leave max |x| per row and per column, and the check that follows the split
+// (sink_finalize) flags the tensor when a non-zero row or column maximum is
+// below PLANE_TINY / s (18 bits left) or when the tensor's maximum overflowed
+// the predicted scale.  The
 // tensor-core kernels compute a product with a flagged operand on the CUDA
 // cores from the fp32 tensors instead.
 #pragma once
@@ -37,7 +36,7 @@
 
 namespace dlb {
 
-constexpr int SLOT_S = 0, SLOT_INV = 1, SLOT_AMAX = 2, SLOT_FLAGS = 3, SLOT_NEXT = 4, SLOT_TICKET = 5;
+constexpr int SLOT_S = 0, SLOT_INV = 1, SLOT_AMAX = 2, SLOT_FLAGS = 3, SLOT_NEXT = 4;
 constexpr int PLANE_EXP_OWN = 14;        // s max in [2^14, 2^15): the scale from the tensor's own maximum
 constexpr int PLANE_EXP_PREDICTED = 12;  // s max in [2^12, 2^13): the scale predicted for the next split
 constexpr float PLANE_TINY = 0.0078125f; // 2^-7: a line whose largest s |x| is below this has under 18 bits
@@ -76,11 +75,18 @@ __device__ __forceinline__ void plane_halves(float v, float s, __half *h, __half
 // Four consecutive elements starting at element `off` (a multiple of 4): one
 // 8-byte store into each plane.
 __device__ __forceinline__ void sink_store4(const PlaneSink &k, size_t off, const float (&v)[4], float s) {
-  __half h[4], l[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) plane_halves(v[j], s, h + j, l + j);
-  *reinterpret_cast<uint2 *>(k.hi + off) = *reinterpret_cast<uint2 *>(h);
-  *reinterpret_cast<uint2 *>(k.lo + off) = *reinterpret_cast<uint2 *>(l);
+  // Two values per conversion instruction: the same roundings as plane_halves.
+  const float t0 = v[0] * s, t1 = v[1] * s, t2 = v[2] * s, t3 = v[3] * s;
+  const __half2 h01 = __floats2half2_rn(t0, t1), h23 = __floats2half2_rn(t2, t3);
+  const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+  const __half2 l01 = __floats2half2_rn(t0 - f01.x, t1 - f01.y), l23 = __floats2half2_rn(t2 - f23.x, t3 - f23.y);
+  uint2 hi, lo;
+  hi.x = *reinterpret_cast<const unsigned *>(&h01);
+  hi.y = *reinterpret_cast<const unsigned *>(&h23);
+  lo.x = *reinterpret_cast<const unsigned *>(&l01);
+  lo.y = *reinterpret_cast<const unsigned *>(&l23);
+  *reinterpret_cast<uint2 *>(k.hi + off) = hi;
+  *reinterpret_cast<uint2 *>(k.lo + off) = lo;
 }
 
 // Statistics of a thread that owns four columns and visits whole rows together
@@ -124,24 +130,14 @@ struct LineTracker {
   }
 };
 
-// Last step of a kernel that wrote planes through `k`, called by every thread of
-// every block once the block's stores and statistics are out.  The block that
-// finishes last turns the statistics into what the consumers read: the scale
-// and its inverse, the guard flag, the scale predicted for the next split; and
-// it clears what the next split accumulates into (maximum, line maxima, ticket).
-__device__ __forceinline__ void sink_complete(const PlaneSink &k) {
-  if (!k.slot) return;
-  __shared__ int is_last;
+// After a split (planes_finalize_kernel, one block): turns the statistics into
+// what the consumers read: the scale and its inverse, the guard flag, the scale
+// predicted for the next split; and clears what the next split accumulates into
+// (maximum, line maxima).  A launch of its own: letting the last block of the
+// writing kernel do it (a fence and a ticket per block) was measured at 13 us per
+// 64 MiB tensor, the launch at 6.
+__device__ __forceinline__ void sink_finalize(const PlaneSink &k) {
   unsigned *uslot = reinterpret_cast<unsigned *>(k.slot);
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned blocks = gridDim.x * gridDim.y * gridDim.z;
-    is_last = atomicAdd(uslot + SLOT_TICKET, 1u) == blocks - 1;
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
   const unsigned amax = __ldcg(uslot + SLOT_AMAX);
   const float s = k.predicted ? __ldcg(k.slot + SLOT_NEXT) : plane_scale_from_bits(amax, PLANE_EXP_OWN);
   int tiny = 0;
@@ -165,7 +161,6 @@ __device__ __forceinline__ void sink_complete(const PlaneSink &k) {
     // non-finite tensor leaves the prediction where it was.
     k.slot[SLOT_NEXT] = (amax == 0u || (amax >> 23) == 255u) ? s : plane_scale_from_bits(amax, PLANE_EXP_PREDICTED);
     uslot[SLOT_AMAX] = 0u;
-    uslot[SLOT_TICKET] = 0u;
     if (unsafe && k.guard) atomicAdd(k.guard, 1ull);
   }
 }

@@ -66,6 +66,7 @@ __device__ __forceinline__ float hat(float z, float mean, float r_over_sigma, fl
 
 __global__ void time_quotient_kernel(const float *__restrict__ r, const float *__restrict__ sigma,
                                      float *__restrict__ rs, size_t total) {
+  pdl_enter();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < total) rs[i] = r[i] / sigma[i];
 }
@@ -78,6 +79,7 @@ __device__ __forceinline__ float recur(float y, float u, float h_prev) { return 
 template <int W>
 __global__ void time_major_kernel(const float *__restrict__ x, float *__restrict__ out,
                                   float *__restrict__ out_lo, int rows, int T, int n, unsigned *amax) {
+  pdl_enter();
   const int nw = n / W;
   const size_t total = (size_t)T * rows * nw;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -109,6 +111,7 @@ __global__ void time_major_kernel(const float *__restrict__ x, float *__restrict
 template <int NSUM, int W, class Op>
 __global__ void __launch_bounds__(TR_LANES_X *TR_LANES_Y)
     time_reduce_kernel(Op op, int T, int rows, int n, double *__restrict__ sums) {
+  pdl_enter();
   __shared__ double red[TR_LANES_Y][NSUM][TR_LANES_X * W + 1];
   const int tx = threadIdx.x % TR_LANES_X, ty = threadIdx.x / TR_LANES_X;
   const int col = (blockIdx.x * TR_LANES_X + tx) * W;
@@ -215,6 +218,7 @@ struct TimeBackwardOp {
 __global__ void time_finalize_kernel(const double *__restrict__ sums, int T, int n, float batch_scale,
                                      float momentum, float eps, float r_max, float d_max,
                                      dlb_brn_unit_arrays u) {
+  pdl_enter();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t total = (size_t)T * n;
   if (i >= total) return;
@@ -234,6 +238,7 @@ __global__ void time_finalize_kernel(const double *__restrict__ sums, int T, int
 
 // out[h] (+)= sum over t (from T-1 down, the backward order) of sums[t, h].
 __global__ void time_fold_kernel(const double *__restrict__ sums, int T, int n, float *out) {
+  pdl_enter();
   const int h = blockIdx.x * blockDim.x + threadIdx.x;
   if (h >= n) return;
   double v = 0.0;
@@ -268,6 +273,7 @@ __global__ void __launch_bounds__(256)
                         const uint8_t *__restrict__ mask, float keep_scale,
                         float *__restrict__ A, float *__restrict__ A_lo, int T, int rows, int n,
                         unsigned *amax) {
+  pdl_enter();
   const int nw = n / W;
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)rows * nw) return;
@@ -315,6 +321,7 @@ __global__ void __launch_bounds__(256)
     time_backward_kernel(float *__restrict__ E, const float *__restrict__ Z,
                          const float *__restrict__ A, TimeBrn u, const float *__restrict__ rec, int af,
                          int T, int rows, int n) {
+  pdl_enter();
   const int nw = n / W;
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)rows * nw) return;
@@ -358,6 +365,7 @@ __global__ void __launch_bounds__(TR_LANES_X *TR_LANES_Y)
     time_apply_kernel(float *__restrict__ delta, float *__restrict__ delta_lo,
                       const float *__restrict__ Z, TimeBrn u, const double *__restrict__ sums,
                       float inv_rows, float rows_f, int T, int rows, int n, unsigned *amax) {
+  pdl_enter();
   const int tx = threadIdx.x % TR_LANES_X, ty = threadIdx.x / TR_LANES_X;
   const int col = (blockIdx.x * TR_LANES_X + tx) * W;
   const int t = blockIdx.y;
@@ -396,6 +404,7 @@ __global__ void __launch_bounds__(TR_LANES_X *TR_LANES_Y)
 }
 
 __global__ void clamp_kernel(float *p, int n, float lo, float hi) {
+  pdl_enter();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) p[i] = clipf(p[i], lo, hi);
 }
@@ -414,7 +423,7 @@ dlb_status time_quotients(dlb_ctx *ctx, TimeBrn *p, int T, int n) {
   void *scr = nullptr;
   DLB_TRY(scratch(ctx, total * sizeof(float), &scr));
   float *rs = static_cast<float *>(scr);
-  time_quotient_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(p->r, p->sigma, rs, total);
+  DLB_LAUNCH_KERNEL(ctx, time_quotient_kernel, (unsigned)((total + 255) / 256), 256, 0, p->r, p->sigma, rs, total);
   DLB_LAUNCHED(ctx);
   p->rs = rs;
   return DLB_OK;
@@ -433,8 +442,8 @@ dlb_status time_major_impl(dlb_ctx *ctx, const float *x, float *out, float *out_
   const bool v4 = n % 4 == 0 && aligned16({x, out, out_lo});
   const size_t items = (size_t)seq_w * rows * (v4 ? n / 4 : n);
   const int grid = (int)min((items + 255) / 256, (size_t)ctx->sm_count * 16);
-  if (v4) time_major_kernel<4><<<grid, 256, 0, ctx->stream>>>(x, out, out_lo, rows, seq_w, n, amax);
-  else time_major_kernel<1><<<grid, 256, 0, ctx->stream>>>(x, out, out_lo, rows, seq_w, n, amax);
+  if (v4) DLB_LAUNCH_KERNEL(ctx, time_major_kernel<4>, grid, 256, 0, x, out, out_lo, rows, seq_w, n, amax);
+  else DLB_LAUNCH_KERNEL(ctx, time_major_kernel<1>, grid, 256, 0, x, out, out_lo, rows, seq_w, n, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -445,11 +454,9 @@ dlb_status dlb_brn_time_forward_sums(dlb_ctx *ctx, const float *Z, int seq_w, in
   const bool v4 = n % 4 == 0 && aligned16({Z});
   const dim3 grid(ceil_div(n, TR_LANES_X * (v4 ? 4 : 1)), seq_w);
   if (v4)
-    time_reduce_kernel<2, 4, TimeSumSqOp><<<grid, TR_LANES_X * TR_LANES_Y, 0, ctx->stream>>>(
-        TimeSumSqOp{Z}, seq_w, rows, n, sums);
+    DLB_LAUNCH_KERNEL(ctx, (time_reduce_kernel<2, 4, TimeSumSqOp>), grid, TR_LANES_X * TR_LANES_Y, 0, TimeSumSqOp{Z}, seq_w, rows, n, sums);
   else
-    time_reduce_kernel<2, 1, TimeSumSqOp><<<grid, TR_LANES_X * TR_LANES_Y, 0, ctx->stream>>>(
-        TimeSumSqOp{Z}, seq_w, rows, n, sums);
+    DLB_LAUNCH_KERNEL(ctx, (time_reduce_kernel<2, 1, TimeSumSqOp>), grid, TR_LANES_X * TR_LANES_Y, 0, TimeSumSqOp{Z}, seq_w, rows, n, sums);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -461,8 +468,7 @@ dlb_status dlb_brn_time_forward_finalize(dlb_ctx *ctx, const double *sums, int g
   DLB_REQUIRE(u->mean && u->sigma && u->mean_average && u->sigma_average && u->r && u->d,
               "dlb_brn_time_forward_finalize: null unit array");
   const size_t total = (size_t)seq_w * n;
-  time_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
-      sums, seq_w, n, 1.f / (float)global_rows, momentum, epsilon, r_max, d_max, *u);
+  DLB_LAUNCH_KERNEL(ctx, time_finalize_kernel, (unsigned)((total + 255) / 256), 256, 0, sums, seq_w, n, 1.f / (float)global_rows, momentum, epsilon, r_max, d_max, *u);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -482,11 +488,9 @@ dlb_status indrnn_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_
 #define LAUNCH(W, NORM, REC)                                                                          \
   do {                                                                                                \
     if (drop)                                                                                         \
-      time_forward_kernel<W, NORM, REC, true><<<grid, 256, 0, ctx->stream>>>(                         \
-          Z, p, recurrent, af, mask, keep_scale, A, A_lo, seq_w, rows, n, amax);                      \
+      DLB_LAUNCH_KERNEL(ctx, (time_forward_kernel<W, NORM, REC, true>), grid, 256, 0, Z, p, recurrent, af, mask, keep_scale, A, A_lo, seq_w, rows, n, amax);                      \
     else                                                                                              \
-      time_forward_kernel<W, NORM, REC, false><<<grid, 256, 0, ctx->stream>>>(                        \
-          Z, p, recurrent, af, nullptr, 1.f, A, A_lo, seq_w, rows, n, amax);                          \
+      DLB_LAUNCH_KERNEL(ctx, (time_forward_kernel<W, NORM, REC, false>), grid, 256, 0, Z, p, recurrent, af, nullptr, 1.f, A, A_lo, seq_w, rows, n, amax);                          \
   } while (0)
 #define PICK(W)                                                        \
   do {                                                                 \
@@ -513,8 +517,7 @@ dlb_status dlb_indrnn_backward_walk(dlb_ctx *ctx, float *E, const float *Z, cons
   const bool v4 = n % 4 == 0 && aligned16({E, Z, A, p.mean, p.rs, p.d});
   const int grid = walk_grid((size_t)rows * (v4 ? n / 4 : n));
 #define LAUNCH(W, NORM, REC)                                                                 \
-  time_backward_kernel<W, NORM, REC><<<grid, 256, 0, ctx->stream>>>(E, Z, A, p, recurrent, af, \
-                                                                    seq_w, rows, n)
+  DLB_LAUNCH_KERNEL(ctx, (time_backward_kernel<W, NORM, REC>), grid, 256, 0, E, Z, A, p, recurrent, af, seq_w, rows, n)
   if (v4) PICK(4); else PICK(1);
 #undef LAUNCH
 #undef PICK
@@ -534,8 +537,8 @@ dlb_status dlb_indrnn_backward_sums(dlb_ctx *ctx, const float *E, const float *Z
   const dim3 grid(ceil_div(n, TR_LANES_X * (v4 ? 4 : 1)), seq_w);
   const int threads = TR_LANES_X * TR_LANES_Y;
 #define LAUNCH(W, NORM, REC)                                                                  \
-  time_reduce_kernel<TimeBackwardOp<NORM, REC>::NS, W, TimeBackwardOp<NORM, REC>>             \
-      <<<grid, threads, 0, ctx->stream>>>(TimeBackwardOp<NORM, REC>{E, Z, A, p}, seq_w, rows, n, sums)
+  DLB_LAUNCH_KERNEL(ctx, (time_reduce_kernel<TimeBackwardOp<NORM, REC>::NS, W, TimeBackwardOp<NORM, REC>>), grid, \
+                    threads, 0, (TimeBackwardOp<NORM, REC>{E, Z, A, p}), seq_w, rows, n, sums)
 #define PICK(W)                                           \
   do {                                                    \
     if (u && recurrent) LAUNCH(W, true, true);            \
@@ -551,7 +554,7 @@ dlb_status dlb_indrnn_backward_sums(dlb_ctx *ctx, const float *E, const float *Z
 
 dlb_status dlb_time_fold(dlb_ctx *ctx, const double *sums, int seq_w, int n, float *out) {
   DLB_REQUIRE(ctx && sums && out && seq_w > 0 && n > 0, "dlb_time_fold");
-  time_fold_kernel<<<ceil_div(n, 256), 256, 0, ctx->stream>>>(sums, seq_w, n, out);
+  DLB_LAUNCH_KERNEL(ctx, time_fold_kernel, ceil_div(n, 256), 256, 0, sums, seq_w, n, out);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -565,18 +568,16 @@ dlb_status brn_time_backward_apply_impl(dlb_ctx *ctx, float *delta, float *delta
   const dim3 grid(ceil_div(n, TR_LANES_X * (v4 ? 4 : 1)), seq_w);
   const float nf = (float)global_rows;
   if (v4)
-    time_apply_kernel<4><<<grid, TR_LANES_X * TR_LANES_Y, 0, ctx->stream>>>(
-        delta, delta_lo, Z, time_brn(u), sums, 1.f / nf, nf, seq_w, rows, n, amax);
+    DLB_LAUNCH_KERNEL(ctx, time_apply_kernel<4>, grid, TR_LANES_X * TR_LANES_Y, 0, delta, delta_lo, Z, time_brn(u), sums, 1.f / nf, nf, seq_w, rows, n, amax);
   else
-    time_apply_kernel<1><<<grid, TR_LANES_X * TR_LANES_Y, 0, ctx->stream>>>(
-        delta, delta_lo, Z, time_brn(u), sums, 1.f / nf, nf, seq_w, rows, n, amax);
+    DLB_LAUNCH_KERNEL(ctx, time_apply_kernel<1>, grid, TR_LANES_X * TR_LANES_Y, 0, delta, delta_lo, Z, time_brn(u), sums, 1.f / nf, nf, seq_w, rows, n, amax);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
 
 dlb_status dlb_indrnn_clamp(dlb_ctx *ctx, float *recurrent, int n, float lo, float hi) {
   DLB_REQUIRE(ctx && recurrent && n > 0 && lo <= hi, "dlb_indrnn_clamp");
-  clamp_kernel<<<ceil_div(n, 256), 256, 0, ctx->stream>>>(recurrent, n, lo, hi);
+  DLB_LAUNCH_KERNEL(ctx, clamp_kernel, ceil_div(n, 256), 256, 0, recurrent, n, lo, hi);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }

@@ -121,6 +121,7 @@ SIGNATURES = {
     "dlb_model_set_hparam": (_i, [_vp, _cp, _d]),
     "dlb_model_get_hparam": (_d, [_vp, _cp]),
     "dlb_model_set_weight_decay": (_i, [_vp, _f]),
+    "dlb_model_set_l2": (_i, [_vp, _f]),
     "dlb_model_set_max_batch_size": (_i, [_vp, _sz]),
     "dlb_model_set_seq_w": (_i, [_vp, _sz]),
     "dlb_model_seed_weights": (_i, [_vp, C.c_uint]),
@@ -157,6 +158,11 @@ SIGNATURES = {
     "dlb_model_save_params": (_i, [_vp, _cp]),
     "dlb_model_save_spec_params": (_i, [_vp, _cp]),
     "dlb_model_load": (_i, [_vp, _cp, _cp]),
+    "dlb_checkpointer_create": (_i, [C.POINTER(_vp), _vp, _cp, _i, _i]),
+    "dlb_checkpointer_destroy": (_i, [_vp]),
+    "dlb_checkpointer_save": (_i, [_vp, _i]),
+    "dlb_checkpointer_step": (_i, [_vp, _i, _i, _i, _i, C.POINTER(_i)]),
+    "dlb_checkpointer_load": (_i, [_vp, C.POINTER(_i)]),
     "dlb_noise_uniform": (_i, [_vp, _vp, _sz, _f, _f, _u64, C.c_uint32, C.c_uint32, _u64]),
     "dlb_noise_bernoulli": (_i, [_vp, _vp, _sz, _f, _u64, C.c_uint32, C.c_uint32, _u64]),
     "dlb_model_draw_noise": (_i, [_vp, _sz, _u64, C.c_uint32, _sz]),
@@ -449,6 +455,9 @@ class Model:
     def set_seq_w(self, delays):
         check(self.L.dlb_model_set_seq_w(self.h, delays), "set_seq_w")
 
+    def set_l2(self, value):
+        check(self.L.dlb_model_set_l2(self.h, float(value)), "set_l2")
+
     def set_weight_decay(self, value):
         check(self.L.dlb_model_set_weight_decay(self.h, float(value)), "set_weight_decay")
 
@@ -629,3 +638,38 @@ class Model:
         out = np.empty((T, batch, n_out), dtype=np.float32)
         check(self.L.dlb_model_get_layer_errors(self.h, layer, batch, which, _ptr(out)), "get_layer_errors")
         return out
+
+
+class Checkpointer:
+    """DL::Checkpointer / CheckpointerInterval over a Model: rotating checkpoint
+    directories in the reference's layout, plus the optimizer moments."""
+
+    def __init__(self, model, ckpt_dir, max_to_keep=3, interval=1):
+        self.L = lib()
+        self.model = model
+        h = _vp()
+        check(self.L.dlb_checkpointer_create(C.byref(h), model.h, os.fsencode(ckpt_dir), max_to_keep, interval),
+              "dlb_checkpointer_create")
+        self.h = h
+
+    def save(self, step):
+        check(self.L.dlb_checkpointer_save(self.h, step), "dlb_checkpointer_save")
+
+    def __call__(self, g, step=None, is_top=True, force=False):
+        saved = _i(0)
+        check(self.L.dlb_checkpointer_step(self.h, g, g if step is None else step, int(is_top), int(force),
+                                           C.byref(saved)), "dlb_checkpointer_step")
+        return bool(saved.value)
+
+    def load(self):
+        found = _i(0)
+        check(self.L.dlb_checkpointer_load(self.h, C.byref(found)), "dlb_checkpointer_load")
+        return bool(found.value)
+
+    def __del__(self):
+        try:
+            if getattr(self, "h", None):
+                self.L.dlb_checkpointer_destroy(self.h)
+                self.h = None
+        except Exception:
+            pass

@@ -521,6 +521,11 @@ double dlb_model_get_hparam(dlb_model *m, const char *name);
  * ref: Model::set_weight_decay (v1/ops/regularizers/weight_decay.cpp L:26-60),
  * Model::normalized_wd (v1/learner/train.cpp L:278-283). */
 dlb_status dlb_model_set_weight_decay(dlb_model *m, float value);
+/* ref: Model::set_l2 (v1/ops/regularizers/l2.cpp L:31-66).  Kept and written to
+ * the hyperparameter file; like the reference's, the value never reaches the
+ * gradient (its update calls the L2 routine over an empty index range:
+ * v1/learner/model.cpp L:4717-4719 against l2.cpp L:92-104). */
+dlb_status dlb_model_set_l2(dlb_model *m, float value);
 dlb_status dlb_model_set_max_batch_size(dlb_model *m, size_t rows);
 dlb_status dlb_model_set_seq_w(dlb_model *m, size_t time_delays);
 dlb_status dlb_model_seed_weights(dlb_model *m, unsigned seed);
@@ -629,6 +634,24 @@ dlb_status dlb_model_draw_noise(dlb_model *m, size_t rows, uint64_t seed, uint32
 dlb_status dlb_model_save_params(dlb_model *m, const char *path);
 dlb_status dlb_model_save_spec_params(dlb_model *m, const char *path);
 dlb_status dlb_model_load(dlb_model *m, const char *path_params, const char *path_spec);
+/* Checkpoint directories with rotation, in the reference's layout
+ * (DL::Checkpointer, nn/checkpointer.cpp L:41-221): <dir>/ckpt-<step>/model.net
+ * and model.nn (the two files above), <dir>/checkpoint naming the newest, the
+ * newest max_to_keep directories kept.  The library adds <dir>/ckpt-<step>/
+ * model.opt, the optimizer's moments and time step, which the reference's format
+ * lacks and its loader ignores; dlb_checkpointer_load restores them when present.
+ * dlb_checkpointer_step is CheckpointerInterval::operator() (L:230-250): saves
+ * (as step_train) when forced, or when g has reached the next due step and
+ * is_top is set, then moves the due step to g + interval.
+ * dlb_checkpointer_load wants a model that has not been compiled; *found = 0 when
+ * the directory holds no checkpoint. */
+typedef struct dlb_checkpointer dlb_checkpointer;
+dlb_status dlb_checkpointer_create(dlb_checkpointer **out, dlb_model *model, const char *ckpt_dir,
+                                   int max_to_keep, int interval);
+dlb_status dlb_checkpointer_destroy(dlb_checkpointer *c);
+dlb_status dlb_checkpointer_save(dlb_checkpointer *c, int step_train);
+dlb_status dlb_checkpointer_step(dlb_checkpointer *c, int g, int step_train, int is_top, int force, int *saved);
+dlb_status dlb_checkpointer_load(dlb_checkpointer *c, int *found);
 /* Model::set_clip_gradient, both overloads (v1/ops/constraints/clip_gradient.cpp
  * L:30-73): whether update_weights clips, and the norm; the norm also sets the
  * default bound of IndRNN recurrent weights, clip(value, 2, 10)^(1/seq_w)

@@ -22,18 +22,25 @@ _szp = np.ctypeslib.ndpointer(dtype=np.uint64, flags="C_CONTIGUOUS")
 _i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
 _f64p = np.ctypeslib.ndpointer(dtype=np.float64, flags="C_CONTIGUOUS")
 
-_lib = None
+DROPIN_LIB_PATH = os.path.join(_HERE, "_ref", "libdlref_dropin.so")
+
+_libs = {}
 
 
 def available() -> bool:
     return os.path.exists(LIB_PATH)
 
 
-def lib():
-    global _lib
-    if _lib is not None:
-        return _lib
-    L = C.CDLL(LIB_PATH)
+def dropin_available() -> bool:
+    """The reference built with its step routed to libdlb200 (`make -C oracle dropin`)."""
+    return os.path.exists(DROPIN_LIB_PATH)
+
+
+def lib(path=None):
+    path = path or LIB_PATH
+    if path in _libs:
+        return _libs[path]
+    L = C.CDLL(path)
     vp, sz, i, f, d, cp = C.c_void_p, C.c_size_t, C.c_int, C.c_float, C.c_double, C.c_char_p
     sig = {
         "ref_model_create": (vp, []),
@@ -54,6 +61,7 @@ def lib():
         "ref_set_mp": (i, [vp, i]),
         "ref_set_weight_decay": (i, [vp, C.c_double]),
         "ref_set_clip_gradient": (i, [vp, i, C.c_double]),
+        "ref_set_l2": (i, [vp, C.c_double]),
         "ref_save": (i, [vp, cp, cp]),
         "ref_load": (i, [vp, cp, cp]),
         "ref_set_propagation": (i, [vp, i]),
@@ -89,11 +97,13 @@ def lib():
         "ref_get_layer_errors": (i, [vp, sz, sz, i, _f32p]),
         "ref_optimizer_sweep": (d, [i, sz, i, i, _f32p, _f32p, _f32p, _f32p, _f32p, _f64p]),
     }
+    if path == DROPIN_LIB_PATH:
+        sig["ref_set_b200"] = (i, [vp, i, i])
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
         fn.restype = res
         fn.argtypes = args
-    _lib = L
+    _libs[path] = L
     return L
 
 
@@ -106,9 +116,10 @@ class RefModel:
     """Same method names as the CUDA library's Python ``Model``."""
 
     backend = "reference-openmp"
+    lib_path = None
 
     def __init__(self):
-        self.L = lib()
+        self.L = lib(self.lib_path)
         self.h = self.L.ref_model_create()
 
     def close(self):
@@ -198,6 +209,9 @@ class RefModel:
 
     def load(self, path_params, path_spec):
         _ck(self.L.ref_load(self.h, path_params.encode(), path_spec.encode()), "load")
+
+    def set_l2(self, value):
+        _ck(self.L.ref_set_l2(self.h, float(value)), "set_l2")
 
     def set_clip_gradient(self, use, value):
         _ck(self.L.ref_set_clip_gradient(self.h, int(bool(use)), float(value)), "set_clip_gradient")
@@ -300,6 +314,19 @@ class RefModel:
         out = np.empty((T, batch, n_out), dtype=np.float32)
         _ck(self.L.ref_get_layer_errors(self.h, layer, batch, which, out), "get_layer_errors")
         return out
+
+
+class DropinModel(RefModel):
+    """The reference's own Model class, built with its step entry points routed to
+    libdlb200 (oracle/dropin_patch.py, oracle/dropin_glue.cpp): construction and
+    the step go through the reference's methods; after `set_b200(True)` the
+    numerical work of the step runs in the CUDA library."""
+
+    backend = "reference-with-dlb200"
+    lib_path = DROPIN_LIB_PATH
+
+    def set_b200(self, on, device=0):
+        _ck(self.L.ref_set_b200(self.h, int(bool(on)), device), "set_b200")
 
 
 def uout_draws(seed, betas, rows, widths):

@@ -203,6 +203,9 @@ int ref_set_mp(ref_model m, int use_mp) {
 int ref_set_weight_decay(ref_model m, double value) {
   return H(m)->model.set_weight_decay(static_cast<real>(value)) ? 0 : -1;
 }
+int ref_set_l2(ref_model m, double value) {
+  return H(m)->model.set_l2(static_cast<real>(value)) ? 0 : -1;
+}
 int ref_set_clip_gradient(ref_model m, int use, double value) {
   H(m)->model.set_clip_gradient(use != 0);
   return H(m)->model.set_clip_gradient(static_cast<real>(value)) ? 0 : -1;

@@ -97,3 +97,80 @@ def test_a_file_outside_the_supported_path_is_refused(gpu_ctx, tmp_path):
         dlb200.Model(gpu_ctx).load(*files)
     with pytest.raises(dlb200.DlbError):
         dlb200.Model(gpu_ctx).load(str(tmp_path / "missing.net"), files[1])
+
+
+def test_checkpointer_rotation_moments_and_resume(gpu_ctx, tmp_path):
+    """Checkpoint directories as DL::Checkpointer writes them (nn/checkpointer.cpp
+    L:94-160): ckpt-<step>/model.net + model.nn, a `checkpoint` file naming the
+    newest, the newest max_to_keep kept; the interval policy of
+    CheckpointerInterval (L:230-250); and the side file with the optimizer's
+    moments, with which a run resumed from the directory continues bit for bit."""
+    import os
+    import time
+
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96)
+    B = cfg["batch"]
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+
+    def with_masks(m):
+        for li, mk in masks.items():
+            m.set_dropout_mask(li, mk)
+        return m
+
+    model = with_masks(util.build(dlb200.Model(gpu_ctx), cfg, seed=7))
+    ck = dlb200.Checkpointer(model, str(tmp_path), max_to_keep=2, interval=3)
+    saved_at = []
+    for g in range(8):
+        model.train_step(B, X, Y)
+        if ck(g):
+            saved_at.append(g)
+            time.sleep(0.02)   # rotation orders the directories by time of last write
+    assert saved_at == [0, 3, 6]                                   # due steps 0, 3, 6
+    assert sorted(os.listdir(tmp_path)) == ["checkpoint", "ckpt-3", "ckpt-6"]   # ckpt-0 rotated out
+    assert open(tmp_path / "checkpoint", "rb").read() == b"model_checkpoint_path: ckpt-6"
+    assert sorted(os.listdir(tmp_path / "ckpt-6")) == ["model.net", "model.nn", "model.opt"]
+    assert not ck(7) and ck(7, force=True)                         # not due, then forced
+    assert sorted(os.listdir(tmp_path)) == ["checkpoint", "ckpt-6", "ckpt-7"]
+    # Resume: a fresh model loads the newest checkpoint and continues exactly.
+    resumed = dlb200.Model(gpu_ctx)
+    assert dlb200.Checkpointer(resumed, str(tmp_path)).load()
+    with_masks(resumed)
+    util.copy_trained_state(model, resumed, cfg)                   # running averages travel in model.net already
+    for key in ("parameters", "first_moment", "second_moment", "second_moment_hat"):
+        assert np.array_equal(resumed.get_array(key), model.get_array(key)), key
+    assert resumed.get_hparam("optimizer_time_step") == model.get_hparam("optimizer_time_step") == 8.0
+    a = [model.train_step(B, X, Y) for _ in range(3)]
+    b = [resumed.train_step(B, X, Y) for _ in range(3)]
+    np.testing.assert_allclose(b, a, rtol=1e-12)
+    assert np.array_equal(resumed.get_array("parameters"), model.get_array("parameters"))
+    # Without the side file (a checkpoint the reference wrote) the moments start at zero.
+    os.remove(tmp_path / "ckpt-7" / "model.opt")
+    plain = dlb200.Model(gpu_ctx)
+    assert dlb200.Checkpointer(plain, str(tmp_path)).load()
+    assert not plain.get_array("first_moment").any()
+    empty = dlb200.Model(gpu_ctx)
+    assert not dlb200.Checkpointer(empty, str(tmp_path / "nothing_here")).load()
+    assert gpu_ctx.sync() == 0
+
+
+def test_l2_is_kept_and_saved_but_does_not_touch_the_step(gpu_ctx, tmp_path):
+    """Model::set_l2: the reference's update calls its L2 routine over an empty
+    range (tests/test_oracle.py pins that), so the value only travels through the
+    hyperparameter file."""
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 96)
+    B = cfg["batch"]
+    X, Y = configs.synthetic_batch(cfg)
+    a = util.build(dlb200.Model(gpu_ctx), cfg, seed=7)
+    b = util.build(dlb200.Model(gpu_ctx), cfg, seed=7)
+    b.set_l2(0.1)
+    for m in (a, b):
+        m.train_step(B, X, Y)
+    assert np.array_equal(a.get_array("parameters"), b.get_array("parameters"))
+    b.save(str(tmp_path / "m.net"), str(tmp_path / "m.nn"))
+    assert "regularization__l2 0.1" in open(tmp_path / "m.nn", "rb").read().decode().replace("0.1000000014901161", "0.1")
+    c = dlb200.Model(gpu_ctx)
+    c.load(str(tmp_path / "m.net"), str(tmp_path / "m.nn"))
+    with pytest.raises(dlb200.DlbError):
+        b.set_l2(1.5)
+    assert gpu_ctx.sync() == 0

@@ -284,3 +284,25 @@ def test_input_layer_dropout_matches_compiled_reference(kind):
         outs.append(m.get_layer_outputs(last, B).reshape(B, -1))
         m.set_propagation(1)
     assert util.rel_l2(outs[1], outs[0]) <= TOL_L2
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("mp", [True, False], ids=["openmp", "serial"])
+def test_l2_regularization_has_no_effect_in_the_reference(mp):
+    """Model::set_l2 stores its value, but the update's call of the L2 routine
+    passes (batch_size, 0, total_weights) where the routine takes (start, end,
+    batch_size) (v1/learner/model.cpp L:4717-4719, L:4804-4806; l2.cpp L:79-104):
+    the loop covers no element.  A run with l2 = 0.1 equals a run without, bit
+    for bit; the drop-in therefore keeps the value and leaves the gradient alone."""
+    cfg = dict(configs.deep_brn_mlp(20, 32, 2, 12, 24), mp=mp)
+    plain = util.build(ref_binding.RefModel(), cfg, seed=0)
+    p0 = plain.get_array("parameters")
+    want = util.trace(plain, cfg, steps=3)
+    with_l2 = util.build(ref_binding.RefModel(), cfg, params=p0)
+    with_l2.set_l2(0.1)
+    got = util.trace(with_l2, cfg, steps=3)
+    assert np.array_equal(got["params_last"], want["params_last"])
+    assert np.array_equal(got["grads"], want["grads"])
+    ora = util.build(fc_step.OracleModel(), cfg, params=p0)
+    ora.set_l2(0.1)
+    assert util.rel_l2(util.trace(ora, cfg, steps=3)["params_last"], want["params_last"]) <= TOL_L2
