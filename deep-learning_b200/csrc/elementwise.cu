@@ -5,10 +5,12 @@
 // context scratch arena and are finished in double in a fixed order, so results
 // do not depend on block scheduling.
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "math.cuh"
 #include "planes.cuh"
+#include "ring.cuh"
 
 namespace dlb {
 
@@ -21,6 +23,8 @@ namespace dlb {
 // shared memory in double, and the block writes NSUM x 128 doubles to
 // partials[chunk][s][col].  reduce_partials then sums the chunks in order.
 // ---------------------------------------------------------------------------
+// 32 x 8 threads: 64 x 4 (1 KB of a row per block) was measured within 3 % either
+// way on every kernel of the family.
 constexpr int CR_LANES_X = 32;
 constexpr int CR_LANES_Y = 8;
 constexpr int CR_COLS = CR_LANES_X * 4;
@@ -30,11 +34,20 @@ constexpr int CR_COLS = CR_LANES_X * 4;
 // and three blocks per SM).
 constexpr int CR_MAX_PER_SM = 4;
 
+// Shared memory of a reduction block: the copy ring while it walks the rows,
+// then the fold of the 8 row lanes.
 template <int NSUM, class Op>
-__global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
+constexpr size_t column_reduce_shared_bytes() {
+  const size_t ring = ring_bytes(Op::NIN, Op::DEPTH > 0 ? Op::DEPTH : 0, CR_LANES_X * CR_LANES_Y);
+  const size_t fold = sizeof(double) * CR_LANES_Y * NSUM * (CR_COLS + 1);
+  return ring > fold ? ring : fold;
+}
+
+template <int NSUM, class Op>
+__global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y, Op::MIN_BLOCKS)
     column_reduce_kernel(Op op, int rows, int n, int rows_per_chunk, double *partials) {
   pdl_enter();
-  __shared__ double red[CR_LANES_Y][NSUM][CR_COLS + 1];
+  extern __shared__ float4 cr_shared[];
   const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
   const int col = blockIdx.x * CR_COLS + tx * 4;
   const int r0 = blockIdx.y * rows_per_chunk;
@@ -49,18 +62,30 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
     if ((n & 3) == 0) {
       typename Op::Cols4 c;
       op.load_cols4(col, c);
-      // Op::IN_FLIGHT rows per iteration, their loads first: each thread keeps
-      // that many 16-byte requests per input tensor in flight.  The sums take
-      // the rows in ascending order either way.
-      constexpr int U = Op::IN_FLIGHT;
-      for (int r = r0 + ty; r < r1; r += U * CR_LANES_Y) {
-        typename Op::Row4 x[U];
+      // The rows come through the thread's copy ring (Op::DEPTH - 1 rows of
+      // Op::NIN tensors under way); the sums take them in ascending order.
+      const float *in[Op::NIN];
+      op.inputs(in);
+      if constexpr (Op::DEPTH > 0) {
+        ring_walk<Op::NIN, Op::DEPTH, CR_LANES_X * CR_LANES_Y>(cr_shared, in, (size_t)n, col, r0 + ty, r1, CR_LANES_Y,
+                                      [&](int r, const float4(&x)[Op::NIN]) { op.use4(r, col, c, x, acc); });
+      } else {
+        // Read-only kernels with registers to spare: Op::IN_FLIGHT rows per
+        // iteration by plain loads, all of them sent before the first is used.
+        constexpr int U = Op::IN_FLIGHT;
+        for (int r = r0 + ty; r < r1; r += U * CR_LANES_Y) {
+          float4 x[U][Op::NIN];
 #pragma unroll
-        for (int k = 0; k < U; ++k)
-          if (r + k * CR_LANES_Y < r1) op.load4(r + k * CR_LANES_Y, col, x[k]);
+          for (int k = 0; k < U; ++k)
+            if (r + k * CR_LANES_Y < r1) {
 #pragma unroll
-        for (int k = 0; k < U; ++k)
-          if (r + k * CR_LANES_Y < r1) op.use4(r + k * CR_LANES_Y, col, c, x[k], acc);
+              for (int i = 0; i < Op::NIN; ++i)
+                x[k][i] = __ldg(reinterpret_cast<const float4 *>(in[i] + (size_t)(r + k * CR_LANES_Y) * n + col));
+            }
+#pragma unroll
+          for (int k = 0; k < U; ++k)
+            if (r + k * CR_LANES_Y < r1) op.use4(r + k * CR_LANES_Y, col, c, x[k], acc);
+        }
       }
     } else {
       for (int j = 0; j < 4 && col + j < n; ++j) {
@@ -75,6 +100,8 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
       }
     }
   }
+  ring_drain();
+  double(*red)[NSUM][CR_COLS + 1] = reinterpret_cast<double(*)[NSUM][CR_COLS + 1]>(cr_shared);
 #pragma unroll
   for (int s = 0; s < NSUM; ++s)
 #pragma unroll
@@ -102,14 +129,15 @@ __global__ void reduce_partials_kernel(const double *partials, int chunks, int t
   out[i] = t;
 }
 
-// Chunking of the rows: one wave of blocks over the SMs, `per_sm` blocks on each
-// (what the kernel's registers allow, at most CR_MAX_PER_SM; a grid larger than
-// one wave leaves a partial second wave that costs a whole one), chunks of at
-// least 64 rows.
-static void column_reduce_plan(int sm_count, int rows, int n, int per_sm, int *chunks, int *rows_per_chunk) {
+// Chunking of the rows: one wave of blocks over the SMs, CR_MAX_PER_SM blocks on
+// each or as many as `resident` (what an SM holds of the kernel) allows if that
+// is fewer; a grid larger than what is resident at once leaves a partial second
+// wave that costs a whole one.  Chunks of at least 64 rows.
+static void column_reduce_plan(int sm_count, int rows, int n, int resident, int *chunks, int *rows_per_chunk) {
   const int col_blocks = ceil_div(n, CR_COLS);
-  int c = per_sm == CR_MAX_PER_SM ? ceil_div(sm_count * per_sm, col_blocks)
-                                  : max(1, sm_count * per_sm / col_blocks);
+  const int target = max(1, min(resident, CR_MAX_PER_SM));
+  int c = ceil_div(sm_count * target, col_blocks);
+  if ((long long)c * col_blocks > (long long)sm_count * resident) c = max(1, sm_count * target / col_blocks);
   c = max(1, min(c, ceil_div(rows, 64)));
   *rows_per_chunk = ceil_div(ceil_div(rows, c), CR_LANES_Y) * CR_LANES_Y;
   *chunks = ceil_div(rows, *rows_per_chunk);
@@ -119,21 +147,35 @@ static void column_reduce_plan(int sm_count, int rows, int n, int per_sm, int *c
 // sums behind them in the same scratch request).
 static size_t column_reduce_partial_bytes(dlb_ctx *ctx, int nsum, int rows, int n) {
   int chunks, rpc;
-  column_reduce_plan(ctx->sm_count, rows, n, CR_MAX_PER_SM, &chunks, &rpc);
+  column_reduce_plan(ctx->sm_count, rows, n, 1 << 20, &chunks, &rpc);  // the most chunks any kernel's plan makes
   return align_up((size_t)chunks * nsum * n * sizeof(double), 256);
 }
 
-// Blocks of one reduction kernel an SM of the current device holds, at most
-// CR_MAX_PER_SM.  The query allocates nothing.
+// Lets `Kernel` take `bytes` of dynamic shared memory on the current device
+// (needed above 48 KB); once per kernel and device.
+template <auto Kernel>
+static void kernel_shared_limit(size_t bytes) {
+  static bool done[MAX_DEVICES] = {};
+  int dev = 0;
+  if (bytes <= 48 * 1024 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES || done[dev]) return;
+  if (cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) == cudaSuccess)
+    done[dev] = true;
+  else
+    cudaGetLastError();
+}
+
+// Blocks of one reduction kernel an SM of the current device holds.  The query
+// allocates nothing.
 template <int NSUM, class Op>
 static int column_reduce_per_sm() {
   int blocks = CR_MAX_PER_SM;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, column_reduce_kernel<NSUM, Op>,
-                                                    CR_LANES_X * CR_LANES_Y, 0) != cudaSuccess) {
+  kernel_shared_limit<column_reduce_kernel<NSUM, Op>>(column_reduce_shared_bytes<NSUM, Op>());
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, column_reduce_kernel<NSUM, Op>, CR_LANES_X * CR_LANES_Y,
+                                                    column_reduce_shared_bytes<NSUM, Op>()) != cudaSuccess) {
     cudaGetLastError();
     blocks = CR_MAX_PER_SM;
   }
-  return max(1, min(blocks, CR_MAX_PER_SM));
+  return max(1, blocks);
 }
 
 template <int NSUM, class Op>
@@ -147,7 +189,7 @@ static dlb_status column_reduce(dlb_ctx *ctx, Op op, int rows, int n, double *ou
   void *scr = nullptr;
   DLB_TRY(scratch(ctx, column_reduce_partial_bytes(ctx, NSUM, rows, n), &scr));
   double *partials = static_cast<double *>(scr);
-  DLB_LAUNCH_KERNEL(ctx, (column_reduce_kernel<NSUM, Op>), dim3(col_blocks, chunks), CR_LANES_X * CR_LANES_Y, 0, op, rows, n, rows_per_chunk, partials);
+  DLB_LAUNCH_KERNEL(ctx, (column_reduce_kernel<NSUM, Op>), dim3(col_blocks, chunks), CR_LANES_X * CR_LANES_Y, (column_reduce_shared_bytes<NSUM, Op>()), op, rows, n, rows_per_chunk, partials);
   DLB_LAUNCHED(ctx);
   const int total = NSUM * n;
   DLB_LAUNCH_KERNEL(ctx, reduce_partials_kernel, ceil_div(total, 256), 256, 0, partials, chunks, total, out);
@@ -156,6 +198,9 @@ static dlb_status column_reduce(dlb_ctx *ctx, Op op, int rows, int n, double *ou
 }
 
 // --- sum(z), sum(z^2) --------------------------------------------------------
+// The two read-only reductions use plain loads, four rows per thread in flight:
+// six or eight in flight, or the copy ring, leave the 64 MiB pass where it is
+// (15.1 - 15.7 us with its second launch; 10 us of it is the transfer).
 struct SumSqOp {
   const float *Z;
   int n;
@@ -163,13 +208,10 @@ struct SumSqOp {
   struct Cols1 {};
   __device__ void load_cols4(int, Cols4 &) const {}
   __device__ void load_cols1(int, Cols1 &) const {}
-  static constexpr int IN_FLIGHT = 4;
-  struct Row4 { float4 z; };
-  __device__ void load4(int r, int col, Row4 &x) const {
-    x.z = __ldg(reinterpret_cast<const float4 *>(Z + (size_t)r * n + col));
-  }
-  __device__ void use4(int, int, const Cols4 &, const Row4 &x, float (&acc)[2][4]) const {
-    const float4 z = x.z;
+  static constexpr int NIN = 1, DEPTH = 0, IN_FLIGHT = 4, MIN_BLOCKS = 1;
+  __device__ void inputs(const float *(&in)[1]) const { in[0] = Z; }
+  __device__ void use4(int, int, const Cols4 &, const float4 (&x)[1], float (&acc)[2][4]) const {
+    const float4 z = x[0];
     acc[0][0] += z.x; acc[0][1] += z.y; acc[0][2] += z.z; acc[0][3] += z.w;
     acc[1][0] += z.x * z.x; acc[1][1] += z.y * z.y; acc[1][2] += z.z * z.z; acc[1][3] += z.w * z.w;
   }
@@ -188,13 +230,10 @@ struct SumOp {
   struct Cols1 {};
   __device__ void load_cols4(int, Cols4 &) const {}
   __device__ void load_cols1(int, Cols1 &) const {}
-  static constexpr int IN_FLIGHT = 4;
-  struct Row4 { float4 z; };
-  __device__ void load4(int r, int col, Row4 &x) const {
-    x.z = __ldg(reinterpret_cast<const float4 *>(X + (size_t)r * n + col));
-  }
-  __device__ void use4(int, int, const Cols4 &, const Row4 &x, float (&acc)[1][4]) const {
-    const float4 z = x.z;
+  static constexpr int NIN = 1, DEPTH = 0, IN_FLIGHT = 4, MIN_BLOCKS = 1;
+  __device__ void inputs(const float *(&in)[1]) const { in[0] = X; }
+  __device__ void use4(int, int, const Cols4 &, const float4 (&x)[1], float (&acc)[1][4]) const {
+    const float4 z = x[0];
     acc[0][0] += z.x; acc[0][1] += z.y; acc[0][2] += z.z; acc[0][3] += z.w;
   }
   __device__ void row1(int r, int col, const Cols1 &, float (&acc)[1]) const {
@@ -231,7 +270,9 @@ __device__ __forceinline__ float brn_norm(float xh, const BrnCol &c) {
 }
 
 // --- activation backward (+ BRN backward sums) --------------------------------
-template <bool NORM>
+// AF: the activation function when the caller knows it at compile time (the
+// switch then folds away), or -1 to read it from `af`.
+template <bool NORM, int AF = -1>
 struct ActBackwardOp {
   float *dA;
   const float *Z, *A;
@@ -268,7 +309,7 @@ struct ActBackwardOp {
       xh = brn_hat(z, k.c);
       y = brn_norm(xh, k.c);
     }
-    const float e = da * af_derive(af, y, a);
+    const float e = da * af_derive(AF >= 0 ? AF : af, y, a);
     if (NORM) {
       // bwp_mp.cpp L:1559-1574
       *s0 += e * xh;
@@ -279,18 +320,12 @@ struct ActBackwardOp {
     }
     return e;
   }
-  static constexpr int IN_FLIGHT = 2;
-  struct Row4 { float4 da, z, a; };
-  __device__ void load4(int r, int col, Row4 &x) const {
+  static constexpr int NIN = 3, DEPTH = 4, IN_FLIGHT = 0, MIN_BLOCKS = 3;
+  __device__ void inputs(const float *(&in)[3]) const { in[0] = dA; in[1] = Z; in[2] = A; }
+  __device__ void use4(int r, int col, const Cols4 &k, const float4 (&x)[3], float (&acc)[4][4]) const {
     const size_t o = (size_t)r * n + col;
-    x.da = *reinterpret_cast<const float4 *>(dA + o);
-    x.z = __ldg(reinterpret_cast<const float4 *>(Z + o));
-    x.a = __ldg(reinterpret_cast<const float4 *>(A + o));
-  }
-  __device__ void use4(int r, int col, const Cols4 &k, const Row4 &x, float (&acc)[4][4]) const {
-    const size_t o = (size_t)r * n + col;
-    float4 da = x.da;
-    const float4 z = x.z, a = x.a;
+    float4 da = x[0];
+    const float4 z = x[1], a = x[2];
     da.x = one(da.x, z.x, a.x, k.k[0], &acc[0][0], &acc[1][0], &acc[2][0], &acc[3][0]);
     da.y = one(da.y, z.y, a.y, k.k[1], &acc[0][1], &acc[1][1], &acc[2][1], &acc[3][1]);
     da.z = one(da.z, z.z, a.z, k.k[2], &acc[0][2], &acc[1][2], &acc[2][2], &acc[3][2]);
@@ -313,11 +348,12 @@ static inline int stream_grid(dlb_ctx *ctx, size_t work_items, int block) {
   return (int)max((size_t)1, min(blocks, cap));
 }
 
-// Row chunking of the row-loop kernels: about 8 blocks of 256 threads per SM,
-// chunks a multiple of the 8 row lanes.
+// Row chunking of the row-loop kernels: one wave of four blocks of 256 threads
+// per SM (what their shared memory and registers are sized for), chunks a
+// multiple of the 8 row lanes.
 static void rows_plan(dlb_ctx *ctx, int rows, int n, int *chunks, int *rows_per_chunk) {
   const int col_blocks = ceil_div(n, CR_COLS);
-  int c = ceil_div(ctx->sm_count * 8, col_blocks);
+  int c = max(1, ctx->sm_count * 4 / col_blocks);
   c = max(1, min(c, ceil_div(rows, CR_LANES_Y)));
   *rows_per_chunk = ceil_div(ceil_div(rows, c), CR_LANES_Y) * CR_LANES_Y;
   *chunks = ceil_div(rows, *rows_per_chunk);
@@ -496,23 +532,38 @@ __global__ void activation_backward_plain_kernel(float *__restrict__ dA, const f
 // with stride 8, so the inner loop is one 16-byte load per input tensor and
 // one 16-byte store per output tensor, each warp touching 512 contiguous bytes.
 // ---------------------------------------------------------------------------
-// Rows a thread of activation_forward_rows_kernel has in flight (template
-// parameter AF_ROWS: 4, or 2 with DLB_AF_ROWS=2 for measurements).  Four at 76
-// registers, three blocks per SM, measured slower than two (36.7 us against
-// 31.9 us on 4096 x 4096); held to 64 registers, four blocks per SM, four rows
-// are the faster (a few bytes of spills).
+// Calls f with the activation function as a compile-time constant, so that the
+// per-element switch of af_fire / af_derive folds away in the hot kernels.
+template <class F>
+static dlb_status with_af(int af, F f) {
+  switch (af) {
+    case DLB_AF_RELU: return f(std::integral_constant<int, DLB_AF_RELU>{});
+    case DLB_AF_LEAKY_RELU: return f(std::integral_constant<int, DLB_AF_LEAKY_RELU>{});
+    case DLB_AF_ELU: return f(std::integral_constant<int, DLB_AF_ELU>{});
+    case DLB_AF_SELU: return f(std::integral_constant<int, DLB_AF_SELU>{});
+    case DLB_AF_ISRLU: return f(std::integral_constant<int, DLB_AF_ISRLU>{});
+    default: return f(std::integral_constant<int, DLB_AF_LINEAR>{});  // what af_fire does with any other value
+  }
+}
+
+// The rows come through a thread-private copy ring in shared memory: AF_DEPTH - 1
+// rows of 16 bytes per thread under way, 44 KB per block, where plain loads held
+// four (a register quadruple each, at the 64 registers four blocks per SM allow).
+constexpr int AF_DEPTH = 12;     // one input tensor
+constexpr int APPLY_DEPTH = 6;   // two input tensors
+constexpr int ROWS_PER_SM = 4;   // blocks per SM both kernels are built for
 
 // PLANES: the kernel also writes the fp16 planes of A (with the scale predicted
 // from the buffer's previous split) and the row / column maxima of the range
 // guard; otherwise it leaves max |A| in the sink's slot for the split pass that
 // follows.
-template <bool PLANES, int AF_ROWS>
-__global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y, 4)
-    activation_forward_rows_kernel(const float *__restrict__ Z, BrnPtrs u, int af, DropoutDev dp,
+template <bool PLANES, int AF>
+__global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y, ROWS_PER_SM)
+    activation_forward_rows_kernel(const float *__restrict__ Z, BrnPtrs u, DropoutDev dp,
                                    float *__restrict__ A, float *__restrict__ A_lo, int rows, int n,
                                    int rows_per_chunk, PlaneSink sink) {
   pdl_enter();
-  __shared__ unsigned line_shared[PLANES ? CR_LANES_Y * CR_COLS : 1];
+  extern __shared__ float4 row_ring[];
   const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
   const int col = blockIdx.x * CR_COLS + tx * 4;
   const bool live_col = col < n;
@@ -522,7 +573,9 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y, 4)
   const float plane_scale = PLANES ? sink_scale(sink) : 1.f;
   if (live_col) {
     BrnCol c[4];
-    // Bernoulli dropout has one flag per unit: a factor per owned column.
+    // Bernoulli dropout has one flag per unit: a factor per owned column, 0 for a
+    // dropped unit, 1 (plain: kept units pass unchanged, as the reference leaves
+    // them; a * 1 is a) or 1 / keep probability (inverted) for a kept one.
     float keep[4];
     const bool bern = dp.type == DLB_DROPOUT_BERNOULLI || dp.type == DLB_DROPOUT_BERNOULLI_INVERTED;
 #pragma unroll
@@ -530,60 +583,50 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y, 4)
       c[j] = u.at(col + j);
       keep[j] = bern ? (dp.mask[col + j] ? (dp.type == DLB_DROPOUT_BERNOULLI_INVERTED ? dp.scale : 1.f) : 0.f) : 1.f;
     }
-    // AF_ROWS rows per iteration, loads first, so that each thread keeps that many
-    // 16-byte requests in flight.
-    for (int r = r0 + ty; r < r1; r += AF_ROWS * CR_LANES_Y) {
-      size_t o[AF_ROWS];
-      bool live[AF_ROWS];
-      float4 z[AF_ROWS];
+    const float *in[1] = {Z};
+    ring_walk<1, AF_DEPTH, CR_LANES_X * CR_LANES_Y>(row_ring, in, (size_t)n, col, r0 + ty, r1, CR_LANES_Y, [&](int r, const float4(&x)[1]) {
+      const size_t o = (size_t)r * n + col;
+      const float zz[4] = {x[0].x, x[0].y, x[0].z, x[0].w};
+      float out[4];
 #pragma unroll
-      for (int k = 0; k < AF_ROWS; ++k) {
-        const int rk = r + k * CR_LANES_Y;
-        live[k] = rk < r1;
-        o[k] = (size_t)rk * n + col;
-        if (live[k]) z[k] = __ldg(reinterpret_cast<const float4 *>(Z + o[k]));
+      for (int j = 0; j < 4; ++j) out[j] = af_fire(AF, brn_norm(brn_hat(zz[j], c[j]), c[j]));
+      if (bern || dp.type == DLB_DROPOUT_NONE) {
+        // A dropped unit is 0 whatever the activation came to (a select, not a product).
+#pragma unroll
+        for (int j = 0; j < 4; ++j) out[j] = keep[j] == 0.f ? 0.f : out[j] * keep[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) out[j] = apply_dropout(out[j], dp, col + j, o + j);
       }
+      *reinterpret_cast<float4 *>(A + o) = make_float4(out[0], out[1], out[2], out[3]);
+      if (PLANES) {
+        sink_store4(sink, o, out, plane_scale);
+        track.row(sink, r, out);
+      } else {
 #pragma unroll
-      for (int k = 0; k < AF_ROWS; ++k) {
-        if (!live[k]) break;
-        const float zz[4] = {z[k].x, z[k].y, z[k].z, z[k].w};
-        float out[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float a = af_fire(af, brn_norm(brn_hat(zz[j], c[j]), c[j]));
-          // Kept units pass unchanged under plain Bernoulli, as the reference leaves them.
-          if (bern) out[j] = keep[j] == 1.f ? a : (keep[j] == 0.f ? 0.f : a * keep[j]);
-          else out[j] = apply_dropout(a, dp, col + j, o[k] + j);
-        }
-        *reinterpret_cast<float4 *>(A + o[k]) = make_float4(out[0], out[1], out[2], out[3]);
-        if (PLANES) {
-          sink_store4(sink, o[k], out, plane_scale);
-          track.row(sink, r + k * CR_LANES_Y, out);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) track.all = max(track.all, abs_bits(out[j]));
-          if (A_lo)
-            *reinterpret_cast<float4 *>(A_lo + o[k]) =
-                make_float4(tf32_lo(out[0]), tf32_lo(out[1]), tf32_lo(out[2]), tf32_lo(out[3]));
-        }
+        for (int j = 0; j < 4; ++j) track.all = max(track.all, abs_bits(out[j]));
+        if (A_lo)
+          *reinterpret_cast<float4 *>(A_lo + o) =
+              make_float4(tf32_lo(out[0]), tf32_lo(out[1]), tf32_lo(out[2]), tf32_lo(out[3]));
       }
-    }
+    });
   }
   if (PLANES) {
-    track.finish(sink, line_shared, tx, ty, CR_LANES_Y, blockIdx.x * CR_COLS, n, live_col);
+    ring_drain();
+    track.finish(sink, reinterpret_cast<unsigned *>(row_ring), tx, ty, CR_LANES_Y, blockIdx.x * CR_COLS, n, live_col, CR_LANES_X);
   } else if (sink.slot) {
     amax_commit(reinterpret_cast<unsigned *>(sink.slot) + SLOT_AMAX, track.all);
   }
 }
 
 template <bool PLANES>
-__global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
+__global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y, ROWS_PER_SM)
     brn_backward_apply_rows_kernel(float *__restrict__ delta, float *__restrict__ delta_lo,
                                    const float *__restrict__ Z, BrnPtrs u,
                                    const double *__restrict__ sums, float inv_rows, float rows_f,
                                    int rows, int n, int rows_per_chunk, PlaneSink sink) {
   pdl_enter();
-  __shared__ unsigned line_shared[PLANES ? CR_LANES_Y * CR_COLS : 1];
+  extern __shared__ float4 row_ring[];
   const int tx = threadIdx.x % CR_LANES_X, ty = threadIdx.x / CR_LANES_X;
   const int col = blockIdx.x * CR_COLS + tx * 4;
   const bool live_col = col < n;
@@ -593,62 +636,50 @@ __global__ void __launch_bounds__(CR_LANES_X *CR_LANES_Y)
   const float plane_scale = PLANES ? sink_scale(sink) : 1.f;
   if (live_col) {
     // Per-unit factors in the reference's grouping (bwp_mp.cpp L:1608-1621):
-    // r / sigma, N * sigma, d_sigma, d_mean / N.
-    float gamma[4], mean[4], r_over_sigma[4], n_sigma[4], d_sigma[4], d_mean_n[4];
+    // r / sigma, d_sigma / (N * sigma), d_mean / N.  The reference divides
+    // (z - mean) by N * sigma per element; the quotient d_sigma / (N sigma) is
+    // formed once per unit here (a division is a dozen instructions, and this
+    // kernel is bound by instruction issue), a difference of one rounding in a
+    // term that is summed.
+    float gamma[4], mean[4], r_over_sigma[4], d_sigma_n[4], d_mean_n[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const BrnCol c = u.at(col + j);
       gamma[j] = c.gamma;
       mean[j] = c.mean;
       r_over_sigma[j] = c.r / c.sigma;
-      n_sigma[j] = rows_f * c.sigma;
-      d_sigma[j] = (float)sums[3 * (size_t)n + col + j];
+      d_sigma_n[j] = (float)sums[3 * (size_t)n + col + j] / (rows_f * c.sigma);
       d_mean_n[j] = (float)sums[2 * (size_t)n + col + j] * inv_rows;
     }
-    // APPLY_ROWS rows per iteration, the loads of all of them first.
-    constexpr int APPLY_ROWS = 2;
-    for (int r = r0 + ty; r < r1; r += APPLY_ROWS * CR_LANES_Y) {
-      float4 e4[APPLY_ROWS], z4[APPLY_ROWS];
+    const float *in[2] = {delta, Z};
+    ring_walk<2, APPLY_DEPTH, CR_LANES_X * CR_LANES_Y>(row_ring, in, (size_t)n, col, r0 + ty, r1, CR_LANES_Y, [&](int r, const float4(&x)[2]) {
+      const size_t o = (size_t)r * n + col;
+      const float e[4] = {x[0].x, x[0].y, x[0].z, x[0].w}, z[4] = {x[1].x, x[1].y, x[1].z, x[1].w};
+      float t[4];
 #pragma unroll
-      for (int k = 0; k < APPLY_ROWS; ++k) {
-        const int rk = r + k * CR_LANES_Y;
-        if (rk < r1) {
-          const size_t o = (size_t)rk * n + col;
-          e4[k] = *reinterpret_cast<const float4 *>(delta + o);
-          z4[k] = __ldg(reinterpret_cast<const float4 *>(Z + o));
-        }
+      for (int j = 0; j < 4; ++j) {
+        float v = e[j] * gamma[j];
+        v *= r_over_sigma[j];
+        v += d_sigma_n[j] * (z[j] - mean[j]);
+        v += d_mean_n[j];
+        t[j] = v;
       }
+      *reinterpret_cast<float4 *>(delta + o) = make_float4(t[0], t[1], t[2], t[3]);
+      if (PLANES) {
+        sink_store4(sink, o, t, plane_scale);
+        track.row(sink, r, t);
+      } else {
 #pragma unroll
-      for (int k = 0; k < APPLY_ROWS; ++k) {
-        const int rk = r + k * CR_LANES_Y;
-        if (rk >= r1) break;
-        const size_t o = (size_t)rk * n + col;
-        const float e[4] = {e4[k].x, e4[k].y, e4[k].z, e4[k].w}, z[4] = {z4[k].x, z4[k].y, z4[k].z, z4[k].w};
-        float t[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float v = e[j] * gamma[j];
-          v *= r_over_sigma[j];
-          v += d_sigma[j] * ((z[j] - mean[j]) / n_sigma[j]);
-          v += d_mean_n[j];
-          t[j] = v;
-        }
-        *reinterpret_cast<float4 *>(delta + o) = make_float4(t[0], t[1], t[2], t[3]);
-        if (PLANES) {
-          sink_store4(sink, o, t, plane_scale);
-          track.row(sink, rk, t);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) track.all = max(track.all, abs_bits(t[j]));
-          if (delta_lo)
-            *reinterpret_cast<float4 *>(delta_lo + o) =
-                make_float4(tf32_lo(t[0]), tf32_lo(t[1]), tf32_lo(t[2]), tf32_lo(t[3]));
-        }
+        for (int j = 0; j < 4; ++j) track.all = max(track.all, abs_bits(t[j]));
+        if (delta_lo)
+          *reinterpret_cast<float4 *>(delta_lo + o) =
+              make_float4(tf32_lo(t[0]), tf32_lo(t[1]), tf32_lo(t[2]), tf32_lo(t[3]));
       }
-    }
+    });
   }
   if (PLANES) {
-    track.finish(sink, line_shared, tx, ty, CR_LANES_Y, blockIdx.x * CR_COLS, n, live_col);
+    ring_drain();
+    track.finish(sink, reinterpret_cast<unsigned *>(row_ring), tx, ty, CR_LANES_Y, blockIdx.x * CR_COLS, n, live_col, CR_LANES_X);
   } else if (sink.slot) {
     amax_commit(reinterpret_cast<unsigned *>(sink.slot) + SLOT_AMAX, track.all);
   }
@@ -844,17 +875,16 @@ dlb_status activation_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_u
     int chunks, rpc;
     rows_plan(ctx, rows, n_units, &chunks, &rpc);
     const dim3 grid(ceil_div(n_units, CR_COLS), chunks);
-    static const int in_flight = [] {
-      const char *e = getenv("DLB_AF_ROWS");
-      return e && atoi(e) == 2 ? 2 : 4;
-    }();
-#define DLB_AF_LAUNCH(PL, R)                                                                        \
-  DLB_LAUNCH_KERNEL(ctx, (activation_forward_rows_kernel<PL, R>), grid, CR_LANES_X * CR_LANES_Y, 0, Z, p, af, dp, A, A_lo, rows, n_units, rpc, sink)
-    if (sink.hi) { if (in_flight == 4) DLB_AF_LAUNCH(true, 4); else DLB_AF_LAUNCH(true, 2); }
-    else         { if (in_flight == 4) DLB_AF_LAUNCH(false, 4); else DLB_AF_LAUNCH(false, 2); }
-#undef DLB_AF_LAUNCH
-    DLB_LAUNCHED(ctx);
-    return DLB_OK;
+    constexpr size_t shared = ring_bytes(1, AF_DEPTH, CR_LANES_X * CR_LANES_Y);
+    return with_af(af, [&](auto AF) {
+      constexpr int F = decltype(AF)::value;
+      if (sink.hi)
+        DLB_LAUNCH_KERNEL(ctx, (activation_forward_rows_kernel<true, F>), grid, CR_LANES_X * CR_LANES_Y, shared, Z, p, dp, A, A_lo, rows, n_units, rpc, sink);
+      else
+        DLB_LAUNCH_KERNEL(ctx, (activation_forward_rows_kernel<false, F>), grid, CR_LANES_X * CR_LANES_Y, shared, Z, p, dp, A, A_lo, rows, n_units, rpc, sink);
+      DLB_LAUNCHED(ctx);
+      return DLB_OK;
+    });
   }
   DLB_REQUIRE(!sink.hi, "dlb_activation_forward: planes from a kernel that cannot write them");
   const size_t items = vec4 ? (size_t)rows * (n_units / 4) : (size_t)rows * n_units;
@@ -884,8 +914,10 @@ dlb_status dlb_activation_backward(dlb_ctx *ctx, float *dA, const float *Z, cons
     DLB_REQUIRE((n_units & 3) || ((reinterpret_cast<uintptr_t>(dA) | reinterpret_cast<uintptr_t>(Z) |
                                    reinterpret_cast<uintptr_t>(A)) & 15) == 0,
                 "dlb_activation_backward: tensors must be 16-byte aligned");
-    return column_reduce<4>(ctx, ActBackwardOp<true>{dA, Z, A, brn_ptrs(u), af, n_units}, rows,
-                            n_units, sums);
+    return with_af(af, [&](auto AF) {
+      return column_reduce<4>(ctx, ActBackwardOp<true, decltype(AF)::value>{dA, Z, A, brn_ptrs(u), af, n_units}, rows,
+                              n_units, sums);
+    });
   }
   const size_t total = (size_t)rows * n_units;
   const bool vec4 = (total % 4 == 0) && ((reinterpret_cast<uintptr_t>(dA) & 15) == 0) &&
@@ -916,10 +948,11 @@ dlb_status brn_backward_apply_impl(dlb_ctx *ctx, float *delta, float *delta_lo, 
     int chunks, rpc;
     rows_plan(ctx, rows, n_units, &chunks, &rpc);
     const dim3 rgrid(ceil_div(n_units, CR_COLS), chunks);
+    constexpr size_t shared = ring_bytes(2, APPLY_DEPTH, CR_LANES_X * CR_LANES_Y);
     if (sink.hi)
-      DLB_LAUNCH_KERNEL(ctx, brn_backward_apply_rows_kernel<true>, rgrid, CR_LANES_X * CR_LANES_Y, 0, delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc, sink);
+      DLB_LAUNCH_KERNEL(ctx, brn_backward_apply_rows_kernel<true>, rgrid, CR_LANES_X * CR_LANES_Y, shared, delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc, sink);
     else
-      DLB_LAUNCH_KERNEL(ctx, brn_backward_apply_rows_kernel<false>, rgrid, CR_LANES_X * CR_LANES_Y, 0, delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc, sink);
+      DLB_LAUNCH_KERNEL(ctx, brn_backward_apply_rows_kernel<false>, rgrid, CR_LANES_X * CR_LANES_Y, shared, delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, rpc, sink);
   } else {
     DLB_REQUIRE(!sink.hi, "dlb_brn_backward_apply: planes from a kernel that cannot write them");
     DLB_LAUNCH_KERNEL(ctx, brn_backward_apply_kernel<false>, grid, 256, 0, delta, delta_lo, Z, brn_ptrs(u), sums, 1.f / nf, nf, rows, n_units, amax);
@@ -1205,7 +1238,8 @@ extern "C" dlb_status dlb_brn_forward_sums_noalloc(const float *Z, int rows, int
     return DLB_ERR_INVALID;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  column_reduce_kernel<2, SumSqOp><<<dim3(col_blocks, chunks), CR_LANES_X * CR_LANES_Y, 0, s>>>(
+  column_reduce_kernel<2, SumSqOp><<<dim3(col_blocks, chunks), CR_LANES_X * CR_LANES_Y,
+                                     column_reduce_shared_bytes<2, SumSqOp>(), s>>>(
       SumSqOp{Z, n_units}, rows, n_units, rows_per_chunk, dev->partials);
   DLB_CUDA(cudaGetLastError());
   const int total = 2 * n_units;

@@ -14,14 +14,40 @@ namespace dlb {
 #define DLB_SELU_SCALE 1.0507009873554804934193349852946f
 #define DLB_LRELU_ALPHA 0.01f
 
+// e^x for x <= 0, the only range ELU and SELU ask for (anything else, NaN
+// included, is discarded by the caller's select).  2^(x log2(e)) with the
+// rounding error of the product x * log2(e) carried along and applied as a
+// first-order correction, so the result is as good as ex2.approx itself (2^-22
+// relative, the class of expf) at a third of expf's instructions: these
+// kernels are bound by instruction issue.  Arguments below -88 count as -88
+// (the result flushes to 0, as e^x does in fp32 there).
+__device__ __forceinline__ float exp_nonpositive(float x) {
+  const float L_HI = 1.4426950216293335f, L_LO = 1.925963033500011e-8f, LN2 = 0.69314718055994531f;
+  x = fmaxf(x, -88.f);
+  const float t = x * L_HI;
+  float e = __fmaf_rn(x, L_HI, -t);
+  e = __fmaf_rn(x, L_LO, e);
+  // volatile: the compiler then evaluates this for every element and selects,
+  // instead of branching around it per element (a divergent branch and its
+  // reconvergence cost more than the seven instructions they skip).
+  float p;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(t));
+  return __fmaf_rn(p * LN2, e, p);
+}
+
 // f(x).  ref: AF_FIRE, v1/ops/activations/functions.hpp L:86-108, L:124-219.
 __device__ __forceinline__ float af_fire(int af, float x) {
   switch (af) {
     case DLB_AF_RELU: return x < 0.f ? 0.f : x;
     case DLB_AF_LEAKY_RELU: return x < 0.f ? DLB_LRELU_ALPHA * x : x;
-    case DLB_AF_ELU: return x < 0.f ? 1.f * (expf(x) - 1.f) : x;
-    case DLB_AF_SELU:
-      return DLB_SELU_SCALE * (x <= 0.f ? DLB_SELU_ALPHA * expf(x) - DLB_SELU_ALPHA : x);
+    case DLB_AF_ELU: {
+      const float neg = 1.f * (exp_nonpositive(x) - 1.f);
+      return x < 0.f ? neg : x;
+    }
+    case DLB_AF_SELU: {
+      const float neg = DLB_SELU_ALPHA * exp_nonpositive(x) - DLB_SELU_ALPHA;
+      return DLB_SELU_SCALE * (x <= 0.f ? neg : x);
+    }
     case DLB_AF_ISRLU: return x < 0.f ? x * (1.f / sqrtf(1.f + 1.f * x * x)) : x;
     default: return x;  // LINEAR
   }

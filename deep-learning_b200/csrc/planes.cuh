@@ -112,20 +112,23 @@ struct LineTracker {
     }
   }
   // Called by every thread of the block (threads past the last column with
-  // live = false).  `shared` holds lanes_y * 128 words; tx in [0, 32), ty in
+  // live = false).  The block is lanes_x x lanes_y threads over lanes_x * 4
+  // columns; `shared` holds lanes_y * lanes_x * 4 words; tx in [0, lanes_x), ty in
   // [0, lanes_y), col0 the block's first column, n the number of columns.
   __device__ __forceinline__ void finish(const PlaneSink &k, unsigned *shared, int tx, int ty, int lanes_y,
-                                         int col0, int n, bool live) {
+                                         int col0, int n, bool live, int lanes_x = 32) {
     if (k.slot) amax_commit(reinterpret_cast<unsigned *>(k.slot) + SLOT_AMAX, live ? all : 0u);
     if (!k.colmax) return;
+    const int cols = lanes_x * 4;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) shared[ty * 128 + tx * 4 + j] = live ? cm[j] : 0u;
+    for (int j = 0; j < 4; ++j) shared[ty * cols + tx * 4 + j] = live ? cm[j] : 0u;
     __syncthreads();
-    const int t = ty * 32 + tx;
-    if (t < 128 && col0 + t < n) {
-      unsigned m = 0u;
-      for (int y = 0; y < lanes_y; ++y) m = max(m, shared[y * 128 + t]);
-      if (m) atomicMax(k.colmax + col0 + t, m);
+    for (int t = ty * lanes_x + tx; t < cols; t += lanes_x * lanes_y) {
+      if (col0 + t < n) {
+        unsigned m = 0u;
+        for (int y = 0; y < lanes_y; ++y) m = max(m, shared[y * cols + t]);
+        if (m) atomicMax(k.colmax + col0 + t, m);
+      }
     }
   }
 };
