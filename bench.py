@@ -20,6 +20,10 @@ all-reduced over NCCL so that every rank holds the full-batch result.
           targets (started one step ahead, so that it runs under the previous
           step's kernels) and the device-to-host read of its loss are inside
           the timed region.
+`e2e_dropin` the same step as the reference's own loop calls it: arrays of host
+          row pointers (pageable memory) through the step entry points
+          forward_pass / compute_error / backward_pass / update_derivatives /
+          merge_derivatives / update_weights and a blocking loss read per step.
 `roofline` the tcgen05 GEMM kernel: algorithmic FLOPs (2*M*N*K per launch, not
           multiplied by the three tensor-core products per FLOP) over the summed
           event-timed launch durations inside the timed region.
@@ -416,6 +420,43 @@ def run_ours(args, rank, local_rank, world):
     e2e_s, loss = end_to_end(1, args.steps)
     model.set_loss_lag(0)
 
+    # ---- the reference's own loop over the step entry points --------------
+    # What Driver::train_mp does with the library behind Model: arrays of host
+    # row pointers into pageable memory go into forward_pass / compute_error,
+    # then backward_pass, update_derivatives, merge, update_weights, and the loss
+    # is read after the update.  No staging ahead, no lag: the boundary as the
+    # reference calls it.
+    def dropin_loop(steps):
+        import ctypes as C
+
+        L, h = model.L, model.h
+        Xr = (C.c_void_p * rows)(*[Xh.ctypes.data + i * Xh.strides[0] for i in range(rows)])
+        Yr = (C.c_void_p * rows)(*[Yh.ctypes.data + i * Yh.strides[0] for i in range(rows)])
+        g = rows * world
+
+        def one():
+            dlb200.check(L.dlb_model_reset_loss(h), "reset_loss")
+            dlb200.check(L.dlb_model_forward_pass(h, rows, Xr), "forward_pass")
+            dlb200.check(L.dlb_model_compute_error(h, rows, Yr), "compute_error")
+            dlb200.check(L.dlb_model_backward_pass(h, rows), "backward_pass")
+            dlb200.check(L.dlb_model_update_derivatives(h, rows), "update_derivatives")
+            dlb200.check(L.dlb_model_merge_derivatives(h), "merge_derivatives")
+            dlb200.check(L.dlb_model_update_weights(h, g, g), "update_weights")
+            return model.get_loss()
+
+        for _ in range(2):
+            one()
+        ctx.sync()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            last = one()
+        ctx.sync()
+        barrier()
+        return max_over_ranks(time.perf_counter() - t0), last
+
+    dropin_s, dropin_loss = dropin_loop(args.steps)
+
     # ---- strong scaling: the 4096-row batch itself sharded over the GPUs -----
     strong = None
     if world > 1 and args.workload == "deep_brn_mlp":
@@ -462,6 +503,12 @@ def run_ours(args, rank, local_rank, world):
                              "the last step's before the clock stops",
                 "in_order": {"value": rows * world * args.steps / in_order_s, "ms_per_step": in_order_s / args.steps * 1e3,
                              "what": "each step waits for its own loss after enqueuing its update"}},
+        "e2e_dropin": {"value": rows * world * args.steps / dropin_s, "unit": UNIT, "ms_per_step": dropin_s / args.steps * 1e3,
+                       "h2d_bytes_per_step": int(Xh.nbytes + Yh.nbytes), "d2h_bytes_per_step": 8, "last_loss": dropin_loss,
+                       "what": "the reference's own loop (Driver::train_mp) over the step entry points it would bind: "
+                               "host row-pointer arrays into pageable memory through dlb_model_forward_pass / "
+                               "compute_error, then backward_pass, update_derivatives, merge_derivatives, "
+                               "update_weights and a blocking get_loss every step; nothing staged ahead"},
         "gpu_launches": launches,
         "range_guard": {"operand_tensors_flagged": guard[0], "products_on_fp32_fallback": guard[1],
                         "note": "3xFP16 form: products whose operand planes the range guard rejected (expected 0)"},

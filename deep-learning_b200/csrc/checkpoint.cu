@@ -271,6 +271,7 @@ struct Reader {
 struct LoadedLayer {
   int type = 0, cls = 0, af = 0, norm = 0, dropout = 0;
   double dropout_value = 0;
+  double rec_lower = 0, rec_upper = 0;  // bounds of the recurrent weights
   size_t units = 0, depth = 0;
   std::vector<float> scale, shift, mean_avg, sigma_avg;  // norm: [units], [units], [T*units] x 2
   std::vector<std::pair<size_t, float>> weights;         // (index in the flat vector, value)
@@ -427,8 +428,8 @@ dlb_status dlb_model_save_params(dlb_model *m, const char *path) {
     out += std::string("    use_tied_parameter 0") + CRLF;
     out += std::string("    k_sparsity 0") + CRLF;
     out += std::string("    alpha_sparsity 1") + CRLF;
-    out += "    constraint_recurrent_weight_lower_bound " + num(indrnn(l) ? -bound : 0.f) + CRLF;
-    out += "    constraint_recurrent_weight_upper_bound " + num(indrnn(l) ? bound : 0.f) + CRLF;
+    out += "    constraint_recurrent_weight_lower_bound " + num(indrnn(l) ? (l.rec_custom ? l.rec_lower : -bound) : 0.f) + CRLF;
+    out += "    constraint_recurrent_weight_upper_bound " + num(indrnn(l) ? (l.rec_custom ? l.rec_upper : bound) : 0.f) + CRLF;
     out += "    number_neuron_units " + num(l.units) + CRLF;
     neuron_lines(out, m, i, h, base);
     if (indrnn(l)) {
@@ -612,8 +613,8 @@ dlb_status dlb_model_load(dlb_model *m, const char *path_params, const char *pat
     DLB_TRY(r.count("use_tied_parameter", &v));
     DLB_TRY(r.count("k_sparsity", &v));
     DLB_TRY(r.real("alpha_sparsity", &d));
-    DLB_TRY(r.real("constraint_recurrent_weight_lower_bound", &d));
-    DLB_TRY(r.real("constraint_recurrent_weight_upper_bound", &d));
+    DLB_TRY(r.real("constraint_recurrent_weight_lower_bound", &l.rec_lower));
+    DLB_TRY(r.real("constraint_recurrent_weight_upper_bound", &l.rec_upper));
     DLB_TRY(r.count("number_neuron_units", &l.units));
     DLB_TRY(read_neurons(r, &l));
     if (l.type == DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT) {
@@ -724,6 +725,11 @@ dlb_status dlb_model_load(dlb_model *m, const char *path_params, const char *pat
   DLB_TRY(s.real("use_clip_gradient", &use_clip));
   DLB_TRY(s.real("clip_gradient", &clip));
   DLB_TRY(dlb_model_set_clip_gradient(m, use_clip != 0.0, (float)clip));
+  // Bounds of the recurrent weights, now that the norm their default derives
+  // from is known: the file's values, which stay the default when they equal it.
+  for (size_t i = 1; i + 1 < n_layers; ++i)
+    if (L[i].type == DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT)
+      DLB_TRY(dlb_model_set_constraint_recurrent_weight(m, i, (float)L[i].rec_lower, (float)L[i].rec_upper));
   DLB_TRY(s.expect("|END| TRAINING PARAMETERS |END|"));
   DLB_TRY(s.expect("|===| REGULARIZATION PARAMETERS |===|"));
   for (const char *k : {"regularization__max_norm_constraints", "regularization__l1", "regularization__l2",

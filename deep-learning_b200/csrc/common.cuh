@@ -205,10 +205,14 @@ struct GemmOperand {
   // the fp32 tensors on the CUDA cores instead.
   const unsigned *guard = nullptr;
 };
+struct FusedEpilogue;
 struct GemmEpilogue {
   const float *bias = nullptr;   // per-n bias added to every row
   float *colsum = nullptr;       // per-n sum over m of C (db), written/accumulated
   int accumulate = 0;            // C += result
+  // Work of the kernel that would follow the product, done on the tile while the
+  // drain warps hold it (2-CTA fp16-plane kernel only: ask gemm_fused_supported).
+  const FusedEpilogue *fused = nullptr;
 };
 
 dlb_status gemm(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C,
@@ -252,6 +256,34 @@ struct PlaneSink {
   int predicted = 0;                       // planes use the scale predicted from the previous split
   unsigned long long *guard = nullptr;     // counter of tensors the range guard flagged
 };
+// Elementwise work fused into the store of a product C[M, N] (all tensors dense,
+// row pitch N).
+//   EPI_ACTIVATION: C receives the sums (+ bias), `out` = dropout(f(C)): the
+//     forward of a layer without normalization (Forward_Pass__FC_AF__OpenMP and
+//     the dropout forwards, v1/learner/fwp_mp.cpp L:4741-4770, L:4809-4985).
+//   EPI_DERIVATIVE: C receives product * f'(z, a): the error of the layer below
+//     a dX product when that layer has no normalization
+//     (Backward_Pass__FC__DF__OpenMP, v1/learner/bwp_mp.cpp L:1150-1186).
+// `sink`, when it has planes, receives the fp16 planes and range statistics of
+// the produced operand (`out`, or C) in the same pass.
+enum { EPI_PLAIN = 0, EPI_ACTIVATION = 1, EPI_DERIVATIVE = 2 };
+struct FusedEpilogue {
+  int mode = EPI_PLAIN;
+  int af = 0;
+  const uint8_t *mask = nullptr;  // EPI_ACTIVATION: Bernoulli flags per unit, or null
+  float keep_scale = 1.f;         //   factor of a kept unit (1, or 1 / keep probability)
+  const float *noise = nullptr;   //   UOut draws [M, N], or null
+  float *out = nullptr;           //   the activation [M, N]
+  const float *z = nullptr;       // EPI_DERIVATIVE: pre-activation and activation [M, N] of the
+  const float *a = nullptr;       //   layer whose error C is
+  PlaneSink sink;
+};
+bool gemm_pair_enabled();  // the 2-CTA kernel is on (DLB_GEMM_PAIR)
+int gemm_pair_chunk();     // its chunk of k-blocks per accumulator drain
+// Whether gemm() would run this product on the kernel that takes a fused epilogue.
+bool gemm_fused_supported(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, const float *C, long long ldc,
+                          int M, int N, int K);
+
 // One split of a tensor into its plane buffer.  planes_open registers the
 // buffer and decides the form: `fused` (the producing kernel writes planes and
 // statistics itself, with the scale predicted from the buffer's previous split)

@@ -86,9 +86,26 @@ static dlb_status gemm_tensor_core(dlb_ctx *ctx, const GemmOperand &A, const Gem
   return st;
 }
 
+// The fused epilogue exists in the 2-CTA fp16-plane kernel at its default
+// chunk, for K-major A, with both operands' planes kept by the caller and a
+// dense output.
+bool gemm_fused_supported(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, const float *C, long long ldc,
+                          int M, int N, int K) {
+  const bool big = (long long)M * N >= 256 * 256 && K >= 32;
+  if (!(ctx->use_tensor_core && ctx->tensor_core_ok && big && ctx->gemm_kind == DLB_GEMM_F16X3)) return false;
+  if (!gemm_pair_enabled() || gemm_pair_chunk() != 8 || A.stride_k != 1 || ldc != N) return false;
+  if (!gemm_f16_supported(A, B, C, ldc, M, N, K)) return false;
+  GemmOperand a = A, b = B;
+  return (a.h_hi || planes_lookup(ctx, a.lo, &a)) && (b.h_hi || planes_lookup(ctx, b.lo, &b));
+}
+
 dlb_status gemm(dlb_ctx *ctx, const GemmOperand &A_in, const GemmOperand &B_in, float *C,
                 long long ldc, int M, int N, int K, const GemmEpilogue &ep) {
   GemmOperand A = A_in, B = B_in;
+  if (ep.fused && !gemm_fused_supported(ctx, A, B, C, ldc, M, N, K)) {
+    set_error("gemm: fused epilogue asked for a product outside gemm_fused_supported");
+    return DLB_ERR_UNSUPPORTED;
+  }
   // The tensor-core tile is 128 x 256; below that the CUDA-core kernel is
   // used, as it is for layouts TMA cannot address.
   const bool big = (long long)M * N >= 128 * 64 && K >= 32;
@@ -523,6 +540,86 @@ dlb_status dlb_fc_backward_input(dlb_ctx *ctx, const float *delta, const float *
   GemmOperand B{W, W_lo, 1, n_in};           // (n=i, k=o): W[o,i]
   GemmEpilogue ep;
   return gemm(ctx, A, B, dX, n_in, rows, n_in, n_out, ep);
+}
+
+// Dropout of the fused forward: what the epilogue can apply (flags per unit, a
+// factor, UOut draws).
+static bool epilogue_dropout(const dlb_dropout_desc *d, FusedEpilogue *fe) {
+  if (!d || d->type == DLB_DROPOUT_NONE) return true;
+  switch (d->type) {
+    case DLB_DROPOUT_BERNOULLI:
+      if (!d->mask) return false;
+      fe->mask = d->mask;
+      return true;
+    case DLB_DROPOUT_BERNOULLI_INVERTED:
+      if (!d->mask || !(d->value > 0.f)) return false;
+      fe->mask = d->mask;
+      fe->keep_scale = 1.f / d->value;
+      return true;
+    case DLB_DROPOUT_UOUT:
+      if (!d->noise) return false;
+      fe->noise = d->noise;
+      return true;
+    default: return false;
+  }
+}
+
+dlb_status dlb_fc_forward_activation(dlb_ctx *ctx, const float *X, const float *X_lo, const float *W,
+                                     const float *W_lo, const float *bias, float *Z, int af,
+                                     const dlb_dropout_desc *dropout, float *A_out, float *A_lo, int rows,
+                                     int n_in, int n_out) {
+  DLB_REQUIRE(ctx && X && W && Z && A_out && rows > 0 && n_in > 0 && n_out > 0, "dlb_fc_forward_activation");
+  GemmOperand A{X, X_lo, n_in, 1};
+  GemmOperand B{W, W_lo, n_in, 1};
+  FusedEpilogue fe;
+  fe.mode = EPI_ACTIVATION;
+  fe.af = af;
+  fe.out = A_out;
+  if (A_lo && epilogue_dropout(dropout, &fe) && gemm_fused_supported(ctx, A, B, Z, n_out, rows, n_out, n_in)) {
+    PlaneJob job;
+    DLB_TRY(planes_open(ctx, A_out, A_lo, (size_t)rows * n_out, rows, n_out, true, &job));
+    if (job.fused) {
+      fe.sink = job.sink;
+      GemmEpilogue ep;
+      ep.bias = bias;
+      ep.fused = &fe;
+      DLB_TRY(gemm(ctx, A, B, Z, n_out, rows, n_out, n_in, ep));
+      return planes_close(ctx, job);
+    }
+    // No scale to predict from yet (the buffer's first split): the two kernels below.
+  }
+  DLB_TRY(dlb_fc_forward(ctx, X, X_lo, W, W_lo, bias, Z, rows, n_in, n_out));
+  return dlb_activation_forward(ctx, Z, nullptr, af, dropout, A_out, A_lo, rows, n_out);
+}
+
+dlb_status dlb_fc_backward_input_derivative(dlb_ctx *ctx, const float *delta, const float *delta_lo,
+                                            const float *W, const float *W_lo, const float *Z_below,
+                                            const float *A_below, int af_below, float *dX, float *dX_lo,
+                                            int rows, int n_in, int n_out) {
+  DLB_REQUIRE(ctx && delta && W && Z_below && A_below && dX && rows > 0 && n_in > 0 && n_out > 0,
+              "dlb_fc_backward_input_derivative");
+  GemmOperand A{delta, delta_lo, n_out, 1};
+  GemmOperand B{W, W_lo, 1, n_in};
+  if (dX_lo && gemm_fused_supported(ctx, A, B, dX, n_in, rows, n_in, n_out)) {
+    PlaneJob job;
+    DLB_TRY(planes_open(ctx, dX, dX_lo, (size_t)rows * n_in, rows, n_in, true, &job));
+    if (job.fused) {
+      FusedEpilogue fe;
+      fe.mode = EPI_DERIVATIVE;
+      fe.af = af_below;
+      fe.z = Z_below;
+      fe.a = A_below;
+      fe.sink = job.sink;
+      GemmEpilogue ep;
+      ep.fused = &fe;
+      DLB_TRY(gemm(ctx, A, B, dX, n_in, rows, n_in, n_out, ep));
+      return planes_close(ctx, job);
+    }
+  }
+  DLB_TRY(dlb_fc_backward_input(ctx, delta, delta_lo, W, W_lo, dX, rows, n_in, n_out));
+  DLB_TRY(dlb_activation_backward(ctx, dX, Z_below, A_below, nullptr, af_below, rows, n_in, nullptr));
+  if (dX_lo) DLB_TRY(dlb_split_planes_2d(ctx, dX, dX_lo, rows, n_in));
+  return DLB_OK;
 }
 
 dlb_status dlb_fc_weight_gradient(dlb_ctx *ctx, const float *delta, const float *delta_lo,

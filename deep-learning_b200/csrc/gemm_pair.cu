@@ -124,7 +124,7 @@ __device__ __forceinline__ PairItem pair_item(int item, int tiles_n, int whole_t
   return w;
 }
 
-template <int STAGES, int CHUNK_KB, bool A_MN, bool B_MN>
+template <int STAGES, int CHUNK_KB, bool A_MN, bool B_MN, bool FUSED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     gemm_x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                         const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
@@ -132,7 +132,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
                         const float *__restrict__ bias, int accumulate, int tiles_n, int whole_tiles,
                         int parts, int total_items, const float *__restrict__ scale_a,
                         const float *__restrict__ scale_b, int *status, const unsigned *guard_a,
-                        const unsigned *guard_b, SimtOperands fp32, unsigned long long *fallbacks) {
+                        const unsigned *guard_b, SimtOperands fp32, unsigned long long *fallbacks,
+                        const FusedEpilogue fe) {
   pdl_enter();
   using P = PairPlan<STAGES>;
   // Range guard: the planes of a flagged operand do not stand for its tensor.
@@ -143,7 +144,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
   if ((guard_a && *guard_a) || (guard_b && *guard_b)) {
     extern __shared__ __align__(16) uint8_t guard_smem[];
     if (fallbacks && blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(fallbacks, 1ull);
-    gemm_simt_guard_path(fp32, C, ldc, M, N, K, bias, accumulate, reinterpret_cast<float *>(guard_smem));
+    gemm_simt_guard_path(fp32, C, ldc, M, N, K, bias, accumulate, reinterpret_cast<float *>(guard_smem),
+                         FUSED ? &fe : nullptr);
     return;
   }
   constexpr int MN_W = 64;  // halfs of one 128-byte column of an MN-major tile
@@ -286,6 +288,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     constexpr int HALF = PN / 2;
     float *tile = reinterpret_cast<float *>(smem + P::EPI_OFFSET) + (warp - 2) * 32 * 33;
     const float out_a = 1.f / __ldg(scale_a), out_b = 1.f / __ldg(scale_b);
+    const float plane_scale = FUSED && fe.sink.hi ? sink_scale(fe.sink) : 1.f;
     const uint32_t lead_acc_empty0 = map_to_cta(acc_empty0, 0);
     float acc[HALF];
     bool ok = true;
@@ -325,7 +328,30 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
           const int col = col0 + lane;
           if (col < N) {
             const float b = (bias && w.piece == 0) ? __ldg(bias + col) : 0.f;
-            if (w.split) {
+            if (FUSED) {
+              // Launches with a fused epilogue have no split tiles and do not
+              // accumulate.  The lanes of the warp that are here hold 32
+              // consecutive columns of one row at a time.
+              const float keep = epilogue_keep(fe, col);
+              unsigned col_max = 0u;
+#pragma unroll 2
+              for (int r = 0; r < 32; ++r) {
+                const int row = row_base + r;
+                if (row < M) {
+                  const size_t at = (size_t)row * N + col;
+                  const float x = epilogue_store(fe, C + (long long)row * ldc + col, at, tile[r * 33 + lane] + b, keep);
+                  if (fe.sink.hi) epilogue_planes(fe, at, x, plane_scale);
+                  const unsigned bits = abs_bits(x);
+                  col_max = max(col_max, bits);
+                  if (fe.sink.rowmax) {
+                    const unsigned row_max = __reduce_max_sync(__activemask(), bits);
+                    if (lane == 0 && row_max) atomicMax(fe.sink.rowmax + row, row_max);
+                  }
+                }
+              }
+              if (fe.sink.colmax && col_max) atomicMax(fe.sink.colmax + col, col_max);
+              if (fe.sink.slot) amax_commit(reinterpret_cast<unsigned *>(fe.sink.slot) + SLOT_AMAX, col_max);
+            } else if (w.split) {
 #pragma unroll 4
               for (int r = 0; r < 32; ++r) {
                 const int row = row_base + r;
@@ -381,7 +407,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 // ---------------------------------------------------------------------------
 namespace {
 
-template <int STAGES, int CHUNK_KB, bool A_MN, bool B_MN>
+template <int STAGES, int CHUNK_KB, bool A_MN, bool B_MN, bool FUSED = false>
 dlb_status launch_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C, long long ldc,
                        int M, int N, int K, const GemmEpilogue &ep) {
   using P = PairPlan<STAGES>;
@@ -395,7 +421,7 @@ dlb_status launch_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B,
     set_error("gemm_pair: cuTensorMapEncodeTiled rejected an operand");
     return DLB_ERR_CUDA;
   }
-  auto kernel = gemm_x3_pair_kernel<STAGES, CHUNK_KB, A_MN, B_MN>;
+  auto kernel = gemm_x3_pair_kernel<STAGES, CHUNK_KB, A_MN, B_MN, FUSED>;
   static bool attr_set[MAX_DEVICES] = {};  // the attribute belongs to the (function, device) pair
   if (!attr_set[ctx->device]) {
     DLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::TOTAL));
@@ -416,7 +442,7 @@ dlb_status launch_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B,
   const int total_kb = ceil_div(K, PBK);
   const int rest = tiles % lanes;
   int parts = 1;
-  if (!ep.accumulate && rest > 0) {
+  if (!ep.accumulate && rest > 0 && !FUSED) {  // a fused epilogue needs the whole sum of an element in one place
     // Twelfths of a round; a cut must save at least a twelfth per extra piece.
     int best = 12;
     constexpr int MAX_PARTS = 2;
@@ -437,7 +463,7 @@ dlb_status launch_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B,
                                (size_t)N * sizeof(float), (size_t)(M - first_row), ctx->stream));
   }
   const int items = whole_tiles + parts * split_tiles;
-  DLB_LAUNCH_KERNEL(ctx, kernel, 2 * min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, parts, items, A.scale, B.scale, ctx->d_status, A.guard, B.guard, SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr);
+  DLB_LAUNCH_KERNEL(ctx, kernel, 2 * min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, parts, items, A.scale, B.scale, ctx->d_status, A.guard, B.guard, SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr, FUSED ? *ep.fused : FusedEpilogue{});
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
@@ -453,14 +479,29 @@ bool gemm_pair_enabled() {
   return on;
 }
 
-dlb_status gemm_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C, long long ldc,
-                     int M, int N, int K, const GemmEpilogue &ep) {
-  const bool a_mn = !(A.stride_k == 1);
-  const bool b_mn = !(B.stride_k == 1);
+// Chunk of k-blocks per accumulator drain: 8 unless DLB_GEMM_PAIR_CHUNK says 4 or 16.
+int gemm_pair_chunk() {
   static const int chunk = [] {
     const char *e = getenv("DLB_GEMM_PAIR_CHUNK");
     return e ? atoi(e) : 8;
   }();
+  return chunk;
+}
+
+dlb_status gemm_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C, long long ldc,
+                     int M, int N, int K, const GemmEpilogue &ep) {
+  const bool a_mn = !(A.stride_k == 1);
+  const bool b_mn = !(B.stride_k == 1);
+  const int chunk = gemm_pair_chunk();
+  if (ep.fused && ep.fused->mode != EPI_PLAIN) {
+    // Instantiated for the two layouts that carry one (forward: both operands
+    // K-major; input gradient: weights MN-major) at the default chunk.
+    if (chunk == 8 && !ep.accumulate && !a_mn)
+      return b_mn ? launch_pair<6, 8, false, true, true>(ctx, A, B, C, ldc, M, N, K, ep)
+                  : launch_pair<6, 8, false, false, true>(ctx, A, B, C, ldc, M, N, K, ep);
+    set_error("gemm_pair: no fused epilogue for this layout");
+    return DLB_ERR_UNSUPPORTED;
+  }
 #define DLB_PAIR(CH)                                                                                  \
   if (chunk == (CH)) {                                                                                \
     if (!a_mn && !b_mn) return launch_pair<6, CH, false, false>(ctx, A, B, C, ldc, M, N, K, ep);      \

@@ -9,6 +9,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "epilogue.cuh"
 
 namespace dlb {
 
@@ -23,10 +24,13 @@ struct SimtOperands {
 };
 
 // `shared` holds SIMT_SMEM_FLOATS floats.  first_tile / tile_stride: the block's
-// share of the tiles.
+// share of the tiles.  fe: the fused epilogue of the launch, or null.
 __device__ __forceinline__ void gemm_simt_body(const SimtOperands &o, float *__restrict__ C, long long ldc, int M,
                                                int N, int K, const float *__restrict__ bias, int accumulate,
-                                               float *shared, int first_tile, int tile_stride) {
+                                               float *shared, int first_tile, int tile_stride,
+                                               const FusedEpilogue *fe = nullptr) {
+  const bool fused = fe && fe->mode != EPI_PLAIN;
+  const float plane_scale = fused && fe->sink.hi ? sink_scale(fe->sink) : 1.f;
   float(*As)[ST_M + 4] = reinterpret_cast<float(*)[ST_M + 4]>(shared);
   float(*Bs)[ST_N + 4] = reinterpret_cast<float(*)[ST_N + 4]>(shared + ST_K * (ST_M + 4));
   const int tid = threadIdx.x;
@@ -82,7 +86,8 @@ __device__ __forceinline__ void gemm_simt_body(const SimtOperands &o, float *__r
           float v = acc[i][j];
           if (bias) v += bias[gn];
           float *c = C + (long long)gm * ldc + gn;
-          *c = accumulate ? *c + v : v;
+          if (fused) epilogue_element(*fe, c, gm, gn, N, v, plane_scale);
+          else *c = accumulate ? *c + v : v;
         }
       }
     }
@@ -92,8 +97,9 @@ __device__ __forceinline__ void gemm_simt_body(const SimtOperands &o, float *__r
 // The same as a call of its own, so that the registers of this rarely taken
 // path are not part of the allocation of the tensor-core kernels' main path.
 static __device__ __noinline__ void gemm_simt_guard_path(SimtOperands o, float *C, long long ldc, int M, int N,
-                                                         int K, const float *bias, int accumulate, float *shared) {
-  gemm_simt_body(o, C, ldc, M, N, K, bias, accumulate, shared, blockIdx.x, gridDim.x);
+                                                         int K, const float *bias, int accumulate, float *shared,
+                                                         const FusedEpilogue *fe = nullptr) {
+  gemm_simt_body(o, C, ldc, M, N, K, bias, accumulate, shared, blockIdx.x, gridDim.x, fe);
 }
 
 }  // namespace dlb

@@ -599,7 +599,15 @@ dlb_status gemm_tcgen05(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B
       return DLB_ERR_UNSUPPORTED;
     }
     if (gemm_pair_enabled() && (long long)M * N >= 256 * 256) return gemm_pair(ctx, A, B, C, ldc, M, N, K, ep);
+    if (ep.fused) {
+      set_error("gemm_tcgen05: a fused epilogue runs on the 2-CTA kernel only");
+      return DLB_ERR_UNSUPPORTED;
+    }
     return launch_majors<2>(ctx, A, B, C, ldc, M, N, K, ep);
+  }
+  if (ep.fused) {
+    set_error("gemm_tcgen05: a fused epilogue needs fp16 planes");
+    return DLB_ERR_UNSUPPORTED;
   }
   if (!gemm_tcgen05_supported(A, B, C, ldc, M, N, K) || !A.lo || !B.lo) {
     set_error("gemm_tcgen05: operand layout outside the TMA path");

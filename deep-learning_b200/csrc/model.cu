@@ -17,6 +17,7 @@
 
 #include <random>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "common.cuh"
@@ -44,6 +45,23 @@ float d_max_of(const dlb_model *m, const LayerRT &l) {
 float indrnn_magnitude(const dlb_model *m) { return fminf(fmaxf(m->clip_gradient, 2.f), 10.f); }
 
 bool is_indrnn(const LayerRT &l) { return l.type == DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT; }
+
+// Bounds the recurrent weights of an IndRNN layer are clamped to after an
+// update: the ones set by hand, else +-mag^(1/T) with mag = clip(clip_gradient,
+// 2, 10) = 2 with the reference's default clip_gradient of 1; every activation of
+// the supported set is in a class that takes this default
+// (Compute__Regularization__Constraint_Recurrent_Weight__Default,
+// v1/ops/constraints/constraint.cpp L:64-95).
+void recurrent_bounds(const dlb_model *m, const LayerRT &l, float *lo, float *hi) {
+  if (l.rec_custom) {
+    *lo = l.rec_lower;
+    *hi = l.rec_upper;
+    return;
+  }
+  const float bound = powf(indrnn_magnitude(m), 1.f / (float)m->seq_w);
+  *lo = -bound;
+  *hi = bound;
+}
 
 // Models that run the [T, rows, n] path: more than one time step, or an IndRNN
 // layer (whose recurrence is then empty at T = 1).
@@ -610,6 +628,18 @@ dlb_status forward_layers(dlb_model *m, size_t rows) {
     const bool last = i + 1 == m->layers.size();
     // The bias enters only where there is no normalisation (model.hpp L:708).
     const float *bias = norm ? nullptr : m->params + l.first_bias;
+    if (!norm && !last && !inference && l.af != DLB_AF_SOFTMAX) {
+      // A hidden layer without normalization: bias, activation and dropout ride
+      // in the product's epilogue (where the kernel that runs has one).
+      DLB_TRY(uout_ready(m, l, i, B));
+      dlb_dropout_desc dp{l.dropout, l.dropout_value, l.mask, l.uout};
+      DLB_TRY(dlb_fc_forward_activation(m->ctx, X, X_lo, m->params + l.first_conn, m->params_lo + l.first_conn,
+                                        bias, l.Z, l.af, l.dropout != DLB_DROPOUT_NONE ? &dp : nullptr, l.A,
+                                        l.A_lo, B, I, H));
+      X = l.A;
+      X_lo = l.A_lo;
+      continue;
+    }
     DLB_TRY(dlb_fc_forward(m->ctx, X, X_lo, m->params + l.first_conn, m->params_lo + l.first_conn,
                            bias, l.Z, B, I, H));
     dlb_brn_unit_arrays u;
@@ -636,8 +666,23 @@ dlb_status forward_layers(dlb_model *m, size_t rows) {
   return DLB_OK;
 }
 
-dlb_status stage_rows(dlb_model *m, float **stage, size_t *stage_elems, size_t rows, size_t width,
+// Host rows (the reference's array of row pointers, pageable memory) into a
+// device tensor: gathered into a page-locked staging buffer by a few host
+// threads, piece by piece, each piece's copy to the device running while the
+// next one is gathered.  The copies run on the copy stream, so that the
+// targets of a step cross while its forward pass computes; the compute stream
+// waits for them where it needs them (rows_staged).  which: 0 inputs, 1 targets.
+dlb_status stage_rows(dlb_model *m, int which, float **stage, size_t *stage_elems, size_t rows, size_t width,
                       const float *const *row_ptrs, float *dev) {
+  DLB_CUDA(cudaSetDevice(m->ctx->device));
+  if (!m->copy_stream) DLB_CUDA(cudaStreamCreateWithFlags(&m->copy_stream, cudaStreamNonBlocking));
+  if (!m->rows_copied[which]) {
+    DLB_CUDA(cudaEventCreateWithFlags(&m->rows_copied[which], cudaEventDisableTiming));
+    DLB_CUDA(cudaEventCreateWithFlags(&m->rows_consumed[which], cudaEventDisableTiming));
+  }
+  // The previous copy out of this staging buffer must have finished, also
+  // before the buffer is replaced by a larger one.
+  if (m->rows_in_flight[which]) DLB_CUDA(cudaEventSynchronize(m->rows_copied[which]));
   const size_t need = rows * width;
   if (need > *stage_elems) {
     if (*stage) DLB_TRY(dlb_host_free(*stage));
@@ -645,10 +690,39 @@ dlb_status stage_rows(dlb_model *m, float **stage, size_t *stage_elems, size_t r
     DLB_TRY(dlb_host_alloc(reinterpret_cast<void **>(stage), need * sizeof(float)));
     *stage_elems = need;
   }
-  // The previous step's copy out of this staging buffer must have finished.
-  DLB_CUDA(cudaStreamSynchronize(m->ctx->stream));
-  for (size_t r = 0; r < rows; ++r) memcpy(*stage + r * width, row_ptrs[r], width * sizeof(float));
-  return dlb_memcpy_h2d(m->ctx, dev, *stage, need * sizeof(float));
+  // The kernels that read the device tensor last must be past it.
+  if (m->rows_in_flight[which]) DLB_CUDA(cudaStreamWaitEvent(m->copy_stream, m->rows_consumed[which], 0));
+  else DLB_CUDA(cudaStreamSynchronize(m->ctx->stream));
+  constexpr size_t PIECE_BYTES = 4u << 20;
+  const size_t piece_rows = std::max<size_t>(1, PIECE_BYTES / (width * sizeof(float)));
+  const unsigned hw = std::thread::hardware_concurrency();
+  const size_t workers = need * sizeof(float) < (1u << 20) ? 1 : std::min<size_t>(8, hw ? hw : 1);
+  for (size_t r0 = 0; r0 < rows; r0 += piece_rows) {
+    const size_t r1 = std::min(rows, r0 + piece_rows);
+    auto gather = [&](size_t a, size_t b) {
+      for (size_t r = a; r < b; ++r) memcpy(*stage + r * width, row_ptrs[r], width * sizeof(float));
+    };
+    if (workers <= 1) {
+      gather(r0, r1);
+    } else {
+      std::vector<std::thread> pool;
+      const size_t per = (r1 - r0 + workers - 1) / workers;
+      for (size_t a = r0; a < r1; a += per) pool.emplace_back(gather, a, std::min(r1, a + per));
+      for (std::thread &t : pool) t.join();
+    }
+    DLB_CUDA(cudaMemcpyAsync(dev + r0 * width, *stage + r0 * width, (r1 - r0) * width * sizeof(float),
+                             cudaMemcpyHostToDevice, m->copy_stream));
+  }
+  DLB_CUDA(cudaEventRecord(m->rows_copied[which], m->copy_stream));
+  DLB_CUDA(cudaStreamWaitEvent(m->ctx->stream, m->rows_copied[which], 0));
+  m->rows_in_flight[which] = true;
+  return DLB_OK;
+}
+
+// After the kernels that read a tensor filled by stage_rows have been enqueued.
+dlb_status rows_consumed(dlb_model *m, int which) {
+  if (m->rows_in_flight[which]) DLB_CUDA(cudaEventRecord(m->rows_consumed[which], m->ctx->stream));
+  return DLB_OK;
 }
 
 dlb_status stage_block(dlb_model *m, float **stage, size_t *stage_elems, size_t elems,
@@ -725,11 +799,15 @@ dlb_status dlb_model_destroy(dlb_model *m) {
   if (m->accu_sum) dlb_free(m->ctx, m->accu_sum);
   if (m->ones) dlb_free(m->ctx, m->ones);
   if (m->zeros) dlb_free(m->ctx, m->zeros);
-  if (m->stage_x) dlb_host_free(m->stage_x);
-  if (m->stage_y) dlb_host_free(m->stage_y);
   if (m->copy_stream) {
     cudaStreamSynchronize(m->copy_stream);
     cudaStreamDestroy(m->copy_stream);
+  }
+  if (m->stage_x) dlb_host_free(m->stage_x);
+  if (m->stage_y) dlb_host_free(m->stage_y);
+  for (int w = 0; w < 2; ++w) {
+    if (m->rows_copied[w]) cudaEventDestroy(m->rows_copied[w]);
+    if (m->rows_consumed[w]) cudaEventDestroy(m->rows_consumed[w]);
   }
   for (auto &a : m->ahead) {
     if (a.x) dlb_free(m->ctx, a.x);
@@ -1250,8 +1328,9 @@ dlb_status dlb_model_forward_pass(dlb_model *m, size_t rows, const float *const 
   DLB_TRY(check_supported(m));
   DLB_TRY(ensure_batch(m, rows));
   float *dst = time_stepped(m) ? m->input_rows : m->input;
-  DLB_TRY(stage_rows(m, &m->stage_x, &m->stage_x_elems, rows, m->seq_w * n_in(m), Xm, dst));
-  return dlb_model_forward_pass_device(m, rows, dst);
+  DLB_TRY(stage_rows(m, 0, &m->stage_x, &m->stage_x_elems, rows, m->seq_w * n_in(m), Xm, dst));
+  DLB_TRY(dlb_model_forward_pass_device(m, rows, dst));
+  return rows_consumed(m, 0);
 }
 
 dlb_status dlb_model_compute_error_device(dlb_model *m, size_t rows, const float *Y_dev) {
@@ -1285,8 +1364,9 @@ dlb_status dlb_model_compute_error_device(dlb_model *m, size_t rows, const float
 dlb_status dlb_model_compute_error(dlb_model *m, size_t rows, const float *const *Ym) {
   DLB_REQUIRE(m && Ym && rows > 0 && rows <= m->alloc_rows, "compute_error");
   float *dst = time_stepped(m) ? m->target_rows : m->target;
-  DLB_TRY(stage_rows(m, &m->stage_y, &m->stage_y_elems, rows, m->seq_w * n_out(m), Ym, dst));
-  return dlb_model_compute_error_device(m, rows, dst);
+  DLB_TRY(stage_rows(m, 1, &m->stage_y, &m->stage_y_elems, rows, m->seq_w * n_out(m), Ym, dst));
+  DLB_TRY(dlb_model_compute_error_device(m, rows, dst));
+  return rows_consumed(m, 1);
 }
 
 static std::vector<size_t> top_level(const dlb_model *m) {
@@ -1414,7 +1494,7 @@ dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows) {
       continue;
     }
     const int H = (int)l.units;
-    if (pos + 1 != tops.size()) {  // hidden layer: l.delta holds dA
+    if (pos + 1 != tops.size() && !l.error_final) {  // hidden layer: l.delta holds dA
       if (l.norm != DLB_NORM_NONE) {
         DLB_TRY(norm_backward(m, l, l.delta, l.delta_lo, l.Z, l.A, l.af, B));
       } else {
@@ -1422,9 +1502,20 @@ dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows) {
         DLB_TRY(dlb_split_planes_2d(m->ctx, l.delta, l.delta_lo, B, H));
       }
     }
-    if (below)
-      DLB_TRY(dlb_fc_backward_input(m->ctx, l.delta, l.delta_lo, m->params + l.first_conn,
-                                    m->params_lo + l.first_conn, below->delta, B, (int)l.fan_in, H));
+    l.error_final = false;
+    if (below) {
+      if (below->type != DLB_LAYER_RESIDUAL && below->norm == DLB_NORM_NONE && pos > 1) {
+        // The layer below has no normalization: its activation derivative rides
+        // in this product's epilogue and below->delta is its final error.
+        DLB_TRY(dlb_fc_backward_input_derivative(m->ctx, l.delta, l.delta_lo, m->params + l.first_conn,
+                                                 m->params_lo + l.first_conn, below->Z, below->A, below->af,
+                                                 below->delta, below->delta_lo, B, (int)l.fan_in, H));
+        below->error_final = true;
+      } else {
+        DLB_TRY(dlb_fc_backward_input(m->ctx, l.delta, l.delta_lo, m->params + l.first_conn,
+                                      m->params_lo + l.first_conn, below->delta, B, (int)l.fan_in, H));
+      }
+    }
   }
   return DLB_OK;
 }
@@ -1577,14 +1668,16 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
   } else {
     DLB_TRY(segment(0, m->total_parameters, nullptr));
   }
-  // Recurrent weights of every IndRNN layer back into +-mag^(1/T), mag =
-  // clip(clip_gradient, 2, 10) = 2 with the reference's default clip_gradient of
-  // 1; every activation of the supported set is in a class that takes this
-  // bound (v1/ops/constraints/constraint.cpp L:64-95, L:245-289).
-  const float bound = powf(indrnn_magnitude(m), 1.f / (float)m->seq_w);
-  for (LayerRT &l : m->layers)
-    if (is_indrnn(l))
-      DLB_TRY(dlb_indrnn_clamp(m->ctx, m->params + l.first_recurrent, (int)l.units, -bound, bound));
+  // Recurrent weights of every IndRNN layer back into the layer's bounds
+  // (Update_Weight_Regularization__Constraint_Recurrent_Weight,
+  // v1/ops/constraints/constraint.cpp L:245-289).
+  for (LayerRT &l : m->layers) {
+    if (!is_indrnn(l)) continue;
+    float lo, hi;
+    recurrent_bounds(m, l, &lo, &hi);
+    if (lo != 0.f || hi != 0.f)
+      DLB_TRY(dlb_indrnn_clamp(m->ctx, m->params + l.first_recurrent, (int)l.units, lo, hi));
+  }
   m->grads_clean = true;  // the update kernel clears every gradient it consumes
   m->params_lo_valid = fused;
   return DLB_OK;
@@ -1595,6 +1688,48 @@ dlb_status dlb_model_set_clip_gradient(dlb_model *m, int use, float value) {
   DLB_REQUIRE(m && value > 0.f, "set_clip_gradient: the norm must be positive");
   m->use_clip_gradient = use != 0;
   m->clip_gradient = value;
+  return DLB_OK;
+}
+
+// ref: Model::Set__Regularization__Constraint_Recurrent_Weight(index, lower,
+// upper) (v1/ops/constraints/constraint.cpp L:143-243): a hidden recurrent layer,
+// lower <= upper; 0 / 0 takes the clamp off.  Bounds equal to the default (within
+// 1e-8, the reference's own test, L:41-57) keep following clip_gradient.
+dlb_status dlb_model_set_constraint_recurrent_weight(dlb_model *m, size_t layer, float lower, float upper) {
+  DLB_REQUIRE(m && layer > 0 && layer + 1 < m->layers.size(),
+              "set_constraint_recurrent_weight: the layer must be a hidden layer");
+  LayerRT &l = m->layers[layer];
+  if (!is_indrnn(l)) {
+    set_error("set_constraint_recurrent_weight: layer %zu has no recurrent weights", layer);
+    return DLB_ERR_INVALID;
+  }
+  DLB_REQUIRE(lower <= upper, "set_constraint_recurrent_weight: lower bound above upper bound");
+  l.rec_custom = false;
+  float dlo, dhi;
+  recurrent_bounds(m, l, &dlo, &dhi);
+  const bool is_default = fabsf(lower - dlo) <= 1e-8f && fabsf(upper - dhi) <= 1e-8f;
+  l.rec_custom = !is_default;
+  l.rec_lower = lower;
+  l.rec_upper = upper;
+  return DLB_OK;
+}
+
+// ref: Set__Regularization__Constraint_Recurrent_Weight__Default (L:97-141).
+dlb_status dlb_model_set_constraint_recurrent_weight_default(dlb_model *m, size_t layer) {
+  DLB_REQUIRE(m && layer > 0 && layer + 1 < m->layers.size(),
+              "set_constraint_recurrent_weight_default: the layer must be a hidden layer");
+  if (!is_indrnn(m->layers[layer])) {
+    set_error("set_constraint_recurrent_weight_default: layer %zu has no recurrent weights", layer);
+    return DLB_ERR_INVALID;
+  }
+  m->layers[layer].rec_custom = false;
+  return DLB_OK;
+}
+
+dlb_status dlb_model_get_constraint_recurrent_weight(dlb_model *m, size_t layer, float *lower, float *upper) {
+  DLB_REQUIRE(m && lower && upper && layer < m->layers.size(), "get_constraint_recurrent_weight");
+  *lower = *upper = 0.f;
+  if (is_indrnn(m->layers[layer])) recurrent_bounds(m, m->layers[layer], lower, upper);
   return DLB_OK;
 }
 
@@ -1654,8 +1789,9 @@ dlb_status dlb_model_compute_loss_device(dlb_model *m, size_t rows, const float 
 dlb_status dlb_model_compute_loss(dlb_model *m, size_t rows, const float *const *Ym) {
   DLB_REQUIRE(m && Ym && rows > 0 && rows <= m->alloc_rows, "compute_loss");
   float *dst = time_stepped(m) ? m->target_rows : m->target;
-  DLB_TRY(stage_rows(m, &m->stage_y, &m->stage_y_elems, rows, m->seq_w * n_out(m), Ym, dst));
-  return dlb_model_compute_loss_device(m, rows, dst);
+  DLB_TRY(stage_rows(m, 1, &m->stage_y, &m->stage_y_elems, rows, m->seq_w * n_out(m), Ym, dst));
+  DLB_TRY(dlb_model_compute_loss_device(m, rows, dst));
+  return rows_consumed(m, 1);
 }
 
 // Percent of trials since reset_loss, over every rank's rows
@@ -1749,7 +1885,7 @@ static dlb_status backward_and_derivatives_overlapped(dlb_model *m, size_t rows)
   for (size_t i = m->layers.size() - 1; i >= 1; --i) {
     LayerRT &l = m->layers[i];
     const int H = (int)l.units;
-    if (i + 1 != m->layers.size()) {  // hidden layer: l.delta holds dA
+    if (i + 1 != m->layers.size() && !l.error_final) {  // hidden layer: l.delta holds dA
       if (l.norm != DLB_NORM_NONE) {
         DLB_TRY(norm_backward(m, l, l.delta, l.delta_lo, l.Z, l.A, l.af, B));
       } else {
@@ -1757,15 +1893,25 @@ static dlb_status backward_and_derivatives_overlapped(dlb_model *m, size_t rows)
         DLB_TRY(dlb_split_planes_2d(m->ctx, l.delta, l.delta_lo, B, H));
       }
     }
+    l.error_final = false;
     const float *X = i == 1 ? m->input : m->layers[i - 1].A;
     const float *X_lo = i == 1 ? m->input_lo : m->layers[i - 1].A_lo;
     float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
     DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn, dbias,
                                    B, (int)l.fan_in, H, accumulate));
     DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
-    if (i > 1)
-      DLB_TRY(dlb_fc_backward_input(m->ctx, l.delta, l.delta_lo, m->params + l.first_conn,
-                                    m->params_lo + l.first_conn, m->layers[i - 1].delta, B, (int)l.fan_in, H));
+    if (i > 1) {
+      LayerRT &below = m->layers[i - 1];
+      if (below.norm == DLB_NORM_NONE) {
+        DLB_TRY(dlb_fc_backward_input_derivative(m->ctx, l.delta, l.delta_lo, m->params + l.first_conn,
+                                                 m->params_lo + l.first_conn, below.Z, below.A, below.af,
+                                                 below.delta, below.delta_lo, B, (int)l.fan_in, H));
+        below.error_final = true;
+      } else {
+        DLB_TRY(dlb_fc_backward_input(m->ctx, l.delta, l.delta_lo, m->params + l.first_conn,
+                                      m->params_lo + l.first_conn, below.delta, B, (int)l.fan_in, H));
+      }
+    }
     if (i == 1) break;
   }
   m->grads_clean = false;

@@ -23,12 +23,18 @@ struct LayerRT {
   // IndRNN layer: its recurrent weights u[units] follow its W inside
   // [first_conn, last_conn) (v1/learner/connections_prepare.cpp L:46-81).
   size_t first_recurrent = 0;
+  // Bounds of the recurrent weights when set by hand
+  // (Set__Regularization__Constraint_Recurrent_Weight); otherwise the default
+  // derived from clip_gradient and seq_w applies.  0 / 0: no clamp.
+  bool rec_custom = false;
+  float rec_lower = 0.f, rec_upper = 0.f;
   // Residual blocks (the reference's layer list: a RESIDUAL layer of depth d
   // followed by its d block layers, v1/learner/compile.cpp).
   int group = 0;            // 1 = layer inside a residual block
   size_t depth = 0;         // RESIDUAL: number of block layers
   size_t pad = 0;           // RESIDUAL: first column of the narrower of shortcut and block in the output
   bool block_input = false; // first layer of a block: no activation in front
+  bool error_final = false; // backward: delta already holds the error w.r.t. Z (the product above formed it)
   size_t norm_units = 0;    // normalised units: width, or fan-in for a block layer
   // Device buffers (allocated by ensure_batch).  Stand-alone FC layer: Z sums,
   // A output after activation and dropout, delta error w.r.t. Z.  Block layer:
@@ -99,6 +105,12 @@ struct dlb_model {
   size_t const_units = 0;
   float *stage_x = nullptr, *stage_y = nullptr;  // pinned
   size_t stage_x_elems = 0, stage_y_elems = 0;
+  // Row-pointer inputs (forward_pass / compute_error / compute_loss) cross on the
+  // copy stream: [0] inputs, [1] targets.  copied: the copy out of the staging
+  // buffer is done (the host may refill it); consumed: the kernels that read
+  // the device tensor have been enqueued up to here (the next copy waits).
+  cudaEvent_t rows_copied[2] = {nullptr, nullptr}, rows_consumed[2] = {nullptr, nullptr};
+  bool rows_in_flight[2] = {false, false};
   // Batches copied ahead of the step that uses them: two device slots filled
   // on a stream of their own, so that the copy of batch i+1 runs under the
   // kernels of batch i.

@@ -165,6 +165,7 @@ bool tmap_cached(dlb_ctx *ctx, CUtensorMap *out, bool mn_major, const void *ptr,
                  uint64_t k, uint64_t ld, uint32_t box_k, uint32_t box_mn);
 // The 2-CTA form of the fp16-plane product (gemm_pair.cu).
 bool gemm_pair_enabled();
+int gemm_pair_chunk();
 dlb_status gemm_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, float *C, long long ldc,
                      int M, int N, int K, const GemmEpilogue &ep);
 

@@ -71,6 +71,8 @@ SIGNATURES = {
     "dlb_brn_forward_sums": (_i, [_vp, _vp, _i, _i, _vp]),
     "dlb_brn_forward_sums_noalloc": (_i, [_vp, _i, _i, _vp, _vp]),
     "dlb_brn_forward_finalize":(_i, [_vp, _vp, _i, _i, _f, _f, _f, _f, C.POINTER(BrnUnitArrays)]),
+    "dlb_fc_forward_activation": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, C.POINTER(DropoutDesc), _vp, _vp, _i, _i, _i]),
+    "dlb_fc_backward_input_derivative": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i]),
     "dlb_activation_forward": (_i, [_vp, _vp, C.POINTER(BrnUnitArrays), _i, C.POINTER(DropoutDesc), _vp, _vp, _i, _i]),
     "dlb_softmax_forward": (_i, [_vp, _vp, _vp, _i, _i]),
     "dlb_activation_backward": (_i, [_vp, _vp, _vp, _vp, C.POINTER(BrnUnitArrays), _i, _i, _i, _vp]),
@@ -155,6 +157,9 @@ SIGNATURES = {
     "dlb_model_train_step": (_i, [_vp, _sz, _vp, _vp, C.POINTER(_d)]),
     "dlb_model_train_step_device": (_i, [_vp, _sz, _vp, _vp]),
     "dlb_model_set_clip_gradient": (_i, [_vp, _i, _f]),
+    "dlb_model_set_constraint_recurrent_weight": (_i, [_vp, _sz, _f, _f]),
+    "dlb_model_set_constraint_recurrent_weight_default": (_i, [_vp, _sz]),
+    "dlb_model_get_constraint_recurrent_weight": (_i, [_vp, _sz, C.POINTER(_f), C.POINTER(_f)]),
     "dlb_model_save_params": (_i, [_vp, _cp]),
     "dlb_model_save_spec_params": (_i, [_vp, _cp]),
     "dlb_model_load": (_i, [_vp, _cp, _cp]),
@@ -602,6 +607,20 @@ class Model:
 
     def set_clip_gradient(self, use, value):
         check(self.L.dlb_model_set_clip_gradient(self.h, int(bool(use)), float(value)), "set_clip_gradient")
+
+    def set_constraint_recurrent_weight(self, layer, lower, upper):
+        check(self.L.dlb_model_set_constraint_recurrent_weight(self.h, layer, float(lower), float(upper)),
+              "set_constraint_recurrent_weight")
+
+    def set_constraint_recurrent_weight_default(self, layer):
+        check(self.L.dlb_model_set_constraint_recurrent_weight_default(self.h, layer),
+              "set_constraint_recurrent_weight_default")
+
+    def get_constraint_recurrent_weight(self, layer):
+        lo, hi = _f(0.0), _f(0.0)
+        check(self.L.dlb_model_get_constraint_recurrent_weight(self.h, layer, C.byref(lo), C.byref(hi)),
+              "get_constraint_recurrent_weight")
+        return lo.value, hi.value
 
     def stage_batch(self, batch, X, Y):
         """Starts the host-to-device copy of one batch; X and Y are contiguous

@@ -274,6 +274,34 @@ dlb_status dlb_activation_backward(dlb_ctx *ctx, float *dA, const float *Z, cons
                                    const dlb_brn_unit_arrays *u, int af, int rows, int n_units,
                                    double *sums);
 
+/* dlb_fc_forward followed by dlb_activation_forward of a layer WITHOUT
+ * normalization, as one call: Z = X W^T + bias, A = dropout(f(Z)) (+ A's plane
+ * buffer).  ref: Forward_Pass__FC__OpenMP + Forward_Pass__Bias__OpenMP +
+ * Forward_Pass__FC_AF__OpenMP and the dropout forwards (v1/learner/fwp_mp.cpp
+ * L:4396-4459, L:4741-4770, L:4809-4985).  Where the product runs on the 2-CTA
+ * tensor-core kernel (fp16 planes, at least 256 x 256 outputs, both operands'
+ * plane buffers kept by the caller, A's buffer split once before), bias,
+ * activation, dropout (Bernoulli flags per unit, inverted Bernoulli, UOut) and
+ * the planes of A are formed in the product's epilogue, on the tile the drain
+ * warps hold: A is never re-read.  Otherwise the two kernels run one after the
+ * other; results are the same either way. */
+dlb_status dlb_fc_forward_activation(dlb_ctx *ctx, const float *X, const float *X_lo, const float *W,
+                                     const float *W_lo, const float *bias, float *Z, int af,
+                                     const dlb_dropout_desc *dropout, float *A, float *A_lo, int rows,
+                                     int n_in, int n_out);
+
+/* dlb_fc_backward_input followed by dlb_activation_backward of the layer below
+ * when that layer has NO normalization, as one call: dX = (delta W) * f'(Z_below,
+ * A_below), the error of the layer below w.r.t. its sums (+ its plane buffer).
+ * ref: Backward_Pass__FC__OpenMP + Backward_Pass__FC__DF__OpenMP
+ * (v1/learner/bwp_mp.cpp L:968-1007, L:1150-1186).  Fused into the product's
+ * epilogue under the conditions of dlb_fc_forward_activation. */
+dlb_status dlb_fc_backward_input_derivative(dlb_ctx *ctx, const float *delta, const float *delta_lo,
+                                            const float *W, const float *W_lo, const float *Z_below,
+                                            const float *A_below, int af_below, float *dX, float *dX_lo,
+                                            int rows, int n_in, int n_out);
+
+
 /* delta = delta_af*gamma*r/sigma + d_sigma*(Z-mean)/(N*sigma) + d_mean/N over
  * delta (in place), N = global_rows; d_mean/d_sigma are sums[2n..4n) after the
  * all-reduce.  delta_lo optional.  ref: pass 3, bwp_mp.cpp L:1600-1626. */
@@ -657,6 +685,17 @@ dlb_status dlb_checkpointer_load(dlb_checkpointer *c, int *found);
  * default bound of IndRNN recurrent weights, clip(value, 2, 10)^(1/seq_w)
  * (v1/ops/constraints/constraint.cpp L:64-95). */
 dlb_status dlb_model_set_clip_gradient(dlb_model *m, int use, float value);
+/* Model::Set__Regularization__Constraint_Recurrent_Weight(index, lower, upper)
+ * and its __Default form (v1/ops/constraints/constraint.cpp L:97-243): the bounds
+ * the recurrent weights of one IndRNN layer are clamped to after every update
+ * (L:245-289).  Hidden layers with recurrent weights only, lower <= upper; 0 / 0
+ * takes the clamp off.  Without a call the default applies and follows
+ * set_clip_gradient, as in the reference; bounds equal to the default (within
+ * 1e-8) count as the default.  The bounds are written to and read from the
+ * parameter file like the reference's. */
+dlb_status dlb_model_set_constraint_recurrent_weight(dlb_model *m, size_t layer, float lower, float upper);
+dlb_status dlb_model_set_constraint_recurrent_weight_default(dlb_model *m, size_t layer);
+dlb_status dlb_model_get_constraint_recurrent_weight(dlb_model *m, size_t layer, float *lower, float *upper);
 /* The same step with the input copy taken off the critical path.  stage_batch
  * starts the host-to-device copy of one batch (contiguous [rows, seq_w*n]
  * arrays, page-locked for the copy to be asynchronous; they must stay

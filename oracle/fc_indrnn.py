@@ -31,7 +31,7 @@ from __future__ import annotations
 import numpy as np
 
 import fc_step
-from fc_step import (LOSS_CROSS_ENTROPY, NORM_NONE, OracleModel, af_derive, af_fire, brn_backward, brn_forward,
+from fc_step import (AF_SOFTMAX, LOSS_CROSS_ENTROPY, NORM_NONE, OracleModel, af_derive, af_fire, brn_backward, brn_forward,
                      f32, loss_and_delta, optimizer_scalars, optimizer_update)
 
 LAYER_FC, LAYER_INDRNN = 3, 4
@@ -175,6 +175,11 @@ class IndRnnOracleModel(OracleModel):
         for t in range(self.time_delay, T):
             total, delta[t] = loss_and_delta(self.loss, o["af"], o["Y"][t], o["A"][t], y[t], self.global_rows)
             self.loss_sum += total
+            if o["af"] == AF_SOFTMAX:
+                # The softmax branch reads the target of time step 0 for every time
+                # step (`Ym[i][k]`, compute_error_mp.cpp L:237-247); the loss above
+                # reads the right one.
+                _, delta[t] = loss_and_delta(self.loss, o["af"], o["Y"][t], o["A"][t], y[0], self.global_rows)
         o["delta"] = delta
         self.loss_rows += batch * (T - self.time_delay)
 
@@ -253,12 +258,31 @@ class IndRnnOracleModel(OracleModel):
                          *self._decay(batch, training_size))
         # mag = clip(clip_gradient, 2, 10): Compute__Regularization__Constraint_
         # Recurrent_Weight__Default, v1/ops/constraints/constraint.cpp L:64-95.
-        mag = f32(min(max(self.hp.get("clip_gradient", 1.0), 2.0), 10.0))
-        bound = f32(np.power(mag, f32(1) / f32(self.T), dtype=f32))
         for l in self.layers[1:]:
             if l["type"] == LAYER_INDRNN:
-                s = slice(l["first_recurrent"], l["first_recurrent"] + l["units"])
-                self.params[s] = np.clip(self.params[s], -bound, bound)
+                lo, hi = self._recurrent_bounds(l)
+                if lo != 0 or hi != 0:  # Layer::Use__Regularization__Constraint_Recurrent_Weight, L:28-31
+                    s = slice(l["first_recurrent"], l["first_recurrent"] + l["units"])
+                    self.params[s] = np.clip(self.params[s], lo, hi)
+
+    def _recurrent_bounds(self, l):
+        """The layer's own bounds when set by hand, else the default."""
+        if l.get("rec_bounds") is not None:
+            return l["rec_bounds"]
+        mag = f32(min(max(self.hp.get("clip_gradient", 1.0), 2.0), 10.0))
+        bound = f32(np.power(mag, f32(1) / f32(self.T), dtype=f32))
+        return -bound, bound
+
+    def set_constraint_recurrent_weight(self, layer, lower, upper):
+        """Model::Set__Regularization__Constraint_Recurrent_Weight(index, lower, upper)
+        (v1/ops/constraints/constraint.cpp L:143-243).  Bounds equal to the default
+        keep following clip_gradient (Check__Use__..__Default, L:41-57)."""
+        l = self.layers[layer]
+        assert l["type"] == LAYER_INDRNN and lower <= upper
+        l["rec_bounds"] = None
+        dlo, dhi = self._recurrent_bounds(l)
+        if abs(f32(lower) - dlo) > 1e-8 or abs(f32(upper) - dhi) > 1e-8:
+            l["rec_bounds"] = (f32(lower), f32(upper))
 
     def get_layer_outputs(self, layer, batch):
         return self.layers[layer]["A"][:, :batch].copy()

@@ -61,6 +61,7 @@ def lib(path=None):
         "ref_set_mp": (i, [vp, i]),
         "ref_set_weight_decay": (i, [vp, C.c_double]),
         "ref_set_clip_gradient": (i, [vp, i, C.c_double]),
+        "ref_set_constraint_recurrent_weight": (i, [vp, sz, C.c_double, C.c_double]),
         "ref_set_l2": (i, [vp, C.c_double]),
         "ref_save": (i, [vp, cp, cp]),
         "ref_load": (i, [vp, cp, cp]),
@@ -215,6 +216,10 @@ class RefModel:
 
     def set_clip_gradient(self, use, value):
         _ck(self.L.ref_set_clip_gradient(self.h, int(bool(use)), float(value)), "set_clip_gradient")
+
+    def set_constraint_recurrent_weight(self, layer, lower, upper):
+        _ck(self.L.ref_set_constraint_recurrent_weight(self.h, layer, float(lower), float(upper)),
+            "set_constraint_recurrent_weight")
 
     def seed_weights(self, seed):
         _ck(self.L.ref_seed_weights(self.h, seed), "seed")

@@ -210,6 +210,12 @@ int ref_set_clip_gradient(ref_model m, int use, double value) {
   H(m)->model.set_clip_gradient(use != 0);
   return H(m)->model.set_clip_gradient(static_cast<real>(value)) ? 0 : -1;
 }
+int ref_set_constraint_recurrent_weight(ref_model m, size_t layer, double lower, double upper) {
+  return H(m)->model.Set__Regularization__Constraint_Recurrent_Weight(layer, static_cast<real>(lower),
+                                                                      static_cast<real>(upper))
+             ? 0
+             : -1;
+}
 int ref_save(ref_model m, const char *path_params, const char *path_spec) {
   std::string a(path_params), b(path_spec);
   Model &M = H(m)->model;

@@ -49,6 +49,7 @@ int ref_set_weight_decay(ref_model m, double value);
 /* Model::set_l2 (v1/ops/regularizers/l2.cpp L:31-66). */
 int ref_set_l2(ref_model m, double value);
 int ref_set_clip_gradient(ref_model m, int use, double value);
+int ref_set_constraint_recurrent_weight(ref_model m, size_t layer, double lower, double upper);
 /* Model::save_params + save_spec_params, Model::load (v1/learner/save.cpp, load.cpp). */
 int ref_save(ref_model m, const char *path_params, const char *path_spec);
 int ref_load(ref_model m, const char *path_params, const char *path_spec);

@@ -96,6 +96,46 @@ def test_clip_gradient_sets_the_recurrent_bound(gpu_ctx):
         assert util.rel_l2(got["params1"], want["params1"]) <= 1e-5
 
 
+def test_recurrent_bounds_set_by_hand(gpu_ctx, tmp_path):
+    """Per-layer bounds of the recurrent weights: one layer with its own interval,
+    one with the clamp off; the bounds survive a save / load, and a default bound
+    keeps following set_clip_gradient."""
+    cfg = configs.indrnn_stack(n_in=64, hidden=128, depth=2, n_out=32, seq_w=4, batch=32)
+    X, Y = configs.synthetic_batch(cfg)
+    p0 = _kink_free(cfg, X)
+    for _, s in configs.recurrent_slices(cfg):
+        p0[s] = np.linspace(-1.5, 1.5, s.stop - s.start, dtype=np.float32)
+    ora = util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0)
+    mod = util.build(dlb200.Model(gpu_ctx), cfg, params=p0)
+    for m in (ora, mod):
+        m.set_constraint_recurrent_weight(1, -0.5, 0.75)
+        m.set_constraint_recurrent_weight(2, 0.0, 0.0)
+    want = util.trace(ora, cfg, 1, X, Y)
+    got = util.trace(mod, cfg, 1, X, Y)
+    assert gpu_ctx.sync() == 0
+    (_, s1), (_, s2) = configs.recurrent_slices(cfg)
+    assert got["params1"][s1].min() == np.float32(-0.5) and got["params1"][s1].max() == np.float32(0.75)
+    assert np.abs(got["params1"][s2]).max() > 1.4
+    assert util.rel_l2(got["params1"], want["params1"]) <= 1e-5
+    # The bounds are part of the parameter file.
+    a, b = str(tmp_path / "m.net"), str(tmp_path / "m.nn")
+    mod.save(a, b)
+    back = dlb200.Model(gpu_ctx)
+    back.load(a, b)
+    assert back.get_constraint_recurrent_weight(1) == (np.float32(-0.5), np.float32(0.75))
+    assert back.get_constraint_recurrent_weight(2) == (0.0, 0.0)
+    # A layer back on the default follows the gradient norm again.
+    back.set_constraint_recurrent_weight_default(1)
+    back.set_clip_gradient(False, 5.0)
+    lo, hi = back.get_constraint_recurrent_weight(1)
+    assert np.isclose(hi, np.float32(5.0) ** np.float32(0.25), rtol=1e-6) and lo == -hi
+    # What is refused: layers without recurrent weights, inverted intervals.
+    with pytest.raises(dlb200.DlbError):
+        back.set_constraint_recurrent_weight(len(cfg["layers"]) - 1, -1.0, 1.0)
+    with pytest.raises(dlb200.DlbError):
+        back.set_constraint_recurrent_weight(1, 1.0, -1.0)
+
+
 @pytest.mark.parametrize("delay", [7, 0], ids=["last_step", "all_steps"])
 def test_indrnn_evaluation_pass(gpu_ctx, delay):
     """Inference through time (each time step's own running averages), loss and

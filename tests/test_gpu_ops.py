@@ -167,6 +167,97 @@ def test_products_with_caller_kept_plane_buffers(gpu_ctx, gemm_kind):
         gpu_ctx.set_gemm_kind(1)
 
 
+@pytest.mark.parametrize("af", [fc_step.AF_LEAKY_RELU, fc_step.AF_SELU, fc_step.AF_ISRLU])
+@pytest.mark.parametrize("dropout", [fc_step.DROPOUT_NONE, fc_step.DROPOUT_BERNOULLI, fc_step.DROPOUT_BERNOULLI_INVERTED,
+                                     fc_step.DROPOUT_UOUT])
+@pytest.mark.parametrize("shape", [(512, 384, 640), (300, 200, 520)], ids=["whole_tiles", "ragged"])
+def test_fc_forward_with_activation_in_the_epilogue(gpu_ctx, af, dropout, shape):
+    """Bias, activation, dropout and the planes of A formed in the product's
+    epilogue (second call: the first split of A's buffer has no scale to predict
+    from and takes the two-kernel path) against the two kernels one after the
+    other and against float64; the planes written by the epilogue are what the
+    next product reads."""
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rows, n_in, n_out = shape
+    rng = np.random.default_rng(af + 7 * dropout)
+    X = rng.standard_normal((rows, n_in), dtype=np.float32)
+    W = (rng.standard_normal((n_out, n_in)) * 0.05).astype(np.float32)
+    W2 = (rng.standard_normal((256, n_out)) * 0.05).astype(np.float32)
+    bias = rng.standard_normal(n_out).astype(np.float32)
+    mask = (rng.random(n_out) < 0.8).astype(np.uint8)
+    noise = ((rng.random((rows, n_out)) * 2 - 1) * 0.1).astype(np.float32)
+    x, w, w2, b, md, nd = (ctx.array(t) for t in (X, W, W2, bias, mask, noise))
+    xp, wp, w2p = ctx.empty(X.shape), ctx.empty(W.shape), ctx.empty(W2.shape)
+    check(L.dlb_split_planes_2d(ctx.h, x.ptr, xp.ptr, rows, n_in))
+    check(L.dlb_split_planes_2d(ctx.h, w.ptr, wp.ptr, n_out, n_in))
+    check(L.dlb_split_planes_2d(ctx.h, w2.ptr, w2p.ptr, 256, n_out))
+    dp = dlb200.DropoutDesc(dropout, 0.8, md.ptr, nd.ptr)
+    dpp = C.byref(dp) if dropout else None
+    # the two kernels
+    z0, a0, a0p = ctx.empty((rows, n_out)), ctx.empty((rows, n_out)), ctx.empty((rows, n_out))
+    check(L.dlb_fc_forward(ctx.h, x.ptr, xp.ptr, w.ptr, wp.ptr, b.ptr, z0.ptr, rows, n_in, n_out))
+    check(L.dlb_activation_forward(ctx.h, z0.ptr, None, af, dpp, a0.ptr, a0p.ptr, rows, n_out))
+    # one call, twice: the second one runs the epilogue
+    z1, a1, a1p = ctx.empty((rows, n_out)), ctx.empty((rows, n_out)), ctx.empty((rows, n_out))
+    launches = []
+    for _ in range(2):
+        before = ctx.launch_count()
+        check(L.dlb_fc_forward_activation(ctx.h, x.ptr, xp.ptr, w.ptr, wp.ptr, b.ptr, z1.ptr, af, dpp, a1.ptr, a1p.ptr,
+                                          rows, n_in, n_out))
+        launches.append(ctx.launch_count() - before)
+    nxt = ctx.empty((rows, 256))
+    check(L.dlb_fc_forward(ctx.h, a1.ptr, a1p.ptr, w2.ptr, w2p.ptr, None, nxt.ptr, rows, n_out, 256))
+    assert ctx.sync() == 0
+    assert launches[1] < launches[0], "the second call did not take the fused path"
+    assert np.array_equal(z1.get(), z0.get())
+    assert np.array_equal(a1.get(), a0.get())
+    Zx = X.astype(np.float64) @ W.T.astype(np.float64) + bias
+    assert util.rel_l2(z1.get(), Zx) <= GEMM_TOL
+    want = fc_step.apply_dropout(fc_step.af_fire(af, z1.get()), dropout, 0.8, mask, noise)
+    assert util.rel_max(a1.get(), want) <= F32_TOL
+    assert util.rel_l2(nxt.get(), a1.get().astype(np.float64) @ W2.T.astype(np.float64)) <= GEMM_TOL
+
+
+@pytest.mark.parametrize("af", [fc_step.AF_LEAKY_RELU, fc_step.AF_SELU, fc_step.AF_ISRLU])
+@pytest.mark.parametrize("shape", [(512, 640, 384), (300, 520, 200)], ids=["whole_tiles", "ragged"])
+def test_fc_backward_input_with_the_derivative_in_the_epilogue(gpu_ctx, af, shape):
+    """dX = (delta W) f'(Z, A) of the layer below formed in the product's
+    epilogue, with the planes of dX, against the three kernels one after the
+    other and against float64."""
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rows, n_in, n_out = shape
+    rng = np.random.default_rng(af)
+    delta = (rng.standard_normal((rows, n_out)) * 1e-3).astype(np.float32)
+    W = (rng.standard_normal((n_out, n_in)) * 0.05).astype(np.float32)
+    Zb = rng.standard_normal((rows, n_in), dtype=np.float32)
+    Ab = fc_step.af_fire(af, Zb)
+    W0 = (rng.standard_normal((n_in, 256)) * 0.05).astype(np.float32)   # the layer below's own weights
+    d, w, zb, ab, w0 = (ctx.array(t) for t in (delta, W, Zb, Ab, W0))
+    dpl, wp, w0p = ctx.empty(delta.shape), ctx.empty(W.shape), ctx.empty(W0.shape)
+    check(L.dlb_split_planes_2d(ctx.h, d.ptr, dpl.ptr, rows, n_out))
+    check(L.dlb_split_planes_2d(ctx.h, w.ptr, wp.ptr, n_out, n_in))
+    check(L.dlb_split_planes_2d(ctx.h, w0.ptr, w0p.ptr, n_in, 256))
+    e0, e0p = ctx.empty((rows, n_in)), ctx.empty((rows, n_in))
+    check(L.dlb_fc_backward_input(ctx.h, d.ptr, dpl.ptr, w.ptr, wp.ptr, e0.ptr, rows, n_in, n_out))
+    check(L.dlb_activation_backward(ctx.h, e0.ptr, zb.ptr, ab.ptr, None, af, rows, n_in, None))
+    e1, e1p = ctx.empty((rows, n_in)), ctx.empty((rows, n_in))
+    launches = []
+    for _ in range(2):
+        before = ctx.launch_count()
+        check(L.dlb_fc_backward_input_derivative(ctx.h, d.ptr, dpl.ptr, w.ptr, wp.ptr, zb.ptr, ab.ptr, af, e1.ptr,
+                                                 e1p.ptr, rows, n_in, n_out))
+        launches.append(ctx.launch_count() - before)
+    # the planes of e1 feed the next product down
+    nxt = ctx.empty((rows, 256))
+    check(L.dlb_fc_backward_input(ctx.h, e1.ptr, e1p.ptr, w0.ptr, w0p.ptr, nxt.ptr, rows, 256, n_in))
+    assert ctx.sync() == 0
+    assert launches[1] < launches[0], "the second call did not take the fused path"
+    assert np.array_equal(e1.get(), e0.get())
+    want = (delta.astype(np.float64) @ W.astype(np.float64)) * fc_step.af_derive(af, Zb, Ab)
+    assert util.rel_l2(e1.get(), want) <= GEMM_TOL
+    assert util.rel_l2(nxt.get(), e1.get().astype(np.float64) @ W0.astype(np.float64)) <= GEMM_TOL
+
+
 def test_large_k_accumulation_stays_fp32_faithful(gpu_ctx):
     """k = 4096: the chunked drain keeps the tensor core's truncating
     accumulation from growing with k; the product is as close to the exact one

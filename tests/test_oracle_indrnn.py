@@ -73,6 +73,31 @@ def test_recurrent_weights_are_clamped_like_the_reference():
 
 
 @pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+def test_recurrent_bounds_set_by_hand_like_the_reference():
+    """Bounds set per layer (Set__Regularization__Constraint_Recurrent_Weight,
+    v1/ops/constraints/constraint.cpp L:143-243): one layer with its own interval,
+    one with the clamp taken off (0 / 0)."""
+    cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=2, n_out=5, seq_w=4, batch=5)
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    p0 = ref.get_array("parameters")
+    for _, s in configs.recurrent_slices(cfg):
+        p0[s] = np.linspace(-1.5, 1.5, s.stop - s.start, dtype=np.float32)
+    ref.set_array("parameters", p0)
+    ref.set_constraint_recurrent_weight(1, -0.5, 0.75)
+    ref.set_constraint_recurrent_weight(2, 0.0, 0.0)
+    want = util.trace(ref, cfg, steps=2)
+    ora = util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0)
+    ora.set_constraint_recurrent_weight(1, -0.5, 0.75)
+    ora.set_constraint_recurrent_weight(2, 0.0, 0.0)
+    got = util.trace(ora, cfg, steps=2)
+    (_, s1), (_, s2) = configs.recurrent_slices(cfg)
+    for t in (want, got):
+        assert t["params1"][s1].min() == np.float32(-0.5) and t["params1"][s1].max() == np.float32(0.75)
+        assert np.abs(t["params1"][s2]).max() > 1.4  # not clamped
+    _check(got, want)
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
 def test_clip_gradient_widens_the_recurrent_bound_like_the_reference():
     """The default bound is clip(clip_gradient, 2, 10)^(1/T)
     (v1/ops/constraints/constraint.cpp L:64-95); setting the norm re-derives it
