@@ -35,18 +35,19 @@ def mlp_softmax(n_in=784, hidden=256, n_out=10, batch=128):
 
 def deep_brn_mlp(n_in=1024, hidden=4096, depth=4, n_out=1024, batch=4096,
                  af=ACTIVATION.SELU, optimizer=OPTIMIZER.AMSBOUND, keep=0.9,
-                 dropout=LAYER_DROPOUT.BERNOULLI):
+                 dropout=LAYER_DROPOUT.BERNOULLI, norm=True):
     """Deep MLP: every hidden layer is FC + batch renorm (r_max 3, d_max 5,
     momentum 0.99, eps 1e-5) + SELU + Bernoulli dropout (keep 0.9); linear
-    output, MSE, AMSBound (final_lr 0.1, gamma 1e-3)."""
+    output, MSE, AMSBound (final_lr 0.1, gamma 1e-3).  norm=False: the same stack
+    with bias instead of normalization."""
     layers = [dict(type=LAYER.FULLY_CONNECTED, units=n_in)]
     for _ in range(depth):
         layers.append(dict(type=LAYER.FULLY_CONNECTED, units=hidden, af=af,
-                           norm=LAYER_NORM.BATCH_RENORMALIZATION,
+                           norm=LAYER_NORM.BATCH_RENORMALIZATION if norm else None,
                            dropout=(dropout, keep) if dropout else None))
     layers.append(dict(type=LAYER.FULLY_CONNECTED, units=n_out, af=ACTIVATION.LINEAR))
     return dict(
-        name=f"brn_mlp_{n_in}-{depth}x{hidden}-{n_out}_b{batch}",
+        name=("brn_mlp_" if norm else "plain_mlp_") + f"{n_in}-{depth}x{hidden}-{n_out}_b{batch}",
         model_type=MODEL.FEEDFORWARD, seq_w=1, time_delays=0, layers=layers,
         loss=LOSS_FN.MSE, optimizer=optimizer,
         hparams=dict(adam_learning_rate=1e-3, adam_beta1=0.9, adam_beta2=0.999, adam_epsilon=1e-8,

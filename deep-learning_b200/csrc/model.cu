@@ -1352,6 +1352,21 @@ dlb_status dlb_model_compute_error_device(dlb_model *m, size_t rows, const float
     DLB_TRY(dlb_loss_delta(m->ctx, m->loss, o.af, o.Z + skip, o.A + skip, m->target + skip,
                            o.delta + skip, o.delta_lo + skip, (int)((T - d) * rows), (int)W, Bg,
                            m->loss_sum));
+    if (o.af == DLB_AF_SOFTMAX && T > 1) {
+      // The softmax branch of compute_error_rec_mp takes the error of every time
+      // step against the target of time step 0 (`Ym[i][k]`,
+      // v1/learner/compute_error_mp.cpp L:237-247) while the loss above reads the
+      // step's own target: the error is formed again against time step 0's rows.
+      const size_t block = rows * W;
+      void *scr = nullptr;
+      DLB_TRY(scratch(m->ctx, (T - d) * block * sizeof(float) + 256, &scr));
+      float *first = static_cast<float *>(scr);
+      double *unused = reinterpret_cast<double *>(first + align_up((T - d) * block, 64));
+      for (size_t t = 0; t < T - d; ++t)
+        DLB_TRY(dlb_memcpy_d2d(m->ctx, first + t * block, m->target, block * sizeof(float)));
+      DLB_TRY(dlb_loss_delta(m->ctx, m->loss, o.af, o.Z + skip, o.A + skip, first, o.delta + skip,
+                             o.delta_lo + skip, (int)((T - d) * rows), (int)W, Bg, unused));
+    }
     m->loss_rows += rows * (T - d);
     return DLB_OK;
   }

@@ -157,6 +157,15 @@ SIGNATURES = {
     "dlb_model_train_step": (_i, [_vp, _sz, _vp, _vp, C.POINTER(_d)]),
     "dlb_model_train_step_device": (_i, [_vp, _sz, _vp, _vp]),
     "dlb_model_set_clip_gradient": (_i, [_vp, _i, _f]),
+    "dlb_minibatch_create": (_i, [C.POINTER(_vp), _vp, _vp, _vp, _sz, _i, _sz, _sz, C.c_uint]),
+    "dlb_minibatch_destroy": (_i, [_vp]),
+    "dlb_minibatch_get_n_batch": (_sz, [_vp]),
+    "dlb_minibatch_examples_per_batch": (_sz, [_vp]),
+    "dlb_minibatch_examples_last_batch": (_sz, [_vp]),
+    "dlb_minibatch_set_shuffle": (_i, [_vp, _i]),
+    "dlb_minibatch_shuffle": (_i, [_vp]),
+    "dlb_minibatch_get_order": (_i, [_vp, C.POINTER(_sz), _sz]),
+    "dlb_minibatch_train": (_i, [_vp, C.POINTER(_d)]),
     "dlb_model_set_constraint_recurrent_weight": (_i, [_vp, _sz, _f, _f]),
     "dlb_model_set_constraint_recurrent_weight_default": (_i, [_vp, _sz]),
     "dlb_model_get_constraint_recurrent_weight": (_i, [_vp, _sz, C.POINTER(_f), C.POINTER(_f)]),
@@ -657,6 +666,61 @@ class Model:
         out = np.empty((T, batch, n_out), dtype=np.float32)
         check(self.L.dlb_model_get_layer_errors(self.h, layer, batch, which, _ptr(out)), "get_layer_errors")
         return out
+
+
+class MiniBatch:
+    """The mini-batch loop of the reference (DL::v1::MiniBatch) over host arrays
+    X [n, seq_w * n_in] and Y [n, seq_w * n_out], handed over as row pointers."""
+
+    def __init__(self, model, X, Y, desired_per_batch, use_shuffle=False, max_batches=0, seed=0):
+        self.L = model.L
+        self.model = model
+        self._x, self._xr = Model._row_pointers(X)
+        self._y, self._yr = Model._row_pointers(Y)
+        self.n = self._x.shape[0]
+        self.h = _vp()
+        check(self.L.dlb_minibatch_create(C.byref(self.h), model.h, self._xr, self._yr, self.n, int(bool(use_shuffle)),
+                                          int(desired_per_batch), int(max_batches), int(seed)), "minibatch_create")
+
+    def close(self):
+        if self.h:
+            self.L.dlb_minibatch_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def n_batch(self):
+        return self.L.dlb_minibatch_get_n_batch(self.h)
+
+    @property
+    def per_batch(self):
+        return self.L.dlb_minibatch_examples_per_batch(self.h)
+
+    @property
+    def last_batch(self):
+        return self.L.dlb_minibatch_examples_last_batch(self.h)
+
+    def set_shuffle(self, on):
+        check(self.L.dlb_minibatch_set_shuffle(self.h, int(bool(on))), "minibatch_set_shuffle")
+
+    def shuffle(self):
+        check(self.L.dlb_minibatch_shuffle(self.h), "minibatch_shuffle")
+
+    def order(self):
+        out = (_sz * self.n)()
+        check(self.L.dlb_minibatch_get_order(self.h, out, self.n), "minibatch_get_order")
+        return np.array(out[:], dtype=np.int64)
+
+    def train(self):
+        """One pass over the data set; the mean of the batch losses."""
+        v = _d(0.0)
+        check(self.L.dlb_minibatch_train(self.h, C.byref(v)), "minibatch_train")
+        return v.value
 
 
 class Checkpointer:

@@ -680,6 +680,39 @@ dlb_status dlb_checkpointer_destroy(dlb_checkpointer *c);
 dlb_status dlb_checkpointer_save(dlb_checkpointer *c, int step_train);
 dlb_status dlb_checkpointer_step(dlb_checkpointer *c, int g, int step_train, int is_top, int force, int *saved);
 dlb_status dlb_checkpointer_load(dlb_checkpointer *c, int *found);
+/* The mini-batch loop around the step: DL::v1::MiniBatch
+ * (v1/data/dataset/minibatch.cpp).  Xm / Ym are the data set's arrays of row
+ * pointers (n_examples rows of seq_w * n_in and seq_w * n_out floats; they must
+ * stay valid while the object lives).  Batches as Set__Desired_Data_Per_Batch
+ * makes them (L:118-190): floor(n_examples / desired_per_batch) of them, at most
+ * max_batches when that is not 0, the last one larger by the remainder as the
+ * reference takes it, (n / desired - batches) * desired in double and truncated
+ * (330 rows in batches of 100 give 100, 100 and 129: the product is 29.99...);
+ * fewer than two batches are refused as in the reference.  Shuffle (L:42-58) is the
+ * reference's Fisher-Yates pass with std::mt19937 and
+ * std::uniform_int_distribution; the reference seeds it from the clock, here
+ * the seed is an argument.  dlb_minibatch_train is MiniBatch::train_mp (L:286-323):
+ * shuffle if asked, then per batch one training step with
+ * update_weights(rows of the batch, rows of the data set) and its loss read;
+ * epoch_time_step + 1; *loss = mean of the batch losses.  Batch k + 1 is
+ * gathered into page-locked memory and copied to the device while batch k
+ * trains (dlb_model_stage_batch).  The accuracy pass of train_mp
+ * (compute_accuracy, an inference pass per batch) is not part of it: run
+ * dlb_model_compute_loss over the rows where it is wanted. */
+typedef struct dlb_minibatch dlb_minibatch;
+dlb_status dlb_minibatch_create(dlb_minibatch **out, dlb_model *model, const float *const *Xm,
+                                const float *const *Ym, size_t n_examples, int use_shuffle,
+                                size_t desired_per_batch, size_t max_batches, unsigned seed);
+dlb_status dlb_minibatch_destroy(dlb_minibatch *mb);
+size_t dlb_minibatch_get_n_batch(const dlb_minibatch *mb);
+size_t dlb_minibatch_examples_per_batch(const dlb_minibatch *mb);
+size_t dlb_minibatch_examples_last_batch(const dlb_minibatch *mb);
+dlb_status dlb_minibatch_set_shuffle(dlb_minibatch *mb, int use_shuffle);
+dlb_status dlb_minibatch_shuffle(dlb_minibatch *mb);
+/* The current order of the rows (MiniBatch::ptr_array_stochastic_index), n = n_examples. */
+dlb_status dlb_minibatch_get_order(const dlb_minibatch *mb, size_t *out, size_t n);
+dlb_status dlb_minibatch_train(dlb_minibatch *mb, double *loss);
+
 /* Model::set_clip_gradient, both overloads (v1/ops/constraints/clip_gradient.cpp
  * L:30-73): whether update_weights clips, and the norm; the norm also sets the
  * default bound of IndRNN recurrent weights, clip(value, 2, 10)^(1/seq_w)

@@ -32,7 +32,7 @@ import numpy as np
 
 import fc_step
 from fc_step import (AF_SOFTMAX, LOSS_CROSS_ENTROPY, NORM_NONE, OracleModel, af_derive, af_fire, brn_backward, brn_forward,
-                     f32, loss_and_delta, optimizer_scalars, optimizer_update)
+                     f32, loss_and_delta, optimizer_scalars, optimizer_update, softmax)
 
 LAYER_FC, LAYER_INDRNN = 3, 4
 
@@ -152,7 +152,7 @@ class IndRnnOracleModel(OracleModel):
                     A[t] = af_fire(l["af"], PRE[t])
                 else:
                     PRE[t] = y
-                    A[t] = af_fire(l["af"], y)
+                    A[t] = softmax(y) if l["af"] == AF_SOFTMAX else af_fire(l["af"], y)
                 # Bernoulli dropout of time step t: flags mask[t * units + u], applied
                 # in place, so that the recurrence of step t + 1 reads the masked
                 # output (fwp_mp.cpp L:1228-1262, L:4842-4868); at inference the

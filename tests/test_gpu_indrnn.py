@@ -96,6 +96,23 @@ def test_clip_gradient_sets_the_recurrent_bound(gpu_ctx):
         assert util.rel_l2(got["params1"], want["params1"]) <= 1e-5
 
 
+@pytest.mark.parametrize("delay", [0, 2], ids=["all_steps", "last_two"])
+def test_softmax_output_in_a_time_stepped_model(gpu_ctx, delay):
+    """Softmax + cross-entropy on the time steps t >= delay: the error against
+    the target of time step 0, the loss against the step's own target, as the
+    reference has them (pinned in tests/test_oracle_indrnn.py)."""
+    from enums import LOSS_FN, OPTIMIZER
+    cfg = configs.indrnn_stack(n_in=64, hidden=128, depth=2, n_out=32, seq_w=4, batch=32, optimizer=OPTIMIZER.ADAM)
+    cfg["layers"][-1]["af"] = ACTIVATION.SOFTMAX
+    cfg = dict(cfg, loss=LOSS_FN.CROSS_ENTROPY, targets="onehot", time_delays=delay)
+    X, Y = configs.synthetic_batch(cfg)
+    p0 = _kink_free(cfg, X)
+    want = util.trace(util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0), cfg, 1, X, Y)
+    got = util.trace(util.build(dlb200.Model(gpu_ctx), cfg, params=p0), cfg, 1, X, Y)
+    assert gpu_ctx.sync() == 0
+    _check(got, want)
+
+
 def test_recurrent_bounds_set_by_hand(gpu_ctx, tmp_path):
     """Per-layer bounds of the recurrent weights: one layer with its own interval,
     one with the clamp off; the bounds survive a save / load, and a default bound

@@ -49,6 +49,48 @@ CASES = [
 ]
 
 
+# (Inverted dropout is left to the entry-point test: the reference's ISRLU
+# derivative (q / x)^3 on the scaled activation q jumps from 1 / keep^3 to 1 at 0.)
+@pytest.mark.parametrize("dropout", [LAYER_DROPOUT.BERNOULLI, None], ids=["bernoulli", "no_dropout"])
+def test_layers_without_normalization_use_the_product_epilogues(gpu_ctx, dropout):
+    """A stack without normalization at tensor-core sizes: from the second step
+    on bias, activation, dropout and the planes of A come out of the forward
+    product's epilogue and the activation derivative out of the input-gradient
+    product's (fewer launches than the first step, whose plane buffers have no
+    scale to predict from); every step agrees with the restatement."""
+    # ISRLU: a continuous derivative, so that no pre-activation of the 786 432 can
+    # sit on a jump where two correct sums take different branches.
+    cfg = configs.deep_brn_mlp(256, 512, 3, 256, 512, af=ACTIVATION.ISRLU, optimizer=OPTIMIZER.ADAM,
+                               dropout=dropout, norm=False)
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    ora = util.build(fc_step.OracleModel(), cfg)
+    p0, seed = ora.get_array("parameters"), 0
+    nw = ora.size("total_weights")
+    p0[:nw] = (np.random.default_rng(0).standard_normal(nw) / np.sqrt(512)).astype(np.float32)
+    want = util.trace(util.build(fc_step.OracleModel(), cfg, params=p0), cfg, 1, X, Y, masks)
+    # The same first step after a step that primed the plane buffers: the
+    # parameters are put back, so the traced step runs the epilogues.
+    model = gpu_model(gpu_ctx, cfg, p0)
+    for li, mk in masks.items():
+        model.set_dropout_mask(li, mk)
+    B = cfg["batch"]
+    counts = []
+    for _ in range(2):
+        before = gpu_ctx.launch_count()
+        model.train_step(B, X, Y)
+        counts.append(gpu_ctx.launch_count() - before)
+    assert counts[1] < counts[0], f"launches per step {counts}: the second step did not fuse"
+    for name in ("first_moment", "second_moment", "second_moment_hat"):
+        model.set_array(name, np.zeros_like(p0))
+    model.set_hparam("optimizer_time_step", 0.0)
+    model.set_array("parameters", p0)
+    got = util.trace(model, cfg, 1, X, Y, masks)
+    assert gpu_ctx.sync() == 0
+    for key, (l2, mx) in util.compare(got, want).items():
+        assert l2 <= TOL_1, f"{key} (weight seed {seed}): rel_l2 {l2:.2e} (rel_max {mx:.2e})"
+
+
 @pytest.mark.parametrize("cfg", CASES, ids=lambda c: c["name"])
 def test_model_one_step_vs_restatement(gpu_ctx, cfg):
     """Activations, errors, gradients, running statistics and updated weights
@@ -149,6 +191,52 @@ def test_staged_batches_train_like_train_step(gpu_ctx):
     np.testing.assert_allclose(got, want, rtol=1e-12)
     assert np.array_equal(a.get_array("parameters"), b.get_array("parameters"))
     assert gpu_ctx.sync() == 0
+
+
+def test_minibatch_epoch_trains_like_the_batches_one_by_one(gpu_ctx):
+    """The mini-batch loop (DL::v1::MiniBatch): 330 rows in batches of 100 are
+    three batches, the last of 129: Set__Desired_Data_Per_Batch takes the
+    remainder from (330 / 100 - 3) * 100 in double, which is 29.99...; an epoch
+    through it gives, bit for bit, the weights of the same batches passed to
+    train_step with the data set's size as training size, the mean of their
+    losses, and one epoch more on the clock of the normalised weight decay."""
+    cfg = configs.deep_brn_mlp(64, 128, 2, 32, 100)
+    N = 330
+    X, Y = configs.synthetic_batch(cfg, batch=N)
+    a = util.build(dlb200.Model(gpu_ctx), cfg, seed=3)
+    b = util.build(dlb200.Model(gpu_ctx), cfg, seed=3)
+    for m in (a, b):
+        m.set_weight_decay(1e-3)
+    mb = dlb200.MiniBatch(b, X, Y, 100)
+    last = 100 + int((N / 100 - 3) * 100)
+    assert last == 129 and (mb.n_batch, mb.per_batch, mb.last_batch) == (3, 100, last)
+    a.set_training_size(N)
+    for epoch in range(2):
+        want = [a.train_step(hi - lo, X[lo:hi], Y[lo:hi]) for lo, hi in ((0, 100), (100, 200), (200, 200 + last))]
+        a.set_hparam("epoch_time_step", a.get_hparam("epoch_time_step") + 1.0)
+        got = mb.train()
+        np.testing.assert_allclose(got, np.mean(want), rtol=1e-12)
+        assert np.array_equal(a.get_array("parameters"), b.get_array("parameters"))
+    assert b.get_hparam("epoch_time_step") == 3.0
+    assert gpu_ctx.sync() == 0
+    # Shuffled: the reference's Fisher-Yates pass; a permutation fixed by the seed.
+    m1, m2 = dlb200.MiniBatch(b, X, Y, 100, use_shuffle=True, seed=7), dlb200.MiniBatch(b, X, Y, 100, use_shuffle=True, seed=7)
+    assert np.array_equal(m1.order(), np.arange(N))
+    m1.shuffle()
+    m2.shuffle()
+    assert np.array_equal(m1.order(), m2.order())
+    assert np.array_equal(np.sort(m1.order()), np.arange(N)) and not np.array_equal(m1.order(), np.arange(N))
+    before = m1.order()
+    loss = m1.train()      # shuffles again, then trains
+    assert np.isfinite(loss) and not np.array_equal(m1.order(), before)
+    m1.set_shuffle(False)
+    assert np.array_equal(m1.order(), np.arange(N))
+    # Refused as in the reference: a batch larger than the data set, fewer than two batches.
+    with pytest.raises(dlb200.DlbError):
+        dlb200.MiniBatch(b, X, Y, N + 1)
+    with pytest.raises(dlb200.DlbError):
+        dlb200.MiniBatch(b, X, Y, 200)
+    assert dlb200.MiniBatch(b, X, Y, 100, max_batches=2).last_batch == 100 + int((N / 100 - 2) * 100)
 
 
 def test_unsupported_configurations_are_refused(gpu_ctx):

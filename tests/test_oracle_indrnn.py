@@ -53,6 +53,28 @@ def test_indrnn_restatement_matches_compiled_reference(cfg, mp):
     _check(got, want)
 
 
+def _softmax_case(delay):
+    cfg = configs.indrnn_stack(n_in=6, hidden=10, depth=2, n_out=5, seq_w=4, batch=7, optimizer=OPTIMIZER.ADAM)
+    cfg["layers"][-1]["af"] = ACTIVATION.SOFTMAX
+    from enums import LOSS_FN
+    return dict(cfg, loss=LOSS_FN.CROSS_ENTROPY, targets="onehot", time_delays=delay)
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("delay", [0, 2], ids=["all_steps", "last_two"])
+def test_softmax_output_reads_the_target_of_time_step_0_like_the_reference(delay):
+    """With a softmax output the reference takes the error of every time step
+    against the target of time step 0 (v1/learner/compute_error_mp.cpp
+    L:237-247) while its loss reads the step's own target."""
+    cfg = _softmax_case(delay)
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    configs.set_recurrent_uniform(ref, cfg)
+    p0 = ref.get_array("parameters")
+    want = util.trace(ref, cfg, steps=3)
+    got = util.trace(util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0), cfg, steps=3)
+    _check(got, want)
+
+
 @pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
 def test_recurrent_weights_are_clamped_like_the_reference():
     """Recurrent weights outside +-2^(1/T) come back inside after one update

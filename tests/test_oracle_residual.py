@@ -69,3 +69,24 @@ def test_residual_evaluation_pass_matches_compiled_reference():
     (lr, ar, qr), (lo, ao, qo) = out
     assert abs(lr - lo) <= 1e-5 * abs(lr) and ar == ao
     assert util.rel_l2(qo, qr) <= TOL_L2
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("delay", [0, 2], ids=["all_steps", "last_step"])
+def test_residual_blocks_in_a_time_stepped_model_match_compiled_reference(delay):
+    """Residual blocks of FC layers with seq_w = 3 (oracle/fc_residual_time.py):
+    statistics of their own per time step, gradients summed over the steps, the
+    softmax error against the target of time step 0."""
+    import fc_residual_time
+    from enums import LAYER, MODEL
+    cfg = configs.residual_mlp(width=8, blocks=2, n_out=5, batch=6)
+    cfg = dict(cfg, model_type=MODEL.RECURRENT, seq_w=3, time_delays=delay, mp=True)
+    for l in cfg["layers"]:
+        if l["type"] == LAYER.RESIDUAL:
+            l.pop("dropout", None)   # the replay of ShakeDrop draws covers feed-forward models
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    p0 = ref.get_array("parameters")
+    X, Y = configs.synthetic_batch(cfg)
+    want = util.trace_noisy(ref, cfg, 3, X, Y)
+    got = util.trace_noisy(util.build(fc_residual_time.ResidualTimeOracleModel(), cfg, params=p0), cfg, 3, X, Y)
+    _check(got, want)
