@@ -344,10 +344,17 @@ dlb_status check_supported(dlb_model *m) {
       // The time-stepped path covers stacks of IndRNN and fully connected
       // layers with batch renormalization between them and Bernoulli dropout
       // (plain or inverted) on their outputs.
+      // Residual blocks of fully connected layers run too (ShakeDrop on the
+      // block, Bernoulli dropout inside it).
       const bool bern = l.dropout == DLB_DROPOUT_BERNOULLI || l.dropout == DLB_DROPOUT_BERNOULLI_INVERTED;
-      if (l.type == DLB_LAYER_RESIDUAL || (l.dropout != DLB_DROPOUT_NONE && !bern)) {
-        set_error("model: layer %zu: residual blocks and dropout other than Bernoulli are outside the "
+      const bool shake = l.type == DLB_LAYER_RESIDUAL && l.dropout == DLB_DROPOUT_SHAKEDROP;
+      if (l.dropout != DLB_DROPOUT_NONE && !bern && !shake) {
+        set_error("model: layer %zu: dropout other than Bernoulli (ShakeDrop on a residual layer) is outside the "
                   "supported path of time-stepped (recurrent) models", i);
+        return DLB_ERR_UNSUPPORTED;
+      }
+      if (l.group == 1 && is_indrnn(l)) {
+        set_error("model: layer %zu: recurrent layers inside a residual block are outside the supported path", i);
         return DLB_ERR_UNSUPPORTED;
       }
       if (is_indrnn(l) && (i + 1 == m->layers.size() || l.af == DLB_AF_SOFTMAX)) {
@@ -548,6 +555,104 @@ dlb_status forward_residual(dlb_model *m, size_t i, const float *X, const float 
                               shake ? res.sd_fwd : nullptr, res.A, res.A_lo, B, (int)res.units);
 }
 
+// The time-stepped counterparts of norm_statistics / norm_backward: statistics
+// and running averages of their own per time step ([T, units] arrays), all time
+// steps in one launch each.
+dlb_status norm_statistics_time(dlb_model *m, LayerRT &l, const float *in, int T, int B, dlb_brn_unit_arrays *u) {
+  if (m->propagation == DLB_PROPAGATION_INFERENCE) return inference_arrays(m, l, u);
+  const int Bg = (int)(m->global_rows ? m->global_rows : (size_t)B);
+  const int n = (int)l.norm_units;
+  *u = unit_arrays(m, l, 0);
+  DLB_TRY(dlb_brn_time_forward_sums(m->ctx, in, T, B, n, l.fwd_sums));
+  DLB_TRY(dlb_allreduce_f64(m->ctx, l.fwd_sums, 2 * (size_t)T * n));
+  return dlb_brn_time_forward_finalize(m->ctx, l.fwd_sums, Bg, T, n, m->hp.normalization_momentum_average,
+                                       m->hp.normalization_epsilon, r_max_of(m, l), d_max_of(m, l), u);
+}
+
+// `e` [T, B, n] holds dA on entry and the error w.r.t. `in` on return.
+dlb_status norm_backward_time(dlb_model *m, LayerRT &l, float *e, float *e_lo, const float *in, const float *act,
+                              int af, int T, int B) {
+  const int Bg = (int)(m->global_rows ? m->global_rows : (size_t)B);
+  const int n = (int)l.norm_units;
+  const size_t plane = (size_t)T * n;
+  dlb_brn_unit_arrays u = unit_arrays(m, l, 0);
+  DLB_TRY(dlb_indrnn_backward_walk(m->ctx, e, in, act, &u, nullptr, af, T, B, n));
+  DLB_TRY(dlb_indrnn_backward_sums(m->ctx, e, in, act, &u, 0, T, B, n, l.bwd_sums));
+  DLB_TRY(dlb_time_fold(m->ctx, l.bwd_sums, T, n, m->grads + gamma_index(m, l)));
+  DLB_TRY(dlb_time_fold(m->ctx, l.bwd_sums + plane, T, n, m->grads + beta_index(m, l)));
+  DLB_TRY(dlb_allreduce_f64(m->ctx, l.bwd_sums + 2 * plane, 2 * plane));
+  return dlb_brn_time_backward_apply(m->ctx, e, e_lo, in, &u, l.bwd_sums, Bg, T, B, n);
+}
+
+// A residual block inside a time-stepped model
+// (Recurrent__Forward_Pass__Residual__OpenMP and ..__Residual__Layer__OpenMP,
+// v1/learner/fwp_rec_mp.cpp L:510-700): the block's FC layers have no recurrent
+// connections, so all T * B rows go through each product at once; what is per
+// time step are the normalization statistics, the Bernoulli masks
+// (mask[t * width + unit]) and the ShakeDrop flags (flag[t * B + b],
+// fwp_mp.cpp L:4935-4955), which the [T, B, width] layout turns into row flags
+// of the T * B rows.
+dlb_status forward_residual_time(dlb_model *m, size_t i, const float *X, const float *X_lo, int B, int T) {
+  LayerRT &res = m->layers[i];
+  const bool inference = m->propagation == DLB_PROPAGATION_INFERENCE;
+  const int TB = T * B;
+  const float *in = X, *in_lo = X_lo;
+  const float *prev_sums = nullptr;
+  for (size_t j = 1; j <= res.depth; ++j) {
+    LayerRT &b = m->layers[i + j];
+    const bool norm = b.norm != DLB_NORM_NONE;
+    if (!b.block_input) {
+      dlb_brn_unit_arrays u{};
+      if (norm) DLB_TRY(norm_statistics_time(m, b, prev_sums, T, B, &u));
+      const uint8_t *mask = nullptr;
+      float keep_scale = 1.f;
+      if (b.dropout != DLB_DROPOUT_NONE) {
+        if (inference) {
+          if (b.dropout == DLB_DROPOUT_BERNOULLI) keep_scale = b.dropout_value;
+        } else {
+          mask = b.mask;
+          if (b.dropout == DLB_DROPOUT_BERNOULLI_INVERTED)
+            keep_scale = b.dropout_value == 0.f ? 0.f : 1.f / b.dropout_value;
+        }
+      }
+      if (norm || mask || keep_scale != 1.f)
+        DLB_TRY(dlb_indrnn_forward_dropout(m->ctx, prev_sums, norm ? &u : nullptr, nullptr, b.af, mask, keep_scale,
+                                           b.IN, b.IN_lo, T, B, (int)b.fan_in));
+      else
+        DLB_TRY(dlb_activation_forward(m->ctx, prev_sums, nullptr, b.af, nullptr, b.IN, b.IN_lo, TB, (int)b.fan_in));
+      in = b.IN;
+      in_lo = b.IN_lo;
+    }
+    const float *bias = norm ? nullptr : m->params + b.first_bias;
+    DLB_TRY(dlb_fc_forward(m->ctx, in, in_lo, m->params + b.first_conn, m->params_lo + b.first_conn, bias, b.A, TB,
+                           (int)b.fan_in, (int)b.units));
+    prev_sums = b.A;
+  }
+  LayerRT &last = m->layers[i + res.depth];
+  float *block = last.A;
+  const bool scale = inference && res.dropout == DLB_DROPOUT_SHAKEDROP;
+  if (res.norm != DLB_NORM_NONE || scale) {
+    dlb_brn_unit_arrays u{};
+    if (res.norm != DLB_NORM_NONE) DLB_TRY(norm_statistics_time(m, res, last.A, T, B, &u));
+    DLB_TRY(dlb_indrnn_forward_dropout(m->ctx, last.A, res.norm != DLB_NORM_NONE ? &u : nullptr, nullptr,
+                                       DLB_AF_LINEAR, nullptr, scale ? 1.f - res.dropout_value : 1.f, last.delta,
+                                       nullptr, T, B, (int)last.units));
+    block = last.delta;
+  }
+  const bool shake = !inference && res.dropout == DLB_DROPOUT_SHAKEDROP;
+  if (shake && (!res.sd_mask || res.sd_rows < (size_t)TB)) {
+    set_error("model: residual layer %zu uses ShakeDrop but no noise was set for %d rows (seq_w * rows; "
+              "dlb_model_set_shakedrop_noise)", i, TB);
+    return DLB_ERR_INVALID;
+  }
+  if (last.units != res.fan_in)
+    return dlb_residual_forward_padded(m->ctx, X, (int)res.fan_in, block, (int)last.units,
+                                       shake ? res.sd_mask : nullptr, shake ? res.sd_fwd : nullptr, res.A,
+                                       res.A_lo, TB);
+  return dlb_residual_forward(m->ctx, X, block, shake ? res.sd_mask : nullptr, shake ? res.sd_fwd : nullptr,
+                              res.A, res.A_lo, TB, (int)res.units);
+}
+
 // Time-stepped forward, layer-major as the reference
 // (RNN__Forward_Pass_Batch__OpenMP, v1/learner/fwp_rec_mp.cpp L:29-110): one
 // GEMM over all T * rows rows of a layer, statistics for every time step in one
@@ -560,6 +665,13 @@ dlb_status forward_layers_time(dlb_model *m, size_t rows) {
   const float *X = m->input, *X_lo = m->input_lo;
   for (size_t i = 1; i < m->layers.size(); ++i) {
     LayerRT &l = m->layers[i];
+    if (l.type == DLB_LAYER_RESIDUAL) {
+      DLB_TRY(forward_residual_time(m, i, X, X_lo, B, T));
+      X = l.A;
+      X_lo = l.A_lo;
+      i += l.depth;
+      continue;
+    }
     const int I = (int)l.fan_in, H = (int)l.units;
     const bool norm = l.norm != DLB_NORM_NONE;
     const bool last = i + 1 == m->layers.size();
@@ -1425,6 +1537,34 @@ static dlb_status backward_residual(dlb_model *m, size_t i, int B) {
   return DLB_OK;
 }
 
+// Backward of a residual block inside a time-stepped model: backward_residual
+// over the T * B rows with the per-time-step normalization backward.
+static dlb_status backward_residual_time(dlb_model *m, size_t i, int B, int T) {
+  LayerRT &res = m->layers[i];
+  LayerRT &last = m->layers[i + res.depth];
+  const int TB = T * B;
+  const bool shake = res.dropout == DLB_DROPOUT_SHAKEDROP;
+  const bool rnorm = res.norm != DLB_NORM_NONE;
+  const int first = last.units < res.units ? (int)res.pad : 0;
+  DLB_TRY(dlb_shakedrop_backward_window(m->ctx, res.delta, (int)res.units, first, shake ? res.sd_mask : nullptr,
+                                        shake ? res.sd_bwd : nullptr, last.delta,
+                                        rnorm ? nullptr : last.delta_lo, TB, (int)last.units));
+  if (rnorm) DLB_TRY(norm_backward_time(m, res, last.delta, last.delta_lo, last.A, last.A, DLB_AF_LINEAR, T, B));
+  for (size_t j = res.depth; j >= 2; --j) {
+    LayerRT &b = m->layers[i + j];
+    LayerRT &prev = m->layers[i + j - 1];
+    DLB_TRY(dlb_fc_backward_input(m->ctx, b.delta, b.delta_lo, m->params + b.first_conn, m->params_lo + b.first_conn,
+                                  prev.delta, TB, (int)b.fan_in, (int)b.units));
+    if (b.norm != DLB_NORM_NONE) {
+      DLB_TRY(norm_backward_time(m, b, prev.delta, prev.delta_lo, prev.A, b.IN, b.af, T, B));
+    } else {
+      DLB_TRY(dlb_activation_backward(m->ctx, prev.delta, prev.A, b.IN, nullptr, b.af, TB, (int)b.fan_in, nullptr));
+      DLB_TRY(dlb_split_planes_2d(m->ctx, prev.delta, prev.delta_lo, TB, (int)b.fan_in));
+    }
+  }
+  return DLB_OK;
+}
+
 // ref: Model::RNN__Backward_Pass_Batch__OpenMP (v1/learner/bwp_rec_mp.cpp
 // L:29-110) with Backward_Pass__FC__DF_Ind_RNN__OpenMP (bwp_mp.cpp L:1188-1263)
 // and the recurrent-weight gradient of update_derivative_rec_mp.cpp L:460-487,
@@ -1434,13 +1574,33 @@ static dlb_status backward_pass_time(dlb_model *m, size_t rows) {
   const int B = (int)rows, T = (int)m->seq_w;
   const int TB = T * B;
   const int Bg = (int)(m->global_rows ? m->global_rows : rows);
-  for (size_t i = m->layers.size() - 1; i >= 1; --i) {
+  const std::vector<size_t> tops = top_level(m);
+  for (size_t pos = tops.size() - 1; pos >= 1; --pos) {
+    const size_t i = tops[pos];
     LayerRT &l = m->layers[i];
+    LayerRT *below = pos > 1 ? &m->layers[tops[pos - 1]] : nullptr;  // the error into the input layer is never formed
+    if (l.type == DLB_LAYER_RESIDUAL) {
+      DLB_TRY(backward_residual_time(m, i, B, T));
+      if (below) {
+        // shortcut error (its window of the residual layer's error) + delta_1 W_1
+        LayerRT &first = m->layers[i + 1];
+        const size_t first_col = l.fan_in < l.units ? l.pad : 0;
+        DLB_CUDA(cudaMemcpy2DAsync(below->delta, l.fan_in * sizeof(float), l.delta + first_col,
+                                   l.units * sizeof(float), l.fan_in * sizeof(float), (size_t)TB,
+                                   cudaMemcpyDeviceToDevice, m->ctx->stream));
+        GemmOperand A{first.delta, first.delta_lo, (long long)first.units, 1};
+        GemmOperand Bo{m->params + first.first_conn, m->params_lo + first.first_conn, 1, (long long)first.fan_in};
+        GemmEpilogue ep;
+        ep.accumulate = 1;
+        DLB_TRY(gemm(m->ctx, A, Bo, below->delta, (long long)first.fan_in, TB, (int)first.fan_in, (int)first.units, ep));
+      }
+      continue;
+    }
     const int H = (int)l.units;
     const bool norm = l.norm != DLB_NORM_NONE, rec = is_indrnn(l);
     // Rows of this layer's error that can be non-zero.
     size_t first_row = 0;
-    if (i + 1 == m->layers.size()) {
+    if (pos + 1 == tops.size()) {
       first_row = m->n_time_delay * rows;
     } else if (norm || rec) {  // hidden layer: l.delta holds dA
       const float *u_rec = rec ? m->params + l.first_recurrent : nullptr;
@@ -1465,14 +1625,13 @@ static dlb_status backward_pass_time(dlb_model *m, size_t rows) {
       DLB_TRY(dlb_activation_backward(m->ctx, l.delta, l.Z, l.A, nullptr, l.af, TB, H, nullptr));
       DLB_TRY(dlb_split_planes_2d(m->ctx, l.delta, l.delta_lo, TB, H));
     }
-    if (i == 1) break;  // the error into the input layer is never formed
-    LayerRT &below = m->layers[i - 1];
+    if (!below) break;
     const size_t I = l.fan_in;
-    if (first_row) DLB_TRY(dlb_memset(m->ctx, below.delta, 0, first_row * I * sizeof(float)));
+    if (first_row) DLB_TRY(dlb_memset(m->ctx, below->delta, 0, first_row * I * sizeof(float)));
     if (first_row < (size_t)TB)
       DLB_TRY(dlb_fc_backward_input(m->ctx, l.delta + first_row * H, l.delta_lo + first_row * H,
                                     m->params + l.first_conn, m->params_lo + l.first_conn,
-                                    below.delta + first_row * I, TB - (int)first_row, (int)I, H));
+                                    below->delta + first_row * I, TB - (int)first_row, (int)I, H));
   }
   return DLB_OK;
 }
@@ -1540,9 +1699,15 @@ dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows) {
 // sums of a layer are one GEMM whose reduction runs over all T * rows rows.
 static dlb_status update_derivatives_time(dlb_model *m, size_t rows) {
   const size_t TB = m->seq_w * rows;
-  const float *X = m->input, *X_lo = m->input_lo;
+  const float *top = m->input, *top_lo = m->input_lo;  // output of the top-level layer below
   for (size_t i = 1; i < m->layers.size(); ++i) {
     LayerRT &l = m->layers[i];
+    if (l.type == DLB_LAYER_RESIDUAL) continue;  // its block layers follow; its output is set after them
+    const float *X = top, *X_lo = top_lo;
+    if (l.group == 1 && !l.block_input) {
+      X = l.IN;
+      X_lo = l.IN_lo;
+    }
     const size_t H = l.units, I = l.fan_in;
     // The output layer's error is zero before the first step that has a target.
     const size_t first_row = i + 1 == m->layers.size() ? m->n_time_delay * rows : 0;
@@ -1552,8 +1717,16 @@ static dlb_status update_derivatives_time(dlb_model *m, size_t rows) {
                                    dbias, (int)(TB - first_row), (int)I, (int)H, m->grads_clean ? 0 : 1));
     if (m->overlap_grad_allreduce)
       DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
-    X = l.A;
-    X_lo = l.A_lo;
+    if (l.group == 0) {
+      top = l.A;
+      top_lo = l.A_lo;
+    } else if (i + 1 < m->layers.size() && m->layers[i + 1].group == 0) {
+      // last layer of a block: what follows reads the residual layer's output
+      size_t r = i;
+      while (m->layers[r].type != DLB_LAYER_RESIDUAL) --r;
+      top = m->layers[r].A;
+      top_lo = m->layers[r].A_lo;
+    }
   }
   m->grads_clean = false;
   return DLB_OK;

@@ -135,3 +135,45 @@ def test_blocks_of_another_width_than_the_shortcut(gpu_ctx, width, block_width):
     assert gpu_ctx.sync() == 0
     _check(got, want)
     assert mod.layer_info(1)["n_out"] == max(width, block_width)
+
+
+@pytest.mark.parametrize("delay", [0, 2], ids=["all_steps", "last_step"])
+@pytest.mark.parametrize("width,block_width", [(256, 256), (128, 192)], ids=["equal", "padded"])
+def test_residual_blocks_in_a_time_stepped_model(gpu_ctx, delay, width, block_width):
+    """Residual blocks of FC layers with seq_w = 3: statistics, Bernoulli masks
+    and ShakeDrop flags of their own per time step, the products over all
+    T * rows rows at once; against the CPU restatement (which is pinned to the
+    compiled reference in tests/test_oracle_residual.py), ShakeDrop noise as
+    arrays of seq_w * rows rows given to both."""
+    import fc_residual_time
+    from enums import ACTIVATION, LAYER, LAYER_DROPOUT, MODEL
+    T, B = 3, 128
+    cfg = configs.residual_mlp(width=width, blocks=2, n_out=10, batch=B, block_width=block_width)
+    cfg = dict(cfg, model_type=MODEL.RECURRENT, seq_w=T, time_delays=delay)
+    for l in cfg["layers"]:
+        if l["type"] == LAYER.FULLY_CONNECTED and l.get("norm"):
+            l["af"] = ACTIVATION.ISRLU     # a continuous derivative: no branch for two correct sums to differ on
+            l["dropout"] = (LAYER_DROPOUT.BERNOULLI, 0.8)
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    rng = np.random.default_rng(11)
+    noise = {}
+    for li, p in configs.shakedrop_layers(cfg):
+        noise[li] = ((rng.random(T * B) < max(p, 0.3)).astype(np.uint8),
+                     (rng.random((T * B, block_width)) * 2 - 1).astype(np.float32),
+                     rng.random((T * B, block_width)).astype(np.float32))
+    ora = util.build(fc_residual_time.ResidualTimeOracleModel(), cfg)
+    p0 = ora.get_array("parameters")
+    nw = ora.size("total_weights")
+    p0[:nw] = (np.random.default_rng(0).standard_normal(nw) / np.sqrt(width)).astype(np.float32)
+
+    def run(model):
+        for li, (mk, fw, bw) in noise.items():
+            model.set_shakedrop_noise(li, mk, fw, bw)
+        return util.trace(model, cfg, 1, X, Y, masks)
+
+    want = run(util.build(fc_residual_time.ResidualTimeOracleModel(), cfg, params=p0))
+    got = run(util.build(dlb200.Model(gpu_ctx), cfg, params=p0))
+    assert gpu_ctx.sync() == 0
+    residual = {f"delta{li}" for li, l in enumerate(cfg["layers"]) if l["type"] == LAYER.RESIDUAL}
+    _check(got, want, skip=residual)
