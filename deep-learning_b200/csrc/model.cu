@@ -348,9 +348,10 @@ dlb_status check_supported(dlb_model *m) {
       // block, Bernoulli dropout inside it).
       const bool bern = l.dropout == DLB_DROPOUT_BERNOULLI || l.dropout == DLB_DROPOUT_BERNOULLI_INVERTED;
       const bool shake = l.type == DLB_LAYER_RESIDUAL && l.dropout == DLB_DROPOUT_SHAKEDROP;
-      if (l.dropout != DLB_DROPOUT_NONE && !bern && !shake) {
-        set_error("model: layer %zu: dropout other than Bernoulli (ShakeDrop on a residual layer) is outside the "
-                  "supported path of time-stepped (recurrent) models", i);
+      const bool uout = l.dropout == DLB_DROPOUT_UOUT && l.group == 0 && l.type != DLB_LAYER_RESIDUAL;
+      if (l.dropout != DLB_DROPOUT_NONE && !bern && !shake && !uout) {
+        set_error("model: layer %zu: dropout other than Bernoulli, UOut on a layer outside a block and ShakeDrop "
+                  "on a residual layer is outside the supported path of time-stepped (recurrent) models", i);
         return DLB_ERR_UNSUPPORTED;
       }
       if (l.group == 1 && is_indrnn(l)) {
@@ -707,9 +708,17 @@ dlb_status forward_layers_time(dlb_model *m, size_t rows) {
             keep_scale = l.dropout_value == 0.f ? 0.f : 1.f / l.dropout_value;
         }
       }
-      DLB_TRY(dlb_indrnn_forward_dropout(m->ctx, l.Z, norm ? &u : nullptr,
-                                         is_indrnn(l) ? m->params + l.first_recurrent : nullptr, l.af, mask,
-                                         keep_scale, l.A, last ? nullptr : l.A_lo, T, B, H));
+      if (l.dropout == DLB_DROPOUT_UOUT && !last && m->propagation != DLB_PROPAGATION_INFERENCE) {
+        // Draws for all T * B rows, [T, B, H] (an input of the step like the masks).
+        DLB_TRY(uout_ready(m, l, i, TB));
+        DLB_TRY(dlb_indrnn_forward_uout(m->ctx, l.Z, norm ? &u : nullptr,
+                                        is_indrnn(l) ? m->params + l.first_recurrent : nullptr, l.af, l.uout, l.A,
+                                        l.A_lo, T, B, H));
+      } else {
+        DLB_TRY(dlb_indrnn_forward_dropout(m->ctx, l.Z, norm ? &u : nullptr,
+                                           is_indrnn(l) ? m->params + l.first_recurrent : nullptr, l.af, mask,
+                                           keep_scale, l.A, last ? nullptr : l.A_lo, T, B, H));
+      }
     } else {
       DLB_TRY(dlb_activation_forward(m->ctx, l.Z, nullptr, l.af, nullptr, l.A, last ? nullptr : l.A_lo,
                                      TB, H));

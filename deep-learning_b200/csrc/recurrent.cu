@@ -270,7 +270,7 @@ __device__ __forceinline__ Vec<W> normalised(const Vec<W> &z, const TimeBrn &u, 
 template <int W, bool NORM, bool REC, bool DROP>
 __global__ void __launch_bounds__(256)
     time_forward_kernel(const float *__restrict__ Z, TimeBrn u, const float *__restrict__ rec, int af,
-                        const uint8_t *__restrict__ mask, float keep_scale,
+                        const uint8_t *__restrict__ mask, float keep_scale, const float *__restrict__ noise,
                         float *__restrict__ A, float *__restrict__ A_lo, int T, int rows, int n,
                         unsigned *amax) {
   pdl_enter();
@@ -299,6 +299,8 @@ __global__ void __launch_bounds__(256)
       const float pre = (REC && t > 0) ? recur(y.v[j], w[j], h[j]) : y.v[j];
       h[j] = af_fire(af, pre);
       if (DROP) {
+        // UOut: h += h * U(-beta, beta), a draw per element (fwp_mp.cpp L:4959-4985).
+        if (noise) h[j] = h[j] + h[j] * noise[o + j];
         const float f = mask ? (mask[(size_t)t * n + col + j] ? keep_scale : 0.f) : keep_scale;
         h[j] = f == 0.f ? 0.f : (f == 1.f ? h[j] : h[j] * f);
       }
@@ -475,7 +477,8 @@ dlb_status dlb_brn_time_forward_finalize(dlb_ctx *ctx, const double *sums, int g
 
 dlb_status indrnn_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
                               const float *recurrent, int af, const uint8_t *mask, float keep_scale,
-                              float *A, float *A_lo, int seq_w, int rows, int n, unsigned *amax) {
+                              const float *noise, float *A, float *A_lo, int seq_w, int rows, int n,
+                              unsigned *amax) {
   DLB_REQUIRE(ctx && Z && A && seq_w > 0 && rows > 0 && n > 0, "dlb_indrnn_forward");
   TimeBrn p{};
   if (u) {
@@ -484,13 +487,13 @@ dlb_status indrnn_forward_impl(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_
   }
   const bool v4 = n % 4 == 0 && aligned16({Z, A, A_lo, p.mean, p.rs, p.d});
   const int grid = walk_grid((size_t)rows * (v4 ? n / 4 : n));
-  const bool drop = mask != nullptr || keep_scale != 1.f;
+  const bool drop = mask != nullptr || keep_scale != 1.f || noise != nullptr;
 #define LAUNCH(W, NORM, REC)                                                                          \
   do {                                                                                                \
     if (drop)                                                                                         \
-      DLB_LAUNCH_KERNEL(ctx, (time_forward_kernel<W, NORM, REC, true>), grid, 256, 0, Z, p, recurrent, af, mask, keep_scale, A, A_lo, seq_w, rows, n, amax);                      \
+      DLB_LAUNCH_KERNEL(ctx, (time_forward_kernel<W, NORM, REC, true>), grid, 256, 0, Z, p, recurrent, af, mask, keep_scale, noise, A, A_lo, seq_w, rows, n, amax);                      \
     else                                                                                              \
-      DLB_LAUNCH_KERNEL(ctx, (time_forward_kernel<W, NORM, REC, false>), grid, 256, 0, Z, p, recurrent, af, nullptr, 1.f, A, A_lo, seq_w, rows, n, amax);                          \
+      DLB_LAUNCH_KERNEL(ctx, (time_forward_kernel<W, NORM, REC, false>), grid, 256, 0, Z, p, recurrent, af, nullptr, 1.f, nullptr, A, A_lo, seq_w, rows, n, amax);                          \
   } while (0)
 #define PICK(W)                                                        \
   do {                                                                 \
@@ -625,7 +628,7 @@ dlb_status dlb_indrnn_forward(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_a
   const size_t total = (size_t)(seq_w > 0 ? seq_w : 0) * (rows > 0 ? rows : 0) * (n > 0 ? n : 0);
   TimePlanes p;
   DLB_TRY(p.begin(ctx, A, A_lo, total / (size_t)(n > 0 ? n : 1), n));
-  DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, nullptr, 1.f, A, p.kernel_arg, seq_w, rows, n, p.amax));
+  DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, nullptr, 1.f, nullptr, A, p.kernel_arg, seq_w, rows, n, p.amax));
   return p.finish(ctx);
 }
 
@@ -635,7 +638,18 @@ dlb_status dlb_indrnn_forward_dropout(dlb_ctx *ctx, const float *Z, const dlb_br
   const size_t total = (size_t)(seq_w > 0 ? seq_w : 0) * (rows > 0 ? rows : 0) * (n > 0 ? n : 0);
   TimePlanes p;
   DLB_TRY(p.begin(ctx, A, A_lo, total / (size_t)(n > 0 ? n : 1), n));
-  DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, mask, keep_scale, A, p.kernel_arg, seq_w, rows, n, p.amax));
+  DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, mask, keep_scale, nullptr, A, p.kernel_arg, seq_w, rows, n, p.amax));
+  return p.finish(ctx);
+}
+
+dlb_status dlb_indrnn_forward_uout(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
+                                   const float *recurrent, int af, const float *noise, float *A, float *A_lo,
+                                   int seq_w, int rows, int n) {
+  DLB_REQUIRE(noise, "dlb_indrnn_forward_uout: UOut needs its draws");
+  const size_t total = (size_t)(seq_w > 0 ? seq_w : 0) * (rows > 0 ? rows : 0) * (n > 0 ? n : 0);
+  TimePlanes p;
+  DLB_TRY(p.begin(ctx, A, A_lo, total / (size_t)(n > 0 ? n : 1), n));
+  DLB_TRY(indrnn_forward_impl(ctx, Z, u, recurrent, af, nullptr, 1.f, noise, A, p.kernel_arg, seq_w, rows, n, p.amax));
   return p.finish(ctx);
 }
 

@@ -89,6 +89,7 @@ SIGNATURES = {
     "dlb_brn_time_forward_finalize": (_i, [_vp, _vp, _i, _i, _i, _f, _f, _f, _f, C.POINTER(BrnUnitArrays)]),
     "dlb_indrnn_forward": (_i, [_vp, _vp, C.POINTER(BrnUnitArrays), _vp, _i, _vp, _vp, _i, _i, _i]),
     "dlb_indrnn_forward_dropout": (_i, [_vp, _vp, C.POINTER(BrnUnitArrays), _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i]),
+    "dlb_indrnn_forward_uout": (_i, [_vp, _vp, C.POINTER(BrnUnitArrays), _vp, _i, _vp, _vp, _vp, _i, _i, _i]),
     "dlb_indrnn_backward_walk": (_i, [_vp, _vp, _vp, _vp, C.POINTER(BrnUnitArrays), _vp, _i, _i, _i, _i]),
     "dlb_indrnn_backward_sums": (_i, [_vp, _vp, _vp, _vp, C.POINTER(BrnUnitArrays), _i, _i, _i, _i, _vp]),
     "dlb_time_fold": (_i, [_vp, _vp, _i, _i, _vp]),

@@ -388,6 +388,14 @@ dlb_status dlb_indrnn_forward_dropout(dlb_ctx *ctx, const float *Z, const dlb_br
                                       float keep_scale, float *A, float *A_lo, int seq_w, int rows,
                                       int n);
 
+/* The same walk with UOut: the output of time step t becomes h + h * noise[t,
+ * row, unit] (draws of U(-beta, beta), [seq_w, rows, n]) before it is stored and
+ * before the recurrence of step t + 1 reads it (fwp_mp.cpp L:1252-1257,
+ * L:4959-4985). */
+dlb_status dlb_indrnn_forward_uout(dlb_ctx *ctx, const float *Z, const dlb_brn_unit_arrays *u,
+                                   const float *recurrent, int af, const float *noise, float *A, float *A_lo,
+                                   int seq_w, int rows, int n);
+
 /* E holds dA on entry and dAF on return, t from seq_w-1 down to 0:
  *   f'_t = f'(pre_t, A_t), dAF_t = dA_t f'_t + recurrent f'_t dAF_{t+1}.
  * ref: Backward_Pass__FC__DF_Ind_RNN__OpenMP (v1/learner/bwp_mp.cpp L:1188-1263). */

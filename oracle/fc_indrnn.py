@@ -158,6 +158,11 @@ class IndRnnOracleModel(OracleModel):
                 # output (fwp_mp.cpp L:1228-1262, L:4842-4868); at inference the
                 # keep probability scales instead (fwp_rec_mp.cpp L:299-312).
                 kind, value = l["dropout"]
+                if kind == fc_step.DROPOUT_UOUT and i + 1 < len(self.layers) and self.training:
+                    # UOut of time step t, in place like the masks: draws [T * batch, units],
+                    # rows t * batch .. of them (fwp_mp.cpp L:1252-1257, L:4959-4985).
+                    nz = l["noise"].reshape(T, -1, H)[t, :batch]
+                    A[t] = fc_step.apply_dropout(A[t], kind, value, None, nz)
                 if kind in (fc_step.DROPOUT_BERNOULLI, fc_step.DROPOUT_BERNOULLI_INVERTED) and i + 1 < len(self.layers):
                     if not self.training:
                         if kind == fc_step.DROPOUT_BERNOULLI:

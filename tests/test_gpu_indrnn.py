@@ -338,9 +338,27 @@ def test_bernoulli_dropout_through_time(gpu_ctx, kind, norm):
     assert util.rel_l2(out[1], out[0]) <= 1e-5
 
 
-def test_other_dropout_in_a_time_stepped_model_is_refused(gpu_ctx):
-    cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=1, n_out=5, seq_w=4, batch=3)
-    m = util.build(dlb200.Model(gpu_ctx), cfg)
-    m.set_dropout(1, LAYER_DROPOUT.UOUT, 0.5, False)
+def test_uout_in_a_time_stepped_model(gpu_ctx):
+    """UOut on IndRNN layers: the output of a time step becomes h + h * draw before
+    the next step's recurrence reads it; draws [seq_w * rows, units] are inputs of
+    the step (the restatement is pinned to the compiled reference with the
+    reference's own draws in tests/test_oracle_indrnn.py).  Without draws the step
+    is refused."""
+    T, B, H = 4, 32, 128
+    cfg = configs.indrnn_stack(n_in=64, hidden=H, depth=2, n_out=32, seq_w=T, batch=B,
+                               dropout=(LAYER_DROPOUT.UOUT, 0.25))
+    X, Y = configs.synthetic_batch(cfg)
+    p0 = _kink_free(configs.indrnn_stack(n_in=64, hidden=H, depth=2, n_out=32, seq_w=T, batch=B), X)
+    rng = np.random.default_rng(5)
+    noise = {li: ((rng.random((T * B, H)) * 2 - 1) * 0.25).astype(np.float32) for li in (1, 2)}
+    out = []
+    for model in (util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0),
+                  util.build(dlb200.Model(gpu_ctx), cfg, params=p0)):
+        for li, nz in noise.items():
+            model.set_uout_noise(li, nz)
+        out.append(util.trace(model, cfg, 1, X, Y))
+    assert gpu_ctx.sync() == 0
+    _check(out[1], out[0])
+    bare = util.build(dlb200.Model(gpu_ctx), cfg, params=p0)
     with pytest.raises(dlb200.DlbError):
-        m.forward_pass(3, np.zeros((3, 24), np.float32))
+        bare.forward_pass(B, X)

@@ -53,6 +53,30 @@ def test_indrnn_restatement_matches_compiled_reference(cfg, mp):
     _check(got, want)
 
 
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+def test_uout_in_a_time_stepped_model_like_the_reference():
+    """UOut on IndRNN layers against the compiled reference, which draws its
+    noise itself: layer by layer, inside a layer time step by time step, row by
+    row (the serial order), replayed from the same seed."""
+    from enums import LAYER_DROPOUT
+    T, B, H = 4, 5, 8
+    cfg = dict(configs.indrnn_stack(n_in=6, hidden=H, depth=2, n_out=5, seq_w=T, batch=B,
+                                    dropout=(LAYER_DROPOUT.UOUT, 0.3)), mp=False)
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    configs.set_recurrent_uniform(ref, cfg)
+    p0 = ref.get_array("parameters")
+    ora = util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0)
+    X, Y = configs.synthetic_batch(cfg)
+    for step in range(3):
+        ref.seed_uout(100 + step)
+        noise = ref_binding.uout_draws(100 + step, [0.3, 0.3], T * B, [H, H])
+        ora.set_uout_noise(1, noise[0])
+        ora.set_uout_noise(2, noise[1])
+        want = util.trace(ref, cfg, 1, X, Y)
+        got = util.trace(ora, cfg, 1, X, Y)
+        _check(got, want)
+
+
 def _softmax_case(delay):
     cfg = configs.indrnn_stack(n_in=6, hidden=10, depth=2, n_out=5, seq_w=4, batch=7, optimizer=OPTIMIZER.ADAM)
     cfg["layers"][-1]["af"] = ACTIVATION.SOFTMAX
