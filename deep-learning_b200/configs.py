@@ -111,6 +111,27 @@ def indrnn_stack(n_in=512, hidden=2048, depth=4, n_out=512, seq_w=256, batch=102
     )
 
 
+def lstm_stack(n_in=16, blocks=8, cells=2, depth=1, n_out=8, seq_w=4, batch=8, optimizer=OPTIMIZER.ADAM,
+               hidden_fc=None, af=ACTIVATION.LINEAR):
+    """`depth` LSTM layers of `blocks` memory blocks with `cells` cells each
+    (peephole connections, tanh / sigmoid as the reference fixes them), optionally
+    a fully connected layer of `hidden_fc` units in front, a fully connected
+    output layer with activation `af`, MSE on every time step, Adam."""
+    layers = [dict(type=LAYER.FULLY_CONNECTED, units=n_in)]
+    if hidden_fc:
+        layers.append(dict(type=LAYER.FULLY_CONNECTED, units=hidden_fc, af=ACTIVATION.ISRLU))
+    for _ in range(depth):
+        layers.append(dict(type=LAYER.LSTM, units=blocks, cells=cells))
+    layers.append(dict(type=LAYER.FULLY_CONNECTED, units=n_out, af=af))
+    return dict(
+        name=f"lstm_{n_in}-{depth}x{blocks}x{cells}-{n_out}_T{seq_w}_b{batch}",
+        model_type=MODEL.RECURRENT, seq_w=seq_w, time_delays=0, layers=layers,
+        loss=LOSS_FN.MSE, optimizer=optimizer,
+        hparams=dict(adam_learning_rate=1e-3, adam_beta1=0.9, adam_beta2=0.999, adam_epsilon=1e-8),
+        batch=batch, weight_seed=0, data_seed=0, inputs="normal", targets="normal", mp=False,
+    )
+
+
 def recurrent_slices(cfg):
     """[(layer index, slice of the flat parameter vector)] of the recurrent
     weights: an IndRNN layer's u[units] follows its W[units, fan_in]
@@ -156,8 +177,12 @@ def build_model(m, cfg, batch=None):
     """Calls the reference's construction sequence on ``m``
     (run/deep-learning/mnist.cpp L:43-80 is the model for the order)."""
     layers = cfg["layers"]
+    extra = {}
+    if any(l.get("cells") for l in layers):
+        # LSTM layers: `units` memory blocks of `cells` cells (Layer_Parameters::unit_parameters[0], [1]).
+        extra["layer_units2"] = [l.get("cells", 0) for l in layers]
     m.compile([l["type"] for l in layers], [l["units"] for l in layers],
-              seq_w=cfg.get("seq_w", 1), model_type=cfg["model_type"])
+              seq_w=cfg.get("seq_w", 1), model_type=cfg["model_type"], **extra)
     for i, l in enumerate(layers):
         if l.get("af") is not None:
             m.set_layer_activation_function(i, l["af"])

@@ -11,6 +11,7 @@ step supports are listed.
 class LAYER:
     FULLY_CONNECTED = 3
     FULLY_CONNECTED_INDEPENDENTLY_RECURRENT = 4
+    LSTM = 7
     RESIDUAL = 9
 
 

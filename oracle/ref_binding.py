@@ -46,6 +46,7 @@ def lib(path=None):
         "ref_model_create": (vp, []),
         "ref_model_destroy": (None, [vp]),
         "ref_compile": (i, [vp, sz, sz, i, _i32p, _szp, sz]),
+        "ref_compile2": (i, [vp, sz, sz, i, _i32p, _szp, _szp, sz]),
         "ref_set_layer_activation_function": (i, [vp, sz, i]),
         "ref_set_layer_normalization": (i, [vp, sz, i]),
         "ref_set_dropout": (i, [vp, sz, i, f, i]),
@@ -135,9 +136,13 @@ class RefModel:
             pass
 
     # --- construction ---------------------------------------------------
-    def compile(self, layer_types, layer_units, seq_w=1, model_type=3, allowable_memory=48 << 30):
+    def compile(self, layer_types, layer_units, seq_w=1, model_type=3, allowable_memory=48 << 30, layer_units2=None):
         lt = np.ascontiguousarray(layer_types, dtype=np.int32)
         lu = np.ascontiguousarray(layer_units, dtype=np.uint64)
+        if layer_units2 is not None:
+            lu2 = np.ascontiguousarray(layer_units2, dtype=np.uint64)
+            _ck(self.L.ref_compile2(self.h, len(lt), seq_w, model_type, lt, lu, lu2, allowable_memory), "compile")
+            return
         _ck(self.L.ref_compile(self.h, len(lt), seq_w, model_type, lt, lu, allowable_memory), "compile")
 
     def set_layer_activation_function(self, layer, af):

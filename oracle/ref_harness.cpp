@@ -90,6 +90,21 @@ int ref_compile(ref_model m, size_t n_layers, size_t seq_w, int model_type,
              : -1;
 }
 
+/* compile() with the second unit parameter of a layer (cells per block of an
+ * LSTM layer; Layer_Parameters::unit_parameters[1]). */
+int ref_compile2(ref_model m, size_t n_layers, size_t seq_w, int model_type, const int *layer_types,
+                 const size_t *layer_units, const size_t *layer_units2, size_t allowable_memory) {
+  std::vector<Layer_Parameters> ls(n_layers);
+  for (size_t i = 0; i < n_layers; ++i) {
+    ls[i].type_layer = static_cast<LAYER::TYPE>(layer_types[i]);
+    ls[i].unit_parameters[0] = layer_units[i];
+    ls[i].unit_parameters[1] = layer_units2[i];
+  }
+  return H(m)->model.compile(n_layers, seq_w, static_cast<MODEL::TYPE>(model_type), ls.data(), allowable_memory)
+             ? 0
+             : -1;
+}
+
 int ref_set_layer_activation_function(ref_model m, size_t layer, int af) {
   return H(m)->model.set_layer_activation_function(
              layer, static_cast<ACTIVATION::TYPE>(af))

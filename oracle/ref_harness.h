@@ -28,6 +28,8 @@ void ref_model_destroy(ref_model m);
 int ref_compile(ref_model m, size_t n_layers, size_t seq_w, int model_type,
                 const int *layer_types, const size_t *layer_units,
                 size_t allowable_memory);
+int ref_compile2(ref_model m, size_t n_layers, size_t seq_w, int model_type, const int *layer_types,
+                 const size_t *layer_units, const size_t *layer_units2, size_t allowable_memory);
 int ref_set_layer_activation_function(ref_model m, size_t layer, int af);
 int ref_set_layer_normalization(ref_model m, size_t layer, int norm);
 int ref_set_dropout(ref_model m, size_t layer, int type, float value0,

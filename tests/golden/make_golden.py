@@ -62,6 +62,41 @@ def recurrent_cases():
     }
 
 
+def lstm_cases():
+    """LSTM workloads: name -> (config, steps).  The layer after an LSTM layer is at
+    least as wide as the LSTM layer has cells: the reference reads that many bias
+    entries past the LSTM layer's own, out of its parameter vector otherwise."""
+    c = configs.lstm_stack
+    last = c(n_in=5, blocks=4, cells=1, depth=1, n_out=6, seq_w=6, batch=7)
+    last["time_delays"] = 5   # an error on the last time step only
+    last["name"] += "_laststep"
+    return {
+        "lstm_3x2_peephole_adam": (c(n_in=4, blocks=3, cells=2, depth=1, n_out=8, seq_w=3, batch=5), 6),
+        "lstm_two_layers": (c(n_in=4, blocks=3, cells=2, depth=2, n_out=8, seq_w=5, batch=6), 6),
+        "lstm_under_fc": (c(n_in=6, blocks=2, cells=3, depth=2, n_out=7, seq_w=4, batch=5, hidden_fc=6), 6),
+        "lstm_last_step_only": (last, 6),
+    }
+
+
+def make_lstm(name, cfg, steps):
+    """The biases are drawn at random first, so that the reference's bias indices
+    are told apart from any other.  Serial mode: the reference's LSTM code leaves
+    its heap damaged (glibc reports it when the process frees), so every fixture
+    comes from a process of its own that leaves without cleaning up."""
+    ref = util.build(ref_binding.RefModel(), dict(cfg, mp=False), seed=0)
+    p0 = ref.get_array("parameters")
+    nw = ref.size("total_weights")
+    p0[nw:] = (np.random.default_rng(1).standard_normal(p0.size - nw) * 0.1).astype(np.float32)
+    ref.set_array("parameters", p0)
+    X, Y = configs.synthetic_batch(cfg)
+    out = util.trace(ref, cfg, steps=steps, X=X, Y=Y)
+    blob = {"in_X": X, "in_Y": Y, "in_params": p0, "steps": np.int64(steps)}
+    blob.update({f"out_{k}": v for k, v in out.items()})
+    path = os.path.join(HERE, name + ".npz")
+    np.savez_compressed(path, **blob)
+    print(f"{name}: {os.path.getsize(path)} bytes, loss {out['losses'][0]:.6f} -> {out['losses'][-1]:.6f}", flush=True)
+
+
 def make_plain(name, cfg, steps):
     ref = util.build(ref_binding.RefModel(), cfg, seed=0)
     configs.set_recurrent_uniform(ref, cfg)
@@ -99,6 +134,9 @@ def main():
     """With arguments, regenerates only the named fixtures."""
     if not ref_binding.available():
         sys.exit("oracle/_ref/libdlref.so is missing: run `make -C oracle` where the reference sources are")
+    if len(sys.argv) == 3 and sys.argv[1] == "--one-lstm":
+        make_lstm(sys.argv[2], *lstm_cases()[sys.argv[2]])
+        os._exit(0)
     only = set(sys.argv[1:])
     for name, (cfg, steps) in {**cases(), **recurrent_cases()}.items():
         if not only or name in only:
@@ -106,6 +144,10 @@ def main():
     for name, (cfg, steps) in noisy_cases().items():
         if not only or name in only:
             make_noisy(name, cfg, steps)
+    import subprocess
+    for name in lstm_cases():
+        if not only or name in only:
+            subprocess.run([sys.executable, os.path.abspath(__file__), "--one-lstm", name], check=True)
 
 
 if __name__ == "__main__":

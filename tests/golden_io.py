@@ -14,11 +14,12 @@ _spec.loader.exec_module(make_golden)
 
 CASES = make_golden.cases()
 RECURRENT_CASES = make_golden.recurrent_cases()
+LSTM_CASES = make_golden.lstm_cases()
 
 
 def load(name):
     z = np.load(os.path.join(GOLDEN, name + ".npz"))
-    cfg, steps = CASES[name] if name in CASES else RECURRENT_CASES[name]
+    cfg, steps = {**CASES, **RECURRENT_CASES, **LSTM_CASES}[name]
     masks = {int(k[len("in_mask"):]): z[k] for k in z.files if k.startswith("in_mask")}
     want = {k[len("out_"):]: z[k] for k in z.files if k.startswith("out_")}
     return cfg, int(z["steps"]), z["in_X"], z["in_Y"], masks, z["in_params"], want
