@@ -369,6 +369,11 @@ extern "C" {
 
 dlb_status dlb_model_save_params(dlb_model *m, const char *path) {
   DLB_REQUIRE(m && path && m->layers.size() >= 2, "save_params");
+  for (const LayerRT &l : m->layers)
+    if (l.type == DLB_LAYER_LSTM) {
+      set_error("save_params: writing LSTM layers in the reference's format is not supported");
+      return DLB_ERR_UNSUPPORTED;
+    }
   HostState h;
   DLB_TRY(fetch(m, &h));
   const UnitBase base = unit_bases(m);

@@ -45,6 +45,8 @@ float d_max_of(const dlb_model *m, const LayerRT &l) {
 float indrnn_magnitude(const dlb_model *m) { return fminf(fmaxf(m->clip_gradient, 2.f), 10.f); }
 
 bool is_indrnn(const LayerRT &l) { return l.type == DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT; }
+bool is_lstm(const LayerRT &l) { return l.type == DLB_LAYER_LSTM; }
+size_t lstm_gates(const LayerRT &l) { return l.units + 3 * l.blocks; }
 
 // Bounds the recurrent weights of an IndRNN layer are clamped to after an
 // update: the ones set by hand, else +-mag^(1/T) with mag = clip(clip_gradient,
@@ -68,7 +70,7 @@ void recurrent_bounds(const dlb_model *m, const LayerRT &l, float *lo, float *hi
 bool time_stepped(const dlb_model *m) {
   if (m->seq_w > 1) return true;
   for (const LayerRT &l : m->layers)
-    if (is_indrnn(l)) return true;
+    if (is_indrnn(l) || is_lstm(l)) return true;
   return false;
 }
 
@@ -129,6 +131,13 @@ dlb_status layout_parameters(dlb_model *m) {
     LayerRT &l = m->layers[i];
     if (l.type == DLB_LAYER_RESIDUAL) continue;
     l.first_conn = w;
+    if (is_lstm(l)) {
+      // Per block: per cell [W_z | R_z], W_i W_f W_o, R_i R_f R_o, p_i p_f p_o
+      // (Prepare__Connections__LSTM, v1/learner/connections_prepare.cpp L:83-225).
+      w += l.blocks * (l.cells * (l.fan_in + l.units) + 3 * l.fan_in + 3 * l.units + 3 * l.cells);
+      l.last_conn = w;
+      continue;
+    }
     w += l.units * l.fan_in;
     if (l.type == DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT) {
       l.first_recurrent = w;
@@ -142,7 +151,7 @@ dlb_status layout_parameters(dlb_model *m) {
     LayerRT &l = m->layers[i];
     if (l.type == DLB_LAYER_RESIDUAL) continue;
     l.first_bias = b;
-    b += l.units;
+    b += is_lstm(l) ? lstm_gates(l) : l.units;  // Prepare__Bias__LSTM: cells, then three per block
     l.last_bias = b;
   }
   m->total_bias = b - w;
@@ -167,6 +176,65 @@ size_t beta_index(const dlb_model *m, const LayerRT &l) {
 
 // (Re)allocates the flat vectors, keeping existing weights and biases when the
 // normalisation block is added later, as the reference's reallocation does.
+// Packed weight buffers of the LSTM layers and the maps from their rows to the
+// flat parameter vector (offsets in floats), for gather before the forward pass
+// and scatter-add of the gradients.  Bias offsets are the reference's own: its
+// kernels index the layer's biases from first_bias_connection_index, which
+// Prepare__Bias__LSTM leaves at the block part (connections_prepare.cpp
+// L:240-262), so b_z[c] sits units entries into the layer's reserved range, the
+// gates behind it, the last `units` of them in the next layer's biases.
+dlb_status lstm_prepare(dlb_model *m) {
+  for (size_t li = 1; li < m->layers.size(); ++li) {
+    LayerRT &l = m->layers[li];
+    if (!is_lstm(l)) continue;
+    const size_t I = l.fan_in, C = l.units, B = l.blocks, K = l.cells, G = lstm_gates(l);
+    std::vector<unsigned long long> ff(G), rec(G), bias(G), peep(3 * C);
+    size_t w = l.first_conn;
+    for (size_t b = 0; b < B; ++b) {
+      for (size_t k = 0; k < K; ++k) {
+        ff[b * K + k] = w;
+        w += I;
+        rec[b * K + k] = w;
+        w += C;
+      }
+      for (size_t g = 0; g < 3; ++g) {
+        ff[C + g * B + b] = w;
+        w += I;
+      }
+      for (size_t g = 0; g < 3; ++g) {
+        rec[C + g * B + b] = w;
+        w += C;
+      }
+      for (size_t g = 0; g < 3; ++g)
+        for (size_t k = 0; k < K; ++k) peep[g * C + b * K + k] = w++;
+    }
+    DLB_REQUIRE(w == l.last_conn, "lstm: parameter layout");
+    const size_t base = l.first_bias + C;
+    DLB_REQUIRE(base + G <= m->total_parameters,
+                "lstm: the layer after an LSTM layer must have at least as many units as the LSTM layer has cells "
+                "(the reference's bias indices reach that far past the layer's own biases)");
+    for (size_t g = 0; g < G; ++g) bias[g] = base + g;
+    struct { unsigned long long **dev; std::vector<unsigned long long> *host; } maps[] = {
+        {&l.lstm_map_ff, &ff}, {&l.lstm_map_rec, &rec}, {&l.lstm_map_bias, &bias}, {&l.lstm_map_peep, &peep}};
+    for (auto &mp : maps) {
+      if (*mp.dev) DLB_TRY(dlb_free(m->ctx, *mp.dev));
+      *mp.dev = nullptr;
+      DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(mp.dev), mp.host->size() * sizeof(unsigned long long)));
+      DLB_TRY(dlb_memcpy_h2d(m->ctx, *mp.dev, mp.host->data(), mp.host->size() * sizeof(unsigned long long)));
+    }
+    DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));  // the host vectors go out of scope
+    DLB_TRY(dev_alloc(m, &l.lstm_wff, G * I, false));
+    DLB_TRY(dev_alloc(m, &l.lstm_wrec, G * C, false));
+    DLB_TRY(dev_alloc(m, &l.lstm_bias, G, false));
+    DLB_TRY(dev_alloc(m, &l.lstm_peep, 3 * C, false));
+    DLB_TRY(dev_alloc(m, &l.lstm_dwff, G * I, false));
+    DLB_TRY(dev_alloc(m, &l.lstm_dwrec, G * C, true));
+    DLB_TRY(dev_alloc(m, &l.lstm_dbias, G, false));
+    DLB_TRY(dev_alloc(m, &l.lstm_dpeep, 3 * C, false));
+  }
+  return DLB_OK;
+}
+
 dlb_status allocate_parameters(dlb_model *m) {
   const size_t old_wb = m->params ? m->total_weights + m->total_bias : 0;
   std::vector<float> keep;
@@ -196,6 +264,7 @@ dlb_status allocate_parameters(dlb_model *m) {
     DLB_TRY(dlb_free(m->ctx, m->wd_mask));
     m->wd_mask = nullptr;
   }
+  DLB_TRY(lstm_prepare(m));
   m->grads_clean = true;
   m->params_lo_valid = false;
   return DLB_OK;
@@ -203,7 +272,8 @@ dlb_status allocate_parameters(dlb_model *m) {
 
 dlb_status free_batch_buffers(dlb_model *m) {
   for (auto &l : m->layers) {
-    float **bufs[] = {&l.Z, &l.A, &l.A_lo, &l.delta, &l.delta_lo, &l.IN, &l.IN_lo};
+    float **bufs[] = {&l.Z, &l.A, &l.A_lo, &l.delta, &l.delta_lo, &l.IN, &l.IN_lo, &l.lstm_gin, &l.lstm_grec,
+                      &l.lstm_z, &l.lstm_c, &l.lstm_ca, &l.lstm_gi, &l.lstm_gf, &l.lstm_go, &l.lstm_d, &l.lstm_dc};
     for (float **b : bufs) {
       if (*b) DLB_TRY(dlb_free(m->ctx, *b));
       *b = nullptr;
@@ -269,6 +339,21 @@ dlb_status ensure_batch(dlb_model *m, size_t rows) {
       continue;
     }
     DLB_TRY(dev_alloc(m, &l.delta_lo, n, false));
+    if (is_lstm(l)) {
+      const size_t TB = T * rows, G = lstm_gates(l);
+      DLB_TRY(dev_alloc(m, &l.A_lo, n, false));
+      DLB_TRY(dev_alloc(m, &l.lstm_gin, TB * G, false));
+      DLB_TRY(dev_alloc(m, &l.lstm_grec, rows * G, false));
+      DLB_TRY(dev_alloc(m, &l.lstm_z, n, false));
+      DLB_TRY(dev_alloc(m, &l.lstm_c, n, false));
+      DLB_TRY(dev_alloc(m, &l.lstm_ca, n, false));
+      DLB_TRY(dev_alloc(m, &l.lstm_gi, TB * l.blocks, false));
+      DLB_TRY(dev_alloc(m, &l.lstm_gf, TB * l.blocks, false));
+      DLB_TRY(dev_alloc(m, &l.lstm_go, TB * l.blocks, false));
+      DLB_TRY(dev_alloc(m, &l.lstm_d, TB * G, false));
+      DLB_TRY(dev_alloc(m, &l.lstm_dc, 2 * rows * l.units, false));
+      continue;
+    }
     if (l.group == 1) {
       // Block layer: A holds its sums; later layers also keep their GEMM input.
       if (!l.block_input) {
@@ -366,6 +451,17 @@ dlb_status check_supported(dlb_model *m) {
     if (is_indrnn(l)) {
       if (!af_supported(l.af)) {
         set_error("model: layer %zu activation %d is outside the supported set", i, l.af);
+        return DLB_ERR_UNSUPPORTED;
+      }
+      continue;
+    }
+    if (is_lstm(l)) {
+      // Unidirectional, tanh / sigmoid as the reference fixes them
+      // (connections_prepare.cpp L:123-124), peepholes; no normalization, dropout
+      // or zoneout on the layer, not inside a residual block.
+      if (l.norm != DLB_NORM_NONE || l.dropout != DLB_DROPOUT_NONE || l.group == 1 || i + 1 == m->layers.size()) {
+        set_error("model: LSTM layer %zu: normalization, dropout, a place inside a residual block or as output "
+                  "layer are outside the supported path", i);
         return DLB_ERR_UNSUPPORTED;
       }
       continue;
@@ -654,6 +750,79 @@ dlb_status forward_residual_time(dlb_model *m, size_t i, const float *X, const f
                               res.A, res.A_lo, TB, (int)res.units);
 }
 
+// LSTM layer forward (Recurrent__Forward_Pass__LSTM__OpenMP,
+// v1/learner/fwp_rec_mp.cpp L:395-418, L:802-1526): the input sums of all time
+// steps are one product over T * B rows; per time step the recurrent sums are a
+// product over B rows and the cells one kernel.
+dlb_status forward_lstm(dlb_model *m, LayerRT &l, const float *X, const float *X_lo, int B, int T) {
+  const int I = (int)l.fan_in, C = (int)l.units, G = (int)lstm_gates(l);
+  DLB_TRY(dlb_gather_rows(m->ctx, m->params, l.lstm_map_ff, l.lstm_wff, (size_t)G, I));
+  DLB_TRY(dlb_gather_rows(m->ctx, m->params, l.lstm_map_rec, l.lstm_wrec, (size_t)G, C));
+  DLB_TRY(dlb_gather_rows(m->ctx, m->params, l.lstm_map_bias, l.lstm_bias, (size_t)G, 1));
+  DLB_TRY(dlb_gather_rows(m->ctx, m->params, l.lstm_map_peep, l.lstm_peep, (size_t)3 * C, 1));
+  DLB_TRY(dlb_fc_forward(m->ctx, X, X_lo, l.lstm_wff, nullptr, nullptr, l.lstm_gin, T * B, I, G));
+  const size_t sc = (size_t)B * C, sb = (size_t)B * l.blocks, sg = (size_t)B * G;
+  for (int t = 0; t < T; ++t) {
+    if (t > 0)
+      DLB_TRY(dlb_fc_forward(m->ctx, l.A + (t - 1) * sc, nullptr, l.lstm_wrec, nullptr, nullptr, l.lstm_grec, B, C, G));
+    DLB_TRY(dlb_lstm_forward_step(m->ctx, l.lstm_gin + t * sg, t ? l.lstm_grec : nullptr, l.lstm_bias, l.lstm_peep,
+                                  t ? l.lstm_c + (t - 1) * sc : nullptr, l.lstm_z + t * sc, l.lstm_c + t * sc,
+                                  l.lstm_ca + t * sc, l.A + t * sc, l.lstm_gi + t * sb, l.lstm_gf + t * sb,
+                                  l.lstm_go + t * sb, B, (int)l.blocks, (int)l.cells));
+  }
+  return dlb_split_planes_2d(m->ctx, l.A, l.A_lo, T * B, C);
+}
+
+// Backward through time: l.delta holds the error of the layer's outputs from
+// above; per time step, from the last, the recurrent part is added (the gates'
+// errors of t + 1 times R) and the cell kernel forms the gates' errors of t.
+// Then the error of the layer's inputs is one product over T * B rows.
+dlb_status backward_lstm(dlb_model *m, LayerRT &l, float *below_delta, int B, int T) {
+  const int I = (int)l.fan_in, C = (int)l.units, G = (int)lstm_gates(l);
+  const size_t sc = (size_t)B * C, sb = (size_t)B * l.blocks, sg = (size_t)B * G;
+  for (int t = T - 1; t >= 0; --t) {
+    const bool last = t == T - 1;
+    float *dH = l.delta + t * sc;
+    if (!last) {
+      // dH_t += D_{t+1} Wrec  (Backward_Pass__LSTM_Derivative__Output, bwp_rec_mp.cpp L:1160-1196)
+      GemmOperand A{l.lstm_d + (t + 1) * sg, nullptr, (long long)G, 1};
+      GemmOperand Bo{l.lstm_wrec, nullptr, 1, (long long)C};
+      GemmEpilogue ep;
+      ep.accumulate = 1;
+      DLB_TRY(gemm(m->ctx, A, Bo, dH, (long long)C, B, C, G, ep));
+    }
+    float *dC = l.lstm_dc + (size_t)(t & 1) * sc, *dC_next = l.lstm_dc + (size_t)((t + 1) & 1) * sc;
+    DLB_TRY(dlb_lstm_backward_step(m->ctx, dH, l.lstm_z + t * sc, l.lstm_ca + t * sc, l.lstm_gi + t * sb,
+                                   l.lstm_gf + t * sb, l.lstm_go + t * sb, t ? l.lstm_c + (t - 1) * sc : nullptr,
+                                   last ? nullptr : l.lstm_gf + (t + 1) * sb, last ? nullptr : dC_next,
+                                   last ? nullptr : l.lstm_d + (t + 1) * sg, l.lstm_peep, dC, l.lstm_d + t * sg, B,
+                                   (int)l.blocks, (int)l.cells));
+  }
+  if (below_delta)
+    DLB_TRY(dlb_fc_backward_input(m->ctx, l.lstm_d, nullptr, l.lstm_wff, nullptr, below_delta, T * B, I, G));
+  return DLB_OK;
+}
+
+// Weight gradients of an LSTM layer in packed form, scattered (added) into the
+// gradient vector; the bias gradients wait in l.lstm_dbias for the end of the
+// pass (their indices reach into the next layer's biases, which that layer's
+// own gradient would overwrite).
+dlb_status derivatives_lstm(dlb_model *m, LayerRT &l, const float *X, const float *X_lo, int B, int T) {
+  const int I = (int)l.fan_in, C = (int)l.units, G = (int)lstm_gates(l);
+  const size_t sg = (size_t)B * G;
+  // dWff = D^T X over all T * B rows, with the column sums of D as bias gradient.
+  DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.lstm_d, nullptr, X, X_lo, l.lstm_dwff, l.lstm_dbias, T * B, I, G, 0));
+  DLB_TRY(dlb_scatter_add_rows(m->ctx, l.lstm_dwff, l.lstm_map_ff, m->grads, (size_t)G, I));
+  if (T > 1) {
+    // dWrec = sum_t D_{t+1}^T h_t (update_derivative_rec_mp.cpp L:571-575, L:616-622).
+    DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.lstm_d + sg, nullptr, l.A, l.A_lo, l.lstm_dwrec, nullptr, (T - 1) * B,
+                                   C, G, 0));
+    DLB_TRY(dlb_scatter_add_rows(m->ctx, l.lstm_dwrec, l.lstm_map_rec, m->grads, (size_t)G, C));
+  }
+  DLB_TRY(dlb_lstm_peephole_gradient(m->ctx, l.lstm_d, l.lstm_c, l.lstm_dpeep, T, B, (int)l.blocks, (int)l.cells));
+  return dlb_scatter_add_rows(m->ctx, l.lstm_dpeep, l.lstm_map_peep, m->grads, (size_t)3 * C, 1);
+}
+
 // Time-stepped forward, layer-major as the reference
 // (RNN__Forward_Pass_Batch__OpenMP, v1/learner/fwp_rec_mp.cpp L:29-110): one
 // GEMM over all T * rows rows of a layer, statistics for every time step in one
@@ -671,6 +840,12 @@ dlb_status forward_layers_time(dlb_model *m, size_t rows) {
       X = l.A;
       X_lo = l.A_lo;
       i += l.depth;
+      continue;
+    }
+    if (is_lstm(l)) {
+      DLB_TRY(forward_lstm(m, l, X, X_lo, B, T));
+      X = l.A;
+      X_lo = l.A_lo;
       continue;
     }
     const int I = (int)l.fan_in, H = (int)l.units;
@@ -908,6 +1083,10 @@ dlb_status dlb_model_destroy(dlb_model *m) {
     if (l.sd_bwd) dlb_free(m->ctx, l.sd_bwd);
     if (l.fwd_sums) dlb_free(m->ctx, l.fwd_sums);
     if (l.bwd_sums) dlb_free(m->ctx, l.bwd_sums);
+    void *lstm[] = {l.lstm_wff, l.lstm_wrec, l.lstm_bias, l.lstm_peep, l.lstm_dwff, l.lstm_dwrec, l.lstm_dbias,
+                    l.lstm_dpeep, l.lstm_map_ff, l.lstm_map_rec, l.lstm_map_bias, l.lstm_map_peep};
+    for (void *p : lstm)
+      if (p) dlb_free(m->ctx, p);
   }
   float *flat[] = {m->params, m->params_lo, m->grads, m->m1, m->m2, m->m2hat, m->wd_mask};
   for (float *p : flat)
@@ -942,6 +1121,13 @@ dlb_status dlb_model_destroy(dlb_model *m) {
 
 dlb_status dlb_model_compile(dlb_model *m, size_t n_layers, size_t seq_w, int model_type,
                              const int *layer_types, const size_t *layer_units) {
+  return dlb_model_compile2(m, n_layers, seq_w, model_type, layer_types, layer_units, nullptr);
+}
+
+// layer_units2: Layer_Parameters::unit_parameters[1], the cells per block of an
+// LSTM layer (its unit_parameters[0] being the number of blocks; compile.cpp L:98-118).
+dlb_status dlb_model_compile2(dlb_model *m, size_t n_layers, size_t seq_w, int model_type,
+                              const int *layer_types, const size_t *layer_units, const size_t *layer_units2) {
   DLB_REQUIRE(m && layer_types && layer_units && n_layers >= 2 && seq_w >= 1, "dlb_model_compile");
   DLB_REQUIRE(m->layers.empty(), "dlb_model_compile: already compiled");
   DLB_REQUIRE(layer_types[0] == DLB_LAYER_FULLY_CONNECTED &&
@@ -953,8 +1139,20 @@ dlb_status dlb_model_compile(dlb_model *m, size_t n_layers, size_t seq_w, int mo
   for (size_t i = 0; i < n_layers; ++i) {
     m->layers[i].type = layer_types[i];
     // For a RESIDUAL layer the parameter is the block depth (model.hpp L:78-82).
-    if (layer_types[i] == DLB_LAYER_RESIDUAL) m->layers[i].depth = layer_units[i];
-    else m->layers[i].units = layer_units[i];
+    if (layer_types[i] == DLB_LAYER_RESIDUAL) {
+      m->layers[i].depth = layer_units[i];
+    } else if (layer_types[i] == DLB_LAYER_LSTM) {
+      if (!layer_units2 || layer_units2[i] == 0) {
+        m->layers.clear();
+        set_error("dlb_model_compile: LSTM layer %zu needs its cells per block (dlb_model_compile2)", i);
+        return DLB_ERR_INVALID;
+      }
+      m->layers[i].blocks = layer_units[i];
+      m->layers[i].cells = layer_units2[i];
+      m->layers[i].units = layer_units[i] * layer_units2[i];
+    } else {
+      m->layers[i].units = layer_units[i];
+    }
   }
   m->seq_w = seq_w;
   m->model_type = model_type;
@@ -1605,6 +1803,10 @@ static dlb_status backward_pass_time(dlb_model *m, size_t rows) {
       }
       continue;
     }
+    if (is_lstm(l)) {
+      DLB_TRY(backward_lstm(m, l, below ? below->delta : nullptr, B, T));
+      continue;
+    }
     const int H = (int)l.units;
     const bool norm = l.norm != DLB_NORM_NONE, rec = is_indrnn(l);
     // Rows of this layer's error that can be non-zero.
@@ -1717,6 +1919,14 @@ static dlb_status update_derivatives_time(dlb_model *m, size_t rows) {
       X = l.IN;
       X_lo = l.IN_lo;
     }
+    if (is_lstm(l)) {
+      DLB_TRY(derivatives_lstm(m, l, X, X_lo, (int)rows, (int)m->seq_w));
+      if (m->overlap_grad_allreduce)
+        DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
+      top = l.A;
+      top_lo = l.A_lo;
+      continue;
+    }
     const size_t H = l.units, I = l.fan_in;
     // The output layer's error is zero before the first step that has a target.
     const size_t first_row = i + 1 == m->layers.size() ? m->n_time_delay * rows : 0;
@@ -1737,6 +1947,11 @@ static dlb_status update_derivatives_time(dlb_model *m, size_t rows) {
       top_lo = m->layers[r].A_lo;
     }
   }
+  // LSTM bias gradients last: they are added at the reference's indices, part of
+  // which the next layer's bias gradient has just written.
+  for (LayerRT &l : m->layers)
+    if (is_lstm(l))
+      DLB_TRY(dlb_scatter_add_rows(m->ctx, l.lstm_dbias, l.lstm_map_bias, m->grads, lstm_gates(l), 1));
   m->grads_clean = false;
   return DLB_OK;
 }

@@ -28,6 +28,18 @@ struct LayerRT {
   // derived from clip_gradient and seq_w applies.  0 / 0: no clamp.
   bool rec_custom = false;
   float rec_lower = 0.f, rec_upper = 0.f;
+  // LSTM layer: `blocks` memory blocks of `cells` cells, units = blocks * cells
+  // outputs.  Its products run on packed copies of its weights (lstm.cu): G =
+  // units + 3 * blocks rows {z per cell | i | f | o per block}.
+  size_t blocks = 0, cells = 0;
+  float *lstm_wff = nullptr, *lstm_wrec = nullptr, *lstm_bias = nullptr, *lstm_peep = nullptr;   // [G, I], [G, C], [G], [3, C]
+  float *lstm_dwff = nullptr, *lstm_dwrec = nullptr, *lstm_dbias = nullptr, *lstm_dpeep = nullptr;
+  unsigned long long *lstm_map_ff = nullptr, *lstm_map_rec = nullptr, *lstm_map_bias = nullptr, *lstm_map_peep = nullptr;
+  // Per batch: sums W x_t of all time steps [T, rows, G], R h_{t-1} of one step
+  // [rows, G], cell inputs, states, activated states [T, rows, C], gates [T,
+  // rows, B], the gates' errors [T, rows, G] and the state errors of two steps.
+  float *lstm_gin = nullptr, *lstm_grec = nullptr, *lstm_z = nullptr, *lstm_c = nullptr, *lstm_ca = nullptr;
+  float *lstm_gi = nullptr, *lstm_gf = nullptr, *lstm_go = nullptr, *lstm_d = nullptr, *lstm_dc = nullptr;
   // Residual blocks (the reference's layer list: a RESIDUAL layer of depth d
   // followed by its d block layers, v1/learner/compile.cpp).
   int group = 0;            // 1 = layer inside a residual block

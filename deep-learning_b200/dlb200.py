@@ -112,6 +112,12 @@ SIGNATURES = {
     "dlb_model_create": (_i, [C.POINTER(_vp), _vp]),
     "dlb_model_destroy": (_i, [_vp]),
     "dlb_model_compile": (_i, [_vp, _sz, _sz, _i, _vp, _vp]),
+    "dlb_model_compile2": (_i, [_vp, _sz, _sz, _i, _vp, _vp, _vp]),
+    "dlb_gather_rows": (_i, [_vp, _vp, _vp, _vp, _sz, _i]),
+    "dlb_scatter_add_rows": (_i, [_vp, _vp, _vp, _vp, _sz, _i]),
+    "dlb_lstm_forward_step": (_i, [_vp] * 13 + [_i, _i, _i]),
+    "dlb_lstm_backward_step": (_i, [_vp] * 14 + [_i, _i, _i]),
+    "dlb_lstm_peephole_gradient": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i]),
     "dlb_model_set_layer_activation_function": (_i, [_vp, _sz, _i]),
     "dlb_model_set_layer_normalization": (_i, [_vp, _sz, _i]),
     "dlb_model_set_dropout": (_i, [_vp, _sz, _i, _f, _i]),
@@ -423,9 +429,13 @@ class Model:
             pass
 
     # --- construction ---------------------------------------------------
-    def compile(self, layer_types, layer_units, seq_w=1, model_type=3, allowable_memory=None):
+    def compile(self, layer_types, layer_units, seq_w=1, model_type=3, allowable_memory=None, layer_units2=None):
         lt = np.ascontiguousarray(layer_types, dtype=np.int32)
         lu = np.ascontiguousarray(layer_units, dtype=np.uint64)
+        if layer_units2 is not None:
+            lu2 = np.ascontiguousarray(layer_units2, dtype=np.uint64)
+            check(self.L.dlb_model_compile2(self.h, len(lt), seq_w, model_type, _ptr(lt), _ptr(lu), _ptr(lu2)), "compile")
+            return
         check(self.L.dlb_model_compile(self.h, len(lt), seq_w, model_type, _ptr(lt), _ptr(lu)), "compile")
 
     def set_layer_activation_function(self, layer, af):

@@ -46,7 +46,7 @@ enum { DLB_OPT_ADABOUND = 1, DLB_OPT_ADAM = 2, DLB_OPT_ADAMAX = 3, DLB_OPT_AMSBO
        DLB_OPT_AMSGRAD = 5, DLB_OPT_GD = 6, DLB_OPT_NOSADAM = 9 };
 enum { DLB_LOSS_CROSS_ENTROPY = 2, DLB_LOSS_MSE = 10 };
 enum { DLB_LAYER_FULLY_CONNECTED = 3, DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT = 4,
-       DLB_LAYER_RESIDUAL = 9 };
+       DLB_LAYER_LSTM = 7, DLB_LAYER_RESIDUAL = 9 };
 enum { DLB_NORM_NONE = 0, DLB_NORM_BATCH_NORMALIZATION = 1, DLB_NORM_BATCH_RENORMALIZATION = 2 };
 enum { DLB_MODEL_FEEDFORWARD = 3, DLB_MODEL_RECURRENT = 4 };
 enum { DLB_PROPAGATION_INFERENCE = 0, DLB_PROPAGATION_TRAINING = 1 };
@@ -421,6 +421,30 @@ dlb_status dlb_brn_time_backward_apply(dlb_ctx *ctx, float *delta, float *delta_
                                        const dlb_brn_unit_arrays *u, const double *sums,
                                        int global_rows, int seq_w, int rows, int n);
 
+/* LSTM layer, the parts that are not matrix products (lstm.cu).  Gates' sums and
+ * gates' errors of a time step are rows of G = C + 3 B values {z of every cell | i
+ * | f | o of every block}, C = blocks * cells; peep = {p_i | p_f | p_o}, C each.
+ * forward_step: one time step from the sums g_in = W x_t and g_rec = R h_{t-1}
+ * (NULL with c_prev at t = 0).  backward_step: the gates' errors d of one time
+ * step from dH (error of the outputs, recurrent part included), what follows it
+ * (gf_next, dC_next, d_next: NULL at the last step) and c_prev (NULL at t = 0).
+ * peephole_gradient: out [3, C] from all time steps' errors d [seq_w, rows, G]
+ * and states c [seq_w, rows, C].  gather_rows / scatter_add_rows move rows of
+ * `width` floats between a packed matrix and offsets in a flat vector. */
+dlb_status dlb_gather_rows(dlb_ctx *ctx, const float *src, const unsigned long long *offsets, float *dst,
+                           size_t rows, int width);
+dlb_status dlb_scatter_add_rows(dlb_ctx *ctx, const float *src, const unsigned long long *offsets, float *dst,
+                                size_t rows, int width);
+dlb_status dlb_lstm_forward_step(dlb_ctx *ctx, const float *g_in, const float *g_rec, const float *bias,
+                                 const float *peep, const float *c_prev, float *z, float *c, float *ca, float *h,
+                                 float *gi, float *gf, float *go, int rows, int blocks, int cells);
+dlb_status dlb_lstm_backward_step(dlb_ctx *ctx, const float *dH, const float *z, const float *ca, const float *gi,
+                                  const float *gf, const float *go, const float *c_prev, const float *gf_next,
+                                  const float *dC_next, const float *d_next, const float *peep, float *dC, float *d,
+                                  int rows, int blocks, int cells);
+dlb_status dlb_lstm_peephole_gradient(dlb_ctx *ctx, const float *d, const float *c, float *out, int seq_w, int rows,
+                                      int blocks, int cells);
+
 /* recurrent[h] = clip(recurrent[h], lo, hi).
  * ref: Model::Update_Weight_Regularization__Constraint_Recurrent_Weight
  * (v1/ops/constraints/constraint.cpp L:245-289). */
@@ -539,6 +563,18 @@ dlb_status dlb_model_destroy(dlb_model *m);
 /* ref: Model::compile (model.hpp L:2528). */
 dlb_status dlb_model_compile(dlb_model *m, size_t n_layers, size_t seq_w, int model_type,
                              const int *layer_types, const size_t *layer_units);
+/* compile() with Layer_Parameters::unit_parameters[1] of every layer
+ * (layer_units2, may be NULL): the cells per memory block of an LSTM layer,
+ * whose layer_units entry is its number of blocks (v1/learner/compile.cpp
+ * L:98-118).  An LSTM layer (DLB_LAYER_LSTM) is unidirectional with peephole
+ * connections, tanh on cell input and state, sigmoid gates
+ * (v1/learner/fwp_rec_mp.cpp L:802-1526, bwp_rec_mp.cpp L:1006-1582,
+ * update_derivative_rec_mp.cpp L:489-774), its parameters laid out block by
+ * block and its biases indexed as the reference does
+ * (connections_prepare.cpp L:83-262).  Not supported on it: normalization,
+ * dropout, zoneout, the bidirectional form; saving a model with LSTM layers. */
+dlb_status dlb_model_compile2(dlb_model *m, size_t n_layers, size_t seq_w, int model_type,
+                              const int *layer_types, const size_t *layer_units, const size_t *layer_units2);
 dlb_status dlb_model_set_layer_activation_function(dlb_model *m, size_t layer, int af);
 dlb_status dlb_model_set_layer_normalization(dlb_model *m, size_t layer, int norm);
 dlb_status dlb_model_set_dropout(dlb_model *m, size_t layer, int type, float value0,
