@@ -39,6 +39,14 @@ def test_bench_line_of_the_library():
     c = d["cpu_baseline"]
     assert c["value"] > 0 and c["cores"] >= 1 and c["kind"] in ("reference", "port") and c["sample"] and c["unit"] == d["unit"]
     assert set(d["clocks"]) >= {"sm_mhz", "sm_max_mhz", "reasons"}
+    # The boundary as the reference calls it (row pointers in, a loss per step), the
+    # range guard's counters, and the two records that only exist on several GPUs.
+    dr = d["e2e_dropin"]
+    assert dr["value"] > 0 and dr["unit"] == d["unit"] and dr["h2d_bytes_per_step"] == e["h2d_bytes_per_step"]
+    assert e["in_order"]["value"] > 0
+    assert d["range_guard"] == {"operand_tensors_flagged": 0, "products_on_fp32_fallback": 0,
+                                "note": d["range_guard"]["note"]}
+    assert d["comm"] is None and d["strong"] is None
 
 
 def test_bench_line_of_the_reference_arm():
