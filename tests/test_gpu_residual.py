@@ -177,3 +177,34 @@ def test_residual_blocks_in_a_time_stepped_model(gpu_ctx, delay, width, block_wi
     assert gpu_ctx.sync() == 0
     residual = {f"delta{li}" for li, l in enumerate(cfg["layers"]) if l["type"] == LAYER.RESIDUAL}
     _check(got, want, skip=residual)
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+def test_residual_100_steps_vs_compiled_reference(gpu_ctx):
+    """An unpicked weight seed, 100 steps of a residual stack (ShakeDrop with
+    probability 0, so that the reference's serial and OpenMP modes see the same
+    model): every tensor of the first step and the weights after 100 steps agree
+    with the OpenMP reference to the bar, or to three times what the reference's
+    two modes differ by on the same tensor."""
+    cfg = configs.residual_mlp(width=64, blocks=2, n_out=10, batch=64, p_last=1.0)
+    serial = util.build(ref_binding.RefModel(), dict(cfg, mp=False), seed=0)
+    p0 = serial.get_array("parameters")
+    X, Y = configs.synthetic_batch(cfg)
+    noise = {li: (np.zeros(64, np.uint8), np.zeros((64, 64), np.float32), np.zeros((64, 64), np.float32))
+             for li, _ in configs.shakedrop_layers(cfg)}
+    ws = util.trace(serial, dict(cfg, mp=False), 100, X, Y)
+    want = util.trace(util.build(ref_binding.RefModel(), dict(cfg, mp=True), params=p0), cfg, 100, X, Y)
+    model = util.build(dlb200.Model(gpu_ctx), cfg, params=p0)
+    for li, (mk, fw, bw) in noise.items():
+        model.set_shakedrop_noise(li, mk, fw, bw)
+    got = util.trace(model, cfg, 100, X, Y)
+    assert gpu_ctx.sync() == 0
+    skip = {f"delta{li}" for li, l in enumerate(cfg["layers"]) if l["type"] == 9}
+    drift = {k: v[0] for k, v in util.compare(ws, want).items()}
+    cmp = util.compare(got, want)
+    print({k: f"{v[0]:.2e} (reference against itself {drift[k]:.2e})" for k, v in cmp.items() if k not in skip})
+    for key, (l2, _) in cmp.items():
+        if key in skip or key.startswith("mean_average"):
+            continue   # (running means of units centred on zero have no scale for a relative error)
+        base = 1e-4 if key in ("params_last", "losses") else (TOL_PARAMS if key.startswith("params") else TOL_1)
+        assert l2 <= max(base, 3 * drift[key]), f"{key}: {l2:.2e}, reference against itself {drift[key]:.2e}"
