@@ -240,6 +240,19 @@ dlb_status peer_exchange_f64(dlb_ctx *ctx, double *buf, size_t n);
 dlb_status comm_allgather_host(dlb_ctx *ctx, const void *mine, void *all, size_t bytes);
 dlb_status comm_min_int(dlb_ctx *ctx, int *value);
 
+// Owner-computes update of a weight matrix across ranks (ctx.cu).  buf holds
+// world * per_rank floats, rank r owns [r * per_rank, (r + 1) * per_rank).
+// *_begin: the transfer starts on the second stream once the kernels enqueued
+// so far are done; *done is recorded behind it (created on first use) and
+// comm_wait makes the main stream wait for it.  comm_all_gather_begin also
+// clears, behind the gather, the slices of `clear` this rank does not own.
+// dlb_comm_join waits for everything still in flight.
+bool comm_can_shard(dlb_ctx *ctx);
+dlb_status comm_reduce_scatter_begin(dlb_ctx *ctx, float *buf, size_t per_rank, cudaEvent_t *done);
+dlb_status comm_all_gather_begin(dlb_ctx *ctx, float *buf, size_t per_rank, float *clear, cudaEvent_t *done);
+dlb_status comm_wait(dlb_ctx *ctx, cudaEvent_t done);
+dlb_status comm_all_gather(dlb_ctx *ctx, float *buf, size_t per_rank);  // on the main stream, in order
+
 // Fills o.h_hi / h_lo / scale / guard from the plane buffer registered for
 // (o.ptr, aux), if there is one and the planes are 16-byte aligned.
 bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o);

@@ -193,6 +193,8 @@ struct Nccl {
   ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
                             cudaStream_t) = nullptr;
+  ncclResult_t (*ReduceScatter)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
+                                cudaStream_t) = nullptr;
   const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 
@@ -209,6 +211,7 @@ static Nccl *nccl() {
       n.CommDestroy = (decltype(n.CommDestroy))dlsym(n.handle, "ncclCommDestroy");
       n.AllReduce = (decltype(n.AllReduce))dlsym(n.handle, "ncclAllReduce");
       n.AllGather = (decltype(n.AllGather))dlsym(n.handle, "ncclAllGather");
+      n.ReduceScatter = (decltype(n.ReduceScatter))dlsym(n.handle, "ncclReduceScatter");
       n.GetErrorString = (decltype(n.GetErrorString))dlsym(n.handle, "ncclGetErrorString");
     }
   }
@@ -691,6 +694,69 @@ dlb_status dlb_allreduce_f32_overlapped(dlb_ctx *ctx, float *buf, size_t n) {
   ctx->comm_pending = true;
   return DLB_OK;
 }
+
+}  // extern "C"
+
+// ---- owner-computes update: the pieces of one weight matrix -----------------
+static dlb_status comm_stream_ready(dlb_ctx *ctx) {
+  if (ctx->comm_stream) return DLB_OK;
+  DLB_CUDA(cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking));
+  DLB_CUDA(cudaEventCreateWithFlags(&ctx->ev_main, cudaEventDisableTiming));
+  DLB_CUDA(cudaEventCreateWithFlags(&ctx->ev_comm, cudaEventDisableTiming));
+  return DLB_OK;
+}
+
+static dlb_status comm_mark(dlb_ctx *ctx, cudaEvent_t *done) {
+  if (!*done) DLB_CUDA(cudaEventCreateWithFlags(done, cudaEventDisableTiming));
+  DLB_CUDA(cudaEventRecord(*done, ctx->comm_stream));
+  ctx->comm_pending = true;
+  return DLB_OK;
+}
+
+bool dlb::comm_can_shard(dlb_ctx *ctx) {
+  return ctx->comm && ctx->world > 1 && nccl() && nccl()->ReduceScatter && nccl()->AllGather;
+}
+
+dlb_status dlb::comm_reduce_scatter_begin(dlb_ctx *ctx, float *buf, size_t per_rank, cudaEvent_t *done) {
+  DLB_REQUIRE(comm_can_shard(ctx) && buf && per_rank > 0 && done, "comm_reduce_scatter_begin");
+  DLB_TRY(comm_stream_ready(ctx));
+  DLB_CUDA(cudaEventRecord(ctx->ev_main, ctx->stream));
+  DLB_CUDA(cudaStreamWaitEvent(ctx->comm_stream, ctx->ev_main, 0));
+  DLB_NCCL(nccl()->ReduceScatter(buf, buf + (size_t)ctx->rank * per_rank, per_rank, ncclFloat32, ncclSum, ctx->comm,
+                                 ctx->comm_stream));
+  return comm_mark(ctx, done);
+}
+
+dlb_status dlb::comm_all_gather_begin(dlb_ctx *ctx, float *buf, size_t per_rank, float *clear, cudaEvent_t *done) {
+  DLB_REQUIRE(comm_can_shard(ctx) && buf && per_rank > 0 && done, "comm_all_gather_begin");
+  DLB_TRY(comm_stream_ready(ctx));
+  DLB_CUDA(cudaEventRecord(ctx->ev_main, ctx->stream));
+  DLB_CUDA(cudaStreamWaitEvent(ctx->comm_stream, ctx->ev_main, 0));
+  DLB_NCCL(nccl()->AllGather(buf + (size_t)ctx->rank * per_rank, buf, per_rank, ncclFloat32, ctx->comm,
+                             ctx->comm_stream));
+  if (clear) {
+    const size_t before = (size_t)ctx->rank * per_rank, after = (size_t)(ctx->world - ctx->rank - 1) * per_rank;
+    if (before) DLB_CUDA(cudaMemsetAsync(clear, 0, before * sizeof(float), ctx->comm_stream));
+    if (after) DLB_CUDA(cudaMemsetAsync(clear + before + per_rank, 0, after * sizeof(float), ctx->comm_stream));
+  }
+  return comm_mark(ctx, done);
+}
+
+dlb_status dlb::comm_wait(dlb_ctx *ctx, cudaEvent_t done) {
+  DLB_REQUIRE(ctx && done, "comm_wait");
+  ProfileSpan span;  // counted with the time the main stream stands still for transfers
+  DLB_TRY(span.begin(ctx, 1, 0.0));
+  DLB_CUDA(cudaStreamWaitEvent(ctx->stream, done, 0));
+  return span.end();
+}
+
+dlb_status dlb::comm_all_gather(dlb_ctx *ctx, float *buf, size_t per_rank) {
+  DLB_REQUIRE(comm_can_shard(ctx) && buf && per_rank > 0, "comm_all_gather");
+  DLB_NCCL(nccl()->AllGather(buf + (size_t)ctx->rank * per_rank, buf, per_rank, ncclFloat32, ctx->comm, ctx->stream));
+  return DLB_OK;
+}
+
+extern "C" {
 
 dlb_status dlb_comm_join(dlb_ctx *ctx) {
   DLB_REQUIRE(ctx, "dlb_comm_join");

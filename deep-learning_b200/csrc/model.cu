@@ -1083,6 +1083,8 @@ dlb_status dlb_model_destroy(dlb_model *m) {
     if (l.sd_bwd) dlb_free(m->ctx, l.sd_bwd);
     if (l.fwd_sums) dlb_free(m->ctx, l.fwd_sums);
     if (l.bwd_sums) dlb_free(m->ctx, l.bwd_sums);
+    if (l.ev_reduced) cudaEventDestroy(l.ev_reduced);
+    if (l.ev_gathered) cudaEventDestroy(l.ev_gathered);
     void *lstm[] = {l.lstm_wff, l.lstm_wrec, l.lstm_bias, l.lstm_peep, l.lstm_dwff, l.lstm_dwrec, l.lstm_dbias,
                     l.lstm_dpeep, l.lstm_map_ff, l.lstm_map_rec, l.lstm_map_bias, l.lstm_map_peep};
     for (void *p : lstm)
@@ -1426,11 +1428,14 @@ dlb_status dlb_model_layer_info(dlb_model *m, size_t layer, size_t out[10]) {
   return DLB_OK;
 }
 
+static dlb_status gather_moments(dlb_model *m);
+
 dlb_status dlb_model_get_array(dlb_model *m, const char *name, float *host_out, size_t n) {
   DLB_REQUIRE(m && name && host_out, "get_array: null");
   if (!m->params) DLB_TRY(allocate_parameters(m));
   float *p = named_array(m, name);
   DLB_REQUIRE(p && n <= m->total_parameters, "get_array: unknown name or size");
+  if (p == m->m1 || p == m->m2 || p == m->m2hat) DLB_TRY(gather_moments(m));
   return dlb_memcpy_d2h(m->ctx, host_out, p, n * sizeof(float));
 }
 
@@ -1439,6 +1444,7 @@ dlb_status dlb_model_set_array(dlb_model *m, const char *name, const float *host
   if (!m->params) DLB_TRY(allocate_parameters(m));
   float *p = named_array(m, name);
   DLB_REQUIRE(p && n <= m->total_parameters, "set_array: unknown name or size");
+  if (p == m->m1 || p == m->m2 || p == m->m2hat) DLB_TRY(gather_moments(m));
   DLB_TRY(dlb_memcpy_h2d(m->ctx, p, host_in, n * sizeof(float)));
   DLB_TRY(dlb_ctx_sync(m->ctx, nullptr));
   if (p == m->params) m->params_lo_valid = false;
@@ -2000,8 +2006,9 @@ dlb_status dlb_model_merge_derivatives(dlb_model *m) {
   return dlb_allreduce_f32(m->ctx, m->grads, m->total_parameters);
 }
 
-// ref: Model::update_weights_mp (v1/learner/model.cpp L:4711-4796).
-dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_size) {
+// The scalars of one update: hyper-parameters, the advanced time step, the
+// step's weight decay (and its mask, on first use).
+static dlb_status prepare_update(dlb_model *m, size_t rows, size_t training_size, dlb_optimizer_scalars *out) {
   DLB_REQUIRE(m && m->params && rows > 0 && training_size > 0, "update_weights");
   if (!m->optimizer) {
     set_error("update_weights: no optimizer set");
@@ -2033,12 +2040,54 @@ dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_s
     hyper[1] = m->hp.learning_momentum;
     hyper[2] = m->hp.use_nesterov ? 1.f : 0.f;
   }
+  DLB_TRY(dlb_optimizer_prepare(m->optimizer, hyper, &m->hp.optimizer_time_step,
+                                &m->hp.adam_previous_beta2, out));
+  out->weight_decay = wd;
+  return DLB_OK;
+}
+
+// Moments of the weight matrices back on every rank after owner-computes
+// updates.  A collective: every rank calls it at the same point.
+static dlb_status gather_moments(dlb_model *m) {
+  if (!m->moments_sharded) return DLB_OK;
+  const size_t W = (size_t)dlb_comm_world(m->ctx);
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    const LayerRT &l = m->layers[i];
+    const size_t per = l.units * l.fan_in / W;
+    for (float *v : {m->m1, m->m2, m->m2hat})
+      if (v) DLB_TRY(comm_all_gather(m->ctx, v + l.first_conn, per));
+  }
+  m->moments_sharded = false;
+  return DLB_OK;
+}
+
+// One rank's share of the update of a weight segment (same arithmetic per
+// element as the whole-vector pass).
+static dlb_status update_segment(dlb_model *m, const dlb_optimizer_scalars &k, size_t at, size_t n, unsigned *amax) {
+  if (n == 0) return DLB_OK;
+  return optimizer_step_amax(m->ctx, m->optimizer, &k, m->params + at, m->grads + at, m->m1 + at, m->m2 + at,
+                             m->m2hat ? m->m2hat + at : nullptr, k.weight_decay != 0.f ? m->wd_mask + at : nullptr,
+                             n, amax);
+}
+
+// ref: Model::update_weights_mp (v1/learner/model.cpp L:4711-4796).
+dlb_status dlb_model_update_weights(dlb_model *m, size_t rows, size_t training_size) {
+  DLB_REQUIRE(m && m->params && rows > 0 && training_size > 0, "update_weights");
+  if (m->update_prepared) {
+    // The step's backward pass has updated the weight matrices slice by slice
+    // and split them; biases, scales and shifts follow here.
+    m->update_prepared = false;
+    DLB_TRY(update_segment(m, m->update_k, m->total_weights, m->total_parameters - m->total_weights, nullptr));
+    m->grads_clean = true;
+    m->params_lo_valid = true;
+    return DLB_OK;
+  }
+  DLB_TRY(gather_moments(m));
+  dlb_optimizer_scalars k;
+  DLB_TRY(prepare_update(m, rows, training_size, &k));
+  const float wd = k.weight_decay;
   if (m->use_clip_gradient)
     DLB_TRY(dlb_clip_gradient(m->ctx, m->grads, m->total_parameters, m->clip_gradient));
-  dlb_optimizer_scalars k;
-  DLB_TRY(dlb_optimizer_prepare(m->optimizer, hyper, &m->hp.optimizer_time_step,
-                                &m->hp.adam_previous_beta2, &k));
-  k.weight_decay = wd;
   // One pass per weight matrix where the products run on fp16 planes: the pass
   // leaves the matrix's largest |w| in the scale slot of its plane buffer and
   // the split follows at once, while the matrix is still partly in L2; the
@@ -2291,9 +2340,48 @@ static bool plain_stack(const dlb_model *m) {
 // gradient products.  Same kernels on the same operands as
 // dlb_model_backward_pass followed by dlb_model_update_derivatives: the
 // results are identical.
-static dlb_status backward_and_derivatives_overlapped(dlb_model *m, size_t rows) {
+//
+// Where every weight matrix divides by rows among the ranks, the exchange is a
+// reduce-scatter and the update moves in here as well: once the product that
+// reads the layer's weights has been enqueued, the rank updates the rows it
+// owns (gradient, weights and moments of that slice only: 1 / world of the
+// optimizer's traffic), the updated rows are gathered on the second stream,
+// and the matrix is split into its planes one layer later, when the gather
+// has had two products' time.  Same bytes over NVLink as the all-reduce.
+static bool sharded_update_possible(const dlb_model *m) {
+  static const bool off = getenv("DLB_SHARDED_UPDATE") && atoi(getenv("DLB_SHARDED_UPDATE")) == 0;
+  if (off || !m->sharded_update || !comm_can_shard(m->ctx) || m->use_clip_gradient || !m->optimizer) return false;
+  if (m->ctx->gemm_kind != DLB_GEMM_F16X3 || !m->params_lo) return false;
+  const size_t W = (size_t)dlb_comm_world(m->ctx);
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    const LayerRT &l = m->layers[i];
+    if (l.units % W != 0 || ((l.first_conn | (l.units / W * l.fan_in)) & 3) != 0) return false;
+  }
+  return true;
+}
+
+static dlb_status backward_and_derivatives_overlapped(dlb_model *m, size_t rows, size_t update_rows,
+                                                      size_t training_size) {
   const int B = (int)rows;
   const int accumulate = m->grads_clean ? 0 : 1;
+  const bool shard = sharded_update_possible(m);
+  const size_t W = (size_t)dlb_comm_world(m->ctx), rank = (size_t)dlb_comm_rank(m->ctx);
+  if (shard) {
+    DLB_TRY(prepare_update(m, update_rows, training_size, &m->update_k));
+    m->update_prepared = true;
+    m->moments_sharded = true;
+  } else {
+    DLB_TRY(gather_moments(m));
+  }
+  LayerRT *to_split = nullptr;  // gathered last, planes still to be formed
+  auto split_gathered = [&]() -> dlb_status {
+    if (!to_split) return DLB_OK;
+    LayerRT &g = *to_split;
+    to_split = nullptr;
+    DLB_TRY(comm_wait(m->ctx, g.ev_gathered));
+    return dlb_split_planes_2d(m->ctx, m->params + g.first_conn, m->params_lo + g.first_conn, (int)g.units,
+                               (int)g.fan_in);
+  };
   for (size_t i = m->layers.size() - 1; i >= 1; --i) {
     LayerRT &l = m->layers[i];
     const int H = (int)l.units;
@@ -2311,7 +2399,13 @@ static dlb_status backward_and_derivatives_overlapped(dlb_model *m, size_t rows)
     float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
     DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn, dbias,
                                    B, (int)l.fan_in, H, accumulate));
-    DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
+    const size_t per = l.units / W * l.fan_in;  // elements of one rank's rows
+    if (shard) {
+      DLB_TRY(comm_reduce_scatter_begin(m->ctx, m->grads + l.first_conn, per, &l.ev_reduced));
+      DLB_TRY(split_gathered());  // the layer above
+    } else {
+      DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
+    }
     if (i > 1) {
       LayerRT &below = m->layers[i - 1];
       if (below.norm == DLB_NORM_NONE) {
@@ -2324,19 +2418,30 @@ static dlb_status backward_and_derivatives_overlapped(dlb_model *m, size_t rows)
                                       m->params_lo + l.first_conn, below.delta, B, (int)l.fan_in, H));
       }
     }
+    if (shard) {
+      // Nothing reads this layer's weights any more in this step.
+      DLB_TRY(comm_wait(m->ctx, l.ev_reduced));
+      DLB_TRY(update_segment(m, m->update_k, l.first_conn + rank * per, per, nullptr));
+      DLB_TRY(comm_all_gather_begin(m->ctx, m->params + l.first_conn, per, m->grads + l.first_conn, &l.ev_gathered));
+      to_split = &l;
+    }
     if (i == 1) break;
   }
   m->grads_clean = false;
   // Bias, gamma and beta gradients follow the weight blocks.
   DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + m->total_weights,
                                        m->total_parameters - m->total_weights));
+  DLB_TRY(split_gathered());
   return dlb_comm_join(m->ctx);
 }
 
 // Backward, weight gradients and their exchange inside a training step.
 static dlb_status backward_update_merge(dlb_model *m, size_t rows) {
   DLB_REQUIRE(rows > 0 && rows <= m->alloc_rows, "train_step: rows");
-  if (dlb_comm_world(m->ctx) > 1 && plain_stack(m)) return backward_and_derivatives_overlapped(m, rows);
+  if (dlb_comm_world(m->ctx) > 1 && plain_stack(m)) {
+    const size_t g = m->global_rows ? m->global_rows : rows;
+    return backward_and_derivatives_overlapped(m, rows, g, m->training_size ? m->training_size : g);
+  }
   DLB_TRY(dlb_model_backward_pass(m, rows));
   return update_and_merge_overlapped(m, rows);
 }
@@ -2445,6 +2550,12 @@ dlb_status dlb_model_train_step_staged(dlb_model *m, double *loss) {
   const size_t g = m->global_rows ? m->global_rows : rows;
   DLB_TRY(dlb_model_update_weights(m, g, m->training_size ? m->training_size : g));
   if (loss) DLB_TRY(loss_collect(m, m->loss_lag ? slot ^ 1 : slot, loss));
+  return DLB_OK;
+}
+
+dlb_status dlb_model_set_sharded_update(dlb_model *m, int on) {
+  DLB_REQUIRE(m, "set_sharded_update");
+  m->sharded_update = on != 0;
   return DLB_OK;
 }
 

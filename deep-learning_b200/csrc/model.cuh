@@ -46,6 +46,9 @@ struct LayerRT {
   size_t depth = 0;         // RESIDUAL: number of block layers
   size_t pad = 0;           // RESIDUAL: first column of the narrower of shortcut and block in the output
   bool block_input = false; // first layer of a block: no activation in front
+  // Owner-computes update across ranks: the reduce-scatter of the layer's
+  // weight gradient and the gather of its updated weights are behind these.
+  cudaEvent_t ev_reduced = nullptr, ev_gathered = nullptr;
   bool error_final = false; // backward: delta already holds the error w.r.t. Z (the product above formed it)
   size_t norm_units = 0;    // normalised units: width, or fan-in for a block layer
   // Device buffers (allocated by ensure_batch).  Stand-alone FC layer: Z sums,
@@ -155,4 +158,14 @@ struct dlb_model {
   // The gradient vector is all zero (fresh, or cleared by the last update), so
   // the weight-gradient products may overwrite instead of accumulate.
   bool grads_clean = false;
+  // Multi-GPU one-call steps of plain stacks: each rank updates the rows of
+  // every weight matrix it owns (reduce-scatter of the gradient, update of
+  // the slice, gather of the weights) instead of all ranks updating all of it.
+  // moments_sharded: the moments of the weight matrices are current only on
+  // their owners' slices.  update_prepared: the step's scalars were drawn
+  // during the backward pass and the weight matrices are already updated.
+  bool sharded_update = true;
+  bool moments_sharded = false;
+  bool update_prepared = false;
+  dlb_optimizer_scalars update_k = {};
 };

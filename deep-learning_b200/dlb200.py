@@ -190,6 +190,7 @@ SIGNATURES = {
     "dlb_model_stage_batch": (_i, [_vp, _sz, _vp, _vp]),
     "dlb_model_train_step_staged": (_i, [_vp, C.POINTER(_d)]),
     "dlb_model_set_loss_lag": (_i, [_vp, _i]),
+    "dlb_model_set_sharded_update": (_i, [_vp, _i]),
     "dlb_model_get_layer_outputs": (_i, [_vp, _sz, _sz, _vp]),
     "dlb_model_get_layer_errors": (_i, [_vp, _sz, _sz, _i, _vp]),
 }
@@ -660,6 +661,11 @@ class Model:
     def set_loss_lag(self, steps):
         """1: train_step_staged returns the loss of the step before (NaN at first)."""
         check(self.L.dlb_model_set_loss_lag(self.h, int(steps)), "set_loss_lag")
+
+    def set_sharded_update(self, on):
+        """Several ranks, one-call steps: owner-computes update of the weight matrices
+        (default on) or all-reduce and the replicated update."""
+        check(self.L.dlb_model_set_sharded_update(self.h, int(bool(on))), "set_sharded_update")
 
     def train_step_device(self, batch, X_dev, Y_dev):
         check(self.L.dlb_model_train_step_device(self.h, batch, X_dev.ptr, Y_dev.ptr), "train_step_device")

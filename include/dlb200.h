@@ -792,6 +792,22 @@ dlb_status dlb_model_train_step_staged(dlb_model *m, double *loss);
  * (default): the loss of the step itself, for which the host waits after it
  * has enqueued the update. */
 dlb_status dlb_model_set_loss_lag(dlb_model *m, int steps);
+/* Several ranks, one-call steps (dlb_model_train_step*) of a plain stack of
+ * fully connected layers.  on = 1 (default): where the rows of every weight
+ * matrix divide evenly among the ranks and the gradient is not clipped by its
+ * norm, the merge of Model::merge_mp_derivatives (v1/learner/merge.cpp L:76-100)
+ * and the update of Model::update_weights_mp (v1/learner/model.cpp L:4711-4796)
+ * are done owner by owner: the gradient of a matrix is reduce-scattered by rows,
+ * each rank updates weights and moments of its rows, the updated rows are
+ * gathered; every rank ends the step with the same weights as with the
+ * replicated update, element for element the same arithmetic.  The moments of
+ * the matrices are then current only on their owners until they are read
+ * (dlb_model_get_array of a moment vector, the moments file of a checkpoint, a
+ * later replicated update): those calls gather them and are collective, every
+ * rank makes them at the same point.  on = 0: all-reduce and the same update on
+ * every rank.  The environment variable DLB_SHARDED_UPDATE=0 has the same
+ * effect for every model of the process. */
+dlb_status dlb_model_set_sharded_update(dlb_model *m, int on);
 dlb_status dlb_model_get_layer_outputs(dlb_model *m, size_t layer, size_t rows, float *host_out);
 dlb_status dlb_model_get_layer_errors(dlb_model *m, size_t layer, size_t rows, int which,
                                       float *host_out);

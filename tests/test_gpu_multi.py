@@ -87,13 +87,44 @@ def worker(rank, world, tmp, kind="brn_mlp"):
     # Two processes on two GPUs of one host: the statistics cross NVLink through
     # the peer-memory exchange unless the environment turned it off.
     assert ctx.peer_exchange() == (os.environ.get("DLB_PEER_EXCHANGE", "1") != "0")
-    cfg = _cfg(kind)
+    one_call = kind == "one_call"
+    cfg = _cfg("brn_mlp" if one_call else kind)
     B = cfg["batch"]
     X, Y = configs.synthetic_batch(cfg)
     masks = configs.dropout_masks(cfg)
     shard = B // world
     lo, hi = rank * shard, (rank + 1) * shard
     p0 = np.load(os.path.join(tmp, "p0.npy"))
+    if one_call:
+        # One-call steps: the owner-computes update of the weight matrices (default)
+        # beside all-reduce + replicated update, then one step through the
+        # separate entry points, whose replicated update needs the moments back.
+        out = {}
+        for name, on in (("owners", 1), ("replicated", 0)):
+            m = util.build(dlb200.Model(ctx), dict(cfg, batch=shard), params=p0)
+            m.set_global_batch(B)
+            m.set_sharded_update(on)
+            m.train_begin(shard)
+            for li, mk in masks.items():
+                m.set_dropout_mask(li, mk)
+            losses = [m.train_step(shard, X[lo:hi], Y[lo:hi]) for _ in range(3)]
+            out[name + "_params3"] = m.get_array("parameters")
+            out[name + "_grads3"] = m.get_array("derivatives")
+            losses.append(m.train_step(shard, X[lo:hi], Y[lo:hi]))
+            for mom in ("first_moment", "second_moment", "second_moment_hat"):
+                out[name + "_" + mom] = m.get_array(mom)
+            m.reset_loss()
+            m.forward_pass(shard, X[lo:hi])
+            m.compute_error(shard, Y[lo:hi])
+            m.backward_pass(shard)
+            m.update_derivatives(shard)
+            m.merge_derivatives()
+            m.update_weights(B, B)
+            out[name + "_params5"] = m.get_array("parameters")
+            out[name + "_losses"] = np.asarray(losses, np.float64)
+        assert ctx.sync() == 0
+        np.savez(os.path.join(tmp, f"rank{rank}.npz"), **out)
+        return
     m = util.build(dlb200.Model(ctx), dict(cfg, batch=shard), params=p0)
     m.set_global_batch(B)
     out = _run(m, dict(cfg, batch=shard), X[lo:hi], Y[lo:hi], masks, 4, first_row=lo)
@@ -130,6 +161,51 @@ def test_two_gpu_shards_equal_single_gpu_full_batch(gpu_ctx):
             assert util.rel_l2(got["params_last"], want["params_last"]) <= 1e-4, r
         a, b = np.load(os.path.join(tmp, "rank0.npz")), np.load(os.path.join(tmp, "rank1.npz"))
         assert np.array_equal(a["params_last"], b["params_last"])   # replicas stay bit-identical
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_two_gpu_owner_computes_update_equals_replicated_update(gpu_ctx):
+    """One-call steps on two ranks: reduce-scatter, update of the owned rows and
+    gather of the weights give, bit for bit, what all-reduce and the same update
+    on both ranks give (with two ranks both sums are a + b), the cleared
+    gradients and the gathered moments included; a later step through the
+    separate entry points carries on from the gathered moments; and both are the
+    single-GPU full-batch run to rounding of the statistics."""
+    import configs
+    import dlb200
+    import fc_step
+    import util
+
+    cfg = _cfg()
+    B = cfg["batch"]
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    p0, _ = util.kink_free_parameters(cfg, fc_step.OracleModel, X, masks, scale=1.0 / np.sqrt(512))
+    single = util.build(dlb200.Model(gpu_ctx), cfg, params=p0)
+    single.train_begin(B)
+    for li, mk in masks.items():
+        single.set_dropout_mask(li, mk)
+    want_losses = [single.train_step(B, X, Y) for _ in range(3)]
+    want3 = single.get_array("parameters")
+    with tempfile.TemporaryDirectory() as tmp:
+        np.save(os.path.join(tmp, "p0.npy"), p0)
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+        procs = [subprocess.Popen([sys.executable, os.path.abspath(__file__), "--worker", str(r), "2", tmp, "one_call"],
+                                  env=env) for r in range(2)]
+        for p in procs:
+            assert p.wait(timeout=600) == 0
+        ranks = [np.load(os.path.join(tmp, f"rank{r}.npz")) for r in range(2)]
+        for r, got in enumerate(ranks):
+            for key in ("params3", "grads3", "first_moment", "second_moment", "second_moment_hat", "params5"):
+                assert np.array_equal(got["owners_" + key], got["replicated_" + key]), (r, key)
+            # The loss is a sum of doubles added in whatever order the blocks finish.
+            assert np.allclose(got["owners_losses"], got["replicated_losses"], rtol=1e-12, atol=0)
+            assert not got["owners_grads3"].any()          # cleared, the slices of the other rank too
+            assert got["owners_first_moment"].any()
+            assert util.rel_l2(got["owners_params3"], want3) <= 1e-4, r
+            assert np.allclose(got["owners_losses"][:3], want_losses, rtol=1e-5)
+        for key in ("owners_params3", "owners_params5", "owners_second_moment_hat"):
+            assert np.array_equal(ranks[0][key], ranks[1][key]), key
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
