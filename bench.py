@@ -511,7 +511,10 @@ def run_ours(args, rank, local_rank, world):
                                "update_weights and a blocking get_loss every step; nothing staged ahead"},
         "gpu_launches": launches,
         "range_guard": {"operand_tensors_flagged": guard[0], "products_on_fp32_fallback": guard[1],
-                        "note": "3xFP16 form: products whose operand planes the range guard rejected (expected 0)"},
+                        "tensors_split_again": ctx.guard_resplits(),
+                        "note": "3xFP16 form, whole run: operand tensors with lines too small for the tensor's scale, "
+                                "products that therefore ran on the fp32 kernel, tensors split a second time after "
+                                "outgrowing their predicted scale (expected 0 0 0 on this workload)"},
         "clocks": clocks,
         "comm": comm, "strong": strong,
         "roofline": {

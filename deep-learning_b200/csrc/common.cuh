@@ -46,6 +46,8 @@ struct dlb_ctx {
     bool seen = false;          // a split has completed: the slot holds a scale predicted for the next one
   };
   std::map<uintptr_t, PlaneEntry> planes;
+  bool guard_strict = false;        // no exemptions (dlb_ctx_set_guard_strict)
+  std::map<uintptr_t, size_t> rows_exempt;  // plane buffers (address, bytes) of tensors whose small rows are not guarded
   // Bumped by dlb_ctx_set_gemm_kind, which also drops every registration above:
   // a model compares it with the value it last split its weights under and
   // splits them again in the new form.
@@ -74,7 +76,8 @@ struct dlb_ctx {
   std::map<TmapKey, TmapBlob> tmaps;
   float *scale_pool = nullptr;   // SCALE_SLOTS slots of SLOT_WORDS words (planes.cuh)
   // Range guard of the fp16 operand form: [0] operand tensors found unsafe for it,
-  // [1] products that therefore ran on the fp32 CUDA-core kernel.
+  // [1] products that therefore ran on the fp32 CUDA-core kernel, [2] tensors
+  // split again after outgrowing their predicted scale.
   unsigned long long *d_guard = nullptr;
   std::vector<int> scale_free;
   std::map<uintptr_t, size_t> allocs;  // dlb_malloc'd blocks, to retire plane entries on free
@@ -204,7 +207,17 @@ struct GemmOperand {
   // guard, planes.cuh): the tensor-core kernel then computes the product from
   // the fp32 tensors on the CUDA cores instead.
   const unsigned *guard = nullptr;
+  // Bits of that word this operand's use in the product cares about: overflow,
+  // and the small lines along its free dimension.
+  unsigned guard_mask = 7u;
 };
+// Flag bits (planes.cuh) a product looks at for an operand with these strides
+// whose planes belong to a row-major [rows, cols] tensor.
+inline unsigned guard_mask_of(const GemmOperand &o) {
+  if (o.stride_k == 1) return 1u | 2u;   // mn runs over the tensor's rows
+  if (o.stride_mn == 1) return 1u | 4u;  // mn runs over its columns
+  return 7u;
+}
 struct FusedEpilogue;
 struct GemmEpilogue {
   const float *bias = nullptr;   // per-n bias added to every row
@@ -256,6 +269,10 @@ dlb_status comm_all_gather(dlb_ctx *ctx, float *buf, size_t per_rank);  // on th
 // Fills o.h_hi / h_lo / scale / guard from the plane buffer registered for
 // (o.ptr, aux), if there is one and the planes are 16-byte aligned.
 bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o);
+// Marks (or unmarks) the plane buffer [planes, planes + bytes) as that of an error tensor of
+// the backward pass whose rows are the examples of a batch: the range guard
+// then leaves its small rows alone (planes.cuh), unless the context is strict.
+void planes_rows_exempt(dlb_ctx *ctx, const float *planes, size_t bytes, bool on);
 // Drops the plane buffers registered at addresses in [base, base + bytes).
 void planes_forget(dlb_ctx *ctx, uintptr_t base, size_t bytes);
 
@@ -268,6 +285,9 @@ struct PlaneSink {
   int n_lines = 0;                         // rows + cols (0: no line statistics)
   int predicted = 0;                       // planes use the scale predicted from the previous split
   unsigned long long *guard = nullptr;     // counter of tensors the range guard flagged
+  int rows_exempt = 0;                     // small rows are not flagged (planes.cuh)
+  const float *x = nullptr;                // the tensor the planes are of, n elements: read again
+  size_t n = 0;                            //   when it outgrew its predicted scale
 };
 // Elementwise work fused into the store of a product C[M, N] (all tensors dense,
 // row pitch N).

@@ -141,6 +141,7 @@ dlb_status gemm(dlb_ctx *ctx, const GemmOperand &A_in, const GemmOperand &B_in, 
         A.h_lo = h + a_n;
         A.scale = slots;
         A.guard = reinterpret_cast<const unsigned *>(slots) + 3;
+        A.guard_mask = guard_mask_of(A);
       }
       if (!b_have) {
         uint16_t *hb = h + 2 * a_n;
@@ -152,6 +153,7 @@ dlb_status gemm(dlb_ctx *ctx, const GemmOperand &A_in, const GemmOperand &B_in, 
         B.h_lo = hb + b_n;
         B.scale = slots + SLOT_WORDS;
         B.guard = reinterpret_cast<const unsigned *>(slots + SLOT_WORDS) + 3;
+        B.guard_mask = guard_mask_of(B);
       }
     }
     // A product with an operand the range guard flagged is computed by the
@@ -329,6 +331,7 @@ dlb_status dlb_ctx_create(dlb_ctx **out, int device) {
   ctx->sm_count = prop.multiProcessorCount;
   ctx->tensor_core_ok = true;
   if (const char *e = getenv("DLB_TENSOR_CORE")) ctx->use_tensor_core = atoi(e) != 0;
+  if (const char *e = getenv("DLB_GUARD_STRICT")) ctx->guard_strict = atoi(e) != 0;
   if (const char *e = getenv("DLB_GEMM_RESERVE_SMS")) ctx->gemm_reserve_sms = max(0, min(atoi(e), prop.multiProcessorCount - 1));
   if (const char *e = getenv("DLB_PDL")) ctx->use_pdl = atoi(e) != 0;
   if (const char *e = getenv("DLB_GEMM_KIND")) ctx->gemm_kind = e[0] == 't' ? DLB_GEMM_TF32X3 : DLB_GEMM_F16X3;

@@ -132,7 +132,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
                         const float *__restrict__ bias, int accumulate, int tiles_n, int whole_tiles,
                         int parts, int total_items, const float *__restrict__ scale_a,
                         const float *__restrict__ scale_b, int *status, const unsigned *guard_a,
-                        const unsigned *guard_b, SimtOperands fp32, unsigned long long *fallbacks,
+                        const unsigned *guard_b, unsigned mask_a, unsigned mask_b, SimtOperands fp32, unsigned long long *fallbacks,
                         const FusedEpilogue fe) {
   pdl_enter();
   using P = PairPlan<STAGES>;
@@ -141,7 +141,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
   // CTA taking its share of the 64 x 64 tiles (a rare and slow path that keeps
   // the result right; the counter tells the host that it was taken).  Both
   // CTAs of a pair read the same words and take the same branch.
-  if ((guard_a && *guard_a) || (guard_b && *guard_b)) {
+  if ((guard_a && (*guard_a & mask_a)) || (guard_b && (*guard_b & mask_b))) {
     extern __shared__ __align__(16) uint8_t guard_smem[];
     if (fallbacks && blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(fallbacks, 1ull);
     gemm_simt_guard_path(fp32, C, ldc, M, N, K, bias, accumulate, reinterpret_cast<float *>(guard_smem),
@@ -463,7 +463,7 @@ dlb_status launch_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B,
                                (size_t)N * sizeof(float), (size_t)(M - first_row), ctx->stream));
   }
   const int items = whole_tiles + parts * split_tiles;
-  DLB_LAUNCH_KERNEL(ctx, kernel, 2 * min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, parts, items, A.scale, B.scale, ctx->d_status, A.guard, B.guard, SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr, FUSED ? *ep.fused : FusedEpilogue{});
+  DLB_LAUNCH_KERNEL(ctx, kernel, 2 * min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, parts, items, A.scale, B.scale, ctx->d_status, A.guard, B.guard, A.guard_mask, B.guard_mask, SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr, FUSED ? *ep.fused : FusedEpilogue{});
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }

@@ -106,13 +106,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                    const float *__restrict__ bias, int accumulate, int tiles_n, int whole_tiles,
                    int total_items, const float *__restrict__ scale_a,
                    const float *__restrict__ scale_b, int *status, const unsigned *guard_a,
-                   const unsigned *guard_b, SimtOperands fp32, unsigned long long *fallbacks) {
+                   const unsigned *guard_b, unsigned mask_a, unsigned mask_b, SimtOperands fp32, unsigned long long *fallbacks) {
   pdl_enter();
   using P = SmemPlan<BN, BK, STAGES, ES>;
   // Range guard of the fp16 planes: with a flagged operand the product is formed
   // from the fp32 tensors on the CUDA cores by this same launch, every CTA
   // taking its share of the 64 x 64 tiles.
-  if ((guard_a && *guard_a) || (guard_b && *guard_b)) {
+  if ((guard_a && (*guard_a & mask_a)) || (guard_b && (*guard_b & mask_b))) {
     extern __shared__ __align__(16) uint8_t guard_smem[];
     if (fallbacks && blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(fallbacks, 1ull);
     gemm_simt_guard_path(fp32, C, ldc, M, N, K, bias, accumulate, reinterpret_cast<float *>(guard_smem));
@@ -528,7 +528,7 @@ dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, floa
                                (size_t)N * sizeof(float), (size_t)(M - first_row), ctx->stream));
   }
   const int items = whole_tiles + 2 * split_tiles;
-  DLB_LAUNCH_KERNEL(ctx, kernel, min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, items, A.scale, B.scale, ctx->d_status, ES == 2 ? A.guard : nullptr, ES == 2 ? B.guard : nullptr, SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr);
+  DLB_LAUNCH_KERNEL(ctx, kernel, min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, items, A.scale, B.scale, ctx->d_status, ES == 2 ? A.guard : nullptr, ES == 2 ? B.guard : nullptr, A.guard_mask, B.guard_mask, SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }

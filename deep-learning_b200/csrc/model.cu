@@ -274,6 +274,7 @@ dlb_status free_batch_buffers(dlb_model *m) {
   for (auto &l : m->layers) {
     float **bufs[] = {&l.Z, &l.A, &l.A_lo, &l.delta, &l.delta_lo, &l.IN, &l.IN_lo, &l.lstm_gin, &l.lstm_grec,
                       &l.lstm_z, &l.lstm_c, &l.lstm_ca, &l.lstm_gi, &l.lstm_gf, &l.lstm_go, &l.lstm_d, &l.lstm_dc};
+    planes_rows_exempt(m->ctx, l.delta_lo, 0, false);
     for (float **b : bufs) {
       if (*b) DLB_TRY(dlb_free(m->ctx, *b));
       *b = nullptr;
@@ -339,6 +340,8 @@ dlb_status ensure_batch(dlb_model *m, size_t rows) {
       continue;
     }
     DLB_TRY(dev_alloc(m, &l.delta_lo, n, false));
+    // Errors of the backward pass, one row per example (and time step).
+    planes_rows_exempt(m->ctx, l.delta_lo, n * sizeof(float), true);
     if (is_lstm(l)) {
       const size_t TB = T * rows, G = lstm_gates(l);
       DLB_TRY(dev_alloc(m, &l.A_lo, n, false));

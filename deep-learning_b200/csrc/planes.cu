@@ -158,6 +158,21 @@ dlb_status launch_split(dlb_ctx *ctx, const float *x, size_t n, int rows, int co
 
 }  // namespace
 
+void planes_rows_exempt(dlb_ctx *ctx, const float *planes, size_t bytes, bool on) {
+  if (!planes) return;
+  const uintptr_t key = reinterpret_cast<uintptr_t>(planes);
+  if (on && !ctx->guard_strict) ctx->rows_exempt[key] = bytes;
+  else ctx->rows_exempt.erase(key);
+}
+
+// Whether a plane buffer starting at `key` lies inside a marked one.
+static bool rows_exempt_at(const dlb_ctx *ctx, uintptr_t key) {
+  auto it = ctx->rows_exempt.upper_bound(key);
+  if (it == ctx->rows_exempt.begin()) return false;
+  --it;
+  return key < it->first + it->second;
+}
+
 bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o) {
   if (!aux || ctx->planes.empty()) return false;
   const uintptr_t p = reinterpret_cast<uintptr_t>(aux);
@@ -175,6 +190,7 @@ bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o) {
   o->h_lo = lo;
   o->scale = e.scale;
   o->guard = reinterpret_cast<const unsigned *>(e.scale) + SLOT_FLAGS;
+  o->guard_mask = guard_mask_of(*o);
   return true;
 }
 
@@ -230,6 +246,7 @@ dlb_status planes_open(dlb_ctx *ctx, const float *x, float *planes, size_t n, in
   job->sink = PlaneSink{};
   job->sink.slot = e.scale;
   job->sink.guard = ctx->d_guard;
+  job->sink.rows_exempt = rows_exempt_at(ctx, key) ? 1 : 0;
   if (job->fused) {
     job->sink.n_lines = rows + cols;
     job->sink.hi = reinterpret_cast<uint16_t *>(planes);
@@ -237,6 +254,8 @@ dlb_status planes_open(dlb_ctx *ctx, const float *x, float *planes, size_t n, in
     job->sink.rowmax = e.lines;
     job->sink.colmax = e.lines + rows;
     job->sink.predicted = 1;
+    job->sink.x = x;
+    job->sink.n = n;
   }
   return DLB_OK;
 }
@@ -349,6 +368,24 @@ dlb_status dlb_split_planes(dlb_ctx *ctx, const float *x, float *planes, size_t 
   DLB_TRY(planes_open(ctx, x, planes, n, 0, 0, false, &job));
   DLB_TRY(planes_absmax(ctx, x, n, job.sink.slot));
   return planes_close(ctx, job);
+}
+
+dlb_status dlb_ctx_set_guard_strict(dlb_ctx *ctx, int strict) {
+  DLB_REQUIRE(ctx, "dlb_ctx_set_guard_strict: null");
+  ctx->guard_strict = strict != 0;
+  if (ctx->guard_strict) ctx->rows_exempt.clear();
+  return DLB_OK;
+}
+
+dlb_status dlb_ctx_guard_resplits(dlb_ctx *ctx, uint64_t *tensors_resplit) {
+  DLB_REQUIRE(ctx && tensors_resplit, "dlb_ctx_guard_resplits: null");
+  unsigned long long host = 0;
+  if (ctx->d_guard) {
+    DLB_CUDA(cudaMemcpyAsync(&host, ctx->d_guard + 2, sizeof(host), cudaMemcpyDeviceToHost, ctx->stream));
+    DLB_CUDA(cudaStreamSynchronize(ctx->stream));
+  }
+  *tensors_resplit = host;
+  return DLB_OK;
 }
 
 dlb_status dlb_ctx_guard_counters(dlb_ctx *ctx, uint64_t *tensors_flagged, uint64_t *products_on_fallback) {

@@ -24,9 +24,21 @@
 // leave max |x| per row and per column, and the check that follows the split
 // (sink_finalize) flags the tensor when a non-zero row or column maximum is
 // below PLANE_TINY / s (18 bits left) or when the tensor's maximum overflowed
-// the predicted scale.  The
-// tensor-core kernels compute a product with a flagged operand on the CUDA
-// cores from the fp32 tensors instead.
+// the predicted scale; rows and columns have flags of their own.  A small line
+// only hurts where it is a line of the product's output: the lines of an
+// operand along its free dimension (a row of a k-contiguous operand, a column
+// of an mn-contiguous one).  Along the contraction its terms are added to the
+// terms of the large lines, and their error is 2^-39 of those.  The
+// tensor-core kernels therefore look at the overflow flag and at the flag of
+// the operand's free dimension, and compute a product with an operand flagged
+// there on the CUDA cores from the fp32 tensors instead.
+// rows_exempt (PlaneSink): the rows of the tensor are examples of a batch and
+// the tensor is an error of the backward pass.  Such a row reaches the
+// parameters only through sums over the examples; when it is 2^-19 of the
+// largest row it is lost in those sums in fp32 as well, so its own relative
+// error is not guarded (its absolute error stays 2^-39 of the tensor's
+// maximum).  After a few steps on a classifier most rows of the errors are
+// that small: the examples the model already gets right.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -41,6 +53,9 @@ constexpr int PLANE_EXP_OWN = 14;        // s max in [2^14, 2^15): the scale fro
 constexpr int PLANE_EXP_PREDICTED = 12;  // s max in [2^12, 2^13): the scale predicted for the next split
 constexpr float PLANE_TINY = 0.0078125f; // 2^-7: a line whose largest s |x| is below this has under 18 bits
 constexpr float PLANE_HALF_MAX = 65504.f;
+// Bits of a slot's flag word (SLOT_FLAGS): the planes overflowed or hold NaN /
+// infinity; some row; some column of the tensor is too small for the scale.
+constexpr unsigned GUARD_WHOLE = 1u, GUARD_ROWS = 2u, GUARD_COLS = 4u;
 
 // s = 2^(target - E) for max = 1.f * 2^E; 1 for a zero, infinite or NaN maximum.
 __host__ __device__ __forceinline__ float plane_scale_from_bits(unsigned bits, int target) {
@@ -142,29 +157,53 @@ struct LineTracker {
 __device__ __forceinline__ void sink_finalize(const PlaneSink &k) {
   unsigned *uslot = reinterpret_cast<unsigned *>(k.slot);
   const unsigned amax = __ldcg(uslot + SLOT_AMAX);
-  const float s = k.predicted ? __ldcg(k.slot + SLOT_NEXT) : plane_scale_from_bits(amax, PLANE_EXP_OWN);
-  int tiny = 0;
+  float s = k.predicted ? __ldcg(k.slot + SLOT_NEXT) : plane_scale_from_bits(amax, PLANE_EXP_OWN);
+  const bool finite = amax != 0u && (amax >> 23) != 255u;
+  // NaN or infinity in the tensor, or growth past the predicted scale.
+  bool overflow = !(__uint_as_float(amax) * s < PLANE_HALF_MAX);
+  bool resplit = false;
+  if (overflow && finite && k.predicted && k.hi && k.x) {
+    // The tensor outgrew the scale predicted for it (more than eightfold since
+    // its last split): this block writes the planes again with the scale of the
+    // tensor's own maximum.  A few milliseconds for a 256 MB tensor, against
+    // its products on the CUDA cores.
+    s = plane_scale_from_bits(amax, PLANE_EXP_OWN);
+    for (size_t o = (size_t)threadIdx.x * 4; o + 3 < k.n; o += (size_t)blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4 *>(k.x + o);
+      const float a[4] = {v.x, v.y, v.z, v.w};
+      sink_store4(k, o, a, s);
+    }
+    overflow = false;
+    resplit = true;
+  }
+  // Lines [0, rows) are the rows, the rest the columns.
+  int tiny_rows = 0, tiny_cols = 0;
   unsigned *lines = k.rowmax;
+  const int n_rows = lines ? (int)(k.colmax - k.rowmax) : 0;
   for (int i = threadIdx.x; i < (lines ? k.n_lines : 0); i += blockDim.x) {
     const unsigned v = __ldcg(lines + i);
     if (v) {
-      if (__uint_as_float(v) * s < PLANE_TINY) tiny = 1;
+      if (__uint_as_float(v) * s < PLANE_TINY) {
+        if (i < n_rows) tiny_rows = 1;
+        else tiny_cols = 1;
+      }
       lines[i] = 0u;
     }
   }
-  tiny = __syncthreads_or(tiny);
+  tiny_rows = __syncthreads_or(tiny_rows);
+  tiny_cols = __syncthreads_or(tiny_cols);
+  if (k.rows_exempt) tiny_rows = 0;
   if (threadIdx.x == 0) {
-    // NaN or infinity in the tensor, or growth past the predicted scale.
-    const bool overflow = !(__uint_as_float(amax) * s < PLANE_HALF_MAX);
-    const unsigned unsafe = (tiny || overflow) ? 1u : 0u;
+    const unsigned unsafe = (overflow ? GUARD_WHOLE : 0u) | (tiny_rows ? GUARD_ROWS : 0u) | (tiny_cols ? GUARD_COLS : 0u);
     k.slot[SLOT_S] = s;
     k.slot[SLOT_INV] = 1.f / s;
     uslot[SLOT_FLAGS] = unsafe;
     // The next split is predicted from this one's maximum; an empty or
     // non-finite tensor leaves the prediction where it was.
-    k.slot[SLOT_NEXT] = (amax == 0u || (amax >> 23) == 255u) ? s : plane_scale_from_bits(amax, PLANE_EXP_PREDICTED);
+    k.slot[SLOT_NEXT] = finite ? plane_scale_from_bits(amax, PLANE_EXP_PREDICTED) : s;
     uslot[SLOT_AMAX] = 0u;
     if (unsafe && k.guard) atomicAdd(k.guard, 1ull);
+    if (resplit && k.guard) atomicAdd(k.guard + 2, 1ull);
   }
 }
 

@@ -63,6 +63,8 @@ SIGNATURES = {
     "dlb_split_planes": (_i, [_vp, _vp, _vp, _sz]),
     "dlb_split_planes_2d": (_i, [_vp, _vp, _vp, _i, _i]),
     "dlb_ctx_guard_counters": (_i, [_vp, C.POINTER(_u64), C.POINTER(_u64)]),
+    "dlb_ctx_set_guard_strict": (_i, [_vp, _i]),
+    "dlb_ctx_guard_resplits": (_i, [_vp, C.POINTER(_u64)]),
     "dlb_ctx_set_gemm_kind": (_i, [_vp, _i]),
     "dlb_ctx_gemm_kind": (_i, [_vp]),
     "dlb_fc_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
@@ -267,6 +269,16 @@ class Context:
         a, b = _u64(0), _u64(0)
         check(self.L.dlb_ctx_guard_counters(self.h, C.byref(a), C.byref(b)), "dlb_ctx_guard_counters")
         return int(a.value), int(b.value)
+
+    def guard_resplits(self):
+        """Tensors split a second time after outgrowing the scale predicted for them."""
+        a = _u64(0)
+        check(self.L.dlb_ctx_guard_resplits(self.h, C.byref(a)), "dlb_ctx_guard_resplits")
+        return int(a.value)
+
+    def set_guard_strict(self, strict):
+        """True: no tensor is exempt from the range guard (call before a model's first batch)."""
+        check(self.L.dlb_ctx_set_guard_strict(self.h, int(bool(strict))), "dlb_ctx_set_guard_strict")
 
     def launch_count(self):
         return int(self.L.dlb_ctx_launch_count(self.h))

@@ -147,17 +147,39 @@ dlb_status dlb_split_planes(dlb_ctx *ctx, const float *x, float *planes, size_t 
  * it is within 2^-17 of the tensor's largest, so a row or column whose every
  * element is far smaller than the rest of the tensor would come out of a
  * product with less than fp32 accuracy relative to its own size.  Such a tensor
- * (a non-zero row or column maximum below 2^-21 of the tensor's, or a value
- * that overflows the scale) is flagged, the tensor-core kernel skips every
- * product that reads it and an fp32 CUDA-core kernel computes those products
- * instead.  dlb_ctx_guard_counters reads how often that happened: operand
- * tensors flagged, products that took the fp32 kernel.  Entry points that
- * produce an operand tensor together with its plane buffer record the same
- * statistics.  The check sees each operand alone: a column that is small in one
- * operand and made up for by a huge column in the other is not detected; the
- * TF32 form has fp32 range throughout. */
+ * is flagged: rows and columns separately (a non-zero maximum below 2^-21 of
+ * the tensor's), and as a whole when it holds NaN or infinity or, in a
+ * stand-alone split, a value that overflows the scale.  A small line
+ * only costs accuracy where it is a line of the product's output, i.e. along
+ * the operand's free dimension; along the contraction its terms are added to
+ * those of the large lines.  The tensor-core kernel therefore skips a product
+ * when an operand overflowed or has small lines along its free dimension, and an
+ * fp32 CUDA-core kernel computes that product instead.  dlb_ctx_guard_counters
+ * reads how often that happened: operand tensors flagged, products that took the
+ * fp32 kernel.  Entry points that produce an operand tensor together with its
+ * plane buffer record the same statistics.  The check sees each operand alone: a
+ * column that is small in one operand and made up for by a huge column in the
+ * other is not detected; the TF32 form has fp32 range throughout.
+ *
+ * Inside a model (dlb_model_*) the errors of the backward pass are exempt from
+ * the row flag: their rows are the examples of the batch, and after a few steps
+ * of a classifier most of them are 2^-20 and less of the few examples the model
+ * still gets wrong.  Such a row reaches the weights only through sums over the
+ * batch, where it is lost in fp32 as well; its absolute error stays 2^-39 of the
+ * tensor's maximum, only its error relative to its own size is not held at
+ * 1e-5.  dlb_ctx_set_guard_strict(ctx, 1), called before the model's first
+ * batch, (or DLB_GUARD_STRICT=1 in the environment) guards those rows too, at
+ * the price of the fp32 kernel for every input-gradient product once the rows
+ * have spread. */
 dlb_status dlb_split_planes_2d(dlb_ctx *ctx, const float *x, float *planes, int rows, int cols);
 dlb_status dlb_ctx_guard_counters(dlb_ctx *ctx, uint64_t *tensors_flagged, uint64_t *products_on_fallback);
+dlb_status dlb_ctx_set_guard_strict(dlb_ctx *ctx, int strict);
+/* Tensors whose planes were written a second time because the tensor had grown
+ * more than eightfold since its previous split, beyond the scale predicted for
+ * it (entry points that write planes in the producing kernel use that scale):
+ * the check after the producer then splits the tensor again with the scale of
+ * its own maximum, so that no product has to leave the tensor cores for it. */
+dlb_status dlb_ctx_guard_resplits(dlb_ctx *ctx, uint64_t *tensors_resplit);
 
 /* ------------------------------------------------------------------------ */
 /* FC GEMMs. */

@@ -44,7 +44,7 @@ def test_bench_line_of_the_library():
     dr = d["e2e_dropin"]
     assert dr["value"] > 0 and dr["unit"] == d["unit"] and dr["h2d_bytes_per_step"] == e["h2d_bytes_per_step"]
     assert e["in_order"]["value"] > 0
-    assert d["range_guard"] == {"operand_tensors_flagged": 0, "products_on_fp32_fallback": 0,
+    assert d["range_guard"] == {"operand_tensors_flagged": 0, "products_on_fp32_fallback": 0, "tensors_split_again": 0,
                                 "note": d["range_guard"]["note"]}
     assert d["comm"] is None and d["strong"] is None
 
