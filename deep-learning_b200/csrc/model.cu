@@ -1917,6 +1917,86 @@ dlb_status dlb_model_backward_pass(dlb_model *m, size_t rows) {
 // ref: Model::RNN__Update_Derivative_Weight_Batch__OpenMP
 // (v1/learner/update_derivative_rec_mp.cpp L:27-167): the per-time-step rank-1
 // sums of a layer are one GEMM whose reduction runs over all T * rows rows.
+static dlb_status prepare_update(dlb_model *m, size_t rows, size_t training_size, dlb_optimizer_scalars *out);
+static dlb_status update_segment(dlb_model *m, const dlb_optimizer_scalars &k, size_t at, size_t n, unsigned *amax);
+
+// Owner-computes update of the weight matrices across ranks, inside a one-call
+// step (see backward_and_derivatives_overlapped).  Every weight matrix must
+// divide by rows among the ranks and the weights must be fully connected
+// matrices only (no recurrent weights between them).
+static bool sharded_update_possible(const dlb_model *m) {
+  static const bool off = getenv("DLB_SHARDED_UPDATE") && atoi(getenv("DLB_SHARDED_UPDATE")) == 0;
+  if (off || !m->sharded_update || !comm_can_shard(m->ctx) || m->use_clip_gradient || !m->optimizer) return false;
+  if (m->ctx->gemm_kind != DLB_GEMM_F16X3 || !m->params_lo || time_stepped(m)) return false;
+  const size_t W = (size_t)dlb_comm_world(m->ctx);
+  size_t weights = 0;
+  for (size_t i = 1; i < m->layers.size(); ++i) {
+    const LayerRT &l = m->layers[i];
+    if (l.type == DLB_LAYER_RESIDUAL) continue;
+    if (l.type != DLB_LAYER_FULLY_CONNECTED || l.last_conn - l.first_conn != l.units * l.fan_in) return false;
+    if (l.units % W != 0 || ((l.first_conn | (l.units / W * l.fan_in)) & 3) != 0) return false;
+    weights += l.units * l.fan_in;
+  }
+  return weights == m->total_weights;
+}
+
+// One step's owner-computes updates.  begin() draws the step's scalars;
+// reduce(l) follows the layer's weight-gradient product; update(l) comes once
+// no product of the step reads the layer's weights any more; finish() before
+// the streams are joined.  The planes of a gathered matrix are formed one call
+// later, when its gather has had time.
+struct OwnerUpdate {
+  dlb_model *m;
+  size_t W, rank;
+  LayerRT *to_split = nullptr;
+  explicit OwnerUpdate(dlb_model *model)
+      : m(model), W((size_t)dlb_comm_world(model->ctx)), rank((size_t)dlb_comm_rank(model->ctx)) {}
+  size_t per(const LayerRT &l) const { return l.units / W * l.fan_in; }
+  dlb_status begin(size_t update_rows, size_t training_size) {
+    DLB_TRY(prepare_update(m, update_rows, training_size, &m->update_k));
+    m->update_prepared = true;
+    m->moments_sharded = true;
+    return DLB_OK;
+  }
+  dlb_status split_gathered() {
+    if (!to_split) return DLB_OK;
+    LayerRT &g = *to_split;
+    to_split = nullptr;
+    DLB_TRY(comm_wait(m->ctx, g.ev_gathered));
+    return dlb_split_planes_2d(m->ctx, m->params + g.first_conn, m->params_lo + g.first_conn, (int)g.units,
+                               (int)g.fan_in);
+  }
+  dlb_status reduce(LayerRT &l) {
+    DLB_TRY(comm_reduce_scatter_begin(m->ctx, m->grads + l.first_conn, per(l), &l.ev_reduced));
+    return split_gathered();
+  }
+  dlb_status update(LayerRT &l) {
+    DLB_TRY(comm_wait(m->ctx, l.ev_reduced));
+    DLB_TRY(update_segment(m, m->update_k, l.first_conn + rank * per(l), per(l), nullptr));
+    DLB_TRY(comm_all_gather_begin(m->ctx, m->params + l.first_conn, per(l), m->grads + l.first_conn, &l.ev_gathered));
+    to_split = &l;
+    return DLB_OK;
+  }
+  // After the backward pass, where nothing reads the weights any more: the
+  // update of a layer follows the weight-gradient product of the next one, so
+  // that its reduce-scatter has that product's time.
+  LayerRT *pending = nullptr;
+  dlb_status after_gradient(LayerRT &l) {
+    DLB_TRY(reduce(l));
+    if (pending) DLB_TRY(update(*pending));
+    pending = &l;
+    return DLB_OK;
+  }
+  dlb_status finish() {
+    if (pending) {
+      DLB_TRY(split_gathered());
+      DLB_TRY(update(*pending));
+      pending = nullptr;
+    }
+    return split_gathered();
+  }
+};
+
 static dlb_status update_derivatives_time(dlb_model *m, size_t rows) {
   const size_t TB = m->seq_w * rows;
   const float *top = m->input, *top_lo = m->input_lo;  // output of the top-level layer below
@@ -1966,9 +2046,16 @@ static dlb_status update_derivatives_time(dlb_model *m, size_t rows) {
 }
 
 // ref: Model::update_derivatives (v1/learner/update_derivative_fwp_mp.cpp L:27-240).
+static dlb_status update_derivatives_flat(dlb_model *m, size_t rows, OwnerUpdate *owners);
+
 dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows) {
   DLB_REQUIRE(m && rows > 0 && rows <= m->alloc_rows, "update_derivatives");
   if (time_stepped(m)) return update_derivatives_time(m, rows);
+  return update_derivatives_flat(m, rows, nullptr);
+}
+
+// owners: the step's owner-computes updates (one-call steps on several ranks), or null.
+static dlb_status update_derivatives_flat(dlb_model *m, size_t rows, OwnerUpdate *owners) {
   const float *top = m->input, *top_lo = m->input_lo;  // output of the top-level layer below
   for (size_t i = 1; i < m->layers.size(); ++i) {
     LayerRT &l = m->layers[i];
@@ -1981,8 +2068,12 @@ dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows) {
     float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
     DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn,
                                    dbias, (int)rows, (int)l.fan_in, (int)l.units, m->grads_clean ? 0 : 1));
-    if (m->overlap_grad_allreduce)
+    if (owners) {
+      // The backward pass is over: nothing reads the weights any more.
+      DLB_TRY(owners->after_gradient(l));
+    } else if (m->overlap_grad_allreduce) {
       DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
+    }
     if (l.group == 0) {
       top = l.A;
       top_lo = l.A_lo;
@@ -1995,6 +2086,7 @@ dlb_status dlb_model_update_derivatives(dlb_model *m, size_t rows) {
     }
   }
   m->grads_clean = false;
+  if (owners) DLB_TRY(owners->finish());
   return DLB_OK;
 }
 
@@ -2056,6 +2148,7 @@ static dlb_status gather_moments(dlb_model *m) {
   const size_t W = (size_t)dlb_comm_world(m->ctx);
   for (size_t i = 1; i < m->layers.size(); ++i) {
     const LayerRT &l = m->layers[i];
+    if (l.type == DLB_LAYER_RESIDUAL) continue;
     const size_t per = l.units * l.fan_in / W;
     for (float *v : {m->m1, m->m2, m->m2hat})
       if (v) DLB_TRY(comm_all_gather(m->ctx, v + l.first_conn, per));
@@ -2351,40 +2444,14 @@ static bool plain_stack(const dlb_model *m) {
 // optimizer's traffic), the updated rows are gathered on the second stream,
 // and the matrix is split into its planes one layer later, when the gather
 // has had two products' time.  Same bytes over NVLink as the all-reduce.
-static bool sharded_update_possible(const dlb_model *m) {
-  static const bool off = getenv("DLB_SHARDED_UPDATE") && atoi(getenv("DLB_SHARDED_UPDATE")) == 0;
-  if (off || !m->sharded_update || !comm_can_shard(m->ctx) || m->use_clip_gradient || !m->optimizer) return false;
-  if (m->ctx->gemm_kind != DLB_GEMM_F16X3 || !m->params_lo) return false;
-  const size_t W = (size_t)dlb_comm_world(m->ctx);
-  for (size_t i = 1; i < m->layers.size(); ++i) {
-    const LayerRT &l = m->layers[i];
-    if (l.units % W != 0 || ((l.first_conn | (l.units / W * l.fan_in)) & 3) != 0) return false;
-  }
-  return true;
-}
-
 static dlb_status backward_and_derivatives_overlapped(dlb_model *m, size_t rows, size_t update_rows,
                                                       size_t training_size) {
   const int B = (int)rows;
   const int accumulate = m->grads_clean ? 0 : 1;
   const bool shard = sharded_update_possible(m);
-  const size_t W = (size_t)dlb_comm_world(m->ctx), rank = (size_t)dlb_comm_rank(m->ctx);
-  if (shard) {
-    DLB_TRY(prepare_update(m, update_rows, training_size, &m->update_k));
-    m->update_prepared = true;
-    m->moments_sharded = true;
-  } else {
-    DLB_TRY(gather_moments(m));
-  }
-  LayerRT *to_split = nullptr;  // gathered last, planes still to be formed
-  auto split_gathered = [&]() -> dlb_status {
-    if (!to_split) return DLB_OK;
-    LayerRT &g = *to_split;
-    to_split = nullptr;
-    DLB_TRY(comm_wait(m->ctx, g.ev_gathered));
-    return dlb_split_planes_2d(m->ctx, m->params + g.first_conn, m->params_lo + g.first_conn, (int)g.units,
-                               (int)g.fan_in);
-  };
+  OwnerUpdate owners(m);
+  if (shard) DLB_TRY(owners.begin(update_rows, training_size));
+  else DLB_TRY(gather_moments(m));
   for (size_t i = m->layers.size() - 1; i >= 1; --i) {
     LayerRT &l = m->layers[i];
     const int H = (int)l.units;
@@ -2402,10 +2469,8 @@ static dlb_status backward_and_derivatives_overlapped(dlb_model *m, size_t rows,
     float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
     DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn, dbias,
                                    B, (int)l.fan_in, H, accumulate));
-    const size_t per = l.units / W * l.fan_in;  // elements of one rank's rows
     if (shard) {
-      DLB_TRY(comm_reduce_scatter_begin(m->ctx, m->grads + l.first_conn, per, &l.ev_reduced));
-      DLB_TRY(split_gathered());  // the layer above
+      DLB_TRY(owners.reduce(l));
     } else {
       DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + l.first_conn, l.last_conn - l.first_conn));
     }
@@ -2421,20 +2486,14 @@ static dlb_status backward_and_derivatives_overlapped(dlb_model *m, size_t rows,
                                       m->params_lo + l.first_conn, below.delta, B, (int)l.fan_in, H));
       }
     }
-    if (shard) {
-      // Nothing reads this layer's weights any more in this step.
-      DLB_TRY(comm_wait(m->ctx, l.ev_reduced));
-      DLB_TRY(update_segment(m, m->update_k, l.first_conn + rank * per, per, nullptr));
-      DLB_TRY(comm_all_gather_begin(m->ctx, m->params + l.first_conn, per, m->grads + l.first_conn, &l.ev_gathered));
-      to_split = &l;
-    }
+    if (shard) DLB_TRY(owners.update(l));  // nothing reads this layer's weights any more in this step
     if (i == 1) break;
   }
   m->grads_clean = false;
   // Bias, gamma and beta gradients follow the weight blocks.
   DLB_TRY(dlb_allreduce_f32_overlapped(m->ctx, m->grads + m->total_weights,
                                        m->total_parameters - m->total_weights));
-  DLB_TRY(split_gathered());
+  DLB_TRY(owners.finish());
   return dlb_comm_join(m->ctx);
 }
 
@@ -2451,7 +2510,19 @@ static dlb_status backward_update_merge(dlb_model *m, size_t rows) {
 
 static dlb_status update_and_merge_overlapped(dlb_model *m, size_t rows) {
   m->overlap_grad_allreduce = dlb_comm_world(m->ctx) > 1;
-  dlb_status st = dlb_model_update_derivatives(m, rows);
+  dlb_status st;
+  if (m->overlap_grad_allreduce && sharded_update_possible(m)) {
+    // Residual stacks: the backward pass is complete, so each matrix is
+    // reduce-scattered, updated by its owners and gathered right behind its
+    // weight-gradient product.
+    OwnerUpdate owners(m);
+    const size_t g = m->global_rows ? m->global_rows : rows;
+    st = owners.begin(g, m->training_size ? m->training_size : g);
+    if (st == DLB_OK) st = update_derivatives_flat(m, rows, &owners);
+  } else {
+    st = m->overlap_grad_allreduce ? gather_moments(m) : DLB_OK;
+    if (st == DLB_OK) st = dlb_model_update_derivatives(m, rows);
+  }
   if (st == DLB_OK) st = dlb_model_merge_derivatives(m);
   m->overlap_grad_allreduce = false;
   return st;

@@ -87,8 +87,8 @@ def worker(rank, world, tmp, kind="brn_mlp"):
     # Two processes on two GPUs of one host: the statistics cross NVLink through
     # the peer-memory exchange unless the environment turned it off.
     assert ctx.peer_exchange() == (os.environ.get("DLB_PEER_EXCHANGE", "1") != "0")
-    one_call = kind == "one_call"
-    cfg = _cfg("brn_mlp" if one_call else kind)
+    one_call = kind.startswith("one_call")
+    cfg = _cfg(("residual" if kind.endswith("residual") else "brn_mlp") if one_call else kind)
     B = cfg["batch"]
     X, Y = configs.synthetic_batch(cfg)
     masks = configs.dropout_masks(cfg)
@@ -107,12 +107,21 @@ def worker(rank, world, tmp, kind="brn_mlp"):
             m.train_begin(shard)
             for li, mk in masks.items():
                 m.set_dropout_mask(li, mk)
-            losses = [m.train_step(shard, X[lo:hi], Y[lo:hi]) for _ in range(3)]
+            noisy = bool(configs.shakedrop_layers(cfg))
+
+            def step(k):
+                if noisy:
+                    m.draw_noise(shard, 99, k, lo)
+                return m.train_step(shard, X[lo:hi], Y[lo:hi])
+
+            losses = [step(k) for k in range(3)]
             out[name + "_params3"] = m.get_array("parameters")
             out[name + "_grads3"] = m.get_array("derivatives")
-            losses.append(m.train_step(shard, X[lo:hi], Y[lo:hi]))
-            for mom in ("first_moment", "second_moment", "second_moment_hat"):
+            losses.append(step(3))
+            for mom in ("first_moment", "second_moment") + (() if noisy else ("second_moment_hat",)):
                 out[name + "_" + mom] = m.get_array(mom)
+            if noisy:
+                m.draw_noise(shard, 99, 4, lo)
             m.reset_loss()
             m.forward_pass(shard, X[lo:hi])
             m.compute_error(shard, Y[lo:hi])
@@ -161,6 +170,32 @@ def test_two_gpu_shards_equal_single_gpu_full_batch(gpu_ctx):
             assert util.rel_l2(got["params_last"], want["params_last"]) <= 1e-4, r
         a, b = np.load(os.path.join(tmp, "rank0.npz")), np.load(os.path.join(tmp, "rank1.npz"))
         assert np.array_equal(a["params_last"], b["params_last"])   # replicas stay bit-identical
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_two_gpu_owner_computes_update_of_residual_blocks(gpu_ctx):
+    """The same for residual blocks, where the matrices are updated by their
+    owners behind the weight-gradient products, after the backward pass."""
+    import dlb200
+    import util
+
+    cfg = _cfg("residual")
+    p0 = util.build(dlb200.Model(gpu_ctx), cfg, seed=5).get_array("parameters")
+    with tempfile.TemporaryDirectory() as tmp:
+        np.save(os.path.join(tmp, "p0.npy"), p0)
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+        procs = [subprocess.Popen([sys.executable, os.path.abspath(__file__), "--worker", str(r), "2", tmp,
+                                   "one_call_residual"], env=env) for r in range(2)]
+        for p in procs:
+            assert p.wait(timeout=600) == 0
+        ranks = [np.load(os.path.join(tmp, f"rank{r}.npz")) for r in range(2)]
+        for r, got in enumerate(ranks):
+            for key in ("params3", "grads3", "first_moment", "second_moment", "params5"):
+                assert np.array_equal(got["owners_" + key], got["replicated_" + key]), (r, key)
+            assert not got["owners_grads3"].any()
+            assert got["owners_first_moment"].any()
+            assert not np.array_equal(got["owners_params3"], p0)
+        assert np.array_equal(ranks[0]["owners_params5"], ranks[1]["owners_params5"])
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
