@@ -281,7 +281,9 @@ void planes_forget(dlb_ctx *ctx, uintptr_t base, size_t bytes);
 struct PlaneSink {
   uint16_t *hi = nullptr, *lo = nullptr;   // null: the kernel writes no planes
   float *slot = nullptr;                   // scale slot; null: nothing to track
-  unsigned *rowmax = nullptr, *colmax = nullptr;   // rows, then cols words of one array
+  unsigned *rowmax = nullptr, *colmax = nullptr;   // where the producer leaves row / column maxima (null: not wanted)
+  unsigned *lines = nullptr;               // the array both live in: n_rows words, then the columns'
+  int n_rows = 0;
   int n_lines = 0;                         // rows + cols (0: no line statistics)
   int predicted = 0;                       // planes use the scale predicted from the previous split
   unsigned long long *guard = nullptr;     // counter of tensors the range guard flagged

@@ -148,8 +148,8 @@ dlb_status launch_split(dlb_ctx *ctx, const float *x, size_t n, int rows, int co
     DLB_LAUNCH_KERNEL(ctx, split_rows_kernel, dim3(col_blocks, chunks), 32 * SPLIT_LANES_Y, 0, x, rows, cols, rpc, k);
   } else {
     PlaneSink flat = k;
-    flat.rowmax = flat.colmax = nullptr;
-    flat.n_lines = 0;
+    flat.rowmax = flat.colmax = flat.lines = nullptr;
+    flat.n_lines = flat.n_rows = 0;
     DLB_LAUNCH_KERNEL(ctx, split_flat_kernel, stream_blocks(ctx, n / 4 + 1), 256, 0, x, n, flat);
   }
   DLB_LAUNCHED(ctx);
@@ -192,6 +192,17 @@ bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o) {
   o->guard = reinterpret_cast<const unsigned *>(e.scale) + SLOT_FLAGS;
   o->guard_mask = guard_mask_of(*o);
   return true;
+}
+
+// Points a sink at the line statistics of a [rows, cols] tensor; the rows of an
+// exempt tensor are not recorded at all.
+static void sink_lines(PlaneSink &k, unsigned *lines, int rows, int cols, bool exempt) {
+  k.lines = lines;
+  k.n_rows = lines ? rows : 0;
+  k.n_lines = lines ? rows + cols : 0;
+  k.rowmax = lines && !exempt ? lines : nullptr;
+  k.colmax = lines ? lines + rows : nullptr;
+  k.rows_exempt = exempt ? 1 : 0;
 }
 
 // Registers `planes` as the plane buffer of x[0..n) with the given shape (0, 0:
@@ -248,11 +259,9 @@ dlb_status planes_open(dlb_ctx *ctx, const float *x, float *planes, size_t n, in
   job->sink.guard = ctx->d_guard;
   job->sink.rows_exempt = rows_exempt_at(ctx, key) ? 1 : 0;
   if (job->fused) {
-    job->sink.n_lines = rows + cols;
+    sink_lines(job->sink, e.lines, rows, cols, job->sink.rows_exempt != 0);
     job->sink.hi = reinterpret_cast<uint16_t *>(planes);
     job->sink.lo = job->sink.hi + n;
-    job->sink.rowmax = e.lines;
-    job->sink.colmax = e.lines + rows;
     job->sink.predicted = 1;
     job->sink.x = x;
     job->sink.n = n;
@@ -271,17 +280,13 @@ dlb_status planes_close(dlb_ctx *ctx, const PlaneJob &job) {
     k.hi = reinterpret_cast<uint16_t *>(job.planes);
     k.lo = k.hi + job.n;
     k.slot = e.scale;
-    k.rowmax = e.lines;
-    k.colmax = e.lines ? e.lines + e.rows : nullptr;
-    k.n_lines = e.lines ? e.rows + e.cols : 0;
+    sink_lines(k, e.lines, e.rows, e.cols, job.sink.rows_exempt != 0);
     k.predicted = 0;
     k.guard = ctx->d_guard;
     DLB_TRY(launch_split(ctx, job.x, job.n, e.rows, e.cols, k));
   }
   PlaneSink k = job.sink;
-  k.rowmax = e.lines;
-  k.colmax = e.lines ? e.lines + e.rows : nullptr;
-  k.n_lines = e.lines ? e.rows + e.cols : 0;
+  sink_lines(k, e.lines, e.rows, e.cols, job.sink.rows_exempt != 0);
   k.predicted = job.fused ? 1 : 0;
   DLB_LAUNCH_KERNEL(ctx, planes_finalize_kernel, 1, 1024, 0, k);
   DLB_LAUNCHED(ctx);
@@ -306,9 +311,7 @@ dlb_status planes_split_adhoc(dlb_ctx *ctx, const float *x, size_t n, int rows, 
   k.hi = hi;
   k.lo = lo;
   k.slot = slot;
-  k.rowmax = rows > 0 ? lines : nullptr;
-  k.colmax = rows > 0 && lines ? lines + rows : nullptr;
-  k.n_lines = k.rowmax ? rows + cols : 0;
+  sink_lines(k, rows > 0 ? lines : nullptr, rows, cols, false);
   k.guard = ctx->d_guard;
   DLB_TRY(launch_split(ctx, x, n, rows, cols, k));
   DLB_LAUNCH_KERNEL(ctx, planes_finalize_kernel, 1, 1024, 0, k);

@@ -178,9 +178,11 @@ __device__ __forceinline__ void sink_finalize(const PlaneSink &k) {
   }
   // Lines [0, rows) are the rows, the rest the columns.
   int tiny_rows = 0, tiny_cols = 0;
-  unsigned *lines = k.rowmax;
-  const int n_rows = lines ? (int)(k.colmax - k.rowmax) : 0;
-  for (int i = threadIdx.x; i < (lines ? k.n_lines : 0); i += blockDim.x) {
+  // Exempt rows were not recorded (rowmax was null for the producer): their
+  // words are zero and stay so.
+  unsigned *lines = k.lines;
+  const int n_rows = k.n_rows;
+  for (int i = (k.rows_exempt ? n_rows : 0) + threadIdx.x; i < (lines ? k.n_lines : 0); i += blockDim.x) {
     const unsigned v = __ldcg(lines + i);
     if (v) {
       if (__uint_as_float(v) * s < PLANE_TINY) {
@@ -192,7 +194,6 @@ __device__ __forceinline__ void sink_finalize(const PlaneSink &k) {
   }
   tiny_rows = __syncthreads_or(tiny_rows);
   tiny_cols = __syncthreads_or(tiny_cols);
-  if (k.rows_exempt) tiny_rows = 0;
   if (threadIdx.x == 0) {
     const unsigned unsafe = (overflow ? GUARD_WHOLE : 0u) | (tiny_rows ? GUARD_ROWS : 0u) | (tiny_cols ? GUARD_COLS : 0u);
     k.slot[SLOT_S] = s;

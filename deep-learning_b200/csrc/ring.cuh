@@ -93,6 +93,51 @@ __device__ __forceinline__ void ring_walk(float4 *ring, const float *const (&in)
   }
 }
 
+// The general form: `count` steps over NIN streams of float4, stream i starting
+// at src[i] and moving by stride[i] bytes per step (any sign: a walk back in
+// time has negative strides, a per-step vector of statistics a short one).
+// body(k, x) sees step k = 0 .. count - 1 in order.
+// valid[i]: stream i is only read for steps k < valid[i] (x[i] of later steps is
+// whatever the slot held).
+template <int NIN, int DEPTH, int THREADS, class Body>
+__device__ __forceinline__ void ring_steps(float4 *ring, const char *(&src)[NIN], const long long (&stride)[NIN],
+                                           const int (&valid)[NIN], int count, Body body) {
+  constexpr unsigned TENSOR_BYTES = THREADS * 16u;
+  constexpr unsigned SLOT_BYTES = NIN * TENSOR_BYTES;
+  const unsigned base = (unsigned)__cvta_generic_to_shared(ring + threadIdx.x);
+  const unsigned wrap = base + DEPTH * SLOT_BYTES;
+  unsigned fill = base;
+#pragma unroll
+  for (int d = 0; d < DEPTH - 1; ++d) {
+#pragma unroll
+    for (int i = 0; i < NIN; ++i)
+      if (d < valid[i]) cp_async16_to(fill + i * TENSOR_BYTES, src[i]);
+    cp_async_commit();
+#pragma unroll
+    for (int i = 0; i < NIN; ++i) src[i] += stride[i];
+    fill += SLOT_BYTES;
+  }
+  unsigned use = base;
+  for (int k = 0; k < count; ++k) {
+    const int ahead = k + DEPTH - 1;  // the step sent now
+#pragma unroll
+    for (int i = 0; i < NIN; ++i)
+      if (ahead < valid[i]) cp_async16_to(fill + i * TENSOR_BYTES, src[i]);
+    cp_async_commit();
+#pragma unroll
+    for (int i = 0; i < NIN; ++i) src[i] += stride[i];
+    fill += SLOT_BYTES;
+    if (fill == wrap) fill = base;
+    cp_async_wait<DEPTH - 1>();
+    float4 x[NIN];
+#pragma unroll
+    for (int i = 0; i < NIN; ++i) x[i] = ring_read(use + i * TENSOR_BYTES);
+    use += SLOT_BYTES;
+    if (use == wrap) use = base;
+    body(k, x);
+  }
+}
+
 // After the walk, before the block reuses the ring's memory for something else.
 __device__ __forceinline__ void ring_drain() {
   cp_async_wait<0>();
