@@ -210,6 +210,16 @@ struct GemmOperand {
   // Bits of that word this operand's use in the product cares about: overflow,
   // and the small lines along its free dimension.
   unsigned guard_mask = 7u;
+  // Strides of `ptr` where they differ from the planes' (planes transposed into
+  // scratch for the product); 0: the same.
+  long long fp32_stride_mn = 0, fp32_stride_k = 0;
+  // Planes with a scale of their own per mn line (k-contiguous planes made for
+  // one product): 1 / scale of every line; `scale` is then not read.
+  const float *line_inv = nullptr;
+  // Asked by the caller: make such planes for this product (A of a weight
+  // gradient whose columns differ widely in size, e.g. the classes of a softmax
+  // error).  Also done where TMA cannot tile the operand as it lies.
+  bool rescale_lines = false;
 };
 // Flag bits (planes.cuh) a product looks at for an operand with these strides
 // whose planes belong to a row-major [rows, cols] tensor.
@@ -273,6 +283,11 @@ bool planes_lookup(dlb_ctx *ctx, const float *aux, GemmOperand *o);
 // the backward pass whose rows are the examples of a batch: the range guard
 // then leaves its small rows alone (planes.cuh), unless the context is strict.
 void planes_rows_exempt(dlb_ctx *ctx, const float *planes, size_t bytes, bool on);
+// x [K, M] with row pitch `pitch` (mn contiguous) -> fp16 planes [M, kp] (k
+// contiguous), line m scaled by a power of two of its own taken from the
+// line's largest |x| (`cmax`, M words of scratch); line_inv[m] = 1 / scale.
+dlb_status planes_transpose_scaled(dlb_ctx *ctx, const float *x, long long pitch, int K, int M, uint16_t *hi_t,
+                                   uint16_t *lo_t, long long kp, unsigned *cmax, float *line_inv);
 // Drops the plane buffers registered at addresses in [base, base + bytes).
 void planes_forget(dlb_ctx *ctx, uintptr_t base, size_t bytes);
 
@@ -313,6 +328,12 @@ struct FusedEpilogue {
   const float *a = nullptr;       //   layer whose error C is
   PlaneSink sink;
 };
+// dlb_fc_weight_gradient with a say on the planes of the error: rescale_lines
+// asks for planes with a scale per unit (per output row of dW), made for this
+// product (gemm() in ctx.cu).
+dlb_status fc_weight_gradient_lines(dlb_ctx *ctx, const float *delta, const float *delta_lo, const float *X,
+                                    const float *X_lo, float *dW, float *dbias, int rows, int n_in, int n_out,
+                                    int accumulate, bool rescale_lines);
 bool gemm_pair_enabled();  // the 2-CTA kernel is on (DLB_GEMM_PAIR)
 int gemm_pair_chunk();     // its chunk of k-blocks per accumulator drain
 // Whether gemm() would run this product on the kernel that takes a fused epilogue.

@@ -111,6 +111,47 @@ dlb_status gemm(dlb_ctx *ctx, const GemmOperand &A_in, const GemmOperand &B_in, 
   const bool big = (long long)M * N >= 128 * 64 && K >= 32;
   if (!(ctx->use_tensor_core && ctx->tensor_core_ok && big)) return gemm_simt(ctx, A, B, C, ldc, M, N, K, ep);
 
+  // A weight-gradient product (both operands mn-contiguous) whose A TMA cannot
+  // tile as it lies (output rows not a multiple of 64, e.g. 1000 classes), or
+  // whose caller asked for a scale per output row (the classes of a softmax
+  // error differ by many orders of magnitude: the ones nobody is wrong about
+  // have errors 2^-20 and less of the others', and one scale for the tensor
+  // would leave their gradient rows with few bits).  A's planes are made for
+  // this product in scratch: k contiguous, every line with the scale of its own
+  // maximum (two passes over the fp32 tensor, 12 bytes per element), and the
+  // product runs on the 2-CTA kernel in the k-contiguous x mn-contiguous form,
+  // each output row multiplied by its line's 1 / scale.  Nothing of A is left
+  // for the range guard to flag.
+  if (ctx->gemm_kind == DLB_GEMM_F16X3 && A.stride_mn == 1 && A.stride_k != 1 && B.stride_mn == 1 &&
+      B.stride_k != 1 && gemm_pair_enabled() && (long long)M * N >= 256 * 256 && !ep.fused &&
+      (A.rescale_lines || !gemm_f16_supported(A, B, C, ldc, M, N, K))) {
+    GemmOperand a = A, b = B;
+    const bool have_b = b.h_hi || planes_lookup(ctx, b.lo, &b);
+    const long long kp = (long long)align_up((size_t)K, 8);
+    if (have_b && a.stride_k >= M) {
+      const size_t plane = align_up((size_t)M * kp, 64);
+      void *scr = nullptr;
+      DLB_TRY(scratch(ctx, 2 * plane * sizeof(uint16_t) + 2 * (size_t)M * sizeof(float), &scr));
+      uint16_t *hi_t = static_cast<uint16_t *>(scr), *lo_t = hi_t + plane;
+      unsigned *cmax = reinterpret_cast<unsigned *>(lo_t + plane);
+      float *line_inv = reinterpret_cast<float *>(cmax + M);
+      a.fp32_stride_mn = a.stride_mn;
+      a.fp32_stride_k = a.stride_k;
+      a.h_hi = hi_t;
+      a.h_lo = lo_t;
+      a.stride_mn = kp;
+      a.stride_k = 1;
+      a.scale = line_inv;  // not read
+      a.line_inv = line_inv;
+      a.guard = nullptr;
+      if (gemm_f16_supported(a, b, C, ldc, M, N, K)) {
+        DLB_TRY(planes_transpose_scaled(ctx, A.ptr, A.stride_k, K, M, hi_t, lo_t, kp, cmax, line_inv));
+        A = a;
+        B = b;
+      }
+    }
+  }
+
   if (ctx->gemm_kind == DLB_GEMM_F16X3 && gemm_f16_supported(A, B, C, ldc, M, N, K)) {
     // fp16 planes: the caller's registered plane buffers, or planes derived
     // into scratch for this call.
@@ -631,16 +672,27 @@ dlb_status dlb_fc_backward_input_derivative(dlb_ctx *ctx, const float *delta, co
 dlb_status dlb_fc_weight_gradient(dlb_ctx *ctx, const float *delta, const float *delta_lo,
                                   const float *X, const float *X_lo, float *dW, float *dbias,
                                   int rows, int n_in, int n_out, int accumulate) {
+  return fc_weight_gradient_lines(ctx, delta, delta_lo, X, X_lo, dW, dbias, rows, n_in, n_out, accumulate, false);
+}
+
+}  // extern "C"
+
+dlb_status dlb::fc_weight_gradient_lines(dlb_ctx *ctx, const float *delta, const float *delta_lo, const float *X,
+                                         const float *X_lo, float *dW, float *dbias, int rows, int n_in, int n_out,
+                                         int accumulate, bool rescale_lines) {
   DLB_REQUIRE(ctx && delta && X && dW && rows > 0 && n_in > 0 && n_out > 0,
               "dlb_fc_weight_gradient");
   GemmOperand A{delta, delta_lo, 1, n_out};  // (m=o, k=b): delta[b,o]
   GemmOperand B{X, X_lo, 1, n_in};           // (n=i, k=b): X[b,i]
+  A.rescale_lines = rescale_lines;
   GemmEpilogue ep;
   ep.accumulate = accumulate;
   DLB_TRY(gemm(ctx, A, B, dW, n_in, n_out, n_in, rows, ep));
   if (dbias) DLB_TRY(bias_gradient(ctx, delta, rows, n_out, dbias, accumulate));
   return DLB_OK;
 }
+
+extern "C" {
 
 // ---- NCCL -----------------------------------------------------------------------
 

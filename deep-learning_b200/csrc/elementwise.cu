@@ -764,27 +764,61 @@ __global__ void loss_delta_mse_kernel(const float *__restrict__ pre, const float
 }
 
 // Softmax + cross-entropy, one warp per row.
+// delta_j = sum_k (q_j [j == k] - q_k q_j) L'_k with L'_k = 0 unless y_k == 1
+// (compute_error_mp.cpp L:84-107): the warp first lists the classes with
+// y_k == 1 in ascending order (one for a one-hot target), then every j adds the
+// terms of those classes only, in the reference's order and with its
+// expressions; the terms left out are the ones the reference adds as zeros.
+// A row with more than SOFTMAX_LIST such classes takes the full double loop.
+constexpr int SOFTMAX_LIST = 32;
 __global__ void loss_delta_softmax_ce_kernel(const float *__restrict__ q, const float *__restrict__ y,
                                              float *__restrict__ delta, float *__restrict__ delta_lo,
                                              int rows, int n, float rows_global, double *loss_sum,
                                              unsigned *amax) {
   pdl_enter();
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32;
+  __shared__ int list_k[8][SOFTMAX_LIST];
+  __shared__ float list_q[8][SOFTMAX_LIST], list_dl[8][SOFTMAX_LIST];
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x % 32, w = threadIdx.x / 32;
   double local = 0.0;
   unsigned mx = 0;
   if (warp < rows) {
     const float *qr = q + (size_t)warp * n, *yr = y + (size_t)warp * n;
     const float EPS = 1e-7f;
-    for (int j = lane; j < n; j += 32) {
-      const float qj = qr[j];
-      // delta_j = sum_k (q_j [j==k] - q_k q_j) * L'_k ; L'_k = 0 unless y_k == 1.
-      float e = 0.f;
-      for (int k = 0; k < n; ++k) {
-        if (yr[k] == 1.f) {
+    int count = 0;
+    for (int k0 = 0; k0 < n; k0 += 32) {
+      const int k = k0 + lane;
+      const bool hit = k < n && yr[k] == 1.f;
+      const unsigned m = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const int at = count + __popc(m & ((1u << lane) - 1u));
+        if (at < SOFTMAX_LIST) {
           const float qk = qr[k];
           float dl = -1.f / clipf(qk, EPS, 1.f - EPS);
           dl /= rows_global;
-          e += (qj * (j == k ? 1.f : 0.f) - qk * qj) * dl;
+          list_k[w][at] = k;
+          list_q[w][at] = qk;
+          list_dl[w][at] = dl;
+        }
+      }
+      count += __popc(m);
+    }
+    __syncwarp();
+    for (int j = lane; j < n; j += 32) {
+      const float qj = qr[j];
+      float e = 0.f;
+      if (count <= SOFTMAX_LIST) {
+        for (int i = 0; i < count; ++i) {
+          const float qk = list_q[w][i];
+          e += (qj * (j == list_k[w][i] ? 1.f : 0.f) - qk * qj) * list_dl[w][i];
+        }
+      } else {
+        for (int k = 0; k < n; ++k) {
+          if (yr[k] == 1.f) {
+            const float qk = qr[k];
+            float dl = -1.f / clipf(qk, EPS, 1.f - EPS);
+            dl /= rows_global;
+            e += (qj * (j == k ? 1.f : 0.f) - qk * qj) * dl;
+          }
         }
       }
       delta[(size_t)warp * n + j] = e;

@@ -132,7 +132,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
                         const float *__restrict__ bias, int accumulate, int tiles_n, int whole_tiles,
                         int parts, int total_items, const float *__restrict__ scale_a,
                         const float *__restrict__ scale_b, int *status, const unsigned *guard_a,
-                        const unsigned *guard_b, unsigned mask_a, unsigned mask_b, SimtOperands fp32, unsigned long long *fallbacks,
+                        const unsigned *guard_b, unsigned mask_a, unsigned mask_b,
+                        const float *__restrict__ line_inv_a, SimtOperands fp32, unsigned long long *fallbacks,
                         const FusedEpilogue fe) {
   pdl_enter();
   using P = PairPlan<STAGES>;
@@ -287,7 +288,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     const int h = (warp - 2) >> 2;
     constexpr int HALF = PN / 2;
     float *tile = reinterpret_cast<float *>(smem + P::EPI_OFFSET) + (warp - 2) * 32 * 33;
-    const float out_a = 1.f / __ldg(scale_a), out_b = 1.f / __ldg(scale_b);
+    const float out_b = 1.f / __ldg(scale_b);
+    const float tensor_out_a = line_inv_a ? 1.f : 1.f / __ldg(scale_a);
     const float plane_scale = FUSED && fe.sink.hi ? sink_scale(fe.sink) : 1.f;
     const uint32_t lead_acc_empty0 = map_to_cta(acc_empty0, 0);
     float acc[HALF];
@@ -318,6 +320,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
       }
       if (!ok) break;
       const int row_base = w.m0 + (int)rank * BM + q * 32;
+      // This thread holds row row_base + lane; planes with a scale per line bring 1 / scale per row.
+      const float out_a = line_inv_a ? __ldg(line_inv_a + min(row_base + lane, M - 1)) : tensor_out_a;
 #pragma unroll
       for (int j = 0; j < HALF / 32; ++j) {
         const int col0 = w.n0 + h * HALF + j * 32;
@@ -463,7 +467,7 @@ dlb_status launch_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B,
                                (size_t)N * sizeof(float), (size_t)(M - first_row), ctx->stream));
   }
   const int items = whole_tiles + parts * split_tiles;
-  DLB_LAUNCH_KERNEL(ctx, kernel, 2 * min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, parts, items, A.scale, B.scale, ctx->d_status, A.guard, B.guard, A.guard_mask, B.guard_mask, SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr, FUSED ? *ep.fused : FusedEpilogue{});
+  DLB_LAUNCH_KERNEL(ctx, kernel, 2 * min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, parts, items, A.scale, B.scale, ctx->d_status, A.guard, B.guard, A.guard_mask, B.guard_mask, A.line_inv, SimtOperands{A.ptr, A.fp32_stride_mn ? A.fp32_stride_mn : A.stride_mn, A.fp32_stride_k ? A.fp32_stride_k : A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr, FUSED ? *ep.fused : FusedEpilogue{});
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }

@@ -528,7 +528,7 @@ dlb_status launch(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B, floa
                                (size_t)N * sizeof(float), (size_t)(M - first_row), ctx->stream));
   }
   const int items = whole_tiles + 2 * split_tiles;
-  DLB_LAUNCH_KERNEL(ctx, kernel, min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, items, A.scale, B.scale, ctx->d_status, ES == 2 ? A.guard : nullptr, ES == 2 ? B.guard : nullptr, A.guard_mask, B.guard_mask, SimtOperands{A.ptr, A.stride_mn, A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr);
+  DLB_LAUNCH_KERNEL(ctx, kernel, min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, items, A.scale, B.scale, ctx->d_status, ES == 2 ? A.guard : nullptr, ES == 2 ? B.guard : nullptr, A.guard_mask, B.guard_mask, SimtOperands{A.ptr, A.fp32_stride_mn ? A.fp32_stride_mn : A.stride_mn, A.fp32_stride_k ? A.fp32_stride_k : A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr);
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }

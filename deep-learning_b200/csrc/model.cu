@@ -46,6 +46,13 @@ float indrnn_magnitude(const dlb_model *m) { return fminf(fmaxf(m->clip_gradient
 
 bool is_indrnn(const LayerRT &l) { return l.type == DLB_LAYER_FULLY_CONNECTED_INDEPENDENTLY_RECURRENT; }
 bool is_lstm(const LayerRT &l) { return l.type == DLB_LAYER_LSTM; }
+// Layer i holds the error of a softmax output: its columns are the classes,
+// and the classes nobody is wrong about have errors many orders of magnitude
+// below the others' once the model has learnt something, so the layer's weight
+// gradient takes planes with a scale per class.
+bool class_error(const dlb_model *m, size_t i) {
+  return i + 1 == m->layers.size() && m->layers[i].af == DLB_AF_SOFTMAX;
+}
 size_t lstm_gates(const LayerRT &l) { return l.units + 3 * l.blocks; }
 
 // Bounds the recurrent weights of an IndRNN layer are clamped to after an
@@ -2066,8 +2073,9 @@ static dlb_status update_derivatives_flat(dlb_model *m, size_t rows, OwnerUpdate
       X_lo = l.IN_lo;
     }
     float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
-    DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn,
-                                   dbias, (int)rows, (int)l.fan_in, (int)l.units, m->grads_clean ? 0 : 1));
+    DLB_TRY(fc_weight_gradient_lines(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn, dbias,
+                                     (int)rows, (int)l.fan_in, (int)l.units, m->grads_clean ? 0 : 1,
+                                     class_error(m, i)));
     if (owners) {
       // The backward pass is over: nothing reads the weights any more.
       DLB_TRY(owners->after_gradient(l));
@@ -2467,8 +2475,8 @@ static dlb_status backward_and_derivatives_overlapped(dlb_model *m, size_t rows,
     const float *X = i == 1 ? m->input : m->layers[i - 1].A;
     const float *X_lo = i == 1 ? m->input_lo : m->layers[i - 1].A_lo;
     float *dbias = l.norm == DLB_NORM_NONE ? m->grads + l.first_bias : nullptr;
-    DLB_TRY(dlb_fc_weight_gradient(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn, dbias,
-                                   B, (int)l.fan_in, H, accumulate));
+    DLB_TRY(fc_weight_gradient_lines(m->ctx, l.delta, l.delta_lo, X, X_lo, m->grads + l.first_conn, dbias,
+                                     B, (int)l.fan_in, H, accumulate, class_error(m, i)));
     if (shard) {
       DLB_TRY(owners.reduce(l));
     } else {

@@ -95,6 +95,52 @@ __global__ void __launch_bounds__(32 * SPLIT_LANES_Y)
   track.finish(k, shared, tx, ty, SPLIT_LANES_Y, blockIdx.x * 128, cols, live);
 }
 
+// Largest |x| of every column of x [K, M]: blocks of 32 columns x 8 row lanes
+// over a slab of rows, one atomic per column and block.
+__global__ void column_absmax_kernel(const float *__restrict__ x, long long pitch, int K, int M, int rows_per_block,
+                                     unsigned *__restrict__ cmax) {
+  pdl_enter();
+  __shared__ unsigned fold[8][32];
+  const int m = blockIdx.x * 32 + threadIdx.x;
+  const int k0 = blockIdx.y * rows_per_block, k1 = min(K, k0 + rows_per_block);
+  unsigned v = 0u;
+  if (m < M)
+    for (int k = k0 + threadIdx.y; k < k1; k += 8) v = max(v, abs_bits(x[(long long)k * pitch + m]));
+  fold[threadIdx.y][threadIdx.x] = v;
+  __syncthreads();
+  if (threadIdx.y == 0 && m < M) {
+#pragma unroll
+    for (int y = 1; y < 8; ++y) v = max(v, fold[y][threadIdx.x]);
+    if (v) atomicMax(cmax + m, v);
+  }
+}
+
+// planes_t[m, k] = halves of s_m x[k, m], s_m from the column's maximum: 32 x 32
+// tiles through shared memory.
+__global__ void transpose_split_kernel(const float *__restrict__ x, long long pitch, int K, int M,
+                                       const unsigned *__restrict__ cmax, uint16_t *__restrict__ hi_t,
+                                       uint16_t *__restrict__ lo_t, long long kp, float *__restrict__ line_inv) {
+  pdl_enter();
+  __shared__ float tile[32][33];
+  const int m0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  for (int y = threadIdx.y; y < 32; y += 8) {
+    const int k = k0 + y, m = m0 + threadIdx.x;
+    tile[y][threadIdx.x] = (k < K && m < M) ? x[(long long)k * pitch + m] : 0.f;
+  }
+  __syncthreads();
+  for (int y = threadIdx.y; y < 32; y += 8) {
+    const int m = m0 + y, k = k0 + threadIdx.x;
+    if (m < M && k < kp) {
+      const float s = plane_scale_from_bits(cmax[m], PLANE_EXP_OWN);
+      __half h, l;
+      plane_halves(tile[threadIdx.x][y], s, &h, &l);
+      hi_t[(long long)m * kp + k] = *reinterpret_cast<const uint16_t *>(&h);
+      lo_t[(long long)m * kp + k] = *reinterpret_cast<const uint16_t *>(&l);
+      if (k == 0) line_inv[m] = 1.f / s;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(1024) planes_finalize_kernel(PlaneSink k) {
   pdl_enter(); sink_finalize(k); }
 
@@ -157,6 +203,18 @@ dlb_status launch_split(dlb_ctx *ctx, const float *x, size_t n, int rows, int co
 }
 
 }  // namespace
+
+dlb_status planes_transpose_scaled(dlb_ctx *ctx, const float *x, long long pitch, int K, int M, uint16_t *hi_t,
+                                   uint16_t *lo_t, long long kp, unsigned *cmax, float *line_inv) {
+  DLB_CUDA(cudaMemsetAsync(cmax, 0, (size_t)M * sizeof(unsigned), ctx->stream));
+  const int slabs = max(1, min(ceil_div(K, 64), ceil_div(ctx->sm_count * 8, ceil_div(M, 32))));
+  const int rows_per_block = ceil_div(K, slabs);
+  DLB_LAUNCH_KERNEL(ctx, column_absmax_kernel, dim3(ceil_div(M, 32), ceil_div(K, rows_per_block)), dim3(32, 8), 0, x, pitch, K, M, rows_per_block, cmax);
+  DLB_LAUNCHED(ctx);
+  DLB_LAUNCH_KERNEL(ctx, transpose_split_kernel, dim3(ceil_div(M, 32), ceil_div((int)kp, 32)), dim3(32, 8), 0, x, pitch, K, M, cmax, hi_t, lo_t, kp, line_inv);
+  DLB_LAUNCHED(ctx);
+  return DLB_OK;
+}
 
 void planes_rows_exempt(dlb_ctx *ctx, const float *planes, size_t bytes, bool on) {
   if (!planes) return;

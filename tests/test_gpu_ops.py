@@ -93,6 +93,43 @@ def test_fc_forward_bias_and_gradient_accumulate(gpu_ctx):
     assert util.rel_l2(db, delta.astype(np.float64).sum(0)) <= GEMM_TOL
 
 
+def test_weight_gradient_with_output_rows_that_are_no_multiple_of_64(gpu_ctx):
+    """1000 classes: TMA cannot tile the mn-contiguous error [rows, 1000] as the
+    A operand of delta^T X.  The library makes planes of the error for this
+    product, k contiguous and with a scale per class, and the product stays on
+    the tensor cores (one tensor-core launch on record, nothing on the fp32
+    kernel) within the bar of the other products, row by row as well, although
+    every seventh class has errors 2^-30 of the others'."""
+    ctx, L = gpu_ctx, gpu_ctx.L
+    rng = np.random.default_rng(8)
+    rows, n_in, n_out = 1024, 2048, 1000
+    q = rng.random((rows, n_out), dtype=np.float32)
+    q /= q.sum(axis=1, keepdims=True)
+    y = np.zeros((rows, n_out), np.float32)
+    y[np.arange(rows), rng.integers(0, n_out, rows)] = 1.0
+    delta = ((q - y) / rows).astype(np.float32)
+    delta[:, ::7] *= np.float32(2.0 ** -30)
+    X = rng.standard_normal((rows, n_in), dtype=np.float32)
+    d, x = ctx.array(delta), ctx.array(X)
+    dp, xp = ctx.empty(delta.shape), ctx.empty(X.shape)
+    check(L.dlb_split_planes_2d(ctx.h, d.ptr, dp.ptr, rows, n_out), "split")
+    check(L.dlb_split_planes_2d(ctx.h, x.ptr, xp.ptr, rows, n_in), "split")
+    out = ctx.empty((n_out, n_in))
+    ctx.gemm_profile(True)
+    ctx.gemm_profile_read()
+    fell = ctx.guard_counters()[1]
+    check(L.dlb_fc_weight_gradient(ctx.h, d.ptr, dp.ptr, x.ptr, xp.ptr, out.ptr, None, rows, n_in, n_out, 0), "dw")
+    assert ctx.sync() == 0
+    launches, _, _ = ctx.gemm_profile_read()
+    ctx.gemm_profile(False)
+    assert ctx.guard_counters()[1] == fell
+    want = delta.astype(np.float64).T @ X.astype(np.float64)
+    got = out.get()
+    assert launches == 1, "the product ran on the tensor cores"
+    assert util.rel_l2(got, want) <= GEMM_TOL
+    assert util.rowwise_rel_l2(got, want) <= 1e-5
+
+
 @pytest.mark.parametrize("kind", ["fwd", "dx", "dw"])
 def test_products_whose_last_wave_is_split_along_k(gpu_ctx, kind):
     """160 output tiles on 148 SMs: the 12 tiles of the last wave are each
