@@ -200,7 +200,13 @@ dlb_status dlb_fc_backward_input(dlb_ctx *ctx, const float *delta, const float *
 /* dW[o,i] (+)= sum_b delta[b,o] * X[b,i];  dbias[o] (+)= sum_b delta[b,o] when
  * dbias != NULL.  accumulate != 0 adds to dW/dbias, else overwrites.
  * ref: Model::Update_Derivative_Weight__FC__OpenMP
- * (v1/learner/update_derivative_fwp_mp.cpp L:175-213) and ...__Bias (L:215-240). */
+ * (v1/learner/update_derivative_fwp_mp.cpp L:175-213) and ...__Bias (L:215-240).
+ * Where n_out is not a multiple of 64 (and the product is large enough for the
+ * tensor cores) the planes of delta are not used: the call makes planes of its
+ * own for this product, one scale per unit o, from the fp32 tensor.  Inside a
+ * model the weight gradient of a softmax output layer takes the same path
+ * whatever its width, because the errors of its classes differ by many orders
+ * of magnitude. */
 dlb_status dlb_fc_weight_gradient(dlb_ctx *ctx, const float *delta, const float *delta_lo,
                                   const float *X, const float *X_lo, float *dW, float *dbias,
                                   int rows, int n_in, int n_out, int accumulate);
