@@ -212,7 +212,7 @@ def _brn_state(rng, T, n):
     return mean, sigma, r, d, gamma, beta
 
 
-@pytest.mark.parametrize("T,B,n", [(5, 16, 128), (7, 9, 10), (1, 8, 32)])
+@pytest.mark.parametrize("T,B,n", [(5, 16, 128), (7, 9, 10), (1, 8, 32), (6, 40, 256), (3, 5, 132), (2, 3, 384)])
 @pytest.mark.parametrize("af", [ACTIVATION.RELU, ACTIVATION.ELU])
 def test_time_kernels(gpu_ctx, T, B, n, af):
     """Forward walk, reverse walk, sums and apply against numpy on one layer."""
@@ -248,6 +248,15 @@ def test_time_kernels(gpu_ctx, T, B, n, af):
         s = 2.0 ** (14 - np.floor(np.log2(np.abs(got_h).max())))
         both = (planes[:got_h.size] + planes[got_h.size:]) / s
         assert np.allclose(both, got_h.ravel(), rtol=2.0 ** -21, atol=2.0 ** -38 * np.abs(got_h).max())
+        # A second call on the same buffers: the walk writes the planes itself where
+        # the width allows, with the scale predicted from the first call (two
+        # octaves lower); the activations are the same bits either way.
+        dlb200.check(L.dlb_indrnn_forward(ctx.h, Zd.ptr, C.byref(ua), ud.ptr, af, A.ptr, A_lo.ptr, T, B, n))
+        assert np.array_equal(A.get(), got_h)
+        planes = A_lo.get().ravel().view(np.float16).astype(np.float64)
+        s2 = s / 4 if n % 128 == 0 else s
+        both = (planes[:got_h.size] + planes[got_h.size:]) / s2
+        assert np.allclose(both, got_h.ravel(), rtol=2.0 ** -21, atol=2.0 ** -36 * np.abs(got_h).max())
     # reverse walk
     dA = rng.standard_normal((T, B, n)).astype(np.float32)
     E = ctx.array(dA)
@@ -285,7 +294,19 @@ def test_time_kernels(gpu_ctx, T, B, n, af):
     dx = (got_e * gamma * (r / sigma)[:, None]).astype(f32)
     dx = dx + got_s[3].astype(f32)[:, None] * ((Z - mean[:, None]) / (N * sigma[:, None]))
     dx = dx + got_s[2].astype(f32)[:, None] * (f32(1) / N)
-    assert util.rel_l2(E.get(), dx) <= 2e-6
+    got_dx = E.get()
+    assert util.rel_l2(got_dx, dx) <= 2e-6
+    if ctx.gemm_kind() != 0:
+        # The apply again on the same buffers (its own output as the error this
+        # time): the planes it now writes itself hold what it wrote to the tensor.
+        dlb200.check(L.dlb_brn_time_backward_apply(ctx.h, E.ptr, delta_lo.ptr, Zd.ptr, C.byref(ua), sums.ptr, B, T, B, n))
+        again = E.get()
+        planes = delta_lo.get().ravel().view(np.float16).astype(np.float64)
+        ratio = (planes[:again.size] + planes[again.size:]) / np.where(again.ravel() == 0, 1, again.ravel())
+        live = np.abs(again.ravel()) > 2.0 ** -10 * np.abs(again).max()
+        scale = np.median(ratio[live])
+        assert scale == 2.0 ** np.round(np.log2(scale))
+        assert np.allclose(ratio[live], scale, rtol=2.0 ** -20, atol=0)
     assert ctx.sync() == 0
 
 
