@@ -1429,7 +1429,7 @@ __global__ void loss_eval_kernel(int loss, int accu_fn, float accu_var, const fl
     if (accu_fn == DLB_ACCU_DISTANCE) hits += __shfl_xor_sync(0xffffffffu, hits, o);
   }
   if (lane == 0) {
-    if (local != 0.0) atomicAdd(loss_sum, local);
+    if (loss_sum && local != 0.0) atomicAdd(loss_sum, local);
     if (hits != 0.0) atomicAdd(accu_sum, hits);
   }
 }
@@ -1438,7 +1438,7 @@ __global__ void loss_eval_kernel(int loss, int accu_fn, float accu_var, const fl
 extern "C" dlb_status dlb_loss_eval(dlb_ctx *ctx, int loss, int accu_fn, float accu_var, const float *q,
                                     const float *y, int rows, int n_out, double *loss_sum,
                                     double *accu_sum) {
-  DLB_REQUIRE(ctx && q && y && loss_sum && accu_sum && rows > 0 && n_out > 0, "dlb_loss_eval");
+  DLB_REQUIRE(ctx && q && y && accu_sum && rows > 0 && n_out > 0, "dlb_loss_eval");
   if ((loss != DLB_LOSS_MSE && loss != DLB_LOSS_CROSS_ENTROPY) ||
       (accu_fn != DLB_ACCU_DISTANCE && accu_fn != DLB_ACCU_CROSS_ENTROPY)) {
     set_error("dlb_loss_eval: loss %d / accuracy function %d outside the supported set", loss, accu_fn);

@@ -34,6 +34,7 @@ struct dlb_minibatch {
   std::vector<size_t> order;   // MiniBatch::ptr_array_stochastic_index
   std::mt19937 gen;            // DistributionBase::p_generator_mt19937
   float *host_x[2] = {nullptr, nullptr}, *host_y[2] = {nullptr, nullptr};  // page-locked, last_batch rows each
+  double accuracy = 0.0;       // mean of the batch accuracies of the last pass (percent)
 };
 
 namespace {
@@ -165,7 +166,9 @@ dlb_status dlb_minibatch_train(dlb_minibatch *mb, double *loss) {
   const size_t saved_training = m->training_size, saved_global = m->global_rows;
   DLB_TRY(dlb_model_set_training_size(m, mb->n_data * world));  // update_weights_mp(rows of the batch, rows of the data set)
   DLB_TRY(dlb_model_set_loss_lag(m, 0));
-  double sum = 0.0;
+  const bool saved_accuracy = m->training_accuracy;
+  m->training_accuracy = true;  // train_mp adds up the accuracy of every batch beside its loss
+  double sum = 0.0, sum_accuracy = 0.0;
   dlb_status st = DLB_OK;
   gather(mb, 0, 0);
   st = dlb_model_stage_batch(m, rows_of(mb, 0), mb->host_x[0], mb->host_y[0]);
@@ -182,13 +185,20 @@ dlb_status dlb_minibatch_train(dlb_minibatch *mb, double *loss) {
     double batch_loss = 0.0;
     if (st == DLB_OK) st = dlb_model_train_step_staged(m, &batch_loss);
     sum += batch_loss;
+    sum_accuracy += m->step_accuracy;
   }
   m->training_size = saved_training;
   m->global_rows = saved_global;
+  m->training_accuracy = saved_accuracy;
   if (st != DLB_OK) return st;
   m->hp.epoch_time_step += 1.f;
   *loss = sum / (double)mb->n_batch;
+  mb->accuracy = sum_accuracy / (double)mb->n_batch;
   return DLB_OK;
 }
+
+// Mean of the batch accuracies of the last dlb_minibatch_train, in percent
+// (what train_mp hands to Model::set_accu(ENV::TRAIN, ...)).
+double dlb_minibatch_get_accuracy(const dlb_minibatch *mb) { return mb ? mb->accuracy : 0.0; }
 
 }  // extern "C"

@@ -1702,11 +1702,20 @@ dlb_status dlb_model_compute_error_device(dlb_model *m, size_t rows, const float
       DLB_TRY(dlb_loss_delta(m->ctx, m->loss, o.af, o.Z + skip, o.A + skip, first, o.delta + skip,
                              o.delta_lo + skip, (int)((T - d) * rows), (int)W, Bg, unused));
     }
+    // The accuracy counter of the training pass (compute_error_rec_mp,
+    // v1/learner/compute_error_mp.cpp L:178-231), when asked for.
+    if (m->training_accuracy)
+      DLB_TRY(dlb_loss_eval(m->ctx, m->loss, m->accu_fn, m->accu_var, o.A + skip, m->target + skip,
+                            (int)((T - d) * rows), (int)W, nullptr, m->accu_sum));
     m->loss_rows += rows * (T - d);
     return DLB_OK;
   }
   DLB_TRY(dlb_loss_delta(m->ctx, m->loss, o.af, o.Z, o.A, Y_dev, o.delta, o.delta_lo, (int)rows,
                          (int)o.units, Bg, m->loss_sum));
+  // compute_error_fwp_mp counts the accuracy as well (compute_error_mp.cpp L:60-112).
+  if (m->training_accuracy)
+    DLB_TRY(dlb_loss_eval(m->ctx, m->loss, m->accu_fn, m->accu_var, o.A, Y_dev, (int)rows, (int)o.units, nullptr,
+                          m->accu_sum));
   m->loss_rows += rows;
   return DLB_OK;
 }
@@ -2401,21 +2410,27 @@ static dlb_status update_and_merge_overlapped(dlb_model *m, size_t rows);
 static dlb_status loss_capture(dlb_model *m, int slot) {
   DLB_REQUIRE(m->loss_sum, "loss: no step has run");
   if (!m->loss_tmp) {
-    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&m->loss_tmp), 2 * sizeof(double)));
-    DLB_TRY(dlb_host_alloc(reinterpret_cast<void **>(&m->loss_host), 2 * sizeof(double)));
+    DLB_TRY(dlb_malloc(m->ctx, reinterpret_cast<void **>(&m->loss_tmp), 4 * sizeof(double)));
+    DLB_TRY(dlb_host_alloc(reinterpret_cast<void **>(&m->loss_host), 4 * sizeof(double)));
     for (cudaEvent_t &e : m->loss_ready) DLB_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   }
-  DLB_TRY(dlb_memcpy_d2d(m->ctx, m->loss_tmp + slot, m->loss_sum, sizeof(double)));
-  DLB_TRY(dlb_allreduce_f64(m->ctx, m->loss_tmp + slot, 1));
-  DLB_CUDA(cudaMemcpyAsync(m->loss_host + slot, m->loss_tmp + slot, sizeof(double), cudaMemcpyDeviceToHost,
-                           m->ctx->stream));
+  // Per slot {loss sum, accuracy counter}; the counter only when the training
+  // pass keeps it.
+  double *dev = m->loss_tmp + 2 * slot, *host = m->loss_host + 2 * slot;
+  const size_t n = m->training_accuracy ? 2 : 1;
+  DLB_TRY(dlb_memcpy_d2d(m->ctx, dev, m->loss_sum, sizeof(double)));
+  if (n == 2) DLB_TRY(dlb_memcpy_d2d(m->ctx, dev + 1, m->accu_sum, sizeof(double)));
+  DLB_TRY(dlb_allreduce_f64(m->ctx, dev, n));
+  DLB_CUDA(cudaMemcpyAsync(host, dev, n * sizeof(double), cudaMemcpyDeviceToHost, m->ctx->stream));
   DLB_CUDA(cudaEventRecord(m->loss_ready[slot], m->ctx->stream));
   m->loss_rows_at[slot] = m->loss_rows;
   m->loss_valid[slot] = true;
   return DLB_OK;
 }
 
-// Waits for a captured loss and normalises it as dlb_model_get_loss does.
+// Waits for a captured loss and normalises it as dlb_model_get_loss does; the
+// accuracy of the same step (percent, as dlb_model_get_accuracy) goes to
+// m->step_accuracy when the training pass keeps the counter.
 static dlb_status loss_collect(dlb_model *m, int slot, double *loss) {
   if (!m->loss_valid[slot]) {
     *loss = nan("");  // a lagged read before the first step has finished
@@ -2423,7 +2438,11 @@ static dlb_status loss_collect(dlb_model *m, int slot, double *loss) {
   }
   DLB_CUDA(cudaEventSynchronize(m->loss_ready[slot]));
   const double rows = (double)m->loss_rows_at[slot] * (double)dlb_comm_world(m->ctx);
-  const double s = m->loss_host[slot];
+  const double s = m->loss_host[2 * slot];
+  if (m->training_accuracy) {
+    const double trials = rows * (m->accu_fn == DLB_ACCU_CROSS_ENTROPY ? 1.0 : (double)n_out(m));
+    m->step_accuracy = trials == 0.0 ? 0.0 : m->loss_host[2 * slot + 1] / trials * 100.0;
+  }
   if (rows == 0) { *loss = 1.0; return DLB_OK; }
   *loss = m->loss == DLB_LOSS_CROSS_ENTROPY ? s / rows : s / (rows * (double)n_out(m));
   return DLB_OK;
@@ -2632,6 +2651,12 @@ dlb_status dlb_model_train_step_staged(dlb_model *m, double *loss) {
   const size_t g = m->global_rows ? m->global_rows : rows;
   DLB_TRY(dlb_model_update_weights(m, g, m->training_size ? m->training_size : g));
   if (loss) DLB_TRY(loss_collect(m, m->loss_lag ? slot ^ 1 : slot, loss));
+  return DLB_OK;
+}
+
+dlb_status dlb_model_set_training_accuracy(dlb_model *m, int on) {
+  DLB_REQUIRE(m, "set_training_accuracy");
+  m->training_accuracy = on != 0;
   return DLB_OK;
 }
 

@@ -116,6 +116,7 @@ struct dlb_model {
   int accu_fn = DLB_ACCU_DISTANCE;   // v1/learner/model.hpp L:157
   float accu_var = 0.49f;            // L:3019
   double *accu_sum = nullptr;
+  bool training_accuracy = false;    // compute_error counts the accuracy too (one more pass over the outputs)
   float *ones = nullptr, *zeros = nullptr;
   size_t const_units = 0;
   float *stage_x = nullptr, *stage_y = nullptr;  // pinned
@@ -142,8 +143,9 @@ struct dlb_model {
   // sum, its exchange across ranks, a copy into page-locked host memory and an
   // event, two slots used in turn, so that the update is enqueued before the
   // host waits.  loss_lag = 1: a staged step returns the loss of the step before.
-  double *loss_tmp = nullptr;       // device [2]
-  double *loss_host = nullptr;      // page-locked [2]
+  double *loss_tmp = nullptr;       // device [2 slots][loss sum, accuracy counter]
+  double *loss_host = nullptr;      // page-locked, the same
+  double step_accuracy = 0.0;       // percent, of the step whose loss was collected last
   cudaEvent_t loss_ready[2] = {nullptr, nullptr};
   size_t loss_rows_at[2] = {0, 0};
   bool loss_valid[2] = {false, false};

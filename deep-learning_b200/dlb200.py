@@ -193,6 +193,8 @@ SIGNATURES = {
     "dlb_model_train_step_staged": (_i, [_vp, C.POINTER(_d)]),
     "dlb_model_set_loss_lag": (_i, [_vp, _i]),
     "dlb_model_set_sharded_update": (_i, [_vp, _i]),
+    "dlb_model_set_training_accuracy": (_i, [_vp, _i]),
+    "dlb_minibatch_get_accuracy": (_d, [_vp]),
     "dlb_model_get_layer_outputs": (_i, [_vp, _sz, _sz, _vp]),
     "dlb_model_get_layer_errors": (_i, [_vp, _sz, _sz, _i, _vp]),
 }
@@ -674,6 +676,10 @@ class Model:
         """1: train_step_staged returns the loss of the step before (NaN at first)."""
         check(self.L.dlb_model_set_loss_lag(self.h, int(steps)), "set_loss_lag")
 
+    def set_training_accuracy(self, on):
+        """True: compute_error keeps the accuracy counter too (get_accuracy after a training pass)."""
+        check(self.L.dlb_model_set_training_accuracy(self.h, int(bool(on))), "set_training_accuracy")
+
     def set_sharded_update(self, on):
         """Several ranks, one-call steps: owner-computes update of the weight matrices
         (default on) or all-reduce and the replicated update."""
@@ -750,6 +756,10 @@ class MiniBatch:
         v = _d(0.0)
         check(self.L.dlb_minibatch_train(self.h, C.byref(v)), "minibatch_train")
         return v.value
+
+    def accuracy(self):
+        """Mean of the batch accuracies of the last pass, in percent."""
+        return float(self.L.dlb_minibatch_get_accuracy(self.h))
 
 
 class Checkpointer:

@@ -688,6 +688,13 @@ dlb_status dlb_model_set_accu_var(dlb_model *m, float v);
 dlb_status dlb_model_compute_loss(dlb_model *m, size_t rows, const float *const *Ym);
 dlb_status dlb_model_compute_loss_device(dlb_model *m, size_t rows, const float *Y_dev);
 dlb_status dlb_model_get_accuracy(dlb_model *m, double *accuracy);
+/* on = 1: dlb_model_compute_error keeps the accuracy counter as well, as
+ * Model::compute_error does in the reference (compute_error_fwp_mp /
+ * compute_error_rec_mp, v1/learner/compute_error_mp.cpp L:60-112, L:178-231):
+ * one more pass over the outputs and targets per step; dlb_model_get_accuracy
+ * then reads the accuracy of the training pass since dlb_model_reset_loss.
+ * Default 0: training steps leave the counter alone. */
+dlb_status dlb_model_set_training_accuracy(dlb_model *m, int on);
 /* Across GPUs this is the gradient all-reduce (the reference's thread merge,
  * v1/learner/merge.cpp L:76-100). */
 dlb_status dlb_model_merge_derivatives(dlb_model *m);
@@ -768,9 +775,12 @@ dlb_status dlb_checkpointer_load(dlb_checkpointer *c, int *found);
  * update_weights(rows of the batch, rows of the data set) and its loss read;
  * epoch_time_step + 1; *loss = mean of the batch losses.  Batch k + 1 is
  * gathered into page-locked memory and copied to the device while batch k
- * trains (dlb_model_stage_batch).  The accuracy pass of train_mp
- * (compute_accuracy, an inference pass per batch) is not part of it: run
- * dlb_model_compute_loss over the rows where it is wanted. */
+ * trains (dlb_model_stage_batch).  train_mp also adds up the accuracy of every
+ * batch (for the accuracy functions supported here DatasetV1::compute_accuracy
+ * returns the counter the training pass kept,
+ * v1/data/dataset/dataset_v1.cpp L:4540-4640): dlb_minibatch_get_accuracy
+ * returns its mean over the batches of the last pass, in percent, the value
+ * train_mp hands to Model::set_accu(ENV::TRAIN, ...). */
 typedef struct dlb_minibatch dlb_minibatch;
 dlb_status dlb_minibatch_create(dlb_minibatch **out, dlb_model *model, const float *const *Xm,
                                 const float *const *Ym, size_t n_examples, int use_shuffle,
@@ -784,6 +794,7 @@ dlb_status dlb_minibatch_shuffle(dlb_minibatch *mb);
 /* The current order of the rows (MiniBatch::ptr_array_stochastic_index), n = n_examples. */
 dlb_status dlb_minibatch_get_order(const dlb_minibatch *mb, size_t *out, size_t n);
 dlb_status dlb_minibatch_train(dlb_minibatch *mb, double *loss);
+double dlb_minibatch_get_accuracy(const dlb_minibatch *mb);
 
 /* Model::set_clip_gradient, both overloads (v1/ops/constraints/clip_gradient.cpp
  * L:30-73): whether update_weights clips, and the norm; the norm also sets the

@@ -217,6 +217,7 @@ def test_minibatch_epoch_trains_like_the_batches_one_by_one(gpu_ctx):
         got = mb.train()
         np.testing.assert_allclose(got, np.mean(want), rtol=1e-12)
         assert np.array_equal(a.get_array("parameters"), b.get_array("parameters"))
+        assert 0.0 <= mb.accuracy() <= 100.0
     assert b.get_hparam("epoch_time_step") == 3.0
     assert gpu_ctx.sync() == 0
     # Shuffled: the reference's Fisher-Yates pass; a permutation fixed by the seed.
@@ -237,6 +238,54 @@ def test_minibatch_epoch_trains_like_the_batches_one_by_one(gpu_ctx):
     with pytest.raises(dlb200.DlbError):
         dlb200.MiniBatch(b, X, Y, 200)
     assert dlb200.MiniBatch(b, X, Y, 100, max_batches=2).last_batch == 100 + int((N / 100 - 2) * 100)
+
+
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("case", ["brn_bernoulli_distance", "softmax_accuracy"])
+def test_training_accuracy_against_the_compiled_reference(gpu_ctx, case):
+    """Model::compute_error keeps the accuracy counter of the training pass; here
+    it is kept on request.  Three training steps each on the compiled reference
+    and on the GPU, the accuracy of every step read where the reference's loop
+    reads it (after the merge of the threads' counters)."""
+    cfg, fn = {
+        "brn_bernoulli_distance": (configs.deep_brn_mlp(64, 128, 2, 32, 96), fc_step.ACCU_DISTANCE),
+        "softmax_accuracy": (configs.mlp_softmax(96, 128, 10, 128), fc_step.ACCU_CROSS_ENTROPY),
+    }[case]
+    B = cfg["batch"]
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    gpu = gpu_model(gpu_ctx, cfg, ref.get_array("parameters"))
+    gpu.set_training_accuracy(True)
+    seen = []
+    for m in (ref, gpu):
+        m.train_begin(B)
+        m.set_accu_fn(fn)
+        for li, mk in masks.items():
+            m.set_dropout_mask(li, mk)
+        acc = []
+        for _ in range(3):
+            m.reset_loss()
+            m.forward_pass(B, X)
+            m.compute_error(B, Y)
+            m.backward_pass(B)
+            m.update_derivatives(B)
+            m.merge_derivatives()     # the reference adds its threads' counters up here
+            acc.append(m.get_accu(B))
+            m.update_weights(B, B)
+        seen.append(acc)
+    assert gpu_ctx.sync() == 0
+    one_trial = 100.0 / (B * (1 if fn == fc_step.ACCU_CROSS_ENTROPY else cfg["layers"][-1]["units"]))
+    print(case, seen)
+    assert any(a > 0 for a in seen[0])
+    for a_ref, a_gpu in zip(*seen):
+        assert abs(a_ref - a_gpu) <= 2 * one_trial
+    # Off (the default): a training step leaves the counter alone.
+    gpu.set_training_accuracy(False)
+    gpu.reset_loss()
+    gpu.forward_pass(B, X)
+    gpu.compute_error(B, Y)
+    assert gpu.get_accu(B) == 0.0
 
 
 def test_unsupported_configurations_are_refused(gpu_ctx):
