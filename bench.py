@@ -11,7 +11,9 @@ renorm + SELU + Bernoulli dropout keep 0.9 per hidden layer, linear output, MSE,
 AMSBound), fp32, 4096 rows per GPU, synthetic N(0,1) inputs and targets and
 Glorot-uniform weights.  Across GPUs the rows are sharded (weak scaling: every
 GPU keeps 4096 rows); batch-renormalization sums and the gradient vector are
-all-reduced over NCCL so that every rank holds the full-batch result.
+summed over NCCL so that every rank holds the full-batch result (the gradient
+of a weight matrix is reduce-scattered by rows, each rank updates the rows it
+owns and the updated rows are gathered: `comm`, `strong` at N > 1).
 
 `value`   samples/s with inputs resident in HBM, timed with CUDA events on the
           library's stream, max over ranks.
@@ -27,6 +29,9 @@ all-reduced over NCCL so that every rank holds the full-batch result.
 `roofline` the tcgen05 GEMM kernel: algorithmic FLOPs (2*M*N*K per launch, not
           multiplied by the three tensor-core products per FLOP) over the summed
           event-timed launch durations inside the timed region.
+`range_guard` counters of the fp16 operand form's range guard over the whole
+          run: operand tensors flagged, products that ran on the fp32 kernel,
+          tensors whose planes were written a second time (all 0 here).
 `cpu_baseline` the reference's own OpenMP step (oracle/_ref, compiled from the
           reference's sources) on this host's cores, on a bounded sample.
 --impl reference times only that CPU implementation.
