@@ -429,10 +429,6 @@ dlb_status check_supported(dlb_model *m) {
     return DLB_ERR_INVALID;
   }
   const bool stepped = time_stepped(m);
-  if (stepped && m->layers[0].dropout != DLB_DROPOUT_NONE) {
-    set_error("model: dropout on the inputs of a time-stepped (recurrent) model is outside the supported path");
-    return DLB_ERR_UNSUPPORTED;
-  }
   for (size_t i = 1; i < m->layers.size(); ++i) {
     const LayerRT &l = m->layers[i];
     if (stepped) {
@@ -1635,6 +1631,23 @@ dlb_status dlb_model_forward_pass_device(dlb_model *m, size_t rows, const float 
     DLB_REQUIRE(X_dev != m->input, "forward_pass_device: input aliases the model's own buffer");
     DLB_REQUIRE(rows * m->seq_w < ((size_t)1 << 31), "forward_pass_device: rows * seq_w overflows int");
     DLB_TRY(dlb_time_major(m->ctx, X_dev, m->input, m->input_lo, (int)rows, (int)m->seq_w, (int)n_in(m)));
+    // Dropout on the inputs, per time step and unit, on the model's copy of the
+    // batch (Model::assign_inputs_rec_mp, v1/learner/assign_inputs.cpp L:219-266):
+    // the Bernoulli kinds by the input layer's mask in training, the plain kind by
+    // its keep probability at inference.  One walk in place (no recurrence, no
+    // activation), which also writes the planes of the masked batch.
+    const LayerRT &in0 = m->layers[0];
+    const bool bern0 = in0.dropout == DLB_DROPOUT_BERNOULLI || in0.dropout == DLB_DROPOUT_BERNOULLI_INVERTED;
+    if (bern0 && m->propagation == DLB_PROPAGATION_TRAINING) {
+      const float keep_scale = in0.dropout == DLB_DROPOUT_BERNOULLI_INVERTED
+                                   ? (in0.dropout_value == 0.f ? 0.f : 1.f / in0.dropout_value)
+                                   : 1.f;
+      DLB_TRY(dlb_indrnn_forward_dropout(m->ctx, m->input, nullptr, nullptr, DLB_AF_LINEAR, in0.mask, keep_scale,
+                                         m->input, m->input_lo, (int)m->seq_w, (int)rows, (int)n_in(m)));
+    } else if (in0.dropout == DLB_DROPOUT_BERNOULLI) {
+      DLB_TRY(dlb_indrnn_forward_dropout(m->ctx, m->input, nullptr, nullptr, DLB_AF_LINEAR, nullptr, in0.dropout_value,
+                                         m->input, m->input_lo, (int)m->seq_w, (int)rows, (int)n_in(m)));
+    }
     return forward_layers(m, rows);
   }
   if (X_dev != m->input) DLB_TRY(dlb_memcpy_d2d(m->ctx, m->input, X_dev, n * sizeof(float)));

@@ -121,6 +121,17 @@ class IndRnnOracleModel(OracleModel):
         T = self.T
         n_in = self.layers[0]["units"]
         a = np.ascontiguousarray(np.asarray(X[:batch], f32).reshape(batch, T, n_in).transpose(1, 0, 2))
+        # Dropout on the inputs, on the model's copy of the batch and per time step
+        # (Model::assign_inputs_rec_mp, v1/learner/assign_inputs.cpp L:219-266):
+        # the Bernoulli kinds by the input layer's mask in training, the plain
+        # kind by its keep probability at inference.
+        kind0, value0 = self.layers[0]["dropout"]
+        if kind0 in (fc_step.DROPOUT_BERNOULLI, fc_step.DROPOUT_BERNOULLI_INVERTED):
+            for t in range(T):
+                if self.training:
+                    a[t] = fc_step.apply_dropout(a[t], kind0, value0, self.layers[0]["mask"][t * n_in:(t + 1) * n_in])
+                elif kind0 == fc_step.DROPOUT_BERNOULLI:
+                    a[t] = (a[t] * f32(value0)).astype(f32)
         self.layers[0]["A"] = a
         for i in range(1, len(self.layers)):
             l = self.layers[i]

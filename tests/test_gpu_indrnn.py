@@ -359,6 +359,35 @@ def test_bernoulli_dropout_through_time(gpu_ctx, kind, norm):
     assert util.rel_l2(out[1], out[0]) <= 1e-5
 
 
+@pytest.mark.parametrize("kind", [2, 3], ids=["plain", "inverted"])
+def test_dropout_on_the_inputs_of_a_time_stepped_model(gpu_ctx, kind):
+    """The input layer's Bernoulli dropout masks the model's copy of the batch per
+    time step and unit (training), or scales it by the keep probability
+    (inference, plain kind), against the CPU restatement (pinned to the compiled
+    reference)."""
+    cfg = configs.indrnn_stack(n_in=64, hidden=128, depth=2, n_out=32, seq_w=6, batch=32)
+    cfg["layers"][0] = dict(cfg["layers"][0], dropout=(kind, 0.6))
+    B, last = cfg["batch"], len(cfg["layers"]) - 1
+    X, Y = configs.synthetic_batch(cfg)
+    masks = configs.dropout_masks(cfg)
+    assert 0 in masks and not masks[0].all()
+    p0 = _kink_free(cfg, X)
+    ora = util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0)
+    mod = util.build(dlb200.Model(gpu_ctx), cfg, params=p0)
+    want = util.trace(ora, cfg, 2, X, Y, masks)
+    got = util.trace(mod, cfg, 2, X, Y, masks)
+    assert gpu_ctx.sync() == 0
+    for key in ("act1", "act3", "delta1", "grads", "params1", "losses"):
+        assert util.rel_l2(got[key], want[key]) <= (1e-4 if key == "params1" else 2e-5), key
+    util.copy_trained_state(mod, ora, cfg)
+    out = []
+    for m in (ora, mod):
+        m.set_propagation(0)
+        m.forward_pass(B, X)
+        out.append(m.get_layer_outputs(last, B).reshape(-1))
+    assert util.rel_l2(out[1], out[0]) <= 1e-5
+
+
 def test_uout_in_a_time_stepped_model(gpu_ctx):
     """UOut on IndRNN layers: the output of a time step becomes h + h * draw before
     the next step's recurrence reads it; draws [seq_w * rows, units] are inputs of

@@ -192,6 +192,32 @@ def test_bernoulli_dropout_through_time_matches_compiled_reference(kind, norm):
     assert util.rel_l2(out[1], out[0]) <= TOL_L2
 
 
+@pytest.mark.skipif(not ref_binding.available(), reason="oracle/_ref not built on this machine")
+@pytest.mark.parametrize("kind", [2, 3], ids=["plain", "inverted"])
+def test_dropout_on_the_inputs_through_time_matches_compiled_reference(kind):
+    """Dropout on the input layer of a time-stepped model: the batch's copy is
+    masked per time step and unit as it is assigned (assign_inputs_rec_mp,
+    v1/learner/assign_inputs.cpp L:219-266); at inference the plain form scales
+    by the keep probability."""
+    cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=2, n_out=5, seq_w=4, batch=5)
+    cfg["layers"][0] = dict(cfg["layers"][0], dropout=(kind, 0.6))
+    ref = util.build(ref_binding.RefModel(), cfg, seed=0)
+    p0 = ref.get_array("parameters")
+    want = util.trace(ref, cfg, steps=3)
+    got = util.trace(util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0), cfg, steps=3)
+    _check(got, want)
+    ora = util.build(fc_indrnn.IndRnnOracleModel(), cfg, params=p0)
+    util.copy_trained_state(ref, ora, cfg)
+    X, _ = configs.synthetic_batch(dict(cfg, data_seed=5))
+    out = []
+    for m in (ref, ora):
+        m.train_begin(5)
+        m.set_propagation(0)
+        m.forward_pass(5, X)
+        out.append(m.get_layer_outputs(3, 5).reshape(-1))
+    assert util.rel_l2(out[1], out[0]) <= TOL_L2
+
+
 def test_parameter_layout():
     """An IndRNN layer's u follows its W; gamma starts at 0.1 for IndRNN layers."""
     cfg = configs.indrnn_stack(n_in=6, hidden=8, depth=2, n_out=5, seq_w=4, batch=3)
