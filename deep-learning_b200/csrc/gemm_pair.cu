@@ -111,14 +111,37 @@ __host__ __device__ __forceinline__ int piece_start(int piece, int parts, int to
   const int at = (int)(((long long)piece * total_kb / parts + chunk_kb - 1) / chunk_kb * chunk_kb);
   return at < total_kb ? at : total_kb;
 }
+// Order of the tiles.  band = 0: row by row.  band > 0: the tile rows are taken
+// in bands of `band`; inside a band the tiles run down a column of the band,
+// then the next column, so that the pairs working at the same time cover a
+// near-square patch of the output (74 pairs: 8 rows x 9 columns, 17 operand
+// blocks instead of the 21 of 4.6 rows x 16 columns) and the band's rows of A
+// stay in L2 while the columns of B stream past.
+__host__ __device__ __forceinline__ void tile_coords(int tile_id, int tiles_m, int tiles_n, int band, int *tm,
+                                                     int *tn) {
+  if (band <= 0) {
+    *tm = tile_id / tiles_n;
+    *tn = tile_id % tiles_n;
+    return;
+  }
+  const int per_band = band * tiles_n;
+  const int b = tile_id / per_band, in_band = tile_id - b * per_band;
+  const int rows = min(band, tiles_m - b * band);  // the last band may be lower
+  *tn = in_band / rows;
+  *tm = b * band + in_band % rows;
+}
+
 template <int CHUNK_KB>
-__device__ __forceinline__ PairItem pair_item(int item, int tiles_n, int whole_tiles, int parts, int total_kb) {
+__device__ __forceinline__ PairItem pair_item(int item, int tiles_m, int tiles_n, int band, int whole_tiles,
+                                              int parts, int total_kb) {
   PairItem w;
   w.split = item >= whole_tiles;
   const int tile_id = w.split ? whole_tiles + (item - whole_tiles) / parts : item;
   w.piece = w.split ? (item - whole_tiles) % parts : 0;
-  w.n0 = (tile_id % tiles_n) * PN;
-  w.m0 = (tile_id / tiles_n) * PM;
+  int tm, tn;
+  tile_coords(tile_id, tiles_m, tiles_n, band, &tm, &tn);
+  w.n0 = tn * PN;
+  w.m0 = tm * PM;
   w.kb_begin = w.split ? piece_start(w.piece, parts, total_kb, CHUNK_KB) : 0;
   w.num_kb = (w.split ? piece_start(w.piece + 1, parts, total_kb, CHUNK_KB) : total_kb) - w.kb_begin;
   return w;
@@ -129,7 +152,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     gemm_x3_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_lo,
                         const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_b_lo,
                         float *__restrict__ C, long long ldc, int M, int N, int K,
-                        const float *__restrict__ bias, int accumulate, int tiles_n, int whole_tiles,
+                        const float *__restrict__ bias, int accumulate, int tiles_n, int band, int whole_tiles,
                         int parts, int total_items, const float *__restrict__ scale_a,
                         const float *__restrict__ scale_b, int *status, const unsigned *guard_a,
                         const unsigned *guard_b, unsigned mask_a, unsigned mask_b,
@@ -163,6 +186,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
   const uint32_t rank = cluster_rank();  // 0: the CTA that issues the MMAs
   const int pair = blockIdx.x / 2, pairs = gridDim.x / 2;
   const int total_kb = (K + PBK - 1) / PBK;
+  const int tiles_m = (M + PM - 1) / PM;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES),
                  acc_full0 = smem_u32(bars + 2 * STAGES), acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
 
@@ -200,7 +224,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
       unsigned it = 0;
       bool ok = true;
       for (int item = pair; item < total_items && ok; item += pairs) {
-        const PairItem w = pair_item<CHUNK_KB>(item, tiles_n, whole_tiles, parts, total_kb);
+        const PairItem w = pair_item<CHUNK_KB>(item, tiles_m, tiles_n, band, whole_tiles, parts, total_kb);
         const int am0 = w.m0 + (int)rank * BM, bn0 = w.n0 + (int)rank * HALF_N;
         for (int kb = 0; kb < w.num_kb; ++kb, ++it) {
           const unsigned s = it % STAGES;
@@ -245,7 +269,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
       bool ok = true;
       unsigned it = 0, cc = 0;
       for (int item = pair; item < total_items && ok; item += pairs) {
-        const PairItem w = pair_item<CHUNK_KB>(item, tiles_n, whole_tiles, parts, total_kb);
+        const PairItem w = pair_item<CHUNK_KB>(item, tiles_m, tiles_n, band, whole_tiles, parts, total_kb);
         int kb = 0;
         while (kb < w.num_kb && ok) {
           const unsigned buf = cc & 1, use = cc >> 1;
@@ -296,7 +320,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
     bool ok = true;
     unsigned cc = 0;
     for (int item = pair; item < total_items && ok; item += pairs) {
-      const PairItem w = pair_item<CHUNK_KB>(item, tiles_n, whole_tiles, parts, total_kb);
+      const PairItem w = pair_item<CHUNK_KB>(item, tiles_m, tiles_n, band, whole_tiles, parts, total_kb);
       const int num_chunks = (w.num_kb + CHUNK_KB - 1) / CHUNK_KB;
 #pragma unroll
       for (int j = 0; j < HALF; ++j) acc[j] = 0.f;
@@ -461,13 +485,27 @@ dlb_status launch_pair(dlb_ctx *ctx, const GemmOperand &A, const GemmOperand &B,
   }
   const int split_tiles = parts > 1 ? rest : 0;
   const int whole_tiles = tiles - split_tiles;
+  static const int band = getenv("DLB_GEMM_BAND") ? atoi(getenv("DLB_GEMM_BAND")) : 8;
+  const int tiles_m = ceil_div(M, PM);
   if (split_tiles) {
-    const int first_row = (whole_tiles / tiles_n) * PM;
-    DLB_CUDA(cudaMemset2DAsync(C + (long long)first_row * ldc, (size_t)ldc * sizeof(float), 0,
-                               (size_t)N * sizeof(float), (size_t)(M - first_row), ctx->stream));
+    // The cut tiles are the last of the order: a rectangle that holds them all
+    // is cleared (whole tiles inside it store over the zeros).
+    int tm, tn;
+    tile_coords(whole_tiles, tiles_m, tiles_n, band, &tm, &tn);
+    int first_row, first_col;
+    if (band <= 0) {
+      first_row = tm * PM;
+      first_col = 0;
+    } else {
+      first_row = (tm / band) * band * PM;  // the band the first cut tile lies in
+      // Cut tiles that reach into the bands below start those at column 0.
+      first_col = (tm / band + 1) * band >= tiles_m ? tn * PN : 0;
+    }
+    DLB_CUDA(cudaMemset2DAsync(C + (long long)first_row * ldc + first_col, (size_t)ldc * sizeof(float), 0,
+                               (size_t)(N - first_col) * sizeof(float), (size_t)(M - first_row), ctx->stream));
   }
   const int items = whole_tiles + parts * split_tiles;
-  DLB_LAUNCH_KERNEL(ctx, kernel, 2 * min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, whole_tiles, parts, items, A.scale, B.scale, ctx->d_status, A.guard, B.guard, A.guard_mask, B.guard_mask, A.line_inv, SimtOperands{A.ptr, A.fp32_stride_mn ? A.fp32_stride_mn : A.stride_mn, A.fp32_stride_k ? A.fp32_stride_k : A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr, FUSED ? *ep.fused : FusedEpilogue{});
+  DLB_LAUNCH_KERNEL(ctx, kernel, 2 * min(items, lanes), NUM_THREADS, P::TOTAL, ta, tal, tb, tbl, C, ldc, M, N, K, ep.bias, ep.accumulate, tiles_n, band, whole_tiles, parts, items, A.scale, B.scale, ctx->d_status, A.guard, B.guard, A.guard_mask, B.guard_mask, A.line_inv, SimtOperands{A.ptr, A.fp32_stride_mn ? A.fp32_stride_mn : A.stride_mn, A.fp32_stride_k ? A.fp32_stride_k : A.stride_k, B.ptr, B.stride_mn, B.stride_k}, ctx->d_guard ? ctx->d_guard + 1 : nullptr, FUSED ? *ep.fused : FusedEpilogue{});
   DLB_LAUNCHED(ctx);
   return DLB_OK;
 }
