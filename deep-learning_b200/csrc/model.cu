@@ -15,6 +15,7 @@
 #include <math.h>
 #include <string.h>
 
+#include <atomic>
 #include <random>
 #include <string>
 #include <thread>
@@ -968,10 +969,61 @@ dlb_status forward_layers(dlb_model *m, size_t rows) {
   return DLB_OK;
 }
 
+}  // namespace
+
+HostWorkers::HostWorkers(size_t threads) {
+  for (size_t i = 0; i < threads; ++i) threads_.emplace_back([this] { loop(); });
+}
+
+HostWorkers::~HostWorkers() {
+  {
+    std::lock_guard<std::mutex> lock(mu_);
+    stop_ = true;
+  }
+  work_.notify_all();
+  for (std::thread &t : threads_) t.join();
+}
+
+void HostWorkers::loop() {
+  std::unique_lock<std::mutex> lock(mu_);
+  for (;;) {
+    work_.wait(lock, [this] { return stop_ || (fn_ && next_ < parts_); });
+    if (stop_) return;
+    const size_t part = next_++;
+    const std::function<void(size_t)> *fn = fn_;
+    lock.unlock();
+    (*fn)(part);
+    lock.lock();
+    if (++finished_ == parts_) done_.notify_all();
+  }
+}
+
+void HostWorkers::run(size_t parts, const std::function<void(size_t)> &fn) {
+  if (parts == 0) return;
+  std::unique_lock<std::mutex> lock(mu_);
+  fn_ = &fn;
+  parts_ = parts;
+  next_ = finished_ = 0;
+  work_.notify_all();
+  // The caller takes parts as well.
+  while (next_ < parts_) {
+    const size_t part = next_++;
+    lock.unlock();
+    fn(part);
+    lock.lock();
+    ++finished_;
+  }
+  done_.wait(lock, [this] { return finished_ == parts_; });
+  fn_ = nullptr;
+}
+
+namespace {
+
 // Host rows (the reference's array of row pointers, pageable memory) into a
 // device tensor: gathered into a page-locked staging buffer by a few host
-// threads, piece by piece, each piece's copy to the device running while the
-// next one is gathered.  The copies run on the copy stream, so that the
+// threads that the model keeps, piece by piece; the thread that completes a
+// piece starts its copy to the device, which runs while the next pieces are
+// gathered.  The copies run on the copy stream, so that the
 // targets of a step cross while its forward pass computes; the compute stream
 // waits for them where it needs them (rows_staged).  which: 0 inputs, 1 targets.
 dlb_status stage_rows(dlb_model *m, int which, float **stage, size_t *stage_elems, size_t rows, size_t width,
@@ -995,25 +1047,43 @@ dlb_status stage_rows(dlb_model *m, int which, float **stage, size_t *stage_elem
   // The kernels that read the device tensor last must be past it.
   if (m->rows_in_flight[which]) DLB_CUDA(cudaStreamWaitEvent(m->copy_stream, m->rows_consumed[which], 0));
   else DLB_CUDA(cudaStreamSynchronize(m->ctx->stream));
-  constexpr size_t PIECE_BYTES = 4u << 20;
+  constexpr size_t PIECE_BYTES = 2u << 20;
   const size_t piece_rows = std::max<size_t>(1, PIECE_BYTES / (width * sizeof(float)));
-  const unsigned hw = std::thread::hardware_concurrency();
-  const size_t workers = need * sizeof(float) < (1u << 20) ? 1 : std::min<size_t>(8, hw ? hw : 1);
-  for (size_t r0 = 0; r0 < rows; r0 += piece_rows) {
-    const size_t r1 = std::min(rows, r0 + piece_rows);
-    auto gather = [&](size_t a, size_t b) {
-      for (size_t r = a; r < b; ++r) memcpy(*stage + r * width, row_ptrs[r], width * sizeof(float));
-    };
-    if (workers <= 1) {
-      gather(r0, r1);
-    } else {
-      std::vector<std::thread> pool;
-      const size_t per = (r1 - r0 + workers - 1) / workers;
-      for (size_t a = r0; a < r1; a += per) pool.emplace_back(gather, a, std::min(r1, a + per));
-      for (std::thread &t : pool) t.join();
+  const size_t pieces = (rows + piece_rows - 1) / piece_rows;
+  if (need * sizeof(float) < (1u << 20)) {
+    for (size_t r = 0; r < rows; ++r) memcpy(*stage + r * width, row_ptrs[r], width * sizeof(float));
+    DLB_CUDA(cudaMemcpyAsync(dev, *stage, need * sizeof(float), cudaMemcpyHostToDevice, m->copy_stream));
+  } else {
+    if (!m->workers) {
+      const unsigned hw = std::thread::hardware_concurrency();
+      m->workers = new HostWorkers(std::min<size_t>(8, hw ? hw : 1) - 1);
     }
-    DLB_CUDA(cudaMemcpyAsync(dev + r0 * width, *stage + r0 * width, (r1 - r0) * width * sizeof(float),
-                             cudaMemcpyHostToDevice, m->copy_stream));
+    // Every piece is split among `split` threads; the one that finishes a piece
+    // last sends it.
+    const size_t split = std::min<size_t>(m->workers->size(), 4);
+    std::vector<std::atomic<int>> left(pieces);
+    for (auto &a : left) a.store((int)split);
+    std::atomic<int> failed{0};
+    float *staging = *stage;
+    const int device = m->ctx->device;
+    cudaStream_t copy_stream = m->copy_stream;
+    m->workers->run(pieces * split, [&](size_t part) {
+      const size_t piece = part / split, share = part % split;
+      const size_t r0 = piece * piece_rows, r1 = std::min(rows, r0 + piece_rows);
+      const size_t per = (r1 - r0 + split - 1) / split;
+      const size_t a = std::min(r1, r0 + share * per), b = std::min(r1, a + per);
+      for (size_t r = a; r < b; ++r) memcpy(staging + r * width, row_ptrs[r], width * sizeof(float));
+      if (left[piece].fetch_sub(1) == 1) {
+        if (cudaSetDevice(device) != cudaSuccess ||
+            cudaMemcpyAsync(dev + r0 * width, staging + r0 * width, (r1 - r0) * width * sizeof(float),
+                            cudaMemcpyHostToDevice, copy_stream) != cudaSuccess)
+          failed.store(1);
+      }
+    });
+    if (failed.load()) {
+      set_error("stage_rows: copy to the device failed: %s", cudaGetErrorString(cudaGetLastError()));
+      return DLB_ERR_CUDA;
+    }
   }
   DLB_CUDA(cudaEventRecord(m->rows_copied[which], m->copy_stream));
   DLB_CUDA(cudaStreamWaitEvent(m->ctx->stream, m->rows_copied[which], 0));
@@ -1107,6 +1177,7 @@ dlb_status dlb_model_destroy(dlb_model *m) {
   if (m->accu_sum) dlb_free(m->ctx, m->accu_sum);
   if (m->ones) dlb_free(m->ctx, m->ones);
   if (m->zeros) dlb_free(m->ctx, m->zeros);
+  delete m->workers;
   if (m->copy_stream) {
     cudaStreamSynchronize(m->copy_stream);
     cudaStreamDestroy(m->copy_stream);

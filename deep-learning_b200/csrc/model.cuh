@@ -3,12 +3,37 @@
 // reference's text checkpoint format).
 #pragma once
 
+#include <condition_variable>
+#include <functional>
+#include <mutex>
 #include <random>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "common.cuh"
 
+
+// A few host threads that stay around for the row gathers of a model (creating
+// threads per call cost more than the gather of a 16 MB batch).  run(parts, fn)
+// calls fn(0 .. parts - 1), each once, on the workers and the calling thread,
+// and returns when all are done.
+class HostWorkers {
+ public:
+  explicit HostWorkers(size_t threads);
+  ~HostWorkers();
+  void run(size_t parts, const std::function<void(size_t)> &fn);
+  size_t size() const { return threads_.size() + 1; }
+
+ private:
+  void loop();
+  std::vector<std::thread> threads_;
+  std::mutex mu_;
+  std::condition_variable work_, done_;
+  const std::function<void(size_t)> *fn_ = nullptr;
+  size_t parts_ = 0, next_ = 0, finished_ = 0;
+  bool stop_ = false;
+};
 
 struct LayerRT {
   int type = 0;
@@ -137,6 +162,7 @@ struct dlb_model {
     bool in_use = false;  // `consumed` has been recorded at least once
   } ahead[2];
   cudaStream_t copy_stream = nullptr;
+  HostWorkers *workers = nullptr;   // row gathers of forward_pass / compute_error / compute_loss
   size_t ahead_head = 0, ahead_tail = 0;  // staged so far, consumed so far
   double *loss_sum = nullptr;
   // The loss of a one-call step leaves the device asynchronously: a device copy of the
