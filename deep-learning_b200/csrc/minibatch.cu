@@ -41,7 +41,7 @@ namespace {
 
 size_t rows_of(const dlb_minibatch *mb, size_t k) { return k + 1 != mb->n_batch ? mb->per_batch : mb->last_batch; }
 
-// Rows of batch k into staging slot `slot`, by a few host threads.
+// Rows of batch k into staging slot `slot`, by the host threads the model keeps.
 void gather(dlb_minibatch *mb, size_t k, int slot) {
   const size_t first = k * mb->per_batch, rows = rows_of(mb, k);
   auto part = [&](size_t a, size_t b) {
@@ -52,16 +52,18 @@ void gather(dlb_minibatch *mb, size_t k, int slot) {
     }
   };
   const size_t bytes = rows * (mb->width_x + mb->width_y) * sizeof(float);
-  const unsigned hw = std::thread::hardware_concurrency();
-  const size_t workers = bytes < (1u << 20) ? 1 : std::min<size_t>(8, hw ? hw : 1);
-  if (workers <= 1) {
+  if (bytes < (1u << 20)) {
     part(0, rows);
     return;
   }
-  std::vector<std::thread> pool;
-  const size_t per = (rows + workers - 1) / workers;
-  for (size_t a = 0; a < rows; a += per) pool.emplace_back(part, a, std::min(rows, a + per));
-  for (std::thread &t : pool) t.join();
+  dlb_model *m = mb->model;
+  if (!m->workers) {
+    const unsigned hw = std::thread::hardware_concurrency();
+    m->workers = new HostWorkers(std::min<size_t>(8, hw ? hw : 1) - 1);
+  }
+  const size_t parts = m->workers->size() * 4;
+  const size_t per = (rows + parts - 1) / parts;
+  m->workers->run(parts, [&](size_t i) { part(std::min(rows, i * per), std::min(rows, (i + 1) * per)); });
 }
 
 }  // namespace

@@ -288,6 +288,28 @@ def test_training_accuracy_against_the_compiled_reference(gpu_ctx, case):
     assert gpu.get_accu(B) == 0.0
 
 
+def test_minibatch_epoch_with_batches_gathered_by_the_kept_host_threads(gpu_ctx):
+    """Batches above 1 MB are gathered by the model's host threads: the same
+    weights, bit for bit, as the batches passed one by one."""
+    cfg = configs.deep_brn_mlp(1024, 256, 1, 512, 200)
+    N = 660
+    X, Y = configs.synthetic_batch(cfg, batch=N)
+    a = util.build(dlb200.Model(gpu_ctx), cfg, seed=4)
+    b = util.build(dlb200.Model(gpu_ctx), cfg, seed=4)
+    mb = dlb200.MiniBatch(b, X, Y, 200, use_shuffle=True, seed=11)
+    assert (mb.n_batch, mb.last_batch) == (3, 200 + int((N / 200 - 3) * 200))
+    a.set_training_size(N)
+    for epoch in range(2):
+        got = mb.train()                 # shuffles, then trains
+        order = mb.order()
+        bounds = ((0, 200), (200, 400), (400, 400 + mb.last_batch))
+        want = [a.train_step(hi - lo, X[order[lo:hi]], Y[order[lo:hi]]) for lo, hi in bounds]
+        a.set_hparam("epoch_time_step", a.get_hparam("epoch_time_step") + 1.0)
+        np.testing.assert_allclose(got, np.mean(want), rtol=1e-12)
+        assert np.array_equal(a.get_array("parameters"), b.get_array("parameters"))
+    assert gpu_ctx.sync() == 0
+
+
 def test_unsupported_configurations_are_refused(gpu_ctx):
     m = dlb200.Model(gpu_ctx)
     m.compile([3, 3, 3], [8, 8, 4])
